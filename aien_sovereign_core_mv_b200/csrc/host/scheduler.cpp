@@ -1,0 +1,369 @@
+#include "scheduler.h"
+
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <algorithm>
+#include <climits>
+#include <stdexcept>
+
+namespace aien {
+
+namespace {
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+}  // namespace
+
+Scheduler::Scheduler(SchedulerConfig cfg, CacheManager* cache) : cfg_(cfg), cache_(cache) {
+    if (!cache_) throw std::invalid_argument("scheduler needs a cache manager");
+    if (cfg_.max_batch_size <= 0 || cfg_.max_batch_tokens <= 0 || cfg_.max_prefill_tokens <= 0 ||
+        cfg_.prefill_chunk_size <= 0 || cfg_.watermark_blocks < 0)
+        throw std::invalid_argument("scheduler limits must be positive");
+}
+
+void Scheduler::submit(int64_t id, std::vector<int32_t> prompt, int max_tokens, std::vector<int32_t> stop_ids, int priority) {
+    if (seqs_.count(id) && seqs_[id].state != SeqState::Finished)
+        throw std::invalid_argument("request " + std::to_string(id) + " is already live");
+    if (prompt.empty()) throw std::invalid_argument("request " + std::to_string(id) + " has an empty prompt");
+    if (max_tokens <= 0) throw std::invalid_argument("max_tokens must be positive");
+    SeqRecord s;
+    s.id = id;
+    s.prompt = std::move(prompt);
+    s.max_tokens = max_tokens;
+    s.stop_ids = std::move(stop_ids);
+    s.priority = priority;
+    s.arrival = arrivals_++;
+    seqs_[id] = std::move(s);
+    waiting_.push_back(id);
+}
+
+bool Scheduler::cancel(int64_t id) {
+    auto it = seqs_.find(id);
+    if (it == seqs_.end() || it->second.state == SeqState::Finished) return false;
+    finish(it->second, FinishReason::Cancelled, "");
+    return true;
+}
+
+int Scheduler::min_free_pages() const {
+    int m = INT_MAX;
+    for (int g = 0; g < cache_->num_groups(); ++g)
+        if (cache_->group(g).kind != GroupKind::State) m = std::min(m, cache_->free_count(g));
+    return m;
+}
+
+int Scheduler::total_pages_for(int g, int tokens, int portion) const {
+    const int ps = cache_->page_size();
+    const GroupSpec& spec = cache_->group(g);
+    int full = ceil_div(tokens, ps);
+    if (spec.kind == GroupKind::Window) full = std::min(full, ceil_div(spec.window + portion, ps) + 1);
+    return full;
+}
+
+long long Scheduler::outstanding_reservation(int g) const {
+    long long total = 0;
+    for (int64_t id : running_) {
+        const SeqRecord& s = seqs_.at(id);
+        if (!cache_->has(id)) continue;
+        int held = 0;
+        for (int p : cache_->table(id, g)) held += p >= 0 ? 1 : 0;
+        const int want = total_pages_for(g, s.input_len() + 1, cfg_.prefill_chunk_size);
+        if (want > held) total += want - held;
+    }
+    return total;
+}
+
+int64_t Scheduler::pick_victim(const std::vector<int64_t>& among) const {
+    int64_t best = -1;
+    for (int64_t id : among) {
+        if (best < 0) { best = id; continue; }
+        const SeqRecord& a = seqs_.at(id);
+        const SeqRecord& b = seqs_.at(best);
+        if (a.priority < b.priority || (a.priority == b.priority && a.arrival > b.arrival)) best = id;
+    }
+    return best;
+}
+
+void Scheduler::preempt(int64_t id, StepPlan& plan) {
+    SeqRecord& s = seqs_.at(id);
+    if (cache_->has(id)) cache_->free_request(id);
+    s.computed = 0;
+    s.state = SeqState::Preempted;
+    ++s.preemptions;
+    running_.erase(std::remove(running_.begin(), running_.end(), id), running_.end());
+    preempted_.push_back(id);
+    plan.preempted.push_back(id);
+    ++metrics_.preemptions;
+}
+
+void Scheduler::finish(SeqRecord& s, FinishReason why, const std::string& msg) {
+    if (cache_->has(s.id)) cache_->free_request(s.id);
+    running_.erase(std::remove(running_.begin(), running_.end(), s.id), running_.end());
+    waiting_.erase(std::remove(waiting_.begin(), waiting_.end(), s.id), waiting_.end());
+    preempted_.erase(std::remove(preempted_.begin(), preempted_.end(), s.id), preempted_.end());
+    s.state = SeqState::Finished;
+    s.reason = why;
+    s.message = msg;
+    FinishEvent e;
+    e.id = s.id;
+    e.reason = why;
+    e.generated = s.generated;
+    e.message = msg;
+    finished_.push_back(std::move(e));
+    ++metrics_.finished;
+}
+
+StepPlan Scheduler::plan() {
+    if (awaiting_commit_) throw std::logic_error("plan() called again before commit()");
+    StepPlan p;
+    p.step_id = step_counter_++;
+    bool preempted_this_step = false;
+
+    // 1. watermark: keep headroom for the running requests' next pages
+    if (running_.size() > 1 && min_free_pages() < cfg_.watermark_blocks) {
+        preempt(pick_victim(running_), p);
+        preempted_this_step = true;
+    }
+
+    // 2. running requests in id order: one decode token, or the next portion of the input
+    struct Cand { int64_t id; int n; };
+    std::vector<Cand> cands;
+    int seqs = 0, tokens = 0, prefill = 0;
+    for (int64_t id : running_) {
+        if (seqs >= cfg_.max_batch_size || tokens >= cfg_.max_batch_tokens) break;
+        const SeqRecord& s = seqs_.at(id);
+        const int pending = s.input_len() - s.computed;
+        int n = 1;
+        if (pending > 1) {
+            const int budget = std::min(cfg_.max_prefill_tokens - prefill, cfg_.max_batch_tokens - tokens);
+            n = cfg_.chunk_prefill ? std::min({pending, cfg_.prefill_chunk_size, budget}) : (pending <= budget ? pending : 0);
+            if (n <= 0) continue;
+            prefill += n;
+        }
+        cands.push_back({id, n});
+        tokens += n;
+        ++seqs;
+    }
+
+    // 3. take the pages; when they run out, preempt the lowest-priority running request and retry
+    while (!cands.empty()) {
+        std::vector<std::pair<int64_t, int>> batch;
+        for (const Cand& c : cands) batch.emplace_back(c.id, c.n);
+        try {
+            p.copies = cache_->append(batch);
+            break;
+        } catch (const CacheExhausted& e) {
+            if (running_.size() <= 1) {
+                // alone and still too large: it can never run
+                SeqRecord& s = seqs_.at(cands.front().id);
+                finish(s, FinishReason::Aborted, std::string(e.what()) + "; the request alone does not fit the pool");
+                cands.clear();
+                break;
+            }
+            const int64_t victim = pick_victim(running_);
+            for (auto it = cands.begin(); it != cands.end(); ++it)
+                if (it->id == victim) { tokens -= it->n; --seqs; cands.erase(it); break; }
+            preempt(victim, p);
+            preempted_this_step = true;
+        }
+    }
+    for (const Cand& c : cands) {
+        const SeqRecord& s = seqs_.at(c.id);
+        StepEntry e;
+        e.id = c.id;
+        e.start = s.computed;
+        e.tokens.reserve(c.n);
+        for (int i = 0; i < c.n; ++i) e.tokens.push_back(s.input_at(s.computed + i));
+        e.wants_logits = s.computed + c.n == s.input_len();
+        p.entries.push_back(std::move(e));
+    }
+
+    // 4. admission: preempted requests first, then the waiting queue, first come first served
+    auto admit_from = [&](std::deque<int64_t>& q, bool was_preempted) -> bool {
+        while (!q.empty()) {
+            if (seqs >= cfg_.max_batch_size || tokens >= cfg_.max_batch_tokens) return false;
+            const int64_t id = q.front();
+            SeqRecord& s = seqs_.at(id);
+            const int pending = s.input_len();
+            const int budget = std::min(cfg_.max_prefill_tokens - prefill, cfg_.max_batch_tokens - tokens);
+            const int n = cfg_.chunk_prefill ? std::min({pending, cfg_.prefill_chunk_size, budget})
+                                             : (pending <= budget ? pending : 0);
+            if (n <= 0) {
+                if (!cfg_.chunk_prefill && pending > std::min(cfg_.max_prefill_tokens, cfg_.max_batch_tokens)) {
+                    q.pop_front();
+                    finish(s, FinishReason::Aborted, "prompt of " + std::to_string(pending) +
+                           " tokens exceeds the per-step budget and chunk_prefill is off");
+                    continue;
+                }
+                return false;
+            }
+            bool ok = cache_->num_requests() < cache_->max_requests();
+            std::string never;
+            const bool idle = running_.empty();
+            for (int g = 0; g < cache_->num_groups(); ++g) {
+                const GroupSpec& spec = cache_->group(g);
+                if (spec.kind == GroupKind::State) {
+                    if (cache_->free_count(g) < 1) ok = false;
+                    continue;
+                }
+                const int need = total_pages_for(g, pending + 1, n);
+                if (need > spec.capacity) {
+                    never = std::string(kExhaustedPrefix) + " request needs " + std::to_string(need) + " pages of group " +
+                            std::to_string(g) + ", the pool has " + std::to_string(spec.capacity);
+                    break;
+                }
+                const long long avail = static_cast<long long>(cache_->free_count(g)) - outstanding_reservation(g) -
+                                        ((was_preempted && !idle) ? cfg_.watermark_blocks : 0);
+                if (need > avail) ok = false;
+            }
+            if (!never.empty()) {
+                q.pop_front();
+                finish(s, FinishReason::Aborted, never);
+                continue;
+            }
+            if (!ok) return false;
+            q.pop_front();
+            cache_->add_request(id);
+            std::vector<PageCopy> cp = cache_->append({{id, n}});
+            p.copies.insert(p.copies.end(), cp.begin(), cp.end());
+            s.state = SeqState::Running;
+            s.computed = 0;
+            running_.insert(std::upper_bound(running_.begin(), running_.end(), id), id);
+            StepEntry e;
+            e.id = id;
+            e.start = 0;
+            e.tokens.reserve(n);
+            for (int i = 0; i < n; ++i) e.tokens.push_back(s.input_at(i));
+            e.wants_logits = n == pending;
+            p.entries.push_back(std::move(e));
+            tokens += n;
+            prefill += n;
+            ++seqs;
+            ++metrics_.admitted;
+        }
+        return true;
+    };
+    if (!preempted_this_step) {
+        if (admit_from(preempted_, true)) admit_from(waiting_, false);
+    }
+
+    p.num_tokens = tokens;
+    p.prefill_tokens = prefill;
+    if (!p.entries.empty()) {
+        awaiting_commit_ = true;
+        ++metrics_.steps;
+        metrics_.tokens_scheduled += tokens;
+        metrics_.prefill_tokens += prefill;
+        metrics_.decode_tokens += tokens - prefill;
+    }
+    last_ = p;
+    return p;
+}
+
+void Scheduler::commit(const std::vector<int32_t>& sampled) {
+    if (!awaiting_commit_) throw std::logic_error("commit() without a planned step");
+    size_t want = 0;
+    for (const StepEntry& e : last_.entries) want += e.wants_logits ? 1 : 0;
+    if (sampled.size() != want)
+        throw std::invalid_argument("commit: " + std::to_string(want) + " sampled tokens expected, got " + std::to_string(sampled.size()));
+    awaiting_commit_ = false;
+    size_t k = 0;
+    for (const StepEntry& e : last_.entries) {
+        const int32_t tok = e.wants_logits ? sampled[k++] : 0;
+        auto it = seqs_.find(e.id);
+        if (it == seqs_.end() || it->second.state != SeqState::Running) continue;   // cancelled meanwhile
+        SeqRecord& s = it->second;
+        s.computed += static_cast<int>(e.tokens.size());
+        if (!e.wants_logits) continue;
+        if (std::find(s.stop_ids.begin(), s.stop_ids.end(), tok) != s.stop_ids.end()) {
+            finish(s, FinishReason::StopToken, "");
+            continue;
+        }
+        s.generated.push_back(tok);
+        if (static_cast<int>(s.generated.size()) >= s.max_tokens) {
+            finish(s, FinishReason::LengthLimit, "");
+        } else if (cfg_.max_context > 0 && s.input_len() >= cfg_.max_context) {
+            finish(s, FinishReason::LengthLimit, "context limit");
+        }
+    }
+}
+
+std::vector<FinishEvent> Scheduler::take_finished() {
+    std::vector<FinishEvent> out;
+    out.swap(finished_);
+    return out;
+}
+
+void bind_scheduler(pybind11::module_& m) {
+    namespace py = pybind11;
+    py::enum_<FinishReason>(m, "FinishReason")
+        .value("NONE", FinishReason::None)
+        .value("StopToken", FinishReason::StopToken)
+        .value("LengthLimit", FinishReason::LengthLimit)
+        .value("Cancelled", FinishReason::Cancelled)
+        .value("Aborted", FinishReason::Aborted);
+    py::enum_<SeqState>(m, "SeqState")
+        .value("Waiting", SeqState::Waiting)
+        .value("Running", SeqState::Running)
+        .value("Preempted", SeqState::Preempted)
+        .value("Finished", SeqState::Finished);
+    py::class_<SchedulerConfig>(m, "SchedulerConfig")
+        .def(py::init<>())
+        .def_readwrite("max_batch_size", &SchedulerConfig::max_batch_size)
+        .def_readwrite("max_batch_tokens", &SchedulerConfig::max_batch_tokens)
+        .def_readwrite("max_prefill_tokens", &SchedulerConfig::max_prefill_tokens)
+        .def_readwrite("prefill_chunk_size", &SchedulerConfig::prefill_chunk_size)
+        .def_readwrite("chunk_prefill", &SchedulerConfig::chunk_prefill)
+        .def_readwrite("watermark_blocks", &SchedulerConfig::watermark_blocks)
+        .def_readwrite("max_context", &SchedulerConfig::max_context);
+    py::class_<StepEntry>(m, "StepEntry")
+        .def_readonly("id", &StepEntry::id)
+        .def_readonly("tokens", &StepEntry::tokens)
+        .def_readonly("start", &StepEntry::start)
+        .def_readonly("wants_logits", &StepEntry::wants_logits);
+    py::class_<StepPlan>(m, "StepPlan")
+        .def_readonly("step_id", &StepPlan::step_id)
+        .def_readonly("entries", &StepPlan::entries)
+        .def_readonly("preempted", &StepPlan::preempted)
+        .def_readonly("num_tokens", &StepPlan::num_tokens)
+        .def_readonly("prefill_tokens", &StepPlan::prefill_tokens)
+        .def_property_readonly("copies", [](const StepPlan& p) {
+            std::vector<std::tuple<int, int, int>> out;
+            for (const auto& c : p.copies) out.emplace_back(c.group, c.src, c.dst);
+            return out;
+        });
+    py::class_<FinishEvent>(m, "FinishEvent")
+        .def_readonly("id", &FinishEvent::id)
+        .def_readonly("reason", &FinishEvent::reason)
+        .def_readonly("generated", &FinishEvent::generated)
+        .def_readonly("message", &FinishEvent::message);
+    py::class_<SeqRecord>(m, "SeqRecord")
+        .def_readonly("id", &SeqRecord::id)
+        .def_readonly("prompt", &SeqRecord::prompt)
+        .def_readonly("generated", &SeqRecord::generated)
+        .def_readonly("computed", &SeqRecord::computed)
+        .def_readonly("state", &SeqRecord::state)
+        .def_readonly("reason", &SeqRecord::reason)
+        .def_readonly("preemptions", &SeqRecord::preemptions)
+        .def_readonly("priority", &SeqRecord::priority);
+    py::class_<Scheduler>(m, "Scheduler")
+        .def(py::init<SchedulerConfig, CacheManager*>(), py::arg("config"), py::arg("cache"), py::keep_alive<1, 3>())
+        .def("submit", &Scheduler::submit, py::arg("id"), py::arg("prompt"), py::arg("max_tokens"),
+             py::arg("stop_ids") = std::vector<int32_t>{}, py::arg("priority") = 0)
+        .def("cancel", &Scheduler::cancel)
+        .def("has_work", &Scheduler::has_work)
+        .def_property_readonly("num_running", &Scheduler::num_running)
+        .def_property_readonly("num_waiting", &Scheduler::num_waiting)
+        .def("plan", &Scheduler::plan)
+        .def("commit", &Scheduler::commit)
+        .def("take_finished", &Scheduler::take_finished)
+        .def("record", &Scheduler::record, py::return_value_policy::copy)
+        .def("metrics", [](const Scheduler& s) {
+            const SchedulerMetrics& x = s.metrics();
+            py::dict d;
+            d["steps"] = x.steps; d["tokens_scheduled"] = x.tokens_scheduled; d["prefill_tokens"] = x.prefill_tokens;
+            d["decode_tokens"] = x.decode_tokens; d["preemptions"] = x.preemptions; d["finished"] = x.finished;
+            d["admitted"] = x.admitted;
+            return d;
+        });
+}
+
+}  // namespace aien

@@ -1,0 +1,86 @@
+// Shared helpers for the engine's CUDA kernels (sm_100a).
+//
+// Conventions used by every launcher in this directory:
+//   * exported with C linkage, named aien_<op>; returns 0 on success, a cudaError_t value if
+//     the launch failed, or a negative AIEN_E_* code when an argument is refused;
+//   * takes raw device pointers, sizes, a dtype code per tensor family and a cudaStream_t;
+//   * never allocates; scratch comes from the caller.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define AIEN_DT_F32 0
+#define AIEN_DT_BF16 1
+
+#define AIEN_E_DTYPE (-2)      // unsupported dtype combination
+#define AIEN_E_SHAPE (-3)      // a size the kernel refuses
+#define AIEN_E_ALIGN (-4)      // pointer or stride not aligned as required
+#define AIEN_E_STATE (-5)      // library state (tensor map encode, attribute set) failed
+
+#define AIEN_API extern "C" __attribute__((visibility("default")))
+
+namespace aien {
+
+__device__ __forceinline__ float to_f(float v) { return v; }
+__device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Reads element i of a vector whose dtype is only known at run time (norm weights may be
+// stored in 32 bits beside a bfloat16 model).
+__device__ __forceinline__ float load_dyn(const void* p, int dt, size_t i) {
+    return dt == AIEN_DT_F32 ? reinterpret_cast<const float*>(p)[i]
+                             : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum with a fixed combination order (warp tree, then warps in index order), so the
+// result for a row does not depend on what else is in the grid.  `red` holds >= 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float total = 0.f;
+    for (int w = 0; w < nwarps; ++w) total += red[w];
+    return total;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float total = red[0];
+    for (int w = 1; w < nwarps; ++w) total = fmaxf(total, red[w]);
+    return total;
+}
+
+inline int launch_status() {
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+}  // namespace aien
+
+// Dispatch on one dtype code; T is bound inside BODY.
+#define AIEN_DISPATCH_DTYPE(code, T, BODY)                     \
+    do {                                                       \
+        if ((code) == AIEN_DT_F32) { using T = float; BODY; }  \
+        else if ((code) == AIEN_DT_BF16) { using T = __nv_bfloat16; BODY; } \
+        else return AIEN_E_DTYPE;                              \
+    } while (0)

@@ -1,0 +1,227 @@
+// Row-wise kernels of the decoder: embedding gather, fused residual-add + RMSNorm, SwiGLU,
+// rotary table, fused per-head q/k RMSNorm + rotation + cache write, row gather.
+//
+// The residual stream is float32 in both engine precisions; norms and rotation are computed
+// in float32 (angles in float64, then rounded, exactly as the reference builds its table:
+// crates/aien-inference-abi/src/tensor.rs:150-163).
+#include "common.cuh"
+
+namespace aien {
+
+// ---------------------------------------------------------------- embedding
+template <typename TW>
+__global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
+                                    float* __restrict__ x, int H, int V) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* row = x + (size_t)t * H;
+    if (id < 0 || id >= V) {                      // refused on the host; never read out of range
+        for (int i = threadIdx.x; i < H; i += blockDim.x) row[i] = 0.f;
+        return;
+    }
+    const TW* src = table + (size_t)id * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) row[i] = to_f(src[i]);
+}
+
+// ---------------------------------------------------------------- residual add + RMSNorm
+// x[t] += delta[t] (if delta), then h[t] = x[t] * (1/sqrt(mean(x^2)+eps)) * w   (tensor.rs:94-110)
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta,
+                                   const void* __restrict__ w, int wdt, float eps,
+                                   TO* __restrict__ h, int H) {
+    __shared__ float red[32];
+    const size_t base = (size_t)blockIdx.x * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = x[base + i];
+        if (delta != nullptr) {
+            v += to_f(delta[base + i]);
+            x[base + i] = v;
+        }
+        ss += v * v;
+    }
+    const float total = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(total / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        h[base + i] = from_f<TO>(x[base + i] * scale * load_dyn(w, wdt, i));
+    }
+}
+
+// out[r] = x[rows[r]] + delta[rows[r]]   (float32 out; feeds the final norm of wanted rows only)
+template <typename TD>
+__global__ void gather_add_rows_kernel(const float* __restrict__ x, const TD* __restrict__ delta,
+                                       const int* __restrict__ rows, float* __restrict__ out, int H) {
+    const size_t src = (size_t)rows[blockIdx.x] * H, dst = (size_t)blockIdx.x * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = x[src + i];
+        if (delta != nullptr) v += to_f(delta[src + i]);
+        out[dst + i] = v;
+    }
+}
+
+// ---------------------------------------------------------------- SwiGLU
+// a = silu(g) * u, silu(g) = g / (1 + exp(-g))     (backend.rs:572-579); gu = [T, 2I], gate first
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; idx < total; idx += stride) {
+        const size_t t = idx / I, i = idx - t * I;
+        const float g = to_f(gu[t * 2 * I + i]);
+        const float u = to_f(gu[t * 2 * I + I + i]);
+        out[idx] = from_f<T>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+// ---------------------------------------------------------------- rotary table
+__global__ void rope_table_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
+                                  float* __restrict__ cos_t, float* __restrict__ sin_t, int T, int half) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= T * half) return;
+    const int t = idx / half, i = idx - t * half;
+    double s, c;
+    sincos((double)positions[t] * inv_freq[i], &s, &c);
+    cos_t[idx] = (float)c;
+    sin_t[idx] = (float)s;
+}
+
+// ---------------------------------------------------------------- q/k norm + rotation + cache write
+// One block per token; each warp takes heads in turn.  For a q or k head: optional RMSNorm over
+// the head (tensor.rs:114-121), then rotate_half pairing (i, i + rot/2) on the first `rot`
+// values (tensor.rs:165-188).  q is written back in place; k and v go to the cache slot of the
+// token, rounded once to the cache dtype (crates/aien-kv-cache/src/lib.rs:88-101).
+#define AIEN_MAX_HEAD_DIM 256
+template <typename TC, typename TKV>
+__global__ void qk_norm_rope_kv_write_kernel(
+    TC* __restrict__ q, long q_stride, int nq,
+    const TC* __restrict__ k, long k_stride, const TC* __restrict__ v, long v_stride, int nkv,
+    int hd, const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w, int wdt, float eps,
+    const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot,
+    const int* __restrict__ slot_map, TKV* __restrict__ k_cache, TKV* __restrict__ v_cache) {
+    __shared__ float buf[4][AIEN_MAX_HEAD_DIM];
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int half = rot >> 1;
+    const bool write_kv = (k != nullptr);
+    const int n_heads = nq + (write_kv ? 2 * nkv : 0);
+    const long slot = write_kv ? (long)slot_map[t] : -1;
+    float* hb = buf[warp];
+    for (int head = warp; head < n_heads; head += 4) {
+        const bool is_q = head < nq;
+        const bool is_k = !is_q && head < nq + nkv;
+        const int hh = is_q ? head : (is_k ? head - nq : head - nq - nkv);
+        const TC* src = is_q ? (q + (size_t)t * q_stride + (size_t)hh * hd)
+                             : (is_k ? (k + (size_t)t * k_stride + (size_t)hh * hd)
+                                     : (v + (size_t)t * v_stride + (size_t)hh * hd));
+        if (!is_q && slot < 0) continue;                       // token has no cache slot
+        float ss = 0.f;
+        for (int i = lane; i < hd; i += 32) {
+            const float val = to_f(src[i]);
+            hb[i] = val;
+            ss += val * val;
+        }
+        __syncwarp();
+        if (is_q || is_k) {
+            const void* nw = is_q ? q_norm_w : k_norm_w;
+            if (nw != nullptr) {
+                ss = warp_sum(ss);
+                const float scale = 1.0f / sqrtf(ss / (float)hd + eps);
+                for (int i = lane; i < hd; i += 32) hb[i] = hb[i] * scale * load_dyn(nw, wdt, i);
+                __syncwarp();
+            }
+            if (cos_t != nullptr) {
+                for (int i = lane; i < half; i += 32) {
+                    const float a = hb[i], b = hb[i + half];
+                    const float c = cos_t[(size_t)t * half + i], s = sin_t[(size_t)t * half + i];
+                    hb[i] = a * c - b * s;
+                    hb[i + half] = a * s + b * c;
+                }
+                __syncwarp();
+            }
+        }
+        if (is_q) {
+            TC* dst = q + (size_t)t * q_stride + (size_t)hh * hd;
+            for (int i = lane; i < hd; i += 32) dst[i] = from_f<TC>(hb[i]);
+        } else {
+            TKV* dst = (is_k ? k_cache : v_cache) + ((size_t)slot * nkv + hh) * hd;
+            for (int i = lane; i < hd; i += 32) dst[i] = from_f<TKV>(hb[i]);
+        }
+        __syncwarp();
+    }
+}
+
+// ---------------------------------------------------------------- dtype conversion (load time)
+template <typename TI, typename TO>
+__global__ void convert_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; idx < n; idx += stride) out[idx] = from_f<TO>(to_f(in[idx]));
+}
+
+static inline int row_threads(int H) { return H >= 2048 ? 512 : (H >= 512 ? 256 : 128); }
+
+}  // namespace aien
+
+using namespace aien;
+
+AIEN_API int aien_embed_gather(const void* table, int table_dt, const int* ids, float* x,
+                               int T, int H, int V, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    AIEN_DISPATCH_DTYPE(table_dt, TW, (embed_gather_kernel<TW><<<T, row_threads(H), 0, stream>>>(
+        (const TW*)table, ids, x, H, V)));
+    return launch_status();
+}
+
+AIEN_API int aien_add_rmsnorm(float* x, const void* delta, int delta_dt, const void* w, int w_dt,
+                              float eps, void* h, int h_dt, int T, int H, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const int th = row_threads(H);
+    AIEN_DISPATCH_DTYPE(delta_dt, TD, AIEN_DISPATCH_DTYPE(h_dt, TO,
+        (add_rmsnorm_kernel<TD, TO><<<T, th, 0, stream>>>(x, (const TD*)delta, w, w_dt, eps, (TO*)h, H))));
+    return launch_status();
+}
+
+AIEN_API int aien_gather_add_rows(const float* x, const void* delta, int delta_dt, const int* rows,
+                                  float* out, int R, int H, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    AIEN_DISPATCH_DTYPE(delta_dt, TD, (gather_add_rows_kernel<TD><<<R, row_threads(H), 0, stream>>>(
+        x, (const TD*)delta, rows, out, H)));
+    return launch_status();
+}
+
+AIEN_API int aien_swiglu(const void* gu, void* out, int dt, int T, int I, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const size_t total = (size_t)T * I;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    AIEN_DISPATCH_DTYPE(dt, TT, (swiglu_kernel<TT><<<blocks, 256, 0, stream>>>((const TT*)gu, (TT*)out, I, total)));
+    return launch_status();
+}
+
+AIEN_API int aien_rope_table(const int* positions, const double* inv_freq, float* cos_t, float* sin_t,
+                             int T, int half, cudaStream_t stream) {
+    if (T <= 0 || half <= 0) return 0;
+    const int n = T * half;
+    rope_table_kernel<<<(n + 127) / 128, 128, 0, stream>>>(positions, inv_freq, cos_t, sin_t, T, half);
+    return launch_status();
+}
+
+AIEN_API int aien_qk_norm_rope_kv_write(
+    void* q, long q_stride, int nq, const void* k, long k_stride, const void* v, long v_stride, int nkv,
+    int hd, const void* q_norm_w, const void* k_norm_w, int w_dt, float eps,
+    const float* cos_t, const float* sin_t, int rot, const int* slot_map,
+    void* k_cache, void* v_cache, int act_dt, int kv_dt, int T, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (hd <= 0 || hd > AIEN_MAX_HEAD_DIM || rot < 0 || rot > hd || (rot & 1)) return AIEN_E_SHAPE;
+    AIEN_DISPATCH_DTYPE(act_dt, TC, AIEN_DISPATCH_DTYPE(kv_dt, TKV,
+        (qk_norm_rope_kv_write_kernel<TC, TKV><<<T, 128, 0, stream>>>(
+            (TC*)q, q_stride, nq, (const TC*)k, k_stride, (const TC*)v, v_stride, nkv, hd,
+            q_norm_w, k_norm_w, w_dt, eps, cos_t, sin_t, rot, slot_map, (TKV*)k_cache, (TKV*)v_cache))));
+    return launch_status();
+}
+
+AIEN_API int aien_convert(const void* in, int in_dt, void* out, int out_dt, size_t n, cudaStream_t stream) {
+    if (n == 0) return 0;
+    const int blocks = (int)((n + 255) / 256 < 148 * 32 ? (n + 255) / 256 : 148 * 32);
+    AIEN_DISPATCH_DTYPE(in_dt, TI, AIEN_DISPATCH_DTYPE(out_dt, TO,
+        (convert_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)in, (TO*)out, n))));
+    return launch_status();
+}

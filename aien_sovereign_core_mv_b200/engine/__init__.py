@@ -1,0 +1,3 @@
+from .engine import Engine, StepEntry
+
+__all__ = ["Engine", "StepEntry"]

@@ -1,0 +1,260 @@
+"""The engine: one model, its cache, and the step function.
+
+``Engine.step(entries)`` is the single way tokens reach the model.  An entry is
+``(request id, its next tokens, want)``: a portion of a prompt or one decoded token; all
+entries of a call run as one batch from the cache earlier steps left, and float32 logits come
+back for the wanted places only.  The engine keeps no token history: positions follow from how
+many tokens of a request the cache already holds.
+
+Differences from the reference's ``execute_step`` (crates/aien-inference-abi/src/
+transformer_backend.rs:2519-2613), by design: prefill portions and decode tokens run as one
+batch instead of one request after the other; positions are explicit; capacity for the whole
+batch is checked before anything changes; a token id outside the vocabulary is refused rather
+than reduced modulo the vocabulary (transformer_backend.rs:1179).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Mapping, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import kernels as K
+from ..config.engine_config import EngineConfig
+from ..csrc import build as _build
+from ..models.decoder import Decoder
+from ..models.loading import build_model_from_config, build_model_from_folder
+from ..parts.base import GroupView, StepContext, Workspace
+
+
+@dataclass
+class StepEntry:
+    request_id: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+def _align4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class Engine:
+    """Model + cache + step.  Build with :meth:`from_folder` or :meth:`from_config`."""
+
+    def __init__(self, model: Decoder, model_config, engine_config: EngineConfig):
+        if not torch.cuda.is_available():
+            raise RuntimeError("this engine runs on a CUDA device (sm_100a) only; no CPU path exists")
+        K.lib()                                   # compile/load the kernels now, loudly
+        self.host = _build.load_host()
+        self.model = model
+        self.model_config = model_config
+        self.cfg = engine_config
+        self.dtype_name = engine_config.resolved_dtype()
+        self.dtype = torch.bfloat16 if self.dtype_name == "bfloat16" else torch.float32
+        self.device = torch.device("cuda")
+        self.vocab_size = model.vocab_size
+        spec = model.spec
+        self.page_size = int(engine_config.page_size)
+        self.max_context = int(engine_config.max_context or spec.max_position)
+        self.max_requests = int(engine_config.max_requests)
+        self.max_tokens_per_step = int(engine_config.max_batch_tokens)
+
+        # ---- cache groups
+        pages = int(engine_config.num_pages)
+        if pages <= 0:
+            tokens = int(engine_config.max_cache_tokens or self.max_context)
+            pages = (tokens + self.page_size - 1) // self.page_size
+        self.num_pages = pages
+        gspecs, self.storage = [], []
+        kinds = {"full": self.host.GroupKind.Full, "window": self.host.GroupKind.Window, "state": self.host.GroupKind.State}
+        for need, slots in zip(model.group_needs, model.group_slots):
+            if need.kind == "state":
+                gspecs.append(self.host.GroupSpec(kinds["state"], 0, self.max_requests))
+                sdt = getattr(torch, need.state_dtype)
+                self.storage.append(torch.zeros((slots, self.max_requests) + tuple(need.state_shape), dtype=sdt, device=self.device))
+            else:
+                gspecs.append(self.host.GroupSpec(kinds[need.kind], need.window, pages))
+                self.storage.append(torch.zeros((slots, 2, pages * self.page_size, need.num_kv_heads, need.head_dim),
+                                                dtype=self.dtype, device=self.device))
+        self.cache = self.host.CacheManager(self.page_size, gspecs, self.max_requests)
+        self.max_blocks = (self.max_context + self.page_size - 1) // self.page_size
+
+        # ---- workspace and metadata buffers
+        itemsize = 2 if self.dtype == torch.bfloat16 else 4
+        T = self.max_tokens_per_step
+        step_bytes = model.step_workspace_bytes(T, T)
+        layer_bytes = max(model.layer_workspace_bytes(T, itemsize), model.head_workspace_bytes(T, itemsize) + (1 << 16))
+        self.workspace = Workspace(step_bytes, layer_bytes, self.device)
+        meta_len = self._meta_len(T, self.max_requests, T)
+        # pinned staging buffers in a ring: a buffer is rewritten only after its copy has run
+        self._meta_ring = []
+        for _ in range(4):
+            h = torch.empty(meta_len, dtype=torch.int32, pin_memory=True)
+            self._meta_ring.append([h, h.numpy(), None])
+        self._meta_turn = 0
+        self.meta_dev = torch.empty(meta_len, dtype=torch.int32, device=self.device)
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def from_folder(cls, model_dir: str, engine_config: Optional[EngineConfig] = None, strict: bool = False) -> "Engine":
+        ec = engine_config or EngineConfig()
+        cfg, model = build_model_from_folder(model_dir, ec.resolved_dtype(), strict)
+        return cls(model, cfg, ec)
+
+    @classmethod
+    def from_config(cls, raw_config: Mapping, seed: int = 0, engine_config: Optional[EngineConfig] = None,
+                    init_std: Optional[float] = None, device_init: bool = False) -> "Engine":
+        ec = engine_config or EngineConfig()
+        cfg, model = build_model_from_config(raw_config, seed, ec.resolved_dtype(), init_std, device_init)
+        return cls(model, cfg, ec)
+
+    # ------------------------------------------------------------------ metadata layout
+    def _meta_len(self, T: int, S: int, R: int) -> int:
+        return self._layout(T, S, R)[1]
+
+    def _layout(self, T: int, S: int, R: int):
+        off, o = {}, 0
+        for name, n in (("token_ids", T), ("positions", T), ("seq_of_token", T), ("q_start", S + 1), ("ctx_len", S), ("want_rows", R)):
+            off[name] = o
+            o += _align4(max(n, 1))
+        groups = []
+        for need in self.model.group_needs:
+            if need.kind == "state":
+                groups.append((-1, o, 0))
+                o += _align4(max(S, 1))
+            else:
+                bt = o
+                o += _align4(S * self.max_blocks)
+                groups.append((bt, o, self.max_blocks))
+                o += _align4(max(T, 1))
+        off["groups"] = groups
+        return off, o
+
+    # ------------------------------------------------------------------ requests
+    def has_request(self, request_id: int) -> bool:
+        return self.cache.has(int(request_id))
+
+    def num_tokens(self, request_id: int) -> int:
+        return self.cache.num_tokens(int(request_id))
+
+    def end_request(self, request_id: int) -> None:
+        """Give back everything the request holds."""
+        if self.cache.has(int(request_id)):
+            self.cache.free_request(int(request_id))
+
+    def fork(self, parent: int, child: int, at_token: int = -1) -> None:
+        """``child`` shares the cache of the first ``at_token`` tokens of ``parent`` (all by
+        default); pages are copied only when one of the two writes into a shared one."""
+        self._do_copies(self.cache.fork(int(parent), int(child), int(at_token)))
+
+    def _do_copies(self, copies) -> None:
+        ps = self.page_size
+        for g, src, dst in copies:
+            st = self.storage[g]
+            if self.model.group_needs[g].kind == "state":
+                st[:, dst].copy_(st[:, src])
+            else:
+                st[:, :, dst * ps:(dst + 1) * ps].copy_(st[:, :, src * ps:(src + 1) * ps])
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: Sequence, logits_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Run one batch.  ``entries``: StepEntry or (request_id, tokens, want) tuples.  Returns
+        float32 logits [number of wanted places, vocab] on the device, in the order of the
+        entries and of each entry's ``want``."""
+        ents = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        ids, counts, want_rows, flat = [], [], [], []
+        seen = set()
+        t0 = 0
+        for e in ents:
+            rid, n = int(e.request_id), len(e.tokens)
+            if rid in seen:
+                raise ValueError(f"request {rid} appears twice in one step")
+            seen.add(rid)
+            if n == 0:
+                raise ValueError(f"request {rid}: an entry must bring at least one token")
+            for tok in e.tokens:
+                if not (0 <= int(tok) < self.vocab_size):
+                    raise ValueError(f"request {rid}: token id {tok} is outside the vocabulary of {self.vocab_size}")
+            for w in e.want:
+                if not (0 <= int(w) < n):
+                    raise ValueError(f"request {rid}: wanted place {w} is outside its {n} tokens")
+                want_rows.append(t0 + int(w))
+            have = self.cache.num_tokens(rid) if self.cache.has(rid) else 0
+            if have + n > self.max_context:
+                raise ValueError(f"request {rid}: {have + n} tokens exceed the context limit {self.max_context}")
+            ids.append(rid)
+            counts.append(n)
+            flat.extend(int(t) for t in e.tokens)
+            t0 += n
+        T, S, R = t0, len(ents), len(want_rows)
+        if T == 0:
+            return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+        if T > self.max_tokens_per_step:
+            raise ValueError(f"step of {T} tokens exceeds max_batch_tokens {self.max_tokens_per_step}")
+        if S > self.max_requests:
+            raise ValueError(f"step of {S} requests exceeds max_requests {self.max_requests}")
+
+        # ---- cache: all or nothing
+        added = []
+        try:
+            for rid in ids:
+                if not self.cache.has(rid):
+                    self.cache.add_request(rid)
+                    added.append(rid)
+            copies = self.cache.append(list(zip(ids, counts)))
+        except Exception:
+            for rid in added:
+                self.cache.free_request(rid)
+            raise
+        self._do_copies(copies)
+
+        # ---- metadata: one pinned buffer, one copy
+        off, total = self._layout(T, S, R)
+        slot = self._meta_ring[self._meta_turn % len(self._meta_ring)]
+        self._meta_turn += 1
+        if slot[2] is not None:
+            slot[2].synchronize()
+        meta_host, m = slot[0], slot[1]
+        m[off["token_ids"]:off["token_ids"] + T] = flat
+        if R:
+            m[off["want_rows"]:off["want_rows"] + R] = want_rows
+        self.cache.fill_meta(ids, counts, m, off["positions"], off["seq_of_token"], off["q_start"], off["ctx_len"], off["groups"])
+        self.meta_dev[:total].copy_(meta_host[:total], non_blocking=True)
+        if slot[2] is None:
+            slot[2] = torch.cuda.Event()
+        slot[2].record()
+        ctx = self._context(off, T, S, max(counts), decode_only=all(c == 1 for c in counts))
+        if logits_out is None:
+            logits_out = torch.empty((R, self.vocab_size), dtype=torch.float32, device=self.device)
+        d = self.meta_dev
+        self.model.forward(ctx, d[off["want_rows"]:off["want_rows"] + max(R, 1)], R, logits_out)
+        self.steps_run += 1
+        return logits_out
+
+    def _context(self, off, T: int, S: int, max_q: int, decode_only: bool) -> StepContext:
+        d = self.meta_dev
+        groups = []
+        for g, need in enumerate(self.model.group_needs):
+            bt, sm, mb = off["groups"][g]
+            if need.kind == "state":
+                groups.append(GroupView("state", self.page_size, 0, 0, None, d[sm:sm + S], self.storage[g]))
+            else:
+                groups.append(GroupView(need.kind, self.page_size, need.window, mb,
+                                        d[bt:bt + S * mb].view(S, mb), d[sm:sm + T], self.storage[g]))
+        self.workspace.reset()
+        return StepContext(
+            dtype=self.dtype, num_tokens=T, num_seqs=S,
+            token_ids=d[off["token_ids"]:off["token_ids"] + T], positions=d[off["positions"]:off["positions"] + T],
+            seq_of_token=d[off["seq_of_token"]:off["seq_of_token"] + T], q_start=d[off["q_start"]:off["q_start"] + S + 1],
+            ctx_len=d[off["ctx_len"]:off["ctx_len"] + S], groups=groups, workspace=self.workspace,
+            max_q_len=max_q, decode_only=decode_only,
+        )
+
+    # ------------------------------------------------------------------ information
+    def cache_state(self) -> dict:
+        return {
+            "free_pages": [self.cache.free_count(g) for g in range(self.cache.num_groups)],
+            "requests": self.cache.num_requests, "metrics": self.cache.metrics(), "check": self.cache.check(),
+        }

@@ -1,0 +1,272 @@
+"""Python face of the CUDA kernel library (``csrc/kernels``), loaded with ctypes.
+
+Every function here takes torch tensors that already live on the device, checks what the
+kernel cannot check for itself, and launches on the current CUDA stream.  Nothing falls back
+to another implementation: a missing library, a refused size or a failed launch raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_double, c_float, c_int, c_long, c_size_t, c_void_p
+from typing import Optional
+
+import torch
+
+from .csrc import build as _build
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+_ERRORS = {
+    -2: "unsupported dtype combination",
+    -3: "a size this kernel refuses",
+    -4: "pointer or stride not aligned as the kernel requires",
+    -5: "library state error (tensor map / attribute)",
+    -6: "a bounded wait inside the kernel ran out",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        _lib = _build.load_kernels()
+        _declare(_lib)
+    return _lib
+
+
+def _declare(l: ctypes.CDLL) -> None:
+    P, I, L, F = c_void_p, c_int, c_long, c_float
+    sigs = {
+        "aien_embed_gather": [P, I, P, P, I, I, I, P],
+        "aien_add_rmsnorm": [P, P, I, P, I, F, P, I, I, I, P],
+        "aien_gather_add_rows": [P, P, I, P, P, I, I, P],
+        "aien_swiglu": [P, P, I, I, I, P],
+        "aien_rope_table": [P, P, P, P, I, I, P],
+        "aien_qk_norm_rope_kv_write": [P, L, I, P, L, P, L, I, I, P, P, I, F, P, P, I, P, P, P, I, I, I, P],
+        "aien_convert": [P, I, P, I, c_size_t, P],
+        "aien_gemm_simple": [P, I, L, P, I, L, P, I, L, I, I, I, P],
+        "aien_paged_attention_generic": [P, L, P, P, P, I, P, P, P, L, I, I, I, I, I, F, I, I, I, P],
+        "aien_argmax_rows": [P, I, I, P, P],
+        "aien_sample_rows": [P, I, I, P, P, P, P, P, P, P, P, P],
+    }
+    for name, args in sigs.items():
+        fn = getattr(l, name)
+        fn.argtypes = args
+        fn.restype = c_int
+
+
+def declare_optional(name: str, args) -> bool:
+    """Declare a symbol that later kernel files add; returns False when the library lacks it."""
+    l = lib()
+    try:
+        fn = getattr(l, name)
+    except AttributeError:
+        return False
+    fn.argtypes = args
+    fn.restype = c_int
+    return True
+
+
+def _check(rc: int, name: str) -> None:
+    if rc == 0:
+        return
+    if rc < 0:
+        raise KernelError(f"{name}: {_ERRORS.get(rc, 'refused')} (code {rc})")
+    raise KernelError(f"{name}: CUDA error {rc} at launch")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"dtype {t.dtype} is not supported by the kernels") from None
+
+
+def _dev(*ts: Optional[torch.Tensor]) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernel arguments must live on the CUDA device (there is no CPU path)")
+
+
+# ---------------------------------------------------------------------------- row-wise ops
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, x: torch.Tensor) -> None:
+    """x[t] = table[ids[t]] as float32.  table [V,H], ids int32 [T], x float32 [T,H]."""
+    _dev(table, ids, x)
+    T, H = x.shape
+    assert table.is_contiguous() and x.is_contiguous() and ids.dtype == torch.int32 and x.dtype == torch.float32
+    assert table.shape[1] == H and ids.numel() >= T
+    _check(lib().aien_embed_gather(_p(table), dt(table), _p(ids), _p(x), T, H, table.shape[0], _stream()), "embed_gather")
+
+
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """x += delta (when given); out = rmsnorm(x) * weight.  x float32 [T,H] updated in place."""
+    _dev(x, delta, weight, out)
+    T, H = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and out.shape == x.shape
+    assert weight.numel() == H and weight.is_contiguous()
+    if delta is not None:
+        assert delta.shape == x.shape and delta.is_contiguous()
+    _check(lib().aien_add_rmsnorm(_p(x), _p(delta), dt(delta) if delta is not None else F32, _p(weight), dt(weight),
+                                  float(eps), _p(out), dt(out), T, H, _stream()), "add_rmsnorm")
+
+
+def gather_add_rows(x: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = x[rows[r]] + delta[rows[r]] in float32."""
+    _dev(x, delta, rows, out)
+    R, H = out.shape
+    assert x.dtype == torch.float32 and out.dtype == torch.float32 and rows.dtype == torch.int32
+    assert x.is_contiguous() and out.is_contiguous() and x.shape[1] == H and rows.numel() >= R
+    if delta is not None:
+        assert delta.shape == x.shape and delta.is_contiguous()
+    _check(lib().aien_gather_add_rows(_p(x), _p(delta), dt(delta) if delta is not None else F32, _p(rows), _p(out),
+                                      R, H, _stream()), "gather_add_rows")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out = silu(gate) * up for gate_up = [T, 2I] (gate columns first)."""
+    _dev(gate_up, out)
+    T, I = out.shape
+    assert gate_up.shape == (T, 2 * I) and gate_up.is_contiguous() and out.is_contiguous() and gate_up.dtype == out.dtype
+    _check(lib().aien_swiglu(_p(gate_up), _p(out), dt(out), T, I, _stream()), "swiglu")
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> None:
+    """cos/sin [T, half] float32 of positions[t] * inv_freq[i], the angle taken in float64."""
+    _dev(positions, inv_freq, cos, sin)
+    T, half = cos.shape
+    assert positions.dtype == torch.int32 and inv_freq.dtype == torch.float64 and inv_freq.numel() == half
+    assert cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous()
+    _check(lib().aien_rope_table(_p(positions), _p(inv_freq), _p(cos), _p(sin), T, half, _stream()), "rope_table")
+
+
+def qk_norm_rope_kv_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], head_dim: int,
+                          q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], eps: float,
+                          cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int,
+                          slot_map: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                          v_cache: Optional[torch.Tensor]) -> None:
+    """Per-head RMSNorm of q and k (when weights are given), rotation of the first
+    ``rotary_dim`` values, q written back in place, k and v written to their cache slots.
+    q [T, nq*hd], k/v [T, nkv*hd] may be column slices of one projection output."""
+    _dev(q, k, v, q_norm_w, k_norm_w, cos, sin, slot_map, k_cache, v_cache)
+    T = q.shape[0]
+    assert q.stride(1) == 1 and q.shape[1] % head_dim == 0
+    nq = q.shape[1] // head_dim
+    nkv = 0
+    if k is not None:
+        assert v is not None and slot_map is not None and k_cache is not None and v_cache is not None
+        assert k.stride(1) == 1 and v.stride(1) == 1 and k.dtype == q.dtype and v.dtype == q.dtype
+        assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.dtype == v_cache.dtype
+        assert slot_map.dtype == torch.int32 and slot_map.numel() >= T
+        nkv = k.shape[1] // head_dim
+    wdt = F32
+    for w in (q_norm_w, k_norm_w):
+        if w is not None:
+            assert w.numel() == head_dim and w.is_contiguous()
+            wdt = dt(w)
+    if q_norm_w is not None and k_norm_w is not None:
+        assert q_norm_w.dtype == k_norm_w.dtype
+    if cos is not None:
+        assert sin is not None and cos.shape == (T, rotary_dim // 2) and cos.is_contiguous() and sin.is_contiguous()
+    _check(lib().aien_qk_norm_rope_kv_write(
+        _p(q), q.stride(0), nq, _p(k), k.stride(0) if k is not None else 0, _p(v), v.stride(0) if v is not None else 0,
+        nkv, head_dim, _p(q_norm_w), _p(k_norm_w), wdt, float(eps), _p(cos), _p(sin), rotary_dim if cos is not None else 0,
+        _p(slot_map), _p(k_cache), _p(v_cache), dt(q), dt(k_cache) if k_cache is not None else dt(q), T, _stream()),
+        "qk_norm_rope_kv_write")
+
+
+def convert(src: torch.Tensor, dst: torch.Tensor) -> None:
+    _dev(src, dst)
+    assert src.is_contiguous() and dst.is_contiguous() and src.numel() == dst.numel()
+    _check(lib().aien_convert(_p(src), dt(src), _p(dst), dt(dst), src.numel(), _stream()), "convert")
+
+
+# ---------------------------------------------------------------------------- matrix products
+def gemm_simple(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M,N] = a[M,K] . w[N,K]^T, float32 accumulation on the CUDA cores, any sizes."""
+    _dev(a, w, out)
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N)
+    assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    _check(lib().aien_gemm_simple(_p(a), dt(a), a.stride(0), _p(w), dt(w), w.stride(0), _p(out), dt(out), out.stride(0),
+                                  M, N, K, _stream()), "gemm_simple")
+
+
+# ---------------------------------------------------------------------------- attention
+def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                            max_blocks: int, seq_of_token: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
+                            num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
+                            scale: float) -> None:
+    """Causal attention of T query tokens over their requests' pages.  q [T, nq*hd] (row stride
+    free), caches [slots, nkv, hd], block_table int32 [S, max_blocks], out [T, nq*hd]."""
+    _dev(q, k_cache, v_cache, block_table, seq_of_token, positions, out)
+    T = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.dtype == v_cache.dtype
+    assert block_table.dtype == torch.int32 and seq_of_token.dtype == torch.int32 and positions.dtype == torch.int32
+    _check(lib().aien_paged_attention_generic(
+        _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), max_blocks, _p(seq_of_token), _p(positions),
+        _p(out), out.stride(0), num_q_heads, num_kv_heads, head_dim, page_size, window, float(scale),
+        dt(q), dt(k_cache), T, _stream()), "paged_attention_generic")
+
+
+# ---------------------------------------------------------------------------- sampling
+def argmax_rows(logits: torch.Tensor, out_ids: torch.Tensor) -> None:
+    _dev(logits, out_ids)
+    R, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_contiguous() and out_ids.dtype == torch.int32 and out_ids.numel() >= R
+    _check(lib().aien_argmax_rows(_p(logits), R, V, _p(out_ids), _stream()), "argmax_rows")
+
+
+def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, top_k: torch.Tensor,
+                seeds: torch.Tensor, request_ids: torch.Tensor, positions: torch.Tensor, scratch: torch.Tensor,
+                out_ids: torch.Tensor) -> None:
+    """One token per row; see csrc/kernels/sampling.cu for the rules.  scratch: R*V float32."""
+    _dev(logits, temperature, top_p, top_k, seeds, request_ids, positions, scratch, out_ids)
+    R, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    assert temperature.dtype == torch.float32 and top_p.dtype == torch.float32 and top_k.dtype == torch.int32
+    assert seeds.dtype == torch.int64 and request_ids.dtype == torch.int64 and positions.dtype == torch.int32
+    assert scratch.dtype == torch.float32 and scratch.numel() >= R * V and out_ids.dtype == torch.int32
+    _check(lib().aien_sample_rows(_p(logits), R, V, _p(temperature), _p(top_p), _p(top_k), _p(seeds), _p(request_ids),
+                                  _p(positions), _p(scratch), _p(out_ids), _stream()), "sample_rows")
+
+
+# ---------------------------------------------------------------------------- kernel choice
+GEMV_MAX_ROWS = 0          # raised when the decode product kernel is present
+
+
+def gemv_supports(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    return False
+
+
+def gemm_tc_supports(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    return False
+
+
+def attention_workspace_bytes(max_tokens: int, num_heads: int, head_dim: int) -> int:
+    return 0
+
+
+def paged_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, group, out: torch.Tensor,
+                    num_q_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float) -> None:
+    """Attention of the step's tokens over one cache group; picks the kernel for the step."""
+    k2 = k_cache.view(-1, num_kv_heads, head_dim)
+    v2 = v_cache.view(-1, num_kv_heads, head_dim)
+    paged_attention_generic(q, k2, v2, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, out,
+                            num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale)

@@ -1,0 +1,173 @@
+"""The generic decoder: embedding, a run list of blocks, final norm, output head.
+
+It is built from a :class:`ModelSpec` alone.  It knows nothing of architectures: which parts a
+layer has, how many heads, whether the head is tied, in which order layers run and whose cache
+a run reads are all data in the spec.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Mapping, Optional, Tuple
+
+import torch
+
+from .. import kernels as K
+from ..config.spec import LayerSpec, ModelSpec, PartSpec
+from ..parts.base import Block, CacheNeed, Mixer, RunBinding, StepContext
+from ..parts.linear import linear
+from ..registry import make_part
+
+
+def _freeze(v):
+    if isinstance(v, dict):
+        return tuple(sorted((k, _freeze(x)) for k, x in v.items()))
+    if isinstance(v, (list, tuple)):
+        return tuple(_freeze(x) for x in v)
+    return v
+
+
+class Decoder:
+    def __init__(self, spec: ModelSpec):
+        spec.validate()
+        self.spec = spec
+        self.hidden_size, self.vocab_size = spec.hidden_size, spec.vocab_size
+        self._positions: Dict[tuple, object] = {}
+        self.blocks: List[Block] = []
+        for layer in spec.layers:
+            self.blocks.append(self._build_block(layer))
+        self.final_norm = make_part("norm", spec.final_norm.kind, size=spec.hidden_size,
+                                    **{k: v for k, v in spec.final_norm.params.items() if k != "name"})
+        self.embed_table: Optional[torch.Tensor] = None
+        self.head_weight: Optional[torch.Tensor] = None
+        self.tied = bool(spec.head.get("tied", False))
+        # ---- cache groups: runs with equal needs share pools and block tables
+        self.group_needs: List[CacheNeed] = []
+        self.group_slots: List[int] = []          # planes (cache slots) per group
+        self.bindings: List[RunBinding] = []
+        slot_home: Dict[int, Tuple[int, int]] = {}
+        for run in spec.run_list:
+            need = self.blocks[run.layer].mixer.cache_need()
+            if need is None or run.cache < 0:
+                self.bindings.append(RunBinding(-1, -1, False))
+                continue
+            if run.writes_cache:
+                key = need.group_key()
+                for g, have in enumerate(self.group_needs):
+                    if have.group_key() == key:
+                        break
+                else:
+                    g = len(self.group_needs)
+                    self.group_needs.append(need)
+                    self.group_slots.append(0)
+                slot_home[run.cache] = (g, self.group_slots[g])
+                self.group_slots[g] += 1
+                self.bindings.append(RunBinding(g, slot_home[run.cache][1], True))
+            else:
+                g, s = slot_home[run.cache]
+                if self.group_needs[g].group_key() != need.group_key():
+                    raise ValueError(f"a run reads cache slot {run.cache} whose layout differs from its own")
+                self.bindings.append(RunBinding(g, s, False))
+
+    # ------------------------------------------------------------------ construction
+    def _position(self, ps: PartSpec):
+        key = (ps.kind, _freeze(dict(ps.params)))
+        if key not in self._positions:
+            self._positions[key] = make_part("position", ps.kind, **dict(ps.params))
+        return self._positions[key]
+
+    def _build_block(self, layer: LayerSpec) -> Block:
+        position = self._position(layer.position)
+        mixer = make_part("mixer", layer.mixer.kind, position=position, **dict(layer.mixer.params))
+        ff = make_part("feed_forward", layer.feed_forward.kind, **dict(layer.feed_forward.params))
+        n1 = make_part("norm", layer.norm.kind, size=self.spec.hidden_size, **dict(layer.norm.params))
+        n2 = make_part("norm", layer.norm.kind, size=self.spec.hidden_size, **dict(layer.norm.params))
+        return make_part("block", layer.block, mixer=mixer, feed_forward=ff, norm_in=n1, norm_post=n2)
+
+    # ------------------------------------------------------------------ tensors
+    def _layer_names(self, li: int):
+        """(part name, local name) -> checkpoint name, for layer li."""
+        layer = self.spec.layers[li]
+        out = {}
+        for pname, part in self.blocks[li].parts().items():
+            for local, (shape, kind) in part.param_shapes().items():
+                key = f"{pname}.{local}"
+                out[(pname, local)] = (layer.prefix + layer.names.get(key, key), shape, kind)
+        return out
+
+    def catalog(self) -> Dict[str, Tuple[Tuple[int, ...], str]]:
+        """Every tensor the model wants: checkpoint name -> (shape, kind)."""
+        cat: Dict[str, Tuple[Tuple[int, ...], str]] = {}
+        cat[self.spec.embedding.get("name")] = ((self.vocab_size, self.hidden_size), "embedding")
+        for li in range(len(self.blocks)):
+            for (_, _), (name, shape, kind) in self._layer_names(li).items():
+                cat[name] = (tuple(shape), kind)
+        for local, (shape, kind) in self.final_norm.param_shapes().items():
+            cat[self.spec.final_norm.get("name")] = (tuple(shape), kind)
+        if not self.tied:
+            cat[self.spec.head.get("name")] = ((self.vocab_size, self.hidden_size), "matrix")
+        return cat
+
+    def bind(self, tensors) -> None:
+        """``tensors``: iterable of (checkpoint name, tensor); each is moved to the device as it
+        arrives and handed to its part once the part's set is complete."""
+        device = torch.device("cuda")
+        owner: Dict[str, Tuple[int, str, str]] = {}
+        for li in range(len(self.blocks)):
+            for (pname, local), (name, _, _) in self._layer_names(li).items():
+                owner[name] = (li, pname, local)
+        pending: Dict[Tuple[int, str], Dict[str, torch.Tensor]] = {}
+        embed_name, norm_name, head_name = self.spec.embedding.get("name"), self.spec.final_norm.get("name"), self.spec.head.get("name")
+        for name, t in tensors:
+            t = t.to(device, non_blocking=False)
+            if name == embed_name:
+                self.embed_table = t.contiguous()
+            elif name == norm_name:
+                self.final_norm.bind({"weight": t})
+            elif name == head_name and not self.tied:
+                self.head_weight = t.contiguous()
+            elif name in owner:
+                li, pname, local = owner[name]
+                part = self.blocks[li].parts()[pname]
+                bucket = pending.setdefault((li, pname), {})
+                bucket[local] = t
+                if len(bucket) == len(part.param_shapes()):
+                    part.bind(bucket)
+                    del pending[(li, pname)]
+            else:
+                raise KeyError(f"tensor {name!r} belongs to no part of the model")
+        if self.tied:
+            self.head_weight = self.embed_table
+        if pending or self.embed_table is None or self.head_weight is None or self.final_norm.weight is None:
+            raise RuntimeError("bind: some parts did not receive all their tensors")
+
+    # ------------------------------------------------------------------ sizes
+    def layer_workspace_bytes(self, max_tokens: int, itemsize: int) -> int:
+        return max(b.workspace_bytes(max_tokens, itemsize) for b in self.blocks) + (1 << 16)
+
+    def step_workspace_bytes(self, max_tokens: int, max_rows: int) -> int:
+        n = max_tokens * self.hidden_size * 4 + 4096
+        for p in self._positions.values():
+            if hasattr(p, "step_workspace_bytes"):
+                n += p.step_workspace_bytes(max_tokens)
+        return n
+
+    def head_workspace_bytes(self, max_rows: int, itemsize: int) -> int:
+        return max_rows * self.hidden_size * (4 + itemsize) + 4096
+
+    # ------------------------------------------------------------------ one step
+    def forward(self, ctx: StepContext, want_rows: torch.Tensor, num_rows: int, logits: torch.Tensor) -> torch.Tensor:
+        """Runs the step's tokens through the run list; writes float32 logits of the wanted
+        rows into ``logits`` [num_rows, vocab]."""
+        ws = ctx.workspace
+        x = ws.take_step((ctx.num_tokens, self.hidden_size), torch.float32)
+        K.embed_gather(self.embed_table, ctx.token_ids, x)
+        delta = None
+        for run, binding in zip(self.spec.run_list, self.bindings):
+            ws.begin_layer()
+            delta = self.blocks[run.layer].forward(ctx, x, delta, binding)
+        ws.end_layers()
+        if num_rows > 0:
+            rows = ws.take((num_rows, self.hidden_size), torch.float32)
+            K.gather_add_rows(x, delta, want_rows, rows)
+            hn = self.final_norm.forward(ctx, rows, None)
+            linear(ctx, hn, self.head_weight, out=logits)
+        return logits

@@ -1,0 +1,94 @@
+"""Grouped-query attention over the paged cache."""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from .. import kernels as K
+from ..registry import register_mixer
+from .base import CacheNeed, Mixer, Position, RunBinding, StepContext
+from .linear import linear
+
+
+@register_mixer("paged_attention")
+class PagedAttention(Mixer):
+    """q/k/v projection (one product over the stacked rows q|k|v), optional per-head RMSNorm of
+    q and k before rotation, rotation, write of k and v into the token's cache slot, causal
+    attention over the request's pages (optionally only the last ``window`` keys), output
+    projection.  Formulas: crates/aien-inference-abi/src/transformer_backend.rs:1229-1319 and
+    src/backend.rs:311-379; the stacked q|k|v rows follow src/resident.rs:284-288.
+
+    A run that does not write its cache (``run.writes == False``) projects q only and attends
+    over the planes another run filled."""
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, position: Position,
+                 qk_norm: bool = False, qk_norm_eps: float = 1e-6, window: int = 0, scale: Optional[float] = None):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"num_heads {num_heads} is not a multiple of num_kv_heads {num_kv_heads}")
+        if head_dim % 2 or head_dim > 256:
+            raise ValueError(f"head_dim {head_dim}: the attention kernels take even sizes up to 256")
+        self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
+        self.position = position
+        self.qk_norm, self.qk_norm_eps = bool(qk_norm), float(qk_norm_eps)
+        self.window = int(window or 0)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.q_dim, self.kv_dim = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
+        self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
+
+    # ---- tensors
+    def param_shapes(self):
+        H = self.hidden_size
+        shapes = {
+            "q_proj": ((self.q_dim, H), "matrix"), "k_proj": ((self.kv_dim, H), "matrix"),
+            "v_proj": ((self.kv_dim, H), "matrix"), "o_proj": ((H, self.q_dim), "matrix"),
+        }
+        if self.qk_norm:
+            shapes["q_norm"] = ((self.head_dim,), "norm")
+            shapes["k_norm"] = ((self.head_dim,), "norm")
+        return shapes
+
+    def bind(self, tensors):
+        q, k, v = tensors["q_proj"], tensors["k_proj"], tensors["v_proj"]
+        if not (q.dtype == k.dtype == v.dtype):
+            q, k, v = q.float(), k.float(), v.float()
+        self.w_qkv = torch.cat([q, k, v], dim=0).contiguous()       # rows q | k | v
+        self.w_o = tensors["o_proj"].contiguous()
+        if self.qk_norm:
+            qn, kn = tensors["q_norm"], tensors["k_norm"]
+            if qn.dtype != kn.dtype:
+                qn, kn = qn.float(), kn.float()
+            self.q_norm_w, self.k_norm_w = qn.contiguous(), kn.contiguous()
+
+    def cache_need(self):
+        return CacheNeed("window" if self.window > 0 else "full", self.window, self.num_kv_heads, self.head_dim)
+
+    def workspace_bytes(self, max_tokens, itemsize):
+        return max_tokens * (self.q_dim + 2 * self.kv_dim + self.q_dim + self.hidden_size) * itemsize + 1024 \
+            + K.attention_workspace_bytes(max_tokens, self.num_heads, self.head_dim)
+
+    # ---- one step
+    def forward(self, ctx: StepContext, h: torch.Tensor, run: RunBinding) -> torch.Tensor:
+        T = ctx.num_tokens
+        group = ctx.groups[run.group]
+        planes = group.storage[run.slot]                 # [2, tokens, nkv, hd]
+        k_cache, v_cache = planes[0], planes[1]
+        if run.writes:
+            qkv = linear(ctx, h, self.w_qkv)
+            q, k, v = qkv[:, :self.q_dim], qkv[:, self.q_dim:self.q_dim + self.kv_dim], qkv[:, self.q_dim + self.kv_dim:]
+        else:
+            q = linear(ctx, h, self.w_qkv[:self.q_dim])
+            k = v = None
+        rot = self.position.rotary(ctx)
+        cos, sin, rdim = rot if rot is not None else (None, None, 0)
+        if rot is None:
+            self.position.apply(ctx, q, k)
+        K.qk_norm_rope_kv_write(q, k, v, self.head_dim, self.q_norm_w, self.k_norm_w if k is not None else None,
+                                self.qk_norm_eps, cos, sin, rdim,
+                                group.slot_map if k is not None else None,
+                                k_cache if k is not None else None, v_cache if k is not None else None)
+        out = ctx.workspace.take((T, self.q_dim), ctx.dtype)
+        K.paged_attention(ctx, q, k_cache, v_cache, group, out, self.num_heads, self.num_kv_heads, self.head_dim,
+                          self.window, self.scale)
+        return linear(ctx, out, self.w_o)

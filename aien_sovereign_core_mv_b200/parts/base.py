@@ -1,0 +1,186 @@
+"""What a part is, and what it sees of a step.
+
+A model is built from five families of parts, each chosen per layer by the model spec:
+
+* **norm**           ``forward(ctx, x, delta, out_dtype) -> h``; x is the float32 residual stream
+  [T, H]; ``delta`` (or None) is added to it in place first.
+* **position**       describes how positions enter the mixer.  ``rotary(ctx)`` returns
+  ``(cos, sin, rotary_dim)`` tables for this step's tokens (or None), which the attention mixer
+  feeds to its fused kernel; a part without tables implements ``apply(ctx, q, k)`` instead.
+* **mixer**          ``forward(ctx, h, run) -> y``; h and y are [T, H] in the compute dtype.
+  ``cache_need()`` says what it keeps between steps: pages of keys and values (all, or a
+  window), a fixed-size state slot, or nothing.
+* **feed_forward**   ``forward(ctx, h) -> y``.
+* **block**          arranges the others: ``forward(ctx, x, delta, run) -> delta``; the returned
+  delta is added to the residual stream by whoever norms next (the next block or the final
+  norm), which fuses the residual sum into the norm kernel.
+
+Every part lists its tensors with ``param_shapes()`` (local name -> (shape, kind)) and receives
+them, already on the device, through ``bind(tensors)``.  A part takes its sizes and constants
+as constructor parameters and never asks which model it is in.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Mapping, Optional, Tuple
+
+import torch
+
+
+# ------------------------------------------------------------------ what a mixer keeps
+@dataclass(frozen=True)
+class CacheNeed:
+    """kind: "full" (all keys), "window" (the last `window` keys), "state" (fixed size)."""
+
+    kind: str
+    window: int = 0
+    num_kv_heads: int = 0
+    head_dim: int = 0
+    state_shape: Tuple[int, ...] = ()     # "state": per-request tensor shape
+    state_dtype: str = "float32"
+
+    def group_key(self) -> tuple:
+        return (self.kind, self.window, self.num_kv_heads, self.head_dim, self.state_shape, self.state_dtype)
+
+
+@dataclass
+class GroupView:
+    """One cache group as a step sees it (device tensors)."""
+
+    kind: str
+    page_size: int
+    window: int
+    max_blocks: int
+    block_table: Optional[torch.Tensor]    # int32 [S, max_blocks]; None for state groups
+    slot_map: Optional[torch.Tensor]       # int32 [T] token slots (paged) or [S] state slots
+    storage: torch.Tensor                  # paged: [slots_in_group, 2, tokens, nkv, hd]; state: [slots_in_group, capacity, *shape]
+
+
+@dataclass
+class RunBinding:
+    """Where one run of a layer keeps its cache."""
+
+    group: int = -1          # cache group index, -1: none
+    slot: int = -1           # index of this run's planes inside the group's storage
+    writes: bool = True      # False: attend over planes another run wrote
+
+
+@dataclass
+class StepContext:
+    """Everything a part may use during one step.  Tensors are device tensors."""
+
+    dtype: torch.dtype                     # compute dtype: bfloat16 or float32
+    num_tokens: int                        # T (may include padding rows in a captured step)
+    num_seqs: int                          # S
+    token_ids: torch.Tensor                # int32 [T]
+    positions: torch.Tensor                # int32 [T]
+    seq_of_token: torch.Tensor             # int32 [T]
+    q_start: torch.Tensor                  # int32 [S+1]
+    ctx_len: torch.Tensor                  # int32 [S]
+    groups: List[GroupView]
+    workspace: "Workspace"
+    # host copies for parts that plan on the host (never read in a captured step)
+    host: Optional[Mapping[str, Any]] = None
+    max_q_len: int = 0                     # longest portion in the step (host knowledge)
+    max_ctx_len: int = 0
+    decode_only: bool = False
+    shared: Dict[Any, Any] = field(default_factory=dict)   # per-step memo (rotary tables ...)
+
+
+class Workspace:
+    """Scratch for one step, carved from one device buffer so that a step allocates nothing
+    and its addresses repeat (which a captured CUDA graph needs).
+
+    Three regions: a *step* region that lives until the step ends (residual stream, rotary
+    tables) and two *layer* regions used alternately: ``begin_layer()`` flips to the other one
+    and empties it, so what a layer returns (its pending residual delta) stays valid while the
+    next layer runs, and is recycled by the layer after that."""
+
+    def __init__(self, step_bytes: int, layer_bytes: int, device: torch.device):
+        self.step_bytes = (int(step_bytes) + 255) & ~255
+        self.layer_bytes = (int(layer_bytes) + 255) & ~255
+        self.buf = torch.empty(self.step_bytes + 2 * self.layer_bytes, dtype=torch.uint8, device=device)
+        self._base = [0, self.step_bytes, self.step_bytes + self.layer_bytes]
+        self._size = [self.step_bytes, self.layer_bytes, self.layer_bytes]
+        self._off = [0, 0, 0]
+        self._cur = 0
+
+    def reset(self) -> None:
+        self._off = [0, 0, 0]
+        self._cur = 0
+
+    def begin_layer(self) -> None:
+        self._cur = 2 if self._cur == 1 else 1
+        self._off[self._cur] = 0
+
+    def end_layers(self) -> None:
+        """Later takes come from the region not holding the last layer's result."""
+        self.begin_layer()
+
+    def _take(self, region: int, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        start = (self._off[region] + 255) & ~255
+        if start + nbytes > self._size[region]:
+            which = "step" if region == 0 else "layer"
+            raise RuntimeError(
+                f"{which} workspace too small: need {start + nbytes} bytes, have {self._size[region]} "
+                f"(the step brings more tokens than max_batch_tokens allows)")
+        self._off[region] = start + nbytes
+        lo = self._base[region] + start
+        return self.buf[lo:lo + nbytes].view(dtype).view(*shape)
+
+    def take(self, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        return self._take(self._cur, shape, dtype)
+
+    def take_step(self, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        return self._take(0, shape, dtype)
+
+
+# ------------------------------------------------------------------ part base classes
+class Part:
+    def param_shapes(self) -> Dict[str, Tuple[Tuple[int, ...], str]]:
+        """local tensor name -> (shape, kind) with kind in {"matrix", "embedding", "norm"}."""
+        return {}
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        """Receive the tensors named by param_shapes (device tensors, stored dtype kept)."""
+
+    def workspace_bytes(self, max_tokens: int, itemsize: int) -> int:
+        """Upper bound of what forward() takes from the workspace for `max_tokens` tokens."""
+        return 0
+
+
+class Norm(Part):
+    def forward(self, ctx: StepContext, x: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Position(Part):
+    def rotary(self, ctx: StepContext):
+        return None
+
+    def apply(self, ctx: StepContext, q: torch.Tensor, k: Optional[torch.Tensor]) -> None:
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_need(self) -> Optional[CacheNeed]:
+        return None
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, run: RunBinding) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block(Part):
+    mixer: Mixer
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, delta: Optional[torch.Tensor], run: RunBinding) -> torch.Tensor:
+        raise NotImplementedError

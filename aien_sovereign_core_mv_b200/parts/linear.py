@@ -1,0 +1,44 @@
+"""Matrix products y = a . W^T with W in the checkpoint's [out, in] layout.
+
+One entry point, :func:`linear`, chooses among the engine's own kernels by precision and by
+the number of rows; all of them accumulate in float32.  The float32 engine always takes the
+CUDA-core kernel whose per-row result does not depend on the batch.  ``AIEN_B200_GEMM`` can pin
+the choice for debugging (``simple``, ``gemv``, ``tc``): it never selects a library routine.
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+
+from .. import kernels as K
+from .base import StepContext
+
+_FORCE = os.environ.get("AIEN_B200_GEMM", "").strip().lower()
+
+
+def linear(ctx: StepContext, a: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a [M, K] (row stride free), w [N, K] -> [M, N] taken from the step workspace."""
+    M, N = a.shape[0], w.shape[0]
+    if out is None:
+        out = ctx.workspace.take((M, N), out_dtype or a.dtype)
+    choice = _FORCE or _choose(a, w, out, M)
+    if choice == "gemv":
+        K.gemv(a, w, out)
+    elif choice == "tc":
+        K.gemm_tc(a, w, out, ctx.workspace)
+    else:
+        K.gemm_simple(a, w, out)
+    return out
+
+
+def _choose(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, M: int) -> str:
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return "simple"
+    if M <= K.GEMV_MAX_ROWS and K.gemv_supports(a, w, out):
+        return "gemv"
+    if K.gemm_tc_supports(a, w, out):
+        return "tc"
+    return "simple"

@@ -1,0 +1,36 @@
+"""RMSNorm with the residual sum fused in front of it."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import kernels as K
+from ..registry import register_norm
+from .base import Norm, StepContext
+
+
+@register_norm("rmsnorm")
+class RMSNorm(Norm):
+    """h = x * (1/sqrt(mean(x^2) + eps)) * w over the last axis
+    (crates/aien-inference-abi/src/tensor.rs:94-110).  The sum of squares and the scale are
+    float32; x is the float32 residual stream and is updated in place when ``delta`` is given."""
+
+    def __init__(self, size: int, eps: float):
+        self.size = int(size)
+        self.eps = float(eps)
+        self.weight: Optional[torch.Tensor] = None
+
+    def param_shapes(self):
+        return {"weight": ((self.size,), "norm")}
+
+    def bind(self, tensors):
+        self.weight = tensors["weight"].contiguous()
+
+    def workspace_bytes(self, max_tokens, itemsize):
+        return max_tokens * self.size * itemsize + 256
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
+        out = ctx.workspace.take(tuple(x.shape), ctx.dtype)
+        K.add_rmsnorm(x, delta, self.weight, self.eps, out)
+        return out

@@ -1,0 +1,277 @@
+"""Each kernel alone against a plain float32 (or float64) restatement in torch/numpy, at sizes
+other than the engine's: widths and vocabularies that are no power of two, head sizes in steps
+of 16, odd numbers of heads and groups, and inputs made so that a single far key or a window's
+edge decides the result."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+import plain_model as pm
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    from aien_sovereign_core_mv_b200 import kernels
+    kernels.lib()
+    return kernels
+
+
+def dev(a, dtype=torch.float32):
+    return torch.as_tensor(np.asarray(a), dtype=dtype).cuda() if not isinstance(a, torch.Tensor) else a.to("cuda", dtype)
+
+
+def tol_for(dtype):
+    return 2e-5 if dtype == torch.float32 else 1.5e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K_", [(1, 7, 5), (3, 130, 77), (65, 64, 16), (130, 333, 200), (2, 1000, 1031)])
+def test_gemm_simple(K, dtype, M, N, K_):
+    g = torch.Generator().manual_seed(M * 1000 + N)
+    a = torch.randn(M, K_, generator=g).to(dtype).cuda()
+    w = torch.randn(N, K_, generator=g).to(dtype).cuda()
+    out = torch.empty(M, N, dtype=dtype, device="cuda")
+    K.gemm_simple(a, w, out)
+    want = a.double().cpu() @ w.double().cpu().T
+    H.assert_close(out.float().cpu().numpy(), want.numpy(), tol_for(dtype), f"gemm {M}x{N}x{K_}")
+    # float32 logits out of bfloat16 operands, strided input rows
+    big = torch.randn(M, K_ + 9, generator=g).to(dtype).cuda()
+    out32 = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    K.gemm_simple(big[:, 4:4 + K_], w, out32)
+    want = big[:, 4:4 + K_].double().cpu() @ w.double().cpu().T
+    H.assert_close(out32.cpu().numpy(), want.numpy(), 2e-5, "gemm strided, f32 out")
+
+
+def test_gemm_rows_do_not_depend_on_batch(K):
+    g = torch.Generator().manual_seed(5)
+    a = torch.randn(70, 200, generator=g).cuda()
+    w = torch.randn(90, 200, generator=g).cuda()
+    full = torch.empty(70, 90, device="cuda")
+    K.gemm_simple(a, w, full)
+    one = torch.empty(1, 90, device="cuda")
+    for r in (0, 37, 69):
+        K.gemm_simple(a[r:r + 1], w, one)
+        assert torch.equal(one[0], full[r])          # bit-identical
+
+
+@pytest.mark.parametrize("hdt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,Hd", [(1, 72), (5, 96), (3, 4100)])
+def test_embed_and_add_rmsnorm(K, hdt, T, Hd):
+    g = torch.Generator().manual_seed(T + Hd)
+    table = torch.randn(50, Hd, generator=g).to(hdt).cuda()
+    ids = torch.tensor([(7 * i + 3) % 50 for i in range(T)], dtype=torch.int32).cuda()
+    x = torch.empty(T, Hd, device="cuda")
+    K.embed_gather(table, ids, x)
+    assert torch.equal(x, table.float()[ids.long()])
+    delta = torch.randn(T, Hd, generator=g).to(hdt).cuda()
+    w = (torch.rand(Hd, generator=g) * 0.4 + 0.8).to(hdt).cuda()
+    x0 = x.clone()
+    out = torch.empty(T, Hd, dtype=hdt, device="cuda")
+    K.add_rmsnorm(x, delta, w, 1e-5, out)
+    xs = (x0 + delta.float()).cpu().numpy()
+    assert np.array_equal(x.cpu().numpy(), xs.astype(np.float32))
+    want = pm.rms_norm(xs, w.float().cpu().numpy().astype(np.float64), 1e-5)
+    H.assert_close(out.float().cpu().numpy(), want, tol_for(hdt), "rmsnorm")
+    rows = torch.tensor([T - 1, 0], dtype=torch.int32).cuda()
+    got = torch.empty(2, Hd, device="cuda")
+    K.gather_add_rows(x0, delta, rows, got)
+    assert np.array_equal(got.cpu().numpy(), xs[[T - 1, 0]].astype(np.float32))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu(K, dtype):
+    g = torch.Generator().manual_seed(3)
+    gu = (torch.randn(5, 2 * 77, generator=g) * 3).to(dtype).cuda()
+    out = torch.empty(5, 77, dtype=dtype, device="cuda")
+    K.swiglu(gu, out)
+    want = pm.swiglu(gu[:, :77].double().cpu().numpy(), gu[:, 77:].double().cpu().numpy())
+    H.assert_close(out.float().cpu().numpy(), want, tol_for(dtype), "swiglu")
+
+
+def test_rope_table_far_positions(K):
+    inv = torch.tensor(pm.rope_inv_freq(48, 1e6), dtype=torch.float64).cuda()
+    pos = torch.tensor([0, 1, 17, 4095, 131071], dtype=torch.int32).cuda()
+    cos = torch.empty(5, 24, device="cuda"); sin = torch.empty(5, 24, device="cuda")
+    K.rope_table(pos, inv, cos, sin)
+    ang = pos.cpu().numpy().astype(np.float64)[:, None] * inv.cpu().numpy()[None]
+    assert np.abs(cos.cpu().numpy() - np.cos(ang)).max() <= 1.2e-7
+    assert np.abs(sin.cpu().numpy() - np.sin(ang)).max() <= 1.2e-7
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,hd,rot,norm", [(4, 2, 16, 16, False), (6, 3, 48, 48, True), (5, 1, 80, 32, True), (2, 2, 256, 256, True)])
+def test_qk_norm_rope_kv_write(K, dtype, nq, nkv, hd, rot, norm):
+    T, slots = 7, 40
+    g = torch.Generator().manual_seed(nq * hd)
+    qkv = torch.randn(T, (nq + 2 * nkv) * hd, generator=g).to(dtype).cuda()
+    q, k, v = qkv[:, :nq * hd], qkv[:, nq * hd:(nq + nkv) * hd], qkv[:, (nq + nkv) * hd:]
+    qw = (torch.rand(hd, generator=g) * 0.4 + 0.8).to(dtype).cuda() if norm else None
+    kw = (torch.rand(hd, generator=g) * 0.4 + 0.8).to(dtype).cuda() if norm else None
+    pos = [0, 3, 4, 100, 101, 2000, 7]
+    inv = pm.rope_inv_freq(rot, 10000.0)
+    cos = torch.empty(T, rot // 2, device="cuda"); sin = torch.empty(T, rot // 2, device="cuda")
+    K.rope_table(torch.tensor(pos, dtype=torch.int32).cuda(), torch.tensor(inv, dtype=torch.float64).cuda(), cos, sin)
+    slot_map = torch.tensor([5, 6, 39, 0, 17, -1, 8], dtype=torch.int32).cuda()
+    kc = torch.full((slots, nkv, hd), 7.0, dtype=dtype, device="cuda"); vc = torch.full((slots, nkv, hd), 7.0, dtype=dtype, device="cuda")
+    q0, k0, v0 = (t.float().cpu().numpy().astype(np.float64) for t in (q, k, v))
+    K.qk_norm_rope_kv_write(q, k, v, hd, qw, kw, 1e-6, cos, sin, rot, slot_map, kc, vc)
+
+    def ref(x, heads, w):
+        x = x.reshape(T, heads, hd)
+        if w is not None:
+            x = pm.rms_norm(x, w.float().cpu().numpy().astype(np.float64), 1e-6)
+        r = pm.apply_rope(x[..., :rot], pos, inv)
+        return np.concatenate([r, x[..., rot:]], -1)
+    H.assert_close(q.float().cpu().numpy().reshape(T, nq, hd), ref(q0, nq, qw), tol_for(dtype), "q")
+    kref, kcn, vcn = ref(k0, nkv, kw), kc.float().cpu().numpy(), vc.float().cpu().numpy()
+    sm = slot_map.cpu().numpy()
+    for t in range(T):
+        if sm[t] >= 0:
+            H.assert_close(kcn[sm[t]], kref[t], tol_for(dtype), f"k token {t}")
+            H.assert_close(vcn[sm[t]], v0.reshape(T, nkv, hd)[t], tol_for(dtype), f"v token {t}")
+    untouched = [s for s in range(slots) if s not in set(sm.tolist())]
+    assert (kcn[untouched] == 7.0).all() and (vcn[untouched] == 7.0).all()     # a token without a slot writes nothing
+
+
+def paged_setup(rng, seq_lens, nkv, hd, page, dtype, n_pages):
+    """Random K/V for each request scattered over shuffled pages; returns caches, tables, dense copies."""
+    perm = rng.permutation(n_pages)
+    kc = torch.zeros(n_pages * page, nkv, hd); vc = torch.zeros(n_pages * page, nkv, hd)
+    max_blocks = max((n + page - 1) // page for n in seq_lens) + 1
+    bt = np.full((len(seq_lens), max_blocks), -1, dtype=np.int32)
+    dense, nxt = [], 0
+    for s, n in enumerate(seq_lens):
+        k = torch.tensor(rng.standard_normal((n, nkv, hd)), dtype=torch.float32).to(dtype).float()
+        v = torch.tensor(rng.standard_normal((n, nkv, hd)), dtype=torch.float32).to(dtype).float()
+        dense.append((k, v))
+        for b in range((n + page - 1) // page):
+            pg = int(perm[nxt]); nxt += 1
+            bt[s, b] = pg
+            lo, hi = b * page, min(n, (b + 1) * page)
+            kc[pg * page:pg * page + hi - lo] = k[lo:hi]
+            vc[pg * page:pg * page + hi - lo] = v[lo:hi]
+    return kc.to(dtype).cuda(), vc.to(dtype).cuda(), torch.tensor(bt).cuda(), max_blocks, dense
+
+
+def attention_reference(q, dense, seq_of, positions, nq, nkv, hd, window, scale):
+    out = np.zeros((len(seq_of), nq, hd))
+    for t, (s, p) in enumerate(zip(seq_of, positions)):
+        k, v = dense[s]
+        lo = max(0, p - window + 1) if window > 0 else 0
+        kk, vv = k[lo:p + 1].double().numpy(), v[lo:p + 1].double().numpy()
+        for h in range(nq):
+            sc = (kk[:, h // (nq // nkv)] @ q[t, h]) * scale
+            e = np.exp(sc - sc.max()); e /= e.sum()
+            out[t, h] = e @ vv[:, h // (nq // nkv)]
+    return out.reshape(len(seq_of), nq * hd)
+
+
+ATT_CASES = [(4, 2, 16, 16, 0), (6, 3, 48, 8, 0), (5, 1, 80, 16, 0), (8, 2, 128, 16, 0), (3, 3, 32, 4, 21), (2, 1, 256, 32, 0), (8, 4, 64, 16, 40)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,hd,page,window", ATT_CASES)
+def test_paged_attention_generic(K, dtype, nq, nkv, hd, page, window):
+    rng = np.random.default_rng(nq * 100 + hd)
+    seq_lens = [1, 37, 300, 129]
+    kc, vc, bt, mb, dense = paged_setup(rng, seq_lens, nkv, hd, page, dtype, 64 * 16 // page + 8)
+    # tokens: decode rows (last position), a portion in the middle of request 2, the first tokens of request 1
+    seq_of = [0, 1, 2, 3] + [2] * 9 + [1, 1, 1]
+    positions = [0, 36, 299, 128] + list(range(250, 259)) + [0, 1, 2]
+    q = torch.tensor(rng.standard_normal((len(seq_of), nq * hd)), dtype=torch.float32).to(dtype)
+    scale = 1.0 / math.sqrt(hd)
+    out = torch.empty(len(seq_of), nq * hd, dtype=dtype, device="cuda")
+    K.paged_attention_generic(q.cuda(), kc, vc, bt, mb, torch.tensor(seq_of, dtype=torch.int32).cuda(),
+                              torch.tensor(positions, dtype=torch.int32).cuda(), out, nq, nkv, hd, page, window, scale)
+    want = attention_reference(q.float().double().numpy().reshape(-1, nq, hd), dense, seq_of, positions, nq, nkv, hd, window, scale)
+    H.assert_close(out.float().cpu().numpy(), want, tol_for(dtype), "attention")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_one_far_key_decides(K, dtype):
+    """Among 600 keys one far key matches the query; the output must be that key's value.  A kernel
+    that drops a page, misreads a table entry or stops early cannot pass."""
+    nq, nkv, hd, page = 2, 1, 64, 16
+    n = 600
+    for far in (0, 15, 16, 303, 599):
+        kc = torch.zeros(48 * page, nkv, hd); vc = torch.zeros(48 * page, nkv, hd)
+        perm = np.random.default_rng(far).permutation(48)
+        bt = np.full((1, 40), -1, dtype=np.int32)
+        for b in range((n + page - 1) // page):
+            bt[0, b] = perm[b]
+        slot = lambda j: int(bt[0, j // page]) * page + j % page
+        for j in range(n):
+            vc[slot(j), 0, :] = j
+        kc[slot(far), 0, 0] = 40.0
+        q = torch.zeros(1, nq * hd); q[0, 0] = 8.0; q[0, hd] = 8.0
+        out = torch.empty(1, nq * hd, dtype=dtype, device="cuda")
+        K.paged_attention_generic(q.to(dtype).cuda(), kc.to(dtype).cuda(), vc.to(dtype).cuda(), torch.tensor(bt).cuda(), 40,
+                                  torch.zeros(1, dtype=torch.int32).cuda(), torch.tensor([n - 1], dtype=torch.int32).cuda(),
+                                  out, nq, nkv, hd, page, 0, 1.0 / math.sqrt(hd))
+        got = out.float().cpu().numpy()
+        assert np.abs(got - far).max() <= max(1e-3, 0.01 * far), (far, got[0, :4])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_window_edge(K, dtype):
+    """The key just outside the window carries a huge score: it must not be seen; the one just
+    inside must."""
+    nq, nkv, hd, page, window, n = 1, 1, 32, 8, 24, 100
+    bt = np.arange(16, dtype=np.int32)[None]
+    for outside in (True, False):
+        kc = torch.zeros(16 * page, nkv, hd); vc = torch.zeros(16 * page, nkv, hd)
+        for j in range(n):
+            vc[j, 0, :] = 1.0
+        edge = (n - 1) - window + (0 if outside else 1)
+        kc[edge, 0, 0] = 50.0
+        vc[edge, 0, :] = -5.0
+        q = torch.zeros(1, hd); q[0, 0] = 8.0
+        out = torch.empty(1, hd, dtype=dtype, device="cuda")
+        K.paged_attention_generic(q.to(dtype).cuda(), kc.to(dtype).cuda(), vc.to(dtype).cuda(), torch.tensor(bt).cuda(), 16,
+                                  torch.zeros(1, dtype=torch.int32).cuda(), torch.tensor([n - 1], dtype=torch.int32).cuda(),
+                                  out, nq, nkv, hd, page, window, 1.0 / math.sqrt(hd))
+        got = out.float().cpu().numpy()
+        assert np.allclose(got, 1.0 if outside else -5.0, atol=2e-2), (outside, got[0, :3])
+
+
+def test_argmax_and_sampling(K):
+    from aien_sovereign_core_mv_b200.sampling import philox_uniform
+    rng = np.random.default_rng(0)
+    R, V = 6, 1537
+    logits = rng.standard_normal((R, V)).astype(np.float32) * 3
+    logits[0, 700] = logits[0, 30] = logits[0].max() + 1      # tie: the lower id wins
+    lg = torch.tensor(logits).cuda()
+    ids = torch.empty(R, dtype=torch.int32, device="cuda")
+    K.argmax_rows(lg, ids)
+    assert ids.cpu().tolist() == [pm.argmax_token(r) for r in logits]
+    temp = [0.0, 0.7, 1.0, 1.3, 0.7, 0.0005]
+    top_p = [1.0, 0.95, 1.0, 0.5, 0.9, 0.3]
+    top_k = [0, 0, 40, 0, 5, 3]
+    seeds = [11, 12, 13, 14, 15, 16]
+    rids = [1, 2, 3, 4, 2 ** 40 + 5, 6]
+    scratch = torch.empty(R * V, device="cuda")
+    for position in (0, 1, 77, 100000):
+        K.sample_rows(lg, torch.tensor(temp).cuda(), torch.tensor(top_p).cuda(), torch.tensor(top_k, dtype=torch.int32).cuda(),
+                      torch.tensor(seeds, dtype=torch.int64).cuda(), torch.tensor(rids, dtype=torch.int64).cuda(),
+                      torch.full((R,), position, dtype=torch.int32).cuda(), scratch, ids)
+        got = ids.cpu().tolist()
+        for r in range(R):
+            u = philox_uniform(seeds[r], rids[r], position)
+            assert got[r] == pm.sample_token(logits[r], temp[r], top_p[r], top_k[r], u), (position, r)
+    # the draws follow the distribution: many positions, one row
+    counts = np.zeros(V)
+    row = torch.tensor(logits[2:3]).cuda()
+    one = torch.empty(1, dtype=torch.int32, device="cuda")
+    for position in range(300):
+        K.sample_rows(row, torch.tensor([1.0]).cuda(), torch.tensor([1.0]).cuda(), torch.tensor([8], dtype=torch.int32).cuda(),
+                      torch.tensor([5], dtype=torch.int64).cuda(), torch.tensor([9], dtype=torch.int64).cuda(),
+                      torch.tensor([position], dtype=torch.int32).cuda(), scratch, one)
+        counts[one.item()] += 1
+    kept, probs = pm.kept_set(logits[2], 1.0, 1.0, 8)
+    assert counts.sum() == counts[kept].sum()
+    assert counts[int(np.argmax(logits[2]))] == counts.max()
