@@ -3,6 +3,8 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include <algorithm>
+
 #include "cache_manager.h"
 #include "scheduler.h"
 
@@ -13,7 +15,7 @@ namespace {
 
 // offsets: {"positions", "seq_of_token", "q_start", "ctx_len"} -> int offset into `buf`;
 // group_offsets[g] = (block_table_offset, slot_map_offset, max_blocks); -1 offsets are skipped.
-void fill_meta_py(const CacheManager& cm, const std::vector<int64_t>& ids, const std::vector<int>& counts,
+int fill_meta_py(const CacheManager& cm, const std::vector<int64_t>& ids, const std::vector<int>& counts,
                   py::array_t<int32_t, py::array::c_style> buf, int off_positions, int off_seq, int off_qstart,
                   int off_ctx, const std::vector<std::tuple<int, int, int>>& group_offsets) {
     auto info = buf.request(true);
@@ -42,6 +44,9 @@ void fill_meta_py(const CacheManager& cm, const std::vector<int64_t>& ids, const
         lay.max_blocks.push_back(mb);
     }
     cm.fill_meta(ids, counts, lay);
+    int max_ctx = 0;
+    for (long long i = 0; i < S; ++i) max_ctx = std::max(max_ctx, static_cast<int>(lay.ctx_len[i]));
+    return max_ctx;   // longest context in the step
 }
 
 std::vector<std::tuple<int, int, int>> copies_py(const std::vector<PageCopy>& c) {

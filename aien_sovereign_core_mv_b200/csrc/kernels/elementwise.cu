@@ -24,9 +24,18 @@ __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __r
 }
 
 // ---------------------------------------------------------------- residual add + RMSNorm
-// x[t] += delta[t] (if delta), then h[t] = x[t] * (1/sqrt(mean(x^2)+eps)) * w   (tensor.rs:94-110)
+// x[t] += sum_p delta[p][t] (if delta), then h[t] = x[t] * (1/sqrt(mean(x^2)+eps)) * w   (tensor.rs:94-110)
+// `delta` may be `nparts` float32 partial products [nparts][T][H] (the split-K decode product
+// leaves its reduction to this kernel); they are added in index order.
+template <typename TD>
+__device__ __forceinline__ float delta_sum(const TD* __restrict__ delta, int nparts, size_t part_stride, size_t idx) {
+    float d = 0.f;
+    for (int p = 0; p < nparts; ++p) d += to_f(delta[(size_t)p * part_stride + idx]);
+    return d;
+}
+
 template <typename TD, typename TO>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta,
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int nparts, size_t part_stride,
                                    const void* __restrict__ w, int wdt, float eps,
                                    TO* __restrict__ h, int H) {
     __shared__ float red[32];
@@ -35,7 +44,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float v = x[base + i];
         if (delta != nullptr) {
-            v += to_f(delta[base + i]);
+            v += delta_sum(delta, nparts, part_stride, base + i);
             x[base + i] = v;
         }
         ss += v * v;
@@ -47,28 +56,77 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
     }
 }
 
-// out[r] = x[rows[r]] + delta[rows[r]]   (float32 out; feeds the final norm of wanted rows only)
+// Same, for H % 4 == 0 and H <= 256 * 4 * NV: the row stays in registers between the passes and
+// all loads of a thread are issued before the first use.
+template <typename TD, typename TO, int NV>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int nparts, size_t part_stride,
+                       const void* __restrict__ w, int wdt, float eps, TO* __restrict__ h, int H) {
+    __shared__ float red[32];
+    const size_t base = (size_t)blockIdx.x * H;
+    float4 v[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int i = (j * 256 + threadIdx.x) * 4;
+        v[j] = i < H ? *reinterpret_cast<const float4*>(x + base + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (delta != nullptr) {
+        for (int p = 0; p < nparts; ++p) {
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                const int i = (j * 256 + threadIdx.x) * 4;
+                if (i < H) {
+                    const TD* dp = delta + (size_t)p * part_stride + base + i;
+                    v[j].x += to_f(dp[0]); v[j].y += to_f(dp[1]); v[j].z += to_f(dp[2]); v[j].w += to_f(dp[3]);
+                }
+            }
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+    const float total = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(total / (float)H + eps);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int i = (j * 256 + threadIdx.x) * 4;
+        if (i < H) {
+            if (delta != nullptr) *reinterpret_cast<float4*>(x + base + i) = v[j];
+            h[base + i + 0] = from_f<TO>(v[j].x * scale * load_dyn(w, wdt, i + 0));
+            h[base + i + 1] = from_f<TO>(v[j].y * scale * load_dyn(w, wdt, i + 1));
+            h[base + i + 2] = from_f<TO>(v[j].z * scale * load_dyn(w, wdt, i + 2));
+            h[base + i + 3] = from_f<TO>(v[j].w * scale * load_dyn(w, wdt, i + 3));
+        }
+    }
+}
+
+// out[r] = x[rows[r]] + sum_p delta[p][rows[r]]   (float32 out; feeds the final norm of wanted rows only)
 template <typename TD>
-__global__ void gather_add_rows_kernel(const float* __restrict__ x, const TD* __restrict__ delta,
-                                       const int* __restrict__ rows, float* __restrict__ out, int H) {
+__global__ void gather_add_rows_kernel(const float* __restrict__ x, const TD* __restrict__ delta, int nparts,
+                                       size_t part_stride, const int* __restrict__ rows, float* __restrict__ out, int H) {
     const size_t src = (size_t)rows[blockIdx.x] * H, dst = (size_t)blockIdx.x * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float v = x[src + i];
-        if (delta != nullptr) v += to_f(delta[src + i]);
+        if (delta != nullptr) v += delta_sum(delta, nparts, part_stride, src + i);
         out[dst + i] = v;
     }
 }
 
 // ---------------------------------------------------------------- SwiGLU
-// a = silu(g) * u, silu(g) = g / (1 + exp(-g))     (backend.rs:572-579); gu = [T, 2I], gate first
+// a = silu(g) * u, silu(g) = g / (1 + exp(-g))     (backend.rs:572-579).  gu = [T, 2I]:
+// group == 0: gate columns [0, I), up columns [I, 2I);  group > 0: columns interleaved in runs of
+// `group` (gate run, then the matching up run), the layout the fused decode product wants.
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int group, size_t total) {
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; idx < total; idx += stride) {
         const size_t t = idx / I, i = idx - t * I;
-        const float g = to_f(gu[t * 2 * I + i]);
-        const float u = to_f(gu[t * 2 * I + I + i]);
+        size_t gi, ui;
+        if (group == 0) { gi = i; ui = I + i; }
+        else { gi = (i / group) * 2 * group + (i % group); ui = gi + group; }
+        const float g = to_f(gu[t * 2 * I + gi]);
+        const float u = to_f(gu[t * 2 * I + ui]);
         out[idx] = from_f<T>(g / (1.0f + expf(-g)) * u);
     }
 }
@@ -86,15 +144,18 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const doubl
 }
 
 // ---------------------------------------------------------------- q/k norm + rotation + cache write
-// One block per token; each warp takes heads in turn.  For a q or k head: optional RMSNorm over
-// the head (tensor.rs:114-121), then rotate_half pairing (i, i + rot/2) on the first `rot`
-// values (tensor.rs:165-188).  q is written back in place; k and v go to the cache slot of the
-// token, rounded once to the cache dtype (crates/aien-kv-cache/src/lib.rs:88-101).
+// One warp per (token, head).  For a q or k head: optional RMSNorm over the head
+// (tensor.rs:114-121), then rotate_half pairing (i, i + rot/2) on the first `rot` values
+// (tensor.rs:165-188).  q goes to q_out (which may be q itself); k and v go to the cache slot of
+// the token, rounded once to the cache dtype (crates/aien-kv-cache/src/lib.rs:88-101).
+// The inputs may be `nparts` float32 partial products laid out [nparts][T][row] (split-K decode).
 #define AIEN_MAX_HEAD_DIM 256
-template <typename TC, typename TKV>
-__global__ void qk_norm_rope_kv_write_kernel(
-    TC* __restrict__ q, long q_stride, int nq,
-    const TC* __restrict__ k, long k_stride, const TC* __restrict__ v, long v_stride, int nkv,
+template <typename TI, typename TC, typename TKV>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_kv_write_kernel(
+    const TI* q, long q_stride, int nq,
+    const TI* __restrict__ k, long k_stride, const TI* __restrict__ v, long v_stride, int nkv,
+    int nparts, size_t part_stride, TC* q_out, long q_out_stride,
     int hd, const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w, int wdt, float eps,
     const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot,
     const int* __restrict__ slot_map, TKV* __restrict__ k_cache, TKV* __restrict__ v_cache) {
@@ -103,49 +164,49 @@ __global__ void qk_norm_rope_kv_write_kernel(
     const int half = rot >> 1;
     const bool write_kv = (k != nullptr);
     const int n_heads = nq + (write_kv ? 2 * nkv : 0);
+    const int head = blockIdx.y * 4 + warp;
+    if (head >= n_heads) return;
     const long slot = write_kv ? (long)slot_map[t] : -1;
     float* hb = buf[warp];
-    for (int head = warp; head < n_heads; head += 4) {
-        const bool is_q = head < nq;
-        const bool is_k = !is_q && head < nq + nkv;
-        const int hh = is_q ? head : (is_k ? head - nq : head - nq - nkv);
-        const TC* src = is_q ? (q + (size_t)t * q_stride + (size_t)hh * hd)
-                             : (is_k ? (k + (size_t)t * k_stride + (size_t)hh * hd)
-                                     : (v + (size_t)t * v_stride + (size_t)hh * hd));
-        if (!is_q && slot < 0) continue;                       // token has no cache slot
-        float ss = 0.f;
-        for (int i = lane; i < hd; i += 32) {
-            const float val = to_f(src[i]);
-            hb[i] = val;
-            ss += val * val;
+    const bool is_q = head < nq;
+    const bool is_k = !is_q && head < nq + nkv;
+    const int hh = is_q ? head : (is_k ? head - nq : head - nq - nkv);
+    if (!is_q && slot < 0) return;                               // token has no cache slot
+    const TI* src = is_q ? (q + (size_t)t * q_stride + (size_t)hh * hd)
+                         : (is_k ? (k + (size_t)t * k_stride + (size_t)hh * hd)
+                                 : (v + (size_t)t * v_stride + (size_t)hh * hd));
+    float ss = 0.f;
+    for (int i = lane; i < hd; i += 32) {
+        float val = 0.f;
+        for (int p = 0; p < nparts; ++p) val += to_f(src[(size_t)p * part_stride + i]);
+        hb[i] = val;
+        ss += val * val;
+    }
+    __syncwarp();
+    if (is_q || is_k) {
+        const void* nw = is_q ? q_norm_w : k_norm_w;
+        if (nw != nullptr) {
+            ss = warp_sum(ss);
+            const float scale = 1.0f / sqrtf(ss / (float)hd + eps);
+            for (int i = lane; i < hd; i += 32) hb[i] = hb[i] * scale * load_dyn(nw, wdt, i);
+            __syncwarp();
         }
-        __syncwarp();
-        if (is_q || is_k) {
-            const void* nw = is_q ? q_norm_w : k_norm_w;
-            if (nw != nullptr) {
-                ss = warp_sum(ss);
-                const float scale = 1.0f / sqrtf(ss / (float)hd + eps);
-                for (int i = lane; i < hd; i += 32) hb[i] = hb[i] * scale * load_dyn(nw, wdt, i);
-                __syncwarp();
+        if (cos_t != nullptr) {
+            for (int i = lane; i < half; i += 32) {
+                const float a = hb[i], b = hb[i + half];
+                const float c = cos_t[(size_t)t * half + i], s = sin_t[(size_t)t * half + i];
+                hb[i] = a * c - b * s;
+                hb[i + half] = a * s + b * c;
             }
-            if (cos_t != nullptr) {
-                for (int i = lane; i < half; i += 32) {
-                    const float a = hb[i], b = hb[i + half];
-                    const float c = cos_t[(size_t)t * half + i], s = sin_t[(size_t)t * half + i];
-                    hb[i] = a * c - b * s;
-                    hb[i + half] = a * s + b * c;
-                }
-                __syncwarp();
-            }
+            __syncwarp();
         }
-        if (is_q) {
-            TC* dst = q + (size_t)t * q_stride + (size_t)hh * hd;
-            for (int i = lane; i < hd; i += 32) dst[i] = from_f<TC>(hb[i]);
-        } else {
-            TKV* dst = (is_k ? k_cache : v_cache) + ((size_t)slot * nkv + hh) * hd;
-            for (int i = lane; i < hd; i += 32) dst[i] = from_f<TKV>(hb[i]);
-        }
-        __syncwarp();
+    }
+    if (is_q) {
+        TC* dst = q_out + (size_t)t * q_out_stride + (size_t)hh * hd;
+        for (int i = lane; i < hd; i += 32) dst[i] = from_f<TC>(hb[i]);
+    } else {
+        TKV* dst = (is_k ? k_cache : v_cache) + ((size_t)slot * nkv + hh) * hd;
+        for (int i = lane; i < hd; i += 32) dst[i] = from_f<TKV>(hb[i]);
     }
 }
 
@@ -171,28 +232,44 @@ AIEN_API int aien_embed_gather(const void* table, int table_dt, const int* ids, 
     return launch_status();
 }
 
-AIEN_API int aien_add_rmsnorm(float* x, const void* delta, int delta_dt, const void* w, int w_dt,
-                              float eps, void* h, int h_dt, int T, int H, cudaStream_t stream) {
+template <typename TD, typename TO>
+static void launch_add_rmsnorm(float* x, const TD* delta, int nparts, size_t part_stride, const void* w, int w_dt,
+                               float eps, TO* h, int T, int H, cudaStream_t stream) {
+    const bool vec = (H % 4 == 0) && (((uintptr_t)x & 15) == 0);
+    if (vec && H <= 256 * 4 * 2)
+        add_rmsnorm_vec_kernel<TD, TO, 2><<<T, 256, 0, stream>>>(x, delta, nparts, part_stride, w, w_dt, eps, h, H);
+    else if (vec && H <= 256 * 4 * 4)
+        add_rmsnorm_vec_kernel<TD, TO, 4><<<T, 256, 0, stream>>>(x, delta, nparts, part_stride, w, w_dt, eps, h, H);
+    else if (vec && H <= 256 * 4 * 8)
+        add_rmsnorm_vec_kernel<TD, TO, 8><<<T, 256, 0, stream>>>(x, delta, nparts, part_stride, w, w_dt, eps, h, H);
+    else
+        add_rmsnorm_kernel<TD, TO><<<T, row_threads(H), 0, stream>>>(x, delta, nparts, part_stride, w, w_dt, eps, h, H);
+}
+
+// delta: [nparts][T][H] (nparts >= 1; part_stride in elements) or null
+AIEN_API int aien_add_rmsnorm(float* x, const void* delta, int delta_dt, int nparts, size_t part_stride,
+                              const void* w, int w_dt, float eps, void* h, int h_dt, int T, int H, cudaStream_t stream) {
     if (T <= 0) return 0;
-    const int th = row_threads(H);
+    if (delta != nullptr && nparts < 1) return AIEN_E_SHAPE;
     AIEN_DISPATCH_DTYPE(delta_dt, TD, AIEN_DISPATCH_DTYPE(h_dt, TO,
-        (add_rmsnorm_kernel<TD, TO><<<T, th, 0, stream>>>(x, (const TD*)delta, w, w_dt, eps, (TO*)h, H))));
+        (launch_add_rmsnorm<TD, TO>(x, (const TD*)delta, nparts, part_stride, w, w_dt, eps, (TO*)h, T, H, stream))));
     return launch_status();
 }
 
-AIEN_API int aien_gather_add_rows(const float* x, const void* delta, int delta_dt, const int* rows,
-                                  float* out, int R, int H, cudaStream_t stream) {
+AIEN_API int aien_gather_add_rows(const float* x, const void* delta, int delta_dt, int nparts, size_t part_stride,
+                                  const int* rows, float* out, int R, int H, cudaStream_t stream) {
     if (R <= 0) return 0;
     AIEN_DISPATCH_DTYPE(delta_dt, TD, (gather_add_rows_kernel<TD><<<R, row_threads(H), 0, stream>>>(
-        x, (const TD*)delta, rows, out, H)));
+        x, (const TD*)delta, nparts, part_stride, rows, out, H)));
     return launch_status();
 }
 
-AIEN_API int aien_swiglu(const void* gu, void* out, int dt, int T, int I, cudaStream_t stream) {
+AIEN_API int aien_swiglu(const void* gu, void* out, int dt, int T, int I, int group, cudaStream_t stream) {
     if (T <= 0) return 0;
+    if (group < 0 || (group > 0 && I % group != 0)) return AIEN_E_SHAPE;
     const size_t total = (size_t)T * I;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    AIEN_DISPATCH_DTYPE(dt, TT, (swiglu_kernel<TT><<<blocks, 256, 0, stream>>>((const TT*)gu, (TT*)out, I, total)));
+    AIEN_DISPATCH_DTYPE(dt, TT, (swiglu_kernel<TT><<<blocks, 256, 0, stream>>>((const TT*)gu, (TT*)out, I, group, total)));
     return launch_status();
 }
 
@@ -204,17 +281,24 @@ AIEN_API int aien_rope_table(const int* positions, const double* inv_freq, float
     return launch_status();
 }
 
+// in_dt: dtype of q/k/v inputs ([nparts][T][...] when nparts > 1, float32 then); act_dt: dtype of q_out
 AIEN_API int aien_qk_norm_rope_kv_write(
-    void* q, long q_stride, int nq, const void* k, long k_stride, const void* v, long v_stride, int nkv,
+    const void* q, long q_stride, int nq, const void* k, long k_stride, const void* v, long v_stride, int nkv,
+    int in_dt, int nparts, size_t part_stride, void* q_out, long q_out_stride,
     int hd, const void* q_norm_w, const void* k_norm_w, int w_dt, float eps,
     const float* cos_t, const float* sin_t, int rot, const int* slot_map,
     void* k_cache, void* v_cache, int act_dt, int kv_dt, int T, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (hd <= 0 || hd > AIEN_MAX_HEAD_DIM || rot < 0 || rot > hd || (rot & 1)) return AIEN_E_SHAPE;
-    AIEN_DISPATCH_DTYPE(act_dt, TC, AIEN_DISPATCH_DTYPE(kv_dt, TKV,
-        (qk_norm_rope_kv_write_kernel<TC, TKV><<<T, 128, 0, stream>>>(
-            (TC*)q, q_stride, nq, (const TC*)k, k_stride, (const TC*)v, v_stride, nkv, hd,
-            q_norm_w, k_norm_w, w_dt, eps, cos_t, sin_t, rot, slot_map, (TKV*)k_cache, (TKV*)v_cache))));
+    if (hd <= 0 || hd > AIEN_MAX_HEAD_DIM || rot < 0 || rot > hd || (rot & 1) || nparts < 1) return AIEN_E_SHAPE;
+    if (T > 2147483647 / 1) return AIEN_E_SHAPE;
+    const int n_heads = nq + (k != nullptr ? 2 * nkv : 0);
+    dim3 grid(T, (n_heads + 3) / 4);
+    if (grid.y > 65535) return AIEN_E_SHAPE;
+    AIEN_DISPATCH_DTYPE(in_dt, TI, AIEN_DISPATCH_DTYPE(act_dt, TC, AIEN_DISPATCH_DTYPE(kv_dt, TKV,
+        (qk_norm_rope_kv_write_kernel<TI, TC, TKV><<<grid, 128, 0, stream>>>(
+            (const TI*)q, q_stride, nq, (const TI*)k, k_stride, (const TI*)v, v_stride, nkv, nparts, part_stride,
+            (TC*)q_out, q_out_stride, hd, q_norm_w, k_norm_w, w_dt, eps, cos_t, sin_t, rot, slot_map,
+            (TKV*)k_cache, (TKV*)v_cache)))));
     return launch_status();
 }
 

@@ -25,7 +25,7 @@ from ..config.engine_config import EngineConfig
 from ..csrc import build as _build
 from ..models.decoder import Decoder
 from ..models.loading import build_model_from_config, build_model_from_folder
-from ..parts.base import GroupView, StepContext, Workspace
+from ..parts.base import GroupView, StepContext, StepLimits, Workspace
 
 
 @dataclass
@@ -83,9 +83,8 @@ class Engine:
         # ---- workspace and metadata buffers
         itemsize = 2 if self.dtype == torch.bfloat16 else 4
         T = self.max_tokens_per_step
-        step_bytes = model.step_workspace_bytes(T, T)
-        layer_bytes = max(model.layer_workspace_bytes(T, itemsize), model.head_workspace_bytes(T, itemsize) + (1 << 16))
-        self.workspace = Workspace(step_bytes, layer_bytes, self.device)
+        self.limits = StepLimits(max_tokens=T, max_seqs=self.max_requests, max_context=self.max_context, itemsize=itemsize)
+        self.workspace = Workspace(model.step_workspace_bytes(self.limits), model.layer_workspace_bytes(self.limits), self.device)
         meta_len = self._meta_len(T, self.max_requests, T)
         # pinned staging buffers in a ring: a buffer is rewritten only after its copy has run
         self._meta_ring = []
@@ -95,6 +94,7 @@ class Engine:
         self._meta_turn = 0
         self.meta_dev = torch.empty(meta_len, dtype=torch.int32, device=self.device)
         self.steps_run = 0
+        self._graphs = {}
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -162,41 +162,11 @@ class Engine:
     def step(self, entries: Sequence, logits_out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run one batch.  ``entries``: StepEntry or (request_id, tokens, want) tuples.  Returns
         float32 logits [number of wanted places, vocab] on the device, in the order of the
-        entries and of each entry's ``want``."""
-        ents = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
-        ids, counts, want_rows, flat = [], [], [], []
-        seen = set()
-        t0 = 0
-        for e in ents:
-            rid, n = int(e.request_id), len(e.tokens)
-            if rid in seen:
-                raise ValueError(f"request {rid} appears twice in one step")
-            seen.add(rid)
-            if n == 0:
-                raise ValueError(f"request {rid}: an entry must bring at least one token")
-            for tok in e.tokens:
-                if not (0 <= int(tok) < self.vocab_size):
-                    raise ValueError(f"request {rid}: token id {tok} is outside the vocabulary of {self.vocab_size}")
-            for w in e.want:
-                if not (0 <= int(w) < n):
-                    raise ValueError(f"request {rid}: wanted place {w} is outside its {n} tokens")
-                want_rows.append(t0 + int(w))
-            have = self.cache.num_tokens(rid) if self.cache.has(rid) else 0
-            if have + n > self.max_context:
-                raise ValueError(f"request {rid}: {have + n} tokens exceed the context limit {self.max_context}")
-            ids.append(rid)
-            counts.append(n)
-            flat.extend(int(t) for t in e.tokens)
-            t0 += n
-        T, S, R = t0, len(ents), len(want_rows)
-        if T == 0:
+        entries and of each entry's ``want``.  Takes the cache pages the tokens need first; if
+        they cannot all be had, raises with nothing changed."""
+        ids, counts, flat, want_rows = self._validate(entries)
+        if not ids:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
-        if T > self.max_tokens_per_step:
-            raise ValueError(f"step of {T} tokens exceeds max_batch_tokens {self.max_tokens_per_step}")
-        if S > self.max_requests:
-            raise ValueError(f"step of {S} requests exceeds max_requests {self.max_requests}")
-
-        # ---- cache: all or nothing
         added = []
         try:
             for rid in ids:
@@ -209,8 +179,48 @@ class Engine:
                 self.cache.free_request(rid)
             raise
         self._do_copies(copies)
+        return self.run_reserved(ids, counts, flat, want_rows, logits_out)
 
-        # ---- metadata: one pinned buffer, one copy
+    def _validate(self, entries: Sequence):
+        ids, counts, want_rows, chunks = [], [], [], []
+        seen = set()
+        t0 = 0
+        for e in entries:
+            rid, toks, want = (e.request_id, e.tokens, e.want) if isinstance(e, StepEntry) else (e[0], e[1], e[2] if len(e) > 2 else ())
+            rid = int(rid)
+            arr = np.asarray(toks, dtype=np.int64).reshape(-1)
+            n = int(arr.shape[0])
+            if rid in seen:
+                raise ValueError(f"request {rid} appears twice in one step")
+            seen.add(rid)
+            if n == 0:
+                raise ValueError(f"request {rid}: an entry must bring at least one token")
+            if int(arr.min()) < 0 or int(arr.max()) >= self.vocab_size:
+                bad = int(arr[(arr < 0) | (arr >= self.vocab_size)][0])
+                raise ValueError(f"request {rid}: token id {bad} is outside the vocabulary of {self.vocab_size}")
+            for w in want:
+                if not (0 <= int(w) < n):
+                    raise ValueError(f"request {rid}: wanted place {w} is outside its {n} tokens")
+                want_rows.append(t0 + int(w))
+            have = self.cache.num_tokens(rid) if self.cache.has(rid) else 0
+            if have + n > self.max_context:
+                raise ValueError(f"request {rid}: {have + n} tokens exceed the context limit {self.max_context}")
+            ids.append(rid)
+            counts.append(n)
+            chunks.append(arr)
+            t0 += n
+        if t0 > self.max_tokens_per_step:
+            raise ValueError(f"step of {t0} tokens exceeds max_batch_tokens {self.max_tokens_per_step}")
+        if len(ids) > self.max_requests:
+            raise ValueError(f"step of {len(ids)} requests exceeds max_requests {self.max_requests}")
+        flat = np.concatenate(chunks).astype(np.int32) if chunks else np.zeros(0, dtype=np.int32)
+        return ids, counts, flat, want_rows
+
+    def run_reserved(self, ids, counts, flat, want_rows, logits_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The part of a step after its pages were taken (the scheduler takes them itself):
+        metadata to the device in one copy, then the model.  Decode-only steps that want every
+        row replay a captured CUDA graph."""
+        T, S, R = int(sum(counts)), len(ids), len(want_rows)
         off, total = self._layout(T, S, R)
         slot = self._meta_ring[self._meta_turn % len(self._meta_ring)]
         self._meta_turn += 1
@@ -220,20 +230,62 @@ class Engine:
         m[off["token_ids"]:off["token_ids"] + T] = flat
         if R:
             m[off["want_rows"]:off["want_rows"] + R] = want_rows
-        self.cache.fill_meta(ids, counts, m, off["positions"], off["seq_of_token"], off["q_start"], off["ctx_len"], off["groups"])
+        max_ctx = self.cache.fill_meta(ids, counts, m, off["positions"], off["seq_of_token"], off["q_start"], off["ctx_len"], off["groups"])
         self.meta_dev[:total].copy_(meta_host[:total], non_blocking=True)
         if slot[2] is None:
             slot[2] = torch.cuda.Event()
         slot[2].record()
-        ctx = self._context(off, T, S, max(counts), decode_only=all(c == 1 for c in counts))
+        decode_only = T == S
+        self.steps_run += 1
+        if (decode_only and R == T and self.cfg.use_cuda_graphs and self.dtype == torch.bfloat16
+                and want_rows == list(range(T))):
+            return self._replay_decode(off, T, max_ctx, logits_out)
+        ctx = self._context(off, T, S, max(counts), max_ctx, decode_only)
         if logits_out is None:
             logits_out = torch.empty((R, self.vocab_size), dtype=torch.float32, device=self.device)
         d = self.meta_dev
         self.model.forward(ctx, d[off["want_rows"]:off["want_rows"] + max(R, 1)], R, logits_out)
-        self.steps_run += 1
         return logits_out
 
-    def _context(self, off, T: int, S: int, max_q: int, decode_only: bool) -> StepContext:
+    # ------------------------------------------------------------------ captured decode steps
+    def _replay_decode(self, off, T: int, max_ctx: int, logits_out: Optional[torch.Tensor]) -> torch.Tensor:
+        """Decode steps are short chains of small kernels; launching them one by one costs more
+        than running them.  One CUDA graph per (batch size, key-chunk count) is captured at first
+        use and replayed afterwards; its inputs are the metadata buffer, its output a logits
+        buffer of its own."""
+        from ..kernels import DECODE_CHUNK
+        splits = 1
+        while splits * DECODE_CHUNK < max_ctx:
+            splits *= 2
+        key = (T, splits)
+        entry = self._graphs.get(key)
+        if entry is None:
+            logits = torch.empty((T, self.vocab_size), dtype=torch.float32, device=self.device)
+            d = self.meta_dev
+
+            def run():
+                ctx = self._context(off, T, T, 1, splits * DECODE_CHUNK, True)
+                self.model.forward(ctx, d[off["want_rows"]:off["want_rows"] + T], T, logits)
+
+            run()                                         # warm-up outside capture (lazy tables, attributes)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = K.launch_count()
+            with torch.cuda.graph(graph):
+                run()
+            entry = (graph, logits, K.launch_count() - before)
+            if len(self._graphs) >= 48:
+                self._graphs.pop(next(iter(self._graphs)))
+            self._graphs[key] = entry
+        graph, logits, nodes = entry
+        graph.replay()
+        K.add_launches(nodes)
+        if logits_out is not None:
+            logits_out.copy_(logits)
+            return logits_out
+        return logits
+
+    def _context(self, off, T: int, S: int, max_q: int, max_ctx: int, decode_only: bool) -> StepContext:
         d = self.meta_dev
         groups = []
         for g, need in enumerate(self.model.group_needs):
@@ -249,7 +301,7 @@ class Engine:
             token_ids=d[off["token_ids"]:off["token_ids"] + T], positions=d[off["positions"]:off["positions"] + T],
             seq_of_token=d[off["seq_of_token"]:off["seq_of_token"] + T], q_start=d[off["q_start"]:off["q_start"] + S + 1],
             ctx_len=d[off["ctx_len"]:off["ctx_len"] + S], groups=groups, workspace=self.workspace,
-            max_q_len=max_q, decode_only=decode_only,
+            max_q_len=max_q, max_ctx_len=max_ctx, decode_only=decode_only,
         )
 
     # ------------------------------------------------------------------ information

@@ -45,16 +45,18 @@ def _declare(l: ctypes.CDLL) -> None:
     P, I, L, F = c_void_p, c_int, c_long, c_float
     sigs = {
         "aien_embed_gather": [P, I, P, P, I, I, I, P],
-        "aien_add_rmsnorm": [P, P, I, P, I, F, P, I, I, I, P],
-        "aien_gather_add_rows": [P, P, I, P, P, I, I, P],
-        "aien_swiglu": [P, P, I, I, I, P],
+        "aien_add_rmsnorm": [P, P, I, I, c_size_t, P, I, F, P, I, I, I, P],
+        "aien_gather_add_rows": [P, P, I, I, c_size_t, P, P, I, I, P],
+        "aien_swiglu": [P, P, I, I, I, I, P],
         "aien_rope_table": [P, P, P, P, I, I, P],
-        "aien_qk_norm_rope_kv_write": [P, L, I, P, L, P, L, I, I, P, P, I, F, P, P, I, P, P, P, I, I, I, P],
+        "aien_qk_norm_rope_kv_write": [P, L, I, P, L, P, L, I, I, I, c_size_t, P, L, I, P, P, I, F, P, P, I, P, P, P, I, I, I, P],
         "aien_convert": [P, I, P, I, c_size_t, P],
         "aien_gemm_simple": [P, I, L, P, I, L, P, I, L, I, I, I, P],
         "aien_paged_attention_generic": [P, L, P, P, P, I, P, P, P, L, I, I, I, I, I, F, I, I, I, P],
         "aien_argmax_rows": [P, I, I, P, P],
         "aien_sample_rows": [P, I, I, P, P, P, P, P, P, P, P, P],
+        "aien_gemv_bf16": [P, L, P, L, P, I, L, I, I, I, I, I, c_size_t, P],
+        "aien_paged_attention_decode": [P, L, P, P, P, I, P, P, P, L, P, P, I, I, I, I, I, F, I, I, P],
     }
     for name, args in sigs.items():
         fn = getattr(l, name)
@@ -74,8 +76,23 @@ def declare_optional(name: str, args) -> bool:
     return True
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernel launches issued through this module so far (replayed graph nodes included)."""
+    return _launches
+
+
+def add_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
 def _check(rc: int, name: str) -> None:
+    global _launches
     if rc == 0:
+        _launches += 2 if name == "paged_attention_decode" else 1
         return
     if rc < 0:
         raise KernelError(f"{name}: {_ERRORS.get(rc, 'refused')} (code {rc})")
@@ -113,16 +130,27 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, x: torch.Tensor) -> Non
     _check(lib().aien_embed_gather(_p(table), dt(table), _p(ids), _p(x), T, H, table.shape[0], _stream()), "embed_gather")
 
 
+def _parts_of(delta: Optional[torch.Tensor], shape) -> tuple:
+    """(nparts, stride in elements) of a pending sum: [T,H], or float32 partials [P,T,H]."""
+    if delta is None:
+        return 1, 0
+    assert delta.is_contiguous()
+    if delta.dim() == 3:
+        assert tuple(delta.shape[1:]) == tuple(shape) and delta.dtype == torch.float32
+        return delta.shape[0], delta.shape[1] * delta.shape[2]
+    assert tuple(delta.shape) == tuple(shape)
+    return 1, 0
+
+
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
     """x += delta (when given); out = rmsnorm(x) * weight.  x float32 [T,H] updated in place."""
     _dev(x, delta, weight, out)
     T, H = x.shape
     assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and out.shape == x.shape
     assert weight.numel() == H and weight.is_contiguous()
-    if delta is not None:
-        assert delta.shape == x.shape and delta.is_contiguous()
-    _check(lib().aien_add_rmsnorm(_p(x), _p(delta), dt(delta) if delta is not None else F32, _p(weight), dt(weight),
-                                  float(eps), _p(out), dt(out), T, H, _stream()), "add_rmsnorm")
+    nparts, stride = _parts_of(delta, x.shape)
+    _check(lib().aien_add_rmsnorm(_p(x), _p(delta), dt(delta) if delta is not None else F32, nparts, stride,
+                                  _p(weight), dt(weight), float(eps), _p(out), dt(out), T, H, _stream()), "add_rmsnorm")
 
 
 def gather_add_rows(x: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor, out: torch.Tensor) -> None:
@@ -131,18 +159,18 @@ def gather_add_rows(x: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.
     R, H = out.shape
     assert x.dtype == torch.float32 and out.dtype == torch.float32 and rows.dtype == torch.int32
     assert x.is_contiguous() and out.is_contiguous() and x.shape[1] == H and rows.numel() >= R
-    if delta is not None:
-        assert delta.shape == x.shape and delta.is_contiguous()
-    _check(lib().aien_gather_add_rows(_p(x), _p(delta), dt(delta) if delta is not None else F32, _p(rows), _p(out),
-                                      R, H, _stream()), "gather_add_rows")
+    nparts, stride = _parts_of(delta, x.shape)
+    _check(lib().aien_gather_add_rows(_p(x), _p(delta), dt(delta) if delta is not None else F32, nparts, stride,
+                                      _p(rows), _p(out), R, H, _stream()), "gather_add_rows")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out = silu(gate) * up for gate_up = [T, 2I] (gate columns first)."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, group: int = 0) -> None:
+    """out = silu(gate) * up for gate_up = [T, 2I]: gate columns first (group 0), or gate and up
+    columns interleaved in runs of ``group``."""
     _dev(gate_up, out)
     T, I = out.shape
     assert gate_up.shape == (T, 2 * I) and gate_up.is_contiguous() and out.is_contiguous() and gate_up.dtype == out.dtype
-    _check(lib().aien_swiglu(_p(gate_up), _p(out), dt(out), T, I, _stream()), "swiglu")
+    _check(lib().aien_swiglu(_p(gate_up), _p(out), dt(out), T, I, int(group), _stream()), "swiglu")
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> None:
@@ -158,21 +186,30 @@ def qk_norm_rope_kv_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optiona
                           q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], eps: float,
                           cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int,
                           slot_map: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
-                          v_cache: Optional[torch.Tensor]) -> None:
+                          v_cache: Optional[torch.Tensor], q_out: Optional[torch.Tensor] = None) -> None:
     """Per-head RMSNorm of q and k (when weights are given), rotation of the first
-    ``rotary_dim`` values, q written back in place, k and v written to their cache slots.
-    q [T, nq*hd], k/v [T, nkv*hd] may be column slices of one projection output."""
-    _dev(q, k, v, q_norm_w, k_norm_w, cos, sin, slot_map, k_cache, v_cache)
-    T = q.shape[0]
-    assert q.stride(1) == 1 and q.shape[1] % head_dim == 0
-    nq = q.shape[1] // head_dim
+    ``rotary_dim`` values, q written to ``q_out`` (default: in place), k and v written to their
+    cache slots.  q [T, nq*hd], k/v [T, nkv*hd] may be column slices of one projection output, or
+    of float32 partial products [P, T, ...] that are summed on the way in (then q_out is needed)."""
+    _dev(q, k, v, q_norm_w, k_norm_w, cos, sin, slot_map, k_cache, v_cache, q_out)
+    nparts, part_stride = 1, 0
+    if q.dim() == 3:
+        assert q.dtype == torch.float32 and q_out is not None
+        nparts, part_stride = q.shape[0], q.stride(0)
+        if k is not None:
+            assert k.dim() == 3 and v.dim() == 3 and k.stride(0) == part_stride and v.stride(0) == part_stride
+    if q_out is None:
+        q_out = q
+    T = q.shape[-2]
+    assert q.stride(-1) == 1 and q.shape[-1] % head_dim == 0 and q_out.stride(1) == 1 and q_out.shape == (T, q.shape[-1])
+    nq = q.shape[-1] // head_dim
     nkv = 0
     if k is not None:
         assert v is not None and slot_map is not None and k_cache is not None and v_cache is not None
-        assert k.stride(1) == 1 and v.stride(1) == 1 and k.dtype == q.dtype and v.dtype == q.dtype
+        assert k.stride(-1) == 1 and v.stride(-1) == 1 and k.dtype == q.dtype and v.dtype == q.dtype
         assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.dtype == v_cache.dtype
         assert slot_map.dtype == torch.int32 and slot_map.numel() >= T
-        nkv = k.shape[1] // head_dim
+        nkv = k.shape[-1] // head_dim
     wdt = F32
     for w in (q_norm_w, k_norm_w):
         if w is not None:
@@ -183,10 +220,10 @@ def qk_norm_rope_kv_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optiona
     if cos is not None:
         assert sin is not None and cos.shape == (T, rotary_dim // 2) and cos.is_contiguous() and sin.is_contiguous()
     _check(lib().aien_qk_norm_rope_kv_write(
-        _p(q), q.stride(0), nq, _p(k), k.stride(0) if k is not None else 0, _p(v), v.stride(0) if v is not None else 0,
-        nkv, head_dim, _p(q_norm_w), _p(k_norm_w), wdt, float(eps), _p(cos), _p(sin), rotary_dim if cos is not None else 0,
-        _p(slot_map), _p(k_cache), _p(v_cache), dt(q), dt(k_cache) if k_cache is not None else dt(q), T, _stream()),
-        "qk_norm_rope_kv_write")
+        _p(q), q.stride(-2), nq, _p(k), k.stride(-2) if k is not None else 0, _p(v), v.stride(-2) if v is not None else 0,
+        nkv, dt(q), nparts, part_stride, _p(q_out), q_out.stride(0), head_dim, _p(q_norm_w), _p(k_norm_w), wdt, float(eps),
+        _p(cos), _p(sin), rotary_dim if cos is not None else 0, _p(slot_map), _p(k_cache), _p(v_cache),
+        dt(q_out), dt(k_cache) if k_cache is not None else dt(q_out), T, _stream()), "qk_norm_rope_kv_write")
 
 
 def convert(src: torch.Tensor, dst: torch.Tensor) -> None:
@@ -247,26 +284,93 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Te
                                   _p(positions), _p(scratch), _p(out_ids), _stream()), "sample_rows")
 
 
-# ---------------------------------------------------------------------------- kernel choice
-GEMV_MAX_ROWS = 0          # raised when the decode product kernel is present
+# ---------------------------------------------------------------------------- decode product
+GEMV_MAX_ROWS = 16
 
 
 def gemv_supports(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
-    return False
+    K_ = a.shape[1]
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[0] <= GEMV_MAX_ROWS and K_ % 8 == 0
+            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1)
+
+
+def gemv_splits(N: int, K_: int) -> int:
+    """How many ranges K is cut into across CTAs, from the weight's shape alone (never from the
+    batch): enough CTAs to fill the GPU when the matrix has few rows."""
+    tiles = (N + 15) // 16
+    return max(1, min(8, 1184 // tiles, K_ // 512))
+
+
+def gemv(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0) -> None:
+    """out = a . w^T for up to 16 rows of a (bfloat16, float32 accumulation).  ``epilogue=1``:
+    w holds gate|up rows interleaved in groups of 8 and out = silu(gate)*up with N/2 columns.
+    ``out`` of shape [P, M, N] float32 receives P partial products over P ranges of K."""
+    _dev(a, w, out)
+    M, K_ = a.shape
+    N = w.shape[0]
+    splits, part_stride = 1, 0
+    if out.dim() == 3:
+        assert epilogue == 0 and out.dtype == torch.float32 and out.is_contiguous() and tuple(out.shape[1:]) == (M, N)
+        splits, part_stride = out.shape[0], M * N
+    else:
+        assert w.shape[1] == K_ and out.shape == (M, N if epilogue == 0 else N // 2)
+    _check(lib().aien_gemv_bf16(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), dt(out), out.stride(-2), M, N, K_,
+                                epilogue, splits, part_stride, _stream()), "gemv_bf16")
 
 
 def gemm_tc_supports(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
     return False
 
 
-def attention_workspace_bytes(max_tokens: int, num_heads: int, head_dim: int) -> int:
-    return 0
+# ---------------------------------------------------------------------------- attention choice
+DECODE_CHUNK = 256
+
+
+def attention_workspace_bytes(lim, num_heads: int, head_dim: int) -> int:
+    """Scratch of the split-key decode kernel for the largest decode-only step."""
+    splits = (lim.max_context + DECODE_CHUNK - 1) // DECODE_CHUNK
+    return lim.max_seqs * num_heads * splits * (head_dim + 2) * 4 + 1024
+
+
+def paged_attention_decode(q, k_cache, v_cache, block_table, max_blocks, seq_of_token, positions, out,
+                           part_out, part_ml, num_q_heads, num_kv_heads, head_dim, page_size, window, scale,
+                           max_splits) -> None:
+    _dev(q, k_cache, v_cache, block_table, seq_of_token, positions, out, part_out, part_ml)
+    T = q.shape[0]
+    assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert q.stride(1) == 1 and out.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert part_out.dtype == torch.float32 and part_out.numel() >= T * num_q_heads * max_splits * head_dim
+    assert part_ml.dtype == torch.float32 and part_ml.numel() >= T * num_q_heads * max_splits * 2
+    _check(lib().aien_paged_attention_decode(
+        _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), max_blocks, _p(seq_of_token), _p(positions),
+        _p(out), out.stride(0), _p(part_out), _p(part_ml), num_q_heads, num_kv_heads, head_dim, page_size, window,
+        float(scale), max_splits, T, _stream()), "paged_attention_decode")
+
+
+def decode_attention_supports(q: torch.Tensor, k_cache: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int) -> bool:
+    return (q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256
+            and num_q_heads // num_kv_heads <= 16 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0)
+
+
+_FORCE_ATTN = __import__("os").environ.get("AIEN_B200_ATTENTION", "").strip().lower()
 
 
 def paged_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, group, out: torch.Tensor,
                     num_q_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float) -> None:
-    """Attention of the step's tokens over one cache group; picks the kernel for the step."""
+    """Attention of the step's tokens over one cache group; picks the kernel for the step:
+    the split-key kernel when every request brings one token (bfloat16), else the generic one.
+    ``AIEN_B200_ATTENTION=generic`` pins the generic kernel for debugging."""
     k2 = k_cache.view(-1, num_kv_heads, head_dim)
     v2 = v_cache.view(-1, num_kv_heads, head_dim)
+    if (ctx.decode_only and _FORCE_ATTN != "generic"
+            and decode_attention_supports(q, k2, num_q_heads, num_kv_heads, head_dim)):
+        T = q.shape[0]
+        splits = max(1, (ctx.max_ctx_len + DECODE_CHUNK - 1) // DECODE_CHUNK)
+        part_out = ctx.workspace.take((T * num_q_heads * splits * head_dim,), torch.float32)
+        part_ml = ctx.workspace.take((T * num_q_heads * splits * 2,), torch.float32)
+        paged_attention_decode(q, k2, v2, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, out,
+                               part_out, part_ml, num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale, splits)
+        return
     paged_attention_generic(q, k2, v2, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, out,
                             num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale)

@@ -140,18 +140,16 @@ class Decoder:
             raise RuntimeError("bind: some parts did not receive all their tensors")
 
     # ------------------------------------------------------------------ sizes
-    def layer_workspace_bytes(self, max_tokens: int, itemsize: int) -> int:
-        return max(b.workspace_bytes(max_tokens, itemsize) for b in self.blocks) + (1 << 16)
+    def layer_workspace_bytes(self, lim) -> int:
+        head = lim.max_tokens * self.hidden_size * (4 + lim.itemsize) + 4096
+        return max(max(b.workspace_bytes(lim) for b in self.blocks), head) + (1 << 16)
 
-    def step_workspace_bytes(self, max_tokens: int, max_rows: int) -> int:
-        n = max_tokens * self.hidden_size * 4 + 4096
+    def step_workspace_bytes(self, lim) -> int:
+        n = lim.max_tokens * self.hidden_size * 4 + 4096
         for p in self._positions.values():
             if hasattr(p, "step_workspace_bytes"):
-                n += p.step_workspace_bytes(max_tokens)
+                n += p.step_workspace_bytes(lim.max_tokens)
         return n
-
-    def head_workspace_bytes(self, max_rows: int, itemsize: int) -> int:
-        return max_rows * self.hidden_size * (4 + itemsize) + 4096
 
     # ------------------------------------------------------------------ one step
     def forward(self, ctx: StepContext, want_rows: torch.Tensor, num_rows: int, logits: torch.Tensor) -> torch.Tensor:

@@ -64,9 +64,10 @@ class PagedAttention(Mixer):
     def cache_need(self):
         return CacheNeed("window" if self.window > 0 else "full", self.window, self.num_kv_heads, self.head_dim)
 
-    def workspace_bytes(self, max_tokens, itemsize):
-        return max_tokens * (self.q_dim + 2 * self.kv_dim + self.q_dim + self.hidden_size) * itemsize + 1024 \
-            + K.attention_workspace_bytes(max_tokens, self.num_heads, self.head_dim)
+    def workspace_bytes(self, lim):
+        return lim.max_tokens * (2 * self.q_dim + 2 * self.kv_dim + self.q_dim + self.hidden_size) * lim.itemsize + 4096 \
+            + 8 * K.GEMV_MAX_ROWS * (self.q_dim + 2 * self.kv_dim + self.hidden_size) * 4 \
+            + K.attention_workspace_bytes(lim, self.num_heads, self.head_dim)
 
     # ---- one step
     def forward(self, ctx: StepContext, h: torch.Tensor, run: RunBinding) -> torch.Tensor:
@@ -75,20 +76,21 @@ class PagedAttention(Mixer):
         planes = group.storage[run.slot]                 # [2, tokens, nkv, hd]
         k_cache, v_cache = planes[0], planes[1]
         if run.writes:
-            qkv = linear(ctx, h, self.w_qkv)
-            q, k, v = qkv[:, :self.q_dim], qkv[:, self.q_dim:self.q_dim + self.kv_dim], qkv[:, self.q_dim + self.kv_dim:]
+            qkv = linear(ctx, h, self.w_qkv, may_defer_sum=True)
+            q, k, v = qkv[..., :self.q_dim], qkv[..., self.q_dim:self.q_dim + self.kv_dim], qkv[..., self.q_dim + self.kv_dim:]
         else:
-            q = linear(ctx, h, self.w_qkv[:self.q_dim])
+            q = linear(ctx, h, self.w_qkv[:self.q_dim], may_defer_sum=True)
             k = v = None
+        q_out = ctx.workspace.take((T, self.q_dim), ctx.dtype) if q.dim() == 3 else q
         rot = self.position.rotary(ctx)
         cos, sin, rdim = rot if rot is not None else (None, None, 0)
-        if rot is None:
-            self.position.apply(ctx, q, k)
         K.qk_norm_rope_kv_write(q, k, v, self.head_dim, self.q_norm_w, self.k_norm_w if k is not None else None,
                                 self.qk_norm_eps, cos, sin, rdim,
                                 group.slot_map if k is not None else None,
-                                k_cache if k is not None else None, v_cache if k is not None else None)
+                                k_cache if k is not None else None, v_cache if k is not None else None, q_out=q_out)
+        if rot is None:
+            self.position.apply(ctx, q_out, group, run)
         out = ctx.workspace.take((T, self.q_dim), ctx.dtype)
-        K.paged_attention(ctx, q, k_cache, v_cache, group, out, self.num_heads, self.num_kv_heads, self.head_dim,
+        K.paged_attention(ctx, q_out, k_cache, v_cache, group, out, self.num_heads, self.num_kv_heads, self.head_dim,
                           self.window, self.scale)
-        return linear(ctx, out, self.w_o)
+        return linear(ctx, out, self.w_o, may_defer_sum=True)

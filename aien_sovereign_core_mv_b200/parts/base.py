@@ -87,6 +87,16 @@ class StepContext:
     shared: Dict[Any, Any] = field(default_factory=dict)   # per-step memo (rotary tables ...)
 
 
+@dataclass(frozen=True)
+class StepLimits:
+    """The largest step the engine will run; parts size their scratch from it."""
+
+    max_tokens: int
+    max_seqs: int
+    max_context: int
+    itemsize: int          # bytes of the compute dtype
+
+
 class Workspace:
     """Scratch for one step, carved from one device buffer so that a step allocates nothing
     and its addresses repeat (which a captured CUDA graph needs).
@@ -148,8 +158,8 @@ class Part:
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         """Receive the tensors named by param_shapes (device tensors, stored dtype kept)."""
 
-    def workspace_bytes(self, max_tokens: int, itemsize: int) -> int:
-        """Upper bound of what forward() takes from the workspace for `max_tokens` tokens."""
+    def workspace_bytes(self, lim: "StepLimits") -> int:
+        """Upper bound of what forward() takes from the layer workspace within `lim`."""
         return 0
 
 
@@ -162,7 +172,9 @@ class Position(Part):
     def rotary(self, ctx: StepContext):
         return None
 
-    def apply(self, ctx: StepContext, q: torch.Tensor, k: Optional[torch.Tensor]) -> None:
+    def apply(self, ctx: StepContext, q: torch.Tensor, group: "GroupView", run: "RunBinding") -> None:
+        """Called instead of the fused rotation when rotary() returns None: may change q in
+        place (and what the run just wrote into its cache slots)."""
         raise NotImplementedError
 
 

@@ -21,8 +21,8 @@ class PreNormBlock(Block):
     def parts(self):
         return {"norm_in": self.norm_in, "mixer": self.mixer, "norm_post": self.norm_post, "feed_forward": self.feed_forward}
 
-    def workspace_bytes(self, max_tokens, itemsize):
-        return sum(p.workspace_bytes(max_tokens, itemsize) for p in self.parts().values())
+    def workspace_bytes(self, lim):
+        return sum(p.workspace_bytes(lim) for p in self.parts().values())
 
     def forward(self, ctx: StepContext, x: torch.Tensor, delta: Optional[torch.Tensor], run: RunBinding) -> torch.Tensor:
         h = self.norm_in.forward(ctx, x, delta)

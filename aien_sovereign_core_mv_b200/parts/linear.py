@@ -19,9 +19,21 @@ _FORCE = os.environ.get("AIEN_B200_GEMM", "").strip().lower()
 
 
 def linear(ctx: StepContext, a: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-           out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """a [M, K] (row stride free), w [N, K] -> [M, N] taken from the step workspace."""
+           out: Optional[torch.Tensor] = None, may_defer_sum: bool = False) -> torch.Tensor:
+    """a [M, K] (row stride free), w [N, K] -> [M, N] taken from the step workspace.
+
+    ``may_defer_sum``: the caller's consumer can add partial products, so the decode kernel may
+    cut K across CTAs and return float32 partials [P, M, N] instead (the norm kernel, the q/k
+    kernel and the row gather add them in order)."""
     M, N = a.shape[0], w.shape[0]
+    if out is None and may_defer_sum and not _FORCE and M <= K.GEMV_MAX_ROWS and a.dtype == torch.bfloat16 \
+            and w.dtype == torch.bfloat16:
+        splits = K.gemv_splits(N, a.shape[1])
+        if splits > 1:
+            parts = ctx.workspace.take((splits, M, N), torch.float32)
+            if K.gemv_supports(a, w, parts):
+                K.gemv(a, w, parts)
+                return parts
     if out is None:
         out = ctx.workspace.take((M, N), out_dtype or a.dtype)
     choice = _FORCE or _choose(a, w, out, M)

@@ -23,18 +23,30 @@ class SwiGLU(FeedForward):
         H, I = self.hidden_size, self.intermediate_size
         return {"gate_proj": ((I, H), "matrix"), "up_proj": ((I, H), "matrix"), "down_proj": ((H, I), "matrix")}
 
+    GROUP = 8      # gate and up rows interleaved in runs of 8: one decode-kernel tile holds both
+
     def bind(self, tensors):
         g, u = tensors["gate_proj"], tensors["up_proj"]
         if g.dtype != u.dtype:
             g, u = g.float(), u.float()
-        self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
+        I, H = self.intermediate_size, self.hidden_size
+        self.group = self.GROUP if (g.dtype == torch.bfloat16 and I % self.GROUP == 0) else 0
+        if self.group:
+            n = I // self.group
+            self.w_gate_up = torch.stack([g.view(n, self.group, H), u.view(n, self.group, H)], dim=1).reshape(2 * I, H).contiguous()
+        else:
+            self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
         self.w_down = tensors["down_proj"].contiguous()
 
-    def workspace_bytes(self, max_tokens, itemsize):
-        return max_tokens * (3 * self.intermediate_size + self.hidden_size) * itemsize + 1024
+    def workspace_bytes(self, lim):
+        return lim.max_tokens * (3 * self.intermediate_size + self.hidden_size) * lim.itemsize + 4096 \
+            + 8 * K.GEMV_MAX_ROWS * self.hidden_size * 4
 
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
-        gu = linear(ctx, h, self.w_gate_up)
         act = ctx.workspace.take((ctx.num_tokens, self.intermediate_size), ctx.dtype)
-        K.swiglu(gu, act)
-        return linear(ctx, act, self.w_down)
+        if self.group == 8 and h.shape[0] <= K.GEMV_MAX_ROWS and K.gemv_supports(h, self.w_gate_up, act):
+            K.gemv(h, self.w_gate_up, act, epilogue=1)          # silu(gate)*up inside the product
+        else:
+            gu = linear(ctx, h, self.w_gate_up)
+            K.swiglu(gu, act, self.group)
+        return linear(ctx, act, self.w_down, may_defer_sum=True)

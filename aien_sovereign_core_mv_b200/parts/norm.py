@@ -27,8 +27,8 @@ class RMSNorm(Norm):
     def bind(self, tensors):
         self.weight = tensors["weight"].contiguous()
 
-    def workspace_bytes(self, max_tokens, itemsize):
-        return max_tokens * self.size * itemsize + 256
+    def workspace_bytes(self, lim):
+        return lim.max_tokens * self.size * lim.itemsize + 256
 
     def forward(self, ctx: StepContext, x: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
         out = ctx.workspace.take(tuple(x.shape), ctx.dtype)

@@ -79,5 +79,5 @@ class NoPosition(Position):
     def rotary(self, ctx):
         return None
 
-    def apply(self, ctx, q, k):
+    def apply(self, ctx, q, group, run):
         return None

@@ -1,0 +1,289 @@
+#!/usr/bin/env python3
+"""Headline measurement: decode tokens per second of the Qwen3-8B-shaped model on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers N]
+
+A step is one decode step of a batch of requests that each hold a 1,024-token prompt (context
+limit 4,096, pages of 16 tokens), random bfloat16 weights, synthetic uniform token ids.  One JSON
+line is printed:
+
+* ``value``      decoded tokens per second at the default batch, timed on the device with CUDA
+                 events around exactly K steps after W warm-up steps;
+* ``e2e``        the same through the Python entry point (scheduler, sampling, token ids from and
+                 to the host every step);
+* ``prefill``    one 2,048-token prompt in one step: tokens per second and the fraction of the
+                 bfloat16 tensor peak its flops reach;
+* ``roofline``   bytes a decode step must read (every weight once, the cache of the live
+                 requests) per second against the measured copy bandwidth;
+* ``points``     decode tokens per second at batch 1 and 64.
+
+Peaks come from ``MEASURED_PEAKS.json`` beside this file when present, else from the fallback
+measured earlier on the same pool (6.65 TB/s, 1.59 PFLOP/s).  The weights of one step (15 GB) are
+far larger than the 126 MB L2, so consecutive steps cannot be served from cache.
+``--impl reference`` reports that the reference (a Rust workspace) cannot be installed here.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=36, hidden_size=4096,
+    num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=151936,
+    rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=40960,
+    hidden_act="silu", attention_bias=False, eos_token_id=151645,
+)
+PROMPT_LEN, CONTEXT, PAGE, PREFILL_TOKENS, SEED = 1024, 4096, 16, 2048, 2
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    hbm, tf, src = 6650.0, 1590.0, "fallback"
+    if os.path.exists(path):
+        try:
+            with open(path) as f:
+                p = json.load(f)
+            hbm = float(p.get("hbm_gbs", hbm))
+            tf = float(p.get("bf16_tflops", tf))
+            src = "measured"
+        except Exception:
+            pass
+    return hbm, tf, src
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_numbers(cfg, layers_run):
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    Q = cfg["num_attention_heads"] * cfg["head_dim"]
+    KV = cfg["num_key_value_heads"] * cfg["head_dim"]
+    per_layer = (Q + 2 * KV) * H + H * Q + 2 * I * H + H * I
+    linear_params = per_layer * layers_run + V * H                       # matrices a decode step reads
+    norm_params = layers_run * (2 * H + (2 * cfg["head_dim"] if cfg["architectures"][0] == "Qwen3ForCausalLM" else 0)) + H
+    kv_bytes_per_token = 2 * KV * 2 * layers_run
+    return dict(per_layer=per_layer, linear_params=linear_params, weight_bytes=2 * (linear_params + norm_params),
+                kv_bytes_per_token=kv_bytes_per_token, Q=Q, KV=KV)
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (0 = all)")
+    ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--skip-prefill", action="store_true")
+    ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--fill", default="prefill", choices=["prefill", "cache"],
+                    help="how requests get their prompt: real prefill, or (development only) cache pages "
+                         "filled with random keys/values without running the model")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Rust workspace without setup.py/pyproject.toml; pip cannot install it and no cargo/rustc exists here"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (use --gpus 1)")
+        return 2
+    warmup, steps = max(3, args.warmup), max(1, args.steps)
+
+    import numpy as np
+    import torch
+    from aien_sovereign_core_mv_b200 import Engine, EngineConfig
+    from aien_sovereign_core_mv_b200 import kernels as K
+    from aien_sovereign_core_mv_b200.engine.generate import Generator
+    from aien_sovereign_core_mv_b200.sampling import SamplingParams
+
+    cfg = dict(QWEN3_8B)
+    layers_cfg = cfg["num_hidden_layers"]
+    layers_run = args.layers or layers_cfg
+    cfg["num_hidden_layers"] = layers_run
+    nums = model_numbers(cfg, layers_run)
+    hbm_gbs, bf16_tflops, peak_src = peaks()
+    max_batch = max(64, args.batch)
+    pool_tokens = max_batch * (PROMPT_LEN + warmup + steps + 64)
+    ec = EngineConfig(dtype="bfloat16", page_size=PAGE, max_cache_tokens=pool_tokens, max_requests=max_batch,
+                      max_batch_tokens=PREFILL_TOKENS, max_context=CONTEXT, max_batch_size=max_batch,
+                      max_prefill_tokens=PREFILL_TOKENS, prefill_chunk_size=PREFILL_TOKENS)
+    t_load = time.time()
+    engine = Engine.from_config(cfg, seed=SEED, engine_config=ec, init_std=0.02, device_init=True)
+    torch.cuda.synchronize()
+    load_s = time.time() - t_load
+    rng = np.random.default_rng(SEED)
+    V = cfg["vocab_size"]
+    if args.fill == "cache":
+        for st in engine.storage:
+            st.normal_(0.0, 0.5)
+
+    def fill_requests(batch, first_id):
+        """Each request holds a PROMPT_LEN-token prompt: real prefill, 2,048 tokens per step."""
+        ids = list(range(first_id, first_id + batch))
+        if args.fill == "cache":
+            for rid in ids:
+                engine.cache.add_request(rid)
+            engine.cache.append([(rid, PROMPT_LEN) for rid in ids])
+            return ids
+        per_step = max(1, PREFILL_TOKENS // PROMPT_LEN)
+        for i in range(0, batch, per_step):
+            ents = [(rid, rng.integers(0, V, PROMPT_LEN), []) for rid in ids[i:i + per_step]]
+            engine.step(ents)
+        return ids
+
+    def decode_run(batch, first_id, n_warm, n_steps, sample_clocks=False):
+        ids = fill_requests(batch, first_id)
+        toks = rng.integers(0, V, (n_warm + n_steps, batch))
+        for s in range(n_warm):
+            engine.step([(rid, [int(toks[s, j])], [0]) for j, rid in enumerate(ids)])
+        torch.cuda.synchronize()
+        sampler = ClockSampler()
+        if sample_clocks:
+            sampler.start()
+            time.sleep(0.25)
+        launches0 = K.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for s in range(n_warm, n_warm + n_steps):
+            engine.step([(rid, [int(toks[s, j])], [0]) for j, rid in enumerate(ids)])
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        clocks = sampler.stop() if sample_clocks else None
+        launches = K.launch_count() - launches0
+        ctx_mid = PROMPT_LEN + n_warm + n_steps // 2
+        for rid in ids:
+            engine.end_request(rid)
+        return ms, clocks, launches, ctx_mid
+
+    # ---- headline: decode at the default batch
+    ms, clocks, launches, ctx_mid = decode_run(args.batch, 1000, warmup, steps, sample_clocks=True)
+    ms_per_step = ms / steps
+    value = args.batch * steps / (ms / 1e3)
+    step_bytes = nums["weight_bytes"] + args.batch * ctx_mid * nums["kv_bytes_per_token"]
+    achieved = step_bytes / (ms_per_step / 1e3) / 1e9
+
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            pms, _, _, _ = decode_run(b, 2000 + 100 * b, max(3, warmup // 2), max(8, steps // 2))
+            points[f"decode_b{b}"] = round(b * max(8, steps // 2) / (pms / 1e3), 1)
+
+    prefill = None
+    if not args.skip_prefill:
+        ptoks = rng.integers(0, V, PREFILL_TOKENS)
+        times = []
+        for rep in range(3):
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            engine.step([(9000 + rep, ptoks, [PREFILL_TOKENS - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+            engine.end_request(9000 + rep)
+        pms = min(times[1:])
+        T = PREFILL_TOKENS
+        flops = 2.0 * (nums["linear_params"] - V * cfg["hidden_size"]) * T + 2.0 * V * cfg["hidden_size"] \
+            + layers_run * 4.0 * nums["Q"] * T * (T + 1) / 2
+        prefill = {"value": round(T / (pms / 1e3), 1), "tokens": T, "ms": round(pms, 3),
+                   "frac": round(flops / (pms / 1e3) / (bf16_tflops * 1e12), 4), "peak": f"{bf16_tflops} TFLOP/s bf16, of {peak_src}"}
+
+    e2e = None
+    if not args.skip_e2e:
+        gen = Generator(engine)
+        n_new = warmup + steps
+        prompts = [rng.integers(0, V, PROMPT_LEN).tolist() for _ in range(args.batch)]
+        sp = SamplingParams(temperature=0.0, max_tokens=n_new, stop_token_ids=[])
+        for i, p in enumerate(prompts):
+            gen.submit(5000 + i, p, sp)
+        while gen.scheduler.has_work() and gen.scheduler.metrics()["decode_tokens"] < warmup * args.batch:
+            gen.step()
+        torch.cuda.synchronize()
+        h0, d0, s0 = gen.h2d_bytes, gen.d2h_bytes, gen.steps
+        dec0 = gen.scheduler.metrics()["decode_tokens"]
+        t0 = time.perf_counter()
+        while gen.scheduler.has_work():
+            gen.step()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        n_steps = max(1, gen.steps - s0)
+        new_tokens = gen.scheduler.metrics()["decode_tokens"] - dec0
+        e2e = {"value": round(new_tokens / dt, 1), "unit": "tokens/s", "steps": n_steps,
+               "h2d_bytes_per_step": int((gen.h2d_bytes - h0) / n_steps), "d2h_bytes_per_step": int((gen.d2h_bytes - d0) / n_steps)}
+
+    out = {
+        "metric": "decode_tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": {
+            "model": "Qwen3-8B shape, random weights", "layers": layers_cfg, "layers_run": layers_run,
+            "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": V,
+            "global_batch": args.batch, "seq_len": PROMPT_LEN, "context": CONTEXT, "page_size": PAGE,
+            "parallelism": "single GPU", "prefill_tokens": PREFILL_TOKENS, "seed": SEED,
+            "l2": "inputs larger than L2: 15 GB of weights per step", "fill": args.fill,
+        },
+        "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s",
+                     "frac": round(achieved / hbm_gbs, 4), "of": peak_src, "bytes_per_step": int(step_bytes)},
+        "points": points, "load_s": round(load_s, 1),
+        "reference_gb10": {"tokens_per_s": 7.0, "source": "docs/campaigns/open-model-qwen3/RESULT-v7.md:67-68 (Qwen3-8B, GB10, one request)"},
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -275,3 +275,133 @@ def test_argmax_and_sampling(K):
     kept, probs = pm.kept_set(logits[2], 1.0, 1.0, 8)
     assert counts.sum() == counts[kept].sum()
     assert counts[int(np.argmax(logits[2]))] == counts.max()
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K_", [(1, 16, 32), (1, 333, 72), (3, 100, 200), (8, 4096, 512), (9, 77, 1032), (16, 130, 4096), (5, 48, 8)])
+def test_gemv_against_simple(K, out_dtype, M, N, K_):
+    g = torch.Generator().manual_seed(M * 7 + N)
+    a_full = torch.randn(M, K_ + 16, generator=g).to(torch.bfloat16).cuda()
+    a = a_full[:, 8:8 + K_]                                  # row stride differs from K, still 16-byte aligned
+    w = torch.randn(N, K_, generator=g).to(torch.bfloat16).cuda()
+    assert K.gemv_supports(a, w, torch.empty(M, N, dtype=out_dtype, device="cuda"))
+    out = torch.empty(M, N, dtype=out_dtype, device="cuda")
+    K.gemv(a, w, out)
+    want = a.double().cpu() @ w.double().cpu().T
+    H.assert_close(out.float().cpu().numpy(), want.numpy(), 2e-5 if out_dtype == torch.float32 else 1e-2, f"gemv {M}x{N}x{K_}")
+    # a row's result does not depend on the other rows
+    if M > 1:
+        one = torch.empty(1, N, dtype=out_dtype, device="cuda")
+        K.gemv(a[M - 1:M], w, one)
+        assert torch.equal(one[0], out[M - 1])
+
+
+def test_gemv_swiglu_epilogue(K):
+    g = torch.Generator().manual_seed(1)
+    M, I, Hd = 5, 88, 136
+    a = torch.randn(M, Hd, generator=g).to(torch.bfloat16).cuda()
+    gate = torch.randn(I, Hd, generator=g).to(torch.bfloat16)
+    up = torch.randn(I, Hd, generator=g).to(torch.bfloat16)
+    inter = torch.stack([gate.view(I // 8, 8, Hd), up.view(I // 8, 8, Hd)], dim=1).reshape(2 * I, Hd).contiguous().cuda()
+    out = torch.empty(M, I, dtype=torch.bfloat16, device="cuda")
+    K.gemv(a, inter, out, epilogue=1)
+    ad = a.double().cpu()
+    want = pm.swiglu((ad @ gate.double().T).numpy(), (ad @ up.double().T).numpy())
+    H.assert_close(out.float().cpu().numpy(), want, 1e-2, "gemv+swiglu")
+
+
+@pytest.mark.parametrize("nq,nkv,hd,page,window", ATT_CASES + [(16, 1, 64, 16, 0), (12, 1, 96, 16, 300)])
+def test_paged_attention_decode(K, nq, nkv, hd, page, window):
+    dtype = torch.bfloat16
+    rng = np.random.default_rng(nq * 10 + hd)
+    seq_lens = [1, 37, 700, 256, 257, 513]
+    kc, vc, bt, mb, dense = paged_setup(rng, seq_lens, nkv, hd, page, dtype, sum((n + page - 1) // page for n in seq_lens) + 8)
+    seq_of = list(range(len(seq_lens)))
+    positions = [n - 1 for n in seq_lens]
+    T = len(seq_of)
+    big = torch.tensor(rng.standard_normal((T, nq * hd + 64)), dtype=torch.float32).to(dtype).cuda()
+    q = big[:, 32:32 + nq * hd]
+    scale = 1.0 / math.sqrt(hd)
+    splits = (max(seq_lens) + 255) // 256
+    part_out = torch.empty(T * nq * splits * hd, device="cuda"); part_ml = torch.empty(T * nq * splits * 2, device="cuda")
+    out = torch.empty(T, nq * hd, dtype=dtype, device="cuda")
+    K.paged_attention_decode(q, kc, vc, bt, mb, torch.tensor(seq_of, dtype=torch.int32).cuda(),
+                             torch.tensor(positions, dtype=torch.int32).cuda(), out, part_out, part_ml,
+                             nq, nkv, hd, page, window, scale, splits)
+    want = attention_reference(q.float().double().cpu().numpy().reshape(-1, nq, hd), dense, seq_of, positions, nq, nkv, hd, window, scale)
+    H.assert_close(out.float().cpu().numpy(), want, 1.5e-2, "decode attention")
+    ref = torch.empty_like(out)
+    K.paged_attention_generic(q, kc, vc, bt, mb, torch.tensor(seq_of, dtype=torch.int32).cuda(),
+                              torch.tensor(positions, dtype=torch.int32).cuda(), ref, nq, nkv, hd, page, window, scale)
+    H.assert_close(out.float().cpu().numpy(), ref.float().cpu().numpy(), 1e-2, "decode vs generic kernel")
+
+
+def test_decode_attention_one_far_key_decides(K):
+    nq, nkv, hd, page, n = 4, 1, 64, 16, 1500
+    for far in (0, 255, 256, 1023, 1499):
+        pages = (n + page - 1) // page
+        perm = np.random.default_rng(far).permutation(pages + 4)
+        bt = np.full((1, pages + 2), -1, dtype=np.int32)
+        bt[0, :pages] = perm[:pages]
+        slots = (bt[0, np.arange(n) // page] * page + np.arange(n) % page)
+        kc = torch.zeros((pages + 4) * page, nkv, hd); vc = torch.zeros((pages + 4) * page, nkv, hd)
+        vc[slots, 0, :] = torch.arange(n, dtype=torch.float32)[:, None] / 8.0
+        kc[slots[far], 0, 0] = 40.0
+        q = torch.zeros(1, nq * hd)
+        q[0, ::hd] = 8.0
+        splits = (n + 255) // 256
+        out = torch.empty(1, nq * hd, dtype=torch.bfloat16, device="cuda")
+        K.paged_attention_decode(q.to(torch.bfloat16).cuda(), kc.to(torch.bfloat16).cuda(), vc.to(torch.bfloat16).cuda(),
+                                 torch.tensor(bt).cuda(), pages + 2, torch.zeros(1, dtype=torch.int32).cuda(),
+                                 torch.tensor([n - 1], dtype=torch.int32).cuda(), out,
+                                 torch.empty(nq * splits * hd, device="cuda"), torch.empty(nq * splits * 2, device="cuda"),
+                                 nq, nkv, hd, page, 0, 1.0 / math.sqrt(hd), splits)
+        got = out.float().cpu().numpy()
+        assert np.abs(got - far / 8.0).max() <= max(1e-2, 0.01 * far / 8.0), (far, got[0, :4])
+
+
+def test_gemv_partial_products_and_their_consumers(K):
+    """K cut across CTAs: the partial products add up to the plain product, and the kernels that
+    consume them (norm, row gather, q/k kernel) add them on the way in."""
+    g = torch.Generator().manual_seed(11)
+    M, N, K_ = 3, 96, 2048
+    a = torch.randn(M, K_, generator=g).to(torch.bfloat16).cuda()
+    w = torch.randn(N, K_, generator=g).to(torch.bfloat16).cuda()
+    parts = torch.empty(4, M, N, device="cuda")
+    K.gemv(a, w, parts)
+    want = (a.double().cpu() @ w.double().cpu().T).numpy()
+    H.assert_close(parts.sum(0).cpu().numpy(), want, 2e-5, "sum of partials")
+    assert K.gemv_splits(4096, 4096) == 4 and K.gemv_splits(24576, 4096) == 1 and K.gemv_splits(151936, 4096) == 1
+    # norm consumes partials
+    x = torch.randn(M, N, generator=g).cuda()
+    x0 = x.clone()
+    wn = torch.ones(N, dtype=torch.bfloat16, device="cuda")
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    K.add_rmsnorm(x, parts, wn, 1e-6, out)
+    xs = x0.double().cpu().numpy() + want
+    H.assert_close(x.cpu().numpy(), xs, 2e-5, "residual + partials")
+    H.assert_close(out.float().cpu().numpy(), pm.rms_norm(xs, np.ones(N), 1e-6), 1e-2, "norm of residual + partials")
+    rows = torch.tensor([2, 0], dtype=torch.int32).cuda()
+    got = torch.empty(2, N, device="cuda")
+    K.gather_add_rows(x0, parts, rows, got)
+    H.assert_close(got.cpu().numpy(), xs[[2, 0]], 2e-5, "gather of residual + partials")
+    # q/k kernel consumes partials: heads of 32, 1 q head + 1 kv head
+    hd = 32
+    q_out = torch.empty(M, hd, dtype=torch.bfloat16, device="cuda")
+    kc = torch.zeros(8, 1, hd, dtype=torch.bfloat16, device="cuda"); vc = torch.zeros(8, 1, hd, dtype=torch.bfloat16, device="cuda")
+    slot = torch.tensor([1, 5, 2], dtype=torch.int32).cuda()
+    K.qk_norm_rope_kv_write(parts[..., :hd], parts[..., hd:2 * hd], parts[..., 2 * hd:3 * hd], hd, None, None, 1e-6,
+                            None, None, 0, slot, kc, vc, q_out=q_out)
+    H.assert_close(q_out.float().cpu().numpy(), want[:, :hd], 1e-2, "q from partials")
+    H.assert_close(kc[[1, 5, 2], 0].float().cpu().numpy(), want[:, hd:2 * hd], 1e-2, "k from partials")
+    H.assert_close(vc[[1, 5, 2], 0].float().cpu().numpy(), want[:, 2 * hd:3 * hd], 1e-2, "v from partials")
+
+
+def test_swiglu_interleaved_layout(K):
+    g = torch.Generator().manual_seed(4)
+    T, I = 3, 40
+    gate = torch.randn(T, I, generator=g); up = torch.randn(T, I, generator=g)
+    inter = torch.stack([gate.view(T, I // 8, 8), up.view(T, I // 8, 8)], dim=2).reshape(T, 2 * I).contiguous().cuda()
+    out = torch.empty(T, I, device="cuda")
+    K.swiglu(inter, out, 8)
+    H.assert_close(out.cpu().numpy(), pm.swiglu(gate.double().numpy(), up.double().numpy()), 2e-5, "interleaved swiglu")
