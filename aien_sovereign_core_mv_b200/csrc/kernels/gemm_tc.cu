@@ -1,0 +1,299 @@
+// C[M,N] = A[M,K] . W[N,K]^T on the fifth-generation tensor cores: tcgen05.mma with the
+// accumulator in tensor memory, operands brought into shared memory by TMA.
+//
+// One CTA computes one 128 x 128 tile.  Six warps, three roles:
+//   warp 0      producer: one lane issues the TMA loads of the A and W k-blocks (128 rows x 64
+//               bfloat16 = one 128-byte swizzled row each) into a 3-stage ring;
+//   warp 1      allocates tensor memory, then one lane issues tcgen05.mma (M 128, N 128, K 16,
+//               four per k-block) and commits each stage back to the producer;
+//   warps 2-5   epilogue: each owns one 32-lane quarter of tensor memory, reads the float32
+//               accumulator with tcgen05.ld and stores its rows (bfloat16 or float32), or applies
+//               silu(gate)*up first when W holds gate and up rows interleaved in groups of 8.
+// Two CTAs fit on an SM (96 KB of stages, 128 tensor-memory columns each), so one tile's epilogue
+// runs under the other's main loop.  The grid is M-tiles fastest: the CTAs that share a tile of W
+// run together and W is read from HBM once.
+//
+// Rows of A beyond M, rows of W beyond N and columns beyond K are zero-filled by TMA; stores are
+// masked.  Needs K % 8 == 0 and 16-byte aligned bases and row strides (the TMA rules).
+// Every wait is bounded: after the limit the kernel records an error code and goes on without
+// hanging; the host reads the code with aien_gemm_tc_error().
+#include "common.cuh"
+#include <cuda.h>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace aien {
+
+constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64, TC_STAGES = 3;
+constexpr int TC_STAGE_A = TC_BM * TC_BK * 2, TC_STAGE_B = TC_BN * TC_BK * 2;
+constexpr int TC_SMEM = TC_STAGES * (TC_STAGE_A + TC_STAGE_B) + 1024 /*align*/ + 256 /*barriers*/;
+constexpr uint32_t TC_SPIN_LIMIT = 1u << 24;
+
+__device__ int g_tc_error = 0;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after TC_SPIN_LIMIT polls, records `code`, and lets the caller go on.
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int code) {
+    for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i)
+        if (mbar_try_wait(bar, parity)) return;
+    atomicCAS(&g_tc_error, 0, code);
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_c, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t r[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+}
+
+// Shared-memory matrix descriptor of a K-major operand tile whose rows are 128 bytes, 128-byte
+// swizzled (what TMA writes with SWIZZLE_128B): start address and strides in 16-byte units,
+// 1024 bytes between groups of 8 rows, descriptor version 1, layout code 2.
+__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // bits  0-13  start address
+    d |= (uint64_t)1 << 16;                               // bits 16-29  leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                     // bits 32-45  stride byte offset
+    d |= (uint64_t)1 << 46;                               // bits 46-47  version
+    d |= (uint64_t)2 << 61;                               // bits 61-63  SWIZZLE_128B
+    return d;
+}
+
+// EPI 0: store; EPI 1: silu(gate)*up over columns interleaved in runs of 8 (out has N/2 columns)
+template <int EPI, typename TC>
+__global__ void __launch_bounds__(192)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               TC* __restrict__ out, long ldc, int M, int N, int K) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sA = base, sB = base + TC_STAGES * TC_STAGE_A;
+    const uint32_t bars = sB + TC_STAGES * TC_STAGE_B;     // full[3], empty[3], tmem_full, then the tmem slot
+    const uint32_t full0 = bars, empty0 = bars + 8 * TC_STAGES, tmem_full = bars + 16 * TC_STAGES;
+    const uint32_t tmem_slot = tmem_full + 8;
+    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen + (tmem_slot - base));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * TC_BN;
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(tmem_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)TC_BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_acc = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % TC_STAGES;
+                const uint32_t round = kb / TC_STAGES;
+                if (kb >= TC_STAGES) mbar_wait(empty0 + 8 * s, (round - 1) & 1, 1);
+                mbar_expect_tx(full0 + 8 * s, TC_STAGE_A + TC_STAGE_B);
+                tma_load_2d(sA + s * TC_STAGE_A, &map_a, full0 + 8 * s, kb * TC_BK, m0);
+                tma_load_2d(sB + s * TC_STAGE_B, &map_w, full0 + 8 * s, kb * TC_BK, n0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // instruction descriptor: f32 accumulate, bf16 x bf16, both K-major, N at bit 17 (>>3), M at bit 24 (>>4)
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % TC_STAGES;
+                mbar_wait(full0 + 8 * s, (kb / TC_STAGES) & 1, 2);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t da = make_desc_sw128(sA + s * TC_STAGE_A), db = make_desc_sw128(sB + s * TC_STAGE_B);
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k)     // 16 bfloat16 = 32 bytes = 2 descriptor units along K
+                    umma_bf16(tmem_acc, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                umma_commit(empty0 + 8 * s);             // the stage may be refilled once these MMAs have read it
+            }
+            umma_commit(tmem_full);
+        }
+    } else {
+        const int quarter = warp & 3;                    // tensor-memory lanes 32*quarter .. +31
+        mbar_wait(tmem_full, 0, 3);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int row = m0 + quarter * 32 + lane;
+#pragma unroll 1
+        for (int c0 = 0; c0 < TC_BN; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld32(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (row < M) {
+                if (EPI == 0) {
+                    TC* dst = out + (size_t)row * ldc + n0 + c0;
+                    const int valid = N - (n0 + c0);
+                    if (valid >= 32 && (((uintptr_t)dst & 15) == 0)) {
+                        if (sizeof(TC) == 2) {
+                            uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) {
+                                uint4 o;
+                                __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                                __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                                __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                                __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                                o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+                                o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+                                d4[v] = o;
+                            }
+                        } else {
+                            uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+                            for (int v = 0; v < 8; ++v) d4[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (j < valid) dst[j] = from_f<TC>(__uint_as_float(r[j]));
+                    }
+                } else {
+                    // columns c0..c0+31 hold two runs of (8 gate, 8 up): 16 outputs
+                    const int oc0 = (n0 + c0) / 2;
+                    TC* dst = out + (size_t)row * ldc + oc0;
+                    const int valid = N / 2 - oc0;
+#pragma unroll
+                    for (int run = 0; run < 2; ++run)
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float g = __uint_as_float(r[run * 16 + j]), u = __uint_as_float(r[run * 16 + 8 + j]);
+                            if (run * 8 + j < valid) dst[run * 8 + j] = from_f<TC>(g / (1.0f + expf(-g)) * u);
+                        }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)TC_BN) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------- host side: tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// A 2-D bfloat16 row-major matrix [rows, cols] with leading dimension ld, boxes of 128 rows x 64 cols.
+static bool make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld) {
+    static std::map<std::tuple<const void*, uint64_t, uint64_t, uint64_t>, CUtensorMap> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    auto key = std::make_tuple(ptr, rows, cols, ld);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *map = it->second; return true; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {ld * 2};
+    cuuint32_t box[2] = {TC_BK, TC_BM};
+    cuuint32_t estr[2] = {1, 1};
+    if (fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = *map;
+    return true;
+}
+
+template <int EPI, typename TC>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* out, long ldc, int M, int N, int K, cudaStream_t stream) {
+    auto kern = gemm_tc_kernel<EPI, TC>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM) != cudaSuccess) return AIEN_E_STATE;
+        configured = true;
+    }
+    dim3 grid((M + TC_BM - 1) / TC_BM, (N + TC_BN - 1) / TC_BN);
+    kern<<<grid, 192, TC_SMEM, stream>>>(ma, mw, (TC*)out, ldc, M, N, K);
+    return launch_status();
+}
+
+}  // namespace aien
+
+using namespace aien;
+
+// epilogue 0: out[M,N]; 1: out[M,N/2] = silu(gate)*up with gate/up rows of W interleaved in runs of 8
+AIEN_API int aien_gemm_tc(const void* A, long lda, const void* W, long ldw, void* out, int c_dt, long ldc,
+                          int M, int N, int K, int epilogue, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || (K & 7)) return AIEN_E_SHAPE;
+    if ((lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return AIEN_E_ALIGN;
+    if (epilogue == 1 && (N & 15)) return AIEN_E_SHAPE;
+    if ((M + TC_BM - 1) / TC_BM > 2147483647 / 1 || (N + TC_BN - 1) / TC_BN > 65535) return AIEN_E_SHAPE;
+    CUtensorMap ma, mw;
+    if (!make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda) || !make_map(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw))
+        return AIEN_E_STATE;
+    if (epilogue == 0) {
+        if (c_dt == AIEN_DT_BF16) return launch_tc<0, __nv_bfloat16>(ma, mw, out, ldc, M, N, K, stream);
+        if (c_dt == AIEN_DT_F32) return launch_tc<0, float>(ma, mw, out, ldc, M, N, K, stream);
+        return AIEN_E_DTYPE;
+    }
+    if (epilogue == 1) {
+        if (c_dt == AIEN_DT_BF16) return launch_tc<1, __nv_bfloat16>(ma, mw, out, ldc, M, N, K, stream);
+        if (c_dt == AIEN_DT_F32) return launch_tc<1, float>(ma, mw, out, ldc, M, N, K, stream);
+        return AIEN_E_DTYPE;
+    }
+    return AIEN_E_SHAPE;
+}
+
+// Reads and clears the error code a bounded wait may have left (0: none; 1 producer, 2 MMA, 3 epilogue).
+AIEN_API int aien_gemm_tc_error(void) {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
+    return v;
+}

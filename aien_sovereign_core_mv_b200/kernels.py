@@ -56,6 +56,8 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_argmax_rows": [P, I, I, P, P],
         "aien_sample_rows": [P, I, I, P, P, P, P, P, P, P, P, P],
         "aien_gemv_bf16": [P, L, P, L, P, I, L, I, I, I, I, I, c_size_t, P],
+        "aien_gemm_tc": [P, L, P, L, P, I, L, I, I, I, I, P],
+        "aien_gemm_tc_error": [],
         "aien_paged_attention_decode": [P, L, P, P, P, I, P, P, P, L, P, P, I, I, I, I, I, F, I, I, P],
     }
     for name, args in sigs.items():
@@ -292,7 +294,7 @@ def gemv_supports(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
     K_ = a.shape[1]
     return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[0] <= GEMV_MAX_ROWS and K_ % 8 == 0
             and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
-            and a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1)
+            and a.stride(1) == 1 and w.stride(1) == 1 and out.stride(-1) == 1)
 
 
 def gemv_splits(N: int, K_: int) -> int:
@@ -320,7 +322,27 @@ def gemv(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0)
 
 
 def gemm_tc_supports(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
-    return False
+    K_ = a.shape[1]
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K_ % 8 == 0
+            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32))
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0) -> None:
+    """out = a . w^T on the tcgen05 tensor cores (bfloat16 operands, float32 accumulation in
+    tensor memory).  ``epilogue=1``: w holds gate|up rows interleaved in runs of 8 and
+    out = silu(gate)*up with N/2 columns."""
+    _dev(a, w, out)
+    M, K_ = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K_ and out.shape == (M, N if epilogue == 0 else N // 2)
+    _check(lib().aien_gemm_tc(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), dt(out), out.stride(0), M, N, K_,
+                              epilogue, _stream()), "gemm_tc")
+
+
+def gemm_tc_error() -> int:
+    """Error code left by a bounded wait inside the tensor-core kernel (0: none); clears it."""
+    return int(lib().aien_gemm_tc_error())
 
 
 # ---------------------------------------------------------------------------- attention choice

@@ -40,7 +40,7 @@ def linear(ctx: StepContext, a: torch.Tensor, w: torch.Tensor, out_dtype: Option
     if choice == "gemv":
         K.gemv(a, w, out)
     elif choice == "tc":
-        K.gemm_tc(a, w, out, ctx.workspace)
+        K.gemm_tc(a, w, out)
     else:
         K.gemm_simple(a, w, out)
     return out

@@ -6,7 +6,7 @@ import torch
 from .. import kernels as K
 from ..registry import register_feed_forward
 from .base import FeedForward, StepContext
-from .linear import linear
+from .linear import linear, _FORCE
 
 
 @register_feed_forward("swiglu")
@@ -46,6 +46,8 @@ class SwiGLU(FeedForward):
         act = ctx.workspace.take((ctx.num_tokens, self.intermediate_size), ctx.dtype)
         if self.group == 8 and h.shape[0] <= K.GEMV_MAX_ROWS and K.gemv_supports(h, self.w_gate_up, act):
             K.gemv(h, self.w_gate_up, act, epilogue=1)          # silu(gate)*up inside the product
+        elif self.group == 8 and K.gemm_tc_supports(h, self.w_gate_up, act) and not _FORCE:
+            K.gemm_tc(h, self.w_gate_up, act, epilogue=1)       # the same, in the tensor-core epilogue
         else:
             gu = linear(ctx, h, self.w_gate_up)
             K.swiglu(gu, act, self.group)

@@ -405,3 +405,40 @@ def test_swiglu_interleaved_layout(K):
     out = torch.empty(T, I, device="cuda")
     K.swiglu(inter, out, 8)
     H.assert_close(out.cpu().numpy(), pm.swiglu(gate.double().numpy(), up.double().numpy()), 2e-5, "interleaved swiglu")
+
+
+TC_SHAPES = [(128, 128, 64), (1, 16, 8), (17, 100, 200), (130, 333, 72), (256, 384, 4096), (300, 130, 1032), (2048, 512, 256), (64, 1000, 512)]
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K_", TC_SHAPES)
+def test_gemm_tensor_core(K, out_dtype, M, N, K_):
+    g = torch.Generator().manual_seed(M + 3 * N + K_)
+    a_full = torch.randn(M, K_ + 24, generator=g).to(torch.bfloat16).cuda()
+    a = a_full[:, 8:8 + K_]
+    w = torch.randn(N, K_, generator=g).to(torch.bfloat16).cuda()
+    out_full = torch.full((M, N + 5), 9.0, dtype=out_dtype, device="cuda")
+    out = out_full[:, :N]
+    assert K.gemm_tc_supports(a, w, out)
+    K.gemm_tc(a, w, out)
+    torch.cuda.synchronize()
+    assert K.gemm_tc_error() == 0
+    want = a.double().cpu() @ w.double().cpu().T
+    H.assert_close(out.float().cpu().numpy(), want.numpy(), 2e-5 if out_dtype == torch.float32 else 1e-2, f"tc gemm {M}x{N}x{K_}")
+    assert (out_full[:, N:] == 9.0).all()                    # nothing written beyond N
+
+
+def test_gemm_tensor_core_swiglu_epilogue(K):
+    g = torch.Generator().manual_seed(2)
+    M, I, Hd = 150, 264, 136
+    a = torch.randn(M, Hd, generator=g).to(torch.bfloat16).cuda()
+    gate = torch.randn(I, Hd, generator=g).to(torch.bfloat16)
+    up = torch.randn(I, Hd, generator=g).to(torch.bfloat16)
+    inter = torch.stack([gate.view(I // 8, 8, Hd), up.view(I // 8, 8, Hd)], dim=1).reshape(2 * I, Hd).contiguous().cuda()
+    out = torch.empty(M, I, dtype=torch.bfloat16, device="cuda")
+    K.gemm_tc(a, inter, out, epilogue=1)
+    torch.cuda.synchronize()
+    assert K.gemm_tc_error() == 0
+    ad = a.double().cpu()
+    want = pm.swiglu((ad @ gate.double().T).numpy(), (ad @ up.double().T).numpy())
+    H.assert_close(out.float().cpu().numpy(), want, 1e-2, "tc gemm + swiglu")
