@@ -130,6 +130,11 @@ class Engine:
                 groups.append((bt, o, self.max_blocks))
                 o += _align4(max(T, 1))
         off["groups"] = groups
+        n_tiles = T // 64 + S + 1                     # 64-token query tiles of the prefill attention kernel
+        off["tile_seq"] = o
+        o += _align4(n_tiles)
+        off["tile_q0"] = o
+        o += _align4(n_tiles)
         return off, o
 
     # ------------------------------------------------------------------ requests
@@ -231,16 +236,25 @@ class Engine:
         if R:
             m[off["want_rows"]:off["want_rows"] + R] = want_rows
         max_ctx = self.cache.fill_meta(ids, counts, m, off["positions"], off["seq_of_token"], off["q_start"], off["ctx_len"], off["groups"])
+        decode_only = T == S
+        n_tiles = 0
+        if not decode_only:
+            for i, c in enumerate(counts):
+                k = (c + 63) // 64
+                m[off["tile_seq"] + n_tiles:off["tile_seq"] + n_tiles + k] = i
+                m[off["tile_q0"] + n_tiles:off["tile_q0"] + n_tiles + k] = np.arange(k, dtype=np.int32) * 64
+                n_tiles += k
         self.meta_dev[:total].copy_(meta_host[:total], non_blocking=True)
         if slot[2] is None:
             slot[2] = torch.cuda.Event()
         slot[2].record()
-        decode_only = T == S
         self.steps_run += 1
         if (decode_only and R == T and self.cfg.use_cuda_graphs and self.dtype == torch.bfloat16
                 and want_rows == list(range(T))):
             return self._replay_decode(off, T, max_ctx, logits_out)
         ctx = self._context(off, T, S, max(counts), max_ctx, decode_only)
+        d = self.meta_dev
+        ctx.prefill_tiles = (d[off["tile_seq"]:off["tile_seq"] + max(n_tiles, 1)], d[off["tile_q0"]:off["tile_q0"] + max(n_tiles, 1)], n_tiles)
         if logits_out is None:
             logits_out = torch.empty((R, self.vocab_size), dtype=torch.float32, device=self.device)
         d = self.meta_dev

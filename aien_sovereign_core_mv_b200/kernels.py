@@ -58,6 +58,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_gemv_bf16": [P, L, P, L, P, I, L, I, I, I, I, I, c_size_t, P],
         "aien_gemm_tc": [P, L, P, L, P, I, L, I, I, I, I, P],
         "aien_gemm_tc_error": [],
+        "aien_paged_attention_prefill": [P, L, P, P, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P],
         "aien_paged_attention_decode": [P, L, P, P, P, I, P, P, P, L, P, P, I, I, I, I, I, F, I, I, P],
     }
     for name, args in sigs.items():
@@ -394,5 +395,32 @@ def paged_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
         paged_attention_decode(q, k2, v2, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, out,
                                part_out, part_ml, num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale, splits)
         return
+    if (not ctx.decode_only and _FORCE_ATTN != "generic" and ctx.prefill_tiles is not None and ctx.prefill_tiles[2] > 0
+            and prefill_attention_supports(q, k2, out, head_dim)):
+        tile_seq, tile_q0, n = ctx.prefill_tiles
+        paged_attention_prefill(q, k2, v2, group.block_table, group.max_blocks, ctx.q_start, ctx.ctx_len, tile_seq, tile_q0, n,
+                                out, num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale)
+        return
     paged_attention_generic(q, k2, v2, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, out,
                             num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale)
+
+
+def prefill_attention_supports(q: torch.Tensor, k_cache: torch.Tensor, out: torch.Tensor, head_dim: int) -> bool:
+    return (q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 128
+            and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0)
+
+
+def paged_attention_prefill(q, k_cache, v_cache, block_table, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles,
+                            out, num_q_heads, num_kv_heads, head_dim, page_size, window, scale) -> None:
+    """Causal attention of portions of prompts over their requests' pages (bfloat16, tensor
+    cores).  ``tile_seq``/``tile_q0``: for every 64-token query tile, the index of its request in
+    the step and the tile's offset inside that request's portion."""
+    _dev(q, k_cache, v_cache, block_table, q_start, ctx_len, tile_seq, tile_q0, out)
+    assert q.stride(1) == 1 and out.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+    for t in (block_table, q_start, ctx_len, tile_seq, tile_q0):
+        assert t.dtype == torch.int32
+    _check(lib().aien_paged_attention_prefill(
+        _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), max_blocks, _p(q_start), _p(ctx_len), _p(tile_seq),
+        _p(tile_q0), num_tiles, _p(out), out.stride(0), num_q_heads, num_kv_heads, head_dim, page_size, window,
+        float(scale), _stream()), "paged_attention_prefill")

@@ -442,3 +442,54 @@ def test_gemm_tensor_core_swiglu_epilogue(K):
     ad = a.double().cpu()
     want = pm.swiglu((ad @ gate.double().T).numpy(), (ad @ up.double().T).numpy())
     H.assert_close(out.float().cpu().numpy(), want, 1e-2, "tc gemm + swiglu")
+
+
+PREFILL_CASES = [(4, 2, 16, 16, 0), (6, 3, 48, 8, 0), (5, 1, 80, 16, 0), (8, 2, 128, 16, 0), (3, 3, 32, 4, 21), (8, 4, 64, 16, 40), (2, 1, 112, 32, 100)]
+
+
+@pytest.mark.parametrize("nq,nkv,hd,page,window", PREFILL_CASES)
+def test_paged_attention_prefill(K, nq, nkv, hd, page, window):
+    dtype = torch.bfloat16
+    rng = np.random.default_rng(nq * 31 + hd)
+    seq_lens = [130, 64, 300, 5, 200]                 # context after the step
+    q_lens = [130, 1, 77, 2, 64]                      # tokens the step brings: whole, decode, offset portion, 2, one full tile
+    kc, vc, bt, mb, dense = paged_setup(rng, seq_lens, nkv, hd, page, dtype, sum((n + page - 1) // page for n in seq_lens) + 8)
+    seq_of, positions, q_start, tile_seq, tile_q0 = [], [], [0], [], []
+    for s, (n, ql) in enumerate(zip(seq_lens, q_lens)):
+        seq_of += [s] * ql
+        positions += list(range(n - ql, n))
+        q_start.append(q_start[-1] + ql)
+        for t in range((ql + 63) // 64):
+            tile_seq.append(s); tile_q0.append(t * 64)
+    T = len(seq_of)
+    big = torch.tensor(rng.standard_normal((T, nq * hd + 64)), dtype=torch.float32).to(dtype).cuda()
+    q = big[:, 32:32 + nq * hd]
+    scale = 1.0 / math.sqrt(hd)
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32).cuda()
+    out = torch.empty(T, nq * hd, dtype=dtype, device="cuda")
+    K.paged_attention_prefill(q, kc, vc, bt, mb, i32(q_start), i32(seq_lens), i32(tile_seq), i32(tile_q0), len(tile_seq),
+                              out, nq, nkv, hd, page, window, scale)
+    want = attention_reference(q.float().double().cpu().numpy().reshape(-1, nq, hd), dense, seq_of, positions, nq, nkv, hd, window, scale)
+    H.assert_close(out.float().cpu().numpy(), want, 1.5e-2, "prefill attention")
+
+
+def test_prefill_attention_one_far_key_decides(K):
+    nq, nkv, hd, page, n = 2, 1, 64, 16, 700
+    for far in (0, 63, 64, 303, 636):
+        pages = (n + page - 1) // page
+        perm = np.random.default_rng(far).permutation(pages + 4)
+        bt = np.full((1, pages + 2), -1, dtype=np.int32)
+        bt[0, :pages] = perm[:pages]
+        slots = (bt[0, np.arange(n) // page] * page + np.arange(n) % page)
+        kc = torch.zeros((pages + 4) * page, nkv, hd); vc = torch.zeros((pages + 4) * page, nkv, hd)
+        vc[slots, 0, :] = torch.arange(n, dtype=torch.float32)[:, None] / 8.0
+        kc[slots[far], 0, 0] = 40.0
+        ql = 64                                                    # the last 64 tokens are the step's portion
+        q = torch.zeros(ql, nq * hd); q[:, ::hd] = 8.0
+        i32 = lambda a: torch.tensor(a, dtype=torch.int32).cuda()
+        out = torch.empty(ql, nq * hd, dtype=torch.bfloat16, device="cuda")
+        K.paged_attention_prefill(q.to(torch.bfloat16).cuda(), kc.to(torch.bfloat16).cuda(), vc.to(torch.bfloat16).cuda(),
+                                  torch.tensor(bt).cuda(), pages + 2, i32([0, ql]), i32([n]), i32([0]), i32([0]), 1,
+                                  out, nq, nkv, hd, page, 0, 1.0 / math.sqrt(hd))
+        got = out.float().cpu().numpy()
+        assert np.abs(got - far / 8.0).max() <= max(1e-2, 0.01 * far / 8.0), (far, got[0, :4], got[-1, :4])
