@@ -1,0 +1,167 @@
+"""The scheduler's decisions, on the CPU, with a fake model whose next token is a function of
+the request and the position (so a recomputed request must produce the same tokens)."""
+import pytest
+
+from aien_sovereign_core_mv_b200.csrc import build
+
+host = build.load_host()
+
+
+def make(pages=64, page=4, max_requests=8, **limits):
+    cm = host.CacheManager(page, [host.GroupSpec(host.GroupKind.Full, 0, pages)], max_requests)
+    sc = host.SchedulerConfig()
+    sc.max_batch_size, sc.max_batch_tokens, sc.max_prefill_tokens, sc.prefill_chunk_size = 8, 64, 32, 16
+    sc.watermark_blocks = 0
+    for k, v in limits.items():
+        setattr(sc, k, v)
+    return cm, host.Scheduler(sc, cm)
+
+
+def fake_token(rid, position):
+    return 10 + (rid * 7 + position * 3) % 50
+
+
+def drive(sched, cm, max_steps=2000, log=None):
+    """Run to completion; returns {id: (generated, reason)}."""
+    done = {}
+    for _ in range(max_steps):
+        if not sched.has_work():
+            break
+        plan = sched.plan()
+        if log is not None:
+            log.append(plan)
+        sampled = [fake_token(e.id, e.start + len(e.tokens)) for e in plan.entries if e.wants_logits]
+        if plan.entries:
+            sched.commit(sampled)
+        assert cm.check() == ""
+        for ev in sched.take_finished():
+            done[ev.id] = (list(ev.generated), ev.reason.name, ev.message)
+    return done
+
+
+def expected(rid, prompt_len, n):
+    return [fake_token(rid, prompt_len + i) for i in range(n)]
+
+
+def test_portions_budget_and_decode_every_step():
+    cm, s = make()
+    s.submit(1, list(range(40)), 5)
+    s.submit(2, list(range(10)), 5)
+    log = []
+    done = drive(s, cm, log=log)
+    first = log[0]
+    assert [(e.id, len(e.tokens), e.start, e.wants_logits) for e in first.entries] == [(1, 16, 0, False), (2, 10, 0, True)]
+    assert first.prefill_tokens == 26 and first.num_tokens == 26
+    second = log[1]                                           # request 1 goes on, request 2 decodes
+    assert [(e.id, len(e.tokens), e.start) for e in second.entries] == [(1, 16, 16), (2, 1, 10)]
+    third = log[2]
+    assert [(e.id, len(e.tokens), e.start, e.wants_logits) for e in third.entries] == [(1, 8, 32, True), (2, 1, 11, True)]
+    assert done[1][0] == expected(1, 40, 5) and done[2][0] == expected(2, 10, 5)
+    assert done[1][1] == "LengthLimit" and cm.num_requests == 0 and cm.free_count(0) == 64
+    for p in log:
+        assert p.num_tokens <= 64 and p.prefill_tokens <= 32 and len(p.entries) <= 8
+
+
+def test_fifo_admission_under_the_sequence_limit():
+    cm, s = make(max_batch_size=2)
+    for rid in (1, 2, 3):
+        s.submit(rid, [1, 2, 3], 2)
+    log = []
+    done = drive(s, cm, log=log)
+    assert [e.id for e in log[0].entries] == [1, 2]           # the third waits its turn
+    assert 3 not in [e.id for p in log[:2] for e in p.entries]
+    assert set(done) == {1, 2, 3}
+
+
+def test_stop_token_ends_and_is_not_emitted():
+    cm, s = make()
+    stop = fake_token(4, 6 + 2)                               # the third generated token
+    s.submit(4, list(range(6)), 10, [stop])
+    done = drive(s, cm)
+    assert done[4][0] == expected(4, 6, 2) and done[4][1] == "StopToken"
+
+
+def test_whole_prompt_mode():
+    cm, s = make(chunk_prefill=False)
+    s.submit(1, list(range(30)), 1)
+    s.submit(2, list(range(40)), 1)                           # larger than max_prefill_tokens: can never run whole
+    done = drive(s, cm)
+    assert done[1][1] == "LengthLimit" and done[2][1] == "Aborted" and "chunk_prefill" in done[2][2]
+
+
+def test_request_larger_than_the_pool_is_aborted_not_queued_forever():
+    cm, s = make(pages=4)                                      # 16 tokens
+    s.submit(1, list(range(30)), 4)
+    s.submit(2, list(range(5)), 2)
+    done = drive(s, cm)
+    assert done[1][1] == "Aborted" and host.EXHAUSTED_PREFIX in done[1][2]
+    assert done[2][0] == expected(2, 5, 2)
+
+
+def test_admission_reserves_the_whole_input():
+    """Two prompts of 20 tokens need 6 pages each (21 tokens); 8 pages hold only one at a time."""
+    cm, s = make(pages=8)
+    s.submit(1, list(range(20)), 3)
+    s.submit(2, list(range(20)), 3)
+    log = []
+    done = drive(s, cm, log=log)
+    assert [e.id for e in log[0].entries] == [1]
+    first_of_2 = next(i for i, p in enumerate(log) if any(e.id == 2 for e in p.entries))
+    assert all(s_.preempted == [] for s_ in log)               # nobody had to be thrown out
+    assert first_of_2 >= 4
+    assert done[1][0] == expected(1, 20, 3) and done[2][0] == expected(2, 20, 3)
+
+
+def test_out_of_pages_preempts_lowest_priority_and_recomputes():
+    """Decoding outgrows the pool: the lower-priority request is preempted, its pages are given
+    back, and it is recomputed from prompt ++ generated; its tokens are the same as if it had
+    never been interrupted, and none is emitted twice."""
+    cm, s = make(pages=7, page=4)                              # 28 tokens
+    s.submit(1, list(range(8)), 12, [], 5)                     # priority 5
+    s.submit(2, list(range(8)), 12, [], 1)                     # priority 1: the victim
+    log = []
+    done = drive(s, cm, log=log)
+    preempted = [p.preempted for p in log if p.preempted]
+    assert preempted and all(v == [2] for v in preempted)
+    assert done[1][0] == expected(1, 8, 12) and done[2][0] == expected(2, 8, 12)
+    assert s.record(2).preemptions >= 1 and s.record(1).preemptions == 0
+    # after the preemption the victim's next entry starts from position 0 and carries its own tokens
+    k = next(i for i, p in enumerate(log) if p.preempted)
+    again = next(e for p in log[k + 1:] for e in p.entries if e.id == 2)
+    assert again.start == 0 and again.tokens[:8] == list(range(8)) and len(again.tokens) > 8 or again.tokens == list(range(8))
+    assert s.metrics()["preemptions"] == len(preempted) and cm.free_count(0) == 7
+
+
+def test_watermark_preempts_before_the_pool_is_dry():
+    cm, s = make(pages=10, page=4, watermark_blocks=3)
+    s.submit(1, list(range(12)), 20, [], 2)
+    s.submit(2, list(range(12)), 20, [], 1)
+    log = []
+    done = drive(s, cm, log=log)
+    assert any(p.preempted == [2] for p in log)
+    assert done[1][0] == expected(1, 12, 20) and done[2][0] == expected(2, 12, 20)
+
+
+def test_cancel_and_bad_calls():
+    cm, s = make()
+    s.submit(1, [1, 2, 3], 4)
+    with pytest.raises(ValueError, match="already live"):
+        s.submit(1, [1], 1)
+    with pytest.raises(ValueError, match="empty prompt"):
+        s.submit(9, [], 1)
+    plan = s.plan()
+    with pytest.raises(RuntimeError):
+        s.plan()                                               # a planned step must be committed first
+    with pytest.raises(ValueError, match="sampled tokens expected"):
+        s.commit([])
+    assert s.cancel(1) and not s.cancel(1)
+    s.commit([5])                                              # the cancelled request ignores the token
+    ev = s.take_finished()
+    assert [e.reason.name for e in ev] == ["Cancelled"] and cm.num_requests == 0 and not s.has_work()
+
+
+def test_context_limit():
+    cm, s = make(max_context=12)
+    s.submit(1, list(range(8)), 100)
+    done = drive(s, cm)
+    assert done[1][1] == "LengthLimit" and len(done[1][0]) == 4
