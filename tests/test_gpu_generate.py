@@ -1,0 +1,125 @@
+"""Generation through the Python entry point and the command line: greedy tokens equal the plain
+implementation's, sampling follows the plain sampler, preempted requests repeat nothing."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import helpers as H
+import plain_model as pm
+
+pytestmark = pytest.mark.gpu
+
+
+def plain_greedy(folder, prompt, n, stops=()):
+    cfg, w = pm.load_model_folder(folder)
+    seq, out = list(prompt), []
+    for _ in range(n):
+        t = pm.argmax_token(pm.decoder_forward(cfg, w, seq)[-1])
+        if t in stops:
+            break
+        seq.append(t); out.append(t)
+    return out
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("gen")
+    return {w: H.make_folder(root, w) for w in ("A", "B")}
+
+
+@pytest.mark.parametrize("which", ["A", "B"])
+def test_greedy_generation_float32_equals_plain(folders, which):
+    from aien_sovereign_core_mv_b200.engine.generate import Generator, generate, generate_tokens
+    from aien_sovereign_core_mv_b200.sampling import SamplingParams
+    d = folders[which]
+    lens = [7, 13, 29] if which == "A" else [1, 17, 40, 63]
+    prompts = [H.tokens_for(which, n, 900 + n) for n in lens]
+    n_new = 8 if which == "A" else 12
+    want = [plain_greedy(d, p, n_new) for p in prompts]
+    eng = H.engine_for(d, "float32", H.PAGE_SIZE[which], 512, prefill_chunk_size=16, max_prefill_tokens=32)
+    got = generate(eng, prompts, SamplingParams(temperature=0.0, max_tokens=n_new, stop_token_ids=[]))
+    assert got == want
+    assert eng.cache_state()["requests"] == 0 and eng.cache_state()["check"] == ""
+    assert generate_tokens(eng, 5, prompts[1], n_new, 0.0, []) == want[1]          # the reference's signature
+    # the model's own stop ids end a request; the stop id is not emitted
+    stop = want[0][3]
+    res = Generator(eng).generate([prompts[0]], SamplingParams(temperature=0.0, max_tokens=n_new, stop_token_ids=[stop]))
+    assert res[0].tokens == want[0][:want[0].index(stop)] and res[0].finish_reason == "stop"
+
+
+def test_greedy_generation_bfloat16_follows_its_own_logits(folders):
+    """bfloat16 may pick another token where two logits are close; along its own path every chosen
+    token must be the argmax of the engine's logits for that path, recomputed whole."""
+    from aien_sovereign_core_mv_b200.engine.generate import generate
+    from aien_sovereign_core_mv_b200.sampling import SamplingParams
+    d = folders["B"]
+    prompts = [H.tokens_for("B", n, 300 + n) for n in (5, 31, 64)]
+    eng = H.engine_for(d, "bfloat16", 8, 512)
+    got = generate(eng, prompts, SamplingParams(temperature=0.0, max_tokens=20, stop_token_ids=[]))
+    for i, (p, g) in enumerate(zip(prompts, got)):
+        assert len(g) == 20
+        ref = H.plain_logits(d, p + g)
+        for j, tok in enumerate(g):
+            row = ref[len(p) + j - 1]
+            assert row[tok] >= row.max() - H.BF16_TOL * 2 * np.abs(row).max(), (i, j)
+
+
+def test_sampling_through_the_entry_point_matches_the_plain_sampler(folders):
+    from aien_sovereign_core_mv_b200.engine.generate import Generator
+    from aien_sovereign_core_mv_b200.sampling import SamplingParams, philox_uniform
+    d = folders["A"]
+    cfg, w = pm.load_model_folder(d)
+    prompts = [H.tokens_for("A", n, 700 + n) for n in (17, 40)]
+    params = [SamplingParams(temperature=0.7, top_p=0.95, top_k=0, max_tokens=12, stop_token_ids=[], seed=11),
+              SamplingParams(temperature=1.1, top_p=0.8, top_k=20, max_tokens=12, stop_token_ids=[], seed=12)]
+    eng = H.engine_for(d, "float32", 16, 256)
+    res = Generator(eng).generate(prompts, params, request_ids=[41, 42])
+    again = Generator(eng).generate(prompts[::-1], params[::-1], request_ids=[42, 41])      # other batch order: same draws
+    assert [r.tokens for r in res] == [r.tokens for r in again[::-1]]
+    mismatches = 0
+    for rid, p, sp, r in zip([41, 42], prompts, params, res):
+        seq = list(p)
+        for tok in r.tokens:
+            logits = pm.decoder_forward(cfg, w, seq)[-1]
+            u = philox_uniform(sp.seed, rid, len(seq))
+            kept, _ = pm.kept_set(logits, sp.temperature, sp.top_p, sp.top_k)
+            assert tok in kept
+            mismatches += pm.sample_token(logits, sp.temperature, sp.top_p, sp.top_k, u) != tok
+            seq.append(tok)
+        assert len(r.tokens) == 12 and len(set(r.tokens)) > 1
+    assert mismatches <= 1          # float32 logits against float64: only a knife-edge draw may differ
+
+
+def test_preemption_repeats_nothing(folders):
+    """A pool too small for both requests to finish: one is preempted and recomputed; both get
+    exactly the tokens they get alone."""
+    from aien_sovereign_core_mv_b200.engine.generate import Generator
+    from aien_sovereign_core_mv_b200.sampling import SamplingParams
+    d = folders["A"]
+    prompts = [H.tokens_for("A", 20, 1), H.tokens_for("A", 20, 2)]
+    want = [plain_greedy(d, p, 30) for p in prompts]
+    eng = H.engine_for(d, "float32", 16, 80, watermark_blocks=0)             # 5 pages of 16
+    gen = Generator(eng)
+    sp = SamplingParams(temperature=0.0, max_tokens=30, stop_token_ids=[])
+    res = gen.generate(prompts, sp, request_ids=[1, 2])
+    assert [r.tokens for r in res] == want
+    assert sum(r.preemptions for r in res) >= 1
+    assert eng.cache_state()["free_pages"] == [5]
+
+
+def test_command_line(folders, tmp_path):
+    d = folders["A"]
+    prompt = H.tokens_for("A", 13, 3)
+    want = plain_greedy(d, prompt, 6)
+    cmd = [os.path.join(H.ROOT, "bin", "aien-b200"), "generate", "--model-dir", d, "--dtype", "float32", "--prompt-ids",
+           ",".join(map(str, prompt)), "--max-tokens", "6", "--temperature", "0", "--stop-token-ids", "", "--json"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    rec = json.loads(out.stdout.strip().splitlines()[-1])
+    assert rec["tokens"] == [want]
+    bad = subprocess.run([cmd[0], "generate", "--model-dir", str(tmp_path), "--prompt-ids", "1"], capture_output=True, text=True, timeout=600)
+    assert bad.returncode != 0 and "config.json" in bad.stderr
