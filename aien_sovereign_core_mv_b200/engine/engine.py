@@ -95,6 +95,8 @@ class Engine:
         self.meta_dev = torch.empty(meta_len, dtype=torch.int32, device=self.device)
         self.steps_run = 0
         self._graphs = {}
+        # parts that keep fixed-size state run host logic per request: their steps are not captured
+        self._graphable = all(n.kind != "state" for n in model.group_needs)
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -226,7 +228,10 @@ class Engine:
         metadata to the device in one copy, then the model.  Decode-only steps that want every
         row replay a captured CUDA graph."""
         T, S, R = int(sum(counts)), len(ids), len(want_rows)
-        off, total = self._layout(T, S, R)
+        graph_step = (T == S and R == T and self.cfg.use_cuda_graphs and self.dtype == torch.bfloat16
+                      and self._graphable and want_rows == list(range(T)))
+        Tp = self._bucket(T) if graph_step else T          # captured steps run at a few batch sizes; the rest is padding
+        off, total = self._layout(Tp, Tp if graph_step else S, Tp if graph_step else R)
         slot = self._meta_ring[self._meta_turn % len(self._meta_ring)]
         self._meta_turn += 1
         if slot[2] is not None:
@@ -244,14 +249,15 @@ class Engine:
                 m[off["tile_seq"] + n_tiles:off["tile_seq"] + n_tiles + k] = i
                 m[off["tile_q0"] + n_tiles:off["tile_q0"] + n_tiles + k] = np.arange(k, dtype=np.int32) * 64
                 n_tiles += k
+        if Tp > T:
+            self._pad_meta(m, off, T, Tp)
         self.meta_dev[:total].copy_(meta_host[:total], non_blocking=True)
         if slot[2] is None:
             slot[2] = torch.cuda.Event()
         slot[2].record()
         self.steps_run += 1
-        if (decode_only and R == T and self.cfg.use_cuda_graphs and self.dtype == torch.bfloat16
-                and want_rows == list(range(T))):
-            return self._replay_decode(off, T, max_ctx, logits_out)
+        if graph_step:
+            return self._replay_decode(off, Tp, max_ctx, logits_out, T)
         ctx = self._context(off, T, S, max(counts), max_ctx, decode_only)
         d = self.meta_dev
         ctx.prefill_tiles = (d[off["tile_seq"]:off["tile_seq"] + max(n_tiles, 1)], d[off["tile_q0"]:off["tile_q0"] + max(n_tiles, 1)], n_tiles)
@@ -262,7 +268,31 @@ class Engine:
         return logits_out
 
     # ------------------------------------------------------------------ captured decode steps
-    def _replay_decode(self, off, T: int, max_ctx: int, logits_out: Optional[torch.Tensor]) -> torch.Tensor:
+    _BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512)
+
+    def _bucket(self, T: int) -> int:
+        for b in self._BUCKETS:
+            if b >= T:
+                return min(b, self.max_requests) if self.max_requests >= T else T
+        return T
+
+    def _pad_meta(self, m, off, T: int, Tp: int) -> None:
+        """Rows T..Tp of a captured step: a token at position 0 of a request with no pages; it
+        writes no cache slot and attends over nothing."""
+        m[off["token_ids"] + T:off["token_ids"] + Tp] = 0
+        m[off["positions"] + T:off["positions"] + Tp] = 0
+        m[off["seq_of_token"] + T:off["seq_of_token"] + Tp] = np.arange(T, Tp, dtype=np.int32)
+        m[off["q_start"] + T:off["q_start"] + Tp + 1] = np.arange(T, Tp + 1, dtype=np.int32)
+        m[off["ctx_len"] + T:off["ctx_len"] + Tp] = 0
+        m[off["want_rows"]:off["want_rows"] + Tp] = np.arange(Tp, dtype=np.int32)
+        for (bt, sm, mb), need in zip(off["groups"], self.model.group_needs):
+            if need.kind == "state":
+                m[sm + T:sm + Tp] = 0
+            else:
+                m[bt + T * mb:bt + Tp * mb] = -1
+                m[sm + T:sm + Tp] = -1
+
+    def _replay_decode(self, off, T: int, max_ctx: int, logits_out: Optional[torch.Tensor], real: Optional[int] = None) -> torch.Tensor:
         """Decode steps are short chains of small kernels; launching them one by one costs more
         than running them.  One CUDA graph per (batch size, key-chunk count) is captured at first
         use and replayed afterwards; its inputs are the metadata buffer, its output a logits
@@ -294,10 +324,11 @@ class Engine:
         graph, logits, nodes = entry
         graph.replay()
         K.add_launches(nodes)
+        real = T if real is None else real
         if logits_out is not None:
-            logits_out.copy_(logits)
+            logits_out.copy_(logits[:real])
             return logits_out
-        return logits
+        return logits[:real]
 
     def _context(self, off, T: int, S: int, max_q: int, max_ctx: int, decode_only: bool) -> StepContext:
         d = self.meta_dev

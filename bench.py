@@ -241,24 +241,32 @@ def main() -> int:
 
     e2e = None
     if not args.skip_e2e:
+        # The same K decode steps through the public entry point: every step the scheduler plans,
+        # token ids and block tables go host->device from pinned memory, the chosen ids come back.
         gen = Generator(engine)
-        n_new = warmup + steps
         prompts = [rng.integers(0, V, PROMPT_LEN).tolist() for _ in range(args.batch)]
-        sp = SamplingParams(temperature=0.0, max_tokens=n_new, stop_token_ids=[])
+        sp = SamplingParams(temperature=0.0, max_tokens=4 * warmup + steps + 64, stop_token_ids=[])
         for i, p in enumerate(prompts):
             gen.submit(5000 + i, p, sp)
-        while gen.scheduler.has_work() and gen.scheduler.metrics()["decode_tokens"] < warmup * args.batch:
+        def all_decoding():
+            m = gen.scheduler.metrics()
+            return m["prefill_tokens"] >= args.batch * PROMPT_LEN and gen.scheduler.num_running == args.batch
+        while not all_decoding():
+            gen.step()
+        for _ in range(warmup):
             gen.step()
         torch.cuda.synchronize()
         h0, d0, s0 = gen.h2d_bytes, gen.d2h_bytes, gen.steps
         dec0 = gen.scheduler.metrics()["decode_tokens"]
         t0 = time.perf_counter()
-        while gen.scheduler.has_work():
+        for _ in range(steps):
             gen.step()
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
         n_steps = max(1, gen.steps - s0)
         new_tokens = gen.scheduler.metrics()["decode_tokens"] - dec0
+        for i in range(args.batch):
+            gen.scheduler.cancel(5000 + i)
         e2e = {"value": round(new_tokens / dt, 1), "unit": "tokens/s", "steps": n_steps,
                "h2d_bytes_per_step": int((gen.h2d_bytes - h0) / n_steps), "d2h_bytes_per_step": int((gen.d2h_bytes - d0) / n_steps)}
 
