@@ -40,6 +40,8 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
     constexpr int DCH = (HS + 1) / 2;            // 64-dim chunks of the output
     constexpr int NH = NT * 8;
     extern __shared__ float smem[];
+    griddep_launch();
+    griddep_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, c = lane & 3;
     const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
@@ -223,6 +225,8 @@ __global__ void __launch_bounds__(128)
 decode_attention_merge_kernel(const float* __restrict__ part_out, const float* __restrict__ part_ml,
                               const int* __restrict__ positions, __nv_bfloat16* __restrict__ out, long out_stride,
                               int nq, int hd, int window, int max_splits) {
+    griddep_launch();
+    griddep_wait();
     const int h = blockIdx.x, t = blockIdx.y;
     const int pos = positions[t];
     const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
@@ -260,9 +264,9 @@ static int launch_decode(const void* q, long q_stride, const void* kc, const voi
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return AIEN_E_STATE;
     }
     dim3 grid(max_splits, nkv, T);
-    kern<<<grid, AD_WARPS * 32, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc,
-                                                 (const __nv_bfloat16*)vc, bt, max_blocks, seq_of_token, positions,
-                                                 part_out, part_ml, nq, nkv, hd, page_size, window, scale, max_splits);
+    launch_chain(kern, grid, dim3(AD_WARPS * 32), smem, stream, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc,
+                 (const __nv_bfloat16*)vc, bt, max_blocks, seq_of_token, positions,
+                 part_out, part_ml, nq, nkv, hd, page_size, window, scale, max_splits);
     return launch_status();
 }
 
@@ -292,7 +296,7 @@ AIEN_API int aien_paged_attention_decode(
 #undef AD_CASE
     if (rc != 0) return rc;
     dim3 mgrid(nq, T);
-    decode_attention_merge_kernel<<<mgrid, 128, 0, stream>>>(part_out, part_ml, positions, (__nv_bfloat16*)out, out_stride,
-                                                             nq, hd, window, max_splits);
+    launch_chain(decode_attention_merge_kernel, mgrid, dim3(128), 0, stream, (const float*)part_out, (const float*)part_ml, positions,
+                 (__nv_bfloat16*)out, out_stride, nq, hd, window, max_splits);
     return launch_status();
 }

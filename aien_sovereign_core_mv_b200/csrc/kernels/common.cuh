@@ -9,6 +9,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define AIEN_DT_F32 0
 #define AIEN_DT_BF16 1
@@ -68,6 +69,42 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     float total = red[0];
     for (int w = 1; w < nwarps; ++w) total = fmaxf(total, red[w]);
     return total;
+}
+
+// ---- programmatic dependent launch
+// The decode step is a chain of short kernels.  Launched with the programmatic-serialization
+// attribute, a kernel may become resident while its predecessor is still running; it must not
+// read what the predecessor writes, nor write anything, before griddep_wait() returns (which is
+// when the predecessor has completed and its writes are visible).  Weights are never written
+// during a step, so a kernel may prefetch them first.  griddep_launch() lets the successor start
+// its own prologue.  Without the launch attribute both are no-ops.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("AIEN_B200_PDL");
+        v = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
+// Launch `kernel` so that it may overlap the tail of the kernel before it on the stream.  Only for
+// kernels that call griddep_wait() before touching anything but weights.
+template <typename... KArgs, typename... Args>
+inline void launch_chain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 inline int launch_status() {

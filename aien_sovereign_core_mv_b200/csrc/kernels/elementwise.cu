@@ -39,6 +39,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
                                    const void* __restrict__ w, int wdt, float eps,
                                    TO* __restrict__ h, int H) {
     __shared__ float red[32];
+    griddep_launch();
+    griddep_wait();
     const size_t base = (size_t)blockIdx.x * H;
     float ss = 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
@@ -63,6 +65,8 @@ __global__ void __launch_bounds__(256)
 add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int nparts, size_t part_stride,
                        const void* __restrict__ w, int wdt, float eps, TO* __restrict__ h, int H) {
     __shared__ float red[32];
+    griddep_launch();
+    griddep_wait();
     const size_t base = (size_t)blockIdx.x * H;
     float4 v[NV];
 #pragma unroll
@@ -104,6 +108,8 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int 
 template <typename TD>
 __global__ void gather_add_rows_kernel(const float* __restrict__ x, const TD* __restrict__ delta, int nparts,
                                        size_t part_stride, const int* __restrict__ rows, float* __restrict__ out, int H) {
+    griddep_launch();
+    griddep_wait();
     const size_t src = (size_t)rows[blockIdx.x] * H, dst = (size_t)blockIdx.x * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float v = x[src + i];
@@ -118,6 +124,8 @@ __global__ void gather_add_rows_kernel(const float* __restrict__ x, const TD* __
 // `group` (gate run, then the matching up run), the layout the fused decode product wants.
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int group, size_t total) {
+    griddep_launch();
+    griddep_wait();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; idx < total; idx += stride) {
@@ -160,6 +168,8 @@ qk_norm_rope_kv_write_kernel(
     const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot,
     const int* __restrict__ slot_map, TKV* __restrict__ k_cache, TKV* __restrict__ v_cache) {
     __shared__ float buf[4][AIEN_MAX_HEAD_DIM];
+    griddep_launch();
+    griddep_wait();
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int half = rot >> 1;
     const bool write_kv = (k != nullptr);
@@ -237,13 +247,13 @@ static void launch_add_rmsnorm(float* x, const TD* delta, int nparts, size_t par
                                float eps, TO* h, int T, int H, cudaStream_t stream) {
     const bool vec = (H % 4 == 0) && (((uintptr_t)x & 15) == 0);
     if (vec && H <= 256 * 4 * 2)
-        add_rmsnorm_vec_kernel<TD, TO, 2><<<T, 256, 0, stream>>>(x, delta, nparts, part_stride, w, w_dt, eps, h, H);
+        launch_chain(add_rmsnorm_vec_kernel<TD, TO, 2>, dim3(T), dim3(256), 0, stream, x, delta, nparts, part_stride, w, w_dt, eps, h, H);
     else if (vec && H <= 256 * 4 * 4)
-        add_rmsnorm_vec_kernel<TD, TO, 4><<<T, 256, 0, stream>>>(x, delta, nparts, part_stride, w, w_dt, eps, h, H);
+        launch_chain(add_rmsnorm_vec_kernel<TD, TO, 4>, dim3(T), dim3(256), 0, stream, x, delta, nparts, part_stride, w, w_dt, eps, h, H);
     else if (vec && H <= 256 * 4 * 8)
-        add_rmsnorm_vec_kernel<TD, TO, 8><<<T, 256, 0, stream>>>(x, delta, nparts, part_stride, w, w_dt, eps, h, H);
+        launch_chain(add_rmsnorm_vec_kernel<TD, TO, 8>, dim3(T), dim3(256), 0, stream, x, delta, nparts, part_stride, w, w_dt, eps, h, H);
     else
-        add_rmsnorm_kernel<TD, TO><<<T, row_threads(H), 0, stream>>>(x, delta, nparts, part_stride, w, w_dt, eps, h, H);
+        launch_chain(add_rmsnorm_kernel<TD, TO>, dim3(T), dim3(row_threads(H)), 0, stream, x, delta, nparts, part_stride, w, w_dt, eps, h, H);
 }
 
 // delta: [nparts][T][H] (nparts >= 1; part_stride in elements) or null
@@ -259,7 +269,7 @@ AIEN_API int aien_add_rmsnorm(float* x, const void* delta, int delta_dt, int npa
 AIEN_API int aien_gather_add_rows(const float* x, const void* delta, int delta_dt, int nparts, size_t part_stride,
                                   const int* rows, float* out, int R, int H, cudaStream_t stream) {
     if (R <= 0) return 0;
-    AIEN_DISPATCH_DTYPE(delta_dt, TD, (gather_add_rows_kernel<TD><<<R, row_threads(H), 0, stream>>>(
+    AIEN_DISPATCH_DTYPE(delta_dt, TD, (launch_chain(gather_add_rows_kernel<TD>, dim3(R), dim3(row_threads(H)), 0, stream,
         x, (const TD*)delta, nparts, part_stride, rows, out, H)));
     return launch_status();
 }
@@ -269,7 +279,7 @@ AIEN_API int aien_swiglu(const void* gu, void* out, int dt, int T, int I, int gr
     if (group < 0 || (group > 0 && I % group != 0)) return AIEN_E_SHAPE;
     const size_t total = (size_t)T * I;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    AIEN_DISPATCH_DTYPE(dt, TT, (swiglu_kernel<TT><<<blocks, 256, 0, stream>>>((const TT*)gu, (TT*)out, I, group, total)));
+    AIEN_DISPATCH_DTYPE(dt, TT, (launch_chain(swiglu_kernel<TT>, dim3(blocks), dim3(256), 0, stream, (const TT*)gu, (TT*)out, I, group, total)));
     return launch_status();
 }
 
@@ -295,7 +305,7 @@ AIEN_API int aien_qk_norm_rope_kv_write(
     dim3 grid(T, (n_heads + 3) / 4);
     if (grid.y > 65535) return AIEN_E_SHAPE;
     AIEN_DISPATCH_DTYPE(in_dt, TI, AIEN_DISPATCH_DTYPE(act_dt, TC, AIEN_DISPATCH_DTYPE(kv_dt, TKV,
-        (qk_norm_rope_kv_write_kernel<TI, TC, TKV><<<grid, 128, 0, stream>>>(
+        (launch_chain(qk_norm_rope_kv_write_kernel<TI, TC, TKV>, grid, dim3(128), 0, stream,
             (const TI*)q, q_stride, nq, (const TI*)k, k_stride, (const TI*)v, v_stride, nkv, nparts, part_stride,
             (TC*)q_out, q_out_stride, hd, q_norm_w, k_norm_w, w_dt, eps, cos_t, sin_t, rot, slot_map,
             (TKV*)k_cache, (TKV*)v_cache)))));

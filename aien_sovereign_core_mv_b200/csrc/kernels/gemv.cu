@@ -17,7 +17,7 @@
 
 namespace aien {
 
-constexpr int GV_UNROLL = 4;
+constexpr int GV_UNROLL = 2;
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     uint4 r;
@@ -70,24 +70,41 @@ gemv_mma_kernel(const __nv_bfloat16* __restrict__ a, long lda, const __nv_bfloat
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
 
+    // The first slabs of W are requested before waiting for the kernel ahead of this one: weights
+    // do not depend on it, the activations do.  Inside the loop the next slabs of W are requested
+    // before the current ones are used, so two groups of loads are in flight per warp.
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    for (int s = s_begin; s < s_end; s += GV_UNROLL) {
-        uint4 wa[GV_UNROLL], wb[GV_UNROLL], xb[GV_UNROLL][MT];
+    uint4 wa[GV_UNROLL], wb[GV_UNROLL];
+    auto load_w = [&](int s) {
 #pragma unroll
         for (int u = 0; u < GV_UNROLL; ++u) {
             const int k = (s + u) * 32;
             const bool in = (s + u) < s_end && (k + c * 8) < K;      // K % 8 == 0: a chunk is whole or absent
             wa[u] = (in && v0) ? ldg_stream(w0 + k) : zero;
             wb[u] = (in && v1) ? ldg_stream(w1 + k) : zero;
+        }
+    };
+    griddep_launch();
+    load_w(s_begin);
+    griddep_wait();
+    for (int s = s_begin; s < s_end; s += GV_UNROLL) {
+        uint4 xb[GV_UNROLL][MT], ca[GV_UNROLL], cb[GV_UNROLL];
+#pragma unroll
+        for (int u = 0; u < GV_UNROLL; ++u) {
+            const int k = (s + u) * 32;
+            const bool in = (s + u) < s_end && (k + c * 8) < K;
+            ca[u] = wa[u];
+            cb[u] = wb[u];
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) xb[u][mt] = (in && xv[mt]) ? ldg_cached(xa[mt] + k) : zero;
         }
+        if (s + GV_UNROLL < s_end) load_w(s + GV_UNROLL);
 #pragma unroll
         for (int u = 0; u < GV_UNROLL; ++u) {
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-                mma_bf16_16816(acc[mt], wa[u].x, wb[u].x, wa[u].y, wb[u].y, xb[u][mt].x, xb[u][mt].y);
-                mma_bf16_16816(acc[mt], wa[u].z, wb[u].z, wa[u].w, wb[u].w, xb[u][mt].z, xb[u][mt].w);
+                mma_bf16_16816(acc[mt], ca[u].x, cb[u].x, ca[u].y, cb[u].y, xb[u][mt].x, xb[u][mt].y);
+                mma_bf16_16816(acc[mt], ca[u].z, cb[u].z, ca[u].w, cb[u].w, xb[u][mt].z, xb[u][mt].w);
             }
         }
     }
@@ -136,14 +153,14 @@ static int launch_gemv(const void* a, long lda, const void* W, long ldw, void* o
     dim3 grid((N + 15) / 16, splits);
     if (splits > 1) {
         if (c_dt != AIEN_DT_F32) return AIEN_E_DTYPE;
-        gemv_mma_kernel<MT, EPI, float, 4><<<grid, 4 * 32, 0, stream>>>(
-            (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)W, ldw, (float*)out, ldc, part_stride, M, N, K);
+        launch_chain(gemv_mma_kernel<MT, EPI, float, 4>, grid, dim3(4 * 32), 0, stream,
+                     (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)W, ldw, (float*)out, ldc, part_stride, M, N, K);
     } else if (c_dt == AIEN_DT_BF16)
-        gemv_mma_kernel<MT, EPI, __nv_bfloat16, 8><<<grid, 8 * 32, 0, stream>>>(
-            (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)W, ldw, (__nv_bfloat16*)out, ldc, 0, M, N, K);
+        launch_chain(gemv_mma_kernel<MT, EPI, __nv_bfloat16, 8>, grid, dim3(8 * 32), 0, stream,
+                     (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)W, ldw, (__nv_bfloat16*)out, ldc, (size_t)0, M, N, K);
     else if (c_dt == AIEN_DT_F32)
-        gemv_mma_kernel<MT, EPI, float, 8><<<grid, 8 * 32, 0, stream>>>(
-            (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)W, ldw, (float*)out, ldc, 0, M, N, K);
+        launch_chain(gemv_mma_kernel<MT, EPI, float, 8>, grid, dim3(8 * 32), 0, stream,
+                     (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)W, ldw, (float*)out, ldc, (size_t)0, M, N, K);
     else
         return AIEN_E_DTYPE;
     return launch_status();
