@@ -1,16 +1,19 @@
 // Decode attention over the paged bfloat16 cache: one query token per request, keys split by
-// absolute position into chunks of 256, one CTA per (chunk, kv head, token), then a merge.
+// absolute position into chunks of 128, one CTA per (chunk, kv head, token); the CTA that
+// finishes last for a (token, kv head) merges the chunks.
 //
-// A chunk is the keys [c*256, c*256+256) of the request, so which keys are summed together is
-// fixed by their positions and never by the batch or the grid.  Within a CTA eight warps take
-// groups of 16 keys in turn.  Scores for a group come from mma.sync.m16n8k16 with the 16 keys as
-// rows and the (up to 16) query heads that share the kv head as columns; K is read straight from
-// global memory with 16-byte loads (the contraction index is permuted the same way for q and
-// K, see gemv.cu).  Softmax is online and float32; the weighted sum over V is plain FMAs with
-// each lane owning two adjacent dims per 64, V rows read coalesced.  Partial results
-// (unnormalised sum, max, denominator) go to scratch; the merge kernel combines the chunks in
-// chunk order.  Formulas: crates/aien-inference-abi/src/backend.rs:311-379 (online softmax over
-// pages, scale 1/sqrt(head_dim)).
+// A chunk is the keys [c*128, c*128+128) of the request, so which keys are summed together is
+// fixed by their positions and never by the batch or the grid.  Within a CTA each of the eight
+// warps takes one group of 16 keys.  Scores for a group come from mma.sync.m16n8k16 with the 16
+// keys as rows and the (up to 16) query heads that share the kv head as columns; K is read
+// straight from global memory with 16-byte loads (the contraction index is permuted the same way
+// for q and K, see gemv.cu).  Softmax is float32; the weighted sum over V is plain FMAs with each
+// lane owning two adjacent dims per 64, all V loads of the group issued before their first use.
+// The warps are combined in warp order, the CTA's partial result (unnormalised sum, max,
+// denominator) goes to scratch, and a ticket counter per (token, kv head) tells the last CTA to
+// combine the chunks in chunk order, whichever CTA that is, and to put the counter back to zero.
+// Formulas: crates/aien-inference-abi/src/backend.rs:311-379 (online softmax over pages, scale
+// 1/sqrt(head_dim)).
 //
 // Needs head_dim % 16 == 0 and <= 256, at most 16 query heads per kv head, bfloat16 q and cache.
 #include "common.cuh"
@@ -19,7 +22,7 @@
 namespace aien {
 
 constexpr int AD_WARPS = 8;
-constexpr int AD_CHUNK = 256;
+constexpr int AD_CHUNK = 128;
 
 __device__ __forceinline__ uint4 ad_ldg16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
 __device__ __forceinline__ void ad_mma(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -35,7 +38,8 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
                               const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                               const int* __restrict__ block_table, int max_blocks,
                               const int* __restrict__ seq_of_token, const int* __restrict__ positions,
-                              float* __restrict__ part_out, float* __restrict__ part_ml,
+                              float* __restrict__ part_out, float* __restrict__ part_ml, int* __restrict__ counters,
+                              __nv_bfloat16* __restrict__ out, long out_stride,
                               int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits) {
     constexpr int DCH = (HS + 1) / 2;            // 64-dim chunks of the output
     constexpr int NH = NT * 8;
@@ -47,14 +51,21 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
     const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
     const int G = nq / nkv;
     const int pos = positions[t];
+    // In a decode-only step token t is request t (seq_of_token may be null): the table row does not
+    // hang on another load, so the page lookups below go out together with the position load.
+    const int* bt = block_table + (size_t)(seq_of_token ? seq_of_token[t] : t) * max_blocks;
+
+    // pages of this warp's 16 keys: looked up before the position is known (a key beyond the
+    // position is masked later; its page, if the table has one, belongs to this request anyway)
+    const int kj0 = split * AD_CHUNK + warp * 16 + g, kj1 = kj0 + 8;
+    const int pi0 = kj0 / page_size, pi1 = kj1 / page_size;
+    const int pg0 = pi0 < max_blocks ? bt[pi0] : -1, pg1 = pi1 < max_blocks ? bt[pi1] : -1;
     const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int lo = max(first, split * AD_CHUNK), hi = min(pos, split * AD_CHUNK + AD_CHUNK - 1);
     if (lo > hi) return;
-    const int* bt = block_table + (size_t)seq_of_token[t] * max_blocks;
 
-    float* Ps = smem + warp * (16 * NH + NH + 16);       // [16 keys][NH heads], then corr[NH], then slots[16]
+    float* Ps = smem + warp * (16 * NH + NH + 16);       // [16 keys][NH heads], then corr[NH]
     float* Cs = Ps + 16 * NH;
-    int* Ss = reinterpret_cast<int*>(Cs + NH);
 
     // query fragments: head (nt*8 + g), dims ds*32 + c*8 .. +8
     uint4 qf[NT][HS];
@@ -76,30 +87,30 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
         for (int i = 0; i < DCH; ++i) acc[h][i][0] = acc[h][i][1] = 0.f;
 
     const int chunk_base = split * AD_CHUNK;
-    for (int grp = warp; grp * 16 < AD_CHUNK; grp += AD_WARPS) {
-        const int base = chunk_base + grp * 16;
-        if (base > hi) break;
-        if (base + 15 < lo) continue;
-        const int kj0 = base + g, kj1 = base + g + 8;
+    {
+        const int base = chunk_base + warp * 16;                 // AD_CHUNK == 16 * AD_WARPS: one group per warp
+        if (base <= hi && base + 15 >= lo) {
         const bool ok0 = kj0 >= lo && kj0 <= hi, ok1 = kj1 >= lo && kj1 <= hi;
-        int slot0 = -1, slot1 = -1;
-        if (ok0) { const int pg = bt[kj0 / page_size]; slot0 = pg < 0 ? -1 : pg * page_size + kj0 % page_size; }
-        if (ok1) { const int pg = bt[kj1 / page_size]; slot1 = pg < 0 ? -1 : pg * page_size + kj1 % page_size; }
-        if (c == 0) { Ss[g] = slot0; Ss[g + 8] = slot1; }
+        const int slot0 = (ok0 && pg0 >= 0) ? pg0 * page_size + kj0 % page_size : -1;
+        const int slot1 = (ok1 && pg1 >= 0) ? pg1 * page_size + kj1 % page_size : -1;
         float S[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) S[nt][0] = S[nt][1] = S[nt][2] = S[nt][3] = 0.f;
         const __nv_bfloat16* k0p = k_cache + ((size_t)(slot0 < 0 ? 0 : slot0) * nkv + kvh) * hd + c * 8;
         const __nv_bfloat16* k1p = k_cache + ((size_t)(slot1 < 0 ? 0 : slot1) * nkv + kvh) * hd + c * 8;
+        uint4 kav[HS], kbv[HS];
 #pragma unroll
         for (int ds = 0; ds < HS; ++ds) {
             const bool din = ds * 32 + c * 8 < hd;
-            const uint4 ka = (slot0 >= 0 && din) ? ad_ldg16(k0p + ds * 32) : make_uint4(0u, 0u, 0u, 0u);
-            const uint4 kb = (slot1 >= 0 && din) ? ad_ldg16(k1p + ds * 32) : make_uint4(0u, 0u, 0u, 0u);
+            kav[ds] = (slot0 >= 0 && din) ? ad_ldg16(k0p + ds * 32) : make_uint4(0u, 0u, 0u, 0u);
+            kbv[ds] = (slot1 >= 0 && din) ? ad_ldg16(k1p + ds * 32) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int ds = 0; ds < HS; ++ds) {
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                ad_mma(S[nt], ka.x, kb.x, ka.y, kb.y, qf[nt][ds].x, qf[nt][ds].y);
-                ad_mma(S[nt], ka.z, kb.z, ka.w, kb.w, qf[nt][ds].z, qf[nt][ds].w);
+                ad_mma(S[nt], kav[ds].x, kbv[ds].x, kav[ds].y, kbv[ds].y, qf[nt][ds].x, qf[nt][ds].y);
+                ad_mma(S[nt], kav[ds].z, kbv[ds].z, kav[ds].w, kbv[ds].w, qf[nt][ds].z, qf[nt][ds].w);
             }
         }
         // S[nt][e]: key g, head nt*8+2c+e;  S[nt][2+e]: key g+8, same head
@@ -144,7 +155,7 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
         uint32_t vraw[16][DCH];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-            const int sl = Ss[j];
+            const int sl = __shfl_sync(0xffffffffu, j < 8 ? slot0 : slot1, (j & 7) * 4);
             const __nv_bfloat16* vp = v_cache + ((size_t)(sl < 0 ? 0 : sl) * nkv + kvh) * hd;
 #pragma unroll
             for (int i = 0; i < DCH; ++i) {
@@ -170,6 +181,7 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
             }
         }
         __syncwarp();
+        }
     }
 
     // ---- combine the warps in warp order
@@ -218,47 +230,77 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
         part_out[row * hd + d] = o;
         if (d == 0) { part_ml[row * 2] = M; part_ml[row * 2 + 1] = L; }
     }
-}
 
-// Combines the chunks of one (token, head) in chunk order and writes the normalised output.
-__global__ void __launch_bounds__(128)
-decode_attention_merge_kernel(const float* __restrict__ part_out, const float* __restrict__ part_ml,
-                              const int* __restrict__ positions, __nv_bfloat16* __restrict__ out, long out_stride,
-                              int nq, int hd, int window, int max_splits) {
-    griddep_launch();
-    griddep_wait();
-    const int h = blockIdx.x, t = blockIdx.y;
-    const int pos = positions[t];
-    const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    // ---- the last CTA of this (token, kv head) merges the chunks in chunk order
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
     const int s_lo = first / AD_CHUNK, s_hi = pos / AD_CHUNK;
-    const size_t row0 = ((size_t)t * nq + h) * max_splits;
-    float M = -INFINITY;
-    for (int s = s_lo; s <= s_hi; ++s) M = fmaxf(M, part_ml[(row0 + s) * 2]);
-    float L = 0.f;
-    for (int s = s_lo; s <= s_hi; ++s) {
-        const float ms = part_ml[(row0 + s) * 2];
-        if (ms != -INFINITY) L += part_ml[(row0 + s) * 2 + 1] * expf(ms - M);
+    if (threadIdx.x == 0) {
+        const int ticket = atomicAdd(&counters[(size_t)t * nkv + kvh], 1);
+        is_last = ticket == (s_hi - s_lo);
+        if (is_last) counters[(size_t)t * nkv + kvh] = 0;        // ready for the next launch
     }
-    const float inv = L > 0.f ? 1.0f / L : 0.f;
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-        float o = 0.f;
-        for (int s = s_lo; s <= s_hi; ++s) {
-            const float ms = part_ml[(row0 + s) * 2];
-            if (ms != -INFINITY) o += part_out[(row0 + s) * hd + d] * expf(ms - M);
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // All loads of a phase are independent of one another, so a phase costs one round trip to L2.
+    const int nsp = s_hi - s_lo + 1;
+    float* Fm = smem;                                   // [nsp][NH]: chunk max, then the chunk's weight
+    float* Fl = Fm + (size_t)max_splits * NH;            // [nsp][NH]: chunk denominator
+    float* Fi = Fl + (size_t)max_splits * NH;            // [NH]: 1 / total denominator
+    for (int i = threadIdx.x; i < nsp * G; i += AD_WARPS * 32) {
+        const int sp = i / G, h = i - sp * G;
+        const size_t row = ((size_t)t * nq + kvh * G + h) * max_splits + s_lo + sp;
+        Fm[sp * NH + h] = __ldcg(part_ml + row * 2);
+        Fl[sp * NH + h] = __ldcg(part_ml + row * 2 + 1);
+    }
+    __syncthreads();
+    if (threadIdx.x < G) {
+        const int h = threadIdx.x;
+        float M = -INFINITY;
+        for (int sp = 0; sp < nsp; ++sp) M = fmaxf(M, Fm[sp * NH + h]);
+        float L = 0.f;
+        for (int sp = 0; sp < nsp; ++sp) {
+            const float ms = Fm[sp * NH + h];
+            const float f = ms == -INFINITY ? 0.f : expf(ms - M);
+            L += Fl[sp * NH + h] * f;
+            Fm[sp * NH + h] = f;
         }
-        out[(size_t)t * out_stride + (size_t)h * hd + d] = __float2bfloat16_rn(o * inv);
+        Fi[h] = L > 0.f ? 1.0f / L : 0.f;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * hd; idx += AD_WARPS * 32) {
+        const int h = idx / hd, d = idx - h * hd;
+        const float* src = part_out + (((size_t)t * nq + kvh * G + h) * max_splits + s_lo) * hd + d;
+        float o = 0.f;
+        int sp = 0;
+        for (; sp + 4 <= nsp; sp += 4) {
+            const float v0 = __ldcg(src + (size_t)(sp + 0) * hd), v1 = __ldcg(src + (size_t)(sp + 1) * hd);
+            const float v2 = __ldcg(src + (size_t)(sp + 2) * hd), v3 = __ldcg(src + (size_t)(sp + 3) * hd);
+            o += v0 * Fm[(sp + 0) * NH + h];
+            o += v1 * Fm[(sp + 1) * NH + h];
+            o += v2 * Fm[(sp + 2) * NH + h];
+            o += v3 * Fm[(sp + 3) * NH + h];
+        }
+        for (; sp < nsp; ++sp) o += __ldcg(src + (size_t)sp * hd) * Fm[sp * NH + h];
+        out[(size_t)t * out_stride + (size_t)(kvh * G + h) * hd + d] = __float2bfloat16_rn(o * Fi[h]);
     }
 }
 
 template <int HS, int NT>
 static int launch_decode(const void* q, long q_stride, const void* kc, const void* vc, const int* bt, int max_blocks,
-                         const int* seq_of_token, const int* positions, float* part_out, float* part_ml,
+                         const int* seq_of_token, const int* positions, float* part_out, float* part_ml, int* counters,
+                         void* out, long out_stride,
                          int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T,
                          cudaStream_t stream) {
     const int G = nq / nkv, NH = NT * 8;
     const size_t loop_bytes = (size_t)AD_WARPS * (16 * NH + NH + 16) * 4;
     const size_t comb_bytes = ((size_t)2 * AD_WARPS * NH + (size_t)AD_WARPS * G * hd) * 4;
-    const size_t smem = loop_bytes > comb_bytes ? loop_bytes : comb_bytes;
+    const size_t merge_bytes = ((size_t)2 * max_splits * NH + NH) * 4;
+    size_t smem = loop_bytes > comb_bytes ? loop_bytes : comb_bytes;
+    if (merge_bytes > smem) smem = merge_bytes;
+    if (smem > 200 * 1024) return AIEN_E_SHAPE;
     auto kern = paged_decode_attention_kernel<HS, NT>;
     if (smem > 48 * 1024) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return AIEN_E_STATE;
@@ -266,7 +308,7 @@ static int launch_decode(const void* q, long q_stride, const void* kc, const voi
     dim3 grid(max_splits, nkv, T);
     launch_chain(kern, grid, dim3(AD_WARPS * 32), smem, stream, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc,
                  (const __nv_bfloat16*)vc, bt, max_blocks, seq_of_token, positions,
-                 part_out, part_ml, nq, nkv, hd, page_size, window, scale, max_splits);
+                 part_out, part_ml, counters, (__nv_bfloat16*)out, out_stride, nq, nkv, hd, page_size, window, scale, max_splits);
     return launch_status();
 }
 
@@ -275,11 +317,12 @@ static int launch_decode(const void* q, long q_stride, const void* kc, const voi
 using namespace aien;
 
 // Scratch: part_out [T * nq * max_splits * hd] floats, part_ml [T * nq * max_splits * 2] floats.
-// max_splits must cover the longest context in the step: ceil((max position + 1) / 256).
+// counters: T * nkv ints that are zero on entry and are left zero.
+// max_splits must cover the longest context in the step: ceil((max position + 1) / 128).
 AIEN_API int aien_paged_attention_decode(
     const void* q, long q_stride, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
     const int* seq_of_token, const int* positions, void* out, long out_stride, float* part_out, float* part_ml,
-    int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T, cudaStream_t stream) {
+    int* counters, int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (hd <= 0 || hd > 256 || (hd & 15) || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || max_splits <= 0) return AIEN_E_SHAPE;
     const int G = nq / nkv;
@@ -290,13 +333,10 @@ AIEN_API int aien_paged_attention_decode(
 #define AD_CASE(hs, nt)                                                                                              \
     if (HS == hs && NT == nt)                                                                                        \
         rc = launch_decode<hs, nt>(q, q_stride, k_cache, v_cache, block_table, max_blocks, seq_of_token, positions,  \
-                                   part_out, part_ml, nq, nkv, hd, page_size, window, scale, max_splits, T, stream);
+                                   part_out, part_ml, counters, out, out_stride, nq, nkv, hd, page_size, window, scale,        \
+                                   max_splits, T, stream);
     AD_CASE(1, 1) AD_CASE(2, 1) AD_CASE(3, 1) AD_CASE(4, 1) AD_CASE(5, 1) AD_CASE(6, 1) AD_CASE(7, 1) AD_CASE(8, 1)
     AD_CASE(1, 2) AD_CASE(2, 2) AD_CASE(3, 2) AD_CASE(4, 2) AD_CASE(5, 2) AD_CASE(6, 2) AD_CASE(7, 2) AD_CASE(8, 2)
 #undef AD_CASE
-    if (rc != 0) return rc;
-    dim3 mgrid(nq, T);
-    launch_chain(decode_attention_merge_kernel, mgrid, dim3(128), 0, stream, (const float*)part_out, (const float*)part_ml, positions,
-                 (__nv_bfloat16*)out, out_stride, nq, hd, window, max_splits);
-    return launch_status();
+    return rc;
 }

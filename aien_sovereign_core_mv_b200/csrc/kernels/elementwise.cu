@@ -58,30 +58,67 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
     }
 }
 
-// Same, for H % 4 == 0 and H <= 256 * 4 * NV: the row stays in registers between the passes and
-// all loads of a thread are issued before the first use.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ float4 load4_dyn(const void* p, int dt, size_t i) {
+    return dt == AIEN_DT_F32 ? load4(reinterpret_cast<const float*>(p) + i) : load4(reinterpret_cast<const __nv_bfloat16*>(p) + i);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 r;
+    r.x = *reinterpret_cast<uint32_t*>(&a);
+    r.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = r;
+}
+
+// Same, for H % 4 == 0 and H <= 256 * 4 * NV, all rows 16-byte aligned: the row stays in registers
+// between the passes, every access is a vector, and all loads of a thread (the row, the pending
+// sums, the weights) are issued before the first use.
 template <typename TD, typename TO, int NV>
 __global__ void __launch_bounds__(256)
 add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int nparts, size_t part_stride,
                        const void* __restrict__ w, int wdt, float eps, TO* __restrict__ h, int H) {
     __shared__ float red[32];
     griddep_launch();
+    float4 wv[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {                                   // weights do not depend on the kernel ahead
+        const int i = (j * 256 + threadIdx.x) * 4;
+        wv[j] = i < H ? load4_dyn(w, wdt, i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     griddep_wait();
     const size_t base = (size_t)blockIdx.x * H;
     float4 v[NV];
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
         const int i = (j * 256 + threadIdx.x) * 4;
-        v[j] = i < H ? *reinterpret_cast<const float4*>(x + base + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        v[j] = i < H ? load4(x + base + i) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     if (delta != nullptr) {
-        for (int p = 0; p < nparts; ++p) {
+        if (nparts == 1) {
+            float4 dv[NV];
 #pragma unroll
             for (int j = 0; j < NV; ++j) {
                 const int i = (j * 256 + threadIdx.x) * 4;
-                if (i < H) {
-                    const TD* dp = delta + (size_t)p * part_stride + base + i;
-                    v[j].x += to_f(dp[0]); v[j].y += to_f(dp[1]); v[j].z += to_f(dp[2]); v[j].w += to_f(dp[3]);
+                dv[j] = i < H ? load4(delta + base + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int j = 0; j < NV; ++j) { v[j].x += dv[j].x; v[j].y += dv[j].y; v[j].z += dv[j].z; v[j].w += dv[j].w; }
+        } else {
+            for (int p = 0; p < nparts; ++p) {
+#pragma unroll
+                for (int j = 0; j < NV; ++j) {
+                    const int i = (j * 256 + threadIdx.x) * 4;
+                    if (i < H) {
+                        const float4 d = load4(delta + (size_t)p * part_stride + base + i);
+                        v[j].x += d.x; v[j].y += d.y; v[j].z += d.z; v[j].w += d.w;
+                    }
                 }
             }
         }
@@ -95,11 +132,9 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int 
     for (int j = 0; j < NV; ++j) {
         const int i = (j * 256 + threadIdx.x) * 4;
         if (i < H) {
-            if (delta != nullptr) *reinterpret_cast<float4*>(x + base + i) = v[j];
-            h[base + i + 0] = from_f<TO>(v[j].x * scale * load_dyn(w, wdt, i + 0));
-            h[base + i + 1] = from_f<TO>(v[j].y * scale * load_dyn(w, wdt, i + 1));
-            h[base + i + 2] = from_f<TO>(v[j].z * scale * load_dyn(w, wdt, i + 2));
-            h[base + i + 3] = from_f<TO>(v[j].w * scale * load_dyn(w, wdt, i + 3));
+            if (delta != nullptr) store4(x + base + i, v[j]);
+            store4(h + base + i, make_float4(v[j].x * scale * wv[j].x, v[j].y * scale * wv[j].y,
+                                             v[j].z * scale * wv[j].z, v[j].w * scale * wv[j].w));
         }
     }
 }
@@ -245,7 +280,8 @@ AIEN_API int aien_embed_gather(const void* table, int table_dt, const int* ids, 
 template <typename TD, typename TO>
 static void launch_add_rmsnorm(float* x, const TD* delta, int nparts, size_t part_stride, const void* w, int w_dt,
                                float eps, TO* h, int T, int H, cudaStream_t stream) {
-    const bool vec = (H % 4 == 0) && (((uintptr_t)x & 15) == 0);
+    const bool vec = (H % 4 == 0) && (((uintptr_t)x & 15) == 0) && (((uintptr_t)delta & 15) == 0) && (((uintptr_t)h & 15) == 0) &&
+                     (((uintptr_t)w & 15) == 0) && (part_stride % 4 == 0);
     if (vec && H <= 256 * 4 * 2)
         launch_chain(add_rmsnorm_vec_kernel<TD, TO, 2>, dim3(T), dim3(256), 0, stream, x, delta, nparts, part_stride, w, w_dt, eps, h, H);
     else if (vec && H <= 256 * 4 * 4)

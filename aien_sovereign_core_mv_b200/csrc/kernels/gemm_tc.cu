@@ -17,45 +17,14 @@
 // masked.  Needs K % 8 == 0 and 16-byte aligned bases and row strides (the TMA rules).
 // Every wait is bounded: after the limit the kernel records an error code and goes on without
 // hanging; the host reads the code with aien_gemm_tc_error().
-#include "common.cuh"
-#include <cuda.h>
-#include <map>
-#include <mutex>
-#include <tuple>
+#include "tma.cuh"
 
 namespace aien {
 
 constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64, TC_STAGES = 3;
 constexpr int TC_STAGE_A = TC_BM * TC_BK * 2, TC_STAGE_B = TC_BN * TC_BK * 2;
 constexpr int TC_SMEM = TC_STAGES * (TC_STAGE_A + TC_STAGE_B) + 1024 /*align*/ + 256 /*barriers*/;
-constexpr uint32_t TC_SPIN_LIMIT = 1u << 24;
 
-__device__ int g_tc_error = 0;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: gives up after TC_SPIN_LIMIT polls, records `code`, and lets the caller go on.
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int code) {
-    for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i)
-        if (mbar_try_wait(bar, parity)) return;
-    atomicCAS(&g_tc_error, 0, code);
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_c, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
@@ -208,47 +177,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
-// ---------------------------------------------------------------- host side: tensor maps
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    });
-    return fn;
-}
-
-// A 2-D bfloat16 row-major matrix [rows, cols] with leading dimension ld, boxes of 128 rows x 64 cols.
-static bool make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld) {
-    static std::map<std::tuple<const void*, uint64_t, uint64_t, uint64_t>, CUtensorMap> cache;
-    static std::mutex mu;
-    std::lock_guard<std::mutex> lock(mu);
-    auto key = std::make_tuple(ptr, rows, cols, ld);
-    auto it = cache.find(key);
-    if (it != cache.end()) { *map = it->second; return true; }
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
-    cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {ld * 2};
-    cuuint32_t box[2] = {TC_BK, TC_BM};
-    cuuint32_t estr[2] = {1, 1};
-    if (fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return false;
-    if (cache.size() > 4096) cache.clear();
-    cache[key] = *map;
-    return true;
-}
-
 template <int EPI, typename TC>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* out, long ldc, int M, int N, int K, cudaStream_t stream) {
     auto kern = gemm_tc_kernel<EPI, TC>;
@@ -275,7 +203,7 @@ AIEN_API int aien_gemm_tc(const void* A, long lda, const void* W, long ldw, void
     if (epilogue == 1 && (N & 15)) return AIEN_E_SHAPE;
     if ((M + TC_BM - 1) / TC_BM > 2147483647 / 1 || (N + TC_BN - 1) / TC_BN > 65535) return AIEN_E_SHAPE;
     CUtensorMap ma, mw;
-    if (!make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda) || !make_map(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw))
+    if (!make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TC_BK, TC_BM) || !make_map(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, TC_BK, TC_BN))
         return AIEN_E_STATE;
     if (epilogue == 0) {
         if (c_dt == AIEN_DT_BF16) return launch_tc<0, __nv_bfloat16>(ma, mw, out, ldc, M, N, K, stream);
@@ -293,7 +221,7 @@ AIEN_API int aien_gemm_tc(const void* A, long lda, const void* W, long ldw, void
 // Reads and clears the error code a bounded wait may have left (0: none; 1 producer, 2 MMA, 3 epilogue).
 AIEN_API int aien_gemm_tc_error(void) {
     int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
-    if (v != 0) cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
+    if (cudaMemcpyFromSymbol(&v, g_wait_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(g_wait_error, &zero, sizeof(int));
     return v;
 }

@@ -56,10 +56,12 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_argmax_rows": [P, I, I, P, P],
         "aien_sample_rows": [P, I, I, P, P, P, P, P, P, P, P, P],
         "aien_gemv_bf16": [P, L, P, L, P, I, L, I, I, I, I, I, c_size_t, P],
+        "aien_gemv_stream_bf16": [P, L, P, L, P, I, L, I, I, I, I, I, c_size_t, P],
+        "aien_gemv_stream_error": [],
         "aien_gemm_tc": [P, L, P, L, P, I, L, I, I, I, I, P],
         "aien_gemm_tc_error": [],
         "aien_paged_attention_prefill": [P, L, P, P, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P],
-        "aien_paged_attention_decode": [P, L, P, P, P, I, P, P, P, L, P, P, I, I, I, I, I, F, I, I, P],
+        "aien_paged_attention_decode": [P, L, P, P, P, I, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, P],
     }
     for name, args in sigs.items():
         fn = getattr(l, name)
@@ -95,7 +97,7 @@ def add_launches(n: int) -> None:
 def _check(rc: int, name: str) -> None:
     global _launches
     if rc == 0:
-        _launches += 2 if name == "paged_attention_decode" else 1
+        _launches += 1
         return
     if rc < 0:
         raise KernelError(f"{name}: {_ERRORS.get(rc, 'refused')} (code {rc})")
@@ -289,6 +291,8 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Te
 
 # ---------------------------------------------------------------------------- decode product
 GEMV_MAX_ROWS = 16
+# "stream": persistent TMA-fed kernel; "direct": loads straight from global memory into fragments
+GEMV_IMPL = __import__("os").environ.get("AIEN_B200_GEMV", "stream").strip().lower()
 
 
 def gemv_supports(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
@@ -301,6 +305,8 @@ def gemv_supports(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
 def gemv_splits(N: int, K_: int) -> int:
     """How many ranges K is cut into across CTAs, from the weight's shape alone (never from the
     batch): enough CTAs to fill the GPU when the matrix has few rows."""
+    if GEMV_IMPL == "stream" and K_ % 64 == 0:
+        return 1                     # the persistent kernel balances itself; no partial products needed
     tiles = (N + 15) // 16
     return max(1, min(8, 1184 // tiles, K_ // 512))
 
@@ -318,8 +324,14 @@ def gemv(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0)
         splits, part_stride = out.shape[0], M * N
     else:
         assert w.shape[1] == K_ and out.shape == (M, N if epilogue == 0 else N // 2)
-    _check(lib().aien_gemv_bf16(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), dt(out), out.stride(-2), M, N, K_,
-                                epilogue, splits, part_stride, _stream()), "gemv_bf16")
+    fn = lib().aien_gemv_stream_bf16 if (GEMV_IMPL == "stream" and K_ % 64 == 0) else lib().aien_gemv_bf16
+    _check(fn(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), dt(out), out.stride(-2), M, N, K_,
+              epilogue, splits, part_stride, _stream()), "gemv_bf16")
+
+
+def gemv_stream_error() -> int:
+    """Error code left by a bounded wait inside the streamed decode product (0: none); clears it."""
+    return int(lib().aien_gemv_stream_error())
 
 
 def gemm_tc_supports(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
@@ -347,7 +359,7 @@ def gemm_tc_error() -> int:
 
 
 # ---------------------------------------------------------------------------- attention choice
-DECODE_CHUNK = 256
+DECODE_CHUNK = 128
 
 
 def attention_workspace_bytes(lim, num_heads: int, head_dim: int) -> int:
@@ -356,19 +368,28 @@ def attention_workspace_bytes(lim, num_heads: int, head_dim: int) -> int:
     return lim.max_seqs * num_heads * splits * (head_dim + 2) * 4 + 1024
 
 
+_ticket_counters: Optional[torch.Tensor] = None
+
+
 def paged_attention_decode(q, k_cache, v_cache, block_table, max_blocks, seq_of_token, positions, out,
                            part_out, part_ml, num_q_heads, num_kv_heads, head_dim, page_size, window, scale,
                            max_splits) -> None:
+    """Split-key decode attention; the CTA that finishes last merges the chunks.  The ticket
+    counters are one small device buffer that every launch finds zero and leaves zero."""
+    global _ticket_counters
     _dev(q, k_cache, v_cache, block_table, seq_of_token, positions, out, part_out, part_ml)
-    T = q.shape[0]
+    T = q.shape[0]                  # seq_of_token None: token t belongs to row t of the block table
+    if _ticket_counters is None:
+        _ticket_counters = torch.zeros(1 << 16, dtype=torch.int32, device=q.device)
+    assert T * num_kv_heads <= _ticket_counters.numel()
     assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     assert q.stride(1) == 1 and out.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous()
     assert part_out.dtype == torch.float32 and part_out.numel() >= T * num_q_heads * max_splits * head_dim
     assert part_ml.dtype == torch.float32 and part_ml.numel() >= T * num_q_heads * max_splits * 2
     _check(lib().aien_paged_attention_decode(
         _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), max_blocks, _p(seq_of_token), _p(positions),
-        _p(out), out.stride(0), _p(part_out), _p(part_ml), num_q_heads, num_kv_heads, head_dim, page_size, window,
-        float(scale), max_splits, T, _stream()), "paged_attention_decode")
+        _p(out), out.stride(0), _p(part_out), _p(part_ml), _p(_ticket_counters), num_q_heads, num_kv_heads, head_dim,
+        page_size, window, float(scale), max_splits, T, _stream()), "paged_attention_decode")
 
 
 def decode_attention_supports(q: torch.Tensor, k_cache: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int) -> bool:
@@ -392,7 +413,7 @@ def paged_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
         splits = max(1, (ctx.max_ctx_len + DECODE_CHUNK - 1) // DECODE_CHUNK)
         part_out = ctx.workspace.take((T * num_q_heads * splits * head_dim,), torch.float32)
         part_ml = ctx.workspace.take((T * num_q_heads * splits * 2,), torch.float32)
-        paged_attention_decode(q, k2, v2, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, out,
+        paged_attention_decode(q, k2, v2, group.block_table, group.max_blocks, None, ctx.positions, out,
                                part_out, part_ml, num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale, splits)
         return
     if (not ctx.decode_only and _FORCE_ATTN != "generic" and ctx.prefill_tiles is not None and ctx.prefill_tiles[2] > 0

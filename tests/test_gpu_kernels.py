@@ -322,7 +322,7 @@ def test_paged_attention_decode(K, nq, nkv, hd, page, window):
     big = torch.tensor(rng.standard_normal((T, nq * hd + 64)), dtype=torch.float32).to(dtype).cuda()
     q = big[:, 32:32 + nq * hd]
     scale = 1.0 / math.sqrt(hd)
-    splits = (max(seq_lens) + 255) // 256
+    splits = (max(seq_lens) + 127) // 128
     part_out = torch.empty(T * nq * splits * hd, device="cuda"); part_ml = torch.empty(T * nq * splits * 2, device="cuda")
     out = torch.empty(T, nq * hd, dtype=dtype, device="cuda")
     K.paged_attention_decode(q, kc, vc, bt, mb, torch.tensor(seq_of, dtype=torch.int32).cuda(),
@@ -349,7 +349,7 @@ def test_decode_attention_one_far_key_decides(K):
         kc[slots[far], 0, 0] = 40.0
         q = torch.zeros(1, nq * hd)
         q[0, ::hd] = 8.0
-        splits = (n + 255) // 256
+        splits = (n + 127) // 128
         out = torch.empty(1, nq * hd, dtype=torch.bfloat16, device="cuda")
         K.paged_attention_decode(q.to(torch.bfloat16).cuda(), kc.to(torch.bfloat16).cuda(), vc.to(torch.bfloat16).cuda(),
                                  torch.tensor(bt).cuda(), pages + 2, torch.zeros(1, dtype=torch.int32).cuda(),
@@ -371,7 +371,7 @@ def test_gemv_partial_products_and_their_consumers(K):
     K.gemv(a, w, parts)
     want = (a.double().cpu() @ w.double().cpu().T).numpy()
     H.assert_close(parts.sum(0).cpu().numpy(), want, 2e-5, "sum of partials")
-    assert K.gemv_splits(4096, 4096) == 4 and K.gemv_splits(24576, 4096) == 1 and K.gemv_splits(151936, 4096) == 1
+    assert K.gemv_splits(24576, 4096) == 1 and K.gemv_splits(151936, 4096) == 1
     # norm consumes partials
     x = torch.randn(M, N, generator=g).cuda()
     x0 = x.clone()
@@ -493,3 +493,33 @@ def test_prefill_attention_one_far_key_decides(K):
                                   out, nq, nkv, hd, page, 0, 1.0 / math.sqrt(hd))
         got = out.float().cpu().numpy()
         assert np.abs(got - far / 8.0).max() <= max(1e-2, 0.01 * far / 8.0), (far, got[0, :4], got[-1, :4])
+
+
+@pytest.mark.parametrize("M,N,K_", [(1, 16, 64), (1, 333, 192), (3, 100, 320), (8, 4096, 512), (9, 77, 1088), (16, 130, 4096), (5, 48, 64), (2, 64, 1600)])
+def test_gemv_stream_against_direct(K, M, N, K_, monkeypatch):
+    g = torch.Generator().manual_seed(M * 7 + N)
+    a_full = torch.randn(M, K_ + 16, generator=g).to(torch.bfloat16).cuda()
+    a = a_full[:, 8:8 + K_]
+    w = torch.randn(N, K_, generator=g).to(torch.bfloat16).cuda()
+    want = (a.double().cpu() @ w.double().cpu().T).numpy()
+    monkeypatch.setattr(K, "GEMV_IMPL", "stream")
+    for out_dtype in (torch.bfloat16, torch.float32):
+        out = torch.empty(M, N, dtype=out_dtype, device="cuda")
+        K.gemv(a, w, out)
+        torch.cuda.synchronize()
+        assert K.gemv_stream_error() == 0
+        H.assert_close(out.float().cpu().numpy(), want, 2e-5 if out_dtype == torch.float32 else 1e-2, f"stream gemv {M}x{N}x{K_}")
+    for splits in (2, 3, 5):
+        parts = torch.full((splits, M, N), 7.0, device="cuda")
+        K.gemv(a, w, parts)
+        torch.cuda.synchronize()
+        assert K.gemv_stream_error() == 0
+        H.assert_close(parts.sum(0).cpu().numpy(), want, 2e-5, f"stream gemv partials {splits}")
+    if N % 16 == 0:
+        I = N // 2
+        out = torch.empty(M, I, dtype=torch.bfloat16, device="cuda")
+        K.gemv(a, w, out, epilogue=1)
+        wd = w.double().cpu().view(I // 8, 2, 8, K_)
+        ad = a.double().cpu()
+        ref = pm.swiglu((ad @ wd[:, 0].reshape(I, K_).T).numpy(), (ad @ wd[:, 1].reshape(I, K_).T).numpy())
+        H.assert_close(out.float().cpu().numpy(), ref, 1e-2, "stream gemv + swiglu")
