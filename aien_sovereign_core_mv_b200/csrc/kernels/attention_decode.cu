@@ -306,7 +306,9 @@ static int launch_decode(const void* q, long q_stride, const void* kc, const voi
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return AIEN_E_STATE;
     }
     dim3 grid(max_splits, nkv, T);
-    launch_chain(kern, grid, dim3(AD_WARPS * 32), smem, stream, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc,
+    // A plain launch: measured, this kernel loses when its CTAs become resident early (they wait
+    // on the kernel ahead while holding the slots its own tail needs).
+    kern<<<grid, AD_WARPS * 32, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc,
                  (const __nv_bfloat16*)vc, bt, max_blocks, seq_of_token, positions,
                  part_out, part_ml, counters, (__nv_bfloat16*)out, out_stride, nq, nkv, hd, page_size, window, scale, max_splits);
     return launch_status();

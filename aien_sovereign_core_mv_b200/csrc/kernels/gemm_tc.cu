@@ -158,13 +158,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const int oc0 = (n0 + c0) / 2;
                     TC* dst = out + (size_t)row * ldc + oc0;
                     const int valid = N / 2 - oc0;
+                    float y[16];
 #pragma unroll
                     for (int run = 0; run < 2; ++run)
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             const float g = __uint_as_float(r[run * 16 + j]), u = __uint_as_float(r[run * 16 + 8 + j]);
-                            if (run * 8 + j < valid) dst[run * 8 + j] = from_f<TC>(g / (1.0f + expf(-g)) * u);
+                            y[run * 8 + j] = __fdividef(g, 1.0f + __expf(-g)) * u;
                         }
+                    if (valid >= 16 && sizeof(TC) == 2 && (((uintptr_t)dst & 15) == 0)) {
+                        uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+                        for (int v = 0; v < 2; ++v) {
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(y[8 * v + 0], y[8 * v + 1]), p1 = __floats2bfloat162_rn(y[8 * v + 2], y[8 * v + 3]);
+                            __nv_bfloat162 p2 = __floats2bfloat162_rn(y[8 * v + 4], y[8 * v + 5]), p3 = __floats2bfloat162_rn(y[8 * v + 6], y[8 * v + 7]);
+                            uint4 o;
+                            o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+                            o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+                            d4[v] = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (j < valid) dst[j] = from_f<TC>(y[j]);
+                    }
                 }
             }
         }
