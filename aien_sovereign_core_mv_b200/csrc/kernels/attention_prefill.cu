@@ -1,11 +1,12 @@
 // Prefill attention over the paged bfloat16 cache: portions of prompts (any length, any offset
 // into their request) beside single tokens, causal, grouped-query, optional window.
 //
-// One CTA of four warps handles 64 consecutive query tokens of one request for one query head;
+// One CTA of eight warps handles 128 consecutive query tokens of one request for one query head;
 // the host lists these tiles (request, offset into its portion).  Keys are visited in blocks of
 // 64 aligned to absolute positions, read through the block table into shared memory with
-// cp.async (rows of masked or absent keys are zero-filled), K and V in separate buffers so that
-// the next block's loads run under the current block's math.  Scores and the weighted sum run on
+// cp.async (rows of masked or absent keys are zero-filled) into two buffers, so that the next
+// block's K and V arrive under the current block's math.  A warp whose 16 rows lie beyond the
+// portion only helps loading.  Scores and the weighted sum run on
 // mma.sync.m16n8k16 (bfloat16 in, float32 accumulate) with ldmatrix-fed fragments; softmax is
 // online, float32, per query row, with the per-row causal and window limits applied to the
 // scores.  Formulas: crates/aien-inference-abi/src/backend.rs:280-306 (row i of a portion sees
@@ -17,7 +18,7 @@
 
 namespace aien {
 
-constexpr int AP_BM = 64, AP_BN = 64, AP_THREADS = 128;
+constexpr int AP_BM = 128, AP_BN = 64, AP_THREADS = 256;
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
     const int n = valid ? 16 : 0;
@@ -43,7 +44,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 template <int HD>
-__global__ void __launch_bounds__(AP_THREADS)
+__global__ void __launch_bounds__(AP_THREADS, (HD <= 128 ? 2 : 1))
 paged_prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
                                const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                                const int* __restrict__ block_table, int max_blocks,
@@ -57,10 +58,9 @@ paged_prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_strid
     constexpr int CH = HD / 8;                    // 16-byte chunks per row
     extern __shared__ __align__(16) uint8_t ap_smem[];
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(ap_smem);
-    __nv_bfloat16* Ks = Qs + AP_BM * STR;
-    __nv_bfloat16* Vs = Ks + AP_BN * STR;
-    const uint32_t Qs_u = (uint32_t)__cvta_generic_to_shared(Qs), Ks_u = (uint32_t)__cvta_generic_to_shared(Ks),
-                   Vs_u = (uint32_t)__cvta_generic_to_shared(Vs);
+    __nv_bfloat16* KVs = Qs + AP_BM * STR;            // [2 buffers][K | V][AP_BN][STR]
+    const uint32_t Qs_u = (uint32_t)__cvta_generic_to_shared(Qs), KV_u = (uint32_t)__cvta_generic_to_shared(KVs);
+    constexpr uint32_t BUF_BYTES = 2 * AP_BN * STR * 2, V_OFF = AP_BN * STR * 2;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, c = lane & 3;
@@ -96,23 +96,24 @@ paged_prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_strid
             const __nv_bfloat16* src = cache + ((size_t)(valid ? slot : 0) * nkv + kvh) * HD + ch * 8;
             cp_async16(dst_u + (uint32_t)(r * STR + ch * 8) * 2, src, valid);
         }
-        cp_async_commit();
     };
 
     const int kb_begin = first / AP_BN, kb_end = pos_last / AP_BN;
-    load_kv(k_cache, Ks_u, kb_begin);
-    load_kv(v_cache, Vs_u, kb_begin);
+    auto load_block = [&](int kb) {                 // K and V of one block: one commit group
+        const uint32_t buf = KV_u + (uint32_t)((kb - kb_begin) & 1) * BUF_BYTES;
+        load_kv(k_cache, buf, kb);
+        load_kv(v_cache, buf + V_OFF, kb);
+        cp_async_commit();
+    };
+    load_block(kb_begin);
 
     // query fragments of this warp's 16 rows
-    cp_async_wait<2>();
+    cp_async_wait<1>();
     __syncthreads();
-    uint32_t qf[KS][4];
-#pragma unroll
-    for (int kk = 0; kk < KS; ++kk) {
-        const int mi = lane >> 3;
-        const int row = warp * 16 + (mi & 1) * 8 + (lane & 7), col = kk * 16 + (mi >> 1) * 8;
-        ldmatrix_x4(Qs_u + (uint32_t)(row * STR + col) * 2, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
-    }
+    const bool active = warp * 16 < rows;
+    // Q stays in shared memory; its fragments are re-read per k-step (one ldmatrix against the
+    // four that fetch K), which keeps the kernel at two CTAs per SM.
+    const uint32_t q_frag_u = Qs_u + (uint32_t)((warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * STR + (lane >> 4) * 8) * 2;
 
     float o[DT][4];
 #pragma unroll
@@ -123,25 +124,28 @@ paged_prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_strid
 
     for (int kb = kb_begin; kb <= kb_end; ++kb) {
         const bool more = kb < kb_end;
-        cp_async_wait<1>();                          // K(kb) has landed (V(kb) may still be in flight)
-        __syncthreads();
+        if (more) load_block(kb + 1);                // into the other buffer: free since the sync that ended block kb-1
+        if (more) cp_async_wait<1>(); else cp_async_wait<0>();
+        __syncthreads();                             // K(kb), V(kb) have landed for every thread
+        const uint32_t Ks_u = KV_u + (uint32_t)((kb - kb_begin) & 1) * BUF_BYTES, Vs_u = Ks_u + V_OFF;
+        if (active && kb * AP_BN <= pos0 + warp * 16 + 15) {     // the block is not wholly in this warp's future
         float sc[AP_BN / 8][4];
 #pragma unroll
         for (int j = 0; j < AP_BN / 8; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
 #pragma unroll
         for (int kk = 0; kk < KS; ++kk) {
+            uint32_t q0r, q1r, q2r, q3r;
+            ldmatrix_x4(q_frag_u + kk * 32, q0r, q1r, q2r, q3r);
 #pragma unroll
             for (int j = 0; j < AP_BN / 8; j += 2) {
                 const int mi = lane >> 3;
                 const int row = (j + (mi >> 1)) * 8 + (lane & 7), col = kk * 16 + (mi & 1) * 8;
                 uint32_t b0, b1, b2, b3;
                 ldmatrix_x4(Ks_u + (uint32_t)(row * STR + col) * 2, b0, b1, b2, b3);
-                ap_mma(sc[j], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
-                ap_mma(sc[j + 1], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b2, b3);
+                ap_mma(sc[j], q0r, q1r, q2r, q3r, b0, b1);
+                ap_mma(sc[j + 1], q0r, q1r, q2r, q3r, b2, b3);
             }
         }
-        __syncthreads();                             // every warp is done with the K buffer
-        if (more) load_kv(k_cache, Ks_u, kb + 1);
 
         // ---- online softmax (scores in log2 units)
         float mx0 = -INFINITY, mx1 = -INFINITY;
@@ -182,8 +186,6 @@ paged_prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_strid
         for (int d = 0; d < DT; ++d) { o[d][0] *= corr0; o[d][1] *= corr0; o[d][2] *= corr1; o[d][3] *= corr1; }
 
         // ---- O += P . V
-        if (more) cp_async_wait<1>(); else cp_async_wait<0>();   // V(kb) has landed
-        __syncthreads();
 #pragma unroll
         for (int ks = 0; ks < AP_BN / 16; ++ks) {
             const uint32_t a0 = pack_bf16(sc[2 * ks][0], sc[2 * ks][1]), a1 = pack_bf16(sc[2 * ks][2], sc[2 * ks][3]);
@@ -197,8 +199,8 @@ paged_prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_strid
                 ap_mma(o[d + 1], a0, a1, a2, a3, b2, b3);
             }
         }
-        __syncthreads();                             // every warp is done with the V buffer
-        if (more) load_kv(v_cache, Vs_u, kb + 1);
+        }
+        __syncthreads();                             // every warp is done with this block's buffer
     }
 
     l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1); l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
@@ -221,7 +223,7 @@ static int launch_prefill(const void* q, long q_stride, const void* kc, const vo
                           void* out, long out_stride, int nq, int nkv, int page_size, int window, float scale,
                           cudaStream_t stream) {
     constexpr int STR = HD + 8;
-    const int smem = (AP_BM + 2 * AP_BN) * STR * 2;
+    const int smem = (AP_BM + 4 * AP_BN) * STR * 2;
     auto kern = paged_prefill_attention_kernel<HD>;
     static bool configured = false;
     if (smem > 48 * 1024 && !configured) {
@@ -240,7 +242,7 @@ static int launch_prefill(const void* q, long q_stride, const void* kc, const vo
 using namespace aien;
 
 // tile_seq/tile_q0 [num_tiles]: request index in the step and offset of the tile's first query in
-// that request's portion (multiples of 64).
+// that request's portion (multiples of 128).
 AIEN_API int aien_paged_attention_prefill(
     const void* q, long q_stride, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
     const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_q0, int num_tiles,

@@ -132,7 +132,7 @@ class Engine:
                 groups.append((bt, o, self.max_blocks))
                 o += _align4(max(T, 1))
         off["groups"] = groups
-        n_tiles = T // 64 + S + 1                     # 64-token query tiles of the prefill attention kernel
+        n_tiles = T // K.PREFILL_TILE + S + 1         # query tiles of the prefill attention kernel
         off["tile_seq"] = o
         o += _align4(n_tiles)
         off["tile_q0"] = o
@@ -245,9 +245,9 @@ class Engine:
         n_tiles = 0
         if not decode_only:
             for i, c in enumerate(counts):
-                k = (c + 63) // 64
+                k = (c + K.PREFILL_TILE - 1) // K.PREFILL_TILE
                 m[off["tile_seq"] + n_tiles:off["tile_seq"] + n_tiles + k] = i
-                m[off["tile_q0"] + n_tiles:off["tile_q0"] + n_tiles + k] = np.arange(k, dtype=np.int32) * 64
+                m[off["tile_q0"] + n_tiles:off["tile_q0"] + n_tiles + k] = np.arange(k, dtype=np.int32) * K.PREFILL_TILE
                 n_tiles += k
         if Tp > T:
             self._pad_meta(m, off, T, Tp)

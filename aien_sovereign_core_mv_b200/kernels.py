@@ -360,6 +360,7 @@ def gemm_tc_error() -> int:
 
 # ---------------------------------------------------------------------------- attention choice
 DECODE_CHUNK = 128
+PREFILL_TILE = 128         # query tokens per CTA of the prefill attention kernel
 
 
 def attention_workspace_bytes(lim, num_heads: int, head_dim: int) -> int:

@@ -452,15 +452,15 @@ def test_paged_attention_prefill(K, nq, nkv, hd, page, window):
     dtype = torch.bfloat16
     rng = np.random.default_rng(nq * 31 + hd)
     seq_lens = [130, 64, 300, 5, 200]                 # context after the step
-    q_lens = [130, 1, 77, 2, 64]                      # tokens the step brings: whole, decode, offset portion, 2, one full tile
+    q_lens = [130, 1, 77, 2, 128]                     # tokens the step brings: whole, decode, offset portion, 2, one full tile
     kc, vc, bt, mb, dense = paged_setup(rng, seq_lens, nkv, hd, page, dtype, sum((n + page - 1) // page for n in seq_lens) + 8)
     seq_of, positions, q_start, tile_seq, tile_q0 = [], [], [0], [], []
     for s, (n, ql) in enumerate(zip(seq_lens, q_lens)):
         seq_of += [s] * ql
         positions += list(range(n - ql, n))
         q_start.append(q_start[-1] + ql)
-        for t in range((ql + 63) // 64):
-            tile_seq.append(s); tile_q0.append(t * 64)
+        for t in range((ql + K.PREFILL_TILE - 1) // K.PREFILL_TILE):
+            tile_seq.append(s); tile_q0.append(t * K.PREFILL_TILE)
     T = len(seq_of)
     big = torch.tensor(rng.standard_normal((T, nq * hd + 64)), dtype=torch.float32).to(dtype).cuda()
     q = big[:, 32:32 + nq * hd]

@@ -24,8 +24,8 @@ def make_ctx(dtype, positions, seq_of_token, q_start, ctx_len, groups=(), nbytes
     ws.begin_layer()
     tiles_s, tiles_q = [], []
     for s in range(S):
-        for t in range((q_start[s + 1] - q_start[s] + 63) // 64):
-            tiles_s.append(s); tiles_q.append(64 * t)
+        for t in range((q_start[s + 1] - q_start[s] + 127) // 128):
+            tiles_s.append(s); tiles_q.append(128 * t)
     return StepContext(dtype=dtype, num_tokens=T, num_seqs=S, token_ids=i32([0] * T), positions=i32(positions),
                        seq_of_token=i32(seq_of_token), q_start=i32(q_start), ctx_len=i32(ctx_len), groups=list(groups),
                        workspace=ws, max_q_len=max(q_start[i + 1] - q_start[i] for i in range(S)), max_ctx_len=max(ctx_len),
