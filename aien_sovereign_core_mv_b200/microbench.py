@@ -1,0 +1,156 @@
+"""Single kernels at model shapes, for timing and for profiler captures.
+
+    python -m aien_sovereign_core_mv_b200.microbench gemv --n 24576 --k 4096 --m 1 --epilogue 1
+    python -m aien_sovereign_core_mv_b200.microbench gemm --m 2048 --n 24576 --k 4096 --epilogue 1
+    python -m aien_sovereign_core_mv_b200.microbench attn-decode --batch 1 --ctx 1030
+    python -m aien_sovereign_core_mv_b200.microbench attn-prefill --tokens 2048
+    python -m aien_sovereign_core_mv_b200.microbench all
+
+Every case launches its kernel a few times eagerly (what a profiler captures) and then times a
+CUDA graph of back-to-back launches over rotating weight copies larger than L2, with CUDA events.
+Attention cases use 32 query heads, 8 kv heads, head size 128, pages of 16 (the Qwen3-8B shape)
+unless told otherwise.
+"""
+from __future__ import annotations
+
+import argparse
+import math
+import sys
+
+import torch
+
+from . import kernels as K
+
+
+def _time_graph(fn, n: int) -> float:
+    fn(0)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(n):
+            fn(i)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1000.0 / n
+
+
+def gemv_case(n: int, k: int, m: int, epilogue: int, reps: int = 20) -> None:
+    copies = max(2, int(1.5e9 // (n * k * 2)))
+    ws = [torch.randn(n, k, device="cuda", dtype=torch.bfloat16) for _ in range(copies)]
+    a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(m, n // 2 if epilogue else n, device="cuda", dtype=torch.bfloat16)
+    for i in range(3):
+        K.gemv(a, ws[i % copies], out, epilogue=epilogue)
+    us = _time_graph(lambda i: K.gemv(a, ws[i % copies], out, epilogue=epilogue), reps)
+    print(f"gemv[{K.GEMV_IMPL}] N={n} K={k} M={m} epilogue={epilogue}: {us:8.2f} us  {n * k * 2 / us / 1e3:7.0f} GB/s of weights", flush=True)
+
+
+def gemm_case(m: int, n: int, k: int, epilogue: int, reps: int = 10) -> None:
+    w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+    a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(m, n // 2 if epilogue else n, device="cuda", dtype=torch.bfloat16)
+    for _ in range(3):
+        K.gemm_tc(a, w, out, epilogue=epilogue)
+    us = _time_graph(lambda i: K.gemm_tc(a, w, out, epilogue=epilogue), reps)
+    print(f"gemm_tc M={m} N={n} K={k} epilogue={epilogue}: {us:9.1f} us  {2.0 * m * n * k / us / 1e6:7.1f} TFLOP/s  (error flag {K.gemm_tc_error()})", flush=True)
+
+
+def _paged_cache(batch: int, ctx: int, nkv: int, hd: int, page: int):
+    pages_per = (ctx + page - 1) // page
+    n_pages = batch * pages_per + 4
+    kc = torch.randn(n_pages * page, nkv, hd, device="cuda", dtype=torch.bfloat16)
+    vc = torch.randn_like(kc)
+    width = max(256, pages_per + 1)
+    bt = torch.full((batch, width), -1, dtype=torch.int32)
+    bt[:, :pages_per] = torch.randperm(n_pages)[:batch * pages_per].view(batch, pages_per).to(torch.int32)
+    return kc, vc, bt.cuda(), width
+
+
+def attn_decode_case(batch: int, ctx: int, nq: int = 32, nkv: int = 8, hd: int = 128, page: int = 16, reps: int = 40) -> None:
+    kc, vc, bt, width = _paged_cache(batch, ctx, nkv, hd, page)
+    q = torch.randn(batch, nq * hd, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty_like(q)
+    splits = 1
+    while splits * K.DECODE_CHUNK < ctx:
+        splits *= 2
+    po = torch.empty(batch * nq * splits * hd, device="cuda")
+    pml = torch.empty(batch * nq * splits * 2, device="cuda")
+    pos = torch.full((batch,), ctx - 1, dtype=torch.int32, device="cuda")
+
+    def run(_=0):
+        K.paged_attention_decode(q, kc, vc, bt, width, None, pos, out, po, pml, nq, nkv, hd, page, 0, 1 / math.sqrt(hd), splits)
+
+    for _ in range(3):
+        run()
+    us = _time_graph(run, reps)
+    mb = batch * ctx * nkv * hd * 2 * 2 / 1e6
+    print(f"attn-decode batch={batch} ctx={ctx} ({nq}q/{nkv}kv x {hd}): {us:8.2f} us  {mb:.1f} MB of K/V  {mb / us * 1e3:7.0f} GB/s", flush=True)
+
+
+def attn_prefill_case(tokens: int, offset: int = 0, nq: int = 32, nkv: int = 8, hd: int = 128, page: int = 16, reps: int = 10) -> None:
+    ctx = offset + tokens
+    kc, vc, bt, width = _paged_cache(1, ctx, nkv, hd, page)
+    q = torch.randn(tokens, nq * hd, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty_like(q)
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device="cuda")
+    n_tiles = (tokens + K.PREFILL_TILE - 1) // K.PREFILL_TILE
+    args = (i32([0, tokens]), i32([ctx]), i32([0] * n_tiles), i32([t * K.PREFILL_TILE for t in range(n_tiles)]), n_tiles)
+
+    def run(_=0):
+        K.paged_attention_prefill(q, kc, vc, bt, width, *args, out, nq, nkv, hd, page, 0, 1 / math.sqrt(hd))
+
+    for _ in range(3):
+        run()
+    us = _time_graph(run, reps)
+    flops = 4.0 * nq * hd * (tokens * (tokens + 1) / 2 + tokens * offset)
+    print(f"attn-prefill tokens={tokens} offset={offset} ({nq}q/{nkv}kv x {hd}): {us:8.1f} us  {flops / us / 1e6:7.1f} TFLOP/s", flush=True)
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="microbench", description=__doc__.split("\n\n")[0])
+    sub = ap.add_subparsers(dest="case", required=True)
+    p = sub.add_parser("gemv")
+    p.add_argument("--n", type=int, default=24576); p.add_argument("--k", type=int, default=4096)
+    p.add_argument("--m", type=int, default=1); p.add_argument("--epilogue", type=int, default=0)
+    p = sub.add_parser("gemm")
+    p.add_argument("--m", type=int, default=2048); p.add_argument("--n", type=int, default=24576)
+    p.add_argument("--k", type=int, default=4096); p.add_argument("--epilogue", type=int, default=0)
+    p = sub.add_parser("attn-decode")
+    p.add_argument("--batch", type=int, default=1); p.add_argument("--ctx", type=int, default=1030)
+    p = sub.add_parser("attn-prefill")
+    p.add_argument("--tokens", type=int, default=2048); p.add_argument("--offset", type=int, default=0)
+    sub.add_parser("all")
+    args = ap.parse_args(argv)
+    K.lib()
+    if args.case == "gemv":
+        gemv_case(args.n, args.k, args.m, args.epilogue)
+    elif args.case == "gemm":
+        gemm_case(args.m, args.n, args.k, args.epilogue)
+    elif args.case == "attn-decode":
+        attn_decode_case(args.batch, args.ctx)
+    elif args.case == "attn-prefill":
+        attn_prefill_case(args.tokens, args.offset)
+    else:
+        shapes = {"qkv": (6144, 4096, 0), "o": (4096, 4096, 0), "gate_up": (24576, 4096, 1), "down": (4096, 12288, 0), "head": (151936, 4096, 0)}
+        for m in (1, 8, 16):
+            for name, (n, k, epi) in shapes.items():
+                gemv_case(n, k, m, epi)
+        for m in (64, 256, 2048, 8192):
+            for name, (n, k, epi) in shapes.items():
+                if name != "head":
+                    gemm_case(m, n, k, epi)
+        for b in (1, 8, 64):
+            attn_decode_case(b, 1030)
+        attn_decode_case(16, 8192)
+        for t, off in ((2048, 0), (512, 1536), (8192, 0)):
+            attn_prefill_case(t, off)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
