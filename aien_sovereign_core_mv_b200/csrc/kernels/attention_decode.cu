@@ -3,12 +3,13 @@
 // finishes last for a (token, kv head) merges the chunks.
 //
 // A chunk is the keys [c*128, c*128+128) of the request, so which keys are summed together is
-// fixed by their positions and never by the batch or the grid.  Within a CTA each of the eight
-// warps takes one group of 16 keys.  Scores for a group come from mma.sync.m16n8k16 with the 16
-// keys as rows and the (up to 16) query heads that share the kv head as columns; K is read
-// straight from global memory with 16-byte loads (the contraction index is permuted the same way
-// for q and K, see gemv.cu).  Softmax is float32; the weighted sum over V is plain FMAs with each
-// lane owning two adjacent dims per 64, all V loads of the group issued before their first use.
+// fixed by their positions and never by the batch or the grid.  A CTA first requests its whole
+// chunk of K and of V with cp.async (64 KB in flight per CTA at head size 128, three CTAs per SM),
+// then each of the eight warps takes one group of 16 keys.  Scores for a group come from
+// mma.sync.m16n8k16 with the 16 keys as rows and the (up to 16) query heads that share the kv
+// head as columns; the fragments are 16-byte reads of the K rows (the contraction index is
+// permuted the same way for q and K, see gemv.cu).  Softmax is float32; the weighted sum over V
+// is plain FMAs with each lane owning two adjacent dims per 64.
 // The warps are combined in warp order, the CTA's partial result (unnormalised sum, max,
 // denominator) goes to scratch, and a ticket counter per (token, kv head) tells the last CTA to
 // combine the chunks in chunk order, whichever CTA that is, and to put the counter back to zero.
@@ -25,6 +26,15 @@ constexpr int AD_WARPS = 8;
 constexpr int AD_CHUNK = 128;
 
 __device__ __forceinline__ uint4 ad_ldg16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ uint4 ad_lds16(uint32_t addr) {
+    uint4 r;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr));
+    return r;
+}
+__device__ __forceinline__ void ad_cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
 __device__ __forceinline__ void ad_mma(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -40,29 +50,60 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
                               const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                               float* __restrict__ part_out, float* __restrict__ part_ml, int* __restrict__ counters,
                               __nv_bfloat16* __restrict__ out, long out_stride,
-                              int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits) {
+                              int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int misc_bytes) {
     constexpr int DCH = (HS + 1) / 2;            // 64-dim chunks of the output
     constexpr int NH = NT * 8;
     extern __shared__ float smem[];
+    __shared__ int s_slot[AD_CHUNK];
     griddep_launch();
     griddep_wait();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, c = lane & 3;
     const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
     const int G = nq / nkv;
     const int pos = positions[t];
     // In a decode-only step token t is request t (seq_of_token may be null): the table row does not
-    // hang on another load, so the page lookups below go out together with the position load.
+    // hang on another load, so the page lookups go out together with the position load.
     const int* bt = block_table + (size_t)(seq_of_token ? seq_of_token[t] : t) * max_blocks;
-
-    // pages of this warp's 16 keys: looked up before the position is known (a key beyond the
-    // position is masked later; its page, if the table has one, belongs to this request anyway)
-    const int kj0 = split * AD_CHUNK + warp * 16 + g, kj1 = kj0 + 8;
-    const int pi0 = kj0 / page_size, pi1 = kj1 / page_size;
-    const int pg0 = pi0 < max_blocks ? bt[pi0] : -1, pg1 = pi1 < max_blocks ? bt[pi1] : -1;
+    const int chunk_base = split * AD_CHUNK;
+    if (tid < AD_CHUNK) {
+        // looked up before the position is known: a key beyond the position is masked later, and its
+        // page, if the table has one, belongs to this request anyway
+        const int key = chunk_base + tid, pi = key / page_size;
+        const int pg = pi < max_blocks ? bt[pi] : -1;
+        s_slot[tid] = pg < 0 ? -1 : pg * page_size + key % page_size;
+    }
     const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int lo = max(first, split * AD_CHUNK), hi = min(pos, split * AD_CHUNK + AD_CHUNK - 1);
+    const int lo = max(first, chunk_base), hi = min(pos, chunk_base + AD_CHUNK - 1);
     if (lo > hi) return;
+    __syncthreads();
+
+    // ---- the whole chunk of K, then of V, is requested at once with cp.async (rows of keys that are
+    // masked or absent are zero-filled).  K rows are padded so that the fragment reads below
+    // (two rows x four 16-byte pieces per quarter-warp) fall on different banks.
+    const int CH = hd / 8;                                   // 16-byte pieces per row
+    // Rows of 128-byte multiples are not padded: the pieces of odd rows are stored with bit 2 of
+    // their index flipped instead.  Other row sizes are padded to 4 (mod 8) pieces.
+    const bool swz = (CH % 8) == 0;
+    const int k_stride = swz ? hd * 2 : (CH + ((4 - CH % 8) + 8) % 8) * 16;
+    const int v_stride = hd * 2 + 16;                        // an odd number of pieces: ldmatrix rows fall on different banks
+    const uint32_t K_u = (uint32_t)__cvta_generic_to_shared(smem) + misc_bytes;
+    const uint32_t V_u = K_u + AD_CHUNK * k_stride;
+    for (int idx = tid; idx < AD_CHUNK * CH; idx += AD_WARPS * 32) {
+        const int r = idx / CH, ch = idx - r * CH;
+        const int key = chunk_base + r, sl = s_slot[r];
+        const bool valid = key >= lo && key <= hi && sl >= 0;
+        const int pc = swz ? (ch ^ ((r & 1) << 2)) : ch;
+        ad_cp_async16(K_u + r * k_stride + pc * 16, k_cache + ((size_t)(valid ? sl : 0) * nkv + kvh) * hd + ch * 8, valid);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    for (int idx = tid; idx < AD_CHUNK * CH; idx += AD_WARPS * 32) {
+        const int r = idx / CH, ch = idx - r * CH;
+        const int key = chunk_base + r, sl = s_slot[r];
+        const bool valid = key >= lo && key <= hi && sl >= 0;
+        ad_cp_async16(V_u + r * v_stride + ch * 16, v_cache + ((size_t)(valid ? sl : 0) * nkv + kvh) * hd + ch * 8, valid);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
 
     float* Ps = smem + warp * (16 * NH + NH + 16);       // [16 keys][NH heads], then corr[NH]
     float* Cs = Ps + 16 * NH;
@@ -78,39 +119,38 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
                                            : make_uint4(0u, 0u, 0u, 0u);
         }
     float m_run[NT][2], l_run[NT][2];
-    float acc[NH][DCH][2];
+    float oacc[2 * HS][NT][4];                      // out^T tiles: 16 dims x 8 heads each
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) { m_run[nt][0] = m_run[nt][1] = -INFINITY; l_run[nt][0] = l_run[nt][1] = 0.f; }
 #pragma unroll
-    for (int h = 0; h < NH; ++h)
+    for (int mt = 0; mt < 2 * HS; ++mt)
 #pragma unroll
-        for (int i = 0; i < DCH; ++i) acc[h][i][0] = acc[h][i][1] = 0.f;
+        for (int nt = 0; nt < NT; ++nt) oacc[mt][nt][0] = oacc[mt][nt][1] = oacc[mt][nt][2] = oacc[mt][nt][3] = 0.f;
+    __nv_bfloat16* Pt = reinterpret_cast<__nv_bfloat16*>(Ps);   // this warp's probabilities, [head][16 keys], bfloat16
 
-    const int chunk_base = split * AD_CHUNK;
-    {
-        const int base = chunk_base + warp * 16;                 // AD_CHUNK == 16 * AD_WARPS: one group per warp
-        if (base <= hi && base + 15 >= lo) {
-        const bool ok0 = kj0 >= lo && kj0 <= hi, ok1 = kj1 >= lo && kj1 <= hi;
-        const int slot0 = (ok0 && pg0 >= 0) ? pg0 * page_size + kj0 % page_size : -1;
-        const int slot1 = (ok1 && pg1 >= 0) ? pg1 * page_size + kj1 % page_size : -1;
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncthreads();                                         // K of the chunk is in shared memory
+    const int base = chunk_base + warp * 16;                 // AD_CHUNK == 16 * AD_WARPS: one group of 16 keys per warp
+    const bool warp_has_keys = base <= hi && base + 15 >= lo;
+    const int kj0 = base + g, kj1 = kj0 + 8;
+    const bool ok0 = kj0 >= lo && kj0 <= hi && s_slot[warp * 16 + g] >= 0;
+    const bool ok1 = kj1 >= lo && kj1 <= hi && s_slot[warp * 16 + g + 8] >= 0;
+    if (warp_has_keys) {
         float S[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) S[nt][0] = S[nt][1] = S[nt][2] = S[nt][3] = 0.f;
-        const __nv_bfloat16* k0p = k_cache + ((size_t)(slot0 < 0 ? 0 : slot0) * nkv + kvh) * hd + c * 8;
-        const __nv_bfloat16* k1p = k_cache + ((size_t)(slot1 < 0 ? 0 : slot1) * nkv + kvh) * hd + c * 8;
-        uint4 kav[HS], kbv[HS];
+        const uint32_t k0a = K_u + (warp * 16 + g) * k_stride, k1a = k0a + 8 * k_stride;
+        const int sw = swz ? ((g & 1) << 2) : 0;                  // rows g and g+8 have the same parity
 #pragma unroll
         for (int ds = 0; ds < HS; ++ds) {
             const bool din = ds * 32 + c * 8 < hd;
-            kav[ds] = (slot0 >= 0 && din) ? ad_ldg16(k0p + ds * 32) : make_uint4(0u, 0u, 0u, 0u);
-            kbv[ds] = (slot1 >= 0 && din) ? ad_ldg16(k1p + ds * 32) : make_uint4(0u, 0u, 0u, 0u);
-        }
-#pragma unroll
-        for (int ds = 0; ds < HS; ++ds) {
+            const uint32_t piece = (uint32_t)((ds * 4 + c) ^ sw) * 16;
+            const uint4 ka = din ? ad_lds16(k0a + piece) : make_uint4(0u, 0u, 0u, 0u);
+            const uint4 kb = din ? ad_lds16(k1a + piece) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                ad_mma(S[nt], kav[ds].x, kbv[ds].x, kav[ds].y, kbv[ds].y, qf[nt][ds].x, qf[nt][ds].y);
-                ad_mma(S[nt], kav[ds].z, kbv[ds].z, kav[ds].w, kbv[ds].w, qf[nt][ds].z, qf[nt][ds].w);
+                ad_mma(S[nt], ka.x, kb.x, ka.y, kb.y, qf[nt][ds].x, qf[nt][ds].y);
+                ad_mma(S[nt], ka.z, kb.z, ka.w, kb.w, qf[nt][ds].z, qf[nt][ds].w);
             }
         }
         // S[nt][e]: key g, head nt*8+2c+e;  S[nt][2+e]: key g+8, same head
@@ -118,77 +158,58 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                const float s0 = slot0 >= 0 ? S[nt][e] * scale : -INFINITY;
-                const float s1 = slot1 >= 0 ? S[nt][2 + e] * scale : -INFINITY;
+                const float s0 = ok0 ? S[nt][e] * scale : -INFINITY;
+                const float s1 = ok1 ? S[nt][2 + e] * scale : -INFINITY;
                 float mx = fmaxf(s0, s1);
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-                const float m_new = fmaxf(m_run[nt][e], mx);
-                float p0 = 0.f, p1 = 0.f, corr = 1.f;
-                if (m_new != -INFINITY) {
-                    p0 = slot0 >= 0 ? expf(s0 - m_new) : 0.f;
-                    p1 = slot1 >= 0 ? expf(s1 - m_new) : 0.f;
-                    corr = m_run[nt][e] == -INFINITY ? 0.f : expf(m_run[nt][e] - m_new);
+                float p0 = 0.f, p1 = 0.f;
+                if (mx != -INFINITY) {
+                    p0 = ok0 ? expf(s0 - mx) : 0.f;
+                    p1 = ok1 ? expf(s1 - mx) : 0.f;
                 }
                 float sum = p0 + p1;
                 sum += __shfl_xor_sync(0xffffffffu, sum, 4);
                 sum += __shfl_xor_sync(0xffffffffu, sum, 8);
                 sum += __shfl_xor_sync(0xffffffffu, sum, 16);
-                l_run[nt][e] = l_run[nt][e] * corr + sum;
-                m_run[nt][e] = m_new;
+                l_run[nt][e] = sum;
+                m_run[nt][e] = mx;
                 const int h = nt * 8 + 2 * c + e;
-                Ps[g * NH + h] = p0;
-                Ps[(g + 8) * NH + h] = p1;
-                if (g == 0) Cs[h] = corr;
+                Pt[h * 16 + g] = __float2bfloat16_rn(p0);
+                Pt[h * 16 + g + 8] = __float2bfloat16_rn(p1);
             }
-        __syncwarp();
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();                                         // V of the chunk is in shared memory; P is visible
+    if (warp_has_keys) {
+        // out^T[dims, heads] += V^T[dims, 16 keys] . P[16 keys, heads]: V^T fragments by transposing
+        // ldmatrix reads of the V rows, P fragments from this warp's probabilities
+        uint32_t pb[NT][2];
 #pragma unroll
-        for (int h = 0; h < NH; ++h) {
-            if (h < G) {
-                const float cr = Cs[h];
-#pragma unroll
-                for (int i = 0; i < DCH; ++i) { acc[h][i][0] *= cr; acc[h][i][1] *= cr; }
-            }
+        for (int nt = 0; nt < NT; ++nt) {
+            const uint32_t* prow = reinterpret_cast<const uint32_t*>(Pt + (nt * 8 + g) * 16);
+            pb[nt][0] = prow[c];            // keys 2c, 2c+1 of head nt*8+g
+            pb[nt][1] = prow[c + 4];        // keys 2c+8, 2c+9
         }
-        // all V loads of the group are issued before the first use
-        uint32_t vraw[16][DCH];
+        const uint32_t vrow = V_u + (warp * 16 + (lane & 7) + ((lane >> 4) << 3)) * v_stride + ((lane >> 3) & 1) * 16;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const int sl = __shfl_sync(0xffffffffu, j < 8 ? slot0 : slot1, (j & 7) * 4);
-            const __nv_bfloat16* vp = v_cache + ((size_t)(sl < 0 ? 0 : sl) * nkv + kvh) * hd;
+        for (int mt = 0; mt < 2 * HS; ++mt) {
+            if (mt * 16 < hd) {
+                uint32_t a0, a1, a2, a3;
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(vrow + mt * 32));
 #pragma unroll
-            for (int i = 0; i < DCH; ++i) {
-                const int d = i * 64 + lane * 2;
-                vraw[j][i] = (sl >= 0 && d < hd) ? *reinterpret_cast<const uint32_t*>(vp + d) : 0u;
+                for (int nt = 0; nt < NT; ++nt) ad_mma(oacc[mt][nt], a0, a1, a2, a3, pb[nt][0], pb[nt][1]);
             }
-        }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            float2 vv[DCH];
-#pragma unroll
-            for (int i = 0; i < DCH; ++i) vv[i] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vraw[j][i]));
-#pragma unroll
-            for (int h = 0; h < NH; ++h) {
-                if (h < G) {
-                    const float p = Ps[j * NH + h];
-#pragma unroll
-                    for (int i = 0; i < DCH; ++i) {
-                        acc[h][i][0] = fmaf(p, vv[i].x, acc[h][i][0]);
-                        acc[h][i][1] = fmaf(p, vv[i].y, acc[h][i][1]);
-                    }
-                }
-            }
-        }
-        __syncwarp();
         }
     }
 
     // ---- combine the warps in warp order
     __syncthreads();
-    float* Wm = smem;                                  // [AD_WARPS][NH] max
+    float* Wm = smem;                                  // [AD_WARPS][NH] max            (over the per-warp scratch)
     float* Wl = Wm + AD_WARPS * NH;                    // [AD_WARPS][NH] denominator
-    float* Wa = Wl + AD_WARPS * NH;                    // [AD_WARPS][G][hd] sums
+    float* Wa = smem + misc_bytes / 4;                 // [AD_WARPS][G][hd] sums        (over K and V, no longer needed)
     // every lane with g == 0 holds m/l of heads 2c, 2c+1 of each tile
     if (g == 0) {
 #pragma unroll
@@ -199,17 +220,20 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
                 Wl[warp * NH + nt * 8 + 2 * c + e] = l_run[nt][e];
             }
     }
+    // oacc[mt][nt]: dims 16mt+g (regs 0,1) and 16mt+g+8 (regs 2,3), heads nt*8+2c and +1
 #pragma unroll
-    for (int h = 0; h < NH; ++h) {
-        if (h < G) {
+    for (int mt = 0; mt < 2 * HS; ++mt) {
+        if (mt * 16 < hd) {
 #pragma unroll
-            for (int i = 0; i < DCH; ++i) {
-                const int d = i * 64 + lane * 2;
-                if (d < hd) {
-                    Wa[((size_t)warp * G + h) * hd + d] = acc[h][i][0];
-                    Wa[((size_t)warp * G + h) * hd + d + 1] = acc[h][i][1];
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int h = nt * 8 + 2 * c + e;
+                    if (h < G) {
+                        Wa[((size_t)warp * G + h) * hd + mt * 16 + g] = oacc[mt][nt][e];
+                        Wa[((size_t)warp * G + h) * hd + mt * 16 + g + 8] = oacc[mt][nt][2 + e];
+                    }
                 }
-            }
         }
     }
     __syncthreads();
@@ -296,21 +320,31 @@ static int launch_decode(const void* q, long q_stride, const void* kc, const voi
                          cudaStream_t stream) {
     const int G = nq / nkv, NH = NT * 8;
     const size_t loop_bytes = (size_t)AD_WARPS * (16 * NH + NH + 16) * 4;
-    const size_t comb_bytes = ((size_t)2 * AD_WARPS * NH + (size_t)AD_WARPS * G * hd) * 4;
+    const size_t comb_bytes = (size_t)2 * AD_WARPS * NH * 4;
     const size_t merge_bytes = ((size_t)2 * max_splits * NH + NH) * 4;
     size_t smem = loop_bytes > comb_bytes ? loop_bytes : comb_bytes;
     if (merge_bytes > smem) smem = merge_bytes;
+    const int misc_bytes = (int)((smem + 127) & ~(size_t)127);           // per-warp scratch, combine and merge areas
+    const int CH = hd / 8;
+    const int k_stride = (CH % 8) == 0 ? hd * 2 : (CH + ((4 - CH % 8) + 8) % 8) * 16;
+    size_t kv_bytes = (size_t)AD_CHUNK * k_stride + (size_t)AD_CHUNK * (hd * 2 + 16);      // K and V of the chunk
+    const size_t wa_bytes = (size_t)AD_WARPS * G * hd * 4;                                 // the warps' sums reuse that space
+    if (wa_bytes > kv_bytes) kv_bytes = wa_bytes;
+    smem = (size_t)misc_bytes + kv_bytes;
     if (smem > 200 * 1024) return AIEN_E_SHAPE;
     auto kern = paged_decode_attention_kernel<HS, NT>;
-    if (smem > 48 * 1024) {
+    static size_t configured = 0;
+    if (smem > 48 * 1024 && smem > configured) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return AIEN_E_STATE;
+        configured = smem;
     }
     dim3 grid(max_splits, nkv, T);
     // A plain launch: measured, this kernel loses when its CTAs become resident early (they wait
     // on the kernel ahead while holding the slots its own tail needs).
     kern<<<grid, AD_WARPS * 32, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc,
                  (const __nv_bfloat16*)vc, bt, max_blocks, seq_of_token, positions,
-                 part_out, part_ml, counters, (__nv_bfloat16*)out, out_stride, nq, nkv, hd, page_size, window, scale, max_splits);
+                 part_out, part_ml, counters, (__nv_bfloat16*)out, out_stride, nq, nkv, hd, page_size, window, scale, max_splits,
+                 misc_bytes);
     return launch_status();
 }
 
