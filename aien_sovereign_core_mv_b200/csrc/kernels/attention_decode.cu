@@ -5,14 +5,16 @@
 // A chunk is the keys [c*128, c*128+128) of the request, so which keys are summed together is
 // fixed by their positions and never by the batch or the grid.  A CTA first requests its whole
 // chunk of K and of V with cp.async (64 KB in flight per CTA at head size 128, three CTAs per SM),
-// then each of the eight warps takes one group of 16 keys.  Scores for a group come from
-// mma.sync.m16n8k16 with the 16 keys as rows and the (up to 16) query heads that share the kv
-// head as columns; the fragments are 16-byte reads of the K rows (the contraction index is
-// permuted the same way for q and K, see gemv.cu).  Softmax is float32; the weighted sum over V
-// is plain FMAs with each lane owning two adjacent dims per 64.
-// The warps are combined in warp order, the CTA's partial result (unnormalised sum, max,
-// denominator) goes to scratch, and a ticket counter per (token, kv head) tells the last CTA to
-// combine the chunks in chunk order, whichever CTA that is, and to put the counter back to zero.
+// then works in three phases.  Scores: each of the eight warps takes 16 keys;
+// mma.sync.m16n8k16 with the keys as rows and the (up to 16) query heads that share the kv head as
+// columns, fragments from 16-byte reads of the K rows (the contraction index is permuted the same
+// way for q and K, see gemv.cu); the scores go to shared memory.  Softmax: one warp per head takes
+// maximum, probabilities and denominator over the chunk's keys, float32.  Weighted sum: each warp
+// owns 16 output dims and runs V^T . P over all keys of the chunk on the tensor cores (V^T
+// fragments by transposing ldmatrix), so nothing is summed across warps.  The CTA's partial result
+// (unnormalised sum, max, denominator) goes to scratch, and a ticket counter per (token, kv head)
+// tells the last CTA to combine the chunks in chunk order, whichever CTA that is, and to put the
+// counter back to zero.
 // Formulas: crates/aien-inference-abi/src/backend.rs:311-379 (online softmax over pages, scale
 // 1/sqrt(head_dim)).
 //
@@ -105,8 +107,12 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
 
-    float* Ps = smem + warp * (16 * NH + NH + 16);       // [16 keys][NH heads], then corr[NH]
-    float* Cs = Ps + 16 * NH;
+    // shared scratch (floats): scores [AD_CHUNK][NH], then per head max and denominator [2][NH],
+    // then the probabilities as bfloat16 [NH][AD_CHUNK]
+    float* Sc = smem;
+    float* Hm = Sc + AD_CHUNK * NH;
+    float* Hl = Hm + NH;
+    __nv_bfloat16* Pt = reinterpret_cast<__nv_bfloat16*>(Hl + NH);
 
     // query fragments: head (nt*8 + g), dims ds*32 + c*8 .. +8
     uint4 qf[NT][HS];
@@ -118,24 +124,14 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
             qf[nt][ds] = (h < G && d < hd) ? ad_ldg16(q + (size_t)t * q_stride + (size_t)(kvh * G + h) * hd + d)
                                            : make_uint4(0u, 0u, 0u, 0u);
         }
-    float m_run[NT][2], l_run[NT][2];
-    float oacc[2 * HS][NT][4];                      // out^T tiles: 16 dims x 8 heads each
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) { m_run[nt][0] = m_run[nt][1] = -INFINITY; l_run[nt][0] = l_run[nt][1] = 0.f; }
-#pragma unroll
-    for (int mt = 0; mt < 2 * HS; ++mt)
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) oacc[mt][nt][0] = oacc[mt][nt][1] = oacc[mt][nt][2] = oacc[mt][nt][3] = 0.f;
-    __nv_bfloat16* Pt = reinterpret_cast<__nv_bfloat16*>(Ps);   // this warp's probabilities, [head][16 keys], bfloat16
 
     asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncthreads();                                         // K of the chunk is in shared memory
-    const int base = chunk_base + warp * 16;                 // AD_CHUNK == 16 * AD_WARPS: one group of 16 keys per warp
-    const bool warp_has_keys = base <= hi && base + 15 >= lo;
-    const int kj0 = base + g, kj1 = kj0 + 8;
-    const bool ok0 = kj0 >= lo && kj0 <= hi && s_slot[warp * 16 + g] >= 0;
-    const bool ok1 = kj1 >= lo && kj1 <= hi && s_slot[warp * 16 + g + 8] >= 0;
-    if (warp_has_keys) {
+    // ---- phase 1: scores of this warp's 16 keys for every head, to shared memory
+    {
+        const int kj0 = chunk_base + warp * 16 + g, kj1 = kj0 + 8;
+        const bool ok0 = kj0 >= lo && kj0 <= hi && s_slot[warp * 16 + g] >= 0;
+        const bool ok1 = kj1 >= lo && kj1 <= hi && s_slot[warp * 16 + g + 8] >= 0;
         float S[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) S[nt][0] = S[nt][1] = S[nt][2] = S[nt][3] = 0.f;
@@ -158,109 +154,74 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                const float s0 = ok0 ? S[nt][e] * scale : -INFINITY;
-                const float s1 = ok1 ? S[nt][2 + e] * scale : -INFINITY;
-                float mx = fmaxf(s0, s1);
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-                float p0 = 0.f, p1 = 0.f;
-                if (mx != -INFINITY) {
-                    p0 = ok0 ? expf(s0 - mx) : 0.f;
-                    p1 = ok1 ? expf(s1 - mx) : 0.f;
-                }
-                float sum = p0 + p1;
-                sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-                sum += __shfl_xor_sync(0xffffffffu, sum, 8);
-                sum += __shfl_xor_sync(0xffffffffu, sum, 16);
-                l_run[nt][e] = sum;
-                m_run[nt][e] = mx;
                 const int h = nt * 8 + 2 * c + e;
-                Pt[h * 16 + g] = __float2bfloat16_rn(p0);
-                Pt[h * 16 + g + 8] = __float2bfloat16_rn(p1);
+                Sc[(warp * 16 + g) * NH + h] = ok0 ? S[nt][e] * scale : -INFINITY;
+                Sc[(warp * 16 + g + 8) * NH + h] = ok1 ? S[nt][2 + e] * scale : -INFINITY;
             }
+    }
+    __syncthreads();
+    // ---- phase 2: per head, maximum, probabilities and denominator over the chunk (keys in order)
+    for (int h = warp; h < NH; h += AD_WARPS) {
+        float sv[AD_CHUNK / 32];
+        float mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < AD_CHUNK / 32; ++i) { sv[i] = Sc[(i * 32 + lane) * NH + h]; mx = fmaxf(mx, sv[i]); }
+        mx = warp_max(mx);
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < AD_CHUNK / 32; ++i) {
+            const float pv = (mx == -INFINITY || sv[i] == -INFINITY) ? 0.f : expf(sv[i] - mx);
+            sum += pv;
+            Pt[h * AD_CHUNK + i * 32 + lane] = __float2bfloat16_rn(pv);
+        }
+        sum = warp_sum(sum);
+        if (lane == 0) { Hm[h] = mx; Hl[h] = sum; }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();                                         // V of the chunk is in shared memory; P is visible
-    if (warp_has_keys) {
-        // out^T[dims, heads] += V^T[dims, 16 keys] . P[16 keys, heads]: V^T fragments by transposing
-        // ldmatrix reads of the V rows, P fragments from this warp's probabilities
-        uint32_t pb[NT][2];
+    // ---- phase 3: out^T[dims, heads] = V^T[dims, keys] . P[keys, heads]; a warp owns 16 dims at a time, so
+    // no sum over warps is needed.  V^T fragments by transposing ldmatrix reads of the V rows.
+    const int s_lo = first / AD_CHUNK, s_hi = pos / AD_CHUNK;
+    for (int mt = warp; mt * 16 < hd; mt += AD_WARPS) {
+        float oacc[NT][4];
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            const uint32_t* prow = reinterpret_cast<const uint32_t*>(Pt + (nt * 8 + g) * 16);
-            pb[nt][0] = prow[c];            // keys 2c, 2c+1 of head nt*8+g
-            pb[nt][1] = prow[c + 4];        // keys 2c+8, 2c+9
-        }
-        const uint32_t vrow = V_u + (warp * 16 + (lane & 7) + ((lane >> 4) << 3)) * v_stride + ((lane >> 3) & 1) * 16;
+        for (int nt = 0; nt < NT; ++nt) oacc[nt][0] = oacc[nt][1] = oacc[nt][2] = oacc[nt][3] = 0.f;
+        const uint32_t vbase = V_u + ((lane & 7) + ((lane >> 4) << 3)) * v_stride + ((lane >> 3) & 1) * 16 + mt * 32;
 #pragma unroll
-        for (int mt = 0; mt < 2 * HS; ++mt) {
-            if (mt * 16 < hd) {
-                uint32_t a0, a1, a2, a3;
-                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(vrow + mt * 32));
+        for (int ks = 0; ks < AD_CHUNK / 16; ++ks) {
+            uint32_t a0, a1, a2, a3;
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(vbase + ks * 16 * v_stride));
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) ad_mma(oacc[mt][nt], a0, a1, a2, a3, pb[nt][0], pb[nt][1]);
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint32_t* prow = reinterpret_cast<const uint32_t*>(Pt + (nt * 8 + g) * AD_CHUNK + ks * 16);
+                ad_mma(oacc[nt], a0, a1, a2, a3, prow[c], prow[c + 4]);
             }
         }
-    }
-
-    // ---- combine the warps in warp order
-    __syncthreads();
-    float* Wm = smem;                                  // [AD_WARPS][NH] max            (over the per-warp scratch)
-    float* Wl = Wm + AD_WARPS * NH;                    // [AD_WARPS][NH] denominator
-    float* Wa = smem + misc_bytes / 4;                 // [AD_WARPS][G][hd] sums        (over K and V, no longer needed)
-    // every lane with g == 0 holds m/l of heads 2c, 2c+1 of each tile
-    if (g == 0) {
+        // oacc[nt]: dims 16mt+g (regs 0,1) and 16mt+g+8 (regs 2,3), heads nt*8+2c and +1
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                Wm[warp * NH + nt * 8 + 2 * c + e] = m_run[nt][e];
-                Wl[warp * NH + nt * 8 + 2 * c + e] = l_run[nt][e];
+                const int h = nt * 8 + 2 * c + e;
+                if (h < G) {
+                    const size_t row = ((size_t)t * nq + kvh * G + h) * max_splits + split;
+                    part_out[row * hd + mt * 16 + g] = oacc[nt][e];
+                    part_out[row * hd + mt * 16 + g + 8] = oacc[nt][2 + e];
+                }
             }
     }
-    // oacc[mt][nt]: dims 16mt+g (regs 0,1) and 16mt+g+8 (regs 2,3), heads nt*8+2c and +1
-#pragma unroll
-    for (int mt = 0; mt < 2 * HS; ++mt) {
-        if (mt * 16 < hd) {
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int h = nt * 8 + 2 * c + e;
-                    if (h < G) {
-                        Wa[((size_t)warp * G + h) * hd + mt * 16 + g] = oacc[mt][nt][e];
-                        Wa[((size_t)warp * G + h) * hd + mt * 16 + g + 8] = oacc[mt][nt][2 + e];
-                    }
-                }
-        }
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < G * hd; idx += AD_WARPS * 32) {
-        const int h = idx / hd, d = idx - h * hd;
-        float M = -INFINITY;
-        for (int w = 0; w < AD_WARPS; ++w) M = fmaxf(M, Wm[w * NH + h]);
-        float o = 0.f, L = 0.f;
-        for (int w = 0; w < AD_WARPS; ++w) {
-            const float mw = Wm[w * NH + h];
-            if (mw == -INFINITY) continue;
-            const float f = expf(mw - M);
-            o += Wa[((size_t)w * G + h) * hd + d] * f;
-            L += Wl[w * NH + h] * f;
-        }
-        const int head = kvh * G + h;
-        const size_t row = ((size_t)t * nq + head) * max_splits + split;
-        part_out[row * hd + d] = o;
-        if (d == 0) { part_ml[row * 2] = M; part_ml[row * 2 + 1] = L; }
+    if (tid < G) {
+        const size_t row = ((size_t)t * nq + kvh * G + tid) * max_splits + split;
+        part_ml[row * 2] = Hm[tid];
+        part_ml[row * 2 + 1] = Hl[tid];
     }
 
     // ---- the last CTA of this (token, kv head) merges the chunks in chunk order
     __shared__ int is_last;
-    __threadfence();
-    __syncthreads();
-    const int s_lo = first / AD_CHUNK, s_hi = pos / AD_CHUNK;
+    __syncthreads();                                         // every thread's partial results are written
     if (threadIdx.x == 0) {
+        __threadfence();                                     // ... and ordered before the ticket, device-wide
         const int ticket = atomicAdd(&counters[(size_t)t * nkv + kvh], 1);
         is_last = ticket == (s_hi - s_lo);
         if (is_last) counters[(size_t)t * nkv + kvh] = 0;        // ready for the next launch
@@ -319,17 +280,15 @@ static int launch_decode(const void* q, long q_stride, const void* kc, const voi
                          int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T,
                          cudaStream_t stream) {
     const int G = nq / nkv, NH = NT * 8;
-    const size_t loop_bytes = (size_t)AD_WARPS * (16 * NH + NH + 16) * 4;
-    const size_t comb_bytes = (size_t)2 * AD_WARPS * NH * 4;
+    const size_t loop_bytes = ((size_t)AD_CHUNK * NH + 2 * NH) * 4 + (size_t)NH * AD_CHUNK * 2;   // scores, max/denominator, probabilities
+    const size_t comb_bytes = 0;
     const size_t merge_bytes = ((size_t)2 * max_splits * NH + NH) * 4;
     size_t smem = loop_bytes > comb_bytes ? loop_bytes : comb_bytes;
     if (merge_bytes > smem) smem = merge_bytes;
     const int misc_bytes = (int)((smem + 127) & ~(size_t)127);           // per-warp scratch, combine and merge areas
     const int CH = hd / 8;
     const int k_stride = (CH % 8) == 0 ? hd * 2 : (CH + ((4 - CH % 8) + 8) % 8) * 16;
-    size_t kv_bytes = (size_t)AD_CHUNK * k_stride + (size_t)AD_CHUNK * (hd * 2 + 16);      // K and V of the chunk
-    const size_t wa_bytes = (size_t)AD_WARPS * G * hd * 4;                                 // the warps' sums reuse that space
-    if (wa_bytes > kv_bytes) kv_bytes = wa_bytes;
+    const size_t kv_bytes = (size_t)AD_CHUNK * k_stride + (size_t)AD_CHUNK * (hd * 2 + 16);   // K and V of the chunk
     smem = (size_t)misc_bytes + kv_bytes;
     if (smem > 200 * 1024) return AIEN_E_SHAPE;
     auto kern = paged_decode_attention_kernel<HS, NT>;
