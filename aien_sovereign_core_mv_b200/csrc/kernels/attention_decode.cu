@@ -50,7 +50,7 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
                               const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                               const int* __restrict__ block_table, int max_blocks,
                               const int* __restrict__ seq_of_token, const int* __restrict__ positions,
-                              float* __restrict__ part_out, float* __restrict__ part_ml, int* __restrict__ counters,
+                              const int* __restrict__ token_list, float* __restrict__ part_out, float* __restrict__ part_ml, int* __restrict__ counters,
                               __nv_bfloat16* __restrict__ out, long out_stride,
                               int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int misc_bytes) {
     constexpr int DCH = (HS + 1) / 2;            // 64-dim chunks of the output
@@ -61,7 +61,10 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
     griddep_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, c = lane & 3;
-    const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
+    // blockIdx.z counts the tokens this launch serves: all tokens of the step, or those named by
+    // token_list (the single-token requests of a mixed step).  Scratch is indexed by blockIdx.z.
+    const int split = blockIdx.x, kvh = blockIdx.y, zt = blockIdx.z;
+    const int t = token_list ? token_list[zt] : zt;
     const int G = nq / nkv;
     const int pos = positions[t];
     // In a decode-only step token t is request t (seq_of_token may be null): the table row does not
@@ -205,14 +208,14 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
             for (int e = 0; e < 2; ++e) {
                 const int h = nt * 8 + 2 * c + e;
                 if (h < G) {
-                    const size_t row = ((size_t)t * nq + kvh * G + h) * max_splits + split;
+                    const size_t row = ((size_t)zt * nq + kvh * G + h) * max_splits + split;
                     part_out[row * hd + mt * 16 + g] = oacc[nt][e];
                     part_out[row * hd + mt * 16 + g + 8] = oacc[nt][2 + e];
                 }
             }
     }
     if (tid < G) {
-        const size_t row = ((size_t)t * nq + kvh * G + tid) * max_splits + split;
+        const size_t row = ((size_t)zt * nq + kvh * G + tid) * max_splits + split;
         part_ml[row * 2] = Hm[tid];
         part_ml[row * 2 + 1] = Hl[tid];
     }
@@ -222,9 +225,9 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
     __syncthreads();                                         // every thread's partial results are written
     if (threadIdx.x == 0) {
         __threadfence();                                     // ... and ordered before the ticket, device-wide
-        const int ticket = atomicAdd(&counters[(size_t)t * nkv + kvh], 1);
+        const int ticket = atomicAdd(&counters[(size_t)zt * nkv + kvh], 1);
         is_last = ticket == (s_hi - s_lo);
-        if (is_last) counters[(size_t)t * nkv + kvh] = 0;        // ready for the next launch
+        if (is_last) counters[(size_t)zt * nkv + kvh] = 0;        // ready for the next launch
     }
     __syncthreads();
     if (!is_last) return;
@@ -236,7 +239,7 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
     float* Fi = Fl + (size_t)max_splits * NH;            // [NH]: 1 / total denominator
     for (int i = threadIdx.x; i < nsp * G; i += AD_WARPS * 32) {
         const int sp = i / G, h = i - sp * G;
-        const size_t row = ((size_t)t * nq + kvh * G + h) * max_splits + s_lo + sp;
+        const size_t row = ((size_t)zt * nq + kvh * G + h) * max_splits + s_lo + sp;
         Fm[sp * NH + h] = __ldcg(part_ml + row * 2);
         Fl[sp * NH + h] = __ldcg(part_ml + row * 2 + 1);
     }
@@ -257,7 +260,7 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
     __syncthreads();
     for (int idx = threadIdx.x; idx < G * hd; idx += AD_WARPS * 32) {
         const int h = idx / hd, d = idx - h * hd;
-        const float* src = part_out + (((size_t)t * nq + kvh * G + h) * max_splits + s_lo) * hd + d;
+        const float* src = part_out + (((size_t)zt * nq + kvh * G + h) * max_splits + s_lo) * hd + d;
         float o = 0.f;
         int sp = 0;
         for (; sp + 4 <= nsp; sp += 4) {
@@ -275,7 +278,7 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
 
 template <int HS, int NT>
 static int launch_decode(const void* q, long q_stride, const void* kc, const void* vc, const int* bt, int max_blocks,
-                         const int* seq_of_token, const int* positions, float* part_out, float* part_ml, int* counters,
+                         const int* seq_of_token, const int* positions, const int* token_list, float* part_out, float* part_ml, int* counters,
                          void* out, long out_stride,
                          int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T,
                          cudaStream_t stream) {
@@ -301,7 +304,7 @@ static int launch_decode(const void* q, long q_stride, const void* kc, const voi
     // A plain launch: measured, this kernel loses when its CTAs become resident early (they wait
     // on the kernel ahead while holding the slots its own tail needs).
     kern<<<grid, AD_WARPS * 32, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc,
-                 (const __nv_bfloat16*)vc, bt, max_blocks, seq_of_token, positions,
+                 (const __nv_bfloat16*)vc, bt, max_blocks, seq_of_token, positions, token_list,
                  part_out, part_ml, counters, (__nv_bfloat16*)out, out_stride, nq, nkv, hd, page_size, window, scale, max_splits,
                  misc_bytes);
     return launch_status();
@@ -311,13 +314,14 @@ static int launch_decode(const void* q, long q_stride, const void* kc, const voi
 
 using namespace aien;
 
+// T: tokens served (all of the step, or the entries of token_list).
 // Scratch: part_out [T * nq * max_splits * hd] floats, part_ml [T * nq * max_splits * 2] floats.
 // counters: T * nkv ints that are zero on entry and are left zero.
 // max_splits must cover the longest context in the step: ceil((max position + 1) / 128).
 AIEN_API int aien_paged_attention_decode(
     const void* q, long q_stride, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
-    const int* seq_of_token, const int* positions, void* out, long out_stride, float* part_out, float* part_ml,
-    int* counters, int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T, cudaStream_t stream) {
+    const int* seq_of_token, const int* positions, const int* token_list, void* out, long out_stride, float* part_out,
+    float* part_ml, int* counters, int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (hd <= 0 || hd > 256 || (hd & 15) || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || max_splits <= 0) return AIEN_E_SHAPE;
     const int G = nq / nkv;
@@ -328,7 +332,7 @@ AIEN_API int aien_paged_attention_decode(
 #define AD_CASE(hs, nt)                                                                                              \
     if (HS == hs && NT == nt)                                                                                        \
         rc = launch_decode<hs, nt>(q, q_stride, k_cache, v_cache, block_table, max_blocks, seq_of_token, positions,  \
-                                   part_out, part_ml, counters, out, out_stride, nq, nkv, hd, page_size, window, scale,        \
+                                   token_list, part_out, part_ml, counters, out, out_stride, nq, nkv, hd, page_size, window, scale,        \
                                    max_splits, T, stream);
     AD_CASE(1, 1) AD_CASE(2, 1) AD_CASE(3, 1) AD_CASE(4, 1) AD_CASE(5, 1) AD_CASE(6, 1) AD_CASE(7, 1) AD_CASE(8, 1)
     AD_CASE(1, 2) AD_CASE(2, 2) AD_CASE(3, 2) AD_CASE(4, 2) AD_CASE(5, 2) AD_CASE(6, 2) AD_CASE(7, 2) AD_CASE(8, 2)

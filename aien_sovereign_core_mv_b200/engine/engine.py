@@ -137,6 +137,8 @@ class Engine:
         o += _align4(n_tiles)
         off["tile_q0"] = o
         o += _align4(n_tiles)
+        off["single_tokens"] = o                      # token indices of single-token entries in a mixed step
+        o += _align4(max(S, 1))
         return off, o
 
     # ------------------------------------------------------------------ requests
@@ -242,9 +244,16 @@ class Engine:
             m[off["want_rows"]:off["want_rows"] + R] = want_rows
         max_ctx = self.cache.fill_meta(ids, counts, m, off["positions"], off["seq_of_token"], off["q_start"], off["ctx_len"], off["groups"])
         decode_only = T == S
-        n_tiles = 0
+        n_tiles, n_single = 0, 0
         if not decode_only:
+            t_at = 0
             for i, c in enumerate(counts):
+                if c == 1:
+                    m[off["single_tokens"] + n_single] = t_at
+                    n_single += 1
+                    t_at += 1
+                    continue
+                t_at += c
                 k = (c + K.PREFILL_TILE - 1) // K.PREFILL_TILE
                 m[off["tile_seq"] + n_tiles:off["tile_seq"] + n_tiles + k] = i
                 m[off["tile_q0"] + n_tiles:off["tile_q0"] + n_tiles + k] = np.arange(k, dtype=np.int32) * K.PREFILL_TILE
@@ -261,6 +270,7 @@ class Engine:
         ctx = self._context(off, T, S, max(counts), max_ctx, decode_only)
         d = self.meta_dev
         ctx.prefill_tiles = (d[off["tile_seq"]:off["tile_seq"] + max(n_tiles, 1)], d[off["tile_q0"]:off["tile_q0"] + max(n_tiles, 1)], n_tiles)
+        ctx.single_tokens = (d[off["single_tokens"]:off["single_tokens"] + max(n_single, 1)], n_single)
         if logits_out is None:
             logits_out = torch.empty((R, self.vocab_size), dtype=torch.float32, device=self.device)
         d = self.meta_dev

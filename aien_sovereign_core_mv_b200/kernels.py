@@ -61,7 +61,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_gemm_tc": [P, L, P, L, P, I, L, I, I, I, I, P],
         "aien_gemm_tc_error": [],
         "aien_paged_attention_prefill": [P, L, P, P, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P],
-        "aien_paged_attention_decode": [P, L, P, P, P, I, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, P],
+        "aien_paged_attention_decode": [P, L, P, P, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, P],
     }
     for name, args in sigs.items():
         fn = getattr(l, name)
@@ -374,12 +374,13 @@ _ticket_counters: Optional[torch.Tensor] = None
 
 def paged_attention_decode(q, k_cache, v_cache, block_table, max_blocks, seq_of_token, positions, out,
                            part_out, part_ml, num_q_heads, num_kv_heads, head_dim, page_size, window, scale,
-                           max_splits) -> None:
+                           max_splits, token_list=None, num_tokens=None) -> None:
     """Split-key decode attention; the CTA that finishes last merges the chunks.  The ticket
     counters are one small device buffer that every launch finds zero and leaves zero."""
     global _ticket_counters
     _dev(q, k_cache, v_cache, block_table, seq_of_token, positions, out, part_out, part_ml)
-    T = q.shape[0]                  # seq_of_token None: token t belongs to row t of the block table
+    # seq_of_token None: token t belongs to row t of the block table.  token_list: serve only these tokens.
+    T = q.shape[0] if token_list is None else int(num_tokens)
     if _ticket_counters is None:
         _ticket_counters = torch.zeros(1 << 16, dtype=torch.int32, device=q.device)
     assert T * num_kv_heads <= _ticket_counters.numel()
@@ -389,7 +390,7 @@ def paged_attention_decode(q, k_cache, v_cache, block_table, max_blocks, seq_of_
     assert part_ml.dtype == torch.float32 and part_ml.numel() >= T * num_q_heads * max_splits * 2
     _check(lib().aien_paged_attention_decode(
         _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), max_blocks, _p(seq_of_token), _p(positions),
-        _p(out), out.stride(0), _p(part_out), _p(part_ml), _p(_ticket_counters), num_q_heads, num_kv_heads, head_dim,
+        _p(token_list), _p(out), out.stride(0), _p(part_out), _p(part_ml), _p(_ticket_counters), num_q_heads, num_kv_heads, head_dim,
         page_size, window, float(scale), max_splits, T, _stream()), "paged_attention_decode")
 
 
@@ -417,11 +418,22 @@ def paged_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
         paged_attention_decode(q, k2, v2, group.block_table, group.max_blocks, None, ctx.positions, out,
                                part_out, part_ml, num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale, splits)
         return
-    if (not ctx.decode_only and _FORCE_ATTN != "generic" and ctx.prefill_tiles is not None and ctx.prefill_tiles[2] > 0
-            and prefill_attention_supports(q, k2, out, head_dim)):
+    if (not ctx.decode_only and _FORCE_ATTN != "generic" and ctx.prefill_tiles is not None
+            and prefill_attention_supports(q, k2, out, head_dim)
+            and decode_attention_supports(q, k2, num_q_heads, num_kv_heads, head_dim)):
+        # a mixed step: portions go through the tiled kernel, single tokens through the split-key kernel
         tile_seq, tile_q0, n = ctx.prefill_tiles
-        paged_attention_prefill(q, k2, v2, group.block_table, group.max_blocks, ctx.q_start, ctx.ctx_len, tile_seq, tile_q0, n,
-                                out, num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale)
+        if n > 0:
+            paged_attention_prefill(q, k2, v2, group.block_table, group.max_blocks, ctx.q_start, ctx.ctx_len, tile_seq, tile_q0, n,
+                                    out, num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale)
+        tokens, nd = ctx.single_tokens if ctx.single_tokens is not None else (None, 0)
+        if nd > 0:
+            splits = max(1, (ctx.max_ctx_len + DECODE_CHUNK - 1) // DECODE_CHUNK)
+            part_out = ctx.workspace.take((nd * num_q_heads * splits * head_dim,), torch.float32)
+            part_ml = ctx.workspace.take((nd * num_q_heads * splits * 2,), torch.float32)
+            paged_attention_decode(q, k2, v2, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, out,
+                                   part_out, part_ml, num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale,
+                                   splits, token_list=tokens, num_tokens=nd)
         return
     paged_attention_generic(q, k2, v2, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, out,
                             num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale)

@@ -84,7 +84,8 @@ class StepContext:
     max_q_len: int = 0                     # longest portion in the step (host knowledge)
     max_ctx_len: int = 0
     decode_only: bool = False
-    prefill_tiles: Optional[Tuple[torch.Tensor, torch.Tensor, int]] = None   # (tile_seq, tile_q0, count) of 64-token query tiles
+    prefill_tiles: Optional[Tuple[torch.Tensor, torch.Tensor, int]] = None   # (tile_seq, tile_q0, count): query tiles of entries that bring several tokens
+    single_tokens: Optional[Tuple[torch.Tensor, int]] = None                 # (token indices, count) of entries that bring one token, in a mixed step
     shared: Dict[Any, Any] = field(default_factory=dict)   # per-step memo (rotary tables ...)
 
 

@@ -334,6 +334,14 @@ def test_paged_attention_decode(K, nq, nkv, hd, page, window):
     K.paged_attention_generic(q, kc, vc, bt, mb, torch.tensor(seq_of, dtype=torch.int32).cuda(),
                               torch.tensor(positions, dtype=torch.int32).cuda(), ref, nq, nkv, hd, page, window, scale)
     H.assert_close(out.float().cpu().numpy(), ref.float().cpu().numpy(), 1e-2, "decode vs generic kernel")
+    # a subset of the tokens, named by a list (the single-token entries of a mixed step)
+    some = [4, 0, 2]
+    sub = torch.full_like(out, 3.0)
+    K.paged_attention_decode(q, kc, vc, bt, mb, torch.tensor(seq_of, dtype=torch.int32).cuda(),
+                             torch.tensor(positions, dtype=torch.int32).cuda(), sub, part_out, part_ml,
+                             nq, nkv, hd, page, window, scale, splits,
+                             token_list=torch.tensor(some, dtype=torch.int32).cuda(), num_tokens=len(some))
+    assert torch.equal(sub[some], out[some]) and (sub[[1, 3, 5]] == 3.0).all()
 
 
 def test_decode_attention_one_far_key_decides(K):
