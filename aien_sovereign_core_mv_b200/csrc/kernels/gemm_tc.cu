@@ -60,7 +60,7 @@ __device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr) {
 template <int EPI, typename TC>
 __global__ void __launch_bounds__(192)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-               TC* __restrict__ out, long ldc, int M, int N, int K) {
+               TC* __restrict__ out, long ldc, size_t part_stride, int kb_per_split, int M, int N, int K) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sA = base, sB = base + TC_STAGES * TC_STAGE_A;
@@ -72,7 +72,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * TC_BN;
-    const int num_kb = (K + TC_BK - 1) / TC_BK;
+    // blockIdx.z: a range of k-blocks (split-K for small M); the partial product goes to
+    // out + z * part_stride and the consumer adds the ranges in order
+    const int kb_first = blockIdx.z * kb_per_split;
+    const int num_kb = min((K + TC_BK - 1) / TC_BK - kb_first, kb_per_split);
+    out += (size_t)blockIdx.z * part_stride;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
@@ -95,8 +99,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const uint32_t round = kb / TC_STAGES;
                 if (kb >= TC_STAGES) mbar_wait(empty0 + 8 * s, (round - 1) & 1, 1);
                 mbar_expect_tx(full0 + 8 * s, TC_STAGE_A + TC_STAGE_B);
-                tma_load_2d(sA + s * TC_STAGE_A, &map_a, full0 + 8 * s, kb * TC_BK, m0);
-                tma_load_2d(sB + s * TC_STAGE_B, &map_w, full0 + 8 * s, kb * TC_BK, n0);
+                tma_load_2d(sA + s * TC_STAGE_A, &map_a, full0 + 8 * s, (kb_first + kb) * TC_BK, m0);
+                tma_load_2d(sB + s * TC_STAGE_B, &map_w, full0 + 8 * s, (kb_first + kb) * TC_BK, n0);
             }
         }
     } else if (warp == 1) {
@@ -195,15 +199,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 template <int EPI, typename TC>
-static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* out, long ldc, int M, int N, int K, cudaStream_t stream) {
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* out, long ldc, int splits, size_t part_stride,
+                     int M, int N, int K, cudaStream_t stream) {
     auto kern = gemm_tc_kernel<EPI, TC>;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM) != cudaSuccess) return AIEN_E_STATE;
         configured = true;
     }
-    dim3 grid((M + TC_BM - 1) / TC_BM, (N + TC_BN - 1) / TC_BN);
-    kern<<<grid, 192, TC_SMEM, stream>>>(ma, mw, (TC*)out, ldc, M, N, K);
+    const int total_kb = (K + TC_BK - 1) / TC_BK;
+    const int kb_per_split = (total_kb + splits - 1) / splits;
+    dim3 grid((M + TC_BM - 1) / TC_BM, (N + TC_BN - 1) / TC_BN, (total_kb + kb_per_split - 1) / kb_per_split);
+    kern<<<grid, 192, TC_SMEM, stream>>>(ma, mw, (TC*)out, ldc, part_stride, kb_per_split, M, N, K);
     return launch_status();
 }
 
@@ -211,11 +218,22 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* out, lo
 
 using namespace aien;
 
-// epilogue 0: out[M,N]; 1: out[M,N/2] = silu(gate)*up with gate/up rows of W interleaved in runs of 8
+// epilogue 0: out[M,N]; 1: out[M,N/2] = silu(gate)*up with gate/up rows of W interleaved in runs of 8.
+// splits > 1 (epilogue 0, float32 out): K is cut into ranges of whole 64-value blocks and out is
+// [ranges][M][ldc] partial products, part_stride elements apart; aien_gemm_tc_ranges says how many
+// ranges a given (K, splits) really makes.
+AIEN_API int aien_gemm_tc_ranges(int K, int splits) {
+    const int total_kb = (K + TC_BK - 1) / TC_BK;
+    if (splits < 1) splits = 1;
+    const int kb_per_split = (total_kb + splits - 1) / splits;
+    return (total_kb + kb_per_split - 1) / kb_per_split;
+}
+
 AIEN_API int aien_gemm_tc(const void* A, long lda, const void* W, long ldw, void* out, int c_dt, long ldc,
-                          int M, int N, int K, int epilogue, cudaStream_t stream) {
+                          int M, int N, int K, int epilogue, int splits, size_t part_stride, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || (K & 7)) return AIEN_E_SHAPE;
+    if (K <= 0 || (K & 7) || splits < 1 || splits > 64) return AIEN_E_SHAPE;
+    if (splits > 1 && (epilogue != 0 || c_dt != AIEN_DT_F32)) return AIEN_E_SHAPE;
     if ((lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return AIEN_E_ALIGN;
     if (epilogue == 1 && (N & 15)) return AIEN_E_SHAPE;
     if ((M + TC_BM - 1) / TC_BM > 2147483647 / 1 || (N + TC_BN - 1) / TC_BN > 65535) return AIEN_E_SHAPE;
@@ -223,13 +241,13 @@ AIEN_API int aien_gemm_tc(const void* A, long lda, const void* W, long ldw, void
     if (!make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TC_BK, TC_BM) || !make_map(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, TC_BK, TC_BN))
         return AIEN_E_STATE;
     if (epilogue == 0) {
-        if (c_dt == AIEN_DT_BF16) return launch_tc<0, __nv_bfloat16>(ma, mw, out, ldc, M, N, K, stream);
-        if (c_dt == AIEN_DT_F32) return launch_tc<0, float>(ma, mw, out, ldc, M, N, K, stream);
+        if (c_dt == AIEN_DT_BF16) return launch_tc<0, __nv_bfloat16>(ma, mw, out, ldc, 1, 0, M, N, K, stream);
+        if (c_dt == AIEN_DT_F32) return launch_tc<0, float>(ma, mw, out, ldc, splits, part_stride, M, N, K, stream);
         return AIEN_E_DTYPE;
     }
     if (epilogue == 1) {
-        if (c_dt == AIEN_DT_BF16) return launch_tc<1, __nv_bfloat16>(ma, mw, out, ldc, M, N, K, stream);
-        if (c_dt == AIEN_DT_F32) return launch_tc<1, float>(ma, mw, out, ldc, M, N, K, stream);
+        if (c_dt == AIEN_DT_BF16) return launch_tc<1, __nv_bfloat16>(ma, mw, out, ldc, 1, 0, M, N, K, stream);
+        if (c_dt == AIEN_DT_F32) return launch_tc<1, float>(ma, mw, out, ldc, 1, 0, M, N, K, stream);
         return AIEN_E_DTYPE;
     }
     return AIEN_E_SHAPE;

@@ -58,7 +58,8 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_gemv_bf16": [P, L, P, L, P, I, L, I, I, I, I, I, c_size_t, P],
         "aien_gemv_stream_bf16": [P, L, P, L, P, I, L, I, I, I, I, I, c_size_t, P],
         "aien_gemv_stream_error": [],
-        "aien_gemm_tc": [P, L, P, L, P, I, L, I, I, I, I, P],
+        "aien_gemm_tc": [P, L, P, L, P, I, L, I, I, I, I, I, c_size_t, P],
+        "aien_gemm_tc_ranges": [I, I],
         "aien_gemm_tc_error": [],
         "aien_paged_attention_prefill": [P, L, P, P, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P],
         "aien_paged_attention_decode": [P, L, P, P, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, P],
@@ -348,9 +349,34 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int =
     _dev(a, w, out)
     M, K_ = a.shape
     N = w.shape[0]
-    assert w.shape[1] == K_ and out.shape == (M, N if epilogue == 0 else N // 2)
-    _check(lib().aien_gemm_tc(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), dt(out), out.stride(0), M, N, K_,
-                              epilogue, _stream()), "gemm_tc")
+    splits, part_stride = 1, 0
+    if out.dim() == 3:                      # float32 partial products over ranges of K, for the consumer to add
+        assert epilogue == 0 and out.dtype == torch.float32 and out.is_contiguous() and tuple(out.shape[1:]) == (M, N)
+        assert out.shape[0] == gemm_tc_ranges(K_, out.shape[0])
+        splits, part_stride = out.shape[0], M * N
+    else:
+        assert w.shape[1] == K_ and out.shape == (M, N if epilogue == 0 else N // 2)
+    _check(lib().aien_gemm_tc(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), dt(out), out.stride(-2), M, N, K_,
+                              epilogue, splits, part_stride, _stream()), "gemm_tc")
+
+
+# Upper bound of the float32 partial products one deferred product may leave in the workspace:
+# ranges x M x N <= (296 / tiles) x (tiles x 128 x 128) elements.
+PARTIALS_MAX_BYTES = 296 * 128 * 128 * 4 + (1 << 16)
+
+
+def gemm_tc_ranges(K_: int, splits: int) -> int:
+    """How many ranges of K the tensor-core kernel makes when asked for ``splits``."""
+    return int(lib().aien_gemm_tc_ranges(int(K_), int(splits)))
+
+
+def gemm_tc_splits(M: int, N: int, K_: int) -> int:
+    """Ranges of K for a product with few rows: enough CTAs to occupy the GPU (148 SMs, two CTAs
+    each) when the tile grid alone is small.  Depends on the shapes only."""
+    tiles = ((M + 127) // 128) * ((N + 127) // 128)
+    if tiles >= 148:
+        return 1
+    return gemm_tc_ranges(K_, max(1, min(8, 296 // tiles, K_ // 512)))
 
 
 def gemm_tc_error() -> int:

@@ -66,7 +66,7 @@ class PagedAttention(Mixer):
 
     def workspace_bytes(self, lim):
         return lim.max_tokens * (2 * self.q_dim + 2 * self.kv_dim + self.q_dim + self.hidden_size) * lim.itemsize + 4096 \
-            + 8 * K.GEMV_MAX_ROWS * (self.q_dim + 2 * self.kv_dim + self.hidden_size) * 4 \
+            + 8 * K.GEMV_MAX_ROWS * (self.q_dim + 2 * self.kv_dim + self.hidden_size) * 4 + 2 * K.PARTIALS_MAX_BYTES \
             + K.attention_workspace_bytes(lim, self.num_heads, self.head_dim)
 
     # ---- one step

@@ -34,6 +34,14 @@ def linear(ctx: StepContext, a: torch.Tensor, w: torch.Tensor, out_dtype: Option
             if K.gemv_supports(a, w, parts):
                 K.gemv(a, w, parts)
                 return parts
+    if out is None and may_defer_sum and not _FORCE and M > K.GEMV_MAX_ROWS and a.dtype == torch.bfloat16 \
+            and w.dtype == torch.bfloat16:
+        splits = K.gemm_tc_splits(M, N, a.shape[1])
+        if splits > 1:
+            parts = ctx.workspace.take((splits, M, N), torch.float32)
+            if K.gemm_tc_supports(a, w, parts[0]):
+                K.gemm_tc(a, w, parts)
+                return parts
     if out is None:
         out = ctx.workspace.take((M, N), out_dtype or a.dtype)
     choice = _FORCE or _choose(a, w, out, M)

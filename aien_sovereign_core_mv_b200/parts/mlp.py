@@ -40,7 +40,7 @@ class SwiGLU(FeedForward):
 
     def workspace_bytes(self, lim):
         return lim.max_tokens * (3 * self.intermediate_size + self.hidden_size) * lim.itemsize + 4096 \
-            + 8 * K.GEMV_MAX_ROWS * self.hidden_size * 4
+            + 8 * K.GEMV_MAX_ROWS * self.hidden_size * 4 + K.PARTIALS_MAX_BYTES
 
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
         act = ctx.workspace.take((ctx.num_tokens, self.intermediate_size), ctx.dtype)

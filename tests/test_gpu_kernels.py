@@ -531,3 +531,19 @@ def test_gemv_stream_against_direct(K, M, N, K_, monkeypatch):
         ad = a.double().cpu()
         ref = pm.swiglu((ad @ wd[:, 0].reshape(I, K_).T).numpy(), (ad @ wd[:, 1].reshape(I, K_).T).numpy())
         H.assert_close(out.float().cpu().numpy(), ref, 1e-2, "stream gemv + swiglu")
+
+
+@pytest.mark.parametrize("M,N,K_,splits", [(64, 4096, 4096, 4), (17, 130, 1032, 8), (100, 256, 576, 4), (128, 384, 12288, 8)])
+def test_gemm_tensor_core_split_k(K, M, N, K_, splits):
+    g = torch.Generator().manual_seed(M + N)
+    a = torch.randn(M, K_, generator=g).to(torch.bfloat16).cuda()
+    w = torch.randn(N, K_, generator=g).to(torch.bfloat16).cuda()
+    ranges = K.gemm_tc_ranges(K_, splits)
+    assert 1 <= ranges <= splits
+    parts = torch.full((ranges, M, N), 5.0, device="cuda")
+    K.gemm_tc(a, w, parts)
+    torch.cuda.synchronize()
+    assert K.gemm_tc_error() == 0
+    want = (a.double().cpu() @ w.double().cpu().T).numpy()
+    H.assert_close(parts.sum(0).cpu().numpy(), want, 2e-5, f"tc gemm split-K {M}x{N}x{K_}/{ranges}")
+    assert K.gemm_tc_splits(2048, 4096, 4096) == 1 and K.gemm_tc_splits(64, 4096, 4096) > 1
