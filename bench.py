@@ -114,6 +114,50 @@ def model_numbers(cfg, layers_run):
                 kv_bytes_per_token=kv_bytes_per_token, Q=Q, KV=KV)
 
 
+QWEN3_4B = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=36, hidden_size=2560,
+    num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=9728, vocab_size=151936,
+    rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=40960,
+    hidden_act="silu", attention_bias=False, eos_token_id=151645,
+)
+
+
+def serving_workload() -> int:
+    """Continuous batching through the public entry point: 32 requests with uniform-random prompt
+    lengths in [64, 4096], prompts cut into portions under a 512-token budget, 256 greedy tokens
+    each (Qwen3-4B shape, random bfloat16 weights, seed 3).  Wall-clock time of the whole job."""
+    import numpy as np
+    import torch
+    from aien_sovereign_core_mv_b200 import Engine, EngineConfig
+    from aien_sovereign_core_mv_b200.engine.generate import Generator
+    from aien_sovereign_core_mv_b200.sampling import SamplingParams
+    ec = EngineConfig(dtype="bfloat16", page_size=16, max_cache_tokens=32 * 4400, max_requests=32, max_batch_tokens=1024,
+                      max_context=8192, max_batch_size=32, max_prefill_tokens=512, prefill_chunk_size=512)
+    engine = Engine.from_config(QWEN3_4B, seed=3, engine_config=ec, init_std=0.02, device_init=True)
+    rng = np.random.default_rng(3)
+    gen = Generator(engine)
+    lens = rng.integers(64, 4097, 32)
+    sp = SamplingParams(temperature=0.0, max_tokens=256, stop_token_ids=[])
+    for i, n in enumerate(lens):
+        gen.submit(100 + i, rng.integers(0, QWEN3_4B["vocab_size"], int(n)).tolist(), sp)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    done = gen.run()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    m = gen.scheduler.metrics()
+    new = sum(len(r.tokens) for r in done.values())
+    print(json.dumps({
+        "metric": "serving_generated_tokens_per_s", "value": round(new / dt, 1), "unit": "tokens/s", "n_gpus": 1,
+        "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "total_tokens_per_s": round((int(lens.sum()) + new) / dt, 1), "seconds": round(dt, 3), "steps": int(m["steps"]),
+        "preemptions": int(m["preemptions"]), "requests": len(done), "prompt_tokens": int(lens.sum()), "generated_tokens": new,
+        "config": {"model": "Qwen3-4B shape, random weights", "requests": 32, "prompt_len": "uniform 64..4096",
+                   "prefill_budget": 512, "new_tokens": 256, "context": 8192, "page_size": 16, "seed": 3},
+    }))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -125,6 +169,9 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
+                    help="decode: the headline decode-step measurement; serving: continuous batching of 32 requests "
+                         "on the Qwen3-4B shape (prompts of 64..4096 tokens, portions of 512, 256 new tokens each)")
     ap.add_argument("--fill", default="prefill", choices=["prefill", "cache"],
                     help="how requests get their prompt: real prefill, or (development only) cache pages "
                          "filled with random keys/values without running the model")
@@ -138,6 +185,8 @@ def main() -> int:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (use --gpus 1)")
         return 2
     warmup, steps = max(3, args.warmup), max(1, args.steps)
+    if args.workload == "serving":
+        return serving_workload()
 
     import numpy as np
     import torch
