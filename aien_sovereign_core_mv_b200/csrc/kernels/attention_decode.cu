@@ -43,6 +43,55 @@ __device__ __forceinline__ void ad_mma(float c[4], uint32_t a0, uint32_t a1, uin
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// When `k` is set, the kernel also does the work of the q/k kernel for its token: the per-head
+// RMSNorm of q and k, their rotation, and the write of k and v into the token's cache slot (the CTA
+// whose chunk holds the token's position does that, and uses the values directly).  The arithmetic
+// is that of qk_norm_rope_kv_write_kernel (elementwise.cu), so the cache holds the same bits.
+struct FusedQK {
+    const __nv_bfloat16* k;          // raw projections of the step's tokens; null: q is ready, cache is written
+    long k_stride;
+    const __nv_bfloat16* v;
+    long v_stride;
+    const void* q_norm_w;            // null: no norm
+    const void* k_norm_w;
+    int wdt;
+    float eps;
+    const float* cos_t;              // [T, rot/2]; null: no rotation
+    const float* sin_t;
+    int rot;
+    const int* slot_map;             // [T] cache slot of the token
+    __nv_bfloat16* k_cache_w;
+    __nv_bfloat16* v_cache_w;
+};
+
+// One warp: norm (if w) and rotate (if cos_t) the head at src into hb (float32, head_dim values).
+__device__ __forceinline__ void ad_norm_rope_head(const __nv_bfloat16* src, float* hb, int hd, const void* w, int wdt, float eps,
+                                                  const float* cos_t, const float* sin_t, int rot, int t, int lane) {
+    float ss = 0.f;
+    for (int i = lane; i < hd; i += 32) {
+        const float val = __bfloat162float(src[i]);
+        hb[i] = val;
+        ss += val * val;
+    }
+    __syncwarp();
+    if (w != nullptr) {
+        ss = warp_sum(ss);
+        const float sc = 1.0f / sqrtf(ss / (float)hd + eps);
+        for (int i = lane; i < hd; i += 32) hb[i] = hb[i] * sc * load_dyn(w, wdt, i);
+        __syncwarp();
+    }
+    if (cos_t != nullptr) {
+        const int half = rot >> 1;
+        for (int i = lane; i < half; i += 32) {
+            const float a = hb[i], b = hb[i + half];
+            const float cs = cos_t[(size_t)t * half + i], sn = sin_t[(size_t)t * half + i];
+            hb[i] = a * cs - b * sn;
+            hb[i + half] = a * sn + b * cs;
+        }
+        __syncwarp();
+    }
+}
+
 // HS = ceil(head_dim / 32) dim steps of the score product, NT = ceil(G / 8) head tiles
 template <int HS, int NT>
 __global__ void __launch_bounds__(AD_WARPS * 32)
@@ -52,7 +101,8 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
                               const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                               const int* __restrict__ token_list, float* __restrict__ part_out, float* __restrict__ part_ml, int* __restrict__ counters,
                               __nv_bfloat16* __restrict__ out, long out_stride,
-                              int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int misc_bytes) {
+                              int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int misc_bytes,
+                              FusedQK fq) {
     constexpr int DCH = (HS + 1) / 2;            // 64-dim chunks of the output
     constexpr int NH = NT * 8;
     extern __shared__ float smem[];
@@ -97,6 +147,7 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
     for (int idx = tid; idx < AD_CHUNK * CH; idx += AD_WARPS * 32) {
         const int r = idx / CH, ch = idx - r * CH;
         const int key = chunk_base + r, sl = s_slot[r];
+        if (fq.k != nullptr && key == pos) continue;         // this row is computed here, not read
         const bool valid = key >= lo && key <= hi && sl >= 0;
         const int pc = swz ? (ch ^ ((r & 1) << 2)) : ch;
         ad_cp_async16(K_u + r * k_stride + pc * 16, k_cache + ((size_t)(valid ? sl : 0) * nkv + kvh) * hd + ch * 8, valid);
@@ -105,6 +156,7 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
     for (int idx = tid; idx < AD_CHUNK * CH; idx += AD_WARPS * 32) {
         const int r = idx / CH, ch = idx - r * CH;
         const int key = chunk_base + r, sl = s_slot[r];
+        if (fq.k != nullptr && key == pos) continue;
         const bool valid = key >= lo && key <= hi && sl >= 0;
         ad_cp_async16(V_u + r * v_stride + ch * 16, v_cache + ((size_t)(valid ? sl : 0) * nkv + kvh) * hd + ch * 8, valid);
     }
@@ -116,17 +168,64 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
     float* Hm = Sc + AD_CHUNK * NH;
     float* Hl = Hm + NH;
     __nv_bfloat16* Pt = reinterpret_cast<__nv_bfloat16*>(Hl + NH);
+    float* Hb = reinterpret_cast<float*>(Pt + NH * AD_CHUNK);          // fused q/k work: [AD_WARPS][256] floats ...
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(Hb + AD_WARPS * 256);   // ... and q as bfloat16 [NH][hd]
 
     // query fragments: head (nt*8 + g), dims ds*32 + c*8 .. +8
     uint4 qf[NT][HS];
+    if (fq.k == nullptr) {
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
+        for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int ds = 0; ds < HS; ++ds) {
-            const int h = nt * 8 + g, d = ds * 32 + c * 8;
-            qf[nt][ds] = (h < G && d < hd) ? ad_ldg16(q + (size_t)t * q_stride + (size_t)(kvh * G + h) * hd + d)
-                                           : make_uint4(0u, 0u, 0u, 0u);
+            for (int ds = 0; ds < HS; ++ds) {
+                const int h = nt * 8 + g, d = ds * 32 + c * 8;
+                qf[nt][ds] = (h < G && d < hd) ? ad_ldg16(q + (size_t)t * q_stride + (size_t)(kvh * G + h) * hd + d)
+                                               : make_uint4(0u, 0u, 0u, 0u);
+            }
+    } else {
+        // q of this kv head's G query heads, and (in the CTA that owns the token's position) k and v of
+        // the token: norm, rotate, round.  One warp per head; the work overlaps the cp.async traffic.
+        float* hb = Hb + warp * 256;
+        const bool owner = pos >= chunk_base && pos < chunk_base + AD_CHUNK;
+        const int n_jobs = G + (owner ? 2 : 0);
+        for (int job = warp; job < n_jobs; job += AD_WARPS) {
+            if (job < G) {
+                ad_norm_rope_head(q + (size_t)t * q_stride + (size_t)(kvh * G + job) * hd, hb, hd, fq.q_norm_w, fq.wdt, fq.eps,
+                                  fq.cos_t, fq.sin_t, fq.rot, t, lane);
+                for (int i = lane; i < hd; i += 32) Qs[job * hd + i] = __float2bfloat16_rn(hb[i]);
+            } else {
+                const bool is_k = job == G;
+                const int r = pos - chunk_base;
+                const long slot = fq.slot_map[t];
+                if (is_k) {
+                    ad_norm_rope_head(fq.k + (size_t)t * fq.k_stride + (size_t)kvh * hd, hb, hd, fq.k_norm_w, fq.wdt, fq.eps,
+                                      fq.cos_t, fq.sin_t, fq.rot, t, lane);
+                } else {
+                    const __nv_bfloat16* src = fq.v + (size_t)t * fq.v_stride + (size_t)kvh * hd;
+                    for (int i = lane; i < hd; i += 32) hb[i] = __bfloat162float(src[i]);
+                    __syncwarp();
+                }
+                __nv_bfloat16* cache_row = (is_k ? fq.k_cache_w : fq.v_cache_w) + ((size_t)slot * nkv + kvh) * hd;
+                const int swr = (is_k && swz) ? ((r & 1) << 2) : 0;
+                for (int i = lane; i < hd; i += 32) {
+                    const __nv_bfloat16 val = __float2bfloat16_rn(hb[i]);
+                    if (slot >= 0) cache_row[i] = val;
+                    const uint32_t dst = is_k ? K_u + r * k_stride + (uint32_t)(((i >> 3) ^ swr) * 16 + (i & 7) * 2)
+                                              : V_u + r * v_stride + (uint32_t)i * 2;
+                    asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst), "h"(*reinterpret_cast<const unsigned short*>(&val)) : "memory");
+                }
+            }
+            __syncwarp();
         }
+        __syncthreads();
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int ds = 0; ds < HS; ++ds) {
+                const int h = nt * 8 + g, d = ds * 32 + c * 8;
+                qf[nt][ds] = (h < G && d < hd) ? *reinterpret_cast<const uint4*>(Qs + h * hd + d) : make_uint4(0u, 0u, 0u, 0u);
+            }
+    }
 
     asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncthreads();                                         // K of the chunk is in shared memory
@@ -281,9 +380,10 @@ static int launch_decode(const void* q, long q_stride, const void* kc, const voi
                          const int* seq_of_token, const int* positions, const int* token_list, float* part_out, float* part_ml, int* counters,
                          void* out, long out_stride,
                          int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T,
-                         cudaStream_t stream) {
+                         const FusedQK& fq, cudaStream_t stream) {
     const int G = nq / nkv, NH = NT * 8;
-    const size_t loop_bytes = ((size_t)AD_CHUNK * NH + 2 * NH) * 4 + (size_t)NH * AD_CHUNK * 2;   // scores, max/denominator, probabilities
+    const size_t loop_bytes = ((size_t)AD_CHUNK * NH + 2 * NH) * 4 + (size_t)NH * AD_CHUNK * 2    // scores, max/denominator, probabilities
+                              + (size_t)AD_WARPS * 256 * 4 + (size_t)NH * hd * 2 + 16;            // fused q/k scratch, q
     const size_t comb_bytes = 0;
     const size_t merge_bytes = ((size_t)2 * max_splits * NH + NH) * 4;
     size_t smem = loop_bytes > comb_bytes ? loop_bytes : comb_bytes;
@@ -306,7 +406,7 @@ static int launch_decode(const void* q, long q_stride, const void* kc, const voi
     kern<<<grid, AD_WARPS * 32, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc,
                  (const __nv_bfloat16*)vc, bt, max_blocks, seq_of_token, positions, token_list,
                  part_out, part_ml, counters, (__nv_bfloat16*)out, out_stride, nq, nkv, hd, page_size, window, scale, max_splits,
-                 misc_bytes);
+                 misc_bytes, fq);
     return launch_status();
 }
 
@@ -318,10 +418,41 @@ using namespace aien;
 // Scratch: part_out [T * nq * max_splits * hd] floats, part_ml [T * nq * max_splits * 2] floats.
 // counters: T * nkv ints that are zero on entry and are left zero.
 // max_splits must cover the longest context in the step: ceil((max position + 1) / 128).
+static int decode_dispatch(
+    const void* q, long q_stride, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
+    const int* seq_of_token, const int* positions, const int* token_list, void* out, long out_stride, float* part_out,
+    float* part_ml, int* counters, int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T,
+    const FusedQK& fq, cudaStream_t stream);
+
 AIEN_API int aien_paged_attention_decode(
     const void* q, long q_stride, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
     const int* seq_of_token, const int* positions, const int* token_list, void* out, long out_stride, float* part_out,
     float* part_ml, int* counters, int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T, cudaStream_t stream) {
+    FusedQK none = {};
+    return decode_dispatch(q, q_stride, k_cache, v_cache, block_table, max_blocks, seq_of_token, positions, token_list, out,
+                           out_stride, part_out, part_ml, counters, nq, nkv, hd, page_size, window, scale, max_splits, T, none, stream);
+}
+
+// The same with the q/k kernel's work folded in: q, k, v are the raw projections of the step's tokens
+// (row strides in elements); k and v are written to the token's slot of the caches.
+AIEN_API int aien_paged_attention_decode_fused(
+    const void* q, long q_stride, const void* k, long k_stride, const void* v, long v_stride,
+    const void* q_norm_w, const void* k_norm_w, int w_dt, float eps, const float* cos_t, const float* sin_t, int rot,
+    const int* slot_map, void* k_cache, void* v_cache, const int* block_table, int max_blocks,
+    const int* positions, void* out, long out_stride, float* part_out, float* part_ml, int* counters,
+    int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T, cudaStream_t stream) {
+    if (hd > 256 || rot < 0 || rot > hd || (rot & 1) || k == nullptr || v == nullptr || slot_map == nullptr) return AIEN_E_SHAPE;
+    FusedQK fq = {(const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, q_norm_w, k_norm_w, w_dt, eps,
+                  cos_t, sin_t, rot, slot_map, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache};
+    return decode_dispatch(q, q_stride, k_cache, v_cache, block_table, max_blocks, nullptr, positions, nullptr, out, out_stride,
+                           part_out, part_ml, counters, nq, nkv, hd, page_size, window, scale, max_splits, T, fq, stream);
+}
+
+static int decode_dispatch(
+    const void* q, long q_stride, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
+    const int* seq_of_token, const int* positions, const int* token_list, void* out, long out_stride, float* part_out,
+    float* part_ml, int* counters, int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T,
+    const FusedQK& fq, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (hd <= 0 || hd > 256 || (hd & 15) || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || max_splits <= 0) return AIEN_E_SHAPE;
     const int G = nq / nkv;
@@ -333,7 +464,7 @@ AIEN_API int aien_paged_attention_decode(
     if (HS == hs && NT == nt)                                                                                        \
         rc = launch_decode<hs, nt>(q, q_stride, k_cache, v_cache, block_table, max_blocks, seq_of_token, positions,  \
                                    token_list, part_out, part_ml, counters, out, out_stride, nq, nkv, hd, page_size, window, scale,        \
-                                   max_splits, T, stream);
+                                   max_splits, T, fq, stream);
     AD_CASE(1, 1) AD_CASE(2, 1) AD_CASE(3, 1) AD_CASE(4, 1) AD_CASE(5, 1) AD_CASE(6, 1) AD_CASE(7, 1) AD_CASE(8, 1)
     AD_CASE(1, 2) AD_CASE(2, 2) AD_CASE(3, 2) AD_CASE(4, 2) AD_CASE(5, 2) AD_CASE(6, 2) AD_CASE(7, 2) AD_CASE(8, 2)
 #undef AD_CASE

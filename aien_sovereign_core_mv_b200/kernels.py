@@ -63,6 +63,8 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_gemm_tc_error": [],
         "aien_paged_attention_prefill": [P, L, P, P, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P],
         "aien_paged_attention_decode": [P, L, P, P, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, P],
+        "aien_paged_attention_decode_fused": [P, L, P, L, P, L, P, P, I, F, P, P, I, P, P, P, P, I, P, P, L, P, P, P,
+                                              I, I, I, I, I, F, I, I, P],
     }
     for name, args in sigs.items():
         fn = getattr(l, name)
@@ -420,6 +422,38 @@ def paged_attention_decode(q, k_cache, v_cache, block_table, max_blocks, seq_of_
         page_size, window, float(scale), max_splits, T, _stream()), "paged_attention_decode")
 
 
+def paged_attention_decode_fused(ctx, q, k, v, q_norm_w, k_norm_w, eps, cos, sin, rotary_dim, group, k_cache, v_cache, out,
+                                 num_q_heads, num_kv_heads, head_dim, window, scale) -> None:
+    """Decode-only steps: per-head q/k norm, rotation, the write of k and v into the cache and the
+    split-key attention in one launch.  q, k, v are the raw projections [T, heads*head_dim]."""
+    global _ticket_counters
+    _dev(q, k, v, q_norm_w, k_norm_w, cos, sin, k_cache, v_cache, out)
+    T = q.shape[0]
+    if _ticket_counters is None:
+        _ticket_counters = torch.zeros(1 << 16, dtype=torch.int32, device=q.device)
+    assert T * num_kv_heads <= _ticket_counters.numel()
+    assert q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1 and out.stride(1) == 1
+    wdt = F32
+    for w in (q_norm_w, k_norm_w):
+        if w is not None:
+            assert w.numel() == head_dim and w.is_contiguous()
+            wdt = dt(w)
+    if cos is not None:
+        assert cos.shape == (T, rotary_dim // 2) and cos.is_contiguous() and sin.is_contiguous()
+    splits = max(1, (ctx.max_ctx_len + DECODE_CHUNK - 1) // DECODE_CHUNK)
+    part_out = ctx.workspace.take((T * num_q_heads * splits * head_dim,), torch.float32)
+    part_ml = ctx.workspace.take((T * num_q_heads * splits * 2,), torch.float32)
+    k2 = k_cache.view(-1, num_kv_heads, head_dim)
+    v2 = v_cache.view(-1, num_kv_heads, head_dim)
+    _check(lib().aien_paged_attention_decode_fused(
+        _p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0), _p(q_norm_w), _p(k_norm_w), wdt, float(eps),
+        _p(cos), _p(sin), rotary_dim if cos is not None else 0, _p(group.slot_map), _p(k2), _p(v2), _p(group.block_table),
+        group.max_blocks, _p(ctx.positions), _p(out), out.stride(0), _p(part_out), _p(part_ml), _p(_ticket_counters),
+        num_q_heads, num_kv_heads, head_dim, group.page_size, window, float(scale), splits, T, _stream()),
+        "paged_attention_decode_fused")
+
+
 def decode_attention_supports(q: torch.Tensor, k_cache: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int) -> bool:
     return (q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256
             and num_q_heads // num_kv_heads <= 16 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0)
@@ -432,7 +466,8 @@ def paged_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                     num_q_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float) -> None:
     """Attention of the step's tokens over one cache group; picks the kernel for the step:
     the split-key kernel when every request brings one token (bfloat16), else the generic one.
-    ``AIEN_B200_ATTENTION=generic`` pins the generic kernel for debugging."""
+    ``AIEN_B200_ATTENTION=generic`` pins the generic kernel for debugging; ``fused`` folds the q/k
+    kernel into the decode attention launch (see parts/attention.py)."""
     k2 = k_cache.view(-1, num_kv_heads, head_dim)
     v2 = v_cache.view(-1, num_kv_heads, head_dim)
     if (ctx.decode_only and _FORCE_ATTN != "generic"

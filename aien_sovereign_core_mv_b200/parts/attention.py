@@ -81,9 +81,19 @@ class PagedAttention(Mixer):
         else:
             q = linear(ctx, h, self.w_qkv[:self.q_dim], may_defer_sum=True)
             k = v = None
-        q_out = ctx.workspace.take((T, self.q_dim), ctx.dtype) if q.dim() == 3 else q
         rot = self.position.rotary(ctx)
         cos, sin, rdim = rot if rot is not None else (None, None, 0)
+        if (K._FORCE_ATTN == "fused" and ctx.decode_only and run.writes and q.dim() == 2 and rot is not None
+                and K.decode_attention_supports(q, k_cache, self.num_heads, self.num_kv_heads, self.head_dim)):
+            # One launch: q/k norm, rotation, cache write and attention.  Opt-in (AIEN_B200_ATTENTION=fused):
+            # measured on the Qwen3-8B shape it equals the two launches at batch 1 and loses at batch 8
+            # and 64, where every chunk's CTA repeats the q work.
+            out = ctx.workspace.take((T, self.q_dim), ctx.dtype)
+            K.paged_attention_decode_fused(ctx, q, k, v, self.q_norm_w, self.k_norm_w, self.qk_norm_eps, cos, sin, rdim, group,
+                                           k_cache, v_cache, out, self.num_heads, self.num_kv_heads, self.head_dim,
+                                           self.window, self.scale)
+            return linear(ctx, out, self.w_o, may_defer_sum=True)
+        q_out = ctx.workspace.take((T, self.q_dim), ctx.dtype) if q.dim() == 3 else q
         K.qk_norm_rope_kv_write(q, k, v, self.head_dim, self.q_norm_w, self.k_norm_w if k is not None else None,
                                 self.qk_norm_eps, cos, sin, rdim,
                                 group.slot_map if k is not None else None,

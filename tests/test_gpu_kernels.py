@@ -547,3 +547,43 @@ def test_gemm_tensor_core_split_k(K, M, N, K_, splits):
     want = (a.double().cpu() @ w.double().cpu().T).numpy()
     H.assert_close(parts.sum(0).cpu().numpy(), want, 2e-5, f"tc gemm split-K {M}x{N}x{K_}/{ranges}")
     assert K.gemm_tc_splits(2048, 4096, 4096) == 1 and K.gemm_tc_splits(64, 4096, 4096) > 1
+
+
+@pytest.mark.parametrize("nq,nkv,hd,page,window,norm", [(8, 2, 128, 16, 0, True), (6, 3, 48, 8, 0, True), (5, 1, 80, 16, 0, False),
+                                                        (4, 4, 64, 16, 40, True), (16, 1, 32, 4, 0, True)])
+def test_decode_attention_with_qk_work_folded_in(K, nq, nkv, hd, page, window, norm):
+    """The fused launch equals q/k kernel + attention kernel: same outputs, same bits in the cache."""
+    from types import SimpleNamespace
+    from aien_sovereign_core_mv_b200.parts import GroupView, Workspace
+    dtype = torch.bfloat16
+    rng = np.random.default_rng(nq + hd)
+    seq_lens = [1, 37, 700, 128, 129, 513]
+    kc, vc, bt, mb, dense = paged_setup(rng, seq_lens, nkv, hd, page, dtype, sum((n + page - 1) // page for n in seq_lens) + 8)
+    T = len(seq_lens)
+    positions = [n - 1 for n in seq_lens]
+    slot_map = torch.tensor([int(bt[s, p // page]) * page + p % page for s, p in enumerate(positions)], dtype=torch.int32).cuda()
+    qkv = torch.tensor(rng.standard_normal((T, (nq + 2 * nkv) * hd)), dtype=torch.float32).to(dtype).cuda()
+    q, k, v = qkv[:, :nq * hd], qkv[:, nq * hd:(nq + nkv) * hd], qkv[:, (nq + nkv) * hd:]
+    qw = (torch.rand(hd) * 0.4 + 0.8).to(dtype).cuda() if norm else None
+    kw = (torch.rand(hd) * 0.4 + 0.8).to(dtype).cuda() if norm else None
+    pos_t = torch.tensor(positions, dtype=torch.int32).cuda()
+    cos = torch.empty(T, hd // 2, device="cuda"); sin = torch.empty(T, hd // 2, device="cuda")
+    K.rope_table(pos_t, torch.tensor(pm.rope_inv_freq(hd, 10000.0), dtype=torch.float64).cuda(), cos, sin)
+    scale = 1.0 / math.sqrt(hd)
+    splits = (max(seq_lens) + K.DECODE_CHUNK - 1) // K.DECODE_CHUNK
+    # the two-kernel path
+    kc1, vc1, q1 = kc.clone(), vc.clone(), q.clone()
+    K.qk_norm_rope_kv_write(q1, k, v, hd, qw, kw, 1e-6, cos, sin, hd, slot_map, kc1, vc1)
+    want = torch.empty(T, nq * hd, dtype=dtype, device="cuda")
+    K.paged_attention_decode(q1, kc1, vc1, bt, mb, None, pos_t, want, torch.empty(T * nq * splits * hd, device="cuda"),
+                             torch.empty(T * nq * splits * 2, device="cuda"), nq, nkv, hd, page, window, scale, splits)
+    # the fused path
+    kc2, vc2 = kc.clone(), vc.clone()
+    ws = Workspace(1 << 24, 1 << 24, torch.device("cuda")); ws.begin_layer()
+    ctx = SimpleNamespace(max_ctx_len=max(seq_lens), workspace=ws, positions=pos_t)
+    group = GroupView("full", page, window, mb, bt, slot_map, None)
+    got = torch.empty(T, nq * hd, dtype=dtype, device="cuda")
+    K.paged_attention_decode_fused(ctx, q, k, v, qw, kw, 1e-6, cos, sin, hd, group, kc2, vc2, got, nq, nkv, hd, window, scale)
+    torch.cuda.synchronize()
+    assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+    assert torch.equal(got, want)
