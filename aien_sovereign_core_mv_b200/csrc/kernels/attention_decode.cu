@@ -382,8 +382,8 @@ static int launch_decode(const void* q, long q_stride, const void* kc, const voi
                          int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T,
                          const FusedQK& fq, cudaStream_t stream) {
     const int G = nq / nkv, NH = NT * 8;
-    const size_t loop_bytes = ((size_t)AD_CHUNK * NH + 2 * NH) * 4 + (size_t)NH * AD_CHUNK * 2    // scores, max/denominator, probabilities
-                              + (size_t)AD_WARPS * 256 * 4 + (size_t)NH * hd * 2 + 16;            // fused q/k scratch, q
+    size_t loop_bytes = ((size_t)AD_CHUNK * NH + 2 * NH) * 4 + (size_t)NH * AD_CHUNK * 2;          // scores, max/denominator, probabilities
+    if (fq.k != nullptr) loop_bytes += (size_t)AD_WARPS * 256 * 4 + (size_t)NH * hd * 2 + 16;      // fused q/k scratch, q
     const size_t comb_bytes = 0;
     const size_t merge_bytes = ((size_t)2 * max_splits * NH + NH) * 4;
     size_t smem = loop_bytes > comb_bytes ? loop_bytes : comb_bytes;
