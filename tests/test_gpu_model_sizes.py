@@ -1,0 +1,58 @@
+"""The engine at the layer sizes of the real models (Qwen3-8B and Llama-3-8B shapes, two layers, a
+small vocabulary so that the plain implementation stays fast): the kernels meet their production
+shapes here (K = 4096 / 12288 / 14336, 32 query heads in groups of 4, head size 128), whole, in portions and
+decoding, in float32 and bfloat16."""
+import numpy as np
+import pytest
+
+import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = {
+    "qwen3_8b": dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=4096,
+                     num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=2048,
+                     rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096,
+                     hidden_act="silu", eos_token_id=1),
+    "llama3_8b": dict(architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=2, hidden_size=4096,
+                      num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=1000,
+                      rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=8192,
+                      hidden_act="silu", eos_token_id=1),
+}
+
+
+@pytest.fixture(scope="module")
+def big(tmp_path_factory):
+    from aien_sovereign_core_mv_b200 import write_random_model
+    root = tmp_path_factory.mktemp("big")
+    out = {}
+    for name, cfg in SHAPES.items():
+        d = write_random_model(str(root / name), cfg, seed=2, init_std=0.02)
+        toks = [int(t) for t in np.random.default_rng(5).integers(0, cfg["vocab_size"], 200)]
+        out[name] = (d, toks, H.plain_logits(d, toks))
+    return out
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", H.FP32_TOL), ("bfloat16", H.BF16_TOL)])
+@pytest.mark.parametrize("name", list(SHAPES))
+def test_production_layer_sizes(big, name, dtype, tol):
+    d, toks, want = big[name]
+    eng = H.engine_for(d, dtype, 16, 1024, max_requests=16, max_batch_tokens=256)
+    # whole; then 150 tokens in portions of 64 + 64 + 22 followed by 50 single tokens; then a batch of decoding requests
+    got = H.run_steps(eng, [([(1, toks, list(range(len(toks))))], [1])])
+    H.assert_close(np.stack([got[1][p] for p in range(len(toks))]), want, tol, f"{name} {dtype} whole")
+    steps = [([(2, toks[:64], [63])], []), ([(2, toks[64:128], [0, 63])], []), ([(2, toks[128:150], [21])], [])]
+    steps += [([(2, [t], [0])], []) for t in toks[150:]]
+    got = H.run_steps(eng, steps)
+    pos = sorted(got[2])
+    H.assert_close(np.stack([got[2][p] for p in pos]), want[pos], tol, f"{name} {dtype} portions + decode")
+    eng.end_request(2)
+    # twelve requests decoding together (the small-batch product with two token tiles) beside one portion
+    ids = list(range(10, 22))
+    H.run_steps(eng, [([(r, toks[:20 + r], []) for r in ids[:6]], []), ([(r, toks[:20 + r], []) for r in ids[6:]], [])])
+    got = H.run_steps(eng, [([(r, [toks[20 + r]], [0]) for r in ids], []),
+                            ([(r, [toks[21 + r]], [0]) for r in ids] + [(99, toks[:40], [39])], ids + [99])])
+    for r in ids:
+        H.assert_close(np.stack([got[r][0], got[r][1]]), want[[20 + r, 21 + r]], tol, f"{name} {dtype} batched decode, request {r}")
+    H.assert_close(got[99][39], want[39], tol, f"{name} {dtype} portion beside decodes")
+    assert eng.cache_state()["check"] == "" and eng.cache_state()["requests"] == 0

@@ -8,7 +8,9 @@ import pytest
 
 import plain_model as pm
 
-FIX = "/root/reference/crates/aien-inference-abi/fixtures"
+# the reference project, when it is checked out beside this repository (or named by AIEN_REFERENCE_DIR)
+_REF = os.environ.get("AIEN_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
+FIX = os.path.join(_REF, "crates", "aien-inference-abi", "fixtures")
 
 
 @pytest.mark.parametrize("name", ["qwen3-tiny", "openwaldo-byte"])
