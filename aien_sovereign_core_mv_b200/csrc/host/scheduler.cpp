@@ -43,6 +43,32 @@ bool Scheduler::cancel(int64_t id) {
     return true;
 }
 
+std::vector<PageCopy> Scheduler::fork(int64_t parent, int64_t child, int max_tokens, std::vector<int32_t> stop_ids, int priority) {
+    if (awaiting_commit_) throw std::logic_error("fork() between plan() and commit()");
+    auto it = seqs_.find(parent);
+    if (it == seqs_.end() || it->second.state != SeqState::Running)
+        throw std::invalid_argument("request " + std::to_string(parent) + " is not running");
+    if (seqs_.count(child) && seqs_[child].state != SeqState::Finished)
+        throw std::invalid_argument("request " + std::to_string(child) + " is already live");
+    if (max_tokens <= 0) throw std::invalid_argument("max_tokens must be positive");
+    const SeqRecord& p = it->second;
+    std::vector<PageCopy> copies = cache_->fork(parent, child, p.computed);     // throws with nothing changed
+    SeqRecord c;
+    c.id = child;
+    c.prompt = p.prompt;
+    c.prompt.insert(c.prompt.end(), p.generated.begin(), p.generated.end());
+    c.computed = p.computed;
+    c.max_tokens = max_tokens;
+    c.stop_ids = std::move(stop_ids);
+    c.priority = priority;
+    c.arrival = arrivals_++;
+    c.state = SeqState::Running;
+    seqs_[child] = std::move(c);
+    running_.insert(std::upper_bound(running_.begin(), running_.end(), child), child);
+    ++metrics_.admitted;
+    return copies;
+}
+
 int Scheduler::min_free_pages() const {
     int m = INT_MAX;
     for (int g = 0; g < cache_->num_groups(); ++g)
@@ -349,6 +375,11 @@ void bind_scheduler(pybind11::module_& m) {
         .def("submit", &Scheduler::submit, py::arg("id"), py::arg("prompt"), py::arg("max_tokens"),
              py::arg("stop_ids") = std::vector<int32_t>{}, py::arg("priority") = 0)
         .def("cancel", &Scheduler::cancel)
+        .def("fork", [](Scheduler& s, int64_t parent, int64_t child, int max_tokens, std::vector<int32_t> stop_ids, int priority) {
+                 std::vector<std::tuple<int, int, int>> out;
+                 for (const auto& c : s.fork(parent, child, max_tokens, std::move(stop_ids), priority)) out.emplace_back(c.group, c.src, c.dst);
+                 return out;
+             }, py::arg("parent"), py::arg("child"), py::arg("max_tokens"), py::arg("stop_ids") = std::vector<int32_t>{}, py::arg("priority") = 0)
         .def("has_work", &Scheduler::has_work)
         .def_property_readonly("num_running", &Scheduler::num_running)
         .def_property_readonly("num_waiting", &Scheduler::num_waiting)

@@ -94,6 +94,11 @@ class Scheduler {
 
     void submit(int64_t id, std::vector<int32_t> prompt, int max_tokens, std::vector<int32_t> stop_ids, int priority);
     bool cancel(int64_t id);
+    // A running request branches: the child takes the parent's tokens so far as its prompt, shares
+    // the parent's cache pages (copy-on-write) and starts running at once, with its own limits
+    // (crates/aien-scheduler/src/lib.rs:339-362).  Returns the copies the device must perform
+    // (state slots).  Only between steps.
+    std::vector<PageCopy> fork(int64_t parent, int64_t child, int max_tokens, std::vector<int32_t> stop_ids, int priority);
     bool has_work() const { return !waiting_.empty() || !preempted_.empty() || !running_.empty(); }
     int num_running() const { return static_cast<int>(running_.size()); }
     int num_waiting() const { return static_cast<int>(waiting_.size() + preempted_.size()); }

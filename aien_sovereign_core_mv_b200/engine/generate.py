@@ -16,12 +16,18 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence, Union
 
+import os
+import sys
+
 import numpy as np
 import torch
 
 from .. import kernels as K
 from ..sampling.sampler import SamplingParams
 from .engine import Engine
+
+
+_STEP_LOG = os.environ.get("AIEN_STEP_LOG", "") not in ("", "0")
 
 
 @dataclass
@@ -79,6 +85,14 @@ class Generator:
         self.scheduler.submit(int(request_id), prompt, int(p.max_tokens), stops, int(priority))
         self.params[int(request_id)] = p
 
+    def fork(self, parent_id: int, child_id: int, params: Optional[SamplingParams] = None, priority: int = 0) -> None:
+        """A running request branches: the child continues from the parent's tokens so far on shared
+        cache pages (copied only where one of the two writes), with its own sampling parameters."""
+        p = params or self.params.get(int(parent_id)) or SamplingParams()
+        stops = list(self.engine.model.spec.stop_token_ids) if p.stop_token_ids is None else [int(t) for t in p.stop_token_ids]
+        self.engine._do_copies(self.scheduler.fork(int(parent_id), int(child_id), int(p.max_tokens), stops, int(priority)))
+        self.params[int(child_id)] = p
+
     # ------------------------------------------------------------------ one step
     def step(self) -> List[GenerationResult]:
         """Plan, run, sample, commit.  Returns the requests that finished in this step."""
@@ -104,6 +118,10 @@ class Generator:
                 sampled = self._choose(logits, rows)
             self.scheduler.commit(sampled)
             self.steps += 1
+            if _STEP_LOG:
+                # one line per step, like the reference's AIEN_STEP_LOG (crates/aien-runtime/src/server.rs:273-293)
+                print(f"step {plan.step_id}: prefill_tokens={plan.prefill_tokens} decode_tokens={plan.num_tokens - plan.prefill_tokens} "
+                      f"requests={len(entries)} emitted={len(sampled)} preempted={len(plan.preempted)}", file=sys.stderr, flush=True)
         out = []
         for ev in self.scheduler.take_finished():
             rec_pre = self.scheduler.record(ev.id).preemptions

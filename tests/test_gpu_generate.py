@@ -111,6 +111,30 @@ def test_preemption_repeats_nothing(folders):
     assert eng.cache_state()["free_pages"] == [5]
 
 
+def test_fork_through_the_generator(folders):
+    """A request branches after a few tokens: the greedy child on the shared pages repeats the
+    parent's continuation, a sampling child goes its own way, and the parent is not disturbed."""
+    from aien_sovereign_core_mv_b200.engine.generate import Generator
+    from aien_sovereign_core_mv_b200.sampling import SamplingParams
+    d = folders["A"]
+    prompt = H.tokens_for("A", 21, 77)                       # ends inside a page: the tail page is copied on write
+    want = plain_greedy(d, prompt, 14)
+    eng = H.engine_for(d, "float32", 16, 512)
+    gen = Generator(eng)
+    gen.submit(1, prompt, SamplingParams(temperature=0.0, max_tokens=14, stop_token_ids=[]))
+    done = {}
+    while len(gen.scheduler.record(1).generated) < 5:
+        for r in gen.step():
+            done[r.request_id] = r
+    made = len(gen.scheduler.record(1).generated)
+    gen.fork(1, 2, SamplingParams(temperature=0.0, max_tokens=14 - made, stop_token_ids=[]))
+    gen.fork(1, 3, SamplingParams(temperature=1.3, top_p=1.0, top_k=0, max_tokens=6, stop_token_ids=[], seed=5))
+    done.update(gen.run())
+    assert done[1].tokens == want and done[2].tokens == want[made:]
+    assert len(done[3].tokens) == 6 and done[3].tokens != want[made:made + 6]
+    assert eng.cache_state()["requests"] == 0 and eng.cache_state()["check"] == ""
+
+
 def test_command_line(folders, tmp_path):
     d = folders["A"]
     prompt = H.tokens_for("A", 13, 3)

@@ -165,3 +165,22 @@ def test_context_limit():
     s.submit(1, list(range(8)), 100)
     done = drive(s, cm)
     assert done[1][1] == "LengthLimit" and len(done[1][0]) == 4
+
+
+def test_fork_shares_the_cache_and_runs_at_once():
+    cm, s = make()
+    s.submit(1, list(range(10)), 6)
+    plan = s.plan(); s.commit([fake_token(1, 10)])             # prompt done, one token generated
+    copies = s.fork(1, 2, 4, [], 0)
+    assert copies == [] and cm.num_tokens(2) == 10 and cm.table(2, 0) == cm.table(1, 0)
+    rec = s.record(2)
+    assert rec.prompt == list(range(10)) + [fake_token(1, 10)] and rec.computed == 10 and rec.state.name == "Running"
+    plan = s.plan()                                             # both decode the token they share; the tail page is copied for one
+    assert [(e.id, e.start, e.tokens) for e in plan.entries] == [(1, 10, [fake_token(1, 10)]), (2, 10, [fake_token(1, 10)])]
+    assert len(plan.copies) >= 1
+    s.commit([fake_token(1, 11), fake_token(2, 11)])
+    done = drive(s, cm)
+    assert done[1][0] == expected(1, 10, 6) and done[2][0] == [fake_token(2, 11 + i) for i in range(4)]
+    assert cm.free_count(0) == 64
+    with pytest.raises(ValueError, match="not running"):
+        s.fork(1, 3, 4, [], 0)
