@@ -1,0 +1,364 @@
+// Prefill attention over the paged bfloat16 cache on the fifth-generation tensor cores.
+//
+// Same job and same arguments as the mma.sync prefill kernel (portions of prompts of any length
+// at any offset, causal, grouped-query, optional window; the host lists tiles of 128 query tokens),
+// for head sizes 64 and 128 and pages of 8..128 tokens that divide 128.
+//
+// One CTA handles one tile of 128 query tokens for TWO query heads that share a key/value head,
+// so every key/value block it brings into shared memory is used twice.  Ten warps:
+//   warps 0-3   softmax of head A: thread r owns query row r (tensor-memory lane r)
+//   warps 4-7   softmax of head B
+//   warp 8      producer: TMA copies of Q (once) and of the K and V blocks, page by page through
+//               the block table, into a ring of shared-memory slots (absent pages are fetched at an
+//               out-of-range coordinate, which fills zeros)
+//   warp 9      allocates tensor memory; one lane issues tcgen05.mma
+// Per block of 128 keys (aligned to absolute positions) and per head:
+//   S = Q K^T         M 128 x N 128 x K head size; Q and K are K-major tiles; S in tensor memory
+//   softmax           each thread reads its row of S with tcgen05.ld twice (maximum, then
+//                     exponentials in float32 with the causal/window limits of its row), writes
+//                     P as bfloat16 into a swizzled K-major tile in shared memory
+//   O_blk = P V       M 128 x N head size x K 128; V is used as stored ([key][dim]: an MN-major
+//                     tile); the block's product lands in tensor memory and the row's thread
+//                     adds it to its float32 accumulator in registers, rescaled by the running
+//                     maximum, so nothing in tensor memory ever needs rescaling
+// The issue order alternates the heads (PV_A(j), QK_A(j+1), PV_B(j), QK_B(j+1)), so that the
+// tensor core works for one head while the other head's softmax runs.
+// Formulas: crates/aien-inference-abi/src/backend.rs:280-306, scale 1/sqrt(head_dim).
+//
+// Every wait is bounded; one that runs out records a code (aien_attention_prefill_tc_error) and
+// the kernel runs on to its end, frees its tensor memory and returns.  The cache must hold finite
+// values everywhere (it is zero-initialised and only ever written with activations): whole pages
+// are loaded, and a key that is masked still meets a zero weight in P V.
+#include "tma.cuh"
+#include "umma.cuh"
+#include <math.h>
+
+namespace aien {
+
+constexpr int PT_BM = 128, PT_BN = 128, PT_THREADS = 320;
+constexpr int PT_SMEM_MAX = 227 * 1024;
+
+template <int HD> struct PtShape {
+    static constexpr int CHUNKS = HD / 64;                       // 64-column (128-byte) chunks of a row
+    static constexpr int Q_BYTES = PT_BM * HD * 2;               // one head's query tile
+    static constexpr int P_BYTES = PT_BM * PT_BN * 2;            // one head's probabilities
+    static constexpr int SLOT_BYTES = PT_BN * HD * 2;            // one K or V block
+    static constexpr int FIXED = 2 * Q_BYTES + 2 * P_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr int SLOTS_FIT = (PT_SMEM_MAX - FIXED) / SLOT_BYTES;
+    static constexpr int SLOTS = SLOTS_FIT > 6 ? 6 : SLOTS_FIT;
+    static constexpr int SMEM = FIXED + SLOTS * SLOT_BYTES;
+    static_assert(SLOTS >= 3, "the K/V ring needs three slots");
+};
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(PT_THREADS, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                  const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int max_blocks,
+                  const int* __restrict__ q_start, const int* __restrict__ ctx_len, const int* __restrict__ tile_seq,
+                  const int* __restrict__ tile_q0, int num_tiles, __nv_bfloat16* __restrict__ out, long out_stride,
+                  int nq, int nkv, int page_size, int window, float scale_log2e, int cache_rows) {
+    using S = PtShape<HD>;
+    extern __shared__ uint8_t pt_smem[];
+    const uint32_t base = (smem_u32(pt_smem) + 1023u) & ~1023u;
+    const uint32_t sQ = base, sP = sQ + 2 * S::Q_BYTES, sKV = sP + 2 * S::P_BYTES;
+    const uint32_t bars = sKV + S::SLOTS * S::SLOT_BYTES;
+    const uint32_t q_full = bars, kv_full0 = bars + 8, kv_free0 = kv_full0 + 8 * S::SLOTS;
+    const uint32_t s_ready0 = kv_free0 + 8 * S::SLOTS, p_ready0 = s_ready0 + 16, o_ready0 = p_ready0 + 16;
+    const uint32_t tmem_slot = o_ready0 + 16;
+    uint8_t* gen = pt_smem + (base - smem_u32(pt_smem));
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen + (tmem_slot - base));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // ---- which tile, which heads (the last tiles of a request see the most keys: they start first)
+    const int group = nq / nkv, pairs = (group + 1) / 2;
+    const int per_tile = nkv * pairs;
+    const int tile = num_tiles - 1 - (int)(blockIdx.x / per_tile);
+    const int rem = blockIdx.x % per_tile;
+    const int kvh = rem / pairs, pair = rem - kvh * pairs;
+    const int head_a = kvh * group + 2 * pair;
+    const bool has_b = 2 * pair + 1 < group;
+    const int s = tile_seq[tile], q0 = tile_q0[tile];
+    const int qs = q_start[s], q_len = q_start[s + 1] - qs;
+    const int rows = min(PT_BM, q_len - q0);
+    const int pos0 = ctx_len[s] - q_len + q0;                      // position of the tile's first query
+    const int pos_last = pos0 + rows - 1;
+    const int first = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    const int kb_begin = first / PT_BN, kb_end = pos_last / PT_BN;
+    const int nb = kb_end - kb_begin + 1;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int i = 0; i < S::SLOTS; ++i) { mbar_init(kv_full0 + 8 * i, 1); mbar_init(kv_free0 + 8 * i, 1); }
+        for (int h = 0; h < 2; ++h) { mbar_init(s_ready0 + 8 * h, 1); mbar_init(p_ready0 + 8 * h, 128); mbar_init(o_ready0 + 8 * h, 1); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot_ptr;
+    // tensor-memory columns: S of head A, S of head B, then the block products O of A and of B
+    const uint32_t tS0 = tmem, tO0 = tmem + 2 * PT_BN;
+
+    if (warp == 8) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            mbar_expect_tx(q_full, (has_b ? 2 : 1) * S::Q_BYTES);
+            for (int h = 0; h < (has_b ? 2 : 1); ++h)
+                for (int c = 0; c < S::CHUNKS; ++c)
+                    tma_load_2d(sQ + h * S::Q_BYTES + c * (PT_BM * 128), &map_q, q_full, (head_a + h) * HD + c * 64, qs + q0);
+        }
+        const int pages_per_block = PT_BN / page_size;
+        const int* bt = block_table + (size_t)s * max_blocks;
+        for (int item = 0; item < 2 * nb; ++item) {                 // K0 V0 K1 V1 ...
+            const int slot = item % S::SLOTS;
+            if (item >= S::SLOTS) mbar_wait(kv_free0 + 8 * slot, ((item / S::SLOTS) - 1) & 1, 1);
+            const int kb = kb_begin + (item >> 1);
+            if (lane == 0) mbar_expect_tx(kv_full0 + 8 * slot, S::SLOT_BYTES);
+            __syncwarp();
+            if (lane < pages_per_block) {
+                const int key0 = kb * PT_BN + lane * page_size;
+                const int blk = key0 / page_size;
+                int page = -1;
+                if (key0 <= pos_last && key0 + page_size > first && blk < max_blocks) page = bt[blk];
+                const int row = page >= 0 ? page * page_size : cache_rows;     // out of range: zeros
+                const CUtensorMap* map = (item & 1) ? &map_v : &map_k;
+                const uint32_t dst = sKV + slot * S::SLOT_BYTES + lane * page_size * 128;
+                for (int c = 0; c < S::CHUNKS; ++c)
+                    tma_load_2d(dst + c * (PT_BN * 128), map, kv_full0 + 8 * slot, kvh * HD + c * 64, row);
+            }
+        }
+    } else if (warp == 9) {
+        // ------------------------------------------------------------------ MMA issue
+        if (lane == 0) {
+            const uint32_t idesc_qk = umma_idesc_bf16(PT_BM, PT_BN, false);
+            const uint32_t idesc_pv = umma_idesc_bf16(PT_BM, HD, true);
+            auto issue_qk = [&](int h, int slot) {
+                const uint32_t a = sQ + h * S::Q_BYTES, b = sKV + slot * S::SLOT_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * (PT_BM * 128) + (kk & 3) * 32;
+                    umma_bf16(tS0 + h * PT_BN, make_desc_sw128(a + off), make_desc_sw128(b + off), idesc_qk, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(s_ready0 + 8 * h);
+            };
+            auto issue_pv = [&](int h, int slot) {
+                const uint32_t a = sP + h * S::P_BYTES, b = sKV + slot * S::SLOT_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < PT_BN / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * (PT_BM * 128) + (kk & 3) * 32;
+                    umma_bf16(tO0 + h * HD, make_desc_sw128(a + off), make_desc_sw128_mn(b + kk * 16 * 128, PT_BN * 128), idesc_pv, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(o_ready0 + 8 * h);
+            };
+            auto wait_item = [&](int item) {
+                mbar_wait(kv_full0 + 8 * (item % S::SLOTS), (item / S::SLOTS) & 1, 2);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            };
+            mbar_wait(q_full, 0, 3);
+            wait_item(0);
+            issue_qk(0, 0);
+            if (has_b) issue_qk(1, 0);
+            umma_commit(kv_free0);
+            for (int j = 0; j < nb; ++j) {
+                const int v_item = 2 * j + 1, k_item = 2 * j + 2;
+                const bool more = j + 1 < nb;
+                mbar_wait(p_ready0, j & 1, 4);
+                wait_item(v_item);
+                issue_pv(0, v_item % S::SLOTS);
+                if (more) { wait_item(k_item); issue_qk(0, k_item % S::SLOTS); }
+                if (has_b) {
+                    mbar_wait(p_ready0 + 8, j & 1, 5);
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    issue_pv(1, v_item % S::SLOTS);
+                }
+                umma_commit(kv_free0 + 8 * (v_item % S::SLOTS));
+                if (more) {
+                    if (has_b) issue_qk(1, k_item % S::SLOTS);
+                    umma_commit(kv_free0 + 8 * (k_item % S::SLOTS));
+                }
+            }
+        }
+    } else if (warp < 4 || has_b) {
+        // ------------------------------------------------------------------ softmax and accumulation
+        const int h = warp >> 2, quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+        const uint32_t tS = tS0 + h * PT_BN + lane_off, tO = tO0 + h * HD + lane_off;
+        const uint32_t p_row = sP + h * S::P_BYTES + r * 128;
+        const int hi = r < rows ? pos0 + r : -1;                                 // last key this row sees
+        const int lo = (window > 0 && hi - window + 1 > 0) ? hi - window + 1 : 0;
+        float acc[HD];
+#pragma unroll
+        for (int d = 0; d < HD; ++d) acc[d] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;
+
+        for (int j = 0; j < nb; ++j) {
+            const int key_base = (kb_begin + j) * PT_BN;
+            mbar_wait(s_ready0 + 8 * h, j & 1, 6);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const bool masked = key_base + PT_BN - 1 > hi || key_base < lo;
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c0 = 0; c0 < PT_BN; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tS + c0, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (masked) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = key_base + c0 + i;
+                        if (key >= lo && key <= hi) mx = fmaxf(mx, __uint_as_float(v[i]));
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+                }
+            }
+            const float m_new = fmaxf(m_run, mx * scale_log2e);
+            const float alpha = (m_run == -INFINITY) ? 0.f : ex2_approx(m_run - m_new);
+            const float neg_base = (m_new == -INFINITY) ? 0.f : -m_new;
+            float sum = 0.f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < PT_BN; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tS + c0, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                float p[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float sc = __uint_as_float(v[i]);
+                    if (masked) {
+                        const int key = key_base + c0 + i;
+                        if (key < lo || key > hi) sc = -INFINITY;
+                    }
+                    p[i] = ex2_approx(fmaf(sc, scale_log2e, neg_base));          // exp2(-inf) = 0 for masked keys
+                    sum += p[i];
+                }
+                const uint32_t chunk_base = p_row + (c0 >> 6) * (PT_BM * 128);
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const int unit = ((c0 & 63) >> 3) + t;
+                    const uint32_t addr = chunk_base + (uint32_t)((unit ^ (r & 7)) << 4);
+                    __nv_bfloat162 a = __floats2bfloat162_rn(p[8 * t + 0], p[8 * t + 1]), b = __floats2bfloat162_rn(p[8 * t + 2], p[8 * t + 3]);
+                    __nv_bfloat162 c = __floats2bfloat162_rn(p[8 * t + 4], p[8 * t + 5]), d = __floats2bfloat162_rn(p[8 * t + 6], p[8 * t + 7]);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(*reinterpret_cast<uint32_t*>(&a)),
+                                 "r"(*reinterpret_cast<uint32_t*>(&b)), "r"(*reinterpret_cast<uint32_t*>(&c)),
+                                 "r"(*reinterpret_cast<uint32_t*>(&d)) : "memory");
+                }
+            }
+            l_run = l_run * alpha + sum;
+            m_run = m_new;
+            // P is read by the tensor core through the async proxy; S and O of block j-1 have been read
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(p_ready0 + 8 * h);
+
+            mbar_wait(o_ready0 + 8 * h, j & 1, 7);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tO + c0, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(acc[c0 + i], alpha, __uint_as_float(v[i]));
+            }
+        }
+
+        if (r < rows) {
+            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+            __nv_bfloat16* dst = out + (size_t)(qs + q0 + r) * out_stride + (size_t)(head_a + h) * HD;
+#pragma unroll
+            for (int d = 0; d < HD; d += 8) {
+                __nv_bfloat162 a = __floats2bfloat162_rn(acc[d] * inv, acc[d + 1] * inv), b = __floats2bfloat162_rn(acc[d + 2] * inv, acc[d + 3] * inv);
+                __nv_bfloat162 c = __floats2bfloat162_rn(acc[d + 4] * inv, acc[d + 5] * inv), e = __floats2bfloat162_rn(acc[d + 6] * inv, acc[d + 7] * inv);
+                uint4 o;
+                o.x = *reinterpret_cast<uint32_t*>(&a); o.y = *reinterpret_cast<uint32_t*>(&b);
+                o.z = *reinterpret_cast<uint32_t*>(&c); o.w = *reinterpret_cast<uint32_t*>(&e);
+                *reinterpret_cast<uint4*>(dst + d) = o;
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 9) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+template <int HD>
+static int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const int* bt, int max_blocks,
+                             const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_q0, int num_tiles,
+                             void* out, long out_stride, int nq, int nkv, int page_size, int window, float scale, int cache_rows,
+                             cudaStream_t stream) {
+    auto kern = prefill_tc_kernel<HD>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PtShape<HD>::SMEM) != cudaSuccess) return AIEN_E_STATE;
+        configured = true;
+    }
+    const int group = nq / nkv, pairs = (group + 1) / 2;
+    const long ctas = (long)num_tiles * nkv * pairs;
+    if (ctas > 2147483647L) return AIEN_E_SHAPE;
+    kern<<<(unsigned)ctas, PT_THREADS, PtShape<HD>::SMEM, stream>>>(mq, mk, mv, bt, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles,
+                                                                     (__nv_bfloat16*)out, out_stride, nq, nkv, page_size, window,
+                                                                     scale * 1.4426950408889634f, cache_rows);
+    return launch_status();
+}
+
+}  // namespace aien
+
+using namespace aien;
+
+// Whether aien_paged_attention_prefill_tc takes these sizes (1) or the caller must use the
+// mma.sync kernel (0).
+AIEN_API int aien_paged_attention_prefill_tc_supports(int hd, int page_size) {
+    return ((hd == 64 || hd == 128) && page_size >= 8 && page_size <= 128 && (page_size & 7) == 0 && 128 % page_size == 0) ? 1 : 0;
+}
+
+// q [q_rows, nq*hd] (leading dimension q_stride), k_cache/v_cache [cache_rows, nkv*hd] contiguous;
+// the other arguments as aien_paged_attention_prefill.
+AIEN_API int aien_paged_attention_prefill_tc(
+    const void* q, long q_stride, int q_rows, const void* k_cache, const void* v_cache, int cache_rows, const int* block_table,
+    int max_blocks, const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_q0, int num_tiles, void* out,
+    long out_stride, int nq, int nkv, int hd, int page_size, int window, float scale, cudaStream_t stream) {
+    if (num_tiles <= 0) return 0;
+    if (!aien_paged_attention_prefill_tc_supports(hd, page_size) || nkv <= 0 || nq % nkv != 0 || q_rows <= 0 || cache_rows <= 0)
+        return AIEN_E_SHAPE;
+    if ((q_stride & 7) || (out_stride & 7) || ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) ||
+        ((uintptr_t)out & 15))
+        return AIEN_E_ALIGN;
+    CUtensorMap mq, mk, mv;
+    const uint64_t kv_cols = (uint64_t)nkv * hd;
+    if (!make_map(&mq, q, (uint64_t)q_rows, (uint64_t)nq * hd, (uint64_t)q_stride, 64, PT_BM) ||
+        !make_map(&mk, k_cache, (uint64_t)cache_rows, kv_cols, kv_cols, 64, (uint32_t)page_size) ||
+        !make_map(&mv, v_cache, (uint64_t)cache_rows, kv_cols, kv_cols, 64, (uint32_t)page_size))
+        return AIEN_E_STATE;
+    if (hd == 64)
+        return launch_prefill_tc<64>(mq, mk, mv, block_table, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles, out, out_stride,
+                                     nq, nkv, page_size, window, scale, cache_rows, stream);
+    return launch_prefill_tc<128>(mq, mk, mv, block_table, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles, out, out_stride,
+                                  nq, nkv, page_size, window, scale, cache_rows, stream);
+}
+
+// Reads and clears the code a bounded wait may have left (0: none; 1 producer, 2 K/V block,
+// 3 query tile, 4/5 probabilities of head A/B, 6 scores, 7 block product).
+AIEN_API int aien_attention_prefill_tc_error(void) {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_wait_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(g_wait_error, &zero, sizeof(int));
+    return v;
+}

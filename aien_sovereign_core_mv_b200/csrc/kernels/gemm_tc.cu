@@ -18,43 +18,13 @@
 // Every wait is bounded: after the limit the kernel records an error code and goes on without
 // hanging; the host reads the code with aien_gemm_tc_error().
 #include "tma.cuh"
+#include "umma.cuh"
 
 namespace aien {
 
 constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64, TC_STAGES = 3;
 constexpr int TC_STAGE_A = TC_BM * TC_BK * 2, TC_STAGE_B = TC_BN * TC_BK * 2;
 constexpr int TC_SMEM = TC_STAGES * (TC_STAGE_A + TC_STAGE_B) + 1024 /*align*/ + 256 /*barriers*/;
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_c, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t r[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr));
-}
-
-// Shared-memory matrix descriptor of a K-major operand tile whose rows are 128 bytes, 128-byte
-// swizzled (what TMA writes with SWIZZLE_128B): start address and strides in 16-byte units,
-// 1024 bytes between groups of 8 rows, descriptor version 1, layout code 2.
-__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // bits  0-13  start address
-    d |= (uint64_t)1 << 16;                               // bits 16-29  leading byte offset (unused with swizzle)
-    d |= (uint64_t)(1024 >> 4) << 32;                     // bits 32-45  stride byte offset
-    d |= (uint64_t)1 << 46;                               // bits 46-47  version
-    d |= (uint64_t)2 << 61;                               // bits 61-63  SWIZZLE_128B
-    return d;
-}
 
 // EPI 0: store; EPI 1: silu(gate)*up over columns interleaved in runs of 8 (out has N/2 columns)
 template <int EPI, typename TC>

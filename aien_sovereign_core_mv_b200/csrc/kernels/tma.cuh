@@ -32,9 +32,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait: gives up after TC_SPIN_LIMIT polls, records `code`, and lets the caller go on.
+// Once a wait has given up, the others give up after 2^20 polls (far longer than any wait of a
+// working pipeline), so a broken pipeline drains sixteen times faster than one limit per wait.
 __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int code) {
-    for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i)
+    for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return;
+        if ((i & 0xFFFFFu) == 0xFFFFFu && *reinterpret_cast<volatile int*>(&g_wait_error) != 0) return;
+    }
     atomicCAS(&g_wait_error, 0, code);
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {

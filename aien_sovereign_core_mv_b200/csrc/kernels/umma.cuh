@@ -1,0 +1,58 @@
+// tcgen05 helpers shared by the kernels that run on the fifth-generation tensor cores: the MMA
+// issue, its commit to an mbarrier, tensor-memory loads and the shared-memory matrix descriptors.
+#pragma once
+#include "common.cuh"
+
+namespace aien {
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_c, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t r[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+}
+
+// Shared-memory matrix descriptor of a K-major operand tile whose rows are 128 bytes, 128-byte
+// swizzled (what TMA writes with SWIZZLE_128B): start address and strides in 16-byte units,
+// 1024 bytes between groups of 8 rows, descriptor version 1, layout code 2.
+__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // bits  0-13  start address
+    d |= (uint64_t)1 << 16;                               // bits 16-29  leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                     // bits 32-45  stride byte offset
+    d |= (uint64_t)1 << 46;                               // bits 46-47  version
+    d |= (uint64_t)2 << 61;                               // bits 61-63  SWIZZLE_128B
+    return d;
+}
+
+// The same for an operand whose contiguous direction is M or N instead of K (a "MN-major" tile):
+// rows of 128 bytes hold 64 consecutive M/N indices of one K index, 8 K indices form one swizzle
+// atom of 1024 bytes, `lbo_bytes` lies between one block of 64 M/N indices and the next.
+__device__ __forceinline__ uint64_t make_desc_sw128_mn(uint32_t smem_addr, uint32_t lbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor of a bfloat16 x bfloat16 -> float32 product of shape M x N x 16;
+// b_mn_major: the B tile is contiguous along N.
+__device__ __forceinline__ uint32_t umma_idesc_bf16(int M, int N, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+}  // namespace aien

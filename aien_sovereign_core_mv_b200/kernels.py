@@ -61,7 +61,10 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_gemm_tc": [P, L, P, L, P, I, L, I, I, I, I, I, c_size_t, P],
         "aien_gemm_tc_ranges": [I, I],
         "aien_gemm_tc_error": [],
+        "aien_attention_prefill_tc_error": [],
         "aien_paged_attention_prefill": [P, L, P, P, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P],
+        "aien_paged_attention_prefill_tc": [P, L, I, P, P, I, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P],
+        "aien_paged_attention_prefill_tc_supports": [I, I],
         "aien_paged_attention_decode": [P, L, P, P, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, P],
         "aien_paged_attention_decode_fused": [P, L, P, L, P, L, P, P, I, F, P, P, I, P, P, P, P, I, P, P, L, P, P, P,
                                               I, I, I, I, I, F, I, I, P],
@@ -505,17 +508,39 @@ def prefill_attention_supports(q: torch.Tensor, k_cache: torch.Tensor, out: torc
             and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0)
 
 
+_PREFILL_IMPL = __import__("os").environ.get("AIEN_B200_PREFILL", "tc").strip().lower()     # "tc" | "mma"
+
+
+def prefill_tc_supports(q, out, head_dim: int, page_size: int) -> bool:
+    """Whether the tcgen05 prefill kernel takes this case (head size 64 or 128, pages that divide 128)."""
+    return (bool(lib().aien_paged_attention_prefill_tc_supports(head_dim, page_size)) and q.stride(0) % 8 == 0
+            and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
+
+
 def paged_attention_prefill(q, k_cache, v_cache, block_table, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles,
-                            out, num_q_heads, num_kv_heads, head_dim, page_size, window, scale) -> None:
+                            out, num_q_heads, num_kv_heads, head_dim, page_size, window, scale, impl: Optional[str] = None) -> None:
     """Causal attention of portions of prompts over their requests' pages (bfloat16, tensor
-    cores).  ``tile_seq``/``tile_q0``: for every 64-token query tile, the index of its request in
-    the step and the tile's offset inside that request's portion."""
+    cores).  ``tile_seq``/``tile_q0``: for every 128-token query tile, the index of its request in
+    the step and the tile's offset inside that request's portion.  ``impl``: "tc" (tcgen05, where
+    the sizes allow) or "mma" (mma.sync); default from ``AIEN_B200_PREFILL``, else "tc"."""
     _dev(q, k_cache, v_cache, block_table, q_start, ctx_len, tile_seq, tile_q0, out)
     assert q.stride(1) == 1 and out.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous()
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
     for t in (block_table, q_start, ctx_len, tile_seq, tile_q0):
         assert t.dtype == torch.int32
+    impl = impl or _PREFILL_IMPL
+    if impl == "tc" and prefill_tc_supports(q, out, head_dim, page_size):
+        _check(lib().aien_paged_attention_prefill_tc(
+            _p(q), q.stride(0), q.shape[0], _p(k_cache), _p(v_cache), k_cache.shape[0], _p(block_table), max_blocks, _p(q_start),
+            _p(ctx_len), _p(tile_seq), _p(tile_q0), num_tiles, _p(out), out.stride(0), num_q_heads, num_kv_heads, head_dim,
+            page_size, window, float(scale), _stream()), "paged_attention_prefill_tc")
+        return
     _check(lib().aien_paged_attention_prefill(
         _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), max_blocks, _p(q_start), _p(ctx_len), _p(tile_seq),
         _p(tile_q0), num_tiles, _p(out), out.stride(0), num_q_heads, num_kv_heads, head_dim, page_size, window,
         float(scale), _stream()), "paged_attention_prefill")
+
+
+def attention_prefill_tc_error() -> int:
+    """Code left by a wait that ran out in the tcgen05 prefill attention kernel (0: none)."""
+    return int(lib().aien_attention_prefill_tc_error())

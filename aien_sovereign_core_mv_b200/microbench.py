@@ -3,7 +3,7 @@
     python -m aien_sovereign_core_mv_b200.microbench gemv --n 24576 --k 4096 --m 1 --epilogue 1
     python -m aien_sovereign_core_mv_b200.microbench gemm --m 2048 --n 24576 --k 4096 --epilogue 1
     python -m aien_sovereign_core_mv_b200.microbench attn-decode --batch 1 --ctx 1030
-    python -m aien_sovereign_core_mv_b200.microbench attn-prefill --tokens 2048
+    python -m aien_sovereign_core_mv_b200.microbench attn-prefill --tokens 2048 --impl tc
     python -m aien_sovereign_core_mv_b200.microbench all
 
 Every case launches its kernel a few times eagerly (what a profiler captures) and then times a
@@ -92,7 +92,8 @@ def attn_decode_case(batch: int, ctx: int, nq: int = 32, nkv: int = 8, hd: int =
     print(f"attn-decode batch={batch} ctx={ctx} ({nq}q/{nkv}kv x {hd}): {us:8.2f} us  {mb:.1f} MB of K/V  {mb / us * 1e3:7.0f} GB/s", flush=True)
 
 
-def attn_prefill_case(tokens: int, offset: int = 0, nq: int = 32, nkv: int = 8, hd: int = 128, page: int = 16, reps: int = 10) -> None:
+def attn_prefill_case(tokens: int, offset: int = 0, nq: int = 32, nkv: int = 8, hd: int = 128, page: int = 16, reps: int = 10,
+                      impl: str = "tc") -> None:
     ctx = offset + tokens
     kc, vc, bt, width = _paged_cache(1, ctx, nkv, hd, page)
     q = torch.randn(tokens, nq * hd, device="cuda", dtype=torch.bfloat16)
@@ -102,13 +103,14 @@ def attn_prefill_case(tokens: int, offset: int = 0, nq: int = 32, nkv: int = 8, 
     args = (i32([0, tokens]), i32([ctx]), i32([0] * n_tiles), i32([t * K.PREFILL_TILE for t in range(n_tiles)]), n_tiles)
 
     def run(_=0):
-        K.paged_attention_prefill(q, kc, vc, bt, width, *args, out, nq, nkv, hd, page, 0, 1 / math.sqrt(hd))
+        K.paged_attention_prefill(q, kc, vc, bt, width, *args, out, nq, nkv, hd, page, 0, 1 / math.sqrt(hd), impl=impl)
 
     for _ in range(3):
         run()
     us = _time_graph(run, reps)
     flops = 4.0 * nq * hd * (tokens * (tokens + 1) / 2 + tokens * offset)
-    print(f"attn-prefill tokens={tokens} offset={offset} ({nq}q/{nkv}kv x {hd}): {us:8.1f} us  {flops / us / 1e6:7.1f} TFLOP/s", flush=True)
+    print(f"attn-prefill[{impl}] tokens={tokens} offset={offset} ({nq}q/{nkv}kv x {hd}): {us:8.1f} us  {flops / us / 1e6:7.1f} TFLOP/s"
+          f"  (error flag {K.attention_prefill_tc_error()})", flush=True)
 
 
 def main(argv=None) -> int:
@@ -124,6 +126,7 @@ def main(argv=None) -> int:
     p.add_argument("--batch", type=int, default=1); p.add_argument("--ctx", type=int, default=1030)
     p = sub.add_parser("attn-prefill")
     p.add_argument("--tokens", type=int, default=2048); p.add_argument("--offset", type=int, default=0)
+    p.add_argument("--impl", default="tc", choices=["tc", "mma"])
     sub.add_parser("all")
     args = ap.parse_args(argv)
     K.lib()
@@ -134,7 +137,7 @@ def main(argv=None) -> int:
     elif args.case == "attn-decode":
         attn_decode_case(args.batch, args.ctx)
     elif args.case == "attn-prefill":
-        attn_prefill_case(args.tokens, args.offset)
+        attn_prefill_case(args.tokens, args.offset, impl=args.impl)
     else:
         shapes = {"qkv": (6144, 4096, 0), "o": (4096, 4096, 0), "gate_up": (24576, 4096, 1), "down": (4096, 12288, 0), "head": (151936, 4096, 0)}
         for m in (1, 8, 16):
@@ -148,7 +151,8 @@ def main(argv=None) -> int:
             attn_decode_case(b, 1030)
         attn_decode_case(16, 8192)
         for t, off in ((2048, 0), (512, 1536), (8192, 0)):
-            attn_prefill_case(t, off)
+            for impl in ("tc", "mma"):
+                attn_prefill_case(t, off, impl=impl)
     return 0
 
 

@@ -455,12 +455,9 @@ def test_gemm_tensor_core_swiglu_epilogue(K):
 PREFILL_CASES = [(4, 2, 16, 16, 0), (6, 3, 48, 8, 0), (5, 1, 80, 16, 0), (8, 2, 128, 16, 0), (3, 3, 32, 4, 21), (8, 4, 64, 16, 40), (2, 1, 112, 32, 100)]
 
 
-@pytest.mark.parametrize("nq,nkv,hd,page,window", PREFILL_CASES)
-def test_paged_attention_prefill(K, nq, nkv, hd, page, window):
+def _prefill_case(K, nq, nkv, hd, page, window, seq_lens, q_lens, impl):
     dtype = torch.bfloat16
-    rng = np.random.default_rng(nq * 31 + hd)
-    seq_lens = [130, 64, 300, 5, 200]                 # context after the step
-    q_lens = [130, 1, 77, 2, 128]                     # tokens the step brings: whole, decode, offset portion, 2, one full tile
+    rng = np.random.default_rng(nq * 31 + hd + len(seq_lens))
     kc, vc, bt, mb, dense = paged_setup(rng, seq_lens, nkv, hd, page, dtype, sum((n + page - 1) // page for n in seq_lens) + 8)
     seq_of, positions, q_start, tile_seq, tile_q0 = [], [], [0], [], []
     for s, (n, ql) in enumerate(zip(seq_lens, q_lens)):
@@ -474,14 +471,37 @@ def test_paged_attention_prefill(K, nq, nkv, hd, page, window):
     q = big[:, 32:32 + nq * hd]
     scale = 1.0 / math.sqrt(hd)
     i32 = lambda a: torch.tensor(a, dtype=torch.int32).cuda()
-    out = torch.empty(T, nq * hd, dtype=dtype, device="cuda")
+    out = torch.full((T, nq * hd), 7.0, dtype=dtype, device="cuda")
     K.paged_attention_prefill(q, kc, vc, bt, mb, i32(q_start), i32(seq_lens), i32(tile_seq), i32(tile_q0), len(tile_seq),
-                              out, nq, nkv, hd, page, window, scale)
+                              out, nq, nkv, hd, page, window, scale, impl=impl)
+    torch.cuda.synchronize()
+    assert K.attention_prefill_tc_error() == 0
     want = attention_reference(q.float().double().cpu().numpy().reshape(-1, nq, hd), dense, seq_of, positions, nq, nkv, hd, window, scale)
-    H.assert_close(out.float().cpu().numpy(), want, 1.5e-2, "prefill attention")
+    H.assert_close(out.float().cpu().numpy(), want, 1.5e-2, f"prefill attention ({impl})")
 
 
-def test_prefill_attention_one_far_key_decides(K):
+@pytest.mark.parametrize("nq,nkv,hd,page,window", PREFILL_CASES)
+def test_paged_attention_prefill(K, nq, nkv, hd, page, window):
+    # context after the step / tokens the step brings: whole, decode, offset portion, 2, one full tile
+    _prefill_case(K, nq, nkv, hd, page, window, [130, 64, 300, 5, 200], [130, 1, 77, 2, 128], "mma")
+
+
+# query heads, kv heads, head size, page, window: groups of 4, 2, 3 (a pair with one head) and 1; every page size
+PREFILL_TC_CASES = [(8, 2, 128, 16, 0), (8, 4, 64, 16, 40), (3, 1, 128, 8, 0), (2, 2, 64, 32, 0), (4, 1, 128, 64, 300),
+                    (6, 3, 64, 128, 0), (5, 5, 128, 16, 130)]
+
+
+@pytest.mark.parametrize("nq,nkv,hd,page,window", PREFILL_TC_CASES)
+def test_paged_attention_prefill_tensor_memory(K, nq, nkv, hd, page, window):
+    """The tcgen05 kernel: portions that start and end anywhere against key blocks of 128, more key
+    blocks than the shared-memory ring has slots, a single token, a portion of several tiles."""
+    assert K.prefill_tc_supports(torch.empty(1, nq * hd, dtype=torch.bfloat16, device="cuda"),
+                                 torch.empty(1, nq * hd, dtype=torch.bfloat16, device="cuda"), hd, page)
+    _prefill_case(K, nq, nkv, hd, page, window, [130, 64, 300, 5, 200, 1000, 700], [130, 1, 77, 2, 128, 333, 700], "tc")
+
+
+@pytest.mark.parametrize("impl", ["mma", "tc"])
+def test_prefill_attention_one_far_key_decides(K, impl):
     nq, nkv, hd, page, n = 2, 1, 64, 16, 700
     for far in (0, 63, 64, 303, 636):
         pages = (n + page - 1) // page
@@ -498,7 +518,7 @@ def test_prefill_attention_one_far_key_decides(K):
         out = torch.empty(ql, nq * hd, dtype=torch.bfloat16, device="cuda")
         K.paged_attention_prefill(q.to(torch.bfloat16).cuda(), kc.to(torch.bfloat16).cuda(), vc.to(torch.bfloat16).cuda(),
                                   torch.tensor(bt).cuda(), pages + 2, i32([0, ql]), i32([n]), i32([0]), i32([0]), 1,
-                                  out, nq, nkv, hd, page, 0, 1.0 / math.sqrt(hd))
+                                  out, nq, nkv, hd, page, 0, 1.0 / math.sqrt(hd), impl=impl)
         got = out.float().cpu().numpy()
         assert np.abs(got - far / 8.0).max() <= max(1e-2, 0.01 * far / 8.0), (far, got[0, :4], got[-1, :4])
 
