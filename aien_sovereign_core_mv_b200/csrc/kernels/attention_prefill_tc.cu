@@ -14,13 +14,15 @@
 //   warp 9      allocates tensor memory; one lane issues tcgen05.mma
 // Per block of 128 keys (aligned to absolute positions) and per head:
 //   S = Q K^T         M 128 x N 128 x K head size; Q and K are K-major tiles; S in tensor memory
-//   softmax           each thread reads its row of S with tcgen05.ld twice (maximum, then
-//                     exponentials in float32 with the causal/window limits of its row), writes
-//                     P as bfloat16 into a swizzled K-major tile in shared memory
-//   O_blk = P V       M 128 x N head size x K 128; V is used as stored ([key][dim]: an MN-major
-//                     tile); the block's product lands in tensor memory and the row's thread
-//                     adds it to its float32 accumulator in registers, rescaled by the running
-//                     maximum, so nothing in tensor memory ever needs rescaling
+//   softmax           each thread reads its row of S with tcgen05.ld, applies the causal/window
+//                     limits of its row, takes exponentials in float32 and writes P as bfloat16
+//                     into a swizzled K-major tile in shared memory
+//   O += P V          M 128 x N head size x K 128; V is used as stored ([key][dim]: an MN-major
+//                     tile); O accumulates in tensor memory over all blocks.  The exponentials
+//                     are taken against a reference maximum that follows the row's running
+//                     maximum only when that has grown by more than 8 (in log2 units); only then
+//                     is the row of O rescaled (tcgen05.ld, multiply, tcgen05.st), which after
+//                     the first blocks is rare
 // The issue order alternates the heads (PV_A(j), QK_A(j+1), PV_B(j), QK_B(j+1)), so that the
 // tensor core works for one head while the other head's softmax runs.
 // Formulas: crates/aien-inference-abi/src/backend.rs:280-306, scale 1/sqrt(head_dim).
@@ -107,7 +109,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot_ptr;
-    // tensor-memory columns: S of head A, S of head B, then the block products O of A and of B
+    // tensor-memory columns: S of head A, S of head B, then the outputs O of A and of B
     const uint32_t tS0 = tmem, tO0 = tmem + 2 * PT_BN;
 
     if (warp == 8) {
@@ -152,12 +154,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 }
                 umma_commit(s_ready0 + 8 * h);
             };
-            auto issue_pv = [&](int h, int slot) {
+            auto issue_pv = [&](int h, int slot, bool first_block) {
                 const uint32_t a = sP + h * S::P_BYTES, b = sKV + slot * S::SLOT_BYTES;
 #pragma unroll
                 for (int kk = 0; kk < PT_BN / 16; ++kk) {
                     const uint32_t off = (kk >> 2) * (PT_BM * 128) + (kk & 3) * 32;
-                    umma_bf16(tO0 + h * HD, make_desc_sw128(a + off), make_desc_sw128_mn(b + kk * 16 * 128, PT_BN * 128), idesc_pv, kk > 0 ? 1u : 0u);
+                    umma_bf16(tO0 + h * HD, make_desc_sw128(a + off), make_desc_sw128_mn(b + kk * 16 * 128, PT_BN * 128), idesc_pv, (kk > 0 || !first_block) ? 1u : 0u);
                 }
                 umma_commit(o_ready0 + 8 * h);
             };
@@ -175,12 +177,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 const bool more = j + 1 < nb;
                 mbar_wait(p_ready0, j & 1, 4);
                 wait_item(v_item);
-                issue_pv(0, v_item % S::SLOTS);
+                issue_pv(0, v_item % S::SLOTS, j == 0);
                 if (more) { wait_item(k_item); issue_qk(0, k_item % S::SLOTS); }
                 if (has_b) {
                     mbar_wait(p_ready0 + 8, j & 1, 5);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    issue_pv(1, v_item % S::SLOTS);
+                    issue_pv(1, v_item % S::SLOTS, j == 0);
                 }
                 umma_commit(kv_free0 + 8 * (v_item % S::SLOTS));
                 if (more) {
@@ -190,7 +192,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             }
         }
     } else if (warp < 4 || has_b) {
-        // ------------------------------------------------------------------ softmax and accumulation
+        // ------------------------------------------------------------------ softmax
         const int h = warp >> 2, quarter = warp & 3;
         const int r = quarter * 32 + lane;
         const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
@@ -198,95 +200,101 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const uint32_t p_row = sP + h * S::P_BYTES + r * 128;
         const int hi = r < rows ? pos0 + r : -1;                                 // last key this row sees
         const int lo = (window > 0 && hi - window + 1 > 0) ? hi - window + 1 : 0;
-        float acc[HD];
-#pragma unroll
-        for (int d = 0; d < HD; ++d) acc[d] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f;
+        // m_ref: the maximum the exponentials are taken against.  It follows the row's running
+        // maximum only when that has grown by more than 8 (a factor 256, harmless in float32 and
+        // in bfloat16's exponent), so the output in tensor memory is rescaled rarely.
+        float m_ref = -INFINITY, l_run = 0.f;
 
         for (int j = 0; j < nb; ++j) {
             const int key_base = (kb_begin + j) * PT_BN;
             mbar_wait(s_ready0 + 8 * h, j & 1, 6);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const bool masked = key_base + PT_BN - 1 > hi || key_base < lo;
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c0 = 0; c0 < PT_BN; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld32(tS + c0, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (masked) {
+            uint32_t v[PT_BN];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int key = key_base + c0 + i;
-                        if (key >= lo && key <= hi) mx = fmaxf(mx, __uint_as_float(v[i]));
-                    }
-                } else {
+            for (int c0 = 0; c0 < PT_BN; c0 += 32) tmem_ld32(tS + c0, v + c0);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (key_base + PT_BN - 1 > hi || key_base < lo) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+                for (int i = 0; i < PT_BN; ++i) {
+                    const int key = key_base + i;
+                    if (key < lo || key > hi) v[i] = 0xff800000u;                // -inf
                 }
             }
-            const float m_new = fmaxf(m_run, mx * scale_log2e);
-            const float alpha = (m_run == -INFINITY) ? 0.f : ex2_approx(m_run - m_new);
-            const float neg_base = (m_new == -INFINITY) ? 0.f : -m_new;
-            float sum = 0.f;
-#pragma unroll 1
-            for (int c0 = 0; c0 < PT_BN; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld32(tS + c0, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                float p[32];
+            float mx = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float sc = __uint_as_float(v[i]);
-                    if (masked) {
-                        const int key = key_base + c0 + i;
-                        if (key < lo || key > hi) sc = -INFINITY;
+            for (int i = 0; i < PT_BN; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+            mx *= scale_log2e;
+            if (j == 0) {
+                m_ref = mx;
+            } else {
+                const bool grow = mx > m_ref + 8.0f;
+                if (__any_sync(0xffffffffu, grow)) {
+                    // the block product of j-1 must have landed before the output is touched
+                    mbar_wait(o_ready0 + 8 * h, (j - 1) & 1, 7);
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    float f = 1.0f;
+                    if (grow) {
+                        f = (m_ref == -INFINITY) ? 0.f : ex2_approx(m_ref - mx);
+                        m_ref = mx;
+                        l_run *= f;
                     }
-                    p[i] = ex2_approx(fmaf(sc, scale_log2e, neg_base));          // exp2(-inf) = 0 for masked keys
+#pragma unroll 1
+                    for (int c0 = 0; c0 < HD; c0 += 32) {
+                        uint32_t o[32];
+                        tmem_ld32(tO + c0, o);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                        tmem_st32(tO + c0, o);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                }
+            }
+            const float neg_base = (m_ref == -INFINITY) ? 0.f : -m_ref;
+            float sum = 0.f;
+#pragma unroll
+            for (int c0 = 0; c0 < PT_BN; c0 += 8) {
+                float p[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    p[i] = ex2_approx(fmaf(__uint_as_float(v[c0 + i]), scale_log2e, neg_base));   // exp2(-inf) = 0 for masked keys
                     sum += p[i];
                 }
-                const uint32_t chunk_base = p_row + (c0 >> 6) * (PT_BM * 128);
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    const int unit = ((c0 & 63) >> 3) + t;
-                    const uint32_t addr = chunk_base + (uint32_t)((unit ^ (r & 7)) << 4);
-                    __nv_bfloat162 a = __floats2bfloat162_rn(p[8 * t + 0], p[8 * t + 1]), b = __floats2bfloat162_rn(p[8 * t + 2], p[8 * t + 3]);
-                    __nv_bfloat162 c = __floats2bfloat162_rn(p[8 * t + 4], p[8 * t + 5]), d = __floats2bfloat162_rn(p[8 * t + 6], p[8 * t + 7]);
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(*reinterpret_cast<uint32_t*>(&a)),
-                                 "r"(*reinterpret_cast<uint32_t*>(&b)), "r"(*reinterpret_cast<uint32_t*>(&c)),
-                                 "r"(*reinterpret_cast<uint32_t*>(&d)) : "memory");
-                }
+                const uint32_t addr = p_row + (c0 >> 6) * (PT_BM * 128) + (uint32_t)(((((c0 & 63) >> 3)) ^ (r & 7)) << 4);
+                __nv_bfloat162 a = __floats2bfloat162_rn(p[0], p[1]), b = __floats2bfloat162_rn(p[2], p[3]);
+                __nv_bfloat162 c = __floats2bfloat162_rn(p[4], p[5]), d = __floats2bfloat162_rn(p[6], p[7]);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(*reinterpret_cast<uint32_t*>(&a)),
+                             "r"(*reinterpret_cast<uint32_t*>(&b)), "r"(*reinterpret_cast<uint32_t*>(&c)),
+                             "r"(*reinterpret_cast<uint32_t*>(&d)) : "memory");
             }
-            l_run = l_run * alpha + sum;
-            m_run = m_new;
-            // P is read by the tensor core through the async proxy; S and O of block j-1 have been read
+            l_run += sum;
+            // P is read by the tensor core through the async proxy
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(p_ready0 + 8 * h);
-
-            mbar_wait(o_ready0 + 8 * h, j & 1, 7);
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int c0 = 0; c0 < HD; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld32(tO + c0, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(acc[c0 + i], alpha, __uint_as_float(v[i]));
-            }
         }
 
-        if (r < rows) {
-            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-            __nv_bfloat16* dst = out + (size_t)(qs + q0 + r) * out_stride + (size_t)(head_a + h) * HD;
+        mbar_wait(o_ready0 + 8 * h, (nb - 1) & 1, 7);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+        __nv_bfloat16* dst = out + (size_t)(qs + q0 + (r < rows ? r : 0)) * out_stride + (size_t)(head_a + h) * HD;
+#pragma unroll 1
+        for (int c0 = 0; c0 < HD; c0 += 32) {
+            uint32_t o[32];
+            tmem_ld32(tO + c0, o);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (r < rows) {
 #pragma unroll
-            for (int d = 0; d < HD; d += 8) {
-                __nv_bfloat162 a = __floats2bfloat162_rn(acc[d] * inv, acc[d + 1] * inv), b = __floats2bfloat162_rn(acc[d + 2] * inv, acc[d + 3] * inv);
-                __nv_bfloat162 c = __floats2bfloat162_rn(acc[d + 4] * inv, acc[d + 5] * inv), e = __floats2bfloat162_rn(acc[d + 6] * inv, acc[d + 7] * inv);
-                uint4 o;
-                o.x = *reinterpret_cast<uint32_t*>(&a); o.y = *reinterpret_cast<uint32_t*>(&b);
-                o.z = *reinterpret_cast<uint32_t*>(&c); o.w = *reinterpret_cast<uint32_t*>(&e);
-                *reinterpret_cast<uint4*>(dst + d) = o;
+                for (int d = 0; d < 32; d += 8) {
+                    __nv_bfloat162 a = __floats2bfloat162_rn(__uint_as_float(o[d]) * inv, __uint_as_float(o[d + 1]) * inv);
+                    __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(o[d + 2]) * inv, __uint_as_float(o[d + 3]) * inv);
+                    __nv_bfloat162 c = __floats2bfloat162_rn(__uint_as_float(o[d + 4]) * inv, __uint_as_float(o[d + 5]) * inv);
+                    __nv_bfloat162 e = __floats2bfloat162_rn(__uint_as_float(o[d + 6]) * inv, __uint_as_float(o[d + 7]) * inv);
+                    uint4 w;
+                    w.x = *reinterpret_cast<uint32_t*>(&a); w.y = *reinterpret_cast<uint32_t*>(&b);
+                    w.z = *reinterpret_cast<uint32_t*>(&c); w.w = *reinterpret_cast<uint32_t*>(&e);
+                    *reinterpret_cast<uint4*>(dst + c0 + d) = w;
+                }
             }
         }
     }

@@ -500,6 +500,39 @@ def test_paged_attention_prefill_tensor_memory(K, nq, nkv, hd, page, window):
     _prefill_case(K, nq, nkv, hd, page, window, [130, 64, 300, 5, 200, 1000, 700], [130, 1, 77, 2, 128, 333, 700], "tc")
 
 
+def test_prefill_attention_growing_maximum(K):
+    """Scores that keep growing with the key position: every row's maximum rises block after
+    block, so the tensor-memory kernel must rescale its output again and again."""
+    nq, nkv, hd, page, n = 4, 2, 128, 16, 900
+    rng = np.random.default_rng(5)
+    pages = (n + page - 1) // page
+    perm = rng.permutation(pages + 3)
+    bt = np.full((1, pages + 1), -1, dtype=np.int32)
+    bt[0, :pages] = perm[:pages]
+    slots = bt[0, np.arange(n) // page] * page + np.arange(n) % page
+    k = torch.tensor(rng.standard_normal((n, nkv, hd)), dtype=torch.float32)
+    v = torch.tensor(rng.standard_normal((n, nkv, hd)), dtype=torch.float32)
+    k[:, :, 0] += torch.arange(n, dtype=torch.float32)[:, None] / 16.0
+    k, v = k.to(torch.bfloat16).float(), v.to(torch.bfloat16).float()
+    kc = torch.zeros((pages + 3) * page, nkv, hd); vc = torch.zeros_like(kc)
+    kc[slots] = k; vc[slots] = v
+    q = torch.tensor(rng.standard_normal((n, nq, hd)), dtype=torch.float32)
+    q[:, :, 0] = 6.0
+    q = q.to(torch.bfloat16).reshape(n, nq * hd)
+    tiles = (n + K.PREFILL_TILE - 1) // K.PREFILL_TILE
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32).cuda()
+    scale = 1.0 / math.sqrt(hd)
+    want = attention_reference(q.float().double().numpy().reshape(n, nq, hd), [(k, v)], [0] * n, list(range(n)), nq, nkv, hd, 0, scale)
+    for impl in ("tc", "mma"):
+        out = torch.empty(n, nq * hd, dtype=torch.bfloat16, device="cuda")
+        K.paged_attention_prefill(q.cuda(), kc.to(torch.bfloat16).cuda(), vc.to(torch.bfloat16).cuda(), torch.tensor(bt).cuda(), pages + 1,
+                                  i32([0, n]), i32([n]), i32([0] * tiles), i32([t * K.PREFILL_TILE for t in range(tiles)]), tiles,
+                                  out, nq, nkv, hd, page, 0, scale, impl=impl)
+        torch.cuda.synchronize()
+        assert K.attention_prefill_tc_error() == 0
+        H.assert_close(out.float().cpu().numpy(), want, 1.5e-2, f"prefill attention, growing maximum ({impl})")
+
+
 @pytest.mark.parametrize("impl", ["mma", "tc"])
 def test_prefill_attention_one_far_key_decides(K, impl):
     nq, nkv, hd, page, n = 2, 1, 64, 16, 700
