@@ -20,6 +20,7 @@
 //
 // Needs head_dim % 16 == 0 and <= 256, at most 16 query heads per kv head, bfloat16 q and cache.
 #include "common.cuh"
+#include "attention_decode_merge.cuh"
 #include <math.h>
 
 namespace aien {
@@ -103,7 +104,6 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
                               __nv_bfloat16* __restrict__ out, long out_stride,
                               int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int misc_bytes,
                               FusedQK fq) {
-    constexpr int DCH = (HS + 1) / 2;            // 64-dim chunks of the output
     constexpr int NH = NT * 8;
     extern __shared__ float smem[];
     __shared__ int s_slot[AD_CHUNK];
@@ -331,48 +331,8 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    // All loads of a phase are independent of one another, so a phase costs one round trip to L2.
-    const int nsp = s_hi - s_lo + 1;
-    float* Fm = smem;                                   // [nsp][NH]: chunk max, then the chunk's weight
-    float* Fl = Fm + (size_t)max_splits * NH;            // [nsp][NH]: chunk denominator
-    float* Fi = Fl + (size_t)max_splits * NH;            // [NH]: 1 / total denominator
-    for (int i = threadIdx.x; i < nsp * G; i += AD_WARPS * 32) {
-        const int sp = i / G, h = i - sp * G;
-        const size_t row = ((size_t)zt * nq + kvh * G + h) * max_splits + s_lo + sp;
-        Fm[sp * NH + h] = __ldcg(part_ml + row * 2);
-        Fl[sp * NH + h] = __ldcg(part_ml + row * 2 + 1);
-    }
-    __syncthreads();
-    if (threadIdx.x < G) {
-        const int h = threadIdx.x;
-        float M = -INFINITY;
-        for (int sp = 0; sp < nsp; ++sp) M = fmaxf(M, Fm[sp * NH + h]);
-        float L = 0.f;
-        for (int sp = 0; sp < nsp; ++sp) {
-            const float ms = Fm[sp * NH + h];
-            const float f = ms == -INFINITY ? 0.f : expf(ms - M);
-            L += Fl[sp * NH + h] * f;
-            Fm[sp * NH + h] = f;
-        }
-        Fi[h] = L > 0.f ? 1.0f / L : 0.f;
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < G * hd; idx += AD_WARPS * 32) {
-        const int h = idx / hd, d = idx - h * hd;
-        const float* src = part_out + (((size_t)zt * nq + kvh * G + h) * max_splits + s_lo) * hd + d;
-        float o = 0.f;
-        int sp = 0;
-        for (; sp + 4 <= nsp; sp += 4) {
-            const float v0 = __ldcg(src + (size_t)(sp + 0) * hd), v1 = __ldcg(src + (size_t)(sp + 1) * hd);
-            const float v2 = __ldcg(src + (size_t)(sp + 2) * hd), v3 = __ldcg(src + (size_t)(sp + 3) * hd);
-            o += v0 * Fm[(sp + 0) * NH + h];
-            o += v1 * Fm[(sp + 1) * NH + h];
-            o += v2 * Fm[(sp + 2) * NH + h];
-            o += v3 * Fm[(sp + 3) * NH + h];
-        }
-        for (; sp < nsp; ++sp) o += __ldcg(src + (size_t)sp * hd) * Fm[sp * NH + h];
-        out[(size_t)t * out_stride + (size_t)(kvh * G + h) * hd + d] = __float2bfloat16_rn(o * Fi[h]);
-    }
+    ad_merge_chunks<NH>(smem, part_out, part_ml, out + (size_t)t * out_stride + (size_t)kvh * G * hd, (size_t)zt * nq + kvh * G,
+                        G, hd, max_splits, s_lo, s_hi - s_lo + 1, threadIdx.x, AD_WARPS * 32, [] { __syncthreads(); });
 }
 
 template <int HS, int NT>
@@ -381,7 +341,7 @@ static int launch_decode(const void* q, long q_stride, const void* kc, const voi
                          void* out, long out_stride,
                          int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T,
                          const FusedQK& fq, cudaStream_t stream) {
-    const int G = nq / nkv, NH = NT * 8;
+    const int NH = NT * 8;
     size_t loop_bytes = ((size_t)AD_CHUNK * NH + 2 * NH) * 4 + (size_t)NH * AD_CHUNK * 2;          // scores, max/denominator, probabilities
     if (fq.k != nullptr) loop_bytes += (size_t)AD_WARPS * 256 * 4 + (size_t)NH * hd * 2 + 16;      // fused q/k scratch, q
     const size_t comb_bytes = 0;

@@ -66,6 +66,9 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_paged_attention_prefill_tc": [P, L, I, P, P, I, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P],
         "aien_paged_attention_prefill_tc_supports": [I, I],
         "aien_paged_attention_decode": [P, L, P, P, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, P],
+        "aien_paged_attention_decode_stream": [P, L, P, P, I, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, P],
+        "aien_paged_attention_decode_stream_supports": [I, I, I, I, I],
+        "aien_attention_decode_stream_error": [],
         "aien_paged_attention_decode_fused": [P, L, P, L, P, L, P, P, I, F, P, P, I, P, P, P, P, I, P, P, L, P, P, P,
                                               I, I, I, I, I, F, I, I, P],
     }
@@ -403,11 +406,21 @@ def attention_workspace_bytes(lim, num_heads: int, head_dim: int) -> int:
 _ticket_counters: Optional[torch.Tensor] = None
 
 
+_DECODE_ATTN_IMPL = __import__("os").environ.get("AIEN_B200_DECODE_ATTENTION", "stream").strip().lower()     # "stream" | "direct"
+
+
+def decode_stream_supports(num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, max_splits: int) -> bool:
+    """Whether the streamed decode attention kernel takes this case (head size 64 or 128, pages that divide 128)."""
+    return bool(lib().aien_paged_attention_decode_stream_supports(num_q_heads, num_kv_heads, head_dim, page_size, max_splits))
+
+
 def paged_attention_decode(q, k_cache, v_cache, block_table, max_blocks, seq_of_token, positions, out,
                            part_out, part_ml, num_q_heads, num_kv_heads, head_dim, page_size, window, scale,
-                           max_splits, token_list=None, num_tokens=None) -> None:
+                           max_splits, token_list=None, num_tokens=None, impl: Optional[str] = None) -> None:
     """Split-key decode attention; the CTA that finishes last merges the chunks.  The ticket
-    counters are one small device buffer that every launch finds zero and leaves zero."""
+    counters are one small device buffer that every launch finds zero and leaves zero.
+    ``impl``: "stream" (TMA ring, persistent CTAs; where the sizes allow) or "direct" (one CTA per
+    chunk); both give the same bits.  Default from ``AIEN_B200_DECODE_ATTENTION``, else "stream"."""
     global _ticket_counters
     _dev(q, k_cache, v_cache, block_table, seq_of_token, positions, out, part_out, part_ml)
     # seq_of_token None: token t belongs to row t of the block table.  token_list: serve only these tokens.
@@ -419,10 +432,22 @@ def paged_attention_decode(q, k_cache, v_cache, block_table, max_blocks, seq_of_
     assert q.stride(1) == 1 and out.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous()
     assert part_out.dtype == torch.float32 and part_out.numel() >= T * num_q_heads * max_splits * head_dim
     assert part_ml.dtype == torch.float32 and part_ml.numel() >= T * num_q_heads * max_splits * 2
+    impl = impl or _DECODE_ATTN_IMPL
+    if impl == "stream" and decode_stream_supports(num_q_heads, num_kv_heads, head_dim, page_size, max_splits):
+        _check(lib().aien_paged_attention_decode_stream(
+            _p(q), q.stride(0), _p(k_cache), _p(v_cache), k_cache.shape[0], _p(block_table), max_blocks, _p(seq_of_token),
+            _p(positions), _p(token_list), _p(out), out.stride(0), _p(part_out), _p(part_ml), _p(_ticket_counters), num_q_heads,
+            num_kv_heads, head_dim, page_size, window, float(scale), max_splits, T, _stream()), "paged_attention_decode_stream")
+        return
     _check(lib().aien_paged_attention_decode(
         _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), max_blocks, _p(seq_of_token), _p(positions),
         _p(token_list), _p(out), out.stride(0), _p(part_out), _p(part_ml), _p(_ticket_counters), num_q_heads, num_kv_heads, head_dim,
         page_size, window, float(scale), max_splits, T, _stream()), "paged_attention_decode")
+
+
+def attention_decode_stream_error() -> int:
+    """Code left by a wait that ran out in the streamed decode attention kernel (0: none)."""
+    return int(lib().aien_attention_decode_stream_error())
 
 
 def paged_attention_decode_fused(ctx, q, k, v, q_norm_w, k_norm_w, eps, cos, sin, rotary_dim, group, k_cache, v_cache, out,

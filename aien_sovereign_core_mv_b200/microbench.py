@@ -2,7 +2,7 @@
 
     python -m aien_sovereign_core_mv_b200.microbench gemv --n 24576 --k 4096 --m 1 --epilogue 1
     python -m aien_sovereign_core_mv_b200.microbench gemm --m 2048 --n 24576 --k 4096 --epilogue 1
-    python -m aien_sovereign_core_mv_b200.microbench attn-decode --batch 1 --ctx 1030
+    python -m aien_sovereign_core_mv_b200.microbench attn-decode --batch 1 --ctx 1030 --impl stream
     python -m aien_sovereign_core_mv_b200.microbench attn-prefill --tokens 2048 --impl tc
     python -m aien_sovereign_core_mv_b200.microbench all
 
@@ -71,7 +71,8 @@ def _paged_cache(batch: int, ctx: int, nkv: int, hd: int, page: int):
     return kc, vc, bt.cuda(), width
 
 
-def attn_decode_case(batch: int, ctx: int, nq: int = 32, nkv: int = 8, hd: int = 128, page: int = 16, reps: int = 40) -> None:
+def attn_decode_case(batch: int, ctx: int, nq: int = 32, nkv: int = 8, hd: int = 128, page: int = 16, reps: int = 40,
+                     impl: str = "stream") -> None:
     kc, vc, bt, width = _paged_cache(batch, ctx, nkv, hd, page)
     q = torch.randn(batch, nq * hd, device="cuda", dtype=torch.bfloat16)
     out = torch.empty_like(q)
@@ -83,13 +84,14 @@ def attn_decode_case(batch: int, ctx: int, nq: int = 32, nkv: int = 8, hd: int =
     pos = torch.full((batch,), ctx - 1, dtype=torch.int32, device="cuda")
 
     def run(_=0):
-        K.paged_attention_decode(q, kc, vc, bt, width, None, pos, out, po, pml, nq, nkv, hd, page, 0, 1 / math.sqrt(hd), splits)
+        K.paged_attention_decode(q, kc, vc, bt, width, None, pos, out, po, pml, nq, nkv, hd, page, 0, 1 / math.sqrt(hd), splits, impl=impl)
 
     for _ in range(3):
         run()
     us = _time_graph(run, reps)
     mb = batch * ctx * nkv * hd * 2 * 2 / 1e6
-    print(f"attn-decode batch={batch} ctx={ctx} ({nq}q/{nkv}kv x {hd}): {us:8.2f} us  {mb:.1f} MB of K/V  {mb / us * 1e3:7.0f} GB/s", flush=True)
+    print(f"attn-decode[{impl}] batch={batch} ctx={ctx} ({nq}q/{nkv}kv x {hd}): {us:8.2f} us  {mb:.1f} MB of K/V  {mb / us * 1e3:7.0f} GB/s"
+          f"  (error flag {K.attention_decode_stream_error()})", flush=True)
 
 
 def attn_prefill_case(tokens: int, offset: int = 0, nq: int = 32, nkv: int = 8, hd: int = 128, page: int = 16, reps: int = 10,
@@ -124,6 +126,7 @@ def main(argv=None) -> int:
     p.add_argument("--k", type=int, default=4096); p.add_argument("--epilogue", type=int, default=0)
     p = sub.add_parser("attn-decode")
     p.add_argument("--batch", type=int, default=1); p.add_argument("--ctx", type=int, default=1030)
+    p.add_argument("--impl", default="stream", choices=["stream", "direct"])
     p = sub.add_parser("attn-prefill")
     p.add_argument("--tokens", type=int, default=2048); p.add_argument("--offset", type=int, default=0)
     p.add_argument("--impl", default="tc", choices=["tc", "mma"])
@@ -135,7 +138,7 @@ def main(argv=None) -> int:
     elif args.case == "gemm":
         gemm_case(args.m, args.n, args.k, args.epilogue)
     elif args.case == "attn-decode":
-        attn_decode_case(args.batch, args.ctx)
+        attn_decode_case(args.batch, args.ctx, impl=args.impl)
     elif args.case == "attn-prefill":
         attn_prefill_case(args.tokens, args.offset, impl=args.impl)
     else:
@@ -147,9 +150,10 @@ def main(argv=None) -> int:
             for name, (n, k, epi) in shapes.items():
                 if name != "head":
                     gemm_case(m, n, k, epi)
-        for b in (1, 8, 64):
-            attn_decode_case(b, 1030)
-        attn_decode_case(16, 8192)
+        for impl in ("stream", "direct"):
+            for b in (1, 8, 64):
+                attn_decode_case(b, 1030, impl=impl)
+            attn_decode_case(16, 8192, impl=impl)
         for t, off in ((2048, 0), (512, 1536), (8192, 0)):
             for impl in ("tc", "mma"):
                 attn_prefill_case(t, off, impl=impl)

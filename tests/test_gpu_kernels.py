@@ -344,6 +344,50 @@ def test_paged_attention_decode(K, nq, nkv, hd, page, window):
     assert torch.equal(sub[some], out[some]) and (sub[[1, 3, 5]] == 3.0).all()
 
 
+# query heads, kv heads, head size, page, window, requests
+DECODE_STREAM_CASES = [(8, 2, 128, 16, 0, 6), (32, 8, 128, 16, 0, 40), (16, 1, 64, 8, 0, 5), (12, 4, 64, 32, 300, 7),
+                       (5, 5, 128, 128, 0, 9), (9, 1, 128, 64, 150, 3), (32, 8, 128, 16, 200, 70)]
+
+
+@pytest.mark.parametrize("nq,nkv,hd,page,window,n_req", DECODE_STREAM_CASES)
+def test_paged_attention_decode_stream_gives_the_same_bits(K, nq, nkv, hd, page, window, n_req):
+    """The streamed kernel (TMA ring, CTAs that take many chunks, tickets per segment) against the
+    one-CTA-per-chunk kernel: equal bits, for few and for many requests of mixed lengths, with
+    segments of one, two and four chunks, and for a subset of the tokens."""
+    dtype = torch.bfloat16
+    rng = np.random.default_rng(nq + hd + n_req)
+    seq_lens = [1, 37, 700, 256, 257, 513, 128, 129, 1025][:n_req] + [int(x) for x in rng.integers(1, 1100, size=max(0, n_req - 9))]
+    kc, vc, bt, mb, dense = paged_setup(rng, seq_lens, nkv, hd, page, dtype, sum((n + page - 1) // page for n in seq_lens) + 8)
+    T = len(seq_lens)
+    positions = torch.tensor([n - 1 for n in seq_lens], dtype=torch.int32).cuda()
+    seq_of = torch.arange(T, dtype=torch.int32).cuda()
+    q = torch.tensor(rng.standard_normal((T, nq * hd)), dtype=torch.float32).to(dtype).cuda()
+    scale = 1.0 / math.sqrt(hd)
+    splits = (max(seq_lens) + 127) // 128
+    assert K.decode_stream_supports(nq, nkv, hd, page, splits)
+    outs = {}
+    for impl in ("direct", "stream"):
+        part_out = torch.empty(T * nq * splits * hd, device="cuda"); part_ml = torch.empty(T * nq * splits * 2, device="cuda")
+        out = torch.full((T, nq * hd), 5.0, dtype=dtype, device="cuda")
+        for _ in range(2):                                    # twice: the ticket counters must come back to zero
+            K.paged_attention_decode(q, kc, vc, bt, mb, seq_of, positions, out, part_out, part_ml,
+                                     nq, nkv, hd, page, window, scale, splits, impl=impl)
+        torch.cuda.synchronize()
+        assert K.attention_decode_stream_error() == 0
+        outs[impl] = out
+    assert torch.equal(outs["stream"], outs["direct"])
+    want = attention_reference(q.float().double().cpu().numpy().reshape(-1, nq, hd), dense, list(range(T)), [n - 1 for n in seq_lens],
+                               nq, nkv, hd, window, scale)
+    H.assert_close(outs["stream"].float().cpu().numpy(), want, 1.5e-2, "streamed decode attention")
+    some = [T - 1, 0, 2]
+    sub = torch.full_like(out, 3.0)
+    K.paged_attention_decode(q, kc, vc, bt, mb, seq_of, positions, sub, part_out, part_ml, nq, nkv, hd, page, window, scale, splits,
+                             token_list=torch.tensor(some, dtype=torch.int32).cuda(), num_tokens=len(some), impl="stream")
+    rest = [i for i in range(T) if i not in some]
+    assert torch.equal(sub[some], outs["direct"][some]) and (sub[rest] == 3.0).all()
+    assert K.attention_decode_stream_error() == 0
+
+
 def test_decode_attention_one_far_key_decides(K):
     nq, nkv, hd, page, n = 4, 1, 64, 16, 1500
     for far in (0, 255, 256, 1023, 1499):
