@@ -164,10 +164,12 @@ paged_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
 
     // ---------------------------------------------------------------------- math warps
     const int g = lane >> 2, c4 = lane & 3;
-    float* Sc = misc;                                              // scores [DS_CHUNK][NH]
-    float* Hm = Sc + DS_CHUNK * NH;                                // per head max, then denominator
+    // Row strides padded so that neither the writers nor the readers of a phase meet in a bank.
+    constexpr int SC_LD = DS_CHUNK + 4, PT_LD = DS_CHUNK + 8;
+    float* Sc = misc;                                              // scores [NH][SC_LD]
+    float* Hm = Sc + NH * SC_LD;                                   // per head max, then denominator
     float* Hl = Hm + NH;
-    __nv_bfloat16* Pt = reinterpret_cast<__nv_bfloat16*>(Hl + NH);   // probabilities [NH][DS_CHUNK]
+    __nv_bfloat16* Pt = reinterpret_cast<__nv_bfloat16*>(Hl + NH);   // probabilities [NH][PT_LD]
     int item = 0;
     for (int kc = 0;; ++kc) {
         const int slot_k = item % DS_SLOTS;
@@ -212,8 +214,8 @@ paged_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int h = nt * 8 + 2 * c4 + e;
-                    Sc[r0 * NH + h] = ok0 ? S[nt][e] * scale : -INFINITY;
-                    Sc[r1 * NH + h] = ok1 ? S[nt][2 + e] * scale : -INFINITY;
+                    Sc[h * SC_LD + r0] = ok0 ? S[nt][e] * scale : -INFINITY;
+                    Sc[h * SC_LD + r1] = ok1 ? S[nt][2 + e] * scale : -INFINITY;
                 }
         }
         __syncwarp();
@@ -225,14 +227,14 @@ paged_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
             float sv[DS_CHUNK / 32];
             float mx = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < DS_CHUNK / 32; ++i) { sv[i] = Sc[(i * 32 + lane) * NH + h]; mx = fmaxf(mx, sv[i]); }
+            for (int i = 0; i < DS_CHUNK / 32; ++i) { sv[i] = Sc[h * SC_LD + i * 32 + lane]; mx = fmaxf(mx, sv[i]); }
             mx = warp_max(mx);
             float sum = 0.f;
 #pragma unroll
             for (int i = 0; i < DS_CHUNK / 32; ++i) {
                 const float pv = (mx == -INFINITY || sv[i] == -INFINITY) ? 0.f : expf(sv[i] - mx);
                 sum += pv;
-                Pt[h * DS_CHUNK + i * 32 + lane] = __float2bfloat16_rn(pv);
+                Pt[h * PT_LD + i * 32 + lane] = __float2bfloat16_rn(pv);
             }
             sum = warp_sum(sum);
             if (lane == 0) { Hm[h] = mx; Hl[h] = sum; }
@@ -257,7 +259,7 @@ paged_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                              : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(vbase + ks * 16 * 128));
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                    const uint32_t* prow = reinterpret_cast<const uint32_t*>(Pt + (nt * 8 + g) * DS_CHUNK + ks * 16);
+                    const uint32_t* prow = reinterpret_cast<const uint32_t*>(Pt + (nt * 8 + g) * PT_LD + ks * 16);
                     ds_mma(oacc[nt], a0, a1, a2, a3, prow[c4], prow[c4 + 4]);
                 }
             }
@@ -307,7 +309,7 @@ paged_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
 constexpr size_t DS_SMEM_LIMIT = 200 * 1024;
 static size_t ds_smem_bytes(int hd, int nt, int max_splits, size_t* misc_out) {
     const size_t NH = (size_t)nt * 8;
-    const size_t loop_bytes = ((size_t)DS_CHUNK * NH + 2 * NH) * 4 + NH * DS_CHUNK * 2;
+    const size_t loop_bytes = ((size_t)(DS_CHUNK + 4) * NH + 2 * NH) * 4 + NH * (DS_CHUNK + 8) * 2;
     const size_t merge_bytes = ((size_t)2 * max_splits * NH + NH) * 4;
     const size_t misc_bytes = ((loop_bytes > merge_bytes ? loop_bytes : merge_bytes) + 127) & ~(size_t)127;
     if (misc_out) *misc_out = misc_bytes;
