@@ -302,6 +302,37 @@ AIEN_API int aien_add_rmsnorm(float* x, const void* delta, int delta_dt, int npa
     return launch_status();
 }
 
+// out[t][i] = bfloat16(xw[t][i] * r_t), r_t = 1 / sqrt(sum_p ssq[p][t] / H + eps): finishes a norm
+// whose weight is already inside xw and whose sums of squares came in per-CTA parts (see
+// gemv_stream.cu), for a consumer that wants the normalised rows themselves.  T <= 16.
+__global__ void __launch_bounds__(256)
+scale_rows_ssq_kernel(const __nv_bfloat16* __restrict__ xw, long ld, const float* __restrict__ ssq, int parts, float eps,
+                      __nv_bfloat16* __restrict__ out, long ldo, int H) {
+    __shared__ float s_r;
+    griddep_launch();
+    griddep_wait();
+    const int t = blockIdx.x;
+    if (threadIdx.x < 32) {
+        float sq = 0.f;
+        for (int p = threadIdx.x >> 4; p < parts; p += 2) sq += (threadIdx.x & 15) == 0 ? ssq[(size_t)p * 16 + t] : 0.f;
+        sq += __shfl_xor_sync(0xffffffffu, sq, 16);
+        if (threadIdx.x == 0) s_r = 1.0f / sqrtf(sq / (float)H + eps);
+    }
+    __syncthreads();
+    const float r = s_r;
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+        out[(size_t)t * ldo + i] = __float2bfloat16_rn(__bfloat162float(xw[(size_t)t * ld + i]) * r);
+}
+
+AIEN_API int aien_scale_rows_ssq(const void* xw, long ld, const float* ssq, int parts, float eps, void* out, long ldo,
+                                 int T, int H, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (T > 16 || parts <= 0 || H <= 0) return AIEN_E_SHAPE;
+    launch_chain(scale_rows_ssq_kernel, dim3(T), dim3(256), 0, stream, (const __nv_bfloat16*)xw, ld, ssq, parts, eps,
+                 (__nv_bfloat16*)out, ldo, H);
+    return launch_status();
+}
+
 AIEN_API int aien_gather_add_rows(const float* x, const void* delta, int delta_dt, int nparts, size_t part_stride,
                                   const int* rows, float* out, int R, int H, cudaStream_t stream) {
     if (R <= 0) return 0;

@@ -12,6 +12,17 @@
 // silu(gate)*up when W holds gate|up rows interleaved in runs of 8.  The producer does not stop
 // at unit boundaries, so the memory stream never drains.
 //
+// Two optional fusions with the RMSNorm that sits between two products of a decode step
+// (crates/aien-inference-abi/src/transformer_backend.rs: x += delta; h = x * rsqrt(mean(x^2) + eps) * w):
+//   * epilogue 2, the product that ends a residual branch: the result is added to the float32
+//     residual in place, the sum times the next norm's weight is written as bfloat16 (the next
+//     product's operand), and every CTA leaves the sum of squares of the residual values it
+//     produced, per token, in ssq_out[cta][16];
+//   * scaled input, the product that follows: the operand rows are those unnormalised values, so
+//     the result row t is multiplied by 1 / sqrt(sum_cta ssq_in[cta][t] / K + eps); the partial
+//     sums are added in CTA order.
+// Together they do what the norm kernel between the two products did, without the launch.
+//
 // Rows beyond N or M are zero-filled by TMA.  Needs K % 64 == 0 and 16-byte aligned bases and row
 // strides (other sizes take the direct kernel).  Waits are bounded and report through aien_gemv_stream_error().
 #include "tma.cuh"
@@ -35,11 +46,24 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     return r;
 }
 
-// MT token tiles of 8; EPI 0 store / 1 swiglu; STAGES ring depth
+struct GsFuse {
+    const float* ssq_in;       // scaled input: [ssq_parts][16] partial sums of squares per token; null: off
+    int ssq_parts;
+    float eps;
+    float* resid;              // epilogue 2: float32 residual [M, ld_res], updated in place
+    long ld_res;
+    const void* norm_w;        // the next norm's weight [N]
+    int w_dt;
+    __nv_bfloat16* xw;         // bfloat16(residual * norm_w) [M, ld_xw]
+    long ld_xw;
+    float* ssq_out;            // [gridDim.x][16]
+};
+
+// MT token tiles of 8; EPI 0 store / 1 swiglu / 2 residual; STAGES ring depth
 template <int MT, int EPI, typename TC, int STAGES>
 __global__ void __launch_bounds__(GS_THREADS, 1)
 gemv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
-                   TC* __restrict__ out, long ldc, size_t part_stride, int M, int N, int K, int splits, int k_per_split) {
+                   TC* __restrict__ out, long ldc, size_t part_stride, int M, int N, int K, int splits, int k_per_split, GsFuse fz) {
     constexpr int X_BOX = MT * 8 * 128;                               // bytes of one box of a
     constexpr int STAGE_BYTES = GS_CONSUMERS * (GS_W_BOX + X_BOX);
     extern __shared__ uint8_t gs_smem_raw[];
@@ -107,11 +131,42 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
     // ---------------- consumers
     const int g = lane >> 2, c = lane & 3;
+    // scaled input: warp 0 (which finishes every unit) keeps the factors of its tokens in registers
+    float rs[MT][2];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) rs[mt][0] = rs[mt][1] = 1.0f;
+    if (fz.ssq_in != nullptr && warp == 0) {
+        const int t = lane & 15;
+        float sq = 0.f;
+        for (int p = lane >> 4; p < fz.ssq_parts; p += 2) sq += __ldcg(fz.ssq_in + (size_t)p * 16 + t);
+        sq += __shfl_xor_sync(0xffffffffu, sq, 16);
+        const float r = 1.0f / sqrtf(sq / (float)K + fz.eps);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            rs[mt][0] = __shfl_sync(0xffffffffu, r, mt * 8 + 2 * c);
+            rs[mt][1] = __shfl_sync(0xffffffffu, r, mt * 8 + 2 * c + 1);
+        }
+    }
+    float ss[MT][2];                                   // epilogue 2: sums of squares of this CTA's residual values
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) ss[mt][0] = ss[mt][1] = 0.f;
     uint32_t it = 0;
     int parity = 0;
     for (int u = blockIdx.x; u < units; u += gridDim.x, parity ^= 1) {
         const int tile = u / splits, sp = u - tile * splits;
         const int k_begin = sp * k_per_split, k_end = min(K, k_begin + k_per_split);
+        float xr[MT][4];                                // epilogue 2: the residual values, fetched under the stream
+        if (EPI == 2 && warp == 0) {
+            const int r0 = tile * 16 + g, r1 = r0 + 8;
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                const int t0 = mt * 8 + 2 * c;
+                xr[mt][0] = (t0 < M && r0 < N) ? fz.resid[(size_t)t0 * fz.ld_res + r0] : 0.f;
+                xr[mt][1] = (t0 + 1 < M && r0 < N) ? fz.resid[(size_t)(t0 + 1) * fz.ld_res + r0] : 0.f;
+                xr[mt][2] = (t0 < M && r1 < N) ? fz.resid[(size_t)t0 * fz.ld_res + r1] : 0.f;
+                xr[mt][3] = (t0 + 1 < M && r1 < N) ? fz.resid[(size_t)(t0 + 1) * fz.ld_res + r1] : 0.f;
+            }
+        }
         float acc[MT][4];
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
@@ -152,10 +207,22 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     float t = 0.f;
 #pragma unroll
                     for (int w = 0; w < GS_CONSUMERS; ++w) t += red[parity][w][mt][i][lane];
-                    sum[i] = t;
+                    sum[i] = t * rs[mt][i & 1];
                 }
                 const int t0 = mt * 8 + 2 * c;
-                if (EPI == 0) {
+                if (EPI == 2) {
+                    const float w0 = r0 < N ? load_dyn(fz.norm_w, fz.w_dt, r0) : 0.f, w1 = r1 < N ? load_dyn(fz.norm_w, fz.w_dt, r1) : 0.f;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int t = t0 + (i & 1), r = (i < 2) ? r0 : r1;
+                        if (t < M && r < N) {
+                            const float xn = xr[mt][i] + sum[i];
+                            fz.resid[(size_t)t * fz.ld_res + r] = xn;
+                            fz.xw[(size_t)t * fz.ld_xw + r] = __float2bfloat16_rn(xn * ((i < 2) ? w0 : w1));
+                            ss[mt][i & 1] += xn * xn;
+                        }
+                    }
+                } else if (EPI == 0) {
                     if (r0 < N) {
                         if (t0 < M) o[(size_t)t0 * ldc + r0] = from_f<TC>(sum[0]);
                         if (t0 + 1 < M) o[(size_t)(t0 + 1) * ldc + r0] = from_f<TC>(sum[1]);
@@ -174,6 +241,20 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             }
         }
     }
+    if (EPI == 2 && warp == 0) {
+        // rows g of the tile are spread over the lanes with equal c: sum them in a fixed order
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                float v = ss[mt][e];
+                v += __shfl_xor_sync(0xffffffffu, v, 4);
+                v += __shfl_xor_sync(0xffffffffu, v, 8);
+                v += __shfl_xor_sync(0xffffffffu, v, 16);
+                if (g == 0) fz.ssq_out[(size_t)blockIdx.x * 16 + mt * 8 + 2 * c + e] = v;
+            }
+        if (MT == 1 && lane < 8) fz.ssq_out[(size_t)blockIdx.x * 16 + 8 + lane] = 0.f;
+    }
 }
 
 static int sm_count() {
@@ -188,7 +269,7 @@ static int sm_count() {
 
 template <int MT, int EPI, typename TC>
 static int launch_stream(const CUtensorMap& mw, const CUtensorMap& ma, void* out, long ldc, size_t part_stride,
-                         int M, int N, int K, int splits, cudaStream_t stream) {
+                         int M, int N, int K, int splits, const GsFuse& fz, cudaStream_t stream) {
     constexpr int X_BOX = MT * 8 * 128;
     constexpr int STAGE_BYTES = GS_CONSUMERS * (GS_W_BOX + X_BOX);
     constexpr int STAGES = (200 * 1024) / STAGE_BYTES;                // 8 stages of 24 KB, or 6 of 32 KB
@@ -203,7 +284,7 @@ static int launch_stream(const CUtensorMap& mw, const CUtensorMap& ma, void* out
     k_per_split = ((k_per_split + GS_STAGE_COLS - 1) / GS_STAGE_COLS) * GS_STAGE_COLS;
     const int units = ((N + 15) / 16) * splits;
     const int grid = units < sm_count() ? units : sm_count();
-    launch_chain(kern, dim3(grid), dim3(GS_THREADS), (size_t)SMEM, stream, mw, ma, (TC*)out, ldc, part_stride, M, N, K, splits, k_per_split);
+    launch_chain(kern, dim3(grid), dim3(GS_THREADS), (size_t)SMEM, stream, mw, ma, (TC*)out, ldc, part_stride, M, N, K, splits, k_per_split, fz);
     return launch_status();
 }
 
@@ -211,22 +292,21 @@ static int launch_stream(const CUtensorMap& mw, const CUtensorMap& ma, void* out
 
 using namespace aien;
 
-// Same contract as aien_gemv_bf16.  With splits > 1 out is float32 [splits][M][ldc].  A range of K
-// is a multiple of 512 values, so `splits` ranges may cover K with fewer ranges in use; the unused
-// partial products are written as zeros.
-AIEN_API int aien_gemv_stream_bf16(const void* a, long lda, const void* W, long ldw, void* out, int c_dt, long ldc,
-                                   int M, int N, int K, int epilogue, int splits, size_t part_stride, cudaStream_t stream) {
+static int gemv_stream_dispatch(const void* a, long lda, const void* W, long ldw, void* out, int c_dt, long ldc,
+                                int M, int N, int K, int epilogue, int splits, size_t part_stride, const GsFuse& fz, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 16 || K <= 0 || (K & 63) || splits < 1 || splits > 64) return AIEN_E_SHAPE;
     if (splits > 1 && (epilogue != 0 || c_dt != AIEN_DT_F32)) return AIEN_E_SHAPE;
     if ((lda & 7) || (ldw & 7) || ((uintptr_t)a & 15) || ((uintptr_t)W & 15)) return AIEN_E_ALIGN;
     if (epilogue == 1 && (N & 15)) return AIEN_E_SHAPE;
+    if (epilogue == 2 && (splits != 1 || !fz.resid || !fz.norm_w || !fz.xw || !fz.ssq_out || fz.ssq_in)) return AIEN_E_SHAPE;
+    if (fz.ssq_in && (splits != 1 || fz.ssq_parts <= 0)) return AIEN_E_SHAPE;
     CUtensorMap mw, ma;
     const uint32_t xrows = M <= 8 ? 8 : 16;
     if (!make_map_chunked(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, 16, GS_CONSUMERS) ||
         !make_map_chunked(&ma, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, xrows, GS_CONSUMERS))
         return AIEN_E_STATE;
-#define GS_CASE(mt, epi, T) return launch_stream<mt, epi, T>(mw, ma, out, ldc, part_stride, M, N, K, splits, stream)
+#define GS_CASE(mt, epi, T) return launch_stream<mt, epi, T>(mw, ma, out, ldc, part_stride, M, N, K, splits, fz, stream)
     if (epilogue == 0) {
         if (c_dt == AIEN_DT_BF16) { if (M <= 8) GS_CASE(1, 0, __nv_bfloat16); else GS_CASE(2, 0, __nv_bfloat16); }
         if (c_dt == AIEN_DT_F32) { if (M <= 8) GS_CASE(1, 0, float); else GS_CASE(2, 0, float); }
@@ -237,8 +317,49 @@ AIEN_API int aien_gemv_stream_bf16(const void* a, long lda, const void* W, long 
         if (c_dt == AIEN_DT_F32) { if (M <= 8) GS_CASE(1, 1, float); else GS_CASE(2, 1, float); }
         return AIEN_E_DTYPE;
     }
+    if (epilogue == 2) { if (M <= 8) GS_CASE(1, 2, float); else GS_CASE(2, 2, float); }
 #undef GS_CASE
     return AIEN_E_SHAPE;
+}
+
+// Same contract as aien_gemv_bf16.  With splits > 1 out is float32 [splits][M][ldc].  A range of K
+// is a multiple of 512 values, so `splits` ranges may cover K with fewer ranges in use; the unused
+// partial products are written as zeros.
+AIEN_API int aien_gemv_stream_bf16(const void* a, long lda, const void* W, long ldw, void* out, int c_dt, long ldc,
+                                   int M, int N, int K, int epilogue, int splits, size_t part_stride, cudaStream_t stream) {
+    if (epilogue != 0 && epilogue != 1) return AIEN_E_SHAPE;
+    GsFuse none = {};
+    return gemv_stream_dispatch(a, lda, W, ldw, out, c_dt, ldc, M, N, K, epilogue, splits, part_stride, none, stream);
+}
+
+// The CTAs a product over N rows of W is run by: the number of partial sums of squares that
+// aien_gemv_stream_residual leaves.
+AIEN_API int aien_gemv_stream_grid(int N) {
+    const int units = (N + 15) / 16;
+    return units < sm_count() ? units : sm_count();
+}
+
+// The product that follows a fused norm: the rows of a are unnormalised, and row t of the result is
+// multiplied by 1 / sqrt(sum_p ssq[p][t] / K + eps) before it is stored (epilogue 0) or goes through
+// silu(gate)*up (epilogue 1).
+AIEN_API int aien_gemv_stream_scaled(const void* a, long lda, const void* W, long ldw, void* out, int c_dt, long ldc,
+                                     int M, int N, int K, int epilogue, const float* ssq, int ssq_parts, float eps, cudaStream_t stream) {
+    if ((epilogue != 0 && epilogue != 1) || ssq == nullptr) return AIEN_E_SHAPE;
+    GsFuse fz = {};
+    fz.ssq_in = ssq; fz.ssq_parts = ssq_parts; fz.eps = eps;
+    return gemv_stream_dispatch(a, lda, W, ldw, out, c_dt, ldc, M, N, K, epilogue, 1, 0, fz, stream);
+}
+
+// The product that ends a residual branch: resid[M, ld_res] += a . W^T in place (float32),
+// xw[M, ld_xw] = bfloat16(resid * norm_w), ssq_out[aien_gemv_stream_grid(N)][16] = per-CTA sums of
+// squares of the new residual values per token.
+AIEN_API int aien_gemv_stream_residual(const void* a, long lda, const void* W, long ldw, float* resid, long ld_res,
+                                       const void* norm_w, int w_dt, void* xw, long ld_xw, float* ssq_out,
+                                       int M, int N, int K, cudaStream_t stream) {
+    if (w_dt != AIEN_DT_BF16 && w_dt != AIEN_DT_F32) return AIEN_E_DTYPE;
+    GsFuse fz = {};
+    fz.resid = resid; fz.ld_res = ld_res; fz.norm_w = norm_w; fz.w_dt = w_dt; fz.xw = (__nv_bfloat16*)xw; fz.ld_xw = ld_xw; fz.ssq_out = ssq_out;
+    return gemv_stream_dispatch(a, lda, W, ldw, resid, AIEN_DT_F32, ld_res, M, N, K, 2, 1, 0, fz, stream);
 }
 
 AIEN_API int aien_gemv_stream_error(void) {

@@ -60,6 +60,10 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_gemv_stream_error": [],
         "aien_gemm_tc": [P, L, P, L, P, I, L, I, I, I, I, I, c_size_t, P],
         "aien_gemm_tc_ranges": [I, I],
+        "aien_gemv_stream_scaled": [P, L, P, L, P, I, L, I, I, I, I, P, I, F, P],
+        "aien_gemv_stream_residual": [P, L, P, L, P, L, P, I, P, L, P, I, I, I, P],
+        "aien_gemv_stream_grid": [I],
+        "aien_scale_rows_ssq": [P, L, P, I, F, P, L, I, I, P],
         "aien_gemm_tc_error": [],
         "aien_attention_prefill_tc_error": [],
         "aien_paged_attention_prefill": [P, L, P, P, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P],
@@ -385,6 +389,59 @@ def gemm_tc_splits(M: int, N: int, K_: int) -> int:
     if tiles >= 148:
         return 1
     return gemm_tc_ranges(K_, max(1, min(8, 296 // tiles, K_ // 512)))
+
+
+def FUSED_NORM_SCRATCH_BYTES(hidden: int) -> int:
+    """What a product that ends a residual branch takes for the next norm: bfloat16 rows and partial sums, with slack."""
+    return GEMV_MAX_ROWS * hidden * 2 + 1024 * 16 * 4 + 1024
+
+
+def gemv_stream_fusable(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the streamed decode product, and so its fusions with the norm around it, takes a . w^T."""
+    return (GEMV_IMPL == "stream" and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.dim() == 2
+            and a.shape[0] <= GEMV_MAX_ROWS and a.shape[1] % 64 == 0 and a.stride(1) == 1 and w.stride(1) == 1
+            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemv_stream_grid(n_rows: int) -> int:
+    """Number of CTAs (and so of partial sums of squares) of a streamed product over ``n_rows`` rows of W."""
+    return int(lib().aien_gemv_stream_grid(int(n_rows)))
+
+
+def gemv_scaled(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, ssq: torch.Tensor, parts: int, eps: float, epilogue: int = 0) -> None:
+    """out = (a . w^T) with row t multiplied by 1/sqrt(sum_p ssq[p, t] / K + eps) first; epilogue 1
+    then applies silu(gate)*up over rows of w interleaved in runs of 8."""
+    _dev(a, w, out, ssq)
+    M, Kd = a.shape
+    N = w.shape[0]
+    assert gemv_stream_fusable(a, w) and ssq.dtype == torch.float32 and ssq.is_contiguous() and ssq.numel() >= parts * 16
+    assert out.shape == (M, N // 2 if epilogue else N) and out.stride(1) == 1
+    _check(lib().aien_gemv_stream_scaled(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), dt(out), out.stride(0), M, N, Kd,
+                                         int(epilogue), _p(ssq), int(parts), float(eps), _stream()), "gemv_stream_scaled")
+
+
+def gemv_residual(a: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, norm_w: torch.Tensor, xw: torch.Tensor, ssq_out: torch.Tensor) -> int:
+    """resid += a . w^T in place (float32); xw = bfloat16(resid * norm_w); ssq_out[p, t] = partial
+    sums of resid[t]^2.  Returns the number of parts written."""
+    _dev(a, w, resid, norm_w, xw, ssq_out)
+    M, Kd = a.shape
+    N = w.shape[0]
+    parts = gemv_stream_grid(N)
+    assert gemv_stream_fusable(a, w) and resid.dtype == torch.float32 and resid.shape == (M, N) and resid.stride(1) == 1
+    assert xw.dtype == torch.bfloat16 and xw.shape == (M, N) and xw.stride(1) == 1 and norm_w.numel() == N and norm_w.is_contiguous()
+    assert ssq_out.dtype == torch.float32 and ssq_out.is_contiguous() and ssq_out.numel() >= parts * 16
+    _check(lib().aien_gemv_stream_residual(_p(a), a.stride(0), _p(w), w.stride(0), _p(resid), resid.stride(0), _p(norm_w), dt(norm_w),
+                                           _p(xw), xw.stride(0), _p(ssq_out), M, N, Kd, _stream()), "gemv_stream_residual")
+    return parts
+
+
+def scale_rows_ssq(xw: torch.Tensor, ssq: torch.Tensor, parts: int, eps: float, out: torch.Tensor) -> None:
+    """out[t] = bfloat16(xw[t] / sqrt(sum_p ssq[p, t] / H + eps)): the rest of a norm whose weight is inside xw."""
+    _dev(xw, ssq, out)
+    T, H = xw.shape
+    assert xw.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and out.shape == (T, H) and xw.stride(1) == 1 and out.stride(1) == 1
+    _check(lib().aien_scale_rows_ssq(_p(xw), xw.stride(0), _p(ssq), int(parts), float(eps), _p(out), out.stride(0), T, H, _stream()),
+           "scale_rows_ssq")
 
 
 def gemm_tc_error() -> int:

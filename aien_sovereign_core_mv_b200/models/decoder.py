@@ -12,7 +12,7 @@ import torch
 
 from .. import kernels as K
 from ..config.spec import LayerSpec, ModelSpec, PartSpec
-from ..parts.base import Block, CacheNeed, Mixer, RunBinding, StepContext
+from ..parts.base import Prenormed, Block, CacheNeed, Mixer, RunBinding, StepContext
 from ..parts.linear import linear
 from ..registry import make_part
 
@@ -159,10 +159,19 @@ class Decoder:
         x = ws.take_step((ctx.num_tokens, self.hidden_size), torch.float32)
         K.embed_gather(self.embed_table, ctx.token_ids, x)
         delta = None
-        for run, binding in zip(self.spec.run_list, self.bindings):
+        runs = self.spec.run_list
+        for i, (run, binding) in enumerate(zip(runs, self.bindings)):
             ws.begin_layer()
-            delta = self.blocks[run.layer].forward(ctx, x, delta, binding)
+            block = self.blocks[run.layer]
+            if block.chains_norm:
+                # the norm that will take this block's result, so that the block's last product may work for it
+                nxt = self.blocks[runs[i + 1].layer].first_norm() if i + 1 < len(runs) else None
+                delta = block.forward(ctx, x, delta, binding, next_norm=nxt)
+            else:
+                delta = block.forward(ctx, x, delta, binding)
         ws.end_layers()
+        if isinstance(delta, Prenormed):          # the last block has no next norm; a block of another kind may still return one
+            delta = None
         if num_rows > 0:
             rows = ws.take((num_rows, self.hidden_size), torch.float32)
             K.gather_add_rows(x, delta, want_rows, rows)

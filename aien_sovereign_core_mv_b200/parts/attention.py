@@ -8,8 +8,8 @@ import torch
 
 from .. import kernels as K
 from ..registry import register_mixer
-from .base import CacheNeed, Mixer, Position, RunBinding, StepContext
-from .linear import linear
+from .base import CacheNeed, Mixer, Position, Prenormed, ResidualSink, RunBinding, StepContext
+from .linear import linear, linear_into_residual, linear_prenormed
 
 
 @register_mixer("paged_attention")
@@ -67,19 +67,30 @@ class PagedAttention(Mixer):
     def workspace_bytes(self, lim):
         return lim.max_tokens * (2 * self.q_dim + 2 * self.kv_dim + self.q_dim + self.hidden_size) * lim.itemsize + 4096 \
             + 8 * K.GEMV_MAX_ROWS * (self.q_dim + 2 * self.kv_dim + self.hidden_size) * 4 + 2 * K.PARTIALS_MAX_BYTES \
-            + K.attention_workspace_bytes(lim, self.num_heads, self.head_dim)
+            + K.attention_workspace_bytes(lim, self.num_heads, self.head_dim) + K.FUSED_NORM_SCRATCH_BYTES(self.hidden_size)
 
     # ---- one step
-    def forward(self, ctx: StepContext, h: torch.Tensor, run: RunBinding) -> torch.Tensor:
+    takes_prenormed = True
+    feeds_residual = True
+
+    def _project(self, ctx: StepContext, h, w: torch.Tensor) -> torch.Tensor:
+        if isinstance(h, Prenormed):
+            y = linear_prenormed(ctx, h, w)
+            if y is not None:
+                return y
+            h = h.materialise(ctx)
+        return linear(ctx, h, w, may_defer_sum=True)
+
+    def forward(self, ctx: StepContext, h, run: RunBinding, sink: Optional[ResidualSink] = None):
         T = ctx.num_tokens
         group = ctx.groups[run.group]
         planes = group.storage[run.slot]                 # [2, tokens, nkv, hd]
         k_cache, v_cache = planes[0], planes[1]
         if run.writes:
-            qkv = linear(ctx, h, self.w_qkv, may_defer_sum=True)
+            qkv = self._project(ctx, h, self.w_qkv)
             q, k, v = qkv[..., :self.q_dim], qkv[..., self.q_dim:self.q_dim + self.kv_dim], qkv[..., self.q_dim + self.kv_dim:]
         else:
-            q = linear(ctx, h, self.w_qkv[:self.q_dim], may_defer_sum=True)
+            q = self._project(ctx, h, self.w_qkv[:self.q_dim])
             k = v = None
         rot = self.position.rotary(ctx)
         cos, sin, rdim = rot if rot is not None else (None, None, 0)
@@ -103,4 +114,4 @@ class PagedAttention(Mixer):
         out = ctx.workspace.take((T, self.q_dim), ctx.dtype)
         K.paged_attention(ctx, q_out, k_cache, v_cache, group, out, self.num_heads, self.num_kv_heads, self.head_dim,
                           self.window, self.scale)
-        return linear(ctx, out, self.w_o, may_defer_sum=True)
+        return linear_into_residual(ctx, out, self.w_o, sink) or linear(ctx, out, self.w_o, may_defer_sum=True)

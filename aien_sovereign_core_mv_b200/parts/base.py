@@ -151,6 +151,41 @@ class Workspace:
         return self._take(0, shape, dtype)
 
 
+# ------------------------------------------------------------------ a norm spread over its neighbours
+@dataclass
+class Prenormed:
+    """A residual sum whose norm is half done: the sum is already in the residual stream,
+    ``xw`` = bfloat16(x * norm weight) [T, H], and ``ssq`` [parts, 16] holds partial sums of x^2 per
+    token.  What is left is the factor 1/sqrt(sum(ssq[:, t])/H + eps) per row; a product is
+    linear in its rows, so the consumer's first product applies it to its result
+    (``parts/linear.py: linear_prenormed``)."""
+
+    xw: torch.Tensor
+    ssq: torch.Tensor
+    parts: int
+    eps: float
+    norm: "Norm"             # the norm this stands for
+
+    def materialise(self, ctx: "StepContext") -> torch.Tensor:
+        """The normalised rows themselves, for a consumer that cannot take the factor."""
+        from .. import kernels as K
+        out = ctx.workspace.take(tuple(self.xw.shape), torch.bfloat16)
+        K.scale_rows_ssq(self.xw, self.ssq, self.parts, self.eps, out)
+        return out
+
+
+@dataclass
+class ResidualSink:
+    """Offered to a part whose last product ends a residual branch: instead of returning the
+    branch's output for the next norm to add, the product may add it to ``x`` itself and return a
+    :class:`Prenormed` for ``norm`` (``parts/linear.py: linear_into_residual``)."""
+
+    x: torch.Tensor          # float32 residual stream [T, H]
+    norm: "Norm"
+    weight: torch.Tensor     # the norm's weight
+    eps: float
+
+
 # ------------------------------------------------------------------ part base classes
 class Part:
     def param_shapes(self) -> Dict[str, Tuple[Tuple[int, ...], str]]:
@@ -169,6 +204,12 @@ class Norm(Part):
     def forward(self, ctx: StepContext, x: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
         raise NotImplementedError
 
+    def sink(self, ctx: StepContext, x: torch.Tensor) -> Optional[ResidualSink]:
+        """A norm of the form x * f(row) * weight may let the products around it do its work in
+        this step: it then returns a ResidualSink for the producer, and its forward() passes the
+        Prenormed it gets as ``delta`` on to the consumer.  None: not in this step, or never."""
+        return None
+
 
 class Position(Part):
     def rotary(self, ctx: StepContext):
@@ -181,6 +222,9 @@ class Position(Part):
 
 
 class Mixer(Part):
+    takes_prenormed = False      # True: forward() accepts a Prenormed as h
+    feeds_residual = False       # True: forward() accepts sink=ResidualSink and may return a Prenormed
+
     def cache_need(self) -> Optional[CacheNeed]:
         return None
 
@@ -189,12 +233,20 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    takes_prenormed = False
+    feeds_residual = False
+
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
 
 class Block(Part):
     mixer: Mixer
+    chains_norm = False          # True: forward() accepts next_norm= (the norm that will take its result)
+
+    def first_norm(self) -> Optional[Norm]:
+        """The norm that takes the previous block's result, if the block starts with one."""
+        return None
 
     def forward(self, ctx: StepContext, x: torch.Tensor, delta: Optional[torch.Tensor], run: RunBinding) -> torch.Tensor:
         raise NotImplementedError

@@ -13,7 +13,7 @@ from typing import Optional
 import torch
 
 from .. import kernels as K
-from .base import StepContext
+from .base import Prenormed, ResidualSink, StepContext
 
 _FORCE = os.environ.get("AIEN_B200_GEMM", "").strip().lower()
 
@@ -62,3 +62,28 @@ def _choose(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, M: int) -> str:
     if K.gemm_tc_supports(a, w, out):
         return "tc"
     return "simple"
+
+
+def linear_prenormed(ctx: StepContext, h: Prenormed, w: torch.Tensor, epilogue: int = 0) -> Optional[torch.Tensor]:
+    """(norm of the residual) . W^T from a Prenormed input: the streamed product multiplies its
+    result rows by the norm's row factor.  ``epilogue`` 1: silu(gate)*up over rows of W interleaved
+    in runs of 8.  None when the product cannot take it (the caller materialises the norm)."""
+    if _FORCE or not K.gemv_stream_fusable(h.xw, w):
+        return None
+    M, N = h.xw.shape[0], w.shape[0]
+    out = ctx.workspace.take((M, N // 2 if epilogue else N), torch.bfloat16)
+    K.gemv_scaled(h.xw, w, out, h.ssq, h.parts, h.eps, epilogue)
+    return out
+
+
+def linear_into_residual(ctx: StepContext, a: torch.Tensor, w: torch.Tensor, sink: Optional[ResidualSink]) -> Optional[Prenormed]:
+    """sink.x += a . W^T inside the product, which also leaves bfloat16(x * norm weight) and the
+    partial sums of squares for the norm that follows.  None when there is no sink or the product
+    cannot take it (the caller returns the branch output as a delta instead)."""
+    if sink is None or _FORCE or not K.gemv_stream_fusable(a, w) or w.shape[0] != sink.x.shape[1]:
+        return None
+    M, N = a.shape[0], w.shape[0]
+    xw = ctx.workspace.take((M, N), torch.bfloat16)
+    ssq = ctx.workspace.take((K.gemv_stream_grid(N), 16), torch.float32)
+    parts = K.gemv_residual(a, w, sink.x, sink.weight, xw, ssq)
+    return Prenormed(xw, ssq, parts, sink.eps, sink.norm)

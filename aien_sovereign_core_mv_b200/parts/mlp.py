@@ -5,8 +5,10 @@ import torch
 
 from .. import kernels as K
 from ..registry import register_feed_forward
-from .base import FeedForward, StepContext
-from .linear import linear, _FORCE
+from typing import Optional
+
+from .base import FeedForward, Prenormed, ResidualSink, StepContext
+from .linear import linear, linear_into_residual, linear_prenormed, _FORCE
 
 
 @register_feed_forward("swiglu")
@@ -40,9 +42,17 @@ class SwiGLU(FeedForward):
 
     def workspace_bytes(self, lim):
         return lim.max_tokens * (3 * self.intermediate_size + self.hidden_size) * lim.itemsize + 4096 \
-            + 8 * K.GEMV_MAX_ROWS * self.hidden_size * 4 + K.PARTIALS_MAX_BYTES
+            + 8 * K.GEMV_MAX_ROWS * self.hidden_size * 4 + K.PARTIALS_MAX_BYTES + K.FUSED_NORM_SCRATCH_BYTES(self.hidden_size)
 
-    def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
+    takes_prenormed = True
+    feeds_residual = True
+
+    def forward(self, ctx: StepContext, h, sink: Optional[ResidualSink] = None):
+        if isinstance(h, Prenormed):
+            act = linear_prenormed(ctx, h, self.w_gate_up, epilogue=1) if self.group == 8 else None
+            if act is not None:
+                return linear_into_residual(ctx, act, self.w_down, sink) or linear(ctx, act, self.w_down, may_defer_sum=True)
+            h = h.materialise(ctx)
         act = ctx.workspace.take((ctx.num_tokens, self.intermediate_size), ctx.dtype)
         if self.group == 8 and h.shape[0] <= K.GEMV_MAX_ROWS and K.gemv_supports(h, self.w_gate_up, act):
             K.gemv(h, self.w_gate_up, act, epilogue=1)          # silu(gate)*up inside the product
@@ -51,4 +61,4 @@ class SwiGLU(FeedForward):
         else:
             gu = linear(ctx, h, self.w_gate_up)
             K.swiglu(gu, act, self.group)
-        return linear(ctx, act, self.w_down, may_defer_sum=True)
+        return linear_into_residual(ctx, act, self.w_down, sink) or linear(ctx, act, self.w_down, may_defer_sum=True)

@@ -7,7 +7,10 @@ import torch
 
 from .. import kernels as K
 from ..registry import register_norm
-from .base import Norm, StepContext
+from .base import Norm, Prenormed, ResidualSink, StepContext
+
+# AIEN_B200_FUSED_NORM=0 keeps every norm in its own kernel
+_FUSE = __import__("os").environ.get("AIEN_B200_FUSED_NORM", "1").strip() not in ("0", "off", "no")
 
 
 @register_norm("rmsnorm")
@@ -30,7 +33,17 @@ class RMSNorm(Norm):
     def workspace_bytes(self, lim):
         return lim.max_tokens * self.size * lim.itemsize + 256
 
-    def forward(self, ctx: StepContext, x: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
+    def sink(self, ctx: StepContext, x: torch.Tensor) -> Optional[ResidualSink]:
+        # bfloat16 steps of at most 16 tokens, where the products are the streamed decode kernel
+        if not _FUSE or ctx.dtype != torch.bfloat16 or ctx.num_tokens > K.GEMV_MAX_ROWS or K.GEMV_IMPL != "stream":
+            return None
+        return ResidualSink(x, self, self.weight, self.eps)
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, delta):
+        if isinstance(delta, Prenormed):
+            if delta.norm is self:
+                return delta                      # the sum is in x already; the consumer finishes the norm
+            delta = None                          # made for another norm: x is up to date, norm it here
         out = ctx.workspace.take(tuple(x.shape), ctx.dtype)
         K.add_rmsnorm(x, delta, self.weight, self.eps, out)
         return out

@@ -600,6 +600,54 @@ def test_prefill_attention_one_far_key_decides(K, impl):
         assert np.abs(got - far / 8.0).max() <= max(1e-2, 0.01 * far / 8.0), (far, got[0, :4], got[-1, :4])
 
 
+@pytest.mark.parametrize("M,N,K_,N2", [(1, 256, 128, 96), (8, 4096, 512, 1024), (5, 1000, 192, 264), (16, 2560, 1088, 512), (11, 136, 64, 48)])
+def test_gemv_fused_with_the_norm_between_two_products(K, M, N, K_, N2):
+    """The product that ends a residual branch adds into the residual and prepares the next norm;
+    the product after it finishes the norm on its result rows.  Together: x += a W^T;
+    y = rmsnorm(x) W2^T (and silu(gate)*up of it)."""
+    g = torch.Generator().manual_seed(M + N)
+    a = torch.randn(M, K_, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K_, generator=g) / math.sqrt(K_)).to(torch.bfloat16).cuda()
+    x0 = torch.randn(M, N, generator=g)
+    nw = (1.0 + 0.3 * torch.randn(N, generator=g)).to(torch.bfloat16).cuda()
+    eps = 1e-5
+    x = x0.clone().cuda()
+    xw = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    parts = K.gemv_stream_grid(N)
+    ssq = torch.full((parts, 16), 7.0, device="cuda")
+    assert K.gemv_stream_fusable(a, w)
+    assert K.gemv_residual(a, w, x, nw, xw, ssq) == parts
+    torch.cuda.synchronize()
+    assert K.gemv_stream_error() == 0
+    x_want = x0.double() + a.double().cpu() @ w.double().cpu().T
+    H.assert_close(x.cpu().numpy(), x_want.numpy(), 2e-5, "residual sum")
+    H.assert_close(xw.float().cpu().numpy(), (x_want * nw.double().cpu()).numpy(), 1e-2, "weighted copy")
+    got_ss = ssq.double().cpu().sum(0)
+    np.testing.assert_allclose(got_ss[:M].numpy(), (x_want ** 2).sum(1).numpy(), rtol=1e-5)
+    assert (got_ss[M:] == 0).all()
+    # the following product: plain, and with the swiglu epilogue over interleaved rows
+    if N % 64 == 0:
+        r = 1.0 / torch.sqrt((x.double().cpu() ** 2).mean(1) + eps)
+        w2 = (torch.randn(N2, N, generator=g) / math.sqrt(N)).to(torch.bfloat16).cuda()
+        out = torch.empty(M, N2, dtype=torch.bfloat16, device="cuda")
+        K.gemv_scaled(xw, w2, out, ssq, parts, eps)
+        y = (xw.double().cpu() @ w2.double().cpu().T) * r[:, None]
+        H.assert_close(out.float().cpu().numpy(), y.numpy(), 1e-2, "scaled product")
+        I = N2 // 2
+        if I % 8 == 0:
+            gate, up = w2[:I].cpu(), w2[I:].cpu()
+            inter = torch.stack([gate.view(I // 8, 8, N), up.view(I // 8, 8, N)], dim=1).reshape(2 * I, N).contiguous().cuda()
+            act = torch.empty(M, I, dtype=torch.bfloat16, device="cuda")
+            K.gemv_scaled(xw, inter, act, ssq, parts, eps, epilogue=1)
+            want = pm.swiglu(y[:, :I].numpy(), y[:, I:].numpy())
+            H.assert_close(act.float().cpu().numpy(), want, 1e-2, "scaled product + swiglu")
+        hn = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        K.scale_rows_ssq(xw, ssq, parts, eps, hn)
+        H.assert_close(hn.float().cpu().numpy(), (xw.double().cpu() * r[:, None]).numpy(), 1e-2, "materialised norm")
+        torch.cuda.synchronize()
+        assert K.gemv_stream_error() == 0
+
+
 @pytest.mark.parametrize("M,N,K_", [(1, 16, 64), (1, 333, 192), (3, 100, 320), (8, 4096, 512), (9, 77, 1088), (16, 130, 4096), (5, 48, 64), (2, 64, 1600)])
 def test_gemv_stream_against_direct(K, M, N, K_, monkeypatch):
     g = torch.Generator().manual_seed(M * 7 + N)

@@ -56,3 +56,26 @@ def test_production_layer_sizes(big, name, dtype, tol):
         H.assert_close(np.stack([got[r][0], got[r][1]]), want[[20 + r, 21 + r]], tol, f"{name} {dtype} batched decode, request {r}")
     H.assert_close(got[99][39], want[39], tol, f"{name} {dtype} portion beside decodes")
     assert eng.cache_state()["check"] == "" and eng.cache_state()["requests"] == 0
+
+
+def test_norm_spread_over_the_products_around_it(big, monkeypatch):
+    """Decode steps of few tokens run no norm kernel between two products: the product before adds
+    the residual and prepares the norm, the product after finishes it.  Same logits within the
+    bfloat16 tolerance, three launches fewer per layer but the first norm of the first layer."""
+    from aien_sovereign_core_mv_b200 import kernels as K
+    from aien_sovereign_core_mv_b200.parts import norm as norm_part
+    d, toks, want = big["qwen3_8b"]
+    res = {}
+    for fuse in (True, False):
+        monkeypatch.setattr(norm_part, "_FUSE", fuse)
+        eng = H.engine_for(d, "bfloat16", 16, 1024, max_requests=16, max_batch_tokens=256, use_cuda_graphs=False)
+        H.run_steps(eng, [([(1, toks[:100], [])], [])])
+        before = K.launch_count()
+        got = H.run_steps(eng, [([(1, [t], [0])], []) for t in toks[100:110]])
+        res[fuse] = (np.stack([got[1][p] for p in sorted(got[1])]), K.launch_count() - before)
+        eng.end_request(1)
+        assert K.gemv_stream_error() == 0
+    layers = SHAPES["qwen3_8b"]["num_hidden_layers"]
+    assert res[False][1] - res[True][1] == 10 * (2 * layers - 1)
+    for fuse in (True, False):
+        H.assert_close(res[fuse][0], want[100:110], H.BF16_TOL, f"decode, fused={fuse}")
