@@ -68,6 +68,7 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     constexpr int STAGE_BYTES = GS_CONSUMERS * (GS_W_BOX + X_BOX);
     extern __shared__ uint8_t gs_smem_raw[];
     __shared__ float red[2][GS_CONSUMERS][MT][4][32];
+    __shared__ float ssq_red[16][16];
     const uint32_t base = (smem_u32(gs_smem_raw) + 1023u) & ~1023u;
     const uint32_t bars = base + STAGES * STAGE_BYTES;
     const uint32_t full0 = bars, empty0 = bars + 8 * STAGES;
@@ -131,22 +132,19 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
     // ---------------- consumers
     const int g = lane >> 2, c = lane & 3;
-    // scaled input: warp 0 (which finishes every unit) keeps the factors of its tokens in registers
+    // scaled input: every consumer thread sums a share of the partial sums of squares now (the loads
+    // fly while the ring fills); warp 0, which finishes every unit, combines the shares in order at
+    // the end of its first unit and keeps the factors of its tokens in registers
     float rs[MT][2];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) rs[mt][0] = rs[mt][1] = 1.0f;
-    if (fz.ssq_in != nullptr && warp == 0) {
-        const int t = lane & 15;
+    if (fz.ssq_in != nullptr) {
+        const int t = threadIdx.x & 15, share = threadIdx.x >> 4;          // 16 shares of the parts
         float sq = 0.f;
-        for (int p = lane >> 4; p < fz.ssq_parts; p += 2) sq += __ldcg(fz.ssq_in + (size_t)p * 16 + t);
-        sq += __shfl_xor_sync(0xffffffffu, sq, 16);
-        const float r = 1.0f / sqrtf(sq / (float)K + fz.eps);
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-            rs[mt][0] = __shfl_sync(0xffffffffu, r, mt * 8 + 2 * c);
-            rs[mt][1] = __shfl_sync(0xffffffffu, r, mt * 8 + 2 * c + 1);
-        }
+        for (int p = share; p < fz.ssq_parts; p += 16) sq += __ldcg(fz.ssq_in + (size_t)p * 16 + t);
+        ssq_red[share][t] = sq;
     }
+    bool have_rs = fz.ssq_in == nullptr;
     float ss[MT][2];                                   // epilogue 2: sums of squares of this CTA's residual values
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) ss[mt][0] = ss[mt][1] = 0.f;
@@ -197,6 +195,18 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             for (int i = 0; i < 4; ++i) red[parity][warp][mt][i][lane] = acc[mt][i];
         asm volatile("bar.sync 1, %0;" ::"n"(GS_CONSUMERS * 32) : "memory");
         if (warp == 0) {
+            if (!have_rs) {
+                float sq = 0.f;
+#pragma unroll
+                for (int share = 0; share < 16; ++share) sq += ssq_red[share][lane & 15];
+                const float r = 1.0f / sqrtf(sq / (float)K + fz.eps);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    rs[mt][0] = __shfl_sync(0xffffffffu, r, mt * 8 + 2 * c);
+                    rs[mt][1] = __shfl_sync(0xffffffffu, r, mt * 8 + 2 * c + 1);
+                }
+                have_rs = true;
+            }
             const int r0 = tile * 16 + g, r1 = r0 + 8;
             TC* o = out + (size_t)sp * part_stride;
 #pragma unroll
