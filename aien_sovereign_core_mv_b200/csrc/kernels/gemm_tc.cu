@@ -1,7 +1,9 @@
 // C[M,N] = A[M,K] . W[N,K]^T on the fifth-generation tensor cores: tcgen05.mma with the
 // accumulator in tensor memory, operands brought into shared memory by TMA.
 //
-// One CTA computes one 128 x 128 tile.  Six warps, three roles:
+// Two forms (tc_plan chooses): one CTA per 128 x 128 tile, described here, for products with few
+// tiles and for split-K; and a persistent form with 128 x 256 tiles and two accumulators, described
+// further down, for the large products of a prefill.  The first form, six warps, three roles:
 //   warp 0      producer: one lane issues the TMA loads of the A and W k-blocks (128 rows x 64
 //               bfloat16 = one 128-byte swizzled row each) into a 3-stage ring;
 //   warp 1      allocates tensor memory, then one lane issues tcgen05.mma (M 128, N 128, K 16,
@@ -19,12 +21,78 @@
 // hanging; the host reads the code with aien_gemm_tc_error().
 #include "tma.cuh"
 #include "umma.cuh"
+#include <cstdlib>
+#include <cstring>
 
 namespace aien {
 
 constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64, TC_STAGES = 3;
 constexpr int TC_STAGE_A = TC_BM * TC_BK * 2, TC_STAGE_B = TC_BN * TC_BK * 2;
 constexpr int TC_SMEM = TC_STAGES * (TC_STAGE_A + TC_STAGE_B) + 1024 /*align*/ + 256 /*barriers*/;
+
+// Stores 32 consecutive accumulator columns of one row: r holds columns n0+c0 .. +31 of row `row`.
+// EPI 0: as they are; EPI 1: silu(gate)*up over columns interleaved in runs of 8 (out has N/2 columns).
+template <int EPI, typename TC>
+__device__ __forceinline__ void tc_store_chunk(const uint32_t r[32], TC* __restrict__ out, long ldc, int row, int n0, int c0, int N) {
+
+                if (EPI == 0) {
+                    TC* dst = out + (size_t)row * ldc + n0 + c0;
+                    const int valid = N - (n0 + c0);
+                    if (valid >= 32 && (((uintptr_t)dst & 15) == 0)) {
+                        if (sizeof(TC) == 2) {
+                            uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) {
+                                uint4 o;
+                                __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                                __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                                __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                                __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                                o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+                                o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+                                d4[v] = o;
+                            }
+                        } else {
+                            uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+                            for (int v = 0; v < 8; ++v) d4[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (j < valid) dst[j] = from_f<TC>(__uint_as_float(r[j]));
+                    }
+                } else {
+                    // columns c0..c0+31 hold two runs of (8 gate, 8 up): 16 outputs
+                    const int oc0 = (n0 + c0) / 2;
+                    TC* dst = out + (size_t)row * ldc + oc0;
+                    const int valid = N / 2 - oc0;
+                    float y[16];
+#pragma unroll
+                    for (int run = 0; run < 2; ++run)
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float g = __uint_as_float(r[run * 16 + j]), u = __uint_as_float(r[run * 16 + 8 + j]);
+                            y[run * 8 + j] = __fdividef(g, 1.0f + __expf(-g)) * u;
+                        }
+                    if (valid >= 16 && sizeof(TC) == 2 && (((uintptr_t)dst & 15) == 0)) {
+                        uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+                        for (int v = 0; v < 2; ++v) {
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(y[8 * v + 0], y[8 * v + 1]), p1 = __floats2bfloat162_rn(y[8 * v + 2], y[8 * v + 3]);
+                            __nv_bfloat162 p2 = __floats2bfloat162_rn(y[8 * v + 4], y[8 * v + 5]), p3 = __floats2bfloat162_rn(y[8 * v + 6], y[8 * v + 7]);
+                            uint4 o;
+                            o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+                            o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+                            d4[v] = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (j < valid) dst[j] = from_f<TC>(y[j]);
+                    }
+                }
+            }
 
 // EPI 0: store; EPI 1: silu(gate)*up over columns interleaved in runs of 8 (out has N/2 columns)
 template <int EPI, typename TC>
@@ -99,65 +167,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t r[32];
             tmem_ld32(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (row < M) {
-                if (EPI == 0) {
-                    TC* dst = out + (size_t)row * ldc + n0 + c0;
-                    const int valid = N - (n0 + c0);
-                    if (valid >= 32 && (((uintptr_t)dst & 15) == 0)) {
-                        if (sizeof(TC) == 2) {
-                            uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-                            for (int v = 0; v < 4; ++v) {
-                                uint4 o;
-                                __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-                                __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-                                __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-                                __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-                                o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
-                                o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
-                                d4[v] = o;
-                            }
-                        } else {
-                            uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-                            for (int v = 0; v < 8; ++v) d4[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (j < valid) dst[j] = from_f<TC>(__uint_as_float(r[j]));
-                    }
-                } else {
-                    // columns c0..c0+31 hold two runs of (8 gate, 8 up): 16 outputs
-                    const int oc0 = (n0 + c0) / 2;
-                    TC* dst = out + (size_t)row * ldc + oc0;
-                    const int valid = N / 2 - oc0;
-                    float y[16];
-#pragma unroll
-                    for (int run = 0; run < 2; ++run)
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const float g = __uint_as_float(r[run * 16 + j]), u = __uint_as_float(r[run * 16 + 8 + j]);
-                            y[run * 8 + j] = __fdividef(g, 1.0f + __expf(-g)) * u;
-                        }
-                    if (valid >= 16 && sizeof(TC) == 2 && (((uintptr_t)dst & 15) == 0)) {
-                        uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-                        for (int v = 0; v < 2; ++v) {
-                            __nv_bfloat162 p0 = __floats2bfloat162_rn(y[8 * v + 0], y[8 * v + 1]), p1 = __floats2bfloat162_rn(y[8 * v + 2], y[8 * v + 3]);
-                            __nv_bfloat162 p2 = __floats2bfloat162_rn(y[8 * v + 4], y[8 * v + 5]), p3 = __floats2bfloat162_rn(y[8 * v + 6], y[8 * v + 7]);
-                            uint4 o;
-                            o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
-                            o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
-                            d4[v] = o;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (j < valid) dst[j] = from_f<TC>(y[j]);
-                    }
-                }
-            }
+            if (row < M) tc_store_chunk<EPI, TC>(r, out, ldc, row, n0, c0, N);
+
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -166,6 +177,159 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)TC_BN) : "memory");
     }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The persistent form, for products whose tile grid fills the GPU: one CTA per SM walks over
+// tiles of 128 x BN (BN 256), M-tiles fastest.  Tensor memory holds two
+// accumulators, so the four epilogue warps drain tile i while the MMA lane already works on
+// tile i+1, and the producer runs ahead across tile borders.  With BN 256 one k-block reads
+// 16 KB of A and 32 KB of W from shared memory for 512 tensor-core cycles, which leaves the
+// shared-memory bandwidth headroom that 128 x 128 tiles (32 KB for 256 cycles) do not have.
+template <int BN> struct TcP {
+    static constexpr int STAGE_A = TC_BM * TC_BK * 2, STAGE_B = BN * TC_BK * 2;
+    static constexpr int STAGES = (192 * 1024) / (STAGE_A + STAGE_B);          // 4 of 48 KB
+    static constexpr int SMEM = STAGES * (STAGE_A + STAGE_B) + 1024 + 256;
+};
+
+template <int BN, int EPI, typename TC>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                          TC* __restrict__ out, long ldc, int M, int N, int K) {
+    using P = TcP<BN>;
+    constexpr int STAGES = P::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sA = base, sB = base + STAGES * P::STAGE_A;
+    const uint32_t bars = sB + STAGES * P::STAGE_B;
+    const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, tfull0 = bars + 16 * STAGES, tempty0 = tfull0 + 16;
+    const uint32_t tmem_slot = tempty0 + 16;
+    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen + (tmem_slot - base));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
+    const int total = m_tiles * n_tiles;
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)(2 * BN)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_acc = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= (uint32_t)STAGES) mbar_wait(empty0 + 8 * s, ((it / STAGES) - 1) & 1, 1);
+                    mbar_expect_tx(full0 + 8 * s, P::STAGE_A + P::STAGE_B);
+                    tma_load_2d(sA + s * P::STAGE_A, &map_a, full0 + 8 * s, kb * TC_BK, m0);
+                    tma_load_2d(sB + s * P::STAGE_B, &map_w, full0 + 8 * s, kb * TC_BK, n0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_bf16(TC_BM, BN, false);
+            uint32_t it = 0;
+            int i = 0;
+            for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++i) {
+                const int acc = i & 1;
+                if (i >= 2) mbar_wait(tempty0 + 8 * acc, ((i >> 1) - 1) & 1, 4);      // the epilogue has drained this accumulator
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    mbar_wait(full0 + 8 * s, (it / STAGES) & 1, 2);
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t da = make_desc_sw128(sA + s * P::STAGE_A), db = make_desc_sw128(sB + s * P::STAGE_B);
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k)
+                        umma_bf16(tmem_acc + acc * BN, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(empty0 + 8 * s);
+                }
+                umma_commit(tfull0 + 8 * acc);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        int i = 0;
+        for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++i) {
+            const int acc = i & 1;
+            const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
+            mbar_wait(tfull0 + 8 * acc, (i >> 1) & 1, 3);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = m0 + quarter * 32 + lane;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + c0), r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row < M && n0 + c0 < N) tc_store_chunk<EPI, TC>(r, out, ldc, row, n0, c0, N);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)(2 * BN)) : "memory");
+    }
+}
+
+static int tc_num_sms() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <int BN, int EPI, typename TC>
+static int launch_tc_persistent(const void* A, long lda, const void* W, long ldw, void* out, long ldc, int M, int N, int K, cudaStream_t stream) {
+    CUtensorMap ma, mw;
+    if (!make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TC_BK, TC_BM) || !make_map(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, TC_BK, BN))
+        return AIEN_E_STATE;
+    auto kern = gemm_tc_persistent_kernel<BN, EPI, TC>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcP<BN>::SMEM) != cudaSuccess) return AIEN_E_STATE;
+        configured = true;
+    }
+    const long total = (long)((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
+    const unsigned grid = (unsigned)(total < tc_num_sms() ? total : tc_num_sms());
+    kern<<<grid, 192, TcP<BN>::SMEM, stream>>>(ma, mw, (TC*)out, ldc, M, N, K);
+    return launch_status();
+}
+
+// Which kernel a product without split-K takes: 0 the one-tile-per-CTA kernel, 256 the persistent
+// kernel with 128 x 256 tiles, once these give every SM a tile.  (Persistent with 128 x 128 tiles
+// was measured 25-35 % slower than either: one CTA per SM at the shared-memory bandwidth limit.)
+// AIEN_B200_GEMM_TC=tile | p256 pins the choice.
+static int tc_plan(int M, int N) {
+    static int forced = -1;
+    if (forced < 0) {
+        const char* e = getenv("AIEN_B200_GEMM_TC");
+        forced = e == nullptr ? 1 : (!strcmp(e, "tile") ? 0 : (!strcmp(e, "p256") ? 256 : 1));
+    }
+    if (forced != 1) return forced;
+    const long mt = (M + TC_BM - 1) / TC_BM;
+    return mt * ((N + 255) / 256) >= tc_num_sms() ? 256 : 0;
 }
 
 template <int EPI, typename TC>
@@ -207,6 +371,17 @@ AIEN_API int aien_gemm_tc(const void* A, long lda, const void* W, long ldw, void
     if ((lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return AIEN_E_ALIGN;
     if (epilogue == 1 && (N & 15)) return AIEN_E_SHAPE;
     if ((M + TC_BM - 1) / TC_BM > 2147483647 / 1 || (N + TC_BN - 1) / TC_BN > 65535) return AIEN_E_SHAPE;
+    if (splits == 1 && (epilogue == 0 || epilogue == 1)) {
+        const int plan = tc_plan(M, N);
+#define TCP_CASE(BNV, EPIV, T) return launch_tc_persistent<BNV, EPIV, T>(A, lda, W, ldw, out, ldc, M, N, K, stream)
+        if (plan == 256) {
+            if (epilogue == 0 && c_dt == AIEN_DT_BF16) TCP_CASE(256, 0, __nv_bfloat16);
+            if (epilogue == 0 && c_dt == AIEN_DT_F32) TCP_CASE(256, 0, float);
+            if (epilogue == 1 && c_dt == AIEN_DT_BF16) TCP_CASE(256, 1, __nv_bfloat16);
+            if (epilogue == 1 && c_dt == AIEN_DT_F32) TCP_CASE(256, 1, float);
+        }
+#undef TCP_CASE
+    }
     CUtensorMap ma, mw;
     if (!make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TC_BK, TC_BM) || !make_map(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, TC_BK, TC_BN))
         return AIEN_E_STATE;

@@ -459,7 +459,9 @@ def test_swiglu_interleaved_layout(K):
     H.assert_close(out.cpu().numpy(), pm.swiglu(gate.double().numpy(), up.double().numpy()), 2e-5, "interleaved swiglu")
 
 
-TC_SHAPES = [(128, 128, 64), (1, 16, 8), (17, 100, 200), (130, 333, 72), (256, 384, 4096), (300, 130, 1032), (2048, 512, 256), (64, 1000, 512)]
+# the last three have at least 148 tiles of 128 x 256 and take the persistent kernel (ragged edges in M, N and K)
+TC_SHAPES = [(128, 128, 64), (1, 16, 8), (17, 100, 200), (130, 333, 72), (256, 384, 4096), (300, 130, 1032), (2048, 512, 256), (64, 1000, 512),
+             (2053, 2584, 136), (300, 37900, 72), (4096, 1280, 1024)]
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
@@ -480,9 +482,9 @@ def test_gemm_tensor_core(K, out_dtype, M, N, K_):
     assert (out_full[:, N:] == 9.0).all()                    # nothing written beyond N
 
 
-def test_gemm_tensor_core_swiglu_epilogue(K):
+@pytest.mark.parametrize("M,I,Hd", [(150, 264, 136), (1100, 2152, 200)])     # the second: the persistent kernel
+def test_gemm_tensor_core_swiglu_epilogue(K, M, I, Hd):
     g = torch.Generator().manual_seed(2)
-    M, I, Hd = 150, 264, 136
     a = torch.randn(M, Hd, generator=g).to(torch.bfloat16).cuda()
     gate = torch.randn(I, Hd, generator=g).to(torch.bfloat16)
     up = torch.randn(I, Hd, generator=g).to(torch.bfloat16)
