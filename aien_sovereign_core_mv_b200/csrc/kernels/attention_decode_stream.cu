@@ -24,6 +24,7 @@
 #include "tma.cuh"
 #include "attention_decode_merge.cuh"
 #include <math.h>
+#include <cstdlib>
 
 namespace aien {
 
@@ -286,15 +287,18 @@ paged_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
         if (m.seg_chunks > 0) {
             // ---- the segment is done: ticket; the CTA that completes the count merges the chunks
             ds_math_sync();                                        // every thread's partial results are written
-            if (tid == 0) {
-                __threadfence();                                   // ... and ordered before the ticket, device-wide
-                const int before = atomicAdd(&counters[(size_t)m.zt * nkv + m.kvh], m.seg_chunks);
-                s_is_last = before + m.seg_chunks == m.s_hi - m.s_lo + 1;
-                if (s_is_last) counters[(size_t)m.zt * nkv + m.kvh] = 0;     // ready for the next launch
+            const bool solo = m.seg_chunks == m.s_hi - m.s_lo + 1; // this CTA made every chunk of the token: no ticket
+            if (!solo) {
+                if (tid == 0) {
+                    __threadfence();                               // ... and ordered before the ticket, device-wide
+                    const int before = atomicAdd(&counters[(size_t)m.zt * nkv + m.kvh], m.seg_chunks);
+                    s_is_last = before + m.seg_chunks == m.s_hi - m.s_lo + 1;
+                    if (s_is_last) counters[(size_t)m.zt * nkv + m.kvh] = 0;     // ready for the next launch
+                }
+                ds_math_sync();
             }
-            ds_math_sync();
-            if (s_is_last) {
-                __threadfence();
+            if (solo || s_is_last) {
+                if (!solo) __threadfence();
                 ad_merge_chunks<NH>(misc, part_out, part_ml, out + (size_t)m.t * out_stride + (size_t)m.kvh * G * HD,
                                     (size_t)m.zt * nq + m.kvh * G, G, HD, max_splits, m.s_lo, m.s_hi - m.s_lo + 1, tid,
                                     DS_MATH_WARPS * 32, [] { ds_math_sync(); });
@@ -325,6 +329,17 @@ static int ds_num_sms() {
     return n;
 }
 
+// How many consecutive chunks one segment holds, from the launch's shape alone: the shortest
+// segments that still give every CTA at most one segment; with more (token, kv head) pairs than
+// CTAs, the whole token (which then needs no ticket).  Measured on the 32q/8kv x 128 shape at
+// 1,030 keys, batches 4 / 8 / 16 / 32 / 64 are best or within 1 % of best at 1 / 3 / 5 / 9 / 9
+// chunks per segment, and 16 requests of 8,192 keys at 32: what this rule gives.
+static int ds_chunks_per_segment(long items, int max_splits, long slots) {
+    if (items >= slots) return max_splits;
+    const long segs_per_item = slots / items;
+    return (int)((max_splits + segs_per_item - 1) / segs_per_item);
+}
+
 template <int HD, int NT>
 static int launch_decode_stream(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, long q_stride, const int* bt, int max_blocks,
                                 const int* seq_of_token, const int* positions, const int* token_list, float* part_out, float* part_ml,
@@ -339,10 +354,10 @@ static int launch_decode_stream(const CUtensorMap& mk, const CUtensorMap& mv, co
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return AIEN_E_STATE;
         configured = smem;
     }
-    const long chunks = (long)T * nkv * max_splits;
-    const int chunks_per_seg = chunks <= 2048 ? 1 : (chunks <= 8192 ? 2 : 4);
-    const long segs = (long)((max_splits + chunks_per_seg - 1) / chunks_per_seg) * T * nkv;
     const long slots = 2L * ds_num_sms();
+    int chunks_per_seg = ds_chunks_per_segment((long)T * nkv, max_splits, slots);
+    if (const char* e = getenv("AIEN_B200_DECODE_CPS")) { const int v = atoi(e); if (v > 0) chunks_per_seg = v; }
+    const long segs = (long)((max_splits + chunks_per_seg - 1) / chunks_per_seg) * T * nkv;
     const unsigned grid = (unsigned)(segs < slots ? segs : slots);
     kern<<<grid, DS_THREADS, smem, stream>>>(mk, mv, (const __nv_bfloat16*)q, q_stride, bt, max_blocks, seq_of_token, positions, token_list,
                                              part_out, part_ml, counters, (__nv_bfloat16*)out, out_stride, nq, nkv, page_size, window, scale,
