@@ -26,6 +26,7 @@ class EngineConfig:
     watermark_blocks: int = 4
     # execution
     use_cuda_graphs: bool = True       # replay captured graphs for decode-only steps
+    async_scheduling: bool = True      # plan and launch step n+1 while step n runs; its tokens are fed on the device
     seed: int = 0
 
     def resolved_dtype(self) -> str:

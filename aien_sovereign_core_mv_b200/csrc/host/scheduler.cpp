@@ -52,6 +52,7 @@ std::vector<PageCopy> Scheduler::fork(int64_t parent, int64_t child, int max_tok
         throw std::invalid_argument("request " + std::to_string(child) + " is already live");
     if (max_tokens <= 0) throw std::invalid_argument("max_tokens must be positive");
     const SeqRecord& p = it->second;
+    if (p.unresolved > 0) throw std::logic_error("fork() of a request whose last token is not resolved yet");
     std::vector<PageCopy> copies = cache_->fork(parent, child, p.computed);     // throws with nothing changed
     SeqRecord c;
     c.id = child;
@@ -100,6 +101,7 @@ long long Scheduler::outstanding_reservation(int g) const {
 int64_t Scheduler::pick_victim(const std::vector<int64_t>& among) const {
     int64_t best = -1;
     for (int64_t id : among) {
+        if (seqs_.at(id).draining) continue;             // about to end and free its pages by itself
         if (best < 0) { best = id; continue; }
         const SeqRecord& a = seqs_.at(id);
         const SeqRecord& b = seqs_.at(best);
@@ -125,6 +127,9 @@ void Scheduler::finish(SeqRecord& s, FinishReason why, const std::string& msg) {
     running_.erase(std::remove(running_.begin(), running_.end(), s.id), running_.end());
     waiting_.erase(std::remove(waiting_.begin(), waiting_.end(), s.id), waiting_.end());
     preempted_.erase(std::remove(preempted_.begin(), preempted_.end(), s.id), preempted_.end());
+    while (s.unresolved > 0 && !s.generated.empty()) { s.generated.pop_back(); --s.unresolved; }   // values that never came
+    s.unresolved = 0;
+    s.draining = false;
     s.state = SeqState::Finished;
     s.reason = why;
     s.message = msg;
@@ -145,8 +150,11 @@ StepPlan Scheduler::plan() {
 
     // 1. watermark: keep headroom for the running requests' next pages
     if (running_.size() > 1 && min_free_pages() < cfg_.watermark_blocks) {
-        preempt(pick_victim(running_), p);
-        preempted_this_step = true;
+        const int64_t victim = pick_victim(running_);
+        if (victim >= 0) {
+            preempt(victim, p);
+            preempted_this_step = true;
+        }
     }
 
     // 2. running requests in id order: one decode token, or the next portion of the input
@@ -156,6 +164,8 @@ StepPlan Scheduler::plan() {
     for (int64_t id : running_) {
         if (seqs >= cfg_.max_batch_size || tokens >= cfg_.max_batch_tokens) break;
         const SeqRecord& s = seqs_.at(id);
+        if (s.draining) continue;
+        if (s.unresolved > 1) throw std::logic_error("plan(): request " + std::to_string(id) + " has more than one unresolved token");
         const int pending = s.input_len() - s.computed;
         int n = 1;
         if (pending > 1) {
@@ -185,6 +195,7 @@ StepPlan Scheduler::plan() {
                 break;
             }
             const int64_t victim = pick_victim(running_);
+            if (victim < 0) { cands.clear(); break; }     // only requests that are ending hold pages: wait for them
             for (auto it = cands.begin(); it != cands.end(); ++it)
                 if (it->id == victim) { tokens -= it->n; --seqs; cands.erase(it); break; }
             preempt(victim, p);
@@ -312,6 +323,46 @@ void Scheduler::commit(const std::vector<int32_t>& sampled) {
     }
 }
 
+void Scheduler::commit_deferred() {
+    if (!awaiting_commit_) throw std::logic_error("commit_deferred() without a planned step");
+    awaiting_commit_ = false;
+    for (const StepEntry& e : last_.entries) {
+        auto it = seqs_.find(e.id);
+        if (it == seqs_.end() || it->second.state != SeqState::Running) continue;   // cancelled meanwhile
+        SeqRecord& s = it->second;
+        s.computed += static_cast<int>(e.tokens.size());
+        if (!e.wants_logits) continue;
+        s.generated.push_back(-1);
+        ++s.unresolved;
+        if (static_cast<int>(s.generated.size()) >= s.max_tokens) {
+            s.draining = true;
+            s.drain_message = "";
+        } else if (cfg_.max_context > 0 && s.input_len() >= cfg_.max_context) {
+            s.draining = true;
+            s.drain_message = "context limit";
+        }
+    }
+}
+
+void Scheduler::resolve(const std::vector<std::pair<int64_t, int32_t>>& tokens) {
+    for (const auto& [id, tok] : tokens) {
+        auto it = seqs_.find(id);
+        if (it == seqs_.end() || it->second.state == SeqState::Finished) continue;   // ended meanwhile: the value is dropped
+        SeqRecord& s = it->second;
+        if (s.unresolved <= 0) throw std::logic_error("resolve(): request " + std::to_string(id) + " has no unresolved token");
+        const size_t at = s.generated.size() - static_cast<size_t>(s.unresolved);
+        if (std::find(s.stop_ids.begin(), s.stop_ids.end(), tok) != s.stop_ids.end()) {
+            s.generated.resize(at);                       // the stop id is consumed; what was computed after it is dropped
+            s.unresolved = 0;
+            finish(s, FinishReason::StopToken, "");
+            continue;
+        }
+        s.generated[at] = tok;
+        --s.unresolved;
+        if (s.draining && s.unresolved == 0) finish(s, FinishReason::LengthLimit, s.drain_message);
+    }
+}
+
 std::vector<FinishEvent> Scheduler::take_finished() {
     std::vector<FinishEvent> out;
     out.swap(finished_);
@@ -369,6 +420,8 @@ void bind_scheduler(pybind11::module_& m) {
         .def_readonly("state", &SeqRecord::state)
         .def_readonly("reason", &SeqRecord::reason)
         .def_readonly("preemptions", &SeqRecord::preemptions)
+        .def_readonly("unresolved", &SeqRecord::unresolved)
+        .def_readonly("draining", &SeqRecord::draining)
         .def_readonly("priority", &SeqRecord::priority);
     py::class_<Scheduler>(m, "Scheduler")
         .def(py::init<SchedulerConfig, CacheManager*>(), py::arg("config"), py::arg("cache"), py::keep_alive<1, 3>())
@@ -385,6 +438,8 @@ void bind_scheduler(pybind11::module_& m) {
         .def_property_readonly("num_waiting", &Scheduler::num_waiting)
         .def("plan", &Scheduler::plan)
         .def("commit", &Scheduler::commit)
+        .def("commit_deferred", &Scheduler::commit_deferred)
+        .def("resolve", &Scheduler::resolve)
         .def("take_finished", &Scheduler::take_finished)
         .def("record", &Scheduler::record, py::return_value_policy::copy)
         .def("metrics", [](const Scheduler& s) {

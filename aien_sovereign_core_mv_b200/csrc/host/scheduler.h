@@ -53,6 +53,9 @@ struct SeqRecord {
     SeqState state = SeqState::Waiting;
     FinishReason reason = FinishReason::None;
     std::string message;
+    int unresolved = 0;          // trailing tokens of `generated` whose values are not known yet (held as -1)
+    bool draining = false;       // reached a length limit with a token unresolved: runs no more, ends at resolve()
+    std::string drain_message;
 
     int input_len() const { return static_cast<int>(prompt.size() + generated.size()); }
     int32_t input_at(int i) const {
@@ -108,6 +111,14 @@ class Scheduler {
     StepPlan plan();
     // One sampled token for every entry of the last plan that wanted logits, in entry order.
     void commit(const std::vector<int32_t>& sampled);
+    // The same when the step's tokens are still on the device: every entry that wanted logits gets a
+    // placeholder (-1), so that the next step can be planned (and launched, fed on the device) while
+    // this one runs.  Length limits still count; a request that reaches one waits, unscheduled, for
+    // its token.  resolve() later brings the values, oldest first per request: a stop id ends the
+    // request there, and what it computed beyond that point is dropped.  At most one token of a
+    // request may be unresolved when the next step is planned.
+    void commit_deferred();
+    void resolve(const std::vector<std::pair<int64_t, int32_t>>& tokens);
     std::vector<FinishEvent> take_finished();
     const SeqRecord& record(int64_t id) const { return seqs_.at(id); }
     const SchedulerMetrics& metrics() const { return metrics_; }

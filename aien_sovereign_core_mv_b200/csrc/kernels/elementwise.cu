@@ -394,6 +394,19 @@ AIEN_API int aien_scale_rows_ssq(const void* xw, long ld, const float* ssq, int 
     return launch_status();
 }
 
+// token_ids[i] = prev[src[i]] where src[i] >= 0: a step whose tokens were sampled by the step before
+// and have not been to the host takes them on the device.
+__global__ void feed_token_ids_kernel(int* __restrict__ token_ids, const int* __restrict__ src, const int* __restrict__ prev, int T) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < T && src[i] >= 0) token_ids[i] = prev[src[i]];
+}
+
+AIEN_API int aien_feed_token_ids(int* token_ids, const int* src, const int* prev, int T, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    feed_token_ids_kernel<<<(T + 127) / 128, 128, 0, stream>>>(token_ids, src, prev, T);
+    return launch_status();
+}
+
 AIEN_API int aien_gather_add_rows(const float* x, const void* delta, int delta_dt, int nparts, size_t part_stride,
                                   const int* rows, float* out, int R, int H, cudaStream_t stream) {
     if (R <= 0) return 0;

@@ -139,6 +139,8 @@ class Engine:
         o += _align4(n_tiles)
         off["single_tokens"] = o                      # token indices of single-token entries in a mixed step
         o += _align4(max(S, 1))
+        off["feed_src"] = o                           # per token: row of the previous step's sampled ids to take, or -1
+        o += _align4(max(T, 1))
         return off, o
 
     # ------------------------------------------------------------------ requests
@@ -225,10 +227,12 @@ class Engine:
         flat = np.concatenate(chunks).astype(np.int32) if chunks else np.zeros(0, dtype=np.int32)
         return ids, counts, flat, want_rows
 
-    def run_reserved(self, ids, counts, flat, want_rows, logits_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def run_reserved(self, ids, counts, flat, want_rows, logits_out: Optional[torch.Tensor] = None, feed=None) -> torch.Tensor:
         """The part of a step after its pages were taken (the scheduler takes them itself):
         metadata to the device in one copy, then the model.  Decode-only steps that want every
-        row replay a captured CUDA graph."""
+        row replay a captured CUDA graph.  ``feed`` = (ids on the device, rows): tokens given as -1
+        in ``flat`` are taken on the device from ``ids[rows[i]]`` (what the step before sampled,
+        not yet seen by the host)."""
         T, S, R = int(sum(counts)), len(ids), len(want_rows)
         graph_step = (T == S and R == T and self.cfg.use_cuda_graphs and self.dtype == torch.bfloat16
                       and self._graphable and want_rows == list(range(T)))
@@ -240,6 +244,11 @@ class Engine:
             slot[2].synchronize()
         meta_host, m = slot[0], slot[1]
         m[off["token_ids"]:off["token_ids"] + T] = flat
+        if feed is not None:
+            m[off["token_ids"]:off["token_ids"] + T][flat < 0] = 0
+            m[off["feed_src"]:off["feed_src"] + T] = feed[1]
+        elif T and int(flat.min()) < 0:
+            raise ValueError("a step brought a token id of -1 without a device feed")
         if R:
             m[off["want_rows"]:off["want_rows"] + R] = want_rows
         max_ctx = self.cache.fill_meta(ids, counts, m, off["positions"], off["seq_of_token"], off["q_start"], off["ctx_len"], off["groups"])
@@ -264,6 +273,9 @@ class Engine:
         if slot[2] is None:
             slot[2] = torch.cuda.Event()
         slot[2].record()
+        if feed is not None:
+            d = self.meta_dev
+            K.feed_token_ids(d[off["token_ids"]:off["token_ids"] + T], d[off["feed_src"]:off["feed_src"] + T], feed[0])
         self.steps_run += 1
         if graph_step:
             return self._replay_decode(off, Tp, max_ctx, logits_out, T)

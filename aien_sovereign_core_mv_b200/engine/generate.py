@@ -10,6 +10,12 @@ batch and returns logits at the last place of every request that reached the end
 one token per such request is chosen on the device, the ids come back to the host, the
 scheduler commits them and finishes what is done.  A stop id ends a request and is not
 emitted.
+
+``Generator.run`` keeps the device busy between steps (``EngineConfig.async_scheduling``): step
+n+1 is planned and launched while step n still runs; the tokens step n sampled are handed to
+step n+1 on the device, and reach the host, for the stop check and the result, one step later.
+A request that meets a stop id has then computed one token too many, which is dropped; the
+tokens that come out are those of the step-by-step loop.
 """
 from __future__ import annotations
 
@@ -59,11 +65,14 @@ class Generator:
         self.params: Dict[int, SamplingParams] = {}
         R = engine.max_requests
         dev = engine.device
-        self._ids_dev = torch.empty(R, dtype=torch.int32, device=dev)
-        self._ids_host = torch.empty(R, dtype=torch.int32, pin_memory=True)
-        self._fparams_host = torch.empty((2, R), dtype=torch.float32, pin_memory=True)      # temperature, top_p
-        self._iparams_host = torch.empty((2, R), dtype=torch.int32, pin_memory=True)        # top_k, position
-        self._lparams_host = torch.empty((2, R), dtype=torch.int64, pin_memory=True)        # seed, request id
+        # two of each staging buffer: a step is prepared while the one before it is still in flight
+        self._ids_dev2 = [torch.empty(R, dtype=torch.int32, device=dev) for _ in range(2)]
+        self._ids_host2 = [torch.empty(R, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._fparams_host2 = [torch.empty((2, R), dtype=torch.float32, pin_memory=True) for _ in range(2)]   # temperature, top_p
+        self._iparams_host2 = [torch.empty((2, R), dtype=torch.int32, pin_memory=True) for _ in range(2)]     # top_k, position
+        self._lparams_host2 = [torch.empty((2, R), dtype=torch.int64, pin_memory=True) for _ in range(2)]     # seed, request id
+        self._turn = 0
+        self._inflight = None        # (rows, host ids, count, event) of the step whose tokens the host has not seen
         self._fparams = torch.empty((2, R), dtype=torch.float32, device=dev)
         self._iparams = torch.empty((2, R), dtype=torch.int32, device=dev)
         self._lparams = torch.empty((2, R), dtype=torch.int64, device=dev)
@@ -88,6 +97,7 @@ class Generator:
     def fork(self, parent_id: int, child_id: int, params: Optional[SamplingParams] = None, priority: int = 0) -> None:
         """A running request branches: the child continues from the parent's tokens so far on shared
         cache pages (copied only where one of the two writes), with its own sampling parameters."""
+        self._drain()
         p = params or self.params.get(int(parent_id)) or SamplingParams()
         stops = list(self.engine.model.spec.stop_token_ids) if p.stop_token_ids is None else [int(t) for t in p.stop_token_ids]
         self.engine._do_copies(self.scheduler.fork(int(parent_id), int(child_id), int(p.max_tokens), stops, int(priority)))
@@ -96,32 +106,61 @@ class Generator:
     # ------------------------------------------------------------------ one step
     def step(self) -> List[GenerationResult]:
         """Plan, run, sample, commit.  Returns the requests that finished in this step."""
-        eng = self.engine
+        self._drain()
         plan = self.scheduler.plan()
-        entries = plan.entries
-        if entries:
-            eng._do_copies(plan.copies)
-            ids = [e.id for e in entries]
-            counts = [len(e.tokens) for e in entries]
-            flat = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int32, count=sum(counts))
-            want_rows, rows = [], []
-            t0 = 0
-            for e, n in zip(entries, counts):
-                if e.wants_logits:
-                    want_rows.append(t0 + n - 1)
-                    rows.append(e)
-                t0 += n
-            logits = eng.run_reserved(ids, counts, flat, want_rows)
-            self.h2d_bytes += 4 * eng._layout(t0, len(ids), len(want_rows))[1]
+        if plan.entries:
+            rows, ids_dev = self._launch(plan, None)
             sampled: List[int] = []
             if rows:
-                sampled = self._choose(logits, rows)
+                host = self._ids_host2[self._turn & 1]
+                host[:len(rows)].copy_(ids_dev, non_blocking=False)
+                self.d2h_bytes += 4 * len(rows)
+                sampled = host[:len(rows)].tolist()
             self.scheduler.commit(sampled)
-            self.steps += 1
-            if _STEP_LOG:
-                # one line per step, like the reference's AIEN_STEP_LOG (crates/aien-runtime/src/server.rs:273-293)
-                print(f"step {plan.step_id}: prefill_tokens={plan.prefill_tokens} decode_tokens={plan.num_tokens - plan.prefill_tokens} "
-                      f"requests={len(entries)} emitted={len(sampled)} preempted={len(plan.preempted)}", file=sys.stderr, flush=True)
+            self._log(plan, len(sampled))
+        return self._finished()
+
+    def _launch(self, plan, prev):
+        """Runs the planned step and chooses one token per finished input on the device.
+        ``prev``: the step before, whose ids are still on the device: (request id -> row, ids)."""
+        eng = self.engine
+        entries = plan.entries
+        eng._do_copies(plan.copies)
+        self._turn += 1
+        ids = [e.id for e in entries]
+        counts = [len(e.tokens) for e in entries]
+        flat = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int32, count=sum(counts))
+        feed = None
+        if flat.size and int(flat.min()) < 0:
+            if prev is None:
+                raise RuntimeError("a planned token has no value yet and there is no step to take it from")
+            src = np.full(flat.size, -1, dtype=np.int32)
+            t0 = 0
+            for e, n in zip(entries, counts):
+                if e.tokens[n - 1] < 0:
+                    src[t0 + n - 1] = prev[0][e.id]
+                t0 += n
+            feed = (prev[1], src)
+        want_rows, rows = [], []
+        t0 = 0
+        for e, n in zip(entries, counts):
+            if e.wants_logits:
+                want_rows.append(t0 + n - 1)
+                rows.append(e)
+            t0 += n
+        logits = eng.run_reserved(ids, counts, flat, want_rows, feed=feed)
+        self.h2d_bytes += 4 * eng._layout(t0, len(ids), len(want_rows))[1]
+        self.steps += 1
+        ids_dev = self._sample(logits, rows) if rows else None
+        return rows, ids_dev
+
+    def _log(self, plan, emitted: int) -> None:
+        if _STEP_LOG:
+            # one line per step, like the reference's AIEN_STEP_LOG (crates/aien-runtime/src/server.rs:273-293)
+            print(f"step {plan.step_id}: prefill_tokens={plan.prefill_tokens} decode_tokens={plan.num_tokens - plan.prefill_tokens} "
+                  f"requests={len(plan.entries)} emitted={emitted} preempted={len(plan.preempted)}", file=sys.stderr, flush=True)
+
+    def _finished(self) -> List[GenerationResult]:
         out = []
         for ev in self.scheduler.take_finished():
             rec_pre = self.scheduler.record(ev.id).preemptions
@@ -129,15 +168,16 @@ class Generator:
             self.params.pop(ev.id, None)
         return out
 
-    def _choose(self, logits: torch.Tensor, rows) -> List[int]:
+    def _sample(self, logits: torch.Tensor, rows) -> torch.Tensor:
         """One token per row on the device; the ids are the step's only device-to-host traffic."""
         R = len(rows)
+        turn = self._turn & 1
         ps = [self.params[e.id] for e in rows]
-        ids_dev = self._ids_dev[:R]
+        ids_dev = self._ids_dev2[turn][:R]
         if all(p.greedy for p in ps):
             K.argmax_rows(logits, ids_dev)
         else:
-            f, i, l = self._fparams_host, self._iparams_host, self._lparams_host
+            f, i, l = self._fparams_host2[turn], self._iparams_host2[turn], self._lparams_host2[turn]
             for r, (e, p) in enumerate(zip(rows, ps)):
                 f[0, r], f[1, r] = p.temperature, p.top_p
                 i[0, r], i[1, r] = p.top_k, e.start + len(e.tokens)
@@ -150,22 +190,65 @@ class Generator:
                 self._scratch = torch.empty(self.engine.max_requests * logits.shape[1], dtype=torch.float32, device=logits.device)
             K.sample_rows(logits, self._fparams[0], self._fparams[1], self._iparams[0], self._lparams[0], self._lparams[1],
                           self._iparams[1], self._scratch, ids_dev)
-        self._ids_host[:R].copy_(ids_dev, non_blocking=False)
-        self.d2h_bytes += 4 * R
-        return self._ids_host[:R].tolist()
+        return ids_dev
+
+    # ------------------------------------------------------------------ steps that overlap
+    def step_async(self) -> List[GenerationResult]:
+        """Plans and launches the next step, then takes in the tokens of the step before it (which
+        has had that long to finish).  Returns the requests that ended with those tokens."""
+        prev = self._inflight
+        plan = self.scheduler.plan()
+        now = None
+        if plan.entries:
+            feed_from = ({e.id: r for r, e in enumerate(prev[0])}, prev[4]) if prev is not None else None
+            rows, ids_dev = self._launch(plan, feed_from)
+            if rows:
+                host = self._ids_host2[self._turn & 1]
+                host[:len(rows)].copy_(ids_dev, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record()
+                self.d2h_bytes += 4 * len(rows)
+                now = (rows, host, len(rows), ev, ids_dev)
+            self.scheduler.commit_deferred()
+            self._log(plan, len(rows))
+        self._inflight = now
+        if prev is not None:
+            self._resolve(prev)
+        return self._finished()
+
+    def advance(self) -> List[GenerationResult]:
+        """One turn of the loop ``run`` makes: a step that overlaps the one before it, or a plain
+        step, as the engine is configured.  ``flush`` takes in what is still in flight."""
+        return self.step_async() if self.engine.cfg.async_scheduling else self.step()
+
+    def flush(self) -> List[GenerationResult]:
+        self._drain()
+        return self._finished()
+
+    def _resolve(self, flight) -> None:
+        rows, host, n, ev, _ = flight
+        ev.synchronize()
+        toks = host[:n].tolist()
+        self.scheduler.resolve([(e.id, t) for e, t in zip(rows, toks)])
+
+    def _drain(self) -> None:
+        """Takes in the tokens of a step that is still in flight."""
+        if self._inflight is not None:
+            flight, self._inflight = self._inflight, None
+            self._resolve(flight)
 
     # ------------------------------------------------------------------ whole jobs
     def run(self, on_finish: Optional[Callable[[GenerationResult], None]] = None) -> Dict[int, GenerationResult]:
         """Step until nothing is left."""
         done: Dict[int, GenerationResult] = {}
         idle = 0
-        while self.scheduler.has_work():
+        while self.scheduler.has_work() or self._inflight is not None:
             before = self.steps
-            for r in self.step():
+            for r in self.advance():
                 done[r.request_id] = r
                 if on_finish:
                     on_finish(r)
-            idle = idle + 1 if self.steps == before else 0
+            idle = idle + 1 if (self.steps == before and self._inflight is None) else 0
             if idle > 2:
                 raise RuntimeError("scheduler made no progress: waiting requests can never be admitted")
         return done

@@ -63,6 +63,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_gemv_stream_scaled": [P, L, P, L, P, I, L, I, I, I, I, P, I, F, P],
         "aien_gemv_stream_residual": [P, L, P, L, P, L, P, I, P, L, P, I, I, I, P],
         "aien_gemv_stream_grid": [I],
+        "aien_feed_token_ids": [P, P, P, I, P],
         "aien_scale_rows_ssq": [P, L, P, I, F, P, L, I, I, P],
         "aien_gemm_tc_error": [],
         "aien_attention_prefill_tc_error": [],
@@ -433,6 +434,13 @@ def gemv_residual(a: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, norm_w:
     _check(lib().aien_gemv_stream_residual(_p(a), a.stride(0), _p(w), w.stride(0), _p(resid), resid.stride(0), _p(norm_w), dt(norm_w),
                                            _p(xw), xw.stride(0), _p(ssq_out), M, N, Kd, _stream()), "gemv_stream_residual")
     return parts
+
+
+def feed_token_ids(token_ids: torch.Tensor, src: torch.Tensor, prev: torch.Tensor) -> None:
+    """token_ids[i] = prev[src[i]] where src[i] >= 0 (int32 device tensors)."""
+    _dev(token_ids, src, prev)
+    assert token_ids.dtype == torch.int32 and src.dtype == torch.int32 and prev.dtype == torch.int32 and src.numel() >= token_ids.numel()
+    _check(lib().aien_feed_token_ids(_p(token_ids), _p(src), _p(prev), token_ids.numel(), _stream()), "feed_token_ids")
 
 
 def scale_rows_ssq(xw: torch.Tensor, ssq: torch.Tensor, parts: int, eps: float, out: torch.Tensor) -> None:

@@ -301,15 +301,17 @@ def main() -> int:
             m = gen.scheduler.metrics()
             return m["prefill_tokens"] >= args.batch * PROMPT_LEN and gen.scheduler.num_running == args.batch
         while not all_decoding():
-            gen.step()
+            gen.advance()
         for _ in range(warmup):
-            gen.step()
+            gen.advance()
+        gen.flush()
         torch.cuda.synchronize()
         h0, d0, s0 = gen.h2d_bytes, gen.d2h_bytes, gen.steps
         dec0 = gen.scheduler.metrics()["decode_tokens"]
         t0 = time.perf_counter()
         for _ in range(steps):
-            gen.step()
+            gen.advance()          # with async_scheduling (the default) step n+1 is launched before step n's ids are read
+        gen.flush()
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
         n_steps = max(1, gen.steps - s0)

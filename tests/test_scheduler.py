@@ -1,5 +1,6 @@
 """The scheduler's decisions, on the CPU, with a fake model whose next token is a function of
 the request and the position (so a recomputed request must produce the same tokens)."""
+import numpy as np
 import pytest
 
 from aien_sovereign_core_mv_b200.csrc import build
@@ -184,3 +185,70 @@ def test_fork_shares_the_cache_and_runs_at_once():
     assert cm.free_count(0) == 64
     with pytest.raises(ValueError, match="not running"):
         s.fork(1, 3, 4, [], 0)
+
+
+def drive_overlapped(sched, cm, max_steps=4000):
+    """The loop of Generator.step_async without a device: step n+1 is planned while the tokens of
+    step n are still unknown; they are resolved one step late."""
+    done, flight = {}, None
+    for _ in range(max_steps):
+        if not sched.has_work() and flight is None:
+            break
+        plan = sched.plan()
+        now = None
+        if plan.entries:
+            for e in plan.entries:                       # an unknown token may only be the last one of an entry
+                assert all(t >= 0 for t in e.tokens[:-1])
+            now = [(e.id, fake_token(e.id, e.start + len(e.tokens))) for e in plan.entries if e.wants_logits]
+            sched.commit_deferred()
+        if flight:
+            sched.resolve(flight)
+        flight = now
+        assert cm.check() == ""
+        for ev in sched.take_finished():
+            assert all(t >= 0 for t in ev.generated)
+            done[ev.id] = (list(ev.generated), ev.reason.name, ev.message)
+    return done
+
+
+def test_overlapped_steps_give_the_same_tokens():
+    """Lengths, stop ids met early, late and at the length limit, a pool so small that requests are
+    preempted with a token still unknown: the overlapped loop ends every request like the plain loop."""
+    rng = np.random.default_rng(3)
+    for trial in range(30):
+        pages = int(rng.integers(10, 40))
+        reqs = []
+        for rid in range(1, int(rng.integers(2, 9))):
+            plen, n = int(rng.integers(1, 30)), int(rng.integers(1, 25))
+            stop_at = int(rng.integers(0, n + 3))          # sometimes beyond the length limit: never met
+            stops = [fake_token(rid, plen + stop_at)] if rng.random() < 0.6 else []
+            reqs.append((rid, plen, n, stops))
+        outcomes = []
+        for drive_fn in (drive, drive_overlapped):
+            cm, s = make(pages=pages, page=4, max_requests=8)
+            for rid, plen, n, stops in reqs:
+                s.submit(rid, [int(t) for t in rng.integers(0, 9, plen)], n, stops, 0)
+            outcomes.append(drive_fn(s, cm))
+            assert cm.free_count(0) == pages and not s.has_work()
+        plain, overlapped = outcomes
+        assert {k: v[:2] for k, v in plain.items()} == {k: v[:2] for k, v in overlapped.items()}, trial
+
+
+def test_deferred_commit_rules():
+    cm, s = make()
+    s.submit(1, list(range(6)), 3, [fake_token(1, 7)], 0)
+    s.plan(); s.commit_deferred()                           # prompt; first token unknown
+    plan = s.plan()
+    assert plan.entries[0].tokens == [-1] and plan.entries[0].start == 6
+    s.commit_deferred()
+    with pytest.raises(RuntimeError, match="not resolved"):
+        s.fork(1, 2, 4, [], 0)
+    s.resolve([(1, fake_token(1, 6))])                      # the first token comes in: request goes on
+    assert s.record(1).generated == [fake_token(1, 6), -1] and s.record(1).unresolved == 1
+    s.plan(); s.commit_deferred()                           # third token planned: the length limit is reached, unresolved
+    assert s.record(1).draining and s.plan().entries == []
+    s.resolve([(1, fake_token(1, 7))])                      # ... but the second token was the stop id
+    ev = s.take_finished()
+    assert len(ev) == 1 and ev[0].reason.name == "StopToken" and ev[0].generated == [fake_token(1, 6)]
+    s.resolve([(1, 5)])                                     # the value of the dropped token arrives: ignored
+    assert cm.free_count(0) == 64 and not s.has_work()
