@@ -64,7 +64,7 @@ paged_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                            const int* __restrict__ seq_of_token, const int* __restrict__ positions, const int* __restrict__ token_list,
                            float* __restrict__ part_out, float* __restrict__ part_ml, int* __restrict__ counters,
                            __nv_bfloat16* __restrict__ out, long out_stride, int nq, int nkv, int page_size, int window, float scale,
-                           int max_splits, int T, int chunks_per_seg, int cache_rows, int misc_bytes) {
+                           int max_splits, int T, int segs, int cache_rows, int misc_bytes) {
     constexpr int HALVES = HD / 64, HS = HD / 32, NH = NT * 8;
     constexpr uint32_t TILE = DS_CHUNK * HD * 2;                  // one K or V chunk
     extern __shared__ uint8_t ds_smem[];
@@ -83,8 +83,7 @@ paged_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int G = nq / nkv;
-    const int segs = (max_splits + chunks_per_seg - 1) / chunks_per_seg;
-    const long total = (long)segs * T * nkv;
+    const long total = (long)segs * T * nkv;      // segs: segments per (token, kv head)
 
     if (tid == 0) {
         for (int i = 0; i < DS_SLOTS; ++i) { mbar_init(full0 + 8 * i, 1); mbar_init(empty0 + 8 * i, DS_MATH_WARPS); }
@@ -108,7 +107,9 @@ paged_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
             const int pos = positions[t];
             const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
             const int s_lo = first / DS_CHUNK, s_hi = pos / DS_CHUNK;
-            const int c_begin = max(s_lo, seg * chunks_per_seg), c_end = min(s_hi, (seg + 1) * chunks_per_seg - 1);
+            // the token's own chunks are cut into `segs` runs of equal length (the last ones may be empty)
+            const int per_seg = (s_hi - s_lo + segs) / segs;
+            const int c_begin = s_lo + seg * per_seg, c_end = min(s_hi, c_begin + per_seg - 1);
             if (c_begin > c_end) continue;
             const int* bt = block_table + (size_t)(seq_of_token ? seq_of_token[t] : t) * max_blocks;
             for (int c = c_begin; c <= c_end; ++c) {
@@ -329,15 +330,16 @@ static int ds_num_sms() {
     return n;
 }
 
-// How many consecutive chunks one segment holds, from the launch's shape alone: the shortest
-// segments that still give every CTA at most one segment; with more (token, kv head) pairs than
-// CTAs, the whole token (which then needs no ticket).  Measured on the 32q/8kv x 128 shape at
-// 1,030 keys, batches 4 / 8 / 16 / 32 / 64 are best or within 1 % of best at 1 / 3 / 5 / 9 / 9
-// chunks per segment, and 16 requests of 8,192 keys at 32: what this rule gives.
-static int ds_chunks_per_segment(long items, int max_splits, long slots) {
-    if (items >= slots) return max_splits;
-    const long segs_per_item = slots / items;
-    return (int)((max_splits + segs_per_item - 1) / segs_per_item);
+// Into how many segments the chunks of one (token, kv head) pair are cut, from the launch's shape
+// alone: as many as still give every CTA at most one segment; one (the whole token, which then
+// needs no ticket) when there are more pairs than CTAs.  The kernel cuts each token's own chunk
+// count into that many equal runs.  Measured on the 32q/8kv x 128 shape at 1,030 keys (9 chunks),
+// batches 4 / 8 / 16 / 32 / 64 are best or within 1 % of best at 1 / 3 / 5 / 9 / 9 chunks per
+// segment, and 16 requests of 8,192 keys at 32: what this rule gives.
+static int ds_segments_per_pair(long pairs, int max_splits, long slots) {
+    if (pairs >= slots) return 1;
+    const long segs = slots / pairs;
+    return (int)(segs < max_splits ? segs : max_splits);
 }
 
 template <int HD, int NT>
@@ -355,13 +357,13 @@ static int launch_decode_stream(const CUtensorMap& mk, const CUtensorMap& mv, co
         configured = smem;
     }
     const long slots = 2L * ds_num_sms();
-    int chunks_per_seg = ds_chunks_per_segment((long)T * nkv, max_splits, slots);
-    if (const char* e = getenv("AIEN_B200_DECODE_CPS")) { const int v = atoi(e); if (v > 0) chunks_per_seg = v; }
-    const long segs = (long)((max_splits + chunks_per_seg - 1) / chunks_per_seg) * T * nkv;
-    const unsigned grid = (unsigned)(segs < slots ? segs : slots);
+    int segs = ds_segments_per_pair((long)T * nkv, max_splits, slots);
+    if (const char* e = getenv("AIEN_B200_DECODE_SEGMENTS")) { const int v = atoi(e); if (v > 0 && v <= max_splits) segs = v; }
+    const long total = (long)segs * T * nkv;
+    const unsigned grid = (unsigned)(total < slots ? total : slots);
     kern<<<grid, DS_THREADS, smem, stream>>>(mk, mv, (const __nv_bfloat16*)q, q_stride, bt, max_blocks, seq_of_token, positions, token_list,
                                              part_out, part_ml, counters, (__nv_bfloat16*)out, out_stride, nq, nkv, page_size, window, scale,
-                                             max_splits, T, chunks_per_seg, cache_rows, (int)misc_bytes);
+                                             max_splits, T, segs, cache_rows, (int)misc_bytes);
     return launch_status();
 }
 
