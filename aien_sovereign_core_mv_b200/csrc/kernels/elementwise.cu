@@ -257,17 +257,19 @@ qk_norm_rope_kv_write_kernel(
 
 // The same for the common case (bfloat16 everywhere, head size 128, rotation over the whole head or
 // none, one input part): a warp per head, four consecutive values per lane, no shared memory.  The
-// rotation partner of value i is i +- 64, which lane ^ 16 holds.  Weights and angles do not depend
-// on the reduction and are requested before it.
+// rotation partner of value i is i +- 64, which lane ^ 16 holds.  A warp takes QK_TOKENS tokens of
+// its head at once, so that many independent loads are in flight; weights do not depend on the
+// kernel ahead and are requested before the wait for it.
+constexpr int QK_TOKENS = 4;
 __global__ void __launch_bounds__(128)
 qk_norm_rope_kv_write_hd128_kernel(
     const __nv_bfloat16* q, long q_stride, int nq, const __nv_bfloat16* __restrict__ k, long k_stride,
     const __nv_bfloat16* __restrict__ v, long v_stride, int nkv, __nv_bfloat16* q_out, long q_out_stride,
     const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w, int wdt, float eps,
     const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-    const int* __restrict__ slot_map, __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache) {
+    const int* __restrict__ slot_map, __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int T) {
     griddep_launch();
-    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t0 = blockIdx.x * QK_TOKENS, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const bool write_kv = (k != nullptr);
     const int n_heads = nq + (write_kv ? 2 * nkv : 0);
     const int head = blockIdx.y * 4 + warp;
@@ -278,42 +280,56 @@ qk_norm_rope_kv_write_hd128_kernel(
     const void* nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
     const bool rotate = cos_t != nullptr && (is_q || is_k);
     float4 wv = make_float4(1.f, 1.f, 1.f, 1.f);
-    if (nw != nullptr) wv = load4_dyn(nw, wdt, lane * 4);                    // not written by the kernel ahead
+    if (nw != nullptr) wv = load4_dyn(nw, wdt, lane * 4);
     griddep_wait();
-    const long slot = write_kv ? (long)slot_map[t] : -1;
-    if (!is_q && slot < 0) return;                                            // token has no cache slot
-    float4 cs = make_float4(1.f, 1.f, 1.f, 1.f), sn = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (rotate) {
-        cs = load4(cos_t + (size_t)t * 64 + (lane & 15) * 4);
-        sn = load4(sin_t + (size_t)t * 64 + (lane & 15) * 4);
-    }
-    const __nv_bfloat16* src = is_q ? (q + (size_t)t * q_stride + (size_t)hh * 128)
-                                    : (is_k ? (k + (size_t)t * k_stride + (size_t)hh * 128) : (v + (size_t)t * v_stride + (size_t)hh * 128));
-    const uint2 raw = *reinterpret_cast<const uint2*>(src + lane * 4);
-    const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-    float x0 = __low2float(p0), x1 = __high2float(p0), x2 = __low2float(p1), x3 = __high2float(p1);
-    if (nw != nullptr) {
-        const float ss = warp_sum(x0 * x0 + x1 * x1 + x2 * x2 + x3 * x3);
-        const float scale = 1.0f / sqrtf(ss / 128.0f + eps);
-        x0 = x0 * scale * wv.x; x1 = x1 * scale * wv.y; x2 = x2 * scale * wv.z; x3 = x3 * scale * wv.w;
-    }
-    if (cos_t != nullptr) {                                                   // warp-uniform: v heads take part in the shuffles
-        const float y0 = __shfl_xor_sync(0xffffffffu, x0, 16), y1 = __shfl_xor_sync(0xffffffffu, x1, 16);
-        const float y2 = __shfl_xor_sync(0xffffffffu, x2, 16), y3 = __shfl_xor_sync(0xffffffffu, x3, 16);
-        if (rotate) {
-            if (lane < 16) {             // first half: a = own, b = partner: a c - b s
-                x0 = x0 * cs.x - y0 * sn.x; x1 = x1 * cs.y - y1 * sn.y; x2 = x2 * cs.z - y2 * sn.z; x3 = x3 * cs.w - y3 * sn.w;
-            } else {                     // second half: a = partner, b = own: a s + b c
-                x0 = y0 * sn.x + x0 * cs.x; x1 = y1 * sn.y + x1 * cs.y; x2 = y2 * sn.z + x2 * cs.z; x3 = y3 * sn.w + x3 * cs.w;
-            }
+    const __nv_bfloat16* src_base = is_q ? q : (is_k ? k : v);
+    const long src_stride = is_q ? q_stride : (is_k ? k_stride : v_stride);
+    long slot[QK_TOKENS];
+    uint2 raw[QK_TOKENS];
+    float4 cs[QK_TOKENS], sn[QK_TOKENS];
+#pragma unroll
+    for (int j = 0; j < QK_TOKENS; ++j) {
+        const int t = t0 + j;
+        const bool live = t < T;
+        slot[j] = (write_kv && live) ? (long)slot_map[t] : -1;
+        raw[j] = live ? *reinterpret_cast<const uint2*>(src_base + (size_t)t * src_stride + (size_t)hh * 128 + lane * 4) : make_uint2(0u, 0u);
+        if (rotate && live) {
+            cs[j] = load4(cos_t + (size_t)t * 64 + (lane & 15) * 4);
+            sn[j] = load4(sin_t + (size_t)t * 64 + (lane & 15) * 4);
+        } else {
+            cs[j] = make_float4(1.f, 1.f, 1.f, 1.f);
+            sn[j] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
-    __nv_bfloat162 o0 = __floats2bfloat162_rn(x0, x1), o1 = __floats2bfloat162_rn(x2, x3);
-    uint2 o;
-    o.x = *reinterpret_cast<uint32_t*>(&o0); o.y = *reinterpret_cast<uint32_t*>(&o1);
-    __nv_bfloat16* dst = is_q ? (q_out + (size_t)t * q_out_stride + (size_t)hh * 128)
-                              : ((is_k ? k_cache : v_cache) + ((size_t)slot * nkv + hh) * 128);
-    *reinterpret_cast<uint2*>(dst + lane * 4) = o;
+#pragma unroll
+    for (int j = 0; j < QK_TOKENS; ++j) {
+        const int t = t0 + j;
+        const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw[j].x), p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw[j].y);
+        float x0 = __low2float(p0), x1 = __high2float(p0), x2 = __low2float(p1), x3 = __high2float(p1);
+        if (nw != nullptr) {
+            const float ss = warp_sum(x0 * x0 + x1 * x1 + x2 * x2 + x3 * x3);
+            const float scale = 1.0f / sqrtf(ss / 128.0f + eps);
+            x0 = x0 * scale * wv.x; x1 = x1 * scale * wv.y; x2 = x2 * scale * wv.z; x3 = x3 * scale * wv.w;
+        }
+        if (cos_t != nullptr) {                                               // warp-uniform: v heads take part in the shuffles
+            const float y0 = __shfl_xor_sync(0xffffffffu, x0, 16), y1 = __shfl_xor_sync(0xffffffffu, x1, 16);
+            const float y2 = __shfl_xor_sync(0xffffffffu, x2, 16), y3 = __shfl_xor_sync(0xffffffffu, x3, 16);
+            if (rotate) {
+                if (lane < 16) {             // first half: a = own, b = partner: a c - b s
+                    x0 = x0 * cs[j].x - y0 * sn[j].x; x1 = x1 * cs[j].y - y1 * sn[j].y; x2 = x2 * cs[j].z - y2 * sn[j].z; x3 = x3 * cs[j].w - y3 * sn[j].w;
+                } else {                     // second half: a = partner, b = own: a s + b c
+                    x0 = y0 * sn[j].x + x0 * cs[j].x; x1 = y1 * sn[j].y + x1 * cs[j].y; x2 = y2 * sn[j].z + x2 * cs[j].z; x3 = y3 * sn[j].w + x3 * cs[j].w;
+                }
+            }
+        }
+        if (t >= T || (!is_q && slot[j] < 0)) continue;                       // beyond the step, or a token without a cache slot
+        __nv_bfloat162 o0 = __floats2bfloat162_rn(x0, x1), o1 = __floats2bfloat162_rn(x2, x3);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&o0); o.y = *reinterpret_cast<uint32_t*>(&o1);
+        __nv_bfloat16* dst = is_q ? (q_out + (size_t)t * q_out_stride + (size_t)hh * 128)
+                                  : ((is_k ? k_cache : v_cache) + ((size_t)slot[j] * nkv + hh) * 128);
+        *reinterpret_cast<uint2*>(dst + lane * 4) = o;
+    }
 }
 
 // ---------------------------------------------------------------- dtype conversion (load time)
@@ -450,10 +466,10 @@ AIEN_API int aien_qk_norm_rope_kv_write(
                     (((uintptr_t)q_norm_w | (uintptr_t)k_norm_w | (uintptr_t)cos_t | (uintptr_t)sin_t) & 15) == 0;
     if (hd == 128 && nparts == 1 && in_dt == AIEN_DT_BF16 && act_dt == AIEN_DT_BF16 && (k == nullptr || kv_dt == AIEN_DT_BF16) &&
         (cos_t == nullptr || rot == 128) && a8) {
-        launch_chain(qk_norm_rope_kv_write_hd128_kernel, grid, dim3(128), 0, stream,
+        launch_chain(qk_norm_rope_kv_write_hd128_kernel, dim3((T + QK_TOKENS - 1) / QK_TOKENS, grid.y), dim3(128), 0, stream,
                      (const __nv_bfloat16*)q, q_stride, nq, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, nkv,
                      (__nv_bfloat16*)q_out, q_out_stride, q_norm_w, k_norm_w, w_dt, eps, cos_t, sin_t, slot_map,
-                     (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache);
+                     (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, T);
         return launch_status();
     }
     AIEN_DISPATCH_DTYPE(in_dt, TI, AIEN_DISPATCH_DTYPE(act_dt, TC, AIEN_DISPATCH_DTYPE(kv_dt, TKV,

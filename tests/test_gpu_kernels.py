@@ -104,7 +104,8 @@ def test_rope_table_far_positions(K):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("nq,nkv,hd,rot,norm", [(4, 2, 16, 16, False), (6, 3, 48, 48, True), (5, 1, 80, 32, True), (2, 2, 256, 256, True)])
+@pytest.mark.parametrize("nq,nkv,hd,rot,norm", [(4, 2, 16, 16, False), (6, 3, 48, 48, True), (5, 1, 80, 32, True), (2, 2, 256, 256, True),
+                                                 (8, 2, 128, 128, True), (3, 3, 128, 128, False), (6, 2, 128, 64, True)])   # 128: the vectorised kernel (bfloat16, full rotation)
 def test_qk_norm_rope_kv_write(K, dtype, nq, nkv, hd, rot, norm):
     T, slots = 7, 40
     g = torch.Generator().manual_seed(nq * hd)
