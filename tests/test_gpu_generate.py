@@ -135,6 +135,31 @@ def test_fork_through_the_generator(folders):
     assert eng.cache_state()["requests"] == 0 and eng.cache_state()["check"] == ""
 
 
+def test_overlapped_steps_equal_step_by_step(folders):
+    """Generation with steps that overlap (the tokens of step n reach the host while step n+1
+    runs) against the step-by-step loop: same tokens and reasons, with stop ids met at different
+    places, different lengths, sampling, and a pool small enough to preempt."""
+    from aien_sovereign_core_mv_b200.engine.generate import Generator
+    from aien_sovereign_core_mv_b200.sampling import SamplingParams
+    d = folders["A"]
+    prompts = [H.tokens_for("A", n, 40 + n) for n in (9, 23, 31, 5)]
+    free_run = [plain_greedy(d, p, 12) for p in prompts[:3]]
+    params = [SamplingParams(temperature=0.0, max_tokens=12, stop_token_ids=[free_run[0][4]]),           # stops early
+              SamplingParams(temperature=0.0, max_tokens=7, stop_token_ids=[free_run[1][6]]),            # the stop id would be the last token
+              SamplingParams(temperature=0.0, max_tokens=12, stop_token_ids=[]),
+              SamplingParams(temperature=0.9, top_p=0.9, top_k=30, max_tokens=15, stop_token_ids=[], seed=3)]
+    out = {}
+    for overlap in (False, True):
+        eng = H.engine_for(d, "float32", 16, 96, watermark_blocks=0, async_scheduling=overlap)       # 6 pages: someone gets preempted
+        res = Generator(eng).generate(prompts, params, request_ids=[1, 2, 3, 4])
+        out[overlap] = [(r.tokens, r.finish_reason) for r in res]
+        assert eng.cache_state()["requests"] == 0 and eng.cache_state()["check"] == ""
+    assert out[True] == out[False]
+    cut = lambda toks, stop: toks[:toks.index(stop)]
+    assert out[True][0] == (cut(free_run[0], free_run[0][4]), "stop") and out[True][1] == (cut(free_run[1], free_run[1][6]), "stop")
+    assert out[True][2] == (free_run[2], "length") and len(out[True][3][0]) == 15
+
+
 def test_command_line(folders, tmp_path):
     d = folders["A"]
     prompt = H.tokens_for("A", 13, 3)
