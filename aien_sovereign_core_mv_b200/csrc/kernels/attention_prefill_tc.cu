@@ -64,7 +64,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                   const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int max_blocks,
                   const int* __restrict__ q_start, const int* __restrict__ ctx_len, const int* __restrict__ tile_seq,
                   const int* __restrict__ tile_q0, int num_tiles, __nv_bfloat16* __restrict__ out, long out_stride,
-                  int nq, int nkv, int page_size, int window, float scale_log2e, int cache_rows) {
+                  int nq, int nkv, int page_size, int window, float scale_log2e, int cache_rows, int heads_per_cta) {
     using S = PtShape<HD>;
     extern __shared__ uint8_t pt_smem[];
     const uint32_t base = (smem_u32(pt_smem) + 1023u) & ~1023u;
@@ -79,13 +79,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     // ---- which tile, which heads (the last tiles of a request see the most keys: they start first)
-    const int group = nq / nkv, pairs = (group + 1) / 2;
+    // heads_per_cta 2: two query heads of a kv head share the CTA's K/V blocks; 1: one head per CTA,
+    // for steps with so few tiles that the pairs would leave SMs idle
+    const int group = nq / nkv, pairs = (group + heads_per_cta - 1) / heads_per_cta;
     const int per_tile = nkv * pairs;
     const int tile = num_tiles - 1 - (int)(blockIdx.x / per_tile);
     const int rem = blockIdx.x % per_tile;
     const int kvh = rem / pairs, pair = rem - kvh * pairs;
-    const int head_a = kvh * group + 2 * pair;
-    const bool has_b = 2 * pair + 1 < group;
+    const int head_a = kvh * group + heads_per_cta * pair;
+    const bool has_b = heads_per_cta == 2 && 2 * pair + 1 < group;
     const int s = tile_seq[tile], q0 = tile_q0[tile];
     const int qs = q_start[s], q_len = q_start[s + 1] - qs;
     const int rows = min(PT_BM, q_len - q0);
@@ -318,12 +320,16 @@ static int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mk, const
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PtShape<HD>::SMEM) != cudaSuccess) return AIEN_E_STATE;
         configured = true;
     }
-    const int group = nq / nkv, pairs = (group + 1) / 2;
-    const long ctas = (long)num_tiles * nkv * pairs;
+    const int group = nq / nkv;
+    int sms = 148, dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    // pairs of heads halve the K/V traffic; with fewer paired CTAs than SMs, one head per CTA is faster
+    const int heads_per_cta = (group >= 2 && (long)num_tiles * nkv * ((group + 1) / 2) >= sms) ? 2 : 1;
+    const long ctas = (long)num_tiles * nkv * ((group + heads_per_cta - 1) / heads_per_cta);
     if (ctas > 2147483647L) return AIEN_E_SHAPE;
     kern<<<(unsigned)ctas, PT_THREADS, PtShape<HD>::SMEM, stream>>>(mq, mk, mv, bt, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles,
                                                                      (__nv_bfloat16*)out, out_stride, nq, nkv, page_size, window,
-                                                                     scale * 1.4426950408889634f, cache_rows);
+                                                                     scale * 1.4426950408889634f, cache_rows, heads_per_cta);
     return launch_status();
 }
 

@@ -90,7 +90,7 @@ def attn_decode_case(batch: int, ctx: int, nq: int = 32, nkv: int = 8, hd: int =
         run()
     us = _time_graph(run, reps)
     mb = batch * ctx * nkv * hd * 2 * 2 / 1e6
-    print(f"attn-decode[{impl}] batch={batch} ctx={ctx} ({nq}q/{nkv}kv x {hd}): {us:8.2f} us  {mb:.1f} MB of K/V  {mb / us * 1e3:7.0f} GB/s"
+    print(f"attn-decode[{impl}] batch={batch} ctx={ctx} page={page} ({nq}q/{nkv}kv x {hd}): {us:8.2f} us  {mb:.1f} MB of K/V  {mb / us * 1e3:7.0f} GB/s"
           f"  (error flag {K.attention_decode_stream_error()})", flush=True)
 
 
@@ -111,7 +111,7 @@ def attn_prefill_case(tokens: int, offset: int = 0, nq: int = 32, nkv: int = 8, 
         run()
     us = _time_graph(run, reps)
     flops = 4.0 * nq * hd * (tokens * (tokens + 1) / 2 + tokens * offset)
-    print(f"attn-prefill[{impl}] tokens={tokens} offset={offset} ({nq}q/{nkv}kv x {hd}): {us:8.1f} us  {flops / us / 1e6:7.1f} TFLOP/s"
+    print(f"attn-prefill[{impl}] tokens={tokens} offset={offset} page={page} ({nq}q/{nkv}kv x {hd}): {us:8.1f} us  {flops / us / 1e6:7.1f} TFLOP/s"
           f"  (error flag {K.attention_prefill_tc_error()})", flush=True)
 
 
@@ -126,10 +126,10 @@ def main(argv=None) -> int:
     p.add_argument("--k", type=int, default=4096); p.add_argument("--epilogue", type=int, default=0)
     p = sub.add_parser("attn-decode")
     p.add_argument("--batch", type=int, default=1); p.add_argument("--ctx", type=int, default=1030)
-    p.add_argument("--impl", default="stream", choices=["stream", "direct"])
+    p.add_argument("--impl", default="stream", choices=["stream", "direct"]); p.add_argument("--page", type=int, default=16)
     p = sub.add_parser("attn-prefill")
     p.add_argument("--tokens", type=int, default=2048); p.add_argument("--offset", type=int, default=0)
-    p.add_argument("--impl", default="tc", choices=["tc", "mma"])
+    p.add_argument("--impl", default="tc", choices=["tc", "mma"]); p.add_argument("--page", type=int, default=16)
     sub.add_parser("all")
     args = ap.parse_args(argv)
     K.lib()
@@ -138,9 +138,9 @@ def main(argv=None) -> int:
     elif args.case == "gemm":
         gemm_case(args.m, args.n, args.k, args.epilogue)
     elif args.case == "attn-decode":
-        attn_decode_case(args.batch, args.ctx, impl=args.impl)
+        attn_decode_case(args.batch, args.ctx, page=args.page, impl=args.impl)
     elif args.case == "attn-prefill":
-        attn_prefill_case(args.tokens, args.offset, impl=args.impl)
+        attn_prefill_case(args.tokens, args.offset, page=args.page, impl=args.impl)
     else:
         shapes = {"qkv": (6144, 4096, 0), "o": (4096, 4096, 0), "gate_up": (24576, 4096, 1), "down": (4096, 12288, 0), "head": (151936, 4096, 0)}
         for m in (1, 8, 16):
