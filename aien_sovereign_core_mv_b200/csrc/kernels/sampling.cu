@@ -12,7 +12,11 @@
 // Own design: u comes from Philox4x32-10 keyed by the request's seed with counter
 // (request id, position), so a draw depends on nothing else in the batch; the kept set is
 // walked in token-id order.  Thresholds are found by bisection on an order-preserving integer
-// image of the floats, which needs no sort.  `probs` is scratch of V floats per row.
+// image of the floats, which needs no sort.  The nucleus bisects over the few tokens that can
+// belong to it, gathered in shared memory (tokens too light to matter are left out by a bound
+// that is exact); a flat distribution with more than 4,096 such tokens bisects over the row.
+// Masses are summed as integers, so no result depends on an order of summation.
+// `probs` is scratch of V floats per row.
 #include "common.cuh"
 #include <math.h>
 
@@ -65,14 +69,43 @@ __device__ __forceinline__ long long block_sum_i64(long long v, double* red) {
     return total;
 }
 
+__device__ __forceinline__ unsigned long long block_sum_u64(unsigned long long v, double* red) {
+    return (unsigned long long)block_sum_i64((long long)v, red);
+}
+
+// Calls f(i, row[i]) for every i < V.  Which thread visits which elements, and in which order, is
+// fixed by V and the block size alone.  16-byte loads, four in flight per thread, when the row allows.
+template <typename F>
+__device__ __forceinline__ void scan_row(const float* __restrict__ row, int V, F f) {
+    const int nt = blockDim.x, tid = threadIdx.x;
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+        const int V4 = V >> 2;
+        const float4* r4 = reinterpret_cast<const float4*>(row);
+        int i = tid;
+        for (; i + 3 * nt < V4; i += 4 * nt) {
+            const float4 a = r4[i], b = r4[i + nt], c = r4[i + 2 * nt], d = r4[i + 3 * nt];
+            f(4 * i, a.x); f(4 * i + 1, a.y); f(4 * i + 2, a.z); f(4 * i + 3, a.w);
+            f(4 * (i + nt), b.x); f(4 * (i + nt) + 1, b.y); f(4 * (i + nt) + 2, b.z); f(4 * (i + nt) + 3, b.w);
+            f(4 * (i + 2 * nt), c.x); f(4 * (i + 2 * nt) + 1, c.y); f(4 * (i + 2 * nt) + 2, c.z); f(4 * (i + 2 * nt) + 3, c.w);
+            f(4 * (i + 3 * nt), d.x); f(4 * (i + 3 * nt) + 1, d.y); f(4 * (i + 3 * nt) + 2, d.z); f(4 * (i + 3 * nt) + 3, d.w);
+        }
+        for (; i < V4; i += nt) {
+            const float4 a = r4[i];
+            f(4 * i, a.x); f(4 * i + 1, a.y); f(4 * i + 2, a.z); f(4 * i + 3, a.w);
+        }
+        for (int j = (V4 << 2) + tid; j < V; j += nt) f(j, row[j]);
+    } else {
+        for (int j = tid; j < V; j += nt) f(j, row[j]);
+    }
+}
+
 // argmax with ties to the lower index; returns to every thread
 __device__ int block_argmax(const float* __restrict__ row, int V, float* best_val_out, double* red) {
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = row[i];
+    scan_row(row, V, [&](int i, float v) {
         if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
-    }
+    });
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
@@ -93,19 +126,34 @@ __device__ int block_argmax(const float* __restrict__ row, int V, float* best_va
     return bi;
 }
 
-// Smallest id c such that #{i <= c : pred(i)} >= need, pred(i) = (key(row[i]) == thr) [&& extra]
+// Smallest id c such that #{i <= c : pred(i, vals[i])} >= need (need >= 1 and at most the number
+// of hits): every thread counts a run of consecutive ids, the runs are added up in order.
 template <typename Pred>
-__device__ int id_cutoff(int V, long long need, Pred pred, double* red) {
-    int lo = 0, hi = V - 1;                       // answer in [lo, hi]
-    while (lo < hi) {
-        const int mid = lo + (hi - lo) / 2;
-        long long c = 0;
-        for (int i = threadIdx.x; i <= mid; i += blockDim.x) c += pred(i) ? 1 : 0;
-        c = block_sum_i64(c, red);
-        if (c >= need) hi = mid; else lo = mid + 1;
+__device__ int id_cutoff(const float* __restrict__ vals, int V, long long need, Pred pred, long long* run_count, int* result) {
+    const int tid = threadIdx.x, per = (V + blockDim.x - 1) / blockDim.x;
+    const int lo = tid * per, hi = min(V, lo + per);
+    long long c = 0;
+    for (int i = lo; i < hi; ++i) c += pred(i, vals[i]) ? 1 : 0;
+    __syncthreads();
+    run_count[tid] = c;
+    if (tid == 0) *result = V - 1;
+    __syncthreads();
+    long long before = 0;
+    for (int w = 0; w < tid; ++w) before += run_count[w];
+    if (before < need && before + c >= need) {               // the need-th hit lies in this thread's run
+        long long seen = before;
+        for (int i = lo; i < hi; ++i)
+            if (pred(i, vals[i]) && ++seen == need) { *result = i; break; }
     }
-    return lo;
+    __syncthreads();
+    return *result;
 }
+
+// Probabilities are summed as integers (units of 2^-40 of the largest one), so that a sum does not
+// depend on the order of its terms: the candidates of the nucleus are gathered in no fixed order.
+__device__ __forceinline__ unsigned long long prob_units(float e) { return __float2ull_rz(e * 1099511627776.0f); }   // the scaling by 2^40 is exact
+
+constexpr int SM_CAND = 4096;
 
 __global__ void __launch_bounds__(SM_THREADS)
 sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restrict__ temperature,
@@ -115,6 +163,8 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
                    int* __restrict__ out_ids) {
     __shared__ double red[64];
     __shared__ double scan[SM_THREADS];
+    __shared__ uint32_t cand_bits[SM_CAND];         // nucleus candidates: their probabilities, as bit patterns
+    __shared__ int cand_count, cut_result;
     const int r = blockIdx.x, tid = threadIdx.x;
     const float* row = logits + (size_t)r * V;
     float maxv;
@@ -125,6 +175,7 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
         return;
     }
     float* probs = probs_scratch + (size_t)r * V;
+    long long* run_count = reinterpret_cast<long long*>(scan);
 
     // ---- top-k: allowed(i) = key > thr_k || (key == thr_k && i <= cut_k)
     const int k = top_k ? top_k[r] : 0;
@@ -134,65 +185,97 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
         for (int bit = 31; bit >= 0; --bit) {
             const uint32_t cand = prefix | (1u << bit);
             long long c = 0;
-            for (int i = tid; i < V; i += SM_THREADS) c += ordered_key(row[i]) >= cand ? 1 : 0;
+            scan_row(row, V, [&](int, float v) { c += ordered_key(v) >= cand ? 1 : 0; });
             c = block_sum_i64(c, red);
             if (c >= k) prefix = cand;
         }
         thr_k = prefix;
-        long long gt = 0;
-        for (int i = tid; i < V; i += SM_THREADS) gt += ordered_key(row[i]) > thr_k ? 1 : 0;
-        gt = block_sum_i64(gt, red);
+        long long gt = 0, eq = 0;
         const uint32_t tk = thr_k;
-        cut_k = id_cutoff(V, (long long)k - gt, [&](int i) { return ordered_key(row[i]) == tk; }, red);
+        scan_row(row, V, [&](int, float v) { const uint32_t key = ordered_key(v); gt += key > tk ? 1 : 0; eq += key == tk ? 1 : 0; });
+        gt = block_sum_i64(gt, red);
+        eq = block_sum_i64(eq, red);
+        if ((long long)k - gt < eq)                               // ties at the threshold: the lower ids
+            cut_k = id_cutoff(row, V, (long long)k - gt, [&](int, float v) { return ordered_key(v) == tk; }, run_count, &cut_result);
     }
 
-    // ---- unnormalised probabilities e_i = exp((l_i - max) / T) of the allowed tokens
-    const double inv_t = 1.0 / (double)T;
-    double z = 0.0;
-    for (int i = tid; i < V; i += SM_THREADS) {
-        const uint32_t key = ordered_key(row[i]);
-        const bool allowed = key > thr_k || (key == thr_k && i <= cut_k);
-        const float e = allowed ? (float)exp(((double)row[i] - (double)maxv) * inv_t) : 0.f;
-        probs[i] = e;
-        z += (double)e;
+    // ---- unnormalised probabilities e_i = exp((l_i - max) / T) of the allowed tokens, and their sum
+    const float inv_t = 1.0f / T;
+    unsigned long long z_units = 0;
+    {
+        const uint32_t tk = thr_k; const int ck = cut_k;
+        scan_row(row, V, [&](int i, float v) {
+            const uint32_t key = ordered_key(v);
+            const bool allowed = key > tk || (key == tk && i <= ck);
+            const float e = allowed ? expf((v - maxv) * inv_t) : 0.f;
+            probs[i] = e;
+            z_units += prob_units(e);
+        });
     }
-    z = block_sum_f64(z, red);
+    z_units = block_sum_u64(z_units, red);          // also makes every thread's probs visible to the block
 
-    // ---- top-p: kept(i) = e_i > 0 && (key > thr_p || (key == thr_p && i <= cut_p))
+    // ---- top-p: kept(i) = e_i > 0 && (bits(e_i) > thr_p || (bits(e_i) == thr_p && i <= cut_p)); probabilities
+    // are not negative, so their bit patterns order like their values
     const float tp = top_p ? top_p[r] : 1.f;
     uint32_t thr_p = 0; int cut_p = V - 1;
-    double kept_mass = z;
     if (tp > 0.f && tp < 1.f) {
-        const double target = (double)tp * z;
+        unsigned long long target = (unsigned long long)ceil((double)tp * (double)z_units);
+        if (target > z_units) target = z_units;
+        if (target < 1) target = 1;
+        // tokens of at most `small` units each cannot weigh more than z - target together, so the
+        // nucleus lies among the others: gather those (few, when the distribution is peaked)
+        const unsigned long long small = (z_units - target) / (unsigned long long)V;
+        if (tid == 0) cand_count = 0;
+        __syncthreads();
+        // units(e) > small  <=>  e * 2^40 >= small + 1  <=>  e >= the smallest float not below (small + 1) / 2^40
+        const float light = __double2float_ru((double)(small + 1) * (1.0 / 1099511627776.0));
+        scan_row(probs, V, [&](int, float e) {
+            if (e >= light && *(volatile int*)&cand_count <= SM_CAND) {   // once the list has overflowed nobody queues for it any more
+                const int at = atomicAdd(&cand_count, 1);
+                if (at < SM_CAND) cand_bits[at] = __float_as_uint(e);
+            }
+        });
+        __syncthreads();
+        const int C = cand_count;
+        const bool in_smem = C <= SM_CAND;
+        // mass of the tokens whose probability bits are >= cand (bit patterns compare as integers)
+        auto mass_at_least = [&](uint32_t cand) {
+            unsigned long long m = 0;
+            if (in_smem) {
+                for (int j = tid; j < C; j += SM_THREADS) m += cand_bits[j] >= cand ? prob_units(__uint_as_float(cand_bits[j])) : 0ull;
+            } else {
+                scan_row(probs, V, [&](int, float e) { m += __float_as_uint(e) >= cand ? prob_units(e) : 0ull; });
+            }
+            return block_sum_u64(m, red);
+        };
         uint32_t prefix = 0;
-        for (int bit = 31; bit >= 0; --bit) {
+        for (int bit = 30; bit >= 0; --bit) {                   // bit 31 is the sign: never set
             const uint32_t cand = prefix | (1u << bit);
-            double mass = 0.0;
-            for (int i = tid; i < V; i += SM_THREADS)
-                if (ordered_key(row[i]) >= cand) mass += (double)probs[i];
-            mass = block_sum_f64(mass, red);
-            if (mass >= target) prefix = cand;
+            if (mass_at_least(cand) >= target) prefix = cand;
         }
         thr_p = prefix;
-        double m_gt = 0.0; long long n_eq = 0;
-        for (int i = tid; i < V; i += SM_THREADS) {
-            const uint32_t key = ordered_key(row[i]);
-            if (key > thr_p) m_gt += (double)probs[i];
-            else if (key == thr_p && probs[i] > 0.f) n_eq += 1;
+        const uint32_t tpk = thr_p;
+        unsigned long long m_gt = 0; long long n_eq = 0;
+        if (in_smem) {
+            for (int j = tid; j < C; j += SM_THREADS) {
+                if (cand_bits[j] > tpk) m_gt += prob_units(__uint_as_float(cand_bits[j]));
+                else if (cand_bits[j] == tpk) n_eq += 1;
+            }
+        } else {
+            scan_row(probs, V, [&](int, float e) {
+                const uint32_t b = __float_as_uint(e);
+                if (b > tpk) m_gt += prob_units(e); else if (b == tpk && e > 0.f) n_eq += 1;
+            });
         }
-        m_gt = block_sum_f64(m_gt, red);
+        m_gt = block_sum_u64(m_gt, red);
         n_eq = block_sum_i64(n_eq, red);
-        const double p_thr = (double)(float)exp(((double)key_value(thr_p) - (double)maxv) * inv_t);
+        const unsigned long long q_thr = prob_units(__uint_as_float(tpk));
         long long need = 1;
-        if (p_thr > 0.0) {
-            need = (long long)ceil((target - m_gt) / p_thr);
-            if (need < 1) need = 1;
-        }
+        if (q_thr > 0 && target > m_gt) need = (long long)((target - m_gt + q_thr - 1) / q_thr);
         if (need > n_eq) need = n_eq;
         if (need < 1) need = 1;
-        const uint32_t tpk = thr_p;
-        cut_p = id_cutoff(V, need, [&](int i) { return ordered_key(row[i]) == tpk && probs[i] > 0.f; }, red);
-        kept_mass = m_gt + (double)need * p_thr;
+        if (need < n_eq)                                           // ties at the threshold: the lower ids
+            cut_p = id_cutoff(probs, V, need, [&](int, float e) { return __float_as_uint(e) == tpk && e > 0.f; }, run_count, &cut_result);
     }
 
     // ---- draw: walk the kept set in id order
@@ -205,41 +288,54 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
 
     const int per = (V + SM_THREADS - 1) / SM_THREADS;
     const int lo = tid * per, hi = min(V, lo + per);
+    auto kept = [&](int i, float e) {
+        const uint32_t b = __float_as_uint(e);
+        return e > 0.f && (b > thr_p || (b == thr_p && i <= cut_p));
+    };
     double local = 0.0;
     for (int i = lo; i < hi; ++i) {
-        const uint32_t key = ordered_key(row[i]);
-        if (probs[i] > 0.f && (key > thr_p || (key == thr_p && i <= cut_p))) local += (double)probs[i];
+        const float e = probs[i];
+        if (kept(i, e)) local += (double)e;
     }
-    scan[tid] = local;
+    // inclusive sums of the runs in run order (a fixed tree: warp scans, then the warps' totals)
+    double incl = local;
+    const int lane = tid & 31, warp = tid >> 5;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const double up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+    }
+    const double warp_total = __shfl_sync(0xffffffffu, incl, 31);
     __syncthreads();
+    if (lane == 0) red[warp] = warp_total;
+    __syncthreads();
+    double before_warp = 0.0, total = 0.0;
+    for (int w = 0; w < SM_THREADS / 32; ++w) {
+        if (w < warp) before_warp += red[w];
+        total += red[w];
+    }
+    incl += before_warp;
+    const double rr = u * total;
+    // the run that holds the draw: the first whose inclusive sum exceeds it; if rounding leaves none, the last run with mass
     __shared__ int chosen;
-    __shared__ int last_kept_thread;
-    if (tid == 0) {
-        double total = 0.0;
-        for (int w = 0; w < SM_THREADS; ++w) total += scan[w];
-        const double rr = u * total;
-        double cum = 0.0;
-        int pick = -1, last = 0;
-        for (int w = 0; w < SM_THREADS; ++w) {
-            const double s = scan[w];
-            if (s > 0.0) last = w;
-            if (pick < 0 && rr < cum + s) { pick = w; scan[w] = rr - cum; }   // remainder to walk inside w
-            cum += s;
-        }
-        if (pick < 0) { pick = last; scan[last] = INFINITY; }
-        chosen = pick;
-        last_kept_thread = last;
+    __shared__ int last_run;
+    if (tid == 0) { chosen = SM_THREADS; last_run = 0; }
+    __syncthreads();
+    if (local > 0.0) {
+        atomicMax(&last_run, tid);
+        if (rr < incl) atomicMin(&chosen, tid);
     }
     __syncthreads();
-    (void)kept_mass; (void)last_kept_thread;
-    if (tid == chosen) {
-        const double rem = scan[tid];
+    const bool beyond = chosen == SM_THREADS;      // u * total landed at or beyond the total: the last kept token
+    const int run = beyond ? last_run : chosen;
+    if (tid == run) {
+        const double rem = beyond ? (double)INFINITY : rr - (incl - local);    // what is left to walk inside this run
         double cum = 0.0;
         int pick = -1, last = lo;
         for (int i = lo; i < hi; ++i) {
-            const uint32_t key = ordered_key(row[i]);
-            if (probs[i] > 0.f && (key > thr_p || (key == thr_p && i <= cut_p))) {
-                cum += (double)probs[i];
+            const float e = probs[i];
+            if (kept(i, e)) {
+                cum += (double)e;
                 last = i;
                 if (rem < cum) { pick = i; break; }
             }
