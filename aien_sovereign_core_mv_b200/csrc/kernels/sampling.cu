@@ -163,7 +163,8 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
                    int* __restrict__ out_ids) {
     __shared__ double red[64];
     __shared__ double scan[SM_THREADS];
-    __shared__ uint32_t cand_bits[SM_CAND];         // nucleus candidates: their probabilities, as bit patterns
+    __shared__ uint32_t cand_bits[SM_CAND];         // nucleus candidates: their probabilities, as bit patterns,
+    __shared__ int cand_id[SM_CAND];                // and (one-pass case) their token ids
     __shared__ int cand_count, cut_result;
     const int r = blockIdx.x, tid = threadIdx.x;
     const float* row = logits + (size_t)r * V;
@@ -176,6 +177,148 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
     }
     float* probs = probs_scratch + (size_t)r * V;
     long long* run_count = reinterpret_cast<long long*>(scan);
+
+    // the uniform number of this draw
+    uint32_t rnd[4];
+    const unsigned long long seed = seeds ? seeds[r] : 0ull;
+    const unsigned long long rid = request_ids ? (unsigned long long)request_ids[r] : 0ull;
+    const uint32_t posn = positions ? (uint32_t)positions[r] : 0u;
+    philox4x32_10(posn, 0u, (uint32_t)rid, (uint32_t)(rid >> 32), (uint32_t)seed, (uint32_t)(seed >> 32), rnd);
+    const double u = (double)((((unsigned long long)rnd[0] << 32) | rnd[1]) >> 11) * (1.0 / 9007199254740992.0);
+
+    // ---- the usual cases in one pass over the row: a peaked distribution with a nucleus and/or a
+    // small top-k.  The pass gathers, with their ids, the tokens that can matter in shared memory:
+    //   * top-k: those no further below the largest logit than the k-th largest (to a step of 0.5,
+    //     found from a small histogram in a pass of its own): at least k and at most 4,096 of them;
+    //     the k-th largest among them is found there, and the rest of the row is out;
+    //   * nucleus alone: those of at least (1 - top_p) / (2 V) of the heaviest token's probability:
+    //     all lighter tokens together weigh less than what the nucleus leaves out.
+    // Thresholds and the draw then need no further look at the row.  Too many gathered, more than
+    // 1,024 kept, or a tie at a threshold: the general path below.
+    {
+        const int k0 = top_k ? top_k[r] : 0;
+        const float tp0 = top_p ? top_p[r] : 1.f;
+        const bool use_k = k0 > 0 && k0 < V, use_p = tp0 > 0.f && tp0 < 1.f;
+        bool listed = false;
+        unsigned long long z0 = 0;
+        int C = 0;
+        const float inv_t0 = 1.0f / T;
+        if (use_k && k0 <= SM_THREADS) {
+            // how far below the largest logit the k-th largest lies, from counts in steps of 0.5 (only
+            // the few tokens within 32 of the maximum are counted); then those tokens are gathered
+            int* hist = reinterpret_cast<int*>(scan);
+            if (tid < 64) hist[tid] = 0;
+            if (tid == 0) cand_count = 0;
+            __syncthreads();
+            scan_row(row, V, [&](int, float v) {
+                const float d = (maxv - v) * 2.0f;
+                if (d < 64.0f) atomicAdd(&hist[(int)d], 1);
+            });
+            __syncthreads();
+            int step_sel = -1, cum = 0;
+            for (int b = 0; b < 64; ++b) {
+                cum += hist[b];
+                if (cum >= k0) { step_sel = b; break; }
+            }
+            __syncthreads();                                                // hist (in `scan`) is free again
+            C = SM_CAND + 1;
+            if (step_sel >= 0 && cum <= SM_CAND) {
+                scan_row(row, V, [&](int i, float v) {
+                    const float d = (maxv - v) * 2.0f;
+                    if (d < 64.0f && (int)d <= step_sel) {
+                        const int at = atomicAdd(&cand_count, 1);
+                        if (at < SM_CAND) { cand_bits[at] = ordered_key(v); cand_id[at] = i; }
+                    }
+                });
+                __syncthreads();
+                C = cand_count;
+            }
+            if (C <= SM_CAND && C >= k0) {
+                uint32_t prefix = 0;                                        // the k-th largest key among the gathered
+                for (int bit = 31; bit >= 0; --bit) {
+                    const uint32_t cand = prefix | (1u << bit);
+                    long long c = 0;
+                    for (int j = tid; j < C; j += SM_THREADS) c += cand_bits[j] >= cand ? 1 : 0;
+                    if (block_sum_i64(c, red) >= k0) prefix = cand;
+                }
+                long long n_ge = 0;
+                for (int j = tid; j < C; j += SM_THREADS) n_ge += cand_bits[j] >= prefix ? 1 : 0;
+                n_ge = block_sum_i64(n_ge, red);
+                if (n_ge == k0) {                                           // no tie at the k-th place
+                    for (int j = tid; j < C; j += SM_THREADS) {
+                        const float e = cand_bits[j] >= prefix ? expf((key_value(cand_bits[j]) - maxv) * inv_t0) : 0.f;
+                        cand_bits[j] = __float_as_uint(e);                  // from here on: probabilities; 0 = not allowed
+                        z0 += prob_units(e);
+                    }
+                    z0 = block_sum_u64(z0, red);
+                    listed = true;
+                }
+            }
+        } else if (!use_k && use_p) {
+            const float light0 = 0.499f * (1.0f - tp0) / (float)V;
+            if (tid == 0) cand_count = 0;
+            __syncthreads();
+            scan_row(row, V, [&](int i, float v) {
+                const float e = expf((v - maxv) * inv_t0);
+                z0 += prob_units(e);
+                if (e >= light0 && *(volatile int*)&cand_count <= SM_CAND) {
+                    const int at = atomicAdd(&cand_count, 1);
+                    if (at < SM_CAND) { cand_bits[at] = __float_as_uint(e); cand_id[at] = i; }
+                }
+            });
+            z0 = block_sum_u64(z0, red);
+            C = cand_count;
+            listed = C <= SM_CAND;
+        }
+        if (listed) {
+            uint32_t prefix = 1;                                            // kept: probability bits >= prefix (0 marks what top-k left out)
+            bool tie = false;
+            if (use_p) {
+                unsigned long long target = (unsigned long long)ceil((double)tp0 * (double)z0);
+                if (target > z0) target = z0;
+                if (target < 1) target = 1;
+                prefix = 0;
+                for (int bit = 30; bit >= 0; --bit) {
+                    const uint32_t cand = prefix | (1u << bit);
+                    unsigned long long m = 0;
+                    for (int j = tid; j < C; j += SM_THREADS) m += cand_bits[j] >= cand ? prob_units(__uint_as_float(cand_bits[j])) : 0ull;
+                    if (block_sum_u64(m, red) >= target) prefix = cand;
+                }
+                if (prefix == 0) prefix = 1;
+                unsigned long long m_gt = 0; long long n_eq = 0;
+                for (int j = tid; j < C; j += SM_THREADS) {
+                    if (cand_bits[j] > prefix) m_gt += prob_units(__uint_as_float(cand_bits[j]));
+                    else if (cand_bits[j] == prefix) n_eq += 1;
+                }
+                m_gt = block_sum_u64(m_gt, red);
+                n_eq = block_sum_i64(n_eq, red);
+                const unsigned long long q_thr = prob_units(__uint_as_float(prefix));
+                long long need = 1;
+                if (q_thr > 0 && target > m_gt) need = (long long)((target - m_gt + q_thr - 1) / q_thr);
+                tie = need < n_eq;                                          // only some of the tokens at the threshold are kept
+            }
+            unsigned long long total = 0; long long n_kept = 0;
+            for (int j = tid; j < C; j += SM_THREADS)
+                if (cand_bits[j] >= prefix) { total += prob_units(__uint_as_float(cand_bits[j])); n_kept += 1; }
+            total = block_sum_u64(total, red);
+            n_kept = block_sum_i64(n_kept, red);
+            if (!tie && n_kept <= SM_THREADS && total > 0) {
+                unsigned long long rr = (unsigned long long)(u * (double)total);
+                if (rr >= total) rr = total - 1;
+                // the kept token j owns the units [before_j, before_j + units_j) in id order; one of them holds rr
+                for (int j = tid; j < C; j += SM_THREADS) {
+                    if (cand_bits[j] < prefix) continue;
+                    const int my_id = cand_id[j];
+                    unsigned long long before = 0;
+                    for (int i = 0; i < C; ++i)
+                        if (cand_bits[i] >= prefix && cand_id[i] < my_id) before += prob_units(__uint_as_float(cand_bits[i]));
+                    if (rr >= before && rr < before + prob_units(__uint_as_float(cand_bits[j]))) out_ids[r] = my_id;
+                }
+                return;
+            }
+        }
+        __syncthreads();
+    }
 
     // ---- top-k: allowed(i) = key > thr_k || (key == thr_k && i <= cut_k)
     const int k = top_k ? top_k[r] : 0;
@@ -279,13 +422,6 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
     }
 
     // ---- draw: walk the kept set in id order
-    uint32_t rnd[4];
-    const unsigned long long seed = seeds ? seeds[r] : 0ull;
-    const unsigned long long rid = request_ids ? (unsigned long long)request_ids[r] : 0ull;
-    const uint32_t posn = positions ? (uint32_t)positions[r] : 0u;
-    philox4x32_10(posn, 0u, (uint32_t)rid, (uint32_t)(rid >> 32), (uint32_t)seed, (uint32_t)(seed >> 32), rnd);
-    const double u = (double)((((unsigned long long)rnd[0] << 32) | rnd[1]) >> 11) * (1.0 / 9007199254740992.0);
-
     const int per = (V + SM_THREADS - 1) / SM_THREADS;
     const int lo = tid * per, hi = min(V, lo + per);
     auto kept = [&](int i, float e) {

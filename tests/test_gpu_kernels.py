@@ -278,6 +278,40 @@ def test_argmax_and_sampling(K):
     assert counts[int(np.argmax(logits[2]))] == counts.max()
 
 
+def test_sampling_at_a_large_vocabulary(K):
+    """A vocabulary of 40,013 with a language-model-like row (a few tokens far above the rest) and
+    a flat one: the one-pass cases of the sampler (nucleus alone, top-k with and without nucleus)
+    and the general path (flat distribution, large k, pure temperature) against the plain sampler."""
+    from aien_sovereign_core_mv_b200.sampling import philox_uniform
+    rng = np.random.default_rng(7)
+    V = 40013
+    peaked = (rng.standard_normal(V) * 2).astype(np.float32)
+    hot = rng.choice(V, 60, replace=False)
+    peaked[hot] = (rng.random(60) * 9 + 9).astype(np.float32)
+    flat = (rng.standard_normal(V) * 0.5).astype(np.float32)
+    rows = [peaked, peaked, peaked, peaked, peaked, flat, flat]
+    temp = [0.7, 0.6, 1.0, 0.7, 1.2, 0.7, 1.0]
+    top_p = [0.95, 0.8, 1.0, 0.9, 1.0, 0.95, 0.5]
+    top_k = [0, 20, 50, 2000, 0, 0, 40]
+    R = len(rows)
+    lg = torch.tensor(np.stack(rows)).cuda()
+    ids = torch.empty(R, dtype=torch.int32, device="cuda")
+    scratch = torch.empty(R * V, device="cuda")
+    seeds = list(range(21, 21 + R)); rids = list(range(1, R + 1))
+    mismatches = 0
+    for position in (0, 5, 9, 123, 4000, 77777):
+        K.sample_rows(lg, torch.tensor(temp).cuda(), torch.tensor(top_p).cuda(), torch.tensor(top_k, dtype=torch.int32).cuda(),
+                      torch.tensor(seeds, dtype=torch.int64).cuda(), torch.tensor(rids, dtype=torch.int64).cuda(),
+                      torch.full((R,), position, dtype=torch.int32).cuda(), scratch, ids)
+        got = ids.cpu().tolist()
+        for r in range(R):
+            kept, _ = pm.kept_set(rows[r], temp[r], top_p[r], top_k[r])
+            assert got[r] in kept, (position, r)
+            u = philox_uniform(seeds[r], rids[r], position)
+            mismatches += got[r] != pm.sample_token(rows[r], temp[r], top_p[r], top_k[r], u)
+    assert mismatches <= 1          # float32 exponentials against float64: only a knife-edge draw may differ
+
+
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("M,N,K_", [(1, 16, 32), (1, 333, 72), (3, 100, 200), (8, 4096, 512), (9, 77, 1032), (16, 130, 4096), (5, 48, 8)])
 def test_gemv_against_simple(K, out_dtype, M, N, K_):
