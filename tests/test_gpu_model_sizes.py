@@ -79,3 +79,30 @@ def test_norm_spread_over_the_products_around_it(big, monkeypatch):
     assert res[False][1] - res[True][1] == 10 * (2 * layers - 1)
     for fuse in (True, False):
         H.assert_close(res[fuse][0], want[100:110], H.BF16_TOL, f"decode, fused={fuse}")
+
+
+def test_long_context_bfloat16_follows_float32():
+    """9,000 tokens through the production layer sizes: prompt portions at offsets far into the
+    context, then single tokens over 71 key chunks.  The plain implementation is too slow here, so
+    the bfloat16 kernels are held against the engine's own 32-bit path, itself checked above."""
+    from aien_sovereign_core_mv_b200 import Engine, EngineConfig
+    import torch
+    cfg = dict(SHAPES["qwen3_8b"], max_position_embeddings=16384)
+    n = 9000
+    toks = [int(t) for t in np.random.default_rng(1).integers(0, cfg["vocab_size"], n + 12)]
+    out = {}
+    for dtype in ("float32", "bfloat16"):
+        ec = EngineConfig(dtype=dtype, page_size=16, max_cache_tokens=n + 2048, max_requests=4, max_batch_tokens=2048, max_context=n + 1024)
+        eng = Engine.from_config(cfg, seed=3, engine_config=ec, init_std=0.02, device_init=True)
+        rows = []
+        for i in range(0, n, 2048):
+            part = toks[i:i + 2048]
+            lg = eng.step([(1, part, [0, len(part) - 1])])
+            rows += [lg[0].float().cpu().numpy(), lg[1].float().cpu().numpy()]
+        for t in toks[n:]:
+            rows.append(eng.step([(1, [t], [0])])[0].float().cpu().numpy())
+        out[dtype] = np.stack(rows)
+        assert eng.cache_state()["check"] == ""
+        del eng
+        torch.cuda.empty_cache()
+    H.assert_close(out["bfloat16"], out["float32"], H.BF16_TOL, "long context, bfloat16 against float32")
