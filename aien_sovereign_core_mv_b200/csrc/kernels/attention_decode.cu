@@ -28,7 +28,7 @@ namespace aien {
 constexpr int AD_WARPS = 8;
 constexpr int AD_CHUNK = 128;
 
-__device__ __forceinline__ uint4 ad_ldg16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ uint4 ad_ldg16(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }   // q: written by the kernel ahead
 __device__ __forceinline__ uint4 ad_lds16(uint32_t addr) {
     uint4 r;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr));
@@ -70,7 +70,7 @@ __device__ __forceinline__ void ad_norm_rope_head(const __nv_bfloat16* src, floa
                                                   const float* cos_t, const float* sin_t, int rot, int t, int lane) {
     float ss = 0.f;
     for (int i = lane; i < hd; i += 32) {
-        const float val = __bfloat162float(src[i]);
+        const float val = ld_act(src + i);
         hb[i] = val;
         ss += val * val;
     }
@@ -202,7 +202,7 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
                                       fq.cos_t, fq.sin_t, fq.rot, t, lane);
                 } else {
                     const __nv_bfloat16* src = fq.v + (size_t)t * fq.v_stride + (size_t)kvh * hd;
-                    for (int i = lane; i < hd; i += 32) hb[i] = __bfloat162float(src[i]);
+                    for (int i = lane; i < hd; i += 32) hb[i] = ld_act(src + i);
                     __syncwarp();
                 }
                 __nv_bfloat16* cache_row = (is_k ? fq.k_cache_w : fq.v_cache_w) + ((size_t)slot * nkv + kvh) * hd;

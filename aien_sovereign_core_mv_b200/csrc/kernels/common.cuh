@@ -81,6 +81,23 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// What an earlier kernel of the step wrote must be read with these in a kernel launched with
+// launch_chain: a pointer that the compiler can prove read-only (const, no aliasing store) gets
+// ld.global.nc loads, which the assembler may move above griddepcontrol.wait, where the producer
+// may still be running (seen: the q/k kernel read stale projections).  ld.global.cg is never moved.
+__device__ __forceinline__ float ld_act(const float* p) { return __ldcg(p); }
+__device__ __forceinline__ float ld_act(const __nv_bfloat16* p) {
+    const unsigned short b = __ldcg(reinterpret_cast<const unsigned short*>(p));
+    return __bfloat162float(__ushort_as_bfloat16(b));
+}
+__device__ __forceinline__ float4 ld_act4(const float* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ float4 ld_act4(const __nv_bfloat16* p) {
+    const uint2 r = __ldcg(reinterpret_cast<const uint2*>(p));
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
 inline bool pdl_enabled() {
     static int v = -1;
     if (v < 0) {

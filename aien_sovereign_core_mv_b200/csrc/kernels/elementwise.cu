@@ -30,7 +30,7 @@ __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __r
 template <typename TD>
 __device__ __forceinline__ float delta_sum(const TD* __restrict__ delta, int nparts, size_t part_stride, size_t idx) {
     float d = 0.f;
-    for (int p = 0; p < nparts; ++p) d += to_f(delta[(size_t)p * part_stride + idx]);
+    for (int p = 0; p < nparts; ++p) d += ld_act(delta + (size_t)p * part_stride + idx);
     return d;
 }
 
@@ -106,7 +106,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int 
 #pragma unroll
             for (int j = 0; j < NV; ++j) {
                 const int i = (j * 256 + threadIdx.x) * 4;
-                dv[j] = i < H ? load4(delta + base + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                dv[j] = i < H ? ld_act4(delta + base + i) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
 #pragma unroll
             for (int j = 0; j < NV; ++j) { v[j].x += dv[j].x; v[j].y += dv[j].y; v[j].z += dv[j].z; v[j].w += dv[j].w; }
@@ -116,7 +116,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int 
                 for (int j = 0; j < NV; ++j) {
                     const int i = (j * 256 + threadIdx.x) * 4;
                     if (i < H) {
-                        const float4 d = load4(delta + (size_t)p * part_stride + base + i);
+                        const float4 d = ld_act4(delta + (size_t)p * part_stride + base + i);
                         v[j].x += d.x; v[j].y += d.y; v[j].z += d.z; v[j].w += d.w;
                     }
                 }
@@ -147,7 +147,7 @@ __global__ void gather_add_rows_kernel(const float* __restrict__ x, const TD* __
     griddep_wait();
     const size_t src = (size_t)rows[blockIdx.x] * H, dst = (size_t)blockIdx.x * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float v = x[src + i];
+        float v = ld_act(x + src + i);
         if (delta != nullptr) v += delta_sum(delta, nparts, part_stride, src + i);
         out[dst + i] = v;
     }
@@ -168,8 +168,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
         size_t gi, ui;
         if (group == 0) { gi = i; ui = I + i; }
         else { gi = (i / group) * 2 * group + (i % group); ui = gi + group; }
-        const float g = to_f(gu[t * 2 * I + gi]);
-        const float u = to_f(gu[t * 2 * I + ui]);
+        const float g = ld_act(gu + t * 2 * I + gi);
+        const float u = ld_act(gu + t * 2 * I + ui);
         out[idx] = from_f<T>(g / (1.0f + expf(-g)) * u);
     }
 }
@@ -211,7 +211,7 @@ qk_norm_rope_kv_write_kernel(
     const int n_heads = nq + (write_kv ? 2 * nkv : 0);
     const int head = blockIdx.y * 4 + warp;
     if (head >= n_heads) return;
-    const long slot = write_kv ? (long)slot_map[t] : -1;
+    const long slot = write_kv ? (long)__ldcg(slot_map + t) : -1;
     float* hb = buf[warp];
     const bool is_q = head < nq;
     const bool is_k = !is_q && head < nq + nkv;
@@ -223,7 +223,7 @@ qk_norm_rope_kv_write_kernel(
     float ss = 0.f;
     for (int i = lane; i < hd; i += 32) {
         float val = 0.f;
-        for (int p = 0; p < nparts; ++p) val += to_f(src[(size_t)p * part_stride + i]);
+        for (int p = 0; p < nparts; ++p) val += ld_act(src + (size_t)p * part_stride + i);
         hb[i] = val;
         ss += val * val;
     }
@@ -239,7 +239,7 @@ qk_norm_rope_kv_write_kernel(
         if (cos_t != nullptr) {
             for (int i = lane; i < half; i += 32) {
                 const float a = hb[i], b = hb[i + half];
-                const float c = cos_t[(size_t)t * half + i], s = sin_t[(size_t)t * half + i];
+                const float c = __ldcg(cos_t + (size_t)t * half + i), s = __ldcg(sin_t + (size_t)t * half + i);
                 hb[i] = a * c - b * s;
                 hb[i + half] = a * s + b * c;
             }
@@ -261,10 +261,20 @@ qk_norm_rope_kv_write_kernel(
 // its head at once, so that many independent loads are in flight; weights do not depend on the
 // kernel ahead and are requested before the wait for it.
 constexpr int QK_TOKENS = 4;
+__device__ __forceinline__ float4 qk_load4(const __nv_bfloat16* p, int, size_t) { return ld_act4(p); }
+__device__ __forceinline__ float4 qk_load4(const float* p, int nparts, size_t part_stride) {      // float32 partial products, added in order
+    float4 acc = ld_act4(p);
+    for (int i = 1; i < nparts; ++i) {
+        const float4 d = ld_act4(p + (size_t)i * part_stride);
+        acc.x += d.x; acc.y += d.y; acc.z += d.z; acc.w += d.w;
+    }
+    return acc;
+}
+template <typename TI>
 __global__ void __launch_bounds__(128)
 qk_norm_rope_kv_write_hd128_kernel(
-    const __nv_bfloat16* q, long q_stride, int nq, const __nv_bfloat16* __restrict__ k, long k_stride,
-    const __nv_bfloat16* __restrict__ v, long v_stride, int nkv, __nv_bfloat16* q_out, long q_out_stride,
+    const TI* q, long q_stride, int nq, const TI* __restrict__ k, long k_stride,
+    const TI* __restrict__ v, long v_stride, int nkv, int nparts, size_t part_stride, __nv_bfloat16* q_out, long q_out_stride,
     const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w, int wdt, float eps,
     const float* __restrict__ cos_t, const float* __restrict__ sin_t,
     const int* __restrict__ slot_map, __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int T) {
@@ -282,20 +292,20 @@ qk_norm_rope_kv_write_hd128_kernel(
     float4 wv = make_float4(1.f, 1.f, 1.f, 1.f);
     if (nw != nullptr) wv = load4_dyn(nw, wdt, lane * 4);
     griddep_wait();
-    const __nv_bfloat16* src_base = is_q ? q : (is_k ? k : v);
+    const TI* src_base = is_q ? q : (is_k ? k : v);
     const long src_stride = is_q ? q_stride : (is_k ? k_stride : v_stride);
     long slot[QK_TOKENS];
-    uint2 raw[QK_TOKENS];
+    float4 raw[QK_TOKENS];
     float4 cs[QK_TOKENS], sn[QK_TOKENS];
 #pragma unroll
     for (int j = 0; j < QK_TOKENS; ++j) {
         const int t = t0 + j;
         const bool live = t < T;
-        slot[j] = (write_kv && live) ? (long)slot_map[t] : -1;
-        raw[j] = live ? *reinterpret_cast<const uint2*>(src_base + (size_t)t * src_stride + (size_t)hh * 128 + lane * 4) : make_uint2(0u, 0u);
+        slot[j] = (write_kv && live) ? (long)__ldcg(slot_map + t) : -1;
+        raw[j] = live ? qk_load4(src_base + (size_t)t * src_stride + (size_t)hh * 128 + lane * 4, nparts, part_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
         if (rotate && live) {
-            cs[j] = load4(cos_t + (size_t)t * 64 + (lane & 15) * 4);
-            sn[j] = load4(sin_t + (size_t)t * 64 + (lane & 15) * 4);
+            cs[j] = ld_act4(cos_t + (size_t)t * 64 + (lane & 15) * 4);
+            sn[j] = ld_act4(sin_t + (size_t)t * 64 + (lane & 15) * 4);
         } else {
             cs[j] = make_float4(1.f, 1.f, 1.f, 1.f);
             sn[j] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -304,8 +314,7 @@ qk_norm_rope_kv_write_hd128_kernel(
 #pragma unroll
     for (int j = 0; j < QK_TOKENS; ++j) {
         const int t = t0 + j;
-        const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw[j].x), p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw[j].y);
-        float x0 = __low2float(p0), x1 = __high2float(p0), x2 = __low2float(p1), x3 = __high2float(p1);
+        float x0 = raw[j].x, x1 = raw[j].y, x2 = raw[j].z, x3 = raw[j].w;
         if (nw != nullptr) {
             const float ss = warp_sum(x0 * x0 + x1 * x1 + x2 * x2 + x3 * x3);
             const float scale = 1.0f / sqrtf(ss / 128.0f + eps);
@@ -391,14 +400,14 @@ scale_rows_ssq_kernel(const __nv_bfloat16* __restrict__ xw, long ld, const float
     const int t = blockIdx.x;
     if (threadIdx.x < 32) {
         float sq = 0.f;
-        for (int p = threadIdx.x >> 4; p < parts; p += 2) sq += (threadIdx.x & 15) == 0 ? ssq[(size_t)p * 16 + t] : 0.f;
+        for (int p = threadIdx.x >> 4; p < parts; p += 2) sq += (threadIdx.x & 15) == 0 ? __ldcg(ssq + (size_t)p * 16 + t) : 0.f;
         sq += __shfl_xor_sync(0xffffffffu, sq, 16);
         if (threadIdx.x == 0) s_r = 1.0f / sqrtf(sq / (float)H + eps);
     }
     __syncthreads();
     const float r = s_r;
     for (int i = threadIdx.x; i < H; i += blockDim.x)
-        out[(size_t)t * ldo + i] = __float2bfloat16_rn(__bfloat162float(xw[(size_t)t * ld + i]) * r);
+        out[(size_t)t * ldo + i] = __float2bfloat16_rn(ld_act(xw + (size_t)t * ld + i) * r);
 }
 
 AIEN_API int aien_scale_rows_ssq(const void* xw, long ld, const float* ssq, int parts, float eps, void* out, long ldo,
@@ -461,15 +470,23 @@ AIEN_API int aien_qk_norm_rope_kv_write(
     const int n_heads = nq + (k != nullptr ? 2 * nkv : 0);
     dim3 grid(T, (n_heads + 3) / 4);
     if (grid.y > 65535) return AIEN_E_SHAPE;
-    const bool a8 = (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 7) == 0 &&
-                    ((q_stride | k_stride | v_stride | q_out_stride) & 3) == 0 &&
-                    (((uintptr_t)q_norm_w | (uintptr_t)k_norm_w | (uintptr_t)cos_t | (uintptr_t)sin_t) & 15) == 0;
-    if (hd == 128 && nparts == 1 && in_dt == AIEN_DT_BF16 && act_dt == AIEN_DT_BF16 && (k == nullptr || kv_dt == AIEN_DT_BF16) &&
-        (cos_t == nullptr || rot == 128) && a8) {
-        launch_chain(qk_norm_rope_kv_write_hd128_kernel, dim3((T + QK_TOKENS - 1) / QK_TOKENS, grid.y), dim3(128), 0, stream,
-                     (const __nv_bfloat16*)q, q_stride, nq, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, nkv,
-                     (__nv_bfloat16*)q_out, q_out_stride, q_norm_w, k_norm_w, w_dt, eps, cos_t, sin_t, slot_map,
-                     (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, T);
+    const bool a16 = (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & (in_dt == AIEN_DT_F32 ? 15 : 7)) == 0 &&
+                     (((uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 7) == 0 &&
+                     ((q_stride | k_stride | v_stride | q_out_stride) & 3) == 0 && (part_stride & 3) == 0 &&
+                     (((uintptr_t)q_norm_w | (uintptr_t)k_norm_w | (uintptr_t)cos_t | (uintptr_t)sin_t) & 15) == 0;
+    if (hd == 128 && act_dt == AIEN_DT_BF16 && (k == nullptr || kv_dt == AIEN_DT_BF16) && (cos_t == nullptr || rot == 128) && a16 &&
+        ((in_dt == AIEN_DT_BF16 && nparts == 1) || in_dt == AIEN_DT_F32)) {
+        const dim3 fast_grid((T + QK_TOKENS - 1) / QK_TOKENS, grid.y);
+        if (in_dt == AIEN_DT_BF16)
+            launch_chain(qk_norm_rope_kv_write_hd128_kernel<__nv_bfloat16>, fast_grid, dim3(128), 0, stream,
+                         (const __nv_bfloat16*)q, q_stride, nq, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, nkv,
+                         nparts, part_stride, (__nv_bfloat16*)q_out, q_out_stride, q_norm_w, k_norm_w, w_dt, eps, cos_t, sin_t, slot_map,
+                         (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, T);
+        else
+            launch_chain(qk_norm_rope_kv_write_hd128_kernel<float>, fast_grid, dim3(128), 0, stream,
+                         (const float*)q, q_stride, nq, (const float*)k, k_stride, (const float*)v, v_stride, nkv,
+                         nparts, part_stride, (__nv_bfloat16*)q_out, q_out_stride, q_norm_w, k_norm_w, w_dt, eps, cos_t, sin_t, slot_map,
+                         (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, T);
         return launch_status();
     }
     AIEN_DISPATCH_DTYPE(in_dt, TI, AIEN_DISPATCH_DTYPE(act_dt, TC, AIEN_DISPATCH_DTYPE(kv_dt, TKV,

@@ -25,8 +25,9 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
                  : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
     return r;
 }
+// activations: written by the kernel ahead, so read with a load that stays behind griddep_wait()
 __device__ __forceinline__ uint4 ldg_cached(const void* p) {
-    return *reinterpret_cast<const uint4*>(p);
+    return __ldcg(reinterpret_cast<const uint4*>(p));
 }
 __device__ __forceinline__ void mma_bf16_16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {

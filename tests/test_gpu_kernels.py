@@ -484,6 +484,42 @@ def test_gemv_partial_products_and_their_consumers(K):
     H.assert_close(vc[[1, 5, 2], 0].float().cpu().numpy(), want[:, 2 * hd:3 * hd], 1e-2, "v from partials")
 
 
+def test_qk_kernel_head128_takes_partial_products(K):
+    """The vectorised q/k kernel on float32 partial products (what a product cut over K leaves):
+    sum, per-head norm, rotation, cache write, against the same values given whole in bfloat16."""
+    g = torch.Generator().manual_seed(3)
+    T, nq, nkv, hd, P = 7, 4, 2, 128, 3
+    width = (nq + 2 * nkv) * hd
+    parts = torch.randn(P, T, width, generator=g).cuda()
+    whole = parts.sum(0)
+    qw = (torch.rand(hd, generator=g) * 0.4 + 0.8).to(torch.bfloat16).cuda()
+    kw = (torch.rand(hd, generator=g) * 0.4 + 0.8).to(torch.bfloat16).cuda()
+    pos = [0, 3, 4, 100, 101, 2000, 7]
+    inv = pm.rope_inv_freq(hd, 10000.0)
+    cos = torch.empty(T, hd // 2, device="cuda"); sin = torch.empty(T, hd // 2, device="cuda")
+    K.rope_table(torch.tensor(pos, dtype=torch.int32).cuda(), torch.tensor(inv, dtype=torch.float64).cuda(), cos, sin)
+    slot_map = torch.tensor([5, 6, 39, 0, 17, -1, 8], dtype=torch.int32).cuda()
+    kc = torch.full((40, nkv, hd), 7.0, dtype=torch.bfloat16, device="cuda"); vc = torch.full_like(kc, 7.0)
+    q_out = torch.empty(T, nq * hd, dtype=torch.bfloat16, device="cuda")
+    K.qk_norm_rope_kv_write(parts[..., :nq * hd], parts[..., nq * hd:(nq + nkv) * hd], parts[..., (nq + nkv) * hd:], hd, qw, kw, 1e-6,
+                            cos, sin, hd, slot_map, kc, vc, q_out=q_out)
+    w64 = whole.double().cpu().numpy()
+
+    def ref(x, heads, w):
+        x = pm.rms_norm(x.reshape(T, heads, hd), w.float().cpu().numpy().astype(np.float64), 1e-6)
+        return pm.apply_rope(x, pos, inv)
+    H.assert_close(q_out.float().cpu().numpy().reshape(T, nq, hd), ref(w64[:, :nq * hd], nq, qw), 1e-2, "q from partials, head 128")
+    kref = ref(w64[:, nq * hd:(nq + nkv) * hd], nkv, kw)
+    vref = w64[:, (nq + nkv) * hd:].reshape(T, nkv, hd)
+    sm = slot_map.cpu().numpy()
+    for t in range(T):
+        if sm[t] >= 0:
+            H.assert_close(kc[sm[t]].float().cpu().numpy(), kref[t], 1e-2, f"k token {t}")
+            H.assert_close(vc[sm[t]].float().cpu().numpy(), vref[t], 1e-2, f"v token {t}")
+    untouched = [s_ for s_ in range(40) if s_ not in set(sm.tolist())]
+    assert (kc[untouched] == 7.0).all() and (vc[untouched] == 7.0).all()
+
+
 def test_swiglu_interleaved_layout(K):
     g = torch.Generator().manual_seed(4)
     T, I = 3, 40
