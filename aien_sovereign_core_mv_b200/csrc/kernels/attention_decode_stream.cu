@@ -85,6 +85,7 @@ paged_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     const int G = nq / nkv;
     const long total = (long)segs * T * nkv;      // segs: segments per (token, kv head)
 
+    griddep_launch();
     if (tid == 0) {
         for (int i = 0; i < DS_SLOTS; ++i) { mbar_init(full0 + 8 * i, 1); mbar_init(empty0 + 8 * i, DS_MATH_WARPS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -95,8 +96,32 @@ paged_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
         // ------------------------------------------------------------------ producer
         const int pages_per_chunk = DS_CHUNK / page_size;
         int item = 0, kc = 0;                                     // ring items issued, K items issued
+        // The kernel ahead in the step writes the query rows and, in the caches, the row of each
+        // token's own position; everything else this kernel reads (positions, block tables, keys of
+        // earlier positions) was complete before the step's first kernel began.  So the producer
+        // fills the ring with chunks that end before the token's position while the kernel ahead is
+        // still running, and waits for it only before the first chunk that holds the position, or when
+        // the ring is full; the query copies of the items issued by then follow the wait.  No thread
+        // writes global memory before a query has arrived.
+        bool waited = false;
+        int npend = 0;
+        const __nv_bfloat16* pend_src0 = nullptr; const __nv_bfloat16* pend_src1 = nullptr;
+        uint32_t pend_dst0 = 0, pend_dst1 = 0, pend_bar0 = 0, pend_bar1 = 0;
+        auto sync_ahead = [&]() {
+            if (waited) return;
+            griddep_wait();
+            waited = true;
+            if (lane == 0) {
+                if (npend > 0) ds_bulk_copy(pend_dst0, pend_src0, (uint32_t)(G * HD * 2), pend_bar0);
+                if (npend > 1) ds_bulk_copy(pend_dst1, pend_src1, (uint32_t)(G * HD * 2), pend_bar1);
+            }
+            npend = 0;
+        };
         auto acquire = [&](int it) {
-            if (it >= DS_SLOTS) mbar_wait(empty0 + 8 * (it % DS_SLOTS), ((it / DS_SLOTS) - 1) & 1, 1);
+            if (it >= DS_SLOTS) {
+                sync_ahead();                                     // the math warps cannot free a slot without a query
+                mbar_wait(empty0 + 8 * (it % DS_SLOTS), ((it / DS_SLOTS) - 1) & 1, 1);
+            }
         };
         for (long w = blockIdx.x; w < total; w += gridDim.x) {
             // w = (seg * T + zt) * nkv + kvh: neighbours in the order share a token
@@ -123,6 +148,7 @@ paged_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                     }
                 }
                 // K item: meta, the query rows, the K pages
+                if (c == s_hi || npend == 2) sync_ahead();
                 acquire(item);
                 const int slot_k = item % DS_SLOTS;
                 if (lane == 0) {
@@ -133,8 +159,12 @@ paged_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                     m.seg_chunks = (c == c_end) ? (c_end - c_begin + 1) : 0;
                     meta[kc & 1] = m;
                     mbar_expect_tx(full0 + 8 * slot_k, TILE + (uint32_t)(G * HD * 2));
-                    ds_bulk_copy(q_u + (kc & 1) * QBUF, q + (size_t)t * q_stride + (size_t)kvh * G * HD, (uint32_t)(G * HD * 2), full0 + 8 * slot_k);
+                    const __nv_bfloat16* q_src = q + (size_t)t * q_stride + (size_t)kvh * G * HD;
+                    if (waited) ds_bulk_copy(q_u + (kc & 1) * QBUF, q_src, (uint32_t)(G * HD * 2), full0 + 8 * slot_k);
+                    else if (npend == 0) { pend_src0 = q_src; pend_dst0 = q_u + (kc & 1) * QBUF; pend_bar0 = full0 + 8 * slot_k; }
+                    else { pend_src1 = q_src; pend_dst1 = q_u + (kc & 1) * QBUF; pend_bar1 = full0 + 8 * slot_k; }
                 }
+                if (!waited) ++npend;
                 __syncwarp();
                 if (lane < pages_per_chunk)
                     for (int h = 0; h < HALVES; ++h)
@@ -153,6 +183,7 @@ paged_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                 ++item;
             }
         }
+        sync_ahead();
         // the end mark travels like a K item
         acquire(item);
         if (lane == 0) {
@@ -361,9 +392,9 @@ static int launch_decode_stream(const CUtensorMap& mk, const CUtensorMap& mv, co
     if (const char* e = getenv("AIEN_B200_DECODE_SEGMENTS")) { const int v = atoi(e); if (v > 0 && v <= max_splits) segs = v; }
     const long total = (long)segs * T * nkv;
     const unsigned grid = (unsigned)(total < slots ? total : slots);
-    kern<<<grid, DS_THREADS, smem, stream>>>(mk, mv, (const __nv_bfloat16*)q, q_stride, bt, max_blocks, seq_of_token, positions, token_list,
-                                             part_out, part_ml, counters, (__nv_bfloat16*)out, out_stride, nq, nkv, page_size, window, scale,
-                                             max_splits, T, segs, cache_rows, (int)misc_bytes);
+    launch_chain(kern, dim3(grid), dim3(DS_THREADS), smem, stream, mk, mv, (const __nv_bfloat16*)q, q_stride, bt, max_blocks, seq_of_token,
+                 positions, token_list, part_out, part_ml, counters, (__nv_bfloat16*)out, out_stride, nq, nkv, page_size, window, scale,
+                 max_splits, T, segs, cache_rows, (int)misc_bytes);
     return launch_status();
 }
 
