@@ -80,7 +80,8 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
 // Same, for H % 4 == 0 and H <= 256 * 4 * NV, all rows 16-byte aligned: the row stays in registers
 // between the passes, every access is a vector, and all loads of a thread (the row, the pending
 // sums, the weights) are issued before the first use.
-template <typename TD, typename TO, int NV>
+// PARTS: the pending sum comes in several parts (the register budget of that case is its own).
+template <typename TD, typename TO, int NV, bool PARTS>
 __global__ void __launch_bounds__(256)
 add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int nparts, size_t part_stride,
                        const void* __restrict__ w, int wdt, float eps, TO* __restrict__ h, int H) {
@@ -101,7 +102,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int 
         v[j] = i < H ? load4(x + base + i) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     if (delta != nullptr) {
-        if (nparts == 1) {
+        if (!PARTS) {
             float4 dv[NV];
 #pragma unroll
             for (int j = 0; j < NV; ++j) {
@@ -111,15 +112,27 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int 
 #pragma unroll
             for (int j = 0; j < NV; ++j) { v[j].x += dv[j].x; v[j].y += dv[j].y; v[j].z += dv[j].z; v[j].w += dv[j].w; }
         } else {
-            for (int p = 0; p < nparts; ++p) {
+            // four parts are requested at once (the loads of a part do not wait for the sums of the one
+            // before); they are added in index order
+            constexpr int PU = NV <= 4 ? 4 : 2;
+            for (int p0 = 0; p0 < nparts; p0 += PU) {
+                float4 d[PU][NV];
 #pragma unroll
-                for (int j = 0; j < NV; ++j) {
-                    const int i = (j * 256 + threadIdx.x) * 4;
-                    if (i < H) {
-                        const float4 d = ld_act4(delta + (size_t)p * part_stride + base + i);
-                        v[j].x += d.x; v[j].y += d.y; v[j].z += d.z; v[j].w += d.w;
+                for (int pp = 0; pp < PU; ++pp)
+#pragma unroll
+                    for (int j = 0; j < NV; ++j) {
+                        const int i = (j * 256 + threadIdx.x) * 4;
+                        if (p0 + pp < nparts && i < H) d[pp][j] = ld_act4(delta + (size_t)(p0 + pp) * part_stride + base + i);
                     }
-                }
+#pragma unroll
+                for (int pp = 0; pp < PU; ++pp)
+                    if (p0 + pp < nparts) {
+#pragma unroll
+                        for (int j = 0; j < NV; ++j) {
+                            const int i = (j * 256 + threadIdx.x) * 4;
+                            if (i < H) { v[j].x += d[pp][j].x; v[j].y += d[pp][j].y; v[j].z += d[pp][j].z; v[j].w += d[pp][j].w; }
+                        }
+                    }
             }
         }
     }
@@ -261,15 +274,6 @@ qk_norm_rope_kv_write_kernel(
 // its head at once, so that many independent loads are in flight; weights do not depend on the
 // kernel ahead and are requested before the wait for it.
 constexpr int QK_TOKENS = 4;
-__device__ __forceinline__ float4 qk_load4(const __nv_bfloat16* p, int, size_t) { return ld_act4(p); }
-__device__ __forceinline__ float4 qk_load4(const float* p, int nparts, size_t part_stride) {      // float32 partial products, added in order
-    float4 acc = ld_act4(p);
-    for (int i = 1; i < nparts; ++i) {
-        const float4 d = ld_act4(p + (size_t)i * part_stride);
-        acc.x += d.x; acc.y += d.y; acc.z += d.z; acc.w += d.w;
-    }
-    return acc;
-}
 template <typename TI>
 __global__ void __launch_bounds__(128)
 qk_norm_rope_kv_write_hd128_kernel(
@@ -302,13 +306,34 @@ qk_norm_rope_kv_write_hd128_kernel(
         const int t = t0 + j;
         const bool live = t < T;
         slot[j] = (write_kv && live) ? (long)__ldcg(slot_map + t) : -1;
-        raw[j] = live ? qk_load4(src_base + (size_t)t * src_stride + (size_t)hh * 128 + lane * 4, nparts, part_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+        raw[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (sizeof(TI) == 2 && live) raw[j] = ld_act4(src_base + (size_t)t * src_stride + (size_t)hh * 128 + lane * 4);
         if (rotate && live) {
             cs[j] = ld_act4(cos_t + (size_t)t * 64 + (lane & 15) * 4);
             sn[j] = ld_act4(sin_t + (size_t)t * 64 + (lane & 15) * 4);
         } else {
             cs[j] = make_float4(1.f, 1.f, 1.f, 1.f);
             sn[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    if (sizeof(TI) == 4) {
+        // float32 partial products: three parts of all the tokens are requested at once and added in index order
+        constexpr int PU = 3;
+        for (int p0 = 0; p0 < nparts; p0 += PU) {
+            float4 d[PU][QK_TOKENS];
+#pragma unroll
+            for (int pp = 0; pp < PU; ++pp)
+#pragma unroll
+                for (int j = 0; j < QK_TOKENS; ++j)
+                    if (p0 + pp < nparts && t0 + j < T)
+                        d[pp][j] = ld_act4(src_base + (size_t)(p0 + pp) * part_stride + (size_t)(t0 + j) * src_stride + (size_t)hh * 128 + lane * 4);
+#pragma unroll
+            for (int pp = 0; pp < PU; ++pp)
+                if (p0 + pp < nparts) {
+#pragma unroll
+                    for (int j = 0; j < QK_TOKENS; ++j)
+                        if (t0 + j < T) { raw[j].x += d[pp][j].x; raw[j].y += d[pp][j].y; raw[j].z += d[pp][j].z; raw[j].w += d[pp][j].w; }
+                }
         }
     }
 #pragma unroll
@@ -368,14 +393,22 @@ static void launch_add_rmsnorm(float* x, const TD* delta, int nparts, size_t par
                                float eps, TO* h, int T, int H, cudaStream_t stream) {
     const bool vec = (H % 4 == 0) && (((uintptr_t)x & 15) == 0) && (((uintptr_t)delta & 15) == 0) && (((uintptr_t)h & 15) == 0) &&
                      (((uintptr_t)w & 15) == 0) && (part_stride % 4 == 0);
+#define VEC_CASE(NV)                                                                                                              \
+    do {                                                                                                                          \
+        if (delta != nullptr && nparts > 1)                                                                                       \
+            launch_chain(add_rmsnorm_vec_kernel<TD, TO, NV, true>, dim3(T), dim3(256), 0, stream, x, delta, nparts, part_stride, w, w_dt, eps, h, H); \
+        else                                                                                                                      \
+            launch_chain(add_rmsnorm_vec_kernel<TD, TO, NV, false>, dim3(T), dim3(256), 0, stream, x, delta, nparts, part_stride, w, w_dt, eps, h, H); \
+    } while (0)
     if (vec && H <= 256 * 4 * 2)
-        launch_chain(add_rmsnorm_vec_kernel<TD, TO, 2>, dim3(T), dim3(256), 0, stream, x, delta, nparts, part_stride, w, w_dt, eps, h, H);
+        VEC_CASE(2);
     else if (vec && H <= 256 * 4 * 4)
-        launch_chain(add_rmsnorm_vec_kernel<TD, TO, 4>, dim3(T), dim3(256), 0, stream, x, delta, nparts, part_stride, w, w_dt, eps, h, H);
+        VEC_CASE(4);
     else if (vec && H <= 256 * 4 * 8)
-        launch_chain(add_rmsnorm_vec_kernel<TD, TO, 8>, dim3(T), dim3(256), 0, stream, x, delta, nparts, part_stride, w, w_dt, eps, h, H);
+        VEC_CASE(8);
     else
         launch_chain(add_rmsnorm_kernel<TD, TO>, dim3(T), dim3(row_threads(H)), 0, stream, x, delta, nparts, part_stride, w, w_dt, eps, h, H);
+#undef VEC_CASE
 }
 
 // delta: [nparts][T][H] (nparts >= 1; part_stride in elements) or null
