@@ -26,9 +26,17 @@
 
 namespace aien {
 
-constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64, TC_STAGES = 3;
-constexpr int TC_STAGE_A = TC_BM * TC_BK * 2, TC_STAGE_B = TC_BN * TC_BK * 2;
-constexpr int TC_SMEM = TC_STAGES * (TC_STAGE_A + TC_STAGE_B) + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64;
+constexpr int TC_STAGE_B = TC_BN * TC_BK * 2;
+// AR rows of A are brought in per k-block (128, or 64 / 32 when M is that small: the MMA still reads
+// 128 rows, the rest being whatever follows in shared memory; a row of the result depends on its
+// own row of A only, and rows beyond M are never stored).  The shared memory this saves holds more
+// stages of W, which is what a product with few rows waits for.
+template <int AR> struct TcT {
+    static constexpr int STAGE_A = AR * TC_BK * 2;
+    static constexpr int STAGES = AR == 128 ? 3 : (AR == 64 ? 4 : 5);
+    static constexpr int SMEM = STAGES * (STAGE_A + TC_STAGE_B) + 1024 /*align*/ + 256 /*barriers*/;
+};
 
 // Stores 32 consecutive accumulator columns of one row: r holds columns n0+c0 .. +31 of row `row`.
 // EPI 0: as they are; EPI 1: silu(gate)*up over columns interleaved in runs of 8 (out has N/2 columns).
@@ -95,14 +103,15 @@ __device__ __forceinline__ void tc_store_chunk(const uint32_t r[32], TC* __restr
             }
 
 // EPI 0: store; EPI 1: silu(gate)*up over columns interleaved in runs of 8 (out has N/2 columns)
-template <int EPI, typename TC>
+template <int EPI, typename TC, int AR>
 __global__ void __launch_bounds__(192)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                TC* __restrict__ out, long ldc, size_t part_stride, int kb_per_split, int M, int N, int K) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    constexpr int TC_STAGES = TcT<AR>::STAGES, TC_STAGE_A = TcT<AR>::STAGE_A;
     const uint32_t sA = base, sB = base + TC_STAGES * TC_STAGE_A;
-    const uint32_t bars = sB + TC_STAGES * TC_STAGE_B;     // full[3], empty[3], tmem_full, then the tmem slot
+    const uint32_t bars = sB + TC_STAGES * TC_STAGE_B;     // full[], empty[], tmem_full, then the tmem slot
     const uint32_t full0 = bars, empty0 = bars + 8 * TC_STAGES, tmem_full = bars + 16 * TC_STAGES;
     const uint32_t tmem_slot = tmem_full + 8;
     uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
@@ -116,6 +125,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int num_kb = min((K + TC_BK - 1) / TC_BK - kb_first, kb_per_split);
     out += (size_t)blockIdx.z * part_stride;
 
+    griddep_launch();
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         mbar_init(tmem_full, 1);
@@ -132,10 +142,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < num_kb; ++kb) {
+            // The first ring of W is requested before waiting for the kernel ahead in the stream:
+            // weights do not depend on it; A does, and nothing is written before A has arrived.
+            const int ahead = min(num_kb, TC_STAGES);
+            for (int kb = 0; kb < ahead; ++kb) {
+                mbar_expect_tx(full0 + 8 * kb, TC_STAGE_A + TC_STAGE_B);
+                tma_load_2d(sB + kb * TC_STAGE_B, &map_w, full0 + 8 * kb, (kb_first + kb) * TC_BK, n0);
+            }
+            griddep_wait();
+            for (int kb = 0; kb < ahead; ++kb)
+                tma_load_2d(sA + kb * TC_STAGE_A, &map_a, full0 + 8 * kb, (kb_first + kb) * TC_BK, m0);
+            for (int kb = ahead; kb < num_kb; ++kb) {
                 const int s = kb % TC_STAGES;
                 const uint32_t round = kb / TC_STAGES;
-                if (kb >= TC_STAGES) mbar_wait(empty0 + 8 * s, (round - 1) & 1, 1);
+                mbar_wait(empty0 + 8 * s, (round - 1) & 1, 1);
                 mbar_expect_tx(full0 + 8 * s, TC_STAGE_A + TC_STAGE_B);
                 tma_load_2d(sA + s * TC_STAGE_A, &map_a, full0 + 8 * s, (kb_first + kb) * TC_BK, m0);
                 tma_load_2d(sB + s * TC_STAGE_B, &map_w, full0 + 8 * s, (kb_first + kb) * TC_BK, n0);
@@ -163,7 +183,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int row = m0 + quarter * 32 + lane;
 #pragma unroll 1
-        for (int c0 = 0; c0 < TC_BN; c0 += 32) {
+        for (int c0 = 0; c0 < TC_BN && m0 + quarter * 32 < M; c0 += 32) {      // a quarter beyond M has nothing to store
             uint32_t r[32];
             tmem_ld32(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -332,20 +352,32 @@ static int tc_plan(int M, int N) {
     return mt * ((N + 255) / 256) >= tc_num_sms() ? 256 : 0;
 }
 
-template <int EPI, typename TC>
-static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* out, long ldc, int splits, size_t part_stride,
-                     int M, int N, int K, cudaStream_t stream) {
-    auto kern = gemm_tc_kernel<EPI, TC>;
+static int tc_a_rows(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }
+
+template <int EPI, typename TC, int AR>
+static int launch_tc_rows(const CUtensorMap& ma, const CUtensorMap& mw, void* out, long ldc, int splits, size_t part_stride,
+                          int M, int N, int K, cudaStream_t stream) {
+    auto kern = gemm_tc_kernel<EPI, TC, AR>;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM) != cudaSuccess) return AIEN_E_STATE;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcT<AR>::SMEM) != cudaSuccess) return AIEN_E_STATE;
         configured = true;
     }
     const int total_kb = (K + TC_BK - 1) / TC_BK;
     const int kb_per_split = (total_kb + splits - 1) / splits;
     dim3 grid((M + TC_BM - 1) / TC_BM, (N + TC_BN - 1) / TC_BN, (total_kb + kb_per_split - 1) / kb_per_split);
-    kern<<<grid, 192, TC_SMEM, stream>>>(ma, mw, (TC*)out, ldc, part_stride, kb_per_split, M, N, K);
+    launch_chain(kern, grid, dim3(192), (size_t)TcT<AR>::SMEM, stream, ma, mw, (TC*)out, ldc, part_stride, kb_per_split, M, N, K);
     return launch_status();
+}
+
+// `ma` must have been made with a box of tc_a_rows(M) rows.
+template <int EPI, typename TC>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* out, long ldc, int splits, size_t part_stride,
+                     int M, int N, int K, cudaStream_t stream) {
+    const int ar = tc_a_rows(M);
+    if (ar == 32) return launch_tc_rows<EPI, TC, 32>(ma, mw, out, ldc, splits, part_stride, M, N, K, stream);
+    if (ar == 64) return launch_tc_rows<EPI, TC, 64>(ma, mw, out, ldc, splits, part_stride, M, N, K, stream);
+    return launch_tc_rows<EPI, TC, 128>(ma, mw, out, ldc, splits, part_stride, M, N, K, stream);
 }
 
 }  // namespace aien
@@ -383,7 +415,8 @@ AIEN_API int aien_gemm_tc(const void* A, long lda, const void* W, long ldw, void
 #undef TCP_CASE
     }
     CUtensorMap ma, mw;
-    if (!make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TC_BK, TC_BM) || !make_map(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, TC_BK, TC_BN))
+    if (!make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TC_BK, (uint32_t)tc_a_rows(M)) ||
+        !make_map(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, TC_BK, TC_BN))
         return AIEN_E_STATE;
     if (epilogue == 0) {
         if (c_dt == AIEN_DT_BF16) return launch_tc<0, __nv_bfloat16>(ma, mw, out, ldc, 1, 0, M, N, K, stream);
