@@ -27,15 +27,17 @@
 namespace aien {
 
 constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64;
-constexpr int TC_STAGE_B = TC_BN * TC_BK * 2;
 // AR rows of A are brought in per k-block (128, or 64 / 32 when M is that small: the MMA still reads
 // 128 rows, the rest being whatever follows in shared memory; a row of the result depends on its
 // own row of A only, and rows beyond M are never stored).  The shared memory this saves holds more
 // stages of W, which is what a product with few rows waits for.
-template <int AR> struct TcT {
-    static constexpr int STAGE_A = AR * TC_BK * 2;
-    static constexpr int STAGES = AR == 128 ? 3 : (AR == 64 ? 4 : 5);
-    static constexpr int SMEM = STAGES * (STAGE_A + TC_STAGE_B) + 1024 /*align*/ + 256 /*barriers*/;
+// BN rows of W per tile: 128, or 96 where that spreads a product without split-K more evenly over
+// the SMs (tc_tile_cols).  Two CTAs share an SM in every case.
+template <int AR, int BN> struct TcT {
+    static constexpr int STAGE_A = AR * TC_BK * 2, STAGE_B = BN * TC_BK * 2;
+    static constexpr int STAGES = (100 * 1024) / (STAGE_A + STAGE_B);        // BN 128: 3 / 4 / 5 for AR 128 / 64 / 32
+    static constexpr int SMEM = STAGES * (STAGE_A + STAGE_B) + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr int TMEM_COLS = BN <= 64 ? 64 : 128;
 };
 
 // Stores 32 consecutive accumulator columns of one row: r holds columns n0+c0 .. +31 of row `row`.
@@ -103,13 +105,14 @@ __device__ __forceinline__ void tc_store_chunk(const uint32_t r[32], TC* __restr
             }
 
 // EPI 0: store; EPI 1: silu(gate)*up over columns interleaved in runs of 8 (out has N/2 columns)
-template <int EPI, typename TC, int AR>
+template <int EPI, typename TC, int AR, int BN>
 __global__ void __launch_bounds__(192)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                TC* __restrict__ out, long ldc, size_t part_stride, int kb_per_split, int M, int N, int K) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    constexpr int TC_STAGES = TcT<AR>::STAGES, TC_STAGE_A = TcT<AR>::STAGE_A;
+    constexpr int TC_STAGES = TcT<AR, BN>::STAGES, TC_STAGE_A = TcT<AR, BN>::STAGE_A, TC_STAGE_B = TcT<AR, BN>::STAGE_B;
+    constexpr int TC_BN = BN;
     const uint32_t sA = base, sB = base + TC_STAGES * TC_STAGE_A;
     const uint32_t bars = sB + TC_STAGES * TC_STAGE_B;     // full[], empty[], tmem_full, then the tmem slot
     const uint32_t full0 = bars, empty0 = bars + 8 * TC_STAGES, tmem_full = bars + 16 * TC_STAGES;
@@ -132,7 +135,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)TC_BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)TcT<AR, BN>::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -195,7 +198,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)TC_BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)TcT<AR, BN>::TMEM_COLS) : "memory");
     }
 }
 
@@ -354,30 +357,50 @@ static int tc_plan(int M, int N) {
 
 static int tc_a_rows(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }
 
-template <int EPI, typename TC, int AR>
+// Rows of W per tile.  The CTAs of a launch all run at once (two per SM), and the launch ends when
+// the SM with the most rows of W has streamed them: ceil(tiles / SMs) * rows.  96 instead of 128
+// where that is less (24,576 rows over 148 SMs: 256 tiles, two each = 192 rows, against 192 tiles,
+// some SMs two = 256 rows).  Only without split-K and with 64 rows of A at most.
+static int tc_tile_cols(int M, int N, int splits) {
+    if (splits != 1 || M > 64) return 128;
+    const long sms = tc_num_sms();
+    const long t128 = (N + 127) / 128, t96 = (N + 95) / 96;
+    if (t96 > 2 * sms) return 128;
+    return ((t96 + sms - 1) / sms) * 96 < ((t128 + sms - 1) / sms) * 128 ? 96 : 128;
+}
+
+template <int EPI, typename TC, int AR, int BN>
 static int launch_tc_rows(const CUtensorMap& ma, const CUtensorMap& mw, void* out, long ldc, int splits, size_t part_stride,
                           int M, int N, int K, cudaStream_t stream) {
-    auto kern = gemm_tc_kernel<EPI, TC, AR>;
+    auto kern = gemm_tc_kernel<EPI, TC, AR, BN>;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcT<AR>::SMEM) != cudaSuccess) return AIEN_E_STATE;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcT<AR, BN>::SMEM) != cudaSuccess) return AIEN_E_STATE;
         configured = true;
     }
     const int total_kb = (K + TC_BK - 1) / TC_BK;
     const int kb_per_split = (total_kb + splits - 1) / splits;
-    dim3 grid((M + TC_BM - 1) / TC_BM, (N + TC_BN - 1) / TC_BN, (total_kb + kb_per_split - 1) / kb_per_split);
-    launch_chain(kern, grid, dim3(192), (size_t)TcT<AR>::SMEM, stream, ma, mw, (TC*)out, ldc, part_stride, kb_per_split, M, N, K);
+    dim3 grid((M + TC_BM - 1) / TC_BM, (N + BN - 1) / BN, (total_kb + kb_per_split - 1) / kb_per_split);
+    launch_chain(kern, grid, dim3(192), (size_t)TcT<AR, BN>::SMEM, stream, ma, mw, (TC*)out, ldc, part_stride, kb_per_split, M, N, K);
     return launch_status();
 }
 
-// `ma` must have been made with a box of tc_a_rows(M) rows.
+// The tensor maps are made here: their boxes follow the tile (tc_a_rows(M) rows of A, 128 or 96 of W).
 template <int EPI, typename TC>
-static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* out, long ldc, int splits, size_t part_stride,
+static int launch_tc(const void* A, long lda, const void* W, long ldw, void* out, long ldc, int splits, size_t part_stride,
                      int M, int N, int K, cudaStream_t stream) {
-    const int ar = tc_a_rows(M);
-    if (ar == 32) return launch_tc_rows<EPI, TC, 32>(ma, mw, out, ldc, splits, part_stride, M, N, K, stream);
-    if (ar == 64) return launch_tc_rows<EPI, TC, 64>(ma, mw, out, ldc, splits, part_stride, M, N, K, stream);
-    return launch_tc_rows<EPI, TC, 128>(ma, mw, out, ldc, splits, part_stride, M, N, K, stream);
+    const int ar = tc_a_rows(M), bn = tc_tile_cols(M, N, splits);
+    CUtensorMap ma, mw;
+    if (!make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TC_BK, (uint32_t)ar) ||
+        !make_map(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, TC_BK, (uint32_t)bn))
+        return AIEN_E_STATE;
+    if (bn == 96) {
+        if (ar == 32) return launch_tc_rows<EPI, TC, 32, 96>(ma, mw, out, ldc, splits, part_stride, M, N, K, stream);
+        return launch_tc_rows<EPI, TC, 64, 96>(ma, mw, out, ldc, splits, part_stride, M, N, K, stream);
+    }
+    if (ar == 32) return launch_tc_rows<EPI, TC, 32, 128>(ma, mw, out, ldc, splits, part_stride, M, N, K, stream);
+    if (ar == 64) return launch_tc_rows<EPI, TC, 64, 128>(ma, mw, out, ldc, splits, part_stride, M, N, K, stream);
+    return launch_tc_rows<EPI, TC, 128, 128>(ma, mw, out, ldc, splits, part_stride, M, N, K, stream);
 }
 
 }  // namespace aien
@@ -402,7 +425,7 @@ AIEN_API int aien_gemm_tc(const void* A, long lda, const void* W, long ldw, void
     if (splits > 1 && (epilogue != 0 || c_dt != AIEN_DT_F32)) return AIEN_E_SHAPE;
     if ((lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return AIEN_E_ALIGN;
     if (epilogue == 1 && (N & 15)) return AIEN_E_SHAPE;
-    if ((M + TC_BM - 1) / TC_BM > 2147483647 / 1 || (N + TC_BN - 1) / TC_BN > 65535) return AIEN_E_SHAPE;
+    if ((M + TC_BM - 1) / TC_BM > 2147483647 / 1 || (N + 95) / 96 > 65535) return AIEN_E_SHAPE;
     if (splits == 1 && (epilogue == 0 || epilogue == 1)) {
         const int plan = tc_plan(M, N);
 #define TCP_CASE(BNV, EPIV, T) return launch_tc_persistent<BNV, EPIV, T>(A, lda, W, ldw, out, ldc, M, N, K, stream)
@@ -414,18 +437,14 @@ AIEN_API int aien_gemm_tc(const void* A, long lda, const void* W, long ldw, void
         }
 #undef TCP_CASE
     }
-    CUtensorMap ma, mw;
-    if (!make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TC_BK, (uint32_t)tc_a_rows(M)) ||
-        !make_map(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, TC_BK, TC_BN))
-        return AIEN_E_STATE;
     if (epilogue == 0) {
-        if (c_dt == AIEN_DT_BF16) return launch_tc<0, __nv_bfloat16>(ma, mw, out, ldc, 1, 0, M, N, K, stream);
-        if (c_dt == AIEN_DT_F32) return launch_tc<0, float>(ma, mw, out, ldc, splits, part_stride, M, N, K, stream);
+        if (c_dt == AIEN_DT_BF16) return launch_tc<0, __nv_bfloat16>(A, lda, W, ldw, out, ldc, 1, 0, M, N, K, stream);
+        if (c_dt == AIEN_DT_F32) return launch_tc<0, float>(A, lda, W, ldw, out, ldc, splits, part_stride, M, N, K, stream);
         return AIEN_E_DTYPE;
     }
     if (epilogue == 1) {
-        if (c_dt == AIEN_DT_BF16) return launch_tc<1, __nv_bfloat16>(ma, mw, out, ldc, 1, 0, M, N, K, stream);
-        if (c_dt == AIEN_DT_F32) return launch_tc<1, float>(ma, mw, out, ldc, 1, 0, M, N, K, stream);
+        if (c_dt == AIEN_DT_BF16) return launch_tc<1, __nv_bfloat16>(A, lda, W, ldw, out, ldc, 1, 0, M, N, K, stream);
+        if (c_dt == AIEN_DT_F32) return launch_tc<1, float>(A, lda, W, ldw, out, ldc, 1, 0, M, N, K, stream);
         return AIEN_E_DTYPE;
     }
     return AIEN_E_SHAPE;
