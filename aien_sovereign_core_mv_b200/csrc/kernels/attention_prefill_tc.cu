@@ -97,6 +97,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int kb_begin = first / PT_BN, kb_end = pos_last / PT_BN;
     const int nb = kb_end - kb_begin + 1;
 
+    griddep_launch();
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
         for (int i = 0; i < S::SLOTS; ++i) { mbar_init(kv_full0 + 8 * i, 1); mbar_init(kv_free0 + 8 * i, 1); }
@@ -116,6 +117,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
     if (warp == 8) {
         // ------------------------------------------------------------------ producer
+        // Queries and this step's rows of the caches come from the kernel ahead in the stream: with a
+        // dependent launch everything above ran beside its tail, and no other warp touches global
+        // memory before it has data from this one.
+        griddep_wait();
         if (lane == 0) {
             mbar_expect_tx(q_full, (has_b ? 2 : 1) * S::Q_BYTES);
             for (int h = 0; h < (has_b ? 2 : 1); ++h)
@@ -327,7 +332,7 @@ static int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mk, const
     const int heads_per_cta = (group >= 2 && (long)num_tiles * nkv * ((group + 1) / 2) >= sms) ? 2 : 1;
     const long ctas = (long)num_tiles * nkv * ((group + heads_per_cta - 1) / heads_per_cta);
     if (ctas > 2147483647L) return AIEN_E_SHAPE;
-    kern<<<(unsigned)ctas, PT_THREADS, PtShape<HD>::SMEM, stream>>>(mq, mk, mv, bt, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles,
+    launch_chain(kern, dim3((unsigned)ctas), dim3(PT_THREADS), (size_t)PtShape<HD>::SMEM, stream, mq, mk, mv, bt, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles,
                                                                      (__nv_bfloat16*)out, out_stride, nq, nkv, page_size, window,
                                                                      scale * 1.4426950408889634f, cache_rows, heads_per_cta);
     return launch_status();

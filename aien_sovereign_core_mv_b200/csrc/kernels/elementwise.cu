@@ -366,6 +366,94 @@ qk_norm_rope_kv_write_hd128_kernel(
     }
 }
 
+// The same for many tokens (a prompt portion): a CTA of eight warps takes QK_TOKENS tokens and all
+// their heads, warp w the heads w, w + 8, ...; the rotation table of the tokens is read once per
+// warp, and the rows of HB heads x QK_TOKENS tokens are requested before the first is used.
+template <int HB>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_kv_write_hd128_rows_kernel(
+    const __nv_bfloat16* q, long q_stride, int nq, const __nv_bfloat16* __restrict__ k, long k_stride,
+    const __nv_bfloat16* __restrict__ v, long v_stride, int nkv, __nv_bfloat16* q_out, long q_out_stride,
+    const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w, int wdt, float eps,
+    const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+    const int* __restrict__ slot_map, __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int T) {
+    griddep_launch();
+    const int t0 = blockIdx.x * QK_TOKENS, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const bool write_kv = (k != nullptr);
+    const int n_heads = nq + (write_kv ? 2 * nkv : 0);
+    float4 wq = make_float4(1.f, 1.f, 1.f, 1.f), wk = wq;
+    if (q_norm_w != nullptr) wq = load4_dyn(q_norm_w, wdt, lane * 4);
+    if (k_norm_w != nullptr) wk = load4_dyn(k_norm_w, wdt, lane * 4);
+    griddep_wait();
+    long slot[QK_TOKENS];
+    float4 cs[QK_TOKENS], sn[QK_TOKENS];
+#pragma unroll
+    for (int j = 0; j < QK_TOKENS; ++j) {
+        const int t = t0 + j;
+        const bool live = t < T;
+        slot[j] = (write_kv && live) ? (long)__ldcg(slot_map + t) : -1;
+        if (cos_t != nullptr && live) {
+            cs[j] = ld_act4(cos_t + (size_t)t * 64 + (lane & 15) * 4);
+            sn[j] = ld_act4(sin_t + (size_t)t * 64 + (lane & 15) * 4);
+        } else {
+            cs[j] = make_float4(1.f, 1.f, 1.f, 1.f);
+            sn[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    for (int h0 = warp; h0 < n_heads; h0 += 8 * HB) {
+        float4 raw[HB][QK_TOKENS];
+#pragma unroll
+        for (int u = 0; u < HB; ++u) {
+            const int head = h0 + 8 * u;
+            if (head < n_heads) {
+                const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
+                const int hh = is_q ? head : (is_k ? head - nq : head - nq - nkv);
+                const __nv_bfloat16* src = (is_q ? q : (is_k ? k : v)) + (size_t)hh * 128 + lane * 4;
+                const long stride = is_q ? q_stride : (is_k ? k_stride : v_stride);
+#pragma unroll
+                for (int j = 0; j < QK_TOKENS; ++j)
+                    raw[u][j] = (t0 + j < T) ? ld_act4(src + (size_t)(t0 + j) * stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < HB; ++u) {
+            const int head = h0 + 8 * u;
+            if (head >= n_heads) break;
+            const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
+            const int hh = is_q ? head : (is_k ? head - nq : head - nq - nkv);
+            const bool normed = is_q ? (q_norm_w != nullptr) : (is_k && k_norm_w != nullptr);
+            const float4 wv = is_q ? wq : wk;
+            const bool rotate = cos_t != nullptr && (is_q || is_k);
+#pragma unroll
+            for (int j = 0; j < QK_TOKENS; ++j) {
+                const int t = t0 + j;
+                float x0 = raw[u][j].x, x1 = raw[u][j].y, x2 = raw[u][j].z, x3 = raw[u][j].w;
+                if (normed) {
+                    const float ss = warp_sum(x0 * x0 + x1 * x1 + x2 * x2 + x3 * x3);
+                    const float scale = 1.0f / sqrtf(ss / 128.0f + eps);
+                    x0 = x0 * scale * wv.x; x1 = x1 * scale * wv.y; x2 = x2 * scale * wv.z; x3 = x3 * scale * wv.w;
+                }
+                if (rotate) {                                                      // the whole warp works on one head
+                    const float y0 = __shfl_xor_sync(0xffffffffu, x0, 16), y1 = __shfl_xor_sync(0xffffffffu, x1, 16);
+                    const float y2 = __shfl_xor_sync(0xffffffffu, x2, 16), y3 = __shfl_xor_sync(0xffffffffu, x3, 16);
+                    if (lane < 16) {
+                        x0 = x0 * cs[j].x - y0 * sn[j].x; x1 = x1 * cs[j].y - y1 * sn[j].y; x2 = x2 * cs[j].z - y2 * sn[j].z; x3 = x3 * cs[j].w - y3 * sn[j].w;
+                    } else {
+                        x0 = y0 * sn[j].x + x0 * cs[j].x; x1 = y1 * sn[j].y + x1 * cs[j].y; x2 = y2 * sn[j].z + x2 * cs[j].z; x3 = y3 * sn[j].w + x3 * cs[j].w;
+                    }
+                }
+                if (t >= T || (!is_q && slot[j] < 0)) continue;
+                __nv_bfloat162 o0 = __floats2bfloat162_rn(x0, x1), o1 = __floats2bfloat162_rn(x2, x3);
+                uint2 o;
+                o.x = *reinterpret_cast<uint32_t*>(&o0); o.y = *reinterpret_cast<uint32_t*>(&o1);
+                __nv_bfloat16* dst = is_q ? (q_out + (size_t)t * q_out_stride + (size_t)hh * 128)
+                                          : ((is_k ? k_cache : v_cache) + ((size_t)slot[j] * nkv + hh) * 128);
+                *reinterpret_cast<uint2*>(dst + lane * 4) = o;
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------- dtype conversion (load time)
 template <typename TI, typename TO>
 __global__ void convert_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
@@ -510,7 +598,12 @@ AIEN_API int aien_qk_norm_rope_kv_write(
     if (hd == 128 && act_dt == AIEN_DT_BF16 && (k == nullptr || kv_dt == AIEN_DT_BF16) && (cos_t == nullptr || rot == 128) && a16 &&
         ((in_dt == AIEN_DT_BF16 && nparts == 1) || in_dt == AIEN_DT_F32)) {
         const dim3 fast_grid((T + QK_TOKENS - 1) / QK_TOKENS, grid.y);
-        if (in_dt == AIEN_DT_BF16)
+        if (in_dt == AIEN_DT_BF16 && T >= 128)
+            launch_chain(qk_norm_rope_kv_write_hd128_rows_kernel<3>, dim3(fast_grid.x), dim3(256), 0, stream,
+                         (const __nv_bfloat16*)q, q_stride, nq, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, nkv,
+                         (__nv_bfloat16*)q_out, q_out_stride, q_norm_w, k_norm_w, w_dt, eps, cos_t, sin_t, slot_map,
+                         (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, T);
+        else if (in_dt == AIEN_DT_BF16)
             launch_chain(qk_norm_rope_kv_write_hd128_kernel<__nv_bfloat16>, fast_grid, dim3(128), 0, stream,
                          (const __nv_bfloat16*)q, q_stride, nq, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, nkv,
                          nparts, part_stride, (__nv_bfloat16*)q_out, q_out_stride, q_norm_w, k_norm_w, w_dt, eps, cos_t, sin_t, slot_map,

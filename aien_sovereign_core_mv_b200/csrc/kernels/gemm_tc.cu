@@ -235,6 +235,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     const int total = m_tiles * n_tiles;
     const int num_kb = (K + TC_BK - 1) / TC_BK;
 
+    griddep_launch();
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 4); }
@@ -251,11 +252,23 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 
     if (warp == 0) {
         if (lane == 0) {
+            // the first ring of W (of this CTA's first tile) goes out before the wait for the kernel
+            // ahead in the stream: A is its result, W is not
+            const uint32_t ahead = blockIdx.x < total ? (uint32_t)min(num_kb, STAGES) : 0u;
+            for (uint32_t kb = 0; kb < ahead; ++kb) {
+                mbar_expect_tx(full0 + 8 * kb, P::STAGE_A + P::STAGE_B);
+                tma_load_2d(sB + kb * P::STAGE_B, &map_w, full0 + 8 * kb, kb * TC_BK, (blockIdx.x / m_tiles) * BN);
+            }
+            griddep_wait();
             uint32_t it = 0;
             for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
                 const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
+                    if (it < ahead) {                                  // W is on its way already
+                        tma_load_2d(sA + s * P::STAGE_A, &map_a, full0 + 8 * s, kb * TC_BK, m0);
+                        continue;
+                    }
                     if (it >= (uint32_t)STAGES) mbar_wait(empty0 + 8 * s, ((it / STAGES) - 1) & 1, 1);
                     mbar_expect_tx(full0 + 8 * s, P::STAGE_A + P::STAGE_B);
                     tma_load_2d(sA + s * P::STAGE_A, &map_a, full0 + 8 * s, kb * TC_BK, m0);
@@ -336,7 +349,7 @@ static int launch_tc_persistent(const void* A, long lda, const void* W, long ldw
     }
     const long total = (long)((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
     const unsigned grid = (unsigned)(total < tc_num_sms() ? total : tc_num_sms());
-    kern<<<grid, 192, TcP<BN>::SMEM, stream>>>(ma, mw, (TC*)out, ldc, M, N, K);
+    launch_chain(kern, dim3(grid), dim3(192), (size_t)TcP<BN>::SMEM, stream, ma, mw, (TC*)out, ldc, M, N, K);
     return launch_status();
 }
 

@@ -139,6 +139,41 @@ def test_qk_norm_rope_kv_write(K, dtype, nq, nkv, hd, rot, norm):
     assert (kcn[untouched] == 7.0).all() and (vcn[untouched] == 7.0).all()     # a token without a slot writes nothing
 
 
+@pytest.mark.parametrize("nq,nkv,norm", [(5, 2, True), (8, 1, False), (16, 8, True)])
+def test_qk_kernel_head128_many_tokens(K, nq, nkv, norm):
+    """The prompt-portion form of the head-128 q/k kernel (128 tokens and more): a token count that
+    is no multiple of its group of four, head counts that are no multiple of its eight warps,
+    tokens without a cache slot, q rotated in place."""
+    g = torch.Generator().manual_seed(nq)
+    T, hd, slots = 131, 128, 200
+    qkv = torch.randn(T, (nq + 2 * nkv) * hd, generator=g).to(torch.bfloat16).cuda()
+    q, k, v = qkv[:, :nq * hd], qkv[:, nq * hd:(nq + nkv) * hd], qkv[:, (nq + nkv) * hd:]
+    qw = (torch.rand(hd, generator=g) * 0.4 + 0.8).to(torch.bfloat16).cuda() if norm else None
+    kw = (torch.rand(hd, generator=g) * 0.4 + 0.8).to(torch.bfloat16).cuda() if norm else None
+    pos = [(37 * t) % 5000 for t in range(T)]
+    inv = pm.rope_inv_freq(hd, 10000.0)
+    cos = torch.empty(T, hd // 2, device="cuda"); sin = torch.empty(T, hd // 2, device="cuda")
+    K.rope_table(torch.tensor(pos, dtype=torch.int32).cuda(), torch.tensor(inv, dtype=torch.float64).cuda(), cos, sin)
+    sm = np.array([-1 if t % 17 == 3 else (t * 7) % slots for t in range(T)], dtype=np.int32)
+    assert len(set(sm[sm >= 0].tolist())) == (sm >= 0).sum()
+    kc = torch.full((slots, nkv, hd), 7.0, dtype=torch.bfloat16, device="cuda"); vc = torch.full_like(kc, 7.0)
+    q0, k0, v0 = (t.float().cpu().numpy().astype(np.float64) for t in (q, k, v))
+    K.qk_norm_rope_kv_write(q, k, v, hd, qw, kw, 1e-6, cos, sin, hd, torch.tensor(sm).cuda(), kc, vc)
+
+    def ref(x, heads, w):
+        x = x.reshape(T, heads, hd)
+        if w is not None:
+            x = pm.rms_norm(x, w.float().cpu().numpy().astype(np.float64), 1e-6)
+        return pm.apply_rope(x, pos, inv)
+    H.assert_close(q.float().cpu().numpy().reshape(T, nq, hd), ref(q0, nq, qw), 1e-2, "q")
+    kref, kcn, vcn = ref(k0, nkv, kw), kc.float().cpu().numpy(), vc.float().cpu().numpy()
+    live = sm >= 0
+    H.assert_close(kcn[sm[live]], kref[live], 1e-2, "k rows")
+    H.assert_close(vcn[sm[live]], v0.reshape(T, nkv, hd)[live], 1e-2, "v rows")
+    untouched = [s_ for s_ in range(slots) if s_ not in set(sm.tolist())]
+    assert (kcn[untouched] == 7.0).all() and (vcn[untouched] == 7.0).all()
+
+
 def paged_setup(rng, seq_lens, nkv, hd, page, dtype, n_pages):
     """Random K/V for each request scattered over shuffled pages; returns caches, tables, dense copies."""
     perm = rng.permutation(n_pages)
