@@ -27,6 +27,7 @@ class EngineConfig:
     # execution
     use_cuda_graphs: bool = True       # replay captured graphs for decode-only steps
     async_scheduling: bool = True      # plan and launch step n+1 while step n runs; its tokens are fed on the device
+    replay_steps: bool = True          # a step shaped like an earlier one re-issues that step's launches as recorded
     seed: int = 0
 
     def resolved_dtype(self) -> str:

@@ -366,9 +366,10 @@ qk_norm_rope_kv_write_hd128_kernel(
     }
 }
 
-// The same for many tokens (a prompt portion): a CTA of eight warps takes QK_TOKENS tokens and all
-// their heads, warp w the heads w, w + 8, ...; the rotation table of the tokens is read once per
-// warp, and the rows of HB heads x QK_TOKENS tokens are requested before the first is used.
+// The same for many tokens (a prompt portion): a CTA of eight warps takes QK_TOKENS tokens and their
+// heads (all of them, or every gridDim.y-th group of eight), warp w the heads w, w + 8, ...; the
+// rotation table of the tokens is read once per warp, and the rows of HB heads x QK_TOKENS tokens
+// are requested before the first is used.
 template <int HB>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_kv_write_hd128_rows_kernel(
@@ -400,11 +401,13 @@ qk_norm_rope_kv_write_hd128_rows_kernel(
             sn[j] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
-    for (int h0 = warp; h0 < n_heads; h0 += 8 * HB) {
+    // heads of this warp: warp + 8 * (blockIdx.y + gridDim.y * i), i = 0, 1, ...; HB of them at a time
+    const int hstep = 8 * gridDim.y;
+    for (int h0 = warp + 8 * blockIdx.y; h0 < n_heads; h0 += hstep * HB) {
         float4 raw[HB][QK_TOKENS];
 #pragma unroll
         for (int u = 0; u < HB; ++u) {
-            const int head = h0 + 8 * u;
+            const int head = h0 + hstep * u;
             if (head < n_heads) {
                 const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
                 const int hh = is_q ? head : (is_k ? head - nq : head - nq - nkv);
@@ -417,7 +420,7 @@ qk_norm_rope_kv_write_hd128_rows_kernel(
         }
 #pragma unroll
         for (int u = 0; u < HB; ++u) {
-            const int head = h0 + 8 * u;
+            const int head = h0 + hstep * u;
             if (head >= n_heads) break;
             const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
             const int hh = is_q ? head : (is_k ? head - nq : head - nq - nkv);
@@ -598,8 +601,10 @@ AIEN_API int aien_qk_norm_rope_kv_write(
     if (hd == 128 && act_dt == AIEN_DT_BF16 && (k == nullptr || kv_dt == AIEN_DT_BF16) && (cos_t == nullptr || rot == 128) && a16 &&
         ((in_dt == AIEN_DT_BF16 && nparts == 1) || in_dt == AIEN_DT_F32)) {
         const dim3 fast_grid((T + QK_TOKENS - 1) / QK_TOKENS, grid.y);
+        // few tokens: the heads of a token group are shared out over two or four CTAs, so that the grid fills the GPU
+        const unsigned head_ctas = fast_grid.x >= 512 ? 1u : (fast_grid.x >= 256 || n_heads <= 16 ? 2u : 4u);
         if (in_dt == AIEN_DT_BF16 && T >= 128)
-            launch_chain(qk_norm_rope_kv_write_hd128_rows_kernel<3>, dim3(fast_grid.x), dim3(256), 0, stream,
+            launch_chain(qk_norm_rope_kv_write_hd128_rows_kernel<3>, dim3(fast_grid.x, head_ctas), dim3(256), 0, stream,
                          (const __nv_bfloat16*)q, q_stride, nq, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, nkv,
                          (__nv_bfloat16*)q_out, q_out_stride, q_norm_w, k_norm_w, w_dt, eps, cos_t, sin_t, slot_map,
                          (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, T);

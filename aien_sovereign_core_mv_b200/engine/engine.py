@@ -17,6 +17,8 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, List, Mapping, Optional, Sequence, Tuple
 
+import os
+
 import numpy as np
 import torch
 
@@ -25,7 +27,7 @@ from ..config.engine_config import EngineConfig
 from ..csrc import build as _build
 from ..models.decoder import Decoder
 from ..models.loading import build_model_from_config, build_model_from_folder
-from ..parts.base import GroupView, StepContext, StepLimits, Workspace
+from ..parts.base import FeedForward, GroupView, Mixer, Norm, Position, StepContext, StepLimits, Workspace
 
 
 @dataclass
@@ -37,6 +39,17 @@ class StepEntry:
 
 def _align4(n: int) -> int:
     return (n + 3) & ~3
+
+
+def _own_parts_only(model) -> bool:
+    """Whether every part of the model is one of this package's (whose forward passes only launch
+    kernels of this library)."""
+    root = __name__.split(".")[0] + "."
+    seen = [model.final_norm] + list(getattr(model, "_positions", {}).values())
+    for block in model.blocks:
+        seen.append(block)
+        seen.extend(v for v in vars(block).values() if isinstance(v, (Norm, Mixer, FeedForward, Position)))
+    return all(type(o).__module__.startswith(root) for o in seen)
 
 
 class Engine:
@@ -97,6 +110,17 @@ class Engine:
         self._graphs = {}
         # parts that keep fixed-size state run host logic per request: their steps are not captured
         self._graphable = all(n.kind != "state" for n in model.group_needs)
+        # A step that is not captured still repeats: the launches of a forward pass are fixed by a
+        # few host numbers (tokens, requests, wanted rows, attention tiles, key chunks) because every
+        # buffer comes from the step workspace or the metadata block at addresses that follow from
+        # them.  Such a step is written down once and re-issued for every later step with the same
+        # numbers, without the Python in between.  Only for models made of this package's parts
+        # alone: a part defined elsewhere may do work that is not a launch of this library.
+        self._replayable = bool(engine_config.replay_steps) and self._graphable and _own_parts_only(model) \
+            and os.environ.get("AIEN_B200_STEP_REPLAY", "1") != "0"
+        self._plans: Dict[tuple, list] = {}
+        self._plan_logits: Optional[torch.Tensor] = None
+        self.steps_replayed = 0
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -279,15 +303,40 @@ class Engine:
         self.steps_run += 1
         if graph_step:
             return self._replay_decode(off, Tp, max_ctx, logits_out, T)
+        own = logits_out is None
+        key = None
+        if self._replayable and R <= self.max_requests:
+            max_ctx = self._ctx_bucket(max_ctx)
+            if own:
+                if self._plan_logits is None:
+                    self._plan_logits = torch.empty((self.max_requests, self.vocab_size), dtype=torch.float32, device=self.device)
+                logits_out = self._plan_logits[:R]
+            key = (T, S, R, max_ctx, n_tiles, n_single, logits_out.data_ptr(), torch.cuda.current_stream().cuda_stream)
+            plan = self._plans.get(key)
+            if plan is not None:
+                K.replay_launches(plan)
+                self.steps_replayed += 1
+                return logits_out.clone() if own else logits_out     # the engine's own buffer is rewritten by the next such step
+        elif own:
+            logits_out = torch.empty((R, self.vocab_size), dtype=torch.float32, device=self.device)
         ctx = self._context(off, T, S, max(counts), max_ctx, decode_only)
         d = self.meta_dev
         ctx.prefill_tiles = (d[off["tile_seq"]:off["tile_seq"] + max(n_tiles, 1)], d[off["tile_q0"]:off["tile_q0"] + max(n_tiles, 1)], n_tiles)
         ctx.single_tokens = (d[off["single_tokens"]:off["single_tokens"] + max(n_single, 1)], n_single)
-        if logits_out is None:
-            logits_out = torch.empty((R, self.vocab_size), dtype=torch.float32, device=self.device)
-        d = self.meta_dev
-        self.model.forward(ctx, d[off["want_rows"]:off["want_rows"] + max(R, 1)], R, logits_out)
-        return logits_out
+        want = d[off["want_rows"]:off["want_rows"] + max(R, 1)]
+        with K.stream_scope():
+            if key is None:
+                self.model.forward(ctx, want, R, logits_out)
+                return logits_out
+            K.begin_recording()
+            try:
+                self.model.forward(ctx, want, R, logits_out)
+            finally:
+                plan = K.end_recording()
+        if len(self._plans) >= 512:
+            self._plans.pop(next(iter(self._plans)))
+        self._plans[key] = plan
+        return logits_out.clone() if own else logits_out
 
     # ------------------------------------------------------------------ captured decode steps
     _BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512)
@@ -297,6 +346,16 @@ class Engine:
             if b >= T:
                 return min(b, self.max_requests) if self.max_requests >= T else T
         return T
+
+    def _ctx_bucket(self, max_ctx: int) -> int:
+        """The longest context of a step, rounded up to a power-of-two count of key chunks (what
+        sizes the decode attention's partial results), but not beyond the engine's limit."""
+        from ..kernels import DECODE_CHUNK
+        splits = 1
+        while splits * DECODE_CHUNK < max_ctx:
+            splits *= 2
+        limit = (self.max_context + DECODE_CHUNK - 1) // DECODE_CHUNK
+        return max(1, min(splits, limit)) * DECODE_CHUNK
 
     def _pad_meta(self, m, off, T: int, Tp: int) -> None:
         """Rows T..Tp of a captured step: a token at position 0 of a request with no pages; it
@@ -320,9 +379,7 @@ class Engine:
         use and replayed afterwards; its inputs are the metadata buffer, its output a logits
         buffer of its own."""
         from ..kernels import DECODE_CHUNK
-        splits = 1
-        while splits * DECODE_CHUNK < max_ctx:
-            splits *= 2
+        splits = self._ctx_bucket(max_ctx) // DECODE_CHUNK
         key = (T, splits)
         entry = self._graphs.get(key)
         if entry is None:
@@ -331,7 +388,8 @@ class Engine:
 
             def run():
                 ctx = self._context(off, T, T, 1, splits * DECODE_CHUNK, True)
-                self.model.forward(ctx, d[off["want_rows"]:off["want_rows"] + T], T, logits)
+                with K.stream_scope():
+                    self.model.forward(ctx, d[off["want_rows"]:off["want_rows"] + T], T, logits)
 
             run()                                         # warm-up outside capture (lazy tables, attributes)
             torch.cuda.synchronize()

@@ -31,14 +31,78 @@ class KernelError(RuntimeError):
 
 
 _lib: Optional[ctypes.CDLL] = None
+_proxy = None
+_RECORD: Optional[list] = None
+_QUERIES = ("_supports", "_ranges", "_grid", "_error")     # answer a question, launch nothing
 
 
-def lib() -> ctypes.CDLL:
-    global _lib
-    if _lib is None:
+class _Entry:
+    """One launching entry point.  Calls go to the ctypes function and, while a recording is on,
+    into the list; every attribute (argtypes, restype, ...) is the ctypes function's own, so code
+    that declares a signature on what :func:`lib` hands out declares it on the real thing."""
+    __slots__ = ("_fn",)
+
+    def __init__(self, fn):
+        object.__setattr__(self, "_fn", fn)
+
+    def __call__(self, *args):
+        rc = self._fn(*args)
+        if _RECORD is not None:
+            _RECORD.append((self._fn, args))
+        return rc
+
+    def __getattr__(self, key):
+        return getattr(self._fn, key)
+
+    def __setattr__(self, key, value):
+        setattr(self._fn, key, value)
+
+
+class _Library:
+    """The loaded library with its launching entry points wrapped, so that what a forward pass
+    launches can be written down as (function, arguments) and issued again by
+    :func:`replay_launches` without the Python that chose the arguments."""
+
+    def __init__(self, cdll: ctypes.CDLL):
+        self._cdll = cdll
+
+    def __getattr__(self, name: str):
+        fn = getattr(self._cdll, name)
+        wrapped = fn if name.endswith(_QUERIES) else _Entry(fn)
+        self.__dict__[name] = wrapped
+        return wrapped
+
+
+def lib() -> "_Library":
+    global _lib, _proxy
+    if _proxy is None:
         _lib = _build.load_kernels()
         _declare(_lib)
-    return _lib
+        _proxy = _Library(_lib)
+    return _proxy
+
+
+def begin_recording() -> None:
+    """From here every launch made through this module is also written down."""
+    global _RECORD
+    _RECORD = []
+
+
+def end_recording() -> list:
+    global _RECORD
+    plan, _RECORD = _RECORD or [], None
+    return plan
+
+
+def replay_launches(plan: list) -> None:
+    """Issue a recorded list again.  Valid only while every argument still means the same: the
+    same buffers at the same addresses, the same sizes, the same stream."""
+    global _launches
+    for fn, args in plan:
+        rc = fn(*args)
+        if rc != 0:
+            _check(rc, fn.__name__)
+    _launches += len(plan)
 
 
 def _declare(l: ctypes.CDLL) -> None:
@@ -85,9 +149,9 @@ def _declare(l: ctypes.CDLL) -> None:
 
 def declare_optional(name: str, args) -> bool:
     """Declare a symbol that later kernel files add; returns False when the library lacks it."""
-    l = lib()
+    lib()
     try:
-        fn = getattr(l, name)
+        fn = getattr(_lib, name)
     except AttributeError:
         return False
     fn.argtypes = args
@@ -118,8 +182,27 @@ def _check(rc: int, name: str) -> None:
     raise KernelError(f"{name}: CUDA error {rc} at launch")
 
 
+_STREAM: Optional[int] = None
+
+
+class stream_scope:
+    """Looks the current CUDA stream up once for every launch made inside the block (a step
+    makes hundreds; the lookup costs more than the launch)."""
+
+    def __enter__(self):
+        global _STREAM
+        self._prev = _STREAM
+        _STREAM = torch.cuda.current_stream().cuda_stream
+        return self
+
+    def __exit__(self, *exc):
+        global _STREAM
+        _STREAM = self._prev
+        return False
+
+
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    return _STREAM if _STREAM is not None else torch.cuda.current_stream().cuda_stream
 
 
 def _p(t: Optional[torch.Tensor]) -> int:

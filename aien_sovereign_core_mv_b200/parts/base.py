@@ -99,6 +99,9 @@ class StepLimits:
     itemsize: int          # bytes of the compute dtype
 
 
+_ELEMENT_SIZE = {torch.float32: 4, torch.bfloat16: 2, torch.float16: 2, torch.int32: 4, torch.int64: 8, torch.uint8: 1, torch.float64: 8}
+
+
 class Workspace:
     """Scratch for one step, carved from one device buffer so that a step allocates nothing
     and its addresses repeat (which a captured CUDA graph needs).
@@ -133,7 +136,7 @@ class Workspace:
         n = 1
         for s in shape:
             n *= int(s)
-        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        nbytes = n * _ELEMENT_SIZE[dtype]
         start = (self._off[region] + 255) & ~255
         if start + nbytes > self._size[region]:
             which = "step" if region == 0 else "layer"

@@ -205,3 +205,25 @@ def test_step_refusals(models):
     assert eng.num_tokens(1) == 64
     eng.end_request(1)
     assert eng.cache_state()["free_pages"] == [4]
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+def test_steps_of_a_repeated_shape_reissue_recorded_launches(models, dtype, tol):
+    """Mixed steps whose host numbers repeat (two decoded tokens beside a five-token portion, six
+    times, contexts growing, pages changing) run once through the Python parts and afterwards as
+    the recorded launches: the same bits as an engine that records nothing, and the plain logits."""
+    d, reqs, want = models["A"]
+    a = H.engine_for(d, dtype, H.PAGE_SIZE["A"], 256)
+    b = H.engine_for(d, dtype, H.PAGE_SIZE["A"], 256, replay_steps=False)
+    t1, t2, t3 = reqs[4][:40], reqs[3][:29], reqs[4][:150]
+    steps = [([(1, t1[:20], []), (2, t2[:10], []), (3, t3[:100], [])], [])]
+    for k in range(6):
+        steps.append(([(1, [t1[20 + k]], [0]), (2, [t2[10 + k]], [0]), (3, t3[100 + 5 * k:105 + 5 * k], [4])], []))
+    steps.append(([(3, t3[130:], list(range(20)))], [1, 2, 3]))
+    got_a, got_b = H.run_steps(a, steps), H.run_steps(b, steps)
+    assert a.steps_replayed >= 4 and b.steps_replayed == 0      # one of the six crosses into a second key chunk
+    for rid in got_a:
+        for p in got_a[rid]:
+            assert np.array_equal(got_a[rid][p], got_b[rid][p]), f"request {rid} position {p}: replayed launches differ"
+    check(got_a, {1: want[4], 2: want[3], 3: want[4]}, tol, f"A {dtype} repeated shapes")
+    assert a.cache_state()["check"] == "" and a.cache_state()["requests"] == 0
