@@ -421,63 +421,92 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
             cut_p = id_cutoff(probs, V, need, [&](int, float e) { return __float_as_uint(e) == tpk && e > 0.f; }, run_count, &cut_result);
     }
 
-    // ---- draw: walk the kept set in id order
-    const int per = (V + SM_THREADS - 1) / SM_THREADS;
-    const int lo = tid * per, hi = min(V, lo + per);
+    // ---- draw: walk the kept set in id order.  A warp owns a contiguous region of the row and goes
+    // through it in pieces of 128 tokens (four per lane, neighbours in neighbouring lanes), keeping
+    // the kept mass before each piece; pass one gives every region's mass, pass two (the warp whose
+    // region holds the draw) finds the piece, the lane and the token.  Both passes add in the same order.
     auto kept = [&](int i, float e) {
         const uint32_t b = __float_as_uint(e);
         return e > 0.f && (b > thr_p || (b == thr_p && i <= cut_p));
     };
-    double local = 0.0;
-    for (int i = lo; i < hi; ++i) {
-        const float e = probs[i];
-        if (kept(i, e)) local += (double)e;
-    }
-    // inclusive sums of the runs in run order (a fixed tree: warp scans, then the warps' totals)
-    double incl = local;
     const int lane = tid & 31, warp = tid >> 5;
+    constexpr int NW = SM_THREADS / 32;
+    const int region = (((V + NW - 1) / NW) + 127) & ~127;
+    const int wlo = min(V, warp * region), whi = min(V, wlo + region);
+    __shared__ int s_pick, s_last_kept;
+    if (tid == 0) { s_pick = -1; s_last_kept = -1; }
+    // one piece: this lane's four values and their kept sum; then the inclusive sums over the lanes
+    auto piece = [&](int c, float e4[4], double& mine) {
+        mine = 0.0;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const double up = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += up;
+        for (int q = 0; q < 4; ++q) {
+            const int i = c + lane * 4 + q;
+            e4[q] = i < whi ? probs[i] : 0.f;
+            if (i < whi && kept(i, e4[q])) mine += (double)e4[q]; else e4[q] = 0.f;
+        }
+        double incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const double up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        return incl;
+    };
+    double region_mass = 0.0;
+    int my_last = -1;
+    for (int c = wlo; c < whi; c += 128) {
+        float e4[4]; double mine;
+        const double incl = piece(c, e4, mine);
+        region_mass += __shfl_sync(0xffffffffu, incl, 31);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) if (e4[q] > 0.f) my_last = c + lane * 4 + q;
     }
-    const double warp_total = __shfl_sync(0xffffffffu, incl, 31);
     __syncthreads();
-    if (lane == 0) red[warp] = warp_total;
+    if (lane == 0) red[warp] = region_mass;
+    if (my_last >= 0) atomicMax(&s_last_kept, my_last);
     __syncthreads();
-    double before_warp = 0.0, total = 0.0;
-    for (int w = 0; w < SM_THREADS / 32; ++w) {
-        if (w < warp) before_warp += red[w];
+    double before = 0.0, total = 0.0;
+    for (int w = 0; w < NW; ++w) {
+        if (w < warp) before += red[w];
         total += red[w];
     }
-    incl += before_warp;
     const double rr = u * total;
-    // the run that holds the draw: the first whose inclusive sum exceeds it; if rounding leaves none, the last run with mass
-    __shared__ int chosen;
-    __shared__ int last_run;
-    if (tid == 0) { chosen = SM_THREADS; last_run = 0; }
-    __syncthreads();
-    if (local > 0.0) {
-        atomicMax(&last_run, tid);
-        if (rr < incl) atomicMin(&chosen, tid);
-    }
-    __syncthreads();
-    const bool beyond = chosen == SM_THREADS;      // u * total landed at or beyond the total: the last kept token
-    const int run = beyond ? last_run : chosen;
-    if (tid == run) {
-        const double rem = beyond ? (double)INFINITY : rr - (incl - local);    // what is left to walk inside this run
-        double cum = 0.0;
-        int pick = -1, last = lo;
-        for (int i = lo; i < hi; ++i) {
-            const float e = probs[i];
-            if (kept(i, e)) {
-                cum += (double)e;
-                last = i;
-                if (rem < cum) { pick = i; break; }
+    if (rr >= before && rr < before + region_mass) {                    // warp-uniform: this region holds the draw
+        double base = before;
+        bool found = false;
+        for (int c = wlo; c < whi; c += 128) {
+            float e4[4]; double mine;
+            const double incl = piece(c, e4, mine);
+            const double piece_mass = __shfl_sync(0xffffffffu, incl, 31);
+            const unsigned hit = __ballot_sync(0xffffffffu, rr < base + incl);
+            if (hit != 0u) {
+                if (lane == __ffs(hit) - 1) {
+                    double cum = base + incl - mine;
+                    int pick = -1, last = -1;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        if (e4[q] > 0.f) {
+                            cum += (double)e4[q];
+                            last = c + lane * 4 + q;
+                            if (pick < 0 && rr < cum) pick = last;
+                        }
+                    s_pick = pick >= 0 ? pick : last;
+                }
+                found = true;
+                break;
             }
+            base += piece_mass;
         }
-        out_ids[r] = pick >= 0 ? pick : last;
+        if (!found) {                                                    // the pieces added up a rounding short: the region's last kept token
+            int wl = my_last;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) wl = max(wl, __shfl_xor_sync(0xffffffffu, wl, o));
+            if (lane == 0) s_pick = wl;
+        }
     }
+    __syncthreads();
+    // rounding may leave the draw at or beyond the last region's end: the last kept token
+    if (tid == 0) out_ids[r] = s_pick >= 0 ? s_pick : (s_last_kept >= 0 ? s_last_kept : amax);
 }
 
 __global__ void __launch_bounds__(SM_THREADS)

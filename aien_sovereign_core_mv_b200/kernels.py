@@ -101,7 +101,7 @@ def replay_launches(plan: list) -> None:
     for fn, args in plan:
         rc = fn(*args)
         if rc != 0:
-            _check(rc, fn.__name__)
+            _check(rc, getattr(fn, "__name__", "a recorded launch"))
     _launches += len(plan)
 
 
