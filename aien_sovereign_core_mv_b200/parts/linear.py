@@ -26,7 +26,7 @@ def linear(ctx: StepContext, a: torch.Tensor, w: torch.Tensor, out_dtype: Option
     cut K across CTAs and return float32 partials [P, M, N] instead (the norm kernel, the q/k
     kernel and the row gather add them in order)."""
     M, N = a.shape[0], w.shape[0]
-    if out is None and may_defer_sum and not _FORCE and M <= K.GEMV_MAX_ROWS and a.dtype == torch.bfloat16 \
+    if out is None and may_defer_sum and not _FORCE and M <= K.GEMV_ROUTE_ROWS and a.dtype == torch.bfloat16 \
             and w.dtype == torch.bfloat16:
         splits = K.gemv_splits(N, a.shape[1])
         if splits > 1:
@@ -34,7 +34,7 @@ def linear(ctx: StepContext, a: torch.Tensor, w: torch.Tensor, out_dtype: Option
             if K.gemv_supports(a, w, parts):
                 K.gemv(a, w, parts)
                 return parts
-    if out is None and may_defer_sum and not _FORCE and M > K.GEMV_MAX_ROWS and a.dtype == torch.bfloat16 \
+    if out is None and may_defer_sum and not _FORCE and M > K.GEMV_ROUTE_ROWS and a.dtype == torch.bfloat16 \
             and w.dtype == torch.bfloat16:
         splits = K.gemm_tc_splits(M, N, a.shape[1])
         if splits > 1:
@@ -57,7 +57,7 @@ def linear(ctx: StepContext, a: torch.Tensor, w: torch.Tensor, out_dtype: Option
 def _choose(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, M: int) -> str:
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         return "simple"
-    if M <= K.GEMV_MAX_ROWS and K.gemv_supports(a, w, out):
+    if M <= K.GEMV_ROUTE_ROWS and K.gemv_supports(a, w, out):
         return "gemv"
     if K.gemm_tc_supports(a, w, out):
         return "tc"

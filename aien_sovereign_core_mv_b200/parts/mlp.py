@@ -54,7 +54,7 @@ class SwiGLU(FeedForward):
                 return linear_into_residual(ctx, act, self.w_down, sink) or linear(ctx, act, self.w_down, may_defer_sum=True)
             h = h.materialise(ctx)
         act = ctx.workspace.take((ctx.num_tokens, self.intermediate_size), ctx.dtype)
-        if self.group == 8 and h.shape[0] <= K.GEMV_MAX_ROWS and K.gemv_supports(h, self.w_gate_up, act):
+        if self.group == 8 and h.shape[0] <= K.GEMV_ROUTE_ROWS and K.gemv_supports(h, self.w_gate_up, act):
             K.gemv(h, self.w_gate_up, act, epilogue=1)          # silu(gate)*up inside the product
         elif self.group == 8 and K.gemm_tc_supports(h, self.w_gate_up, act) and not _FORCE:
             K.gemm_tc(h, self.w_gate_up, act, epilogue=1)       # the same, in the tensor-core epilogue

@@ -35,7 +35,7 @@ class RMSNorm(Norm):
 
     def sink(self, ctx: StepContext, x: torch.Tensor) -> Optional[ResidualSink]:
         # bfloat16 steps of at most 16 tokens, where the products are the streamed decode kernel
-        if not _FUSE or ctx.dtype != torch.bfloat16 or ctx.num_tokens > K.GEMV_MAX_ROWS or K.GEMV_IMPL != "stream":
+        if not _FUSE or ctx.dtype != torch.bfloat16 or ctx.num_tokens > K.GEMV_ROUTE_ROWS or K.GEMV_IMPL != "stream":
             return None
         return ResidualSink(x, self, self.weight, self.eps)
 
