@@ -4,7 +4,7 @@
 // K (the number of ranges depends on (N, K) only); CTA b takes units b, b + grid, b + 2 grid, ...
 // One producer lane streams each unit through a ring of shared-memory stages with TMA
 // (one 3-D copy of 16 rows x 512 values of W and one of the matching 8 or 16 rows of a per stage,
-// laid out as eight 128-byte-swizzled boxes of 64 values; no multicast), so up to ~190 KB per SM are in flight without holding a register.  Eight
+// laid out as eight 128-byte-swizzled boxes of 64 values, each CTA its own), so up to ~190 KB per SM are in flight without holding a register.  Eight
 // consumer warps each take one box of a stage, read the operand fragments from shared memory
 // (conflict-free thanks to the swizzle) and issue mma.sync.m16n8k16 with float32 accumulators;
 // at the end of a unit the warps are summed in warp order and the result is written as a

@@ -1,5 +1,5 @@
 // TMA and mbarrier helpers shared by the kernels that stream operands through shared memory.
-// No load here uses cluster multicast; every CTA fetches its own tiles.
+// Every CTA fetches its own tiles; no load here is shared out over a cluster.
 #pragma once
 #include "common.cuh"
 #include <cuda.h>
