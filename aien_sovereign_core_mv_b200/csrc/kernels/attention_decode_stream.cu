@@ -123,19 +123,14 @@ paged_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                 mbar_wait(empty0 + 8 * (it % DS_SLOTS), ((it / DS_SLOTS) - 1) & 1, 1);
             }
         };
-        for (long w = blockIdx.x; w < total; w += gridDim.x) {
-            // w = (seg * T + zt) * nkv + kvh: neighbours in the order share a token
-            const int kvh = (int)(w % nkv);
-            const long r1 = w / nkv;
-            const int zt = (int)(r1 % T), seg = (int)(r1 / T);
+        // one run: chunks [s_lo + rel_begin, s_lo + rel_begin + count) of (token zt, kv head kvh)
+        auto emit_run = [&](int zt, int kvh, int rel_begin, int count) {
             const int t = token_list ? token_list[zt] : zt;
             const int pos = positions[t];
             const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
             const int s_lo = first / DS_CHUNK, s_hi = pos / DS_CHUNK;
-            // the token's own chunks are cut into `segs` runs of equal length (the last ones may be empty)
-            const int per_seg = (s_hi - s_lo + segs) / segs;
-            const int c_begin = s_lo + seg * per_seg, c_end = min(s_hi, c_begin + per_seg - 1);
-            if (c_begin > c_end) continue;
+            const int c_begin = s_lo + rel_begin, c_end = min(s_hi, c_begin + count - 1);
+            if (c_begin > c_end) return;
             const int* bt = block_table + (size_t)(seq_of_token ? seq_of_token[t] : t) * max_blocks;
             for (int c = c_begin; c <= c_end; ++c) {
                 const int chunk_base = c * DS_CHUNK;
@@ -181,6 +176,67 @@ paged_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                         tma_load_2d(ring + slot_v * TILE + h * (DS_CHUNK * 128) + lane * page_size * 128, &map_v, full0 + 8 * slot_v,
                                     kvh * HD + h * 64, row);
                 ++item;
+            }
+        };
+        if (segs > 0) {
+            for (long w = blockIdx.x; w < total; w += gridDim.x) {
+                // w = (seg * T + zt) * nkv + kvh: neighbours in the order share a token
+                const int kvh = (int)(w % nkv);
+                const long r1 = w / nkv;
+                const int zt = (int)(r1 % T), seg = (int)(r1 / T);
+                const int t = token_list ? token_list[zt] : zt;
+                const int pos = positions[t];
+                const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+                // the token's own chunks are cut into `segs` runs of equal length (the last ones may be empty)
+                const int per_seg = (pos / DS_CHUNK - first / DS_CHUNK + segs) / segs;
+                emit_run(zt, kvh, seg * per_seg, per_seg);
+            }
+        } else {
+            // More (token, kv head) pairs than CTAs (T <= 256): the chunks of all pairs, in pair order,
+            // are cut into gridDim.x equal ranges, so a CTA takes the tail of one pair, whole pairs and
+            // the head of another, and contexts of different lengths weigh what they hold.  Lane l keeps
+            // the chunk counts of tokens l, l + 32, ... and how many chunks lie before each.
+            int nch[8], pre[8], all = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int zt = j * 32 + lane;
+                int n = 0;
+                if (zt < T) {
+                    const int pos = positions[token_list ? token_list[zt] : zt];
+                    const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+                    n = pos / DS_CHUNK - first / DS_CHUNK + 1;
+                }
+                int incl = n;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += up;
+                }
+                nch[j] = n; pre[j] = all + incl - n;
+                all += __shfl_sync(0xffffffffu, incl, 31);
+            }
+            const long chunks = (long)all * nkv;
+            long at = chunks * blockIdx.x / gridDim.x;
+            const long end = chunks * (blockIdx.x + 1) / gridDim.x;
+            while (at < end) {
+                int zt = -1, before = 0, n = 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const bool mine = nch[j] > 0 && (long)nkv * pre[j] <= at && at < (long)nkv * (pre[j] + nch[j]);
+                    const unsigned m = __ballot_sync(0xffffffffu, mine);
+                    if (m != 0u) {
+                        const int src = __ffs(m) - 1;
+                        zt = j * 32 + src;
+                        before = __shfl_sync(0xffffffffu, pre[j], src);
+                        n = __shfl_sync(0xffffffffu, nch[j], src);
+                    }
+                }
+                if (zt < 0) break;                                 // cannot happen: every chunk index belongs to a token
+                const int rem = (int)(at - (long)nkv * before);
+                const int kvh = rem / n, rel = rem - kvh * n;
+                const int count = (int)min((long)(n - rel), end - at);
+                emit_run(zt, kvh, rel, count);
+                at += count;
             }
         }
         sync_ahead();
@@ -390,7 +446,16 @@ static int launch_decode_stream(const CUtensorMap& mk, const CUtensorMap& mv, co
     const long slots = 2L * ds_num_sms();
     int segs = ds_segments_per_pair((long)T * nkv, max_splits, slots);
     if (const char* e = getenv("AIEN_B200_DECODE_SEGMENTS")) { const int v = atoi(e); if (v > 0 && v <= max_splits) segs = v; }
-    const long total = (long)segs * T * nkv;
+    // more pairs than CTAs: equal ranges of chunks instead of whole pairs (segs = 0 tells the kernel); AIEN_B200_DECODE_BALANCED=0: off
+    static int balanced = -1;
+    if (balanced < 0) { const char* e = getenv("AIEN_B200_DECODE_BALANCED"); balanced = (e && e[0] == '0') ? 0 : 1; }
+    // (measured, 32q/8kv x 128 at 1,030 keys: batch 48, 384 pairs on 296 CTAs, 5.26 -> 5.03 ms a step; batch 64, 512
+    // pairs, whole pairs are as fast or faster: ranges share more pairs between CTAs, and every shared pair is a
+    // ticket and a merge more.  So only when whole pairs would leave a fifth of the CTA rounds empty.)
+    const long pairs = (long)T * nkv, rounds = (pairs + slots - 1) / slots;
+    if (balanced && segs == 1 && pairs > slots && pairs * 10 < slots * rounds * 8 && T <= 256 &&
+        getenv("AIEN_B200_DECODE_SEGMENTS") == nullptr) segs = 0;
+    const long total = segs > 0 ? (long)segs * T * nkv : slots;
     const unsigned grid = (unsigned)(total < slots ? total : slots);
     launch_chain(kern, dim3(grid), dim3(DS_THREADS), smem, stream, mk, mv, (const __nv_bfloat16*)q, q_stride, bt, max_blocks, seq_of_token,
                  positions, token_list, part_out, part_ml, counters, (__nv_bfloat16*)out, out_stride, nq, nkv, page_size, window, scale,

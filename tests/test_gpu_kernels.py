@@ -416,14 +416,16 @@ def test_paged_attention_decode(K, nq, nkv, hd, page, window):
 
 # query heads, kv heads, head size, page, window, requests
 DECODE_STREAM_CASES = [(8, 2, 128, 16, 0, 6), (32, 8, 128, 16, 0, 40), (16, 1, 64, 8, 0, 5), (12, 4, 64, 32, 300, 7),
-                       (5, 5, 128, 128, 0, 9), (9, 1, 128, 64, 150, 3), (32, 8, 128, 16, 200, 70)]
+                       (5, 5, 128, 128, 0, 9), (9, 1, 128, 64, 150, 3), (32, 8, 128, 16, 200, 70), (4, 2, 64, 16, 0, 200)]
 
 
 @pytest.mark.parametrize("nq,nkv,hd,page,window,n_req", DECODE_STREAM_CASES)
 def test_paged_attention_decode_stream_gives_the_same_bits(K, nq, nkv, hd, page, window, n_req):
     """The streamed kernel (TMA ring, CTAs that take many chunks, tickets per segment) against the
     one-CTA-per-chunk kernel: equal bits, for few and for many requests of mixed lengths, with
-    segments of one, two and four chunks, and for a subset of the tokens."""
+    segments of one, two and four chunks, and for a subset of the tokens.  With more (token, kv
+    head) pairs than CTAs (the cases of 40, 70 and 200 requests) the chunks of all pairs are cut into
+    equal ranges, so pairs are shared between CTAs at arbitrary chunks."""
     dtype = torch.bfloat16
     rng = np.random.default_rng(nq + hd + n_req)
     seq_lens = [1, 37, 700, 256, 257, 513, 128, 129, 1025][:n_req] + [int(x) for x in rng.integers(1, 1100, size=max(0, n_req - 9))]
