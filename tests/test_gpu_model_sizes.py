@@ -1,4 +1,4 @@
-"""The engine at the layer sizes of the real models (Qwen3-8B and Llama-3-8B shapes, two layers, a
+"""The engine at the layer sizes of the real models (Qwen3-8B, Llama-3-8B and Llama-3.2-1B shapes, two layers, a
 small vocabulary so that the plain implementation stays fast): the kernels meet their production
 shapes here (K = 4096 / 12288 / 14336, 32 query heads in groups of 4, head size 128), whole, in portions and
 decoding, in float32 and bfloat16."""
@@ -18,6 +18,13 @@ SHAPES = {
                       num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=1000,
                       rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=8192,
                       hidden_act="silu", eos_token_id=1),
+    # heads of 64 at production widths, tied embeddings, scaled rotation (the Llama-3.2-1B layer shape)
+    "llama32_1b": dict(architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=2, hidden_size=2048,
+                       num_attention_heads=32, num_key_value_heads=8, head_dim=64, intermediate_size=8192, vocab_size=1504,
+                       rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=131072,
+                       rope_scaling={"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                     "original_max_position_embeddings": 8192},
+                       hidden_act="silu", eos_token_id=1),
 }
 
 
