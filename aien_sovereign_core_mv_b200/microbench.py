@@ -4,6 +4,8 @@
     python -m aien_sovereign_core_mv_b200.microbench gemm --m 2048 --n 24576 --k 4096 --epilogue 1
     python -m aien_sovereign_core_mv_b200.microbench attn-decode --batch 1 --ctx 1030 --impl stream
     python -m aien_sovereign_core_mv_b200.microbench attn-prefill --tokens 2048 --impl tc
+    python -m aien_sovereign_core_mv_b200.microbench qk --tokens 2048
+    python -m aien_sovereign_core_mv_b200.microbench sample --rows 8 --top-p 0.95
     python -m aien_sovereign_core_mv_b200.microbench all
 
 Every case launches its kernel a few times eagerly (what a profiler captures) and then times a
@@ -115,6 +117,55 @@ def attn_prefill_case(tokens: int, offset: int = 0, nq: int = 32, nkv: int = 8, 
           f"  (error flag {K.attention_prefill_tc_error()})", flush=True)
 
 
+def qk_case(tokens: int, parts: int = 0, nq: int = 32, nkv: int = 8, hd: int = 128, reps: int = 20) -> None:
+    """q/k norm + rotation + cache write on the projections of `tokens` tokens (bfloat16 rows, or
+    `parts` float32 partial products as a product cut over K leaves them)."""
+    width = (nq + 2 * nkv) * hd
+    if parts == 0:
+        buf = torch.randn(tokens, width, device="cuda").to(torch.bfloat16)
+    else:
+        buf = torch.randn(parts, tokens, width, device="cuda")
+    q, k, v = buf[..., :nq * hd], buf[..., nq * hd:(nq + nkv) * hd], buf[..., (nq + nkv) * hd:]
+    q_out = torch.empty(tokens, nq * hd, dtype=torch.bfloat16, device="cuda")
+    qw = torch.ones(hd, dtype=torch.bfloat16, device="cuda"); kw = torch.ones(hd, dtype=torch.bfloat16, device="cuda")
+    cos = torch.empty(tokens, hd // 2, device="cuda"); sin = torch.empty(tokens, hd // 2, device="cuda")
+    inv = torch.tensor([1e6 ** (-2.0 * i / hd) for i in range(hd // 2)], dtype=torch.float64, device="cuda")
+    K.rope_table(torch.arange(tokens, dtype=torch.int32, device="cuda"), inv, cos, sin)
+    slot_map = torch.arange(tokens, dtype=torch.int32, device="cuda")
+    kc = torch.zeros(tokens + 8, nkv, hd, dtype=torch.bfloat16, device="cuda"); vc = torch.zeros_like(kc)
+
+    def run(_=0):
+        K.qk_norm_rope_kv_write(q, k, v, hd, qw, kw, 1e-6, cos, sin, hd, slot_map, kc, vc, q_out=q_out)
+
+    for _ in range(3):
+        run()
+    us = _time_graph(run, reps)
+    moved = buf.numel() * buf.element_size() + tokens * width * 2
+    print(f"qk tokens={tokens} parts={parts} ({nq}q/{nkv}kv x {hd}): {us:8.2f} us  {moved / us / 1e3:7.0f} GB/s read + written", flush=True)
+
+
+def sample_case(rows: int, vocab: int, temperature: float, top_p: float, top_k: int, peaked: bool = True, reps: int = 10) -> None:
+    """One sampling launch over `rows` rows of logits; `peaked`: a handful of tokens far above the rest, like a language model's."""
+    logits = (torch.randn(rows, vocab, device="cuda") * 2).float()
+    if peaked:
+        idx = torch.randint(0, vocab, (rows, 40), device="cuda")
+        logits.scatter_(1, idx, torch.rand(rows, 40, device="cuda") * 8 + 10)
+    ids = torch.empty(rows, dtype=torch.int32, device="cuda")
+    scratch = torch.empty(rows * vocab, device="cuda")
+    t = torch.full((rows,), temperature, device="cuda"); tp = torch.full((rows,), top_p, device="cuda")
+    tk = torch.full((rows,), top_k, dtype=torch.int32, device="cuda")
+    seeds = torch.arange(rows, dtype=torch.int64, device="cuda"); rid = torch.arange(rows, dtype=torch.int64, device="cuda")
+    pos = torch.full((rows,), 100, dtype=torch.int32, device="cuda")
+
+    def run(_=0):
+        K.sample_rows(logits, t, tp, tk, seeds, rid, pos, scratch, ids)
+
+    for _ in range(3):
+        run()
+    us = _time_graph(run, reps)
+    print(f"sample rows={rows} vocab={vocab} T={temperature} top_p={top_p} top_k={top_k} {'peaked' if peaked else 'flat'}: {us:8.1f} us", flush=True)
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="microbench", description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="case", required=True)
@@ -130,6 +181,12 @@ def main(argv=None) -> int:
     p = sub.add_parser("attn-prefill")
     p.add_argument("--tokens", type=int, default=2048); p.add_argument("--offset", type=int, default=0)
     p.add_argument("--impl", default="tc", choices=["tc", "mma"]); p.add_argument("--page", type=int, default=16)
+    p = sub.add_parser("qk")
+    p.add_argument("--tokens", type=int, default=2048); p.add_argument("--parts", type=int, default=0)
+    p = sub.add_parser("sample")
+    p.add_argument("--rows", type=int, default=8); p.add_argument("--vocab", type=int, default=151936)
+    p.add_argument("--temperature", type=float, default=0.7); p.add_argument("--top-p", type=float, default=0.95)
+    p.add_argument("--top-k", type=int, default=0); p.add_argument("--flat", action="store_true")
     sub.add_parser("all")
     args = ap.parse_args(argv)
     K.lib()
@@ -141,6 +198,10 @@ def main(argv=None) -> int:
         attn_decode_case(args.batch, args.ctx, page=args.page, impl=args.impl)
     elif args.case == "attn-prefill":
         attn_prefill_case(args.tokens, args.offset, page=args.page, impl=args.impl)
+    elif args.case == "qk":
+        qk_case(args.tokens, args.parts)
+    elif args.case == "sample":
+        sample_case(args.rows, args.vocab, args.temperature, args.top_p, args.top_k, peaked=not args.flat)
     else:
         shapes = {"qkv": (6144, 4096, 0), "o": (4096, 4096, 0), "gate_up": (24576, 4096, 1), "down": (4096, 12288, 0), "head": (151936, 4096, 0)}
         for m in (1, 8, 16):
@@ -157,6 +218,10 @@ def main(argv=None) -> int:
         for t, off in ((2048, 0), (512, 1536), (8192, 0)):
             for impl in ("tc", "mma"):
                 attn_prefill_case(t, off, impl=impl)
+        for t, parts in ((8, 0), (64, 6), (512, 0), (2048, 0)):
+            qk_case(t, parts)
+        for tp, tk in ((0.95, 0), (0.95, 50), (1.0, 0)):
+            sample_case(8, 151936, 0.7, tp, tk)
     return 0
 
 
