@@ -366,6 +366,120 @@ qk_norm_rope_kv_write_hd128_kernel(
     }
 }
 
+// The same for many tokens with two head rows per warp: lanes 0-15 hold one row (eight values each,
+// one 16-byte load), lanes 16-31 another; the sum of squares runs over 16 lanes, the rotation
+// partner of a value is in lane ^ 8.  A CTA of eight warps takes four tokens, two warps each (the
+// even and the odd pairs of heads), so a warp reads its token's rotation table once; HB pairs of
+// rows are requested before the first is used.  A third of the instructions per row of the kernel
+// above, which is what bounds it.
+template <int HB>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_kv_write_hd128_pairs_kernel(
+    const __nv_bfloat16* q, long q_stride, int nq, const __nv_bfloat16* __restrict__ k, long k_stride,
+    const __nv_bfloat16* __restrict__ v, long v_stride, int nkv, __nv_bfloat16* q_out, long q_out_stride,
+    const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w, int wdt, float eps,
+    const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+    const int* __restrict__ slot_map, __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int T) {
+    griddep_launch();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int half = lane >> 4, l16 = lane & 15;
+    const int t = blockIdx.x * 4 + (warp & 3);
+    const bool write_kv = (k != nullptr);
+    const int n_heads = nq + (write_kv ? 2 * nkv : 0);
+    float wq[8], wk[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) wq[e] = wk[e] = 1.f;
+    if (q_norm_w != nullptr) {
+        const float4 a = load4_dyn(q_norm_w, wdt, l16 * 8), b = load4_dyn(q_norm_w, wdt, l16 * 8 + 4);
+        wq[0] = a.x; wq[1] = a.y; wq[2] = a.z; wq[3] = a.w; wq[4] = b.x; wq[5] = b.y; wq[6] = b.z; wq[7] = b.w;
+    }
+    if (k_norm_w != nullptr) {
+        const float4 a = load4_dyn(k_norm_w, wdt, l16 * 8), b = load4_dyn(k_norm_w, wdt, l16 * 8 + 4);
+        wk[0] = a.x; wk[1] = a.y; wk[2] = a.z; wk[3] = a.w; wk[4] = b.x; wk[5] = b.y; wk[6] = b.z; wk[7] = b.w;
+    }
+    griddep_wait();
+    const bool live = t < T;
+    const long slot = (write_kv && live) ? (long)__ldcg(slot_map + t) : -1;
+    float cs[8], sn[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { cs[e] = 1.f; sn[e] = 0.f; }
+    if (cos_t != nullptr && live) {
+        const float* cp = cos_t + (size_t)t * 64 + (l16 & 7) * 8;
+        const float* sp = sin_t + (size_t)t * 64 + (l16 & 7) * 8;
+        const float4 c0 = ld_act4(cp), c1 = ld_act4(cp + 4), s0 = ld_act4(sp), s1 = ld_act4(sp + 4);
+        cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+        sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+    }
+    // this lane's heads: 2 * pair + half, pair = (warp >> 2) + 2 * gridDim.y * i + 2 * blockIdx.y
+    const int pstep = 2 * gridDim.y;
+    for (int p0 = (warp >> 2) + 2 * blockIdx.y; 2 * p0 < n_heads; p0 += pstep * HB) {
+        uint4 raw[HB];
+#pragma unroll
+        for (int u = 0; u < HB; ++u) {
+            const int head = 2 * (p0 + pstep * u) + half;
+            raw[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (live && head < n_heads) {
+                const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
+                const int hh = is_q ? head : (is_k ? head - nq : head - nq - nkv);
+                const __nv_bfloat16* src = (is_q ? q : (is_k ? k : v)) + (size_t)t * (is_q ? q_stride : (is_k ? k_stride : v_stride)) + (size_t)hh * 128 + l16 * 8;
+                raw[u] = __ldcg(reinterpret_cast<const uint4*>(src));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < HB; ++u) {
+            if (2 * (p0 + pstep * u) >= n_heads) break;                          // warp-uniform: both rows of the pair are beyond the heads
+            const int head = 2 * (p0 + pstep * u) + half;
+            const bool valid = live && head < n_heads;
+            const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
+            const int hh = is_q ? head : (is_k ? head - nq : head - nq - nkv);
+            const bool normed = is_q ? (q_norm_w != nullptr) : (is_k && k_norm_w != nullptr);
+            const bool rotate = cos_t != nullptr && (is_q || is_k);
+            float x[8];
+            {
+                const uint32_t w32[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w32[e]));
+                    x[2 * e] = f.x; x[2 * e + 1] = f.y;
+                }
+            }
+            float ss = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);        // over the 16 lanes of the row
+            if (normed) {
+                const float scale = 1.0f / sqrtf(ss / 128.0f + eps);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e] = x[e] * scale * (is_q ? wq[e] : wk[e]);
+            }
+            float y[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) y[e] = __shfl_xor_sync(0xffffffffu, x[e], 8);        // the rotation partner, 64 values away
+            if (rotate) {
+                if (l16 < 8) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) x[e] = x[e] * cs[e] - y[e] * sn[e];
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) x[e] = y[e] * sn[e] + x[e] * cs[e];
+                }
+            }
+            if (!valid || (!is_q && slot < 0)) continue;
+            uint4 o;
+            {
+                __nv_bfloat162 p0b = __floats2bfloat162_rn(x[0], x[1]), p1b = __floats2bfloat162_rn(x[2], x[3]);
+                __nv_bfloat162 p2b = __floats2bfloat162_rn(x[4], x[5]), p3b = __floats2bfloat162_rn(x[6], x[7]);
+                o.x = *reinterpret_cast<uint32_t*>(&p0b); o.y = *reinterpret_cast<uint32_t*>(&p1b);
+                o.z = *reinterpret_cast<uint32_t*>(&p2b); o.w = *reinterpret_cast<uint32_t*>(&p3b);
+            }
+            __nv_bfloat16* dst = is_q ? (q_out + (size_t)t * q_out_stride + (size_t)hh * 128)
+                                      : ((is_k ? k_cache : v_cache) + ((size_t)slot * nkv + hh) * 128);
+            *reinterpret_cast<uint4*>(dst + l16 * 8) = o;
+        }
+    }
+}
+
 // The same for many tokens (a prompt portion): a CTA of eight warps takes QK_TOKENS tokens and their
 // heads (all of them, or every gridDim.y-th group of eight), warp w the heads w, w + 8, ...; the
 // rotation table of the tokens is read once per warp, and the rows of HB heads x QK_TOKENS tokens
@@ -603,7 +717,14 @@ AIEN_API int aien_qk_norm_rope_kv_write(
         const dim3 fast_grid((T + QK_TOKENS - 1) / QK_TOKENS, grid.y);
         // few tokens: the heads of a token group are shared out over two or four CTAs, so that the grid fills the GPU
         const unsigned head_ctas = fast_grid.x >= 512 ? 1u : (fast_grid.x >= 256 || n_heads <= 16 ? 2u : 4u);
-        if (in_dt == AIEN_DT_BF16 && T >= 128)
+        const bool wide = (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0 &&
+                          ((q_stride | k_stride | v_stride | q_out_stride) & 7) == 0;
+        if (in_dt == AIEN_DT_BF16 && T >= 128 && wide)
+            launch_chain(qk_norm_rope_kv_write_hd128_pairs_kernel<3>, dim3(fast_grid.x, head_ctas), dim3(256), 0, stream,
+                         (const __nv_bfloat16*)q, q_stride, nq, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, nkv,
+                         (__nv_bfloat16*)q_out, q_out_stride, q_norm_w, k_norm_w, w_dt, eps, cos_t, sin_t, slot_map,
+                         (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, T);
+        else if (in_dt == AIEN_DT_BF16 && T >= 128)
             launch_chain(qk_norm_rope_kv_write_hd128_rows_kernel<3>, dim3(fast_grid.x, head_ctas), dim3(256), 0, stream,
                          (const __nv_bfloat16*)q, q_stride, nq, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, nkv,
                          (__nv_bfloat16*)q_out, q_out_stride, q_norm_w, k_norm_w, w_dt, eps, cos_t, sin_t, slot_map,
