@@ -6,6 +6,7 @@
 #include <algorithm>
 #include <climits>
 #include <stdexcept>
+#include <tuple>
 
 namespace aien {
 
@@ -32,7 +33,16 @@ void Scheduler::submit(int64_t id, std::vector<int32_t> prompt, int max_tokens, 
     s.stop_ids = std::move(stop_ids);
     s.priority = priority;
     s.arrival = arrivals_++;
+    const bool too_long = cfg_.max_context > 0 && static_cast<int>(s.prompt.size()) >= cfg_.max_context;
+    const size_t len = s.prompt.size();
     seqs_[id] = std::move(s);
+    if (too_long) {
+        // never planned: its pages would outgrow the block table (the reference sizes contexts from
+        // max_position_embeddings, crates/aien-inference-abi/src/model_dir.rs:116-139)
+        finish(seqs_[id], FinishReason::Aborted, "prompt of " + std::to_string(len) + " tokens leaves no room below the context limit " +
+               std::to_string(cfg_.max_context));
+        return;
+    }
     waiting_.push_back(id);
 }
 
@@ -122,6 +132,46 @@ void Scheduler::preempt(int64_t id, StepPlan& plan) {
     ++metrics_.preemptions;
 }
 
+void Scheduler::requeue(SeqRecord& s) {
+    if (cache_->has(s.id)) cache_->free_request(s.id);
+    while (s.unresolved > 0 && !s.generated.empty()) { s.generated.pop_back(); --s.unresolved; }
+    s.unresolved = 0;
+    s.draining = false;
+    s.computed = 0;
+    s.state = SeqState::Preempted;
+    ++s.preemptions;
+    running_.erase(std::remove(running_.begin(), running_.end(), s.id), running_.end());
+    preempted_.push_back(s.id);
+    ++metrics_.preemptions;
+}
+
+void Scheduler::rollback() {
+    if (!awaiting_commit_) throw std::logic_error("rollback() without a planned step");
+    awaiting_commit_ = false;
+    for (const StepEntry& e : last_.entries) {
+        auto it = seqs_.find(e.id);
+        if (it == seqs_.end() || it->second.state != SeqState::Running || it->second.arrival != e.arrival) continue;
+        SeqRecord& s = it->second;
+        if (!cache_->has(e.id)) continue;
+        try {
+            cache_->truncate(e.id, e.start);
+        } catch (const std::invalid_argument&) {
+            requeue(s);                       // fixed-size state or a window that moved on: recompute
+        }
+    }
+    --metrics_.steps;
+    metrics_.tokens_scheduled -= last_.num_tokens;
+    metrics_.prefill_tokens -= last_.prefill_tokens;
+    metrics_.decode_tokens -= last_.num_tokens - last_.prefill_tokens;
+    last_ = StepPlan{};
+}
+
+void Scheduler::restart_running() {
+    if (awaiting_commit_) rollback();
+    const std::vector<int64_t> ids = running_;
+    for (int64_t id : ids) requeue(seqs_.at(id));
+}
+
 void Scheduler::finish(SeqRecord& s, FinishReason why, const std::string& msg) {
     if (cache_->has(s.id)) cache_->free_request(s.id);
     running_.erase(std::remove(running_.begin(), running_.end(), s.id), running_.end());
@@ -206,6 +256,7 @@ StepPlan Scheduler::plan() {
         const SeqRecord& s = seqs_.at(c.id);
         StepEntry e;
         e.id = c.id;
+        e.arrival = s.arrival;
         e.start = s.computed;
         e.tokens.reserve(c.n);
         for (int i = 0; i < c.n; ++i) e.tokens.push_back(s.input_at(s.computed + i));
@@ -266,6 +317,7 @@ StepPlan Scheduler::plan() {
             running_.insert(std::upper_bound(running_.begin(), running_.end(), id), id);
             StepEntry e;
             e.id = id;
+            e.arrival = s.arrival;
             e.start = 0;
             e.tokens.reserve(n);
             for (int i = 0; i < n; ++i) e.tokens.push_back(s.input_at(i));
@@ -306,7 +358,7 @@ void Scheduler::commit(const std::vector<int32_t>& sampled) {
     for (const StepEntry& e : last_.entries) {
         const int32_t tok = e.wants_logits ? sampled[k++] : 0;
         auto it = seqs_.find(e.id);
-        if (it == seqs_.end() || it->second.state != SeqState::Running) continue;   // cancelled meanwhile
+        if (it == seqs_.end() || it->second.state != SeqState::Running || it->second.arrival != e.arrival) continue;   // cancelled meanwhile
         SeqRecord& s = it->second;
         s.computed += static_cast<int>(e.tokens.size());
         if (!e.wants_logits) continue;
@@ -328,7 +380,7 @@ void Scheduler::commit_deferred() {
     awaiting_commit_ = false;
     for (const StepEntry& e : last_.entries) {
         auto it = seqs_.find(e.id);
-        if (it == seqs_.end() || it->second.state != SeqState::Running) continue;   // cancelled meanwhile
+        if (it == seqs_.end() || it->second.state != SeqState::Running || it->second.arrival != e.arrival) continue;   // cancelled meanwhile
         SeqRecord& s = it->second;
         s.computed += static_cast<int>(e.tokens.size());
         if (!e.wants_logits) continue;
@@ -345,11 +397,25 @@ void Scheduler::commit_deferred() {
 }
 
 void Scheduler::resolve(const std::vector<std::pair<int64_t, int32_t>>& tokens) {
+    std::vector<std::tuple<int64_t, int32_t, uint64_t>> t;
+    t.reserve(tokens.size());
     for (const auto& [id, tok] : tokens) {
         auto it = seqs_.find(id);
+        t.emplace_back(id, tok, it == seqs_.end() ? 0 : it->second.arrival);
+    }
+    resolve_for(t);
+}
+
+void Scheduler::resolve_for(const std::vector<std::tuple<int64_t, int32_t, uint64_t>>& tokens) {
+    for (const auto& [id, tok, arrival] : tokens) {
+        auto it = seqs_.find(id);
         if (it == seqs_.end() || it->second.state == SeqState::Finished) continue;   // ended meanwhile: the value is dropped
+        if (it->second.arrival != arrival) continue;                                  // the id was submitted again: not its token
         SeqRecord& s = it->second;
-        if (s.unresolved <= 0) throw std::logic_error("resolve(): request " + std::to_string(id) + " has no unresolved token");
+        if (s.unresolved <= 0) {
+            if (s.state != SeqState::Running) continue;                               // restarted meanwhile: it recomputes the token
+            throw std::logic_error("resolve(): request " + std::to_string(id) + " has no unresolved token");
+        }
         const size_t at = s.generated.size() - static_cast<size_t>(s.unresolved);
         if (std::find(s.stop_ids.begin(), s.stop_ids.end(), tok) != s.stop_ids.end()) {
             s.generated.resize(at);                       // the stop id is consumed; what was computed after it is dropped
@@ -395,7 +461,8 @@ void bind_scheduler(pybind11::module_& m) {
         .def_readonly("id", &StepEntry::id)
         .def_readonly("tokens", &StepEntry::tokens)
         .def_readonly("start", &StepEntry::start)
-        .def_readonly("wants_logits", &StepEntry::wants_logits);
+        .def_readonly("wants_logits", &StepEntry::wants_logits)
+        .def_readonly("arrival", &StepEntry::arrival);
     py::class_<StepPlan>(m, "StepPlan")
         .def_readonly("step_id", &StepPlan::step_id)
         .def_readonly("entries", &StepPlan::entries)
@@ -440,6 +507,9 @@ void bind_scheduler(pybind11::module_& m) {
         .def("commit", &Scheduler::commit)
         .def("commit_deferred", &Scheduler::commit_deferred)
         .def("resolve", &Scheduler::resolve)
+        .def("resolve_for", &Scheduler::resolve_for)
+        .def("rollback", &Scheduler::rollback)
+        .def("restart_running", &Scheduler::restart_running)
         .def("take_finished", &Scheduler::take_finished)
         .def("record", &Scheduler::record, py::return_value_policy::copy)
         .def("metrics", [](const Scheduler& s) {

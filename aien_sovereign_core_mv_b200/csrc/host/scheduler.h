@@ -19,6 +19,7 @@
 #include <deque>
 #include <map>
 #include <string>
+#include <tuple>
 #include <vector>
 
 #include "cache_manager.h"
@@ -68,6 +69,7 @@ struct StepEntry {
     std::vector<int32_t> tokens;
     int start = 0;               // position of tokens[0]
     bool wants_logits = false;   // the portion reaches the end of the input: sample after it
+    uint64_t arrival = 0;        // which submission of this id the entry belongs to (ids may be used again)
 };
 
 struct StepPlan {
@@ -119,6 +121,17 @@ class Scheduler {
     // request may be unresolved when the next step is planned.
     void commit_deferred();
     void resolve(const std::vector<std::pair<int64_t, int32_t>>& tokens);
+    // The same with the submission each value belongs to (StepEntry::arrival): a value whose request
+    // ended and whose id was submitted again meanwhile is dropped instead of reaching the new request.
+    void resolve_for(const std::vector<std::tuple<int64_t, int32_t, uint64_t>>& tokens);
+    // The planned step failed before commit: every entry's request goes back to the cache length it
+    // had (a request whose cache cannot be rewound is queued to be recomputed instead) and the step
+    // counts as not planned.  Requests the plan preempted stay preempted.
+    void rollback();
+    // Everything the running requests hold in the cache is no longer trusted (a kernel reported a
+    // broken step after later steps had been committed): each is queued to be recomputed from its
+    // prompt and the tokens whose values are known; unresolved placeholders are dropped.
+    void restart_running();
     std::vector<FinishEvent> take_finished();
     const SeqRecord& record(int64_t id) const { return seqs_.at(id); }
     const SchedulerMetrics& metrics() const { return metrics_; }
@@ -131,6 +144,7 @@ class Scheduler {
     void preempt(int64_t id, StepPlan& plan);
     void finish(SeqRecord& s, FinishReason why, const std::string& msg);
     int64_t pick_victim(const std::vector<int64_t>& among) const;
+    void requeue(SeqRecord& s);
 
     SchedulerConfig cfg_;
     CacheManager* cache_;

@@ -381,3 +381,5 @@ AIEN_API int aien_attention_prefill_tc_error(void) {
     if (v != 0) cudaMemcpyToSymbol(g_wait_error, &zero, sizeof(int));
     return v;
 }
+
+AIEN_DEFINE_WAIT_ERROR_ADDRESS(aien_attention_prefill_tc_error_address)

@@ -378,3 +378,5 @@ AIEN_API int aien_gemv_stream_error(void) {
     if (v != 0) cudaMemcpyToSymbol(g_wait_error, &zero, sizeof(int));
     return v;
 }
+
+AIEN_DEFINE_WAIT_ERROR_ADDRESS(aien_gemv_stream_error_address)

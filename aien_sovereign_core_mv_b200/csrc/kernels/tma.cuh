@@ -14,6 +14,13 @@ constexpr uint32_t TC_SPIN_LIMIT = 1u << 24;
 // One error word per translation unit: a bounded wait that runs out stores its code here.
 static __device__ int g_wait_error = 0;
 
+// Gives the translation unit an exported function that tells the device address of its error word,
+// so that one small kernel (wait_errors.cu) can read the words of all of them inside the stream.
+#define AIEN_DEFINE_WAIT_ERROR_ADDRESS(name)                                                        \
+    AIEN_API int name(void** out) {                                                                 \
+        return cudaGetSymbolAddress(out, aien::g_wait_error) == cudaSuccess ? 0 : AIEN_E_STATE;     \
+    }
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {

@@ -79,6 +79,9 @@ class Engine:
             tokens = int(engine_config.max_cache_tokens or self.max_context)
             pages = (tokens + self.page_size - 1) // self.page_size
         self.num_pages = pages
+        if any(need.kind == "full" for need in model.group_needs):
+            # a request that keeps every key can never be longer than the whole pool
+            self.max_context = min(self.max_context, pages * self.page_size)
         gspecs, self.storage = [], []
         kinds = {"full": self.host.GroupKind.Full, "window": self.host.GroupKind.Window, "state": self.host.GroupKind.State}
         for need, slots in zip(model.group_needs, model.group_slots):
@@ -121,6 +124,10 @@ class Engine:
         self._plans: Dict[tuple, list] = {}
         self._plan_logits: Optional[torch.Tensor] = None
         self.steps_replayed = 0
+        # the error words of the kernels with bounded waits, collected behind every step()
+        self._wait_dev = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self._wait_host = torch.zeros(4, dtype=torch.int32, pin_memory=True)
+        self._wait_event: Optional[torch.cuda.Event] = None
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -199,6 +206,7 @@ class Engine:
         float32 logits [number of wanted places, vocab] on the device, in the order of the
         entries and of each entry's ``want``.  Takes the cache pages the tokens need first; if
         they cannot all be had, raises with nothing changed."""
+        self.check_waits(block=False)              # a wait that ran out in the step before is reported now at the latest
         ids, counts, flat, want_rows = self._validate(entries)
         if not ids:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
@@ -208,13 +216,75 @@ class Engine:
                 if not self.cache.has(rid):
                     self.cache.add_request(rid)
                     added.append(rid)
+            before = [self.cache.num_tokens(rid) for rid in ids]
             copies = self.cache.append(list(zip(ids, counts)))
         except Exception:
             for rid in added:
                 self.cache.free_request(rid)
             raise
-        self._do_copies(copies)
-        return self.run_reserved(ids, counts, flat, want_rows, logits_out)
+        try:
+            self._do_copies(copies)
+            logits = self.run_reserved(ids, counts, flat, want_rows, logits_out)
+            self._post_waits()
+        except Exception:
+            self.rollback(ids, before, added)
+            raise
+        self._last_step = (ids, before, added)
+        return logits
+
+    # ------------------------------------------------------------------ failed steps
+    def rollback(self, ids, before, added=()) -> None:
+        """Undo what a failed step took from the cache: every request goes back to the length it
+        had (``before``), requests the step created are removed.  The reference snapshots and
+        rolls back the same way (crates/aien-kv-cache/src/lib.rs:815-858, 1646-1695).  A request
+        of a group that cannot be rewound (fixed-size state, a window that has moved on) is
+        removed instead: what it holds can no longer be trusted."""
+        for rid, n in zip(ids, before):
+            if not self.cache.has(rid):
+                continue
+            if rid in added:
+                self.cache.free_request(rid)
+                continue
+            try:
+                self.cache.truncate(rid, n)
+            except ValueError:
+                self.cache.free_request(rid)
+
+    def collect_waits(self, out: torch.Tensor) -> None:
+        """Writes the four error words of the kernels with bounded waits to out[0:4] (int32 on the
+        device), in the stream, behind the launches made so far."""
+        K.collect_wait_errors(out)
+
+    def _post_waits(self) -> None:
+        K.collect_wait_errors(self._wait_dev)
+        self._wait_host.copy_(self._wait_dev, non_blocking=True)
+        if self._wait_event is None:
+            self._wait_event = torch.cuda.Event()
+        self._wait_event.record()
+
+    def check_waits(self, block: bool = True) -> None:
+        """Raises KernelError if a bounded wait of a kernel ran out in a step() made so far: its
+        logits are not valid.  The requests of that step are put back to the lengths they had.
+        ``block=False`` looks only if the step's words have already arrived on the host.  step()
+        looks this way on entry; a caller that reads the logits on the host calls it after its
+        synchronisation, before it uses them."""
+        ev = self._wait_event
+        if ev is None or (not block and not ev.query()):
+            return
+        ev.synchronize()
+        self._wait_event = None
+        self.raise_on_waits(self._wait_host.tolist())
+
+    def raise_on_waits(self, words) -> None:
+        msg = K.wait_error_message(words)
+        if not msg:
+            return
+        torch.cuda.synchronize()
+        K.read_wait_errors()                       # clears the words
+        last, self._last_step = getattr(self, "_last_step", None), None
+        if last is not None:
+            self.rollback(*last)
+        raise K.KernelError(msg)
 
     def _validate(self, entries: Sequence):
         ids, counts, want_rows, chunks = [], [], [], []
@@ -258,6 +328,9 @@ class Engine:
         in ``flat`` are taken on the device from ``ids[rows[i]]`` (what the step before sampled,
         not yet seen by the host)."""
         T, S, R = int(sum(counts)), len(ids), len(want_rows)
+        for rid in ids:
+            if self.cache.num_tokens(rid) > self.max_context:
+                raise ValueError(f"request {rid}: {self.cache.num_tokens(rid)} tokens exceed the context limit {self.max_context}")
         graph_step = (T == S and R == T and self.cfg.use_cuda_graphs and self.dtype == torch.bfloat16
                       and self._graphable and want_rows == list(range(T)))
         Tp = self._bucket(T) if graph_step else T          # captured steps run at a few batch sizes; the rest is padding
@@ -342,9 +415,10 @@ class Engine:
     _BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512)
 
     def _bucket(self, T: int) -> int:
+        cap = min(self.max_requests, self.max_tokens_per_step)      # what the workspace and the metadata are sized for
         for b in self._BUCKETS:
             if b >= T:
-                return min(b, self.max_requests) if self.max_requests >= T else T
+                return min(b, cap) if cap >= T else T
         return T
 
     def _ctx_bucket(self, max_ctx: int) -> int:

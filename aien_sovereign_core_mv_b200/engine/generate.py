@@ -66,12 +66,14 @@ class Generator:
         R = engine.max_requests
         dev = engine.device
         # two of each staging buffer: a step is prepared while the one before it is still in flight
-        self._ids_dev2 = [torch.empty(R, dtype=torch.int32, device=dev) for _ in range(2)]
-        self._ids_host2 = [torch.empty(R, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        # sampled ids, then the four error words of the kernels with bounded waits: one copy brings both
+        self._ids_dev2 = [torch.zeros(R + 4, dtype=torch.int32, device=dev) for _ in range(2)]
+        self._ids_host2 = [torch.zeros(R + 4, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self._fparams_host2 = [torch.empty((2, R), dtype=torch.float32, pin_memory=True) for _ in range(2)]   # temperature, top_p
         self._iparams_host2 = [torch.empty((2, R), dtype=torch.int32, pin_memory=True) for _ in range(2)]     # top_k, position
         self._lparams_host2 = [torch.empty((2, R), dtype=torch.int64, pin_memory=True) for _ in range(2)]     # seed, request id
         self._turn = 0
+        self._events = [torch.cuda.Event() for _ in range(2)]
         self._inflight = None        # (rows, host ids, count, event) of the step whose tokens the host has not seen
         self._fparams = torch.empty((2, R), dtype=torch.float32, device=dev)
         self._iparams = torch.empty((2, R), dtype=torch.int32, device=dev)
@@ -91,6 +93,8 @@ class Generator:
             if not (0 <= t < self.engine.vocab_size):
                 raise ValueError(f"request {request_id}: token id {t} is outside the vocabulary of {self.engine.vocab_size}")
         stops = list(self.engine.model.spec.stop_token_ids) if p.stop_token_ids is None else [int(t) for t in p.stop_token_ids]
+        if self._inflight is not None and any(e.id == int(request_id) for e in self._inflight[0]):
+            self._drain()                     # a token of an earlier request with this id is still on its way
         self.scheduler.submit(int(request_id), prompt, int(p.max_tokens), stops, int(priority))
         self.params[int(request_id)] = p
 
@@ -109,16 +113,30 @@ class Generator:
         self._drain()
         plan = self.scheduler.plan()
         if plan.entries:
-            rows, ids_dev = self._launch(plan, None)
-            sampled: List[int] = []
-            if rows:
-                host = self._ids_host2[self._turn & 1]
-                host[:len(rows)].copy_(ids_dev, non_blocking=False)
-                self.d2h_bytes += 4 * len(rows)
-                sampled = host[:len(rows)].tolist()
-            self.scheduler.commit(sampled)
-            self._log(plan, len(sampled))
+            rows, ids_dev = self._launch_or_rollback(plan, None)
+            n = len(rows)
+            host = self._ids_host2[self._turn & 1]
+            host[:n + 4].copy_(self._ids_dev2[self._turn & 1][:n + 4], non_blocking=False)
+            self.d2h_bytes += 4 * (n + 4)
+            vals = host[:n + 4].tolist()
+            msg = K.wait_error_message(vals[n:])
+            if msg:
+                # the step's results are not valid: the requests go back to where they were
+                K.read_wait_errors()
+                self.scheduler.rollback()
+                raise K.KernelError(msg)
+            self.scheduler.commit(vals[:n])
+            self._log(plan, n)
         return self._finished()
+
+    def _launch_or_rollback(self, plan, prev):
+        """A launch that is refused (or any other failure before the step is committed) leaves the
+        scheduler and the cache as they were before the plan."""
+        try:
+            return self._launch(plan, prev)
+        except Exception:
+            self.scheduler.rollback()
+            raise
 
     def _launch(self, plan, prev):
         """Runs the planned step and chooses one token per finished input on the device.
@@ -151,7 +169,8 @@ class Generator:
         logits = eng.run_reserved(ids, counts, flat, want_rows, feed=feed)
         self.h2d_bytes += 4 * eng._layout(t0, len(ids), len(want_rows))[1]
         self.steps += 1
-        ids_dev = self._sample(logits, rows) if rows else None
+        ids_dev = self._sample(logits, rows) if rows else self._ids_dev2[self._turn & 1][:0]
+        eng.collect_waits(self._ids_dev2[self._turn & 1][len(rows):len(rows) + 4])
         return rows, ids_dev
 
     def _log(self, plan, emitted: int) -> None:
@@ -201,14 +220,14 @@ class Generator:
         now = None
         if plan.entries:
             feed_from = ({e.id: r for r, e in enumerate(prev[0])}, prev[4]) if prev is not None else None
-            rows, ids_dev = self._launch(plan, feed_from)
-            if rows:
-                host = self._ids_host2[self._turn & 1]
-                host[:len(rows)].copy_(ids_dev, non_blocking=True)
-                ev = torch.cuda.Event()
-                ev.record()
-                self.d2h_bytes += 4 * len(rows)
-                now = (rows, host, len(rows), ev, ids_dev)
+            rows, ids_dev = self._launch_or_rollback(plan, feed_from)
+            n = len(rows)
+            host = self._ids_host2[self._turn & 1]
+            host[:n + 4].copy_(self._ids_dev2[self._turn & 1][:n + 4], non_blocking=True)
+            ev = self._events[self._turn & 1]
+            ev.record()
+            self.d2h_bytes += 4 * (n + 4)
+            now = (rows, host, n, ev, ids_dev)
             self.scheduler.commit_deferred()
             self._log(plan, len(rows))
         self._inflight = now
@@ -228,8 +247,18 @@ class Generator:
     def _resolve(self, flight) -> None:
         rows, host, n, ev, _ = flight
         ev.synchronize()
-        toks = host[:n].tolist()
-        self.scheduler.resolve([(e.id, t) for e, t in zip(rows, toks)])
+        vals = host[:n + 4].tolist()
+        msg = K.wait_error_message(vals[n:])
+        if msg:
+            # Later steps were launched on top of the broken one: nothing the running requests hold
+            # can be trusted.  They are queued again and recomputed from the tokens known so far.
+            torch.cuda.synchronize()
+            K.read_wait_errors()
+            self._inflight = None
+            self.scheduler.restart_running()
+            raise K.KernelError(msg)
+        if n:
+            self.scheduler.resolve_for([(e.id, t, e.arrival) for e, t in zip(rows, vals[:n])])
 
     def _drain(self) -> None:
         """Takes in the tokens of a step that is still in flight."""

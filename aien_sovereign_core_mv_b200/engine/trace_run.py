@@ -43,8 +43,7 @@ def main(argv=None) -> int:
     pool_tokens = ((args.max_tokens + page - 1) // page) * page
     ec = EngineConfig(dtype=args.dtype, page_size=page, max_cache_tokens=pool_tokens, max_requests=args.max_requests,
                       max_batch_tokens=max(pool_tokens, 64), max_context=0)
-    engine = Engine.from_folder(args.model, ec)
-    engine.max_context = min(engine.max_context, pool_tokens) if engine.max_context else pool_tokens
+    engine = Engine.from_folder(args.model, ec)       # its context limit is the model's, or the pool if that is smaller
     print("trace_run: ready", file=sys.stderr, flush=True)
 
     ids = {}                                  # trace ids (any JSON scalar) -> engine request ids
@@ -66,11 +65,13 @@ def main(argv=None) -> int:
             logits = engine.step(entries)
             if logits.shape[0] > 0:
                 arr = logits.to("cpu").numpy().astype("<f4", copy=False)
+                engine.check_waits()                  # a kernel wait that ran out makes the step fail, not write
                 tmp = os.path.join(args.out, f".{step}.f32.tmp")
                 arr.tofile(tmp)
                 os.replace(tmp, os.path.join(args.out, f"{step}.f32"))
             else:
                 torch.cuda.synchronize()
+                engine.check_waits()
         for rid in rec.get("end", []):
             key = json.dumps(rid)
             if key in ids:

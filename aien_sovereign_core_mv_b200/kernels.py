@@ -138,6 +138,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_paged_attention_decode_stream": [P, L, P, P, I, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, P],
         "aien_paged_attention_decode_stream_supports": [I, I, I, I, I],
         "aien_attention_decode_stream_error": [],
+        "aien_collect_wait_errors": [P, P],
         "aien_paged_attention_decode_fused": [P, L, P, L, P, L, P, P, I, F, P, P, I, P, P, P, P, I, P, P, L, P, P, P,
                                               I, I, I, I, I, F, I, I, P],
     }
@@ -721,3 +722,31 @@ def paged_attention_prefill(q, k_cache, v_cache, block_table, max_blocks, q_star
 def attention_prefill_tc_error() -> int:
     """Code left by a wait that ran out in the tcgen05 prefill attention kernel (0: none)."""
     return int(lib().aien_attention_prefill_tc_error())
+
+
+# ---------------------------------------------------------------------------- bounded waits
+# The kernels whose mbarrier waits are bounded, in the order of the words collect_wait_errors writes.
+WAIT_KERNELS = ("gemm_tc", "gemv_stream", "attention_prefill_tc", "attention_decode_stream")
+
+
+def collect_wait_errors(out: torch.Tensor) -> None:
+    """out[0:4] (int32, device) = the error words of WAIT_KERNELS, read in the stream behind
+    whatever was launched before.  The words stay set until read_wait_errors() clears them."""
+    _dev(out)
+    assert out.dtype == torch.int32 and out.numel() >= 4 and out.is_contiguous()
+    _check(lib().aien_collect_wait_errors(_p(out), _stream()), "collect_wait_errors")
+
+
+def read_wait_errors() -> tuple:
+    """The four error words, read with synchronous copies (the device is idle afterwards) and
+    cleared.  All zero: every bounded wait so far was met."""
+    return (gemm_tc_error(), gemv_stream_error(), attention_prefill_tc_error(), attention_decode_stream_error())
+
+
+def wait_error_message(words) -> str:
+    """'' when all words are zero, else which kernels gave up and with which code."""
+    bad = [f"{name} (code {int(w)})" for name, w in zip(WAIT_KERNELS, words) if int(w) != 0]
+    if not bad:
+        return ""
+    return ("a bounded wait ran out inside " + ", ".join(bad) +
+            ": the results of the step are not valid (a broken TMA / tensor-core pipeline, not a property of the inputs)")

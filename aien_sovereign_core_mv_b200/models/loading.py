@@ -28,7 +28,7 @@ def build_model_from_folder(model_dir: str, dtype: str, strict: bool = False) ->
     cfg, spec = model_spec_for(raw, read_generation_config(model_dir), strict)
     model = Decoder(spec)
     shapes = {name: shape for name, (shape, _) in model.catalog().items()}
-    model.bind(iter_checkpoint(model_dir, shapes, dtype))
+    model.bind(iter_checkpoint(model_dir, shapes, dtype, strict))
     return cfg, model
 
 

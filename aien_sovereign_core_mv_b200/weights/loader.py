@@ -1,9 +1,13 @@
 """Bind the tensors of a checkpoint to a catalog of wanted names and shapes.
 
 The catalog is what the model's parts declare (name -> shape).  One :class:`WeightError`
-reports everything that is wrong at once: missing tensors, unexpected tensors and wrong
-shapes, like the reference's strict catalog check (crates/aien-inference-abi/src/checkpoint.rs:
-28-55, 262-319) but collected instead of first-error-only.
+reports everything that is wrong at once: missing tensors, wrong shapes and, under
+``strict``, unexpected tensors; like the reference's catalog check (crates/aien-inference-abi/
+src/checkpoint.rs:28-55, 262-319) but collected instead of first-error-only.  Without ``strict``
+tensors the model does not want are left unread, as the reference leaves them (it has a
+MissingTensor error and none for extras; src/weights.rs:854 skips ``lm_head.weight`` of a tied
+model): a tied checkpoint that still ships its head, or old files with ``rotary_emb.inv_freq``,
+load.
 
 Dtype policy: bfloat16 stays bfloat16; a tensor stored in 32 bits stays 32-bit (float16 is
 widened exactly to float32); integer tables become int32.  The float32 engine widens every
@@ -11,6 +15,7 @@ floating tensor to float32, which is exact for bfloat16 values.
 """
 from __future__ import annotations
 
+import sys
 from typing import Dict, List, Mapping, Sequence, Tuple
 
 import torch
@@ -46,10 +51,12 @@ _FLOAT = ("BF16", "F16", "F32")
 _INT = ("I32", "I64", "U8")
 
 
-def check_catalog(entries: Mapping[str, object], catalog: Mapping[str, Tuple[int, ...]]) -> None:
-    """Raise one WeightError if names or shapes disagree; ``entries`` has ``.shape``/``.dtype``."""
+def check_catalog(entries: Mapping[str, object], catalog: Mapping[str, Tuple[int, ...]], strict: bool = False) -> List[str]:
+    """Raise one WeightError if names or shapes disagree; ``entries`` has ``.shape``/``.dtype``.
+    Returns the names the model does not want: alone they are an error only under ``strict``;
+    beside another fault they are listed in its error."""
     missing = [n for n in catalog if n not in entries]
-    unexpected = [n for n in entries if n not in catalog]
+    extra = sorted(n for n in entries if n not in catalog)
     wrong_shape, wrong_dtype = [], []
     for n, want in catalog.items():
         e = entries.get(n)
@@ -59,15 +66,28 @@ def check_catalog(entries: Mapping[str, object], catalog: Mapping[str, Tuple[int
             wrong_shape.append((n, tuple(want), tuple(e.shape)))
         if e.dtype not in _FLOAT and e.dtype not in _INT:
             wrong_dtype.append((n, e.dtype))
-    if missing or unexpected or wrong_shape or wrong_dtype:
-        raise WeightError(sorted(missing), sorted(unexpected), wrong_shape, wrong_dtype)
+    if missing or wrong_shape or wrong_dtype or (strict and extra):
+        # the error names the unwanted tensors too: a missing tensor is often one stored under another name
+        raise WeightError(sorted(missing), extra, wrong_shape, wrong_dtype)
+    return extra
 
 
-def load_checkpoint(model_dir: str, catalog: Mapping[str, Tuple[int, ...]], dtype: str) -> Dict[str, torch.Tensor]:
+def _catalog_elements(catalog: Mapping[str, Tuple[int, ...]]) -> int:
+    total = 0
+    for shape in catalog.values():
+        n = 1
+        for d in shape:
+            n *= int(d)
+        total += n
+    return total
+
+
+def load_checkpoint(model_dir: str, catalog: Mapping[str, Tuple[int, ...]], dtype: str, strict: bool = False) -> Dict[str, torch.Tensor]:
     """CPU tensors for every catalog name, after the catalog check.  ``dtype`` is the engine's."""
     files = CheckpointFiles(model_dir)
     try:
-        check_catalog(files.entries, catalog)
+        check_catalog(files.entries, catalog, strict)
+        files.check_budget(_catalog_elements(catalog))
         out: Dict[str, torch.Tensor] = {}
         for name in catalog:
             out[name] = convert_stored(files.tensor(name), files.entries[name].dtype, dtype)
@@ -76,11 +96,15 @@ def load_checkpoint(model_dir: str, catalog: Mapping[str, Tuple[int, ...]], dtyp
         files.close()
 
 
-def iter_checkpoint(model_dir: str, catalog: Mapping[str, Tuple[int, ...]], dtype: str):
+def iter_checkpoint(model_dir: str, catalog: Mapping[str, Tuple[int, ...]], dtype: str, strict: bool = False):
     """Like :func:`load_checkpoint` but yields ``(name, tensor)`` one at a time (bounded host memory)."""
     files = CheckpointFiles(model_dir)
     try:
-        check_catalog(files.entries, catalog)
+        extra = check_catalog(files.entries, catalog, strict)
+        files.check_budget(_catalog_elements(catalog))
+        if extra:
+            print(f"[aien-b200] {len(extra)} tensors of the checkpoint are not used by the model: "
+                  + ", ".join(extra[:8]) + (" ..." if len(extra) > 8 else ""), file=sys.stderr)
         for name in catalog:
             yield name, convert_stored(files.tensor(name), files.entries[name].dtype, dtype)
     finally:

@@ -21,7 +21,12 @@ from typing import Dict, Iterable, Iterator, List, Mapping, Optional, Tuple
 import numpy as np
 import torch
 
-MAX_HEADER_BYTES = 256 << 20   # checkpoint.rs:553
+# Bounds on what is read from disk (crates/aien-inference-abi/src/checkpoint.rs:552-556): absurd
+# metadata and sparse files of absurd length are refused before anything is mapped.
+MAX_INDEX_BYTES = 16 << 20
+MAX_HEADER_BYTES = 256 << 20
+MAX_SHARD_BYTES = 256 << 30
+MAX_CHECKPOINT_BYTES = 1 << 40
 
 _DTYPE_BYTES = {"BF16": 2, "F16": 2, "F32": 4, "I32": 4, "I64": 8, "U8": 1, "F64": 8}
 _TORCH_OF = {
@@ -107,6 +112,8 @@ def resolve_files(model_dir_or_file: str) -> List[str]:
     single = os.path.join(p, "model.safetensors")
     index = os.path.join(p, "model.safetensors.index.json")
     if os.path.exists(index):
+        if os.path.getsize(index) > MAX_INDEX_BYTES:
+            raise SafetensorsError(f"{index}: index exceeds {MAX_INDEX_BYTES} bytes")
         with open(index, "r", encoding="utf-8") as f:
             try:
                 wm = json.load(f)["weight_map"]
@@ -128,9 +135,16 @@ class CheckpointFiles:
     def __init__(self, model_dir_or_file: str):
         self.files = resolve_files(model_dir_or_file)
         self.entries: Dict[str, TensorEntry] = {}
+        self.total_bytes = 0
         for path in self.files:
             if not os.path.isfile(path) or os.path.islink(path):
                 raise SafetensorsError(f"{path}: not a regular file")
+            size = os.path.getsize(path)
+            if size > MAX_SHARD_BYTES:
+                raise SafetensorsError(f"{path}: file exceeds {MAX_SHARD_BYTES} bytes")
+            self.total_bytes += size
+            if self.total_bytes > MAX_CHECKPOINT_BYTES:
+                raise SafetensorsError(f"{path}: checkpoint exceeds the aggregate limit of {MAX_CHECKPOINT_BYTES} bytes")
             for name, e in read_header(path).items():
                 if name in self.entries:
                     raise SafetensorsError(f"tensor {name!r} is stored twice ({self.entries[name].file} and {path})")
@@ -139,6 +153,14 @@ class CheckpointFiles:
 
     def names(self) -> List[str]:
         return list(self.entries)
+
+    def check_budget(self, catalog_elements: int) -> None:
+        """A small model must not authorise a huge payload: the files together may hold at most
+        twice the catalog's bytes at two bytes an element, plus one header budget per file
+        (checkpoint.rs:836-857).  Room for extra tensors and for 32-bit storage, not for more."""
+        budget = min(2 * (2 * int(catalog_elements)) + len(self.files) * (MAX_HEADER_BYTES + 8), MAX_CHECKPOINT_BYTES)
+        if self.total_bytes > budget:
+            raise SafetensorsError(f"checkpoint of {self.total_bytes} bytes exceeds the catalog byte budget {budget}")
 
     def _map(self, path: str) -> mmap.mmap:
         m = self._maps.get(path)

@@ -252,3 +252,79 @@ def test_deferred_commit_rules():
     assert len(ev) == 1 and ev[0].reason.name == "StopToken" and ev[0].generated == [fake_token(1, 6)]
     s.resolve([(1, 5)])                                     # the value of the dropped token arrives: ignored
     assert cm.free_count(0) == 64 and not s.has_work()
+
+
+def test_rollback_of_a_failed_step_restores_lengths_and_the_step_can_be_planned_again():
+    cm, s = make()
+    s.submit(1, list(range(20)), 4)
+    s.submit(2, list(range(5)), 4)
+    p0 = s.plan()
+    s.commit([fake_token(e.id, e.start + len(e.tokens)) for e in p0.entries if e.wants_logits])
+    held = {1: cm.num_tokens(1), 2: cm.num_tokens(2)}
+    free = cm.free_count(0)
+    p1 = s.plan()                                             # request 1: rest of the prompt; request 2: one token
+    assert cm.num_tokens(1) == 20 and cm.num_tokens(2) == 6
+    s.rollback()                                              # the launch failed
+    assert {1: cm.num_tokens(1), 2: cm.num_tokens(2)} == held and cm.free_count(0) == free and cm.check() == ""
+    with pytest.raises(RuntimeError):
+        s.rollback()                                          # nothing is planned now
+    p2 = s.plan()                                             # the same step again
+    assert [(e.id, list(e.tokens), e.start) for e in p2.entries] == [(e.id, list(e.tokens), e.start) for e in p1.entries]
+    s.commit([fake_token(e.id, e.start + len(e.tokens)) for e in p2.entries if e.wants_logits])
+    done = drive(s, cm)
+    assert done[1][0] == expected(1, 20, 4) and done[2][0] == expected(2, 5, 4)
+
+
+def test_rollback_of_the_step_that_admitted_a_request():
+    cm, s = make()
+    s.submit(7, list(range(9)), 3)
+    s.plan()
+    s.rollback()
+    assert cm.num_tokens(7) == 0 and cm.free_count(0) == 64 and cm.check() == ""
+    done = drive(s, cm)
+    assert done[7][0] == expected(7, 9, 3) and cm.num_requests == 0
+
+
+def test_restart_running_recomputes_from_known_tokens_only():
+    cm, s = make()
+    s.submit(1, list(range(6)), 6)
+    s.submit(2, list(range(3)), 6)
+    for _ in range(2):                                        # two steps resolved in the ordinary way
+        p = s.plan()
+        s.commit([fake_token(e.id, e.start + len(e.tokens)) for e in p.entries if e.wants_logits])
+    p = s.plan()
+    s.commit_deferred()                                       # a third whose tokens never arrive
+    assert s.record(1).unresolved == 1
+    s.restart_running()
+    assert cm.num_requests == 0 and cm.free_count(0) == 64 and cm.check() == ""
+    r = s.record(1)
+    assert r.unresolved == 0 and list(r.generated) == expected(1, 6, 2) and r.computed == 0 and r.preemptions == 1
+    s.resolve_for([(e.id, 99, e.arrival) for e in p.entries])    # late values of the dropped step change nothing
+    assert list(s.record(1).generated) == expected(1, 6, 2)
+    done = drive(s, cm)
+    assert done[1][0] == expected(1, 6, 6) and done[2][0] == expected(2, 3, 6)
+
+
+def test_prompt_at_or_beyond_the_context_limit_is_aborted_and_blocks_nobody():
+    cm, s = make(pages=64, page=4, max_context=32)
+    s.submit(1, list(range(100)), 4)                          # would need 25 pages of a block table that holds 8
+    s.submit(2, list(range(32)), 4)                           # no room for a single new token either
+    s.submit(3, list(range(10)), 4)
+    ev = {e.id: e for e in s.take_finished()}
+    assert ev[1].reason.name == "Aborted" and "context limit" in ev[1].message and ev[2].reason.name == "Aborted"
+    done = drive(s, cm)
+    assert done[3][0] == expected(3, 10, 4) and cm.check() == "" and cm.num_requests == 0
+
+
+def test_a_value_of_an_earlier_submission_never_reaches_a_new_request_with_the_same_id():
+    cm, s = make()
+    s.submit(5, list(range(4)), 8)
+    p = s.plan()
+    s.commit_deferred()                                       # its first token is still on the device
+    assert s.cancel(5)
+    s.submit(5, list(range(7)), 8)                            # the id is used again before that token arrives
+    s.resolve_for([(e.id, 42, e.arrival) for e in p.entries if e.wants_logits])     # dropped: another submission
+    assert list(s.record(5).generated) == []
+    s.take_finished()
+    done = drive(s, cm)
+    assert done[5][0] == expected(5, 7, 8)

@@ -129,3 +129,41 @@ def test_sharded_index(tmp_path):
     json.dump({"weight_map": {"a": "s1.safetensors", "b": "s2.safetensors"}}, open(os.path.join(d, "model.safetensors.index.json"), "w"))
     with pytest.raises(SafetensorsError, match="stored twice"):
         CheckpointFiles(d)
+
+
+def test_extra_tensors_load_unless_strict(tmp_path):
+    """A tied checkpoint that still ships lm_head.weight, or old files with rotary_emb.inv_freq, load
+    in the reference (crates/aien-inference-abi/src/weights.rs:854 skips the head of a tied model;
+    checkpoint.rs has no error for extras); here too, and `strict` refuses them by name."""
+    d = write_random_model(str(tmp_path / "m"), H.TINY["B"], 1)          # tied
+    f = CheckpointFiles(d)
+    tensors = {n: f.tensor(n) for n in f.names()}
+    f.close()
+    tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(16, dtype=torch.float32)
+    write_safetensors(os.path.join(d, "model.safetensors"), tensors)
+    got = load_checkpoint(d, catalog_of("B"), "bfloat16")
+    assert set(got) == set(catalog_of("B"))
+    with pytest.raises(WeightError) as e:
+        load_checkpoint(d, catalog_of("B"), "bfloat16", strict=True)
+    assert e.value.unexpected == ["lm_head.weight", "model.layers.0.self_attn.rotary_emb.inv_freq"] and not e.value.missing
+
+
+def test_size_caps(tmp_path, monkeypatch):
+    """A small catalog does not authorise a huge payload (crates/aien-inference-abi/src/checkpoint.rs:552-556, 836-857)."""
+    import aien_sovereign_core_mv_b200.weights.safetensors_io as sio
+    d = write_random_model(str(tmp_path / "m"), H.TINY["A"], 1)
+    cat = catalog_of("A")
+    load_checkpoint(d, cat, "bfloat16")
+    f = CheckpointFiles(d)
+    tensors = {n: f.tensor(n) for n in f.names()}
+    f.close()
+    tensors["padding"] = torch.zeros(4 * sum(t.numel() for t in tensors.values()), dtype=torch.bfloat16)
+    write_safetensors(os.path.join(d, "model.safetensors"), tensors)
+    load_checkpoint(d, cat, "bfloat16")                                # inside the real budget (one header allowance)
+    monkeypatch.setattr(sio, "MAX_HEADER_BYTES", 1 << 16)          # shrink the header allowance: the budget is 2 x catalog bytes
+    with pytest.raises(sio.SafetensorsError, match="catalog byte budget"):
+        load_checkpoint(d, cat, "bfloat16")
+    monkeypatch.setattr(sio, "MAX_SHARD_BYTES", 1000)
+    with pytest.raises(sio.SafetensorsError, match="file exceeds 1000 bytes"):
+        load_checkpoint(d, cat, "bfloat16")
