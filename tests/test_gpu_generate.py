@@ -172,3 +172,88 @@ def test_command_line(folders, tmp_path):
     assert rec["tokens"] == [want]
     bad = subprocess.run([cmd[0], "generate", "--model-dir", str(tmp_path), "--prompt-ids", "1"], capture_output=True, text=True, timeout=600)
     assert bad.returncode != 0 and "config.json" in bad.stderr
+
+
+# ------------------------------------------------------------------ a kernel wait that runs out
+def _break_one_step(monkeypatch, K, at_call):
+    """Makes the `at_call`-th reading of the wait words report that the streamed product gave up,
+    without touching the device: the words themselves stay zero."""
+    real = K.wait_error_message
+    calls = {"n": 0}
+
+    def fake(words):
+        calls["n"] += 1
+        return real((0, 7, 0, 0)) if calls["n"] == at_call else real(words)
+
+    monkeypatch.setattr(K, "wait_error_message", fake)
+    return calls
+
+
+def test_a_failed_wait_raises_from_step_and_the_cache_is_rolled_back(folders, monkeypatch):
+    from aien_sovereign_core_mv_b200 import kernels as K
+    d = folders["A"]
+    toks = H.tokens_for("A", 40, 5)
+    eng = H.engine_for(d, "float32", 16, 256)
+    eng.step([(1, toks[:20], [])])
+    eng.check_waits()
+    _break_one_step(monkeypatch, K, 1)
+    logits = eng.step([(1, toks[20:30], [9]), (2, toks[:5], [4])])
+    with pytest.raises(K.KernelError, match="gemv_stream .code 7."):
+        eng.check_waits()                                     # the caller looks before it uses the logits
+    assert eng.num_tokens(1) == 20 and not eng.has_request(2) and eng.cache_state()["check"] == ""
+    again = eng.step([(1, toks[20:30], [9]), (2, toks[:5], [4])]).cpu().numpy()    # the same step, now clean
+    eng.check_waits()
+    want = H.plain_logits(d, toks[:30])
+    H.assert_close(again[0], want[29], H.FP32_TOL, "after the rollback")
+
+
+@pytest.mark.parametrize("overlap", [False, True])
+def test_a_failed_wait_raises_from_generation_and_nothing_is_lost(folders, monkeypatch, overlap):
+    """Step by step the failed step is rolled back (cache lengths as before) and planned again; with
+    overlapping steps everything that runs is queued again and recomputed from the tokens known so
+    far.  Either way the tokens that come out are those of an undisturbed run."""
+    from aien_sovereign_core_mv_b200 import kernels as K
+    from aien_sovereign_core_mv_b200.engine.generate import Generator
+    from aien_sovereign_core_mv_b200.sampling import SamplingParams
+    d = folders["B"]
+    prompts = [H.tokens_for("B", n, 70 + n) for n in (9, 33, 18)]
+    sp = SamplingParams(temperature=0.0, max_tokens=10, stop_token_ids=[])
+    eng = H.engine_for(d, "float32", 8, 512, prefill_chunk_size=16, max_prefill_tokens=32, async_scheduling=overlap)
+    want = [r.tokens for r in Generator(eng).generate(prompts, sp)]
+    gen = Generator(eng)
+    for i, p in enumerate(prompts):
+        gen.submit(100 + i, p, sp)
+    _break_one_step(monkeypatch, K, 4)
+    done, raised = {}, 0
+    for _ in range(200):
+        if not (gen.scheduler.has_work() or gen._inflight is not None):
+            break
+        held = {r: eng.num_tokens(r) for r in (100, 101, 102) if eng.has_request(r)}
+        try:
+            for r in gen.advance():
+                done[r.request_id] = r
+        except K.KernelError as e:
+            raised += 1
+            assert "gemv_stream" in str(e) and eng.cache_state()["check"] == ""
+            if overlap:
+                assert eng.cache_state()["requests"] == 0              # all queued again, their pages given back
+            else:
+                assert {r: eng.num_tokens(r) for r in held} == held    # lengths as before the step
+    for r in gen.flush():
+        done[r.request_id] = r
+    assert raised == 1 and [done[100 + i].tokens for i in range(3)] == want
+    assert eng.cache_state()["requests"] == 0 and eng.cache_state()["check"] == ""
+
+
+def test_prompts_beyond_the_context_limit_are_aborted_and_the_rest_runs(folders):
+    from aien_sovereign_core_mv_b200.engine.generate import Generator
+    from aien_sovereign_core_mv_b200.sampling import SamplingParams
+    d = folders["A"]
+    eng = H.engine_for(d, "float32", 16, 1024, max_context=64, prefill_chunk_size=32)
+    gen = Generator(eng)
+    sp = SamplingParams(temperature=0.0, max_tokens=4, stop_token_ids=[])
+    res = gen.generate([H.tokens_for("A", 100, 1), H.tokens_for("A", 12, 2), H.tokens_for("A", 64, 3)], sp)
+    assert res[0].finish_reason == "aborted" and "context limit" in res[0].message and res[0].tokens == []
+    assert res[2].finish_reason == "aborted"
+    assert res[1].finish_reason == "length" and res[1].tokens == plain_greedy(d, H.tokens_for("A", 12, 2), 4)
+    assert eng.cache_state()["requests"] == 0 and eng.cache_state()["check"] == ""

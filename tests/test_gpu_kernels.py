@@ -842,3 +842,70 @@ def test_decode_attention_with_qk_work_folded_in(K, nq, nkv, hd, page, window, n
     torch.cuda.synchronize()
     assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
     assert torch.equal(got, want)
+
+
+# ------------------------------------------------------------------ the output head of a real vocabulary
+def test_the_kernels_of_the_head_at_151936_rows(K):
+    """N = 151,936 is what the logits product, the argmax and the sampler meet in serving (the
+    vocabulary of Qwen3); K = 256 keeps the float64 reference cheap.  The streamed product with
+    float32 output at 1 and 8 rows, the tensor-core tiles at 64 rows, argmax and a nucleus draw."""
+    from aien_sovereign_core_mv_b200.sampling import philox_uniform
+    V, Kd = 151936, 256
+    g = torch.Generator().manual_seed(9)
+    w = (torch.randn(V, Kd, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    a = torch.randn(64, Kd, generator=g).to(torch.bfloat16).cuda()
+    want = (a.double().cpu() @ w.double().cpu().T).numpy()
+    for M in (1, 8):
+        out = torch.empty(M, V, dtype=torch.float32, device="cuda")
+        K.gemv(a[:M], w, out)
+        H.assert_close(out.cpu().numpy(), want[:M], 2e-5, f"streamed product, {M} rows, float32 logits")
+    out = torch.empty(64, V, dtype=torch.float32, device="cuda")
+    K.gemm_tc(a, w, out)
+    H.assert_close(out.cpu().numpy(), want, 2e-5, "tensor-core product, 64 rows, float32 logits")
+    assert K.read_wait_errors() == (0, 0, 0, 0)
+    # argmax: the maximum in the last 16-byte group and, on another row, twice (the lower id wins)
+    lg = out[:8].clone()
+    lg[0, V - 1] = lg[0].max() + 1
+    lg[1, 151000] = lg[1, 77] = lg[1].max() + 2
+    ids = torch.empty(8, dtype=torch.int32, device="cuda")
+    K.argmax_rows(lg, ids)
+    host = lg.cpu().numpy()
+    assert ids.cpu().tolist() == [pm.argmax_token(r) for r in host] and ids[0].item() == V - 1 and ids[1].item() == 77
+    # sampling: scaled so that a few dozen tokens carry the nucleus; every row against the plain sampler
+    sharp = (lg * 6).contiguous()
+    temp, top_p, top_k = [0.7, 1.0, 0.9, 0.7, 1.3, 0.8, 0.7, 1.0], [0.95, 0.9, 1.0, 0.5, 0.95, 1.0, 0.99, 0.3], [0, 0, 50, 0, 200, 1000, 0, 7]
+    scratch = torch.empty(8 * V, device="cuda")
+    sharp_host = sharp.cpu().numpy()
+    miss = 0
+    for position in (0, 3, 1000):
+        K.sample_rows(sharp, torch.tensor(temp).cuda(), torch.tensor(top_p).cuda(), torch.tensor(top_k, dtype=torch.int32).cuda(),
+                      torch.arange(8, dtype=torch.int64).cuda() + 40, torch.arange(8, dtype=torch.int64).cuda() + 1,
+                      torch.full((8,), position, dtype=torch.int32).cuda(), scratch, ids)
+        got = ids.cpu().tolist()
+        for r in range(8):
+            kept, _ = pm.kept_set(sharp_host[r], temp[r], top_p[r], top_k[r])
+            assert got[r] in kept, (position, r)
+            miss += got[r] != pm.sample_token(sharp_host[r], temp[r], top_p[r], top_k[r], philox_uniform(40 + r, 1 + r, position))
+    assert miss <= 1          # float32 exponentials against float64: only a knife-edge draw may differ
+
+
+def test_philox_known_answers_on_the_device(K):
+    """The uniform number of a draw, read back from a two-token distribution: with probabilities
+    (p, 1 - p) the draw is token 0 iff u < p.  At (seed, request, position) = (0, 0, 0) the counter
+    and the key are all zero, the first known-answer vector of Philox4x32-10 (6627e8d5 e169c58d ...);
+    elsewhere the host function, which tests/test_sampling_host.py holds to all three vectors."""
+    from aien_sovereign_core_mv_b200.sampling import philox_uniform
+    u0 = float(((0x6627e8d5 << 32) | 0xe169c58d) >> 11) / 9007199254740992.0
+    assert philox_uniform(0, 0, 0) == u0
+    cases = [(0, 0, 0), (1, 0, 0), (0, 1, 0), (0, 0, 1), (2 ** 63 - 1, 2 ** 40 + 3, 2 ** 31 - 1), (12345, 678, 90)]
+    for seed, rid, pos in cases:
+        u = philox_uniform(seed, rid, pos)
+        for p, want in ((u + 1e-6, 0), (u - 1e-6, 1)):
+            if not 0.0 < p < 1.0:
+                continue
+            lg = torch.tensor([[math.log(p), math.log1p(-p)]], dtype=torch.float32).cuda()
+            out = torch.empty(1, dtype=torch.int32, device="cuda")
+            K.sample_rows(lg, torch.tensor([1.0]).cuda(), torch.tensor([1.0]).cuda(), torch.tensor([0], dtype=torch.int32).cuda(),
+                          torch.tensor([seed], dtype=torch.int64).cuda(), torch.tensor([rid], dtype=torch.int64).cuda(),
+                          torch.tensor([pos], dtype=torch.int32).cuda(), torch.empty(2, device="cuda"), out)
+            assert out.item() == want, (seed, rid, pos, p)

@@ -113,3 +113,102 @@ def test_long_context_bfloat16_follows_float32():
         del eng
         torch.cuda.empty_cache()
     H.assert_close(out["bfloat16"], out["float32"], H.BF16_TOL, "long context, bfloat16 against float32")
+
+
+# ------------------------------------------------------------------ the schedules of serving, against the plain implementation
+@pytest.fixture(scope="module")
+def prefixes(tmp_path_factory):
+    """One sequence of 1,030 tokens through the plain implementation (Qwen3-8B layer shape, two
+    layers).  Every request of the tests below holds a prefix of it, so the plain logits of one
+    forward pass serve all of them: the model is causal."""
+    from aien_sovereign_core_mv_b200 import write_random_model
+    d = write_random_model(str(tmp_path_factory.mktemp("prefixes") / "m"), SHAPES["qwen3_8b"], seed=2, init_std=0.02)
+    toks = [int(t) for t in np.random.default_rng(11).integers(0, SHAPES["qwen3_8b"]["vocab_size"], 1030)]
+    return d, toks, H.plain_logits(d, toks)
+
+
+def _prefill_prefixes(eng, toks, lengths, first_id, budget=2048):
+    """Requests first_id.. hold toks[:L] for L in lengths; several requests a step under `budget` tokens."""
+    step, used = [], 0
+    for i, L in enumerate(lengths):
+        if used + L > budget and step:
+            eng.step(step)
+            step, used = [], 0
+        step.append((first_id + i, toks[:L], []))
+        used += L
+    if step:
+        eng.step(step)
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", H.FP32_TOL), ("bfloat16", H.BF16_TOL)])
+@pytest.mark.parametrize("batch", [40, 64])
+def test_many_requests_decoding_together_at_unequal_contexts(prefixes, batch, dtype, tol):
+    """What a decode step of a large batch runs: the tile product at 32 / 64 rows with its partial
+    products summed by the norm, q/k and row-gather kernels, and the decode attention's cut of all
+    (token, kv head) pairs into equal ranges, with contexts from 33 to 700 tokens."""
+    d, toks, want = prefixes
+    eng = H.engine_for(d, dtype, 16, batch * 720, max_requests=64, max_batch_tokens=2048)
+    lengths = [33 + (667 * i) // (batch - 1) for i in range(batch)]
+    lengths[1::2] = lengths[1::2][::-1]                      # neighbours in the batch differ widely
+    ids = list(range(1, batch + 1))
+    _prefill_prefixes(eng, toks, lengths, 1)
+    for s in range(3):
+        logits = eng.step([(r, [toks[L + s]], [0]) for r, L in zip(ids, lengths)]).cpu().numpy()
+        eng.check_waits()
+        for row, L in enumerate(lengths):
+            H.assert_close(logits[row], want[L + s], tol, f"{dtype} batch {batch}, step {s}, request {row + 1} at context {L + s + 1}")
+    for r in ids:
+        eng.end_request(r)
+    assert eng.cache_state()["check"] == "" and eng.cache_state()["requests"] == 0
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", H.FP32_TOL), ("bfloat16", H.BF16_TOL)])
+def test_a_long_portion_beside_many_single_tokens(prefixes, dtype, tol):
+    """The step a chunked-prefill server runs all day: a 512-token portion that starts at offset 512
+    (four query tiles, keys from earlier pages) beside 24 requests that bring one token each
+    (the split-key kernel over a list of tokens), products at 536 rows."""
+    d, toks, want = prefixes
+    eng = H.engine_for(d, dtype, 16, 1024 + 24 * 640, max_requests=32, max_batch_tokens=2048)
+    lengths = [20 + 25 * i for i in range(24)]               # 20 .. 595
+    _prefill_prefixes(eng, toks, lengths, 10)
+    eng.step([(1, toks[:512], [])])
+    wanted = [0, 127, 128, 300, 511]
+    entries = [(10 + i, [toks[L]], [0]) for i, L in enumerate(lengths[:12])]
+    entries.append((1, toks[512:1024], wanted))
+    entries += [(22 + i, [toks[L]], [0]) for i, L in enumerate(lengths[12:])]
+    logits = eng.step(entries).cpu().numpy()
+    eng.check_waits()
+    row = 0
+    for rid, tk, wnt in entries:
+        for w in wnt:
+            pos = 512 + w if rid == 1 else lengths[rid - 10]
+            H.assert_close(logits[row], want[pos], tol, f"{dtype} mixed step, request {rid}, position {pos}")
+            row += 1
+    assert eng.cache_state()["check"] == ""
+
+
+@pytest.fixture(scope="module")
+def long_request(tmp_path_factory):
+    """4,200 tokens through one layer of the Qwen3-8B shape in the plain implementation."""
+    from aien_sovereign_core_mv_b200 import write_random_model
+    cfg = dict(SHAPES["qwen3_8b"], num_hidden_layers=1, max_position_embeddings=8192)
+    d = write_random_model(str(tmp_path_factory.mktemp("long") / "m"), cfg, seed=5, init_std=0.02)
+    toks = [int(t) for t in np.random.default_rng(12).integers(0, cfg["vocab_size"], 4200)]
+    rows = [0, 1, 2047, 2048, 2049, 3000, 4095] + list(range(4096, 4200))
+    return d, toks, rows, H.plain_logits(d, toks)[rows]
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", H.FP32_TOL), ("bfloat16", H.BF16_TOL)])
+def test_a_request_of_4200_tokens(long_request, dtype, tol):
+    """2,048 + 2,048 tokens as two portions, then 104 single tokens: the portion at an offset reads
+    16 earlier key blocks, the single tokens attend over 33 key chunks, and the 32-bit attention
+    kernel walks the same length; each is held to the plain implementation, not to one another."""
+    d, toks, rows, want = long_request
+    eng = H.engine_for(d, dtype, 16, 4352, max_requests=2, max_batch_tokens=2048, max_context=4352)
+    got = [eng.step([(1, toks[:2048], [0, 1, 2047])]).cpu().numpy(),
+           eng.step([(1, toks[2048:4096], [0, 1, 952, 2047])]).cpu().numpy()]
+    for t in toks[4096:]:
+        got.append(eng.step([(1, [t], [0])]).cpu().numpy())
+    eng.check_waits()
+    H.assert_close(np.concatenate(got), want, tol, f"{dtype} 4,200-token request (rows {rows[:7]} and 4096..4199)")
+    assert eng.cache_state()["check"] == ""
