@@ -79,9 +79,11 @@ class Engine:
             tokens = int(engine_config.max_cache_tokens or self.max_context)
             pages = (tokens + self.page_size - 1) // self.page_size
         self.num_pages = pages
+        # what block tables, scratch and key-chunk counts are sized for: a request that keeps every
+        # key can never be longer than the whole pool, whatever the context limit says
+        self.table_context = self.max_context
         if any(need.kind == "full" for need in model.group_needs):
-            # a request that keeps every key can never be longer than the whole pool
-            self.max_context = min(self.max_context, pages * self.page_size)
+            self.table_context = min(self.max_context, pages * self.page_size)
         gspecs, self.storage = [], []
         kinds = {"full": self.host.GroupKind.Full, "window": self.host.GroupKind.Window, "state": self.host.GroupKind.State}
         for need, slots in zip(model.group_needs, model.group_slots):
@@ -94,12 +96,12 @@ class Engine:
                 self.storage.append(torch.zeros((slots, 2, pages * self.page_size, need.num_kv_heads, need.head_dim),
                                                 dtype=self.dtype, device=self.device))
         self.cache = self.host.CacheManager(self.page_size, gspecs, self.max_requests)
-        self.max_blocks = (self.max_context + self.page_size - 1) // self.page_size
+        self.max_blocks = (self.table_context + self.page_size - 1) // self.page_size
 
         # ---- workspace and metadata buffers
         itemsize = 2 if self.dtype == torch.bfloat16 else 4
         T = self.max_tokens_per_step
-        self.limits = StepLimits(max_tokens=T, max_seqs=self.max_requests, max_context=self.max_context, itemsize=itemsize)
+        self.limits = StepLimits(max_tokens=T, max_seqs=self.max_requests, max_context=self.table_context, itemsize=itemsize)
         self.workspace = Workspace(model.step_workspace_bytes(self.limits), model.layer_workspace_bytes(self.limits), self.device)
         meta_len = self._meta_len(T, self.max_requests, T)
         # pinned staging buffers in a ring: a buffer is rewritten only after its copy has run
@@ -428,7 +430,7 @@ class Engine:
         splits = 1
         while splits * DECODE_CHUNK < max_ctx:
             splits *= 2
-        limit = (self.max_context + DECODE_CHUNK - 1) // DECODE_CHUNK
+        limit = (self.table_context + DECODE_CHUNK - 1) // DECODE_CHUNK
         return max(1, min(splits, limit)) * DECODE_CHUNK
 
     def _pad_meta(self, m, off, T: int, Tp: int) -> None:
