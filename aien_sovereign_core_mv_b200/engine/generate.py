@@ -82,6 +82,7 @@ class Generator:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.steps = 0
+        self.last_plan = (0, 0, 0)   # (prompt tokens, all tokens, requests) of the step launched last
 
     # ------------------------------------------------------------------ requests
     def submit(self, request_id: int, prompt: Sequence[int], params: Optional[SamplingParams] = None, priority: int = 0) -> None:
@@ -169,6 +170,7 @@ class Generator:
         logits = eng.run_reserved(ids, counts, flat, want_rows, feed=feed)
         self.h2d_bytes += 4 * eng._layout(t0, len(ids), len(want_rows))[1]
         self.steps += 1
+        self.last_plan = (int(plan.prefill_tokens), int(plan.num_tokens), len(entries))
         ids_dev = self._sample(logits, rows) if rows else self._ids_dev2[self._turn & 1][:0]
         eng.collect_waits(self._ids_dev2[self._turn & 1][len(rows):len(rows) + 4])
         return rows, ids_dev

@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Headline measurement: decode tokens per second of the Qwen3-8B-shaped model on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers N]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch B] [--layers N] [--workload decode|llama3_8b|serving]
 
 A step is one decode step of a batch of requests that each hold a 1,024-token prompt (context
 limit 4,096, pages of 16 tokens), random bfloat16 weights, synthetic uniform token ids.  One JSON
@@ -20,6 +20,11 @@ line is printed:
 Peaks come from ``MEASURED_PEAKS.json`` beside this file when present, else from the fallback
 measured earlier on the same pool (6.65 TB/s, 1.59 PFLOP/s).  The weights of one step (15 GB) are
 far larger than the 126 MB L2, so consecutive steps cannot be served from cache.
+``--workload llama3_8b`` prints the same line for the Llama-3-8B shape with 16 requests decoding at
+contexts that end at 8,192 tokens (the cache, 17 GB a step, outweighs the weights) and a 2,048-token
+prefill; ``--workload serving`` runs continuous batching of 32 requests on the Qwen3-4B shape and adds
+the distribution of step times.  Every line carries ``wait_errors``: how many of the kernels' bounded
+waits ran out during the timed regions (0, or the number is void).
 ``--impl reference`` reports that the reference (a Rust workspace) cannot be installed here.
 """
 from __future__ import annotations
@@ -41,7 +46,18 @@ QWEN3_8B = dict(
     rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=40960,
     hidden_act="silu", attention_bias=False, eos_token_id=151645,
 )
-PROMPT_LEN, CONTEXT, PAGE, PREFILL_TOKENS, SEED = 1024, 4096, 16, 2048, 2
+LLAMA3_8B = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=32, hidden_size=4096,
+    num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=128256,
+    rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=8192,
+    hidden_act="silu", attention_bias=False, eos_token_id=128001,
+)
+PAGE, PREFILL_TOKENS = 16, 2048
+# prompt_len None: as long as lets the timed steps end exactly at `context` tokens
+WORKLOADS = {
+    "decode": dict(cfg=QWEN3_8B, label="Qwen3-8B shape, random weights", prompt_len=1024, context=4096, batch=8, seed=2, points=(1, 64)),
+    "llama3_8b": dict(cfg=LLAMA3_8B, label="Llama-3-8B shape, random weights", prompt_len=None, context=8192, batch=16, seed=4, points=()),
+}
 
 
 def peaks():
@@ -122,29 +138,65 @@ QWEN3_4B = dict(
 )
 
 
+def _dist(ms):
+    """p50 / p90 / max of a list of step times in ms."""
+    if not ms:
+        return None
+    v = sorted(ms)
+    pick = lambda q: v[min(len(v) - 1, int(q * len(v)))]
+    return {"n": len(v), "p50_ms": round(pick(0.5), 3), "p90_ms": round(pick(0.9), 3), "max_ms": round(v[-1], 3),
+            "mean_ms": round(sum(v) / len(v), 3)}
+
+
 def serving_workload() -> int:
     """Continuous batching through the public entry point: 32 requests with uniform-random prompt
     lengths in [64, 4096], prompts cut into portions under a 512-token budget, 256 greedy tokens
-    each (Qwen3-4B shape, random bfloat16 weights, seed 3).  Wall-clock time of the whole job."""
+    each (Qwen3-4B shape, random bfloat16 weights, seed 3).  Wall-clock time of the whole job, and
+    the distribution of step times: the time from one turn of the generation loop to the next,
+    which with overlapping steps is what a step adds to the job; steps that carry a portion of a
+    prompt apart from steps that only decode."""
     import numpy as np
     import torch
     from aien_sovereign_core_mv_b200 import Engine, EngineConfig
+    from aien_sovereign_core_mv_b200 import kernels as K
     from aien_sovereign_core_mv_b200.engine.generate import Generator
     from aien_sovereign_core_mv_b200.sampling import SamplingParams
     ec = EngineConfig(dtype="bfloat16", page_size=16, max_cache_tokens=32 * 4400, max_requests=32, max_batch_tokens=1024,
                       max_context=8192, max_batch_size=32, max_prefill_tokens=512, prefill_chunk_size=512)
     engine = Engine.from_config(QWEN3_4B, seed=3, engine_config=ec, init_std=0.02, device_init=True)
     rng = np.random.default_rng(3)
-    gen = Generator(engine)
     lens = rng.integers(64, 4097, 32)
+    prompts = [rng.integers(0, QWEN3_4B["vocab_size"], int(n)).tolist() for n in lens]
     sp = SamplingParams(temperature=0.0, max_tokens=256, stop_token_ids=[])
-    for i, n in enumerate(lens):
-        gen.submit(100 + i, rng.integers(0, QWEN3_4B["vocab_size"], int(n)).tolist(), sp)
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    done = gen.run()
-    torch.cuda.synchronize()
-    dt = time.perf_counter() - t0
+
+    def job(first_id, timed):
+        gen = Generator(engine)
+        for i, p in enumerate(prompts):
+            gen.submit(first_id + i, p, sp)
+        torch.cuda.synchronize()
+        done, kinds, stamps = {}, [], [time.perf_counter()]
+        while gen.scheduler.has_work() or gen._inflight is not None:
+            before = gen.steps
+            for r in gen.advance():
+                done[r.request_id] = r
+            if gen.steps > before:
+                kinds.append(gen.last_plan)
+                stamps.append(time.perf_counter())
+        torch.cuda.synchronize()
+        stamps[-1] = time.perf_counter()
+        return gen, done, kinds, stamps
+
+    job(10000, False)                     # untimed: every step shape is met once (recorded launches, captured graphs)
+    K.read_wait_errors()
+    sampler = ClockSampler()
+    sampler.start()
+    gen, done, kinds, stamps = job(100, True)
+    clocks = sampler.stop()
+    wait_errors = sum(1 for w in K.read_wait_errors() if w != 0)
+    dt = stamps[-1] - stamps[0]
+    step_ms = [(b - a) * 1e3 for a, b in zip(stamps, stamps[1:])]
+    with_prompt = [t for t, k in zip(step_ms, kinds) if k[0] > 0]
+    decode_only = [t for t, k in zip(step_ms, kinds) if k[0] == 0]
     m = gen.scheduler.metrics()
     new = sum(len(r.tokens) for r in done.values())
     print(json.dumps({
@@ -152,8 +204,12 @@ def serving_workload() -> int:
         "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "impl": "ours",
         "total_tokens_per_s": round((int(lens.sum()) + new) / dt, 1), "seconds": round(dt, 3), "steps": int(m["steps"]),
         "preemptions": int(m["preemptions"]), "requests": len(done), "prompt_tokens": int(lens.sum()), "generated_tokens": new,
-        "config": {"model": "Qwen3-4B shape, random weights", "requests": 32, "prompt_len": "uniform 64..4096",
-                   "prefill_budget": 512, "new_tokens": 256, "context": 8192, "page_size": 16, "seed": 3},
+        "step_ms": {"all": _dist(step_ms), "with_prompt_portion": _dist(with_prompt), "decode_only": _dist(decode_only)},
+        "clocks": clocks, "wait_errors": int(wait_errors),
+        "config": {"model": "Qwen3-4B shape, random weights", "layers": 36, "hidden": 2560, "heads": 32, "kv_heads": 8, "head_dim": 128,
+                   "intermediate": 9728, "vocab": 151936, "requests": 32, "prompt_len": "uniform 64..4096",
+                   "prefill_budget": 512, "new_tokens": 256, "context": 8192, "page_size": 16, "seed": 3,
+                   "timing": "second run of the job; the first, untimed, meets every step shape once"},
     }))
     return 0
 
@@ -164,14 +220,15 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=0, help="requests decoding together (0: the workload's own: 8, or 16 for llama3_8b)")
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (0 = all)")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
-                    help="decode: the headline decode-step measurement; serving: continuous batching of 32 requests "
-                         "on the Qwen3-4B shape (prompts of 64..4096 tokens, portions of 512, 256 new tokens each)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "llama3_8b", "serving"],
+                    help="decode: the headline decode-step measurement (Qwen3-8B shape, 1,024-token prompts); llama3_8b: the same "
+                         "line for the Llama-3-8B shape, 16 requests at contexts ending at 8,192 tokens; serving: continuous batching "
+                         "of 32 requests on the Qwen3-4B shape (prompts of 64..4096 tokens, portions of 512, 256 new tokens each)")
     ap.add_argument("--fill", default="prefill", choices=["prefill", "cache"],
                     help="how requests get their prompt: real prefill, or (development only) cache pages "
                          "filled with random keys/values without running the model")
@@ -195,16 +252,21 @@ def main() -> int:
     from aien_sovereign_core_mv_b200.engine.generate import Generator
     from aien_sovereign_core_mv_b200.sampling import SamplingParams
 
-    cfg = dict(QWEN3_8B)
+    wl = WORKLOADS[args.workload]
+    batch_main = args.batch or wl["batch"]
+    cfg = dict(wl["cfg"])
     layers_cfg = cfg["num_hidden_layers"]
     layers_run = args.layers or layers_cfg
     cfg["num_hidden_layers"] = layers_run
     nums = model_numbers(cfg, layers_run)
     hbm_gbs, bf16_tflops, peak_src = peaks()
-    max_batch = max(64, args.batch)
+    CONTEXT, SEED = wl["context"], wl["seed"]
+    # the timed steps end at `context` tokens when the workload gives no prompt length
+    PROMPT_LEN = wl["prompt_len"] or CONTEXT - (warmup + steps)
+    max_batch = max([batch_main, *wl["points"]])
     pool_tokens = max_batch * (PROMPT_LEN + warmup + steps + 64)
     ec = EngineConfig(dtype="bfloat16", page_size=PAGE, max_cache_tokens=pool_tokens, max_requests=max_batch,
-                      max_batch_tokens=PREFILL_TOKENS, max_context=CONTEXT, max_batch_size=max_batch,
+                      max_batch_tokens=PREFILL_TOKENS, max_context=CONTEXT + (0 if wl["prompt_len"] else 64), max_batch_size=max_batch,
                       max_prefill_tokens=PREFILL_TOKENS, prefill_chunk_size=PREFILL_TOKENS)
     t_load = time.time()
     engine = Engine.from_config(cfg, seed=SEED, engine_config=ec, init_std=0.02, device_init=True)
@@ -215,18 +277,34 @@ def main() -> int:
     if args.fill == "cache":
         for st in engine.storage:
             st.normal_(0.0, 0.5)
+    wait_errors = 0
+
+    def count_wait_errors():
+        """After a timed region (the device is idle): how many kernels left an error word."""
+        nonlocal wait_errors
+        wait_errors += sum(1 for w in K.read_wait_errors() if w != 0)
 
     def fill_requests(batch, first_id):
-        """Each request holds a PROMPT_LEN-token prompt: real prefill, 2,048 tokens per step."""
+        """Each request gets a PROMPT_LEN-token prompt by real prefill: portions of at most 2,048
+        tokens, several requests in a step where they fit."""
         ids = list(range(first_id, first_id + batch))
         if args.fill == "cache":
             for rid in ids:
                 engine.cache.add_request(rid)
             engine.cache.append([(rid, PROMPT_LEN) for rid in ids])
             return ids
-        per_step = max(1, PREFILL_TOKENS // PROMPT_LEN)
-        for i in range(0, batch, per_step):
-            ents = [(rid, rng.integers(0, V, PROMPT_LEN), []) for rid in ids[i:i + per_step]]
+        ents, used = [], 0
+        for rid in ids:
+            left = PROMPT_LEN
+            while left > 0:
+                n = min(left, PREFILL_TOKENS - used)
+                ents.append((rid, rng.integers(0, V, n), []))
+                used += n
+                left -= n
+                if used == PREFILL_TOKENS:
+                    engine.step(ents)
+                    ents, used = [], 0
+        if ents:
             engine.step(ents)
         return ids
 
@@ -250,6 +328,8 @@ def main() -> int:
         ms = e0.elapsed_time(e1)
         clocks = sampler.stop() if sample_clocks else None
         launches = K.launch_count() - launches0
+        engine.check_waits()
+        count_wait_errors()
         ctx_mid = PROMPT_LEN + n_warm + n_steps // 2
         for rid in ids:
             engine.end_request(rid)
@@ -273,6 +353,8 @@ def main() -> int:
             torch.cuda.synchronize()
             times.append(e0.elapsed_time(e1))
             engine.end_request(9000 + rep)
+        engine.check_waits()
+        count_wait_errors()
         pms = float(np.median(times[3:]))
         T = PREFILL_TOKENS
         flops = 2.0 * (nums["linear_params"] - V * cfg["hidden_size"]) * T + 2.0 * V * cfg["hidden_size"] \
@@ -283,31 +365,31 @@ def main() -> int:
     # the prefill is timed before the decode runs, as a burst, like the peak it is set against
     prefill = None if args.skip_prefill else prefill_run()
 
-    # ---- headline: decode at the default batch
-    ms, clocks, launches, ctx_mid = decode_run(args.batch, 1000, warmup, steps, sample_clocks=True)
+    # ---- headline: decode at the workload's batch
+    ms, clocks, launches, ctx_mid = decode_run(batch_main, 1000, warmup, steps, sample_clocks=True)
     ms_per_step = ms / steps
-    value = args.batch * steps / (ms / 1e3)
-    step_bytes = nums["weight_bytes"] + args.batch * ctx_mid * nums["kv_bytes_per_token"]
+    value = batch_main * steps / (ms / 1e3)
+    step_bytes = nums["weight_bytes"] + batch_main * ctx_mid * nums["kv_bytes_per_token"]
     achieved = step_bytes / (ms_per_step / 1e3) / 1e9
 
     points = {}
     if not args.skip_points:
-        for b in (1, 64):
-            pms, _, _, _ = decode_run(b, 2000 + 100 * b, max(3, warmup // 2), max(8, steps // 2))
-            points[f"decode_b{b}"] = round(b * max(8, steps // 2) / (pms / 1e3), 1)
+        for b in wl["points"]:                     # the same number of timed steps as the headline
+            pms, _, _, _ = decode_run(b, 2000 + 100 * b, warmup, steps)
+            points[f"decode_b{b}"] = round(b * steps / (pms / 1e3), 1)
 
     e2e = None
     if not args.skip_e2e:
         # The same K decode steps through the public entry point: every step the scheduler plans,
         # token ids and block tables go host->device from pinned memory, the chosen ids come back.
         gen = Generator(engine)
-        prompts = [rng.integers(0, V, PROMPT_LEN).tolist() for _ in range(args.batch)]
+        prompts = [rng.integers(0, V, PROMPT_LEN).tolist() for _ in range(batch_main)]
         sp = SamplingParams(temperature=0.0, max_tokens=4 * warmup + steps + 64, stop_token_ids=[])
         for i, p in enumerate(prompts):
             gen.submit(5000 + i, p, sp)
         def all_decoding():
             m = gen.scheduler.metrics()
-            return m["prefill_tokens"] >= args.batch * PROMPT_LEN and gen.scheduler.num_running == args.batch
+            return m["prefill_tokens"] >= batch_main * PROMPT_LEN and gen.scheduler.num_running == batch_main
         while not all_decoding():
             gen.advance()
         for _ in range(warmup):
@@ -322,9 +404,10 @@ def main() -> int:
         gen.flush()
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
+        count_wait_errors()
         n_steps = max(1, gen.steps - s0)
         new_tokens = gen.scheduler.metrics()["decode_tokens"] - dec0
-        for i in range(args.batch):
+        for i in range(batch_main):
             gen.scheduler.cancel(5000 + i)
         e2e = {"value": round(new_tokens / dt, 1), "unit": "tokens/s", "steps": n_steps,
                "h2d_bytes_per_step": int((gen.h2d_bytes - h0) / n_steps), "d2h_bytes_per_step": int((gen.d2h_bytes - d0) / n_steps)}
@@ -334,20 +417,21 @@ def main() -> int:
         "warmup": warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
         "config": {
-            "model": "Qwen3-8B shape, random weights", "layers": layers_cfg, "layers_run": layers_run,
+            "model": wl["label"], "layers": layers_cfg, "layers_run": layers_run,
             "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
             "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": V,
-            "global_batch": args.batch, "seq_len": PROMPT_LEN, "context": CONTEXT, "page_size": PAGE,
+            "global_batch": batch_main, "seq_len": PROMPT_LEN, "context": CONTEXT, "page_size": PAGE,
             "parallelism": "single GPU", "prefill_tokens": PREFILL_TOKENS, "seed": SEED,
             "l2": "inputs larger than L2: 15 GB of weights per step", "fill": args.fill,
         },
-        "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
+        "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "wait_errors": int(wait_errors),
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s",
                      "frac": round(achieved / hbm_gbs, 4), "of": peak_src, "bytes_per_step": int(step_bytes)},
         "points": points, "load_s": round(load_s, 1),
-        "reference_gb10": {"tokens_per_s": 7.0, "source": "docs/campaigns/open-model-qwen3/RESULT-v7.md:67-68 (Qwen3-8B, GB10, one request)"},
     }
+    if args.workload == "decode":
+        out["reference_gb10"] = {"tokens_per_s": 7.0, "source": "docs/campaigns/open-model-qwen3/RESULT-v7.md:67-68 (Qwen3-8B, GB10, one request)"}
     print(json.dumps(out))
     return 0
 
