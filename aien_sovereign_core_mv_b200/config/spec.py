@@ -5,8 +5,9 @@ generic decoder builds itself from it; nothing in the parts or in the decoder kn
 architecture produced the spec.
 
 * ``PartSpec(kind, params)`` names a registered part and gives its sizes and constants.
-* ``LayerSpec`` lists the parts of one layer (block arrangement, mixer, feed-forward, norm,
-  position encoding) and the prefix under which its tensors are stored.
+* ``LayerSpec`` lists the parts of one layer (block arrangement, mixer, feed-forward, the norms
+  by the slot names the block declares, position encoding) and the prefix under which its
+  tensors are stored.  ``ModelSpec.embedding`` and ``ModelSpec.head`` name registered parts too.
 * ``RunEntry`` is one execution of a layer.  The run list may name a layer twice (shared
   weights) and a run may read the cache another run wrote (``cache`` equal to an earlier
   entry's and ``writes_cache=False``).
@@ -30,12 +31,22 @@ class PartSpec:
 class LayerSpec:
     block: str                      # arrangement of the parts, e.g. "prenorm"
     mixer: PartSpec
-    feed_forward: PartSpec
-    norm: PartSpec                  # used for both norms of the block
+    feed_forward: Optional[PartSpec]  # None: the block has no feed-forward
+    norm: Optional[PartSpec]        # the norm of every slot of the block that `norms` does not name
     position: PartSpec              # handed to the mixer
     prefix: str                     # tensor-name prefix, e.g. "model.layers.3."
     # local tensor name of a part -> name below `prefix` in the checkpoint
     names: Mapping[str, str] = field(default_factory=dict)
+    # norm slot name (as the block kind declares them: Block.norm_slots) -> its norm
+    norms: Mapping[str, PartSpec] = field(default_factory=dict)
+    # further constructor arguments of the block
+    block_params: Mapping[str, Any] = field(default_factory=dict)
+
+    def norm_for(self, slot: str) -> PartSpec:
+        ps = self.norms.get(slot, self.norm)
+        if ps is None:
+            raise ValueError(f"layer {self.prefix!r}: block {self.block!r} wants a norm in slot {slot!r} and the spec names none")
+        return ps
 
 
 @dataclass(frozen=True)
@@ -52,9 +63,11 @@ class ModelSpec:
     vocab_size: int
     layers: Tuple[LayerSpec, ...]
     run_list: Tuple[RunEntry, ...]
-    embedding: PartSpec             # params: name
-    final_norm: PartSpec            # params: eps, name
-    head: PartSpec                  # params: name or tied=True
+    # Each of the three is a registered part; ``name`` in its params is the checkpoint name of its
+    # tensor "weight" (``names`` maps further local names); the rest are constructor arguments.
+    embedding: PartSpec             # family "embedding", e.g. kind "table"
+    final_norm: PartSpec            # family "norm"
+    head: PartSpec                  # family "head", e.g. kind "linear" with tied=True/False
     max_position: int
     stop_token_ids: Tuple[int, ...] = ()
 

@@ -166,6 +166,16 @@ __global__ void gather_add_rows_kernel(const float* __restrict__ x, const TD* __
     }
 }
 
+// x[t] += sum_p delta[p][t]   (the residual sum alone, for arrangements that do not norm right after it)
+template <typename TD>
+__global__ void add_residual_kernel(float* __restrict__ x, const TD* __restrict__ delta, int nparts, size_t part_stride, size_t total) {
+    griddep_launch();
+    griddep_wait();
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; idx < total; idx += stride) x[idx] = ld_act(x + idx) + delta_sum(delta, nparts, part_stride, idx);
+}
+
 // ---------------------------------------------------------------- SwiGLU
 // a = silu(g) * u, silu(g) = g / (1 + exp(-g))     (backend.rs:572-579).  gu = [T, 2I]:
 // group == 0: gate columns [0, I), up columns [I, 2I);  group > 0: columns interleaved in runs of
@@ -675,6 +685,16 @@ AIEN_API int aien_gather_add_rows(const float* x, const void* delta, int delta_d
     if (R <= 0) return 0;
     AIEN_DISPATCH_DTYPE(delta_dt, TD, (launch_chain(gather_add_rows_kernel<TD>, dim3(R), dim3(row_threads(H)), 0, stream,
         x, (const TD*)delta, nparts, part_stride, rows, out, H)));
+    return launch_status();
+}
+
+AIEN_API int aien_add_residual(float* x, const void* delta, int delta_dt, int nparts, size_t part_stride, int T, int H,
+                               cudaStream_t stream) {
+    if (T <= 0 || H <= 0 || delta == nullptr) return 0;
+    const size_t total = (size_t)T * H;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    AIEN_DISPATCH_DTYPE(delta_dt, TD, (launch_chain(add_residual_kernel<TD>, dim3(blocks), dim3(256), 0, stream,
+        x, (const TD*)delta, nparts, part_stride, total)));
     return launch_status();
 }
 

@@ -45,11 +45,7 @@ def _own_parts_only(model) -> bool:
     """Whether every part of the model is one of this package's (whose forward passes only launch
     kernels of this library)."""
     root = __name__.split(".")[0] + "."
-    seen = [model.final_norm] + list(getattr(model, "_positions", {}).values())
-    for block in model.blocks:
-        seen.append(block)
-        seen.extend(v for v in vars(block).values() if isinstance(v, (Norm, Mixer, FeedForward, Position)))
-    return all(type(o).__module__.startswith(root) for o in seen)
+    return all(type(o).__module__.startswith(root) for o in model.parts())
 
 
 class Engine:
@@ -84,17 +80,24 @@ class Engine:
         self.table_context = self.max_context
         if any(need.kind == "full" for need in model.group_needs):
             self.table_context = min(self.max_context, pages * self.page_size)
+        # Device storage per group, from what the mixers declare (CacheNeed): for every plane of a
+        # paged group [runs, tokens of the pool, *per-token shape]; for a state group one plane
+        # "state" [runs, slots + 1, *shape], the extra slot being nobody's (padding rows use it).
+        # Zero-filled: kernels that load whole pages need finite values everywhere.
         gspecs, self.storage = [], []
         kinds = {"full": self.host.GroupKind.Full, "window": self.host.GroupKind.Window, "state": self.host.GroupKind.State}
         for need, slots in zip(model.group_needs, model.group_slots):
             if need.kind == "state":
                 gspecs.append(self.host.GroupSpec(kinds["state"], 0, self.max_requests))
                 sdt = getattr(torch, need.state_dtype)
-                self.storage.append(torch.zeros((slots, self.max_requests) + tuple(need.state_shape), dtype=sdt, device=self.device))
+                self.storage.append({"state": torch.zeros((slots, self.max_requests + 1) + tuple(need.state_shape), dtype=sdt, device=self.device)})
             else:
+                if not need.planes:
+                    raise ValueError(f"a mixer asks for a {need.kind!r} cache and names no planes to keep in it")
                 gspecs.append(self.host.GroupSpec(kinds[need.kind], need.window, pages))
-                self.storage.append(torch.zeros((slots, 2, pages * self.page_size, need.num_kv_heads, need.head_dim),
-                                                dtype=self.dtype, device=self.device))
+                pdt = getattr(torch, need.dtype) if need.dtype else self.dtype
+                self.storage.append({name: torch.zeros((slots, pages * self.page_size) + tuple(int(d) for d in shape), dtype=pdt, device=self.device)
+                                     for name, shape in need.planes})
         self.cache = self.host.CacheManager(self.page_size, gspecs, self.max_requests)
         self.max_blocks = (self.table_context + self.page_size - 1) // self.page_size
 
@@ -113,8 +116,8 @@ class Engine:
         self.meta_dev = torch.empty(meta_len, dtype=torch.int32, device=self.device)
         self.steps_run = 0
         self._graphs = {}
-        # parts that keep fixed-size state run host logic per request: their steps are not captured
-        self._graphable = all(n.kind != "state" for n in model.group_needs)
+        # a part that reads device data on the host cannot be captured
+        self._graphable = not any(getattr(p, "host_reads", False) for p in model.parts())
         # A step that is not captured still repeats: the launches of a forward pass are fixed by a
         # few host numbers (tokens, requests, wanted rows, attention tiles, key chunks) because every
         # buffer comes from the step workspace or the metadata block at addresses that follow from
@@ -196,11 +199,12 @@ class Engine:
     def _do_copies(self, copies) -> None:
         ps = self.page_size
         for g, src, dst in copies:
-            st = self.storage[g]
-            if self.model.group_needs[g].kind == "state":
-                st[:, dst].copy_(st[:, src])
-            else:
-                st[:, :, dst * ps:(dst + 1) * ps].copy_(st[:, :, src * ps:(src + 1) * ps])
+            state = self.model.group_needs[g].kind == "state"
+            for st in self.storage[g].values():
+                if state:
+                    st[:, dst].copy_(st[:, src])
+                else:
+                    st[:, dst * ps:(dst + 1) * ps].copy_(st[:, src * ps:(src + 1) * ps])
 
     # ------------------------------------------------------------------ the step
     def step(self, entries: Sequence, logits_out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -368,6 +372,8 @@ class Engine:
                 n_tiles += k
         if Tp > T:
             self._pad_meta(m, off, T, Tp)
+        if graph_step:
+            self._warm_decode(off, Tp, max_ctx, total)
         self.meta_dev[:total].copy_(meta_host[:total], non_blocking=True)
         if slot[2] is None:
             slot[2] = torch.cuda.Event()
@@ -444,10 +450,32 @@ class Engine:
         m[off["want_rows"]:off["want_rows"] + Tp] = np.arange(Tp, dtype=np.int32)
         for (bt, sm, mb), need in zip(off["groups"], self.model.group_needs):
             if need.kind == "state":
-                m[sm + T:sm + Tp] = 0
+                m[sm + T:sm + Tp] = self.max_requests      # the slot that belongs to nobody
             else:
                 m[bt + T * mb:bt + Tp * mb] = -1
                 m[sm + T:sm + Tp] = -1
+
+    def _decode_forward(self, off, T: int, splits: int, logits: torch.Tensor) -> None:
+        from ..kernels import DECODE_CHUNK
+        d = self.meta_dev
+        ctx = self._context(off, T, T, 1, splits * DECODE_CHUNK, True)
+        with K.stream_scope():
+            self.model.forward(ctx, d[off["want_rows"]:off["want_rows"] + T], T, logits)
+
+    def _warm_decode(self, off, T: int, max_ctx: int, total: int) -> None:
+        """Before a decode step of a new shape is captured, the same launches run once outside the
+        capture (tables and buffers that parts make at first use).  That run sees padding rows
+        only: it writes no cache slot and no request's state, so the step itself runs exactly
+        once, whatever its mixers keep between steps."""
+        from ..kernels import DECODE_CHUNK
+        splits = self._ctx_bucket(max_ctx) // DECODE_CHUNK
+        if (T, splits) in self._graphs:
+            return
+        pad = torch.zeros(total, dtype=torch.int32)
+        self._pad_meta(pad.numpy(), off, 0, T)
+        self.meta_dev[:total].copy_(pad)
+        self._decode_forward(off, T, splits, torch.empty((T, self.vocab_size), dtype=torch.float32, device=self.device))
+        torch.cuda.synchronize()
 
     def _replay_decode(self, off, T: int, max_ctx: int, logits_out: Optional[torch.Tensor], real: Optional[int] = None) -> torch.Tensor:
         """Decode steps are short chains of small kernels; launching them one by one costs more
@@ -460,19 +488,11 @@ class Engine:
         entry = self._graphs.get(key)
         if entry is None:
             logits = torch.empty((T, self.vocab_size), dtype=torch.float32, device=self.device)
-            d = self.meta_dev
-
-            def run():
-                ctx = self._context(off, T, T, 1, splits * DECODE_CHUNK, True)
-                with K.stream_scope():
-                    self.model.forward(ctx, d[off["want_rows"]:off["want_rows"] + T], T, logits)
-
-            run()                                         # warm-up outside capture (lazy tables, attributes)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             before = K.launch_count()
             with torch.cuda.graph(graph):
-                run()
+                self._decode_forward(off, T, splits, logits)
             entry = (graph, logits, K.launch_count() - before)
             if len(self._graphs) >= 48:
                 self._graphs.pop(next(iter(self._graphs)))

@@ -112,6 +112,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_add_rmsnorm": [P, P, I, I, c_size_t, P, I, F, P, I, I, I, P],
         "aien_gather_add_rows": [P, P, I, I, c_size_t, P, P, I, I, P],
         "aien_swiglu": [P, P, I, I, I, I, P],
+        "aien_add_residual": [P, P, I, I, c_size_t, I, I, P],
         "aien_rope_table": [P, P, P, P, I, I, P],
         "aien_qk_norm_rope_kv_write": [P, L, I, P, L, P, L, I, I, I, c_size_t, P, L, I, P, P, I, F, P, P, I, P, P, P, I, I, I, P],
         "aien_convert": [P, I, P, I, c_size_t, P],
@@ -265,6 +266,15 @@ def gather_add_rows(x: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.
     nparts, stride = _parts_of(delta, x.shape)
     _check(lib().aien_gather_add_rows(_p(x), _p(delta), dt(delta) if delta is not None else F32, nparts, stride,
                                       _p(rows), _p(out), R, H, _stream()), "gather_add_rows")
+
+
+def add_residual(x: torch.Tensor, delta: torch.Tensor) -> None:
+    """x += delta in float32; delta [T,H] in any kernel dtype, or float32 partial products [P,T,H]."""
+    _dev(x, delta)
+    T, H = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    nparts, stride = _parts_of(delta, x.shape)
+    _check(lib().aien_add_residual(_p(x), _p(delta), dt(delta), nparts, stride, T, H, _stream()), "add_residual")
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, group: int = 0) -> None:
@@ -478,6 +488,13 @@ def gemm_tc_splits(M: int, N: int, K_: int) -> int:
     if tiles >= 148:
         return 1
     return gemm_tc_ranges(K_, max(1, min(8, 296 // tiles, K_ // 512)))
+
+
+def small_step_products_fuse(dtype: torch.dtype, num_tokens: int) -> bool:
+    """Whether the products of this step are the streamed decode kernel, whose epilogues can do a
+    norm's work (residual add and preparation before it, the row factor after it).  The one place
+    that knows the routing; norms of any kind ask here."""
+    return dtype == torch.bfloat16 and num_tokens <= GEMV_ROUTE_ROWS and GEMV_IMPL == "stream"
 
 
 def FUSED_NORM_SCRATCH_BYTES(hidden: int) -> int:

@@ -13,8 +13,7 @@ import torch
 from .. import kernels as K
 from ..config.spec import LayerSpec, ModelSpec, PartSpec
 from ..parts.base import Prenormed, Block, CacheNeed, Mixer, RunBinding, StepContext
-from ..parts.linear import linear
-from ..registry import make_part
+from ..registry import make_part, part_factory
 
 
 def _freeze(v):
@@ -34,11 +33,15 @@ class Decoder:
         self.blocks: List[Block] = []
         for layer in spec.layers:
             self.blocks.append(self._build_block(layer))
-        self.final_norm = make_part("norm", spec.final_norm.kind, size=spec.hidden_size,
-                                    **{k: v for k, v in spec.final_norm.params.items() if k != "name"})
-        self.embed_table: Optional[torch.Tensor] = None
-        self.head_weight: Optional[torch.Tensor] = None
-        self.tied = bool(spec.head.get("tied", False))
+        own = lambda ps: {k: v for k, v in ps.params.items() if k not in ("name", "names")}
+        self.final_norm = make_part("norm", spec.final_norm.kind, size=spec.hidden_size, **own(spec.final_norm))
+        self.embedding = make_part("embedding", spec.embedding.kind, vocab_size=spec.vocab_size, hidden_size=spec.hidden_size,
+                                   **own(spec.embedding))
+        self.head = make_part("head", spec.head.kind, vocab_size=spec.vocab_size, hidden_size=spec.hidden_size, **own(spec.head))
+        self.tied = bool(getattr(self.head, "tied", False))
+        # the parts outside the layers, with the spec entry that names their tensors
+        self._ends = {"embedding": (self.embedding, spec.embedding), "final_norm": (self.final_norm, spec.final_norm),
+                      "head": (self.head, spec.head)}
         # ---- cache groups: runs with equal needs share pools and block tables
         self.group_needs: List[CacheNeed] = []
         self.group_slots: List[int] = []          # planes (cache slots) per group
@@ -75,12 +78,34 @@ class Decoder:
         return self._positions[key]
 
     def _build_block(self, layer: LayerSpec) -> Block:
+        """The block kind says which norms it wants (``norm_slots``); the layer spec says what each
+        is.  Nothing here knows an arrangement."""
         position = self._position(layer.position)
         mixer = make_part("mixer", layer.mixer.kind, position=position, **dict(layer.mixer.params))
-        ff = make_part("feed_forward", layer.feed_forward.kind, **dict(layer.feed_forward.params))
-        n1 = make_part("norm", layer.norm.kind, size=self.spec.hidden_size, **dict(layer.norm.params))
-        n2 = make_part("norm", layer.norm.kind, size=self.spec.hidden_size, **dict(layer.norm.params))
-        return make_part("block", layer.block, mixer=mixer, feed_forward=ff, norm_in=n1, norm_post=n2)
+        ff = None if layer.feed_forward is None else make_part("feed_forward", layer.feed_forward.kind, **dict(layer.feed_forward.params))
+        norms = {}
+        for slot in getattr(part_factory("block", layer.block), "norm_slots", ()):
+            ps = layer.norm_for(slot)
+            norms[slot] = make_part("norm", ps.kind, size=self.spec.hidden_size, **dict(ps.params))
+        return make_part("block", layer.block, mixer=mixer, feed_forward=ff, **norms, **dict(layer.block_params))
+
+    def parts(self):
+        """Every part of the model, for whoever must ask all of them something."""
+        out = [self.embedding, self.final_norm, self.head] + list(self._positions.values())
+        for block in self.blocks:
+            out.append(block)
+            out.extend(block.parts().values())
+        return out
+
+    def _end_names(self):
+        """(which end, local name) -> (checkpoint name, shape, kind)."""
+        out = {}
+        for which, (part, ps) in self._ends.items():
+            names = dict(ps.params.get("names") or {})
+            for local, (shape, kind) in part.param_shapes().items():
+                name = names.get(local) or (ps.params.get("name") if local == "weight" else None) or f"{which}.{local}"
+                out[(which, local)] = (name, tuple(shape), kind)
+        return out
 
     # ------------------------------------------------------------------ tensors
     def _layer_names(self, li: int):
@@ -96,14 +121,16 @@ class Decoder:
     def catalog(self) -> Dict[str, Tuple[Tuple[int, ...], str]]:
         """Every tensor the model wants: checkpoint name -> (shape, kind)."""
         cat: Dict[str, Tuple[Tuple[int, ...], str]] = {}
-        cat[self.spec.embedding.get("name")] = ((self.vocab_size, self.hidden_size), "embedding")
+        ends = self._end_names()
+        for (which, _), (name, shape, kind) in ends.items():
+            if which == "embedding":
+                cat[name] = (shape, kind)
         for li in range(len(self.blocks)):
             for (_, _), (name, shape, kind) in self._layer_names(li).items():
                 cat[name] = (tuple(shape), kind)
-        for local, (shape, kind) in self.final_norm.param_shapes().items():
-            cat[self.spec.final_norm.get("name")] = (tuple(shape), kind)
-        if not self.tied:
-            cat[self.spec.head.get("name")] = ((self.vocab_size, self.hidden_size), "matrix")
+        for (which, _), (name, shape, kind) in ends.items():
+            if which != "embedding":
+                cat[name] = (shape, kind)
         return cat
 
     def bind(self, tensors) -> None:
@@ -114,29 +141,25 @@ class Decoder:
         for li in range(len(self.blocks)):
             for (pname, local), (name, _, _) in self._layer_names(li).items():
                 owner[name] = (li, pname, local)
+        for (which, local), (name, _, _) in self._end_names().items():
+            owner[name] = (-1, which, local)
         pending: Dict[Tuple[int, str], Dict[str, torch.Tensor]] = {}
-        embed_name, norm_name, head_name = self.spec.embedding.get("name"), self.spec.final_norm.get("name"), self.spec.head.get("name")
+        waiting = {(-1, which) for which, (part, _) in self._ends.items() if part.param_shapes()}
         for name, t in tensors:
             t = t.to(device, non_blocking=False)
-            if name == embed_name:
-                self.embed_table = t.contiguous()
-            elif name == norm_name:
-                self.final_norm.bind({"weight": t})
-            elif name == head_name and not self.tied:
-                self.head_weight = t.contiguous()
-            elif name in owner:
-                li, pname, local = owner[name]
-                part = self.blocks[li].parts()[pname]
-                bucket = pending.setdefault((li, pname), {})
-                bucket[local] = t
-                if len(bucket) == len(part.param_shapes()):
-                    part.bind(bucket)
-                    del pending[(li, pname)]
-            else:
+            if name not in owner:
                 raise KeyError(f"tensor {name!r} belongs to no part of the model")
+            li, pname, local = owner[name]
+            part = self._ends[pname][0] if li < 0 else self.blocks[li].parts()[pname]
+            bucket = pending.setdefault((li, pname), {})
+            bucket[local] = t
+            if len(bucket) == len(part.param_shapes()):
+                part.bind(bucket)
+                del pending[(li, pname)]
+                waiting.discard((li, pname))
         if self.tied:
-            self.head_weight = self.embed_table
-        if pending or self.embed_table is None or self.head_weight is None or self.final_norm.weight is None:
+            self.head.tie(self.embedding)
+        if pending or waiting:
             raise RuntimeError("bind: some parts did not receive all their tensors")
 
     # ------------------------------------------------------------------ sizes
@@ -157,7 +180,7 @@ class Decoder:
         rows into ``logits`` [num_rows, vocab]."""
         ws = ctx.workspace
         x = ws.take_step((ctx.num_tokens, self.hidden_size), torch.float32)
-        K.embed_gather(self.embed_table, ctx.token_ids, x)
+        self.embedding.forward(ctx, ctx.token_ids, x)
         delta = None
         runs = self.spec.run_list
         for i, (run, binding) in enumerate(zip(runs, self.bindings)):
@@ -176,5 +199,5 @@ class Decoder:
             rows = ws.take((num_rows, self.hidden_size), torch.float32)
             K.gather_add_rows(x, delta, want_rows, rows)
             hn = self.final_norm.forward(ctx, rows, None)
-            linear(ctx, hn, self.head_weight, out=logits)
+            self.head.forward(ctx, hn, logits)
         return logits

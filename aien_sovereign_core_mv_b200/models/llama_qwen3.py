@@ -42,8 +42,8 @@ def spec_from_config(cfg: DenseDecoderConfig) -> ModelSpec:
     ff = PartSpec("swiglu", {"hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size})
     norm = PartSpec("rmsnorm", {"eps": cfg.rms_norm_eps})
     layers = tuple(
-        LayerSpec(block="prenorm", mixer=mixer, feed_forward=ff, norm=norm, position=position,
-                  prefix=f"model.layers.{i}.", names=_NAMES)
+        LayerSpec(block="prenorm", mixer=mixer, feed_forward=ff, norm=None, norms={"norm_in": norm, "norm_post": norm},
+                  position=position, prefix=f"model.layers.{i}.", names=_NAMES)
         for i in range(cfg.num_hidden_layers)
     )
     return ModelSpec(

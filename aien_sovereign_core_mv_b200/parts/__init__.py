@@ -1,7 +1,7 @@
-from .base import (Block, CacheNeed, FeedForward, GroupView, Mixer, Norm, Part, Position, RunBinding,
-                   StepContext, StepLimits, Workspace)
-from . import norm, rotary, attention, mlp, block  # noqa: F401  (registers the built-in parts)
+from .base import (Block, CacheNeed, Embedding, FeedForward, GroupView, Head, Mixer, Norm, Part, Position, RunBinding,
+                   StepContext, StepLimits, Workspace, add_to_residual)
+from . import norm, rotary, attention, mlp, block, ends  # noqa: F401  (registers the built-in parts)
 from .linear import linear
 
-__all__ = ["Block", "CacheNeed", "FeedForward", "GroupView", "Mixer", "Norm", "Part", "Position",
-           "RunBinding", "StepContext", "StepLimits", "Workspace", "linear"]
+__all__ = ["Block", "CacheNeed", "Embedding", "FeedForward", "GroupView", "Head", "Mixer", "Norm", "Part", "Position",
+           "RunBinding", "StepContext", "StepLimits", "Workspace", "add_to_residual", "linear"]

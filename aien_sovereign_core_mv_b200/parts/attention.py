@@ -62,7 +62,7 @@ class PagedAttention(Mixer):
             self.q_norm_w, self.k_norm_w = qn.contiguous(), kn.contiguous()
 
     def cache_need(self):
-        return CacheNeed("window" if self.window > 0 else "full", self.window, self.num_kv_heads, self.head_dim)
+        return CacheNeed.keys_and_values("window" if self.window > 0 else "full", self.window, self.num_kv_heads, self.head_dim)
 
     def workspace_bytes(self, lim):
         return lim.max_tokens * (2 * self.q_dim + 2 * self.kv_dim + self.q_dim + self.hidden_size) * lim.itemsize + 4096 \
@@ -84,8 +84,7 @@ class PagedAttention(Mixer):
     def forward(self, ctx: StepContext, h, run: RunBinding, sink: Optional[ResidualSink] = None):
         T = ctx.num_tokens
         group = ctx.groups[run.group]
-        planes = group.storage[run.slot]                 # [2, tokens, nkv, hd]
-        k_cache, v_cache = planes[0], planes[1]
+        k_cache, v_cache = group.storage["k"][run.slot], group.storage["v"][run.slot]     # [tokens, nkv, hd] each
         if run.writes:
             qkv = self._project(ctx, h, self.w_qkv)
             q, k, v = qkv[..., :self.q_dim], qkv[..., self.q_dim:self.q_dim + self.kv_dim], qkv[..., self.q_dim + self.kv_dim:]

@@ -1,6 +1,6 @@
 """What a part is, and what it sees of a step.
 
-A model is built from five families of parts, each chosen per layer by the model spec:
+A model is built from seven families of parts.  Five are chosen per layer by the model spec:
 
 * **norm**           ``forward(ctx, x, delta, out_dtype) -> h``; x is the float32 residual stream
   [T, H]; ``delta`` (or None) is added to it in place first.
@@ -14,6 +14,10 @@ A model is built from five families of parts, each chosen per layer by the model
 * **block**          arranges the others: ``forward(ctx, x, delta, run) -> delta``; the returned
   delta is added to the residual stream by whoever norms next (the next block or the final
   norm), which fuses the residual sum into the norm kernel.
+
+Two stand at the ends of the model: the **embedding** (``forward(ctx, token_ids, x)`` fills the
+float32 residual stream) and the **head** (``forward(ctx, rows, logits)`` turns normed rows
+into float32 logits; it may be tied to the embedding).
 
 Every part lists its tensors with ``param_shapes()`` (local name -> (shape, kind)) and receives
 them, already on the device, through ``bind(tensors)``.  A part takes its sizes and constants
@@ -30,30 +34,55 @@ import torch
 # ------------------------------------------------------------------ what a mixer keeps
 @dataclass(frozen=True)
 class CacheNeed:
-    """kind: "full" (all keys), "window" (the last `window` keys), "state" (fixed size)."""
+    """What a mixer keeps between steps.
+
+    kind "full" (every token's entry stays), "window" (only the last ``window`` tokens' entries
+    are needed; pages behind them are given back) or "state" (one tensor of fixed size per
+    request).  A paged kind names its **planes**: what is stored per token, as (name, shape)
+    pairs, e.g. keys and values of grouped-query attention ``(("k", (nkv, hd)), ("v", (nkv,
+    hd)))`` or one latent ``(("latent", (r,)),)``.  The engine allocates, for every plane,
+    ``[runs of the group, tokens of the pool, *shape]`` in the compute dtype (or ``dtype``) and
+    knows nothing else about what they hold.  "state": ``state_shape`` / ``state_dtype``."""
 
     kind: str
     window: int = 0
-    num_kv_heads: int = 0
-    head_dim: int = 0
+    planes: Tuple[Tuple[str, Tuple[int, ...]], ...] = ()
+    dtype: Optional[str] = None           # paged planes: None = the engine's compute dtype
     state_shape: Tuple[int, ...] = ()     # "state": per-request tensor shape
     state_dtype: str = "float32"
 
+    @staticmethod
+    def keys_and_values(kind: str, window: int, num_kv_heads: int, head_dim: int) -> "CacheNeed":
+        shape = (int(num_kv_heads), int(head_dim))
+        return CacheNeed(kind, int(window), (("k", shape), ("v", shape)))
+
     def group_key(self) -> tuple:
-        return (self.kind, self.window, self.num_kv_heads, self.head_dim, self.state_shape, self.state_dtype)
+        return (self.kind, self.window, self.planes, self.dtype, self.state_shape, self.state_dtype)
 
 
 @dataclass
 class GroupView:
-    """One cache group as a step sees it (device tensors)."""
+    """One cache group as a step sees it (device tensors).
+
+    ``storage`` maps a plane's name to ``[runs of the group, tokens, *shape]``; a run's own part
+    is ``storage[name][run.slot]``.  A state group has the one plane "state":
+    ``[runs, capacity + 1, *state_shape]``; the last slot belongs to nobody (padding rows of a
+    captured step are pointed at it).
+
+    The contract of fixed-size state, all of it on the device: the state slot of request ``s`` of
+    the step is ``slot_map[s]``; the request's portion is the tokens ``q_start[s]`` to
+    ``q_start[s + 1]``; a portion whose first token has position 0 (``positions[q_start[s]] ==
+    0``) starts a new request and must not see what the slot held before.  A mixer that follows
+    this without reading anything on the host leaves ``host_reads`` False and its steps can be
+    captured in CUDA graphs like any other."""
 
     kind: str
     page_size: int
     window: int
     max_blocks: int
     block_table: Optional[torch.Tensor]    # int32 [S, max_blocks]; None for state groups
-    slot_map: Optional[torch.Tensor]       # int32 [T] token slots (paged) or [S] state slots
-    storage: torch.Tensor                  # paged: [slots_in_group, 2, tokens, nkv, hd]; state: [slots_in_group, capacity, *shape]
+    slot_map: Optional[torch.Tensor]       # int32 [T] token slots (paged, -1: write nothing) or [S] state slots
+    storage: Dict[str, torch.Tensor]
 
 
 @dataclass
@@ -191,6 +220,10 @@ class ResidualSink:
 
 # ------------------------------------------------------------------ part base classes
 class Part:
+    # True: forward() reads device data on the host (a synchronisation).  Steps of a model with
+    # such a part are never captured in CUDA graphs.  Leave it False and work on the device.
+    host_reads = False
+
     def param_shapes(self) -> Dict[str, Tuple[Tuple[int, ...], str]]:
         """local tensor name -> (shape, kind) with kind in {"matrix", "embedding", "norm"}."""
         return {}
@@ -243,9 +276,56 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Embedding(Part):
+    """Token ids to the float32 residual stream."""
+
+    def forward(self, ctx: StepContext, token_ids: torch.Tensor, x: torch.Tensor) -> None:
+        """x[t] = embedding of token_ids[t]; x is float32 [T, H]."""
+        raise NotImplementedError
+
+    def tied_weight(self) -> Optional[torch.Tensor]:
+        """The [vocab, hidden] matrix a head tied to this embedding multiplies by (None: cannot be tied)."""
+        return None
+
+
+class Head(Part):
+    """Normed rows to float32 logits."""
+
+    tied = False
+
+    def tie(self, embedding: Embedding) -> None:
+        """Called instead of bind() when the head declares itself tied."""
+        raise NotImplementedError
+
+    def forward(self, ctx: StepContext, rows: torch.Tensor, logits: torch.Tensor) -> None:
+        """logits [R, vocab] float32 from rows [R, H] in the compute dtype."""
+        raise NotImplementedError
+
+
+def add_to_residual(ctx: StepContext, x: torch.Tensor, delta) -> None:
+    """x += delta for whatever a block may hand on as pending: None, a [T, H] tensor, float32
+    partial products [P, T, H], or a Prenormed (whose sum is in x already).  For blocks that do
+    not fuse the residual sum into a norm."""
+    from .. import kernels as K
+    if delta is None or isinstance(delta, Prenormed):
+        return
+    K.add_residual(x, delta)
+
+
 class Block(Part):
     mixer: Mixer
+    # the names of the norms the arrangement uses; the decoder builds one norm per name (from
+    # LayerSpec.norms, else LayerSpec.norm) and passes it to the constructor under that name
+    norm_slots: Tuple[str, ...] = ()
     chains_norm = False          # True: forward() accepts next_norm= (the norm that will take its result)
+
+    def parts(self) -> Dict[str, Part]:
+        """The block's parts by the names their tensors are stored under (below the layer's
+        prefix): e.g. {"norm_in": ..., "mixer": ..., "feed_forward": ...}."""
+        raise NotImplementedError
+
+    def workspace_bytes(self, lim: "StepLimits") -> int:
+        return sum(p.workspace_bytes(lim) for p in self.parts().values())
 
     def first_norm(self) -> Optional[Norm]:
         """The norm that takes the previous block's result, if the block starts with one."""

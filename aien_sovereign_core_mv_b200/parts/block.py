@@ -17,6 +17,7 @@ class PreNormBlock(Block):
     around it allow (``Norm.sink``), the product that ends a branch adds it and the product that
     follows finishes the norm, and no norm kernel runs between them."""
 
+    norm_slots = ("norm_in", "norm_post")
     chains_norm = True
 
     def __init__(self, mixer: Mixer, feed_forward: FeedForward, norm_in: Norm, norm_post: Norm):

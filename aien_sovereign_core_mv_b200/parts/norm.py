@@ -34,8 +34,7 @@ class RMSNorm(Norm):
         return lim.max_tokens * self.size * lim.itemsize + 256
 
     def sink(self, ctx: StepContext, x: torch.Tensor) -> Optional[ResidualSink]:
-        # bfloat16 steps of at most 16 tokens, where the products are the streamed decode kernel
-        if not _FUSE or ctx.dtype != torch.bfloat16 or ctx.num_tokens > K.GEMV_ROUTE_ROWS or K.GEMV_IMPL != "stream":
+        if not _FUSE or not K.small_step_products_fuse(ctx.dtype, ctx.num_tokens):
             return None
         return ResidualSink(x, self, self.weight, self.eps)
 

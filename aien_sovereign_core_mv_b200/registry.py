@@ -11,7 +11,7 @@ from typing import Any, Callable, Dict
 
 _ARCHITECTURES: Dict[str, Callable[..., Any]] = {}
 _PARTS: Dict[str, Dict[str, Callable[..., Any]]] = {
-    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {},
+    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}, "embedding": {}, "head": {},
 }
 
 
@@ -67,14 +67,27 @@ def register_block(kind: str):
     return _register("block", kind)
 
 
-def make_part(family: str, kind: str, *args, **kwargs):
+def register_embedding(kind: str):
+    return _register("embedding", kind)
+
+
+def register_head(kind: str):
+    return _register("head", kind)
+
+
+def part_factory(family: str, kind: str):
+    """The registered class (or function) itself: what a block declares about itself, such as
+    the norm slots it wants, is read from it before anything is built."""
     try:
-        factory = _PARTS[family][kind]
+        return _PARTS[family][kind]
     except KeyError:
         raise KeyError(
             f"no {family} part of kind {kind!r}: registered are {sorted(_PARTS[family])}"
         ) from None
-    return factory(*args, **kwargs)
+
+
+def make_part(family: str, kind: str, *args, **kwargs):
+    return part_factory(family, kind)(*args, **kwargs)
 
 
 def part_kinds(family: str):

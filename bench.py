@@ -275,8 +275,9 @@ def main() -> int:
     rng = np.random.default_rng(SEED)
     V = cfg["vocab_size"]
     if args.fill == "cache":
-        for st in engine.storage:
-            st.normal_(0.0, 0.5)
+        for planes in engine.storage:
+            for st in planes.values():
+                st.normal_(0.0, 0.5)
     wait_errors = 0
 
     def count_wait_errors():

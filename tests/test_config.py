@@ -20,7 +20,7 @@ def test_every_size_comes_from_config():
         assert len(spec.layers) == raw["num_hidden_layers"] == len(spec.run_list)
         m = spec.layers[0].mixer.params
         assert (m["num_heads"], m["num_kv_heads"], m["head_dim"]) == (raw["num_attention_heads"], raw["num_key_value_heads"], raw["head_dim"])
-        assert spec.layers[0].norm.params["eps"] == raw["rms_norm_eps"]
+        assert {slot: n.params["eps"] for slot, n in spec.layers[0].norms.items()} == {"norm_in": raw["rms_norm_eps"], "norm_post": raw["rms_norm_eps"]}
         assert spec.layers[0].position.params["theta"] == raw["rope_theta"]
         assert spec.head.params["tied"] == raw["tie_word_embeddings"]
         assert cfg.to_hf_dict()["intermediate_size"] == raw["intermediate_size"]

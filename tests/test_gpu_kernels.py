@@ -909,3 +909,75 @@ def test_philox_known_answers_on_the_device(K):
                           torch.tensor([seed], dtype=torch.int64).cuda(), torch.tensor([rid], dtype=torch.int64).cuda(),
                           torch.tensor([pos], dtype=torch.int32).cuda(), torch.empty(2, device="cuda"), out)
             assert out.item() == want, (seed, rid, pos, p)
+
+
+# ------------------------------------------------------------------ a window's edge in the kernels that serve
+# (context, window): the first visible key of the last token lands on a 128-key chunk boundary (256),
+# on a page boundary only (272), and inside a page (269)
+WINDOW_EDGES = [(400, 144), (400, 128), (400, 131)]
+
+
+def _edge_cache(n, page, hd, spike_at, released_before):
+    """One request of n tokens on shuffled pages: every value 1, but the key at `spike_at` carries a
+    huge score and the value -5.  Pages wholly before `released_before` are given back (-1 in the table),
+    and what they held is overwritten with poison that a kernel must never let through."""
+    pages = (n + page - 1) // page
+    perm = np.random.default_rng(n + spike_at).permutation(pages + 4)
+    bt = np.full((1, pages + 2), -1, dtype=np.int32)
+    bt[0, :pages] = perm[:pages]
+    slots = bt[0, np.arange(n) // page] * page + np.arange(n) % page
+    kc = torch.zeros((pages + 4) * page, 1, hd); vc = torch.zeros((pages + 4) * page, 1, hd)
+    vc[slots, 0, :] = 1.0
+    kc[slots[spike_at], 0, 0] = 50.0
+    vc[slots[spike_at], 0, :] = -5.0
+    for lp in range(released_before // page):
+        if lp * page <= spike_at < (lp + 1) * page:
+            continue                                           # (never: the spike sits at the edge)
+        lo = bt[0, lp] * page
+        kc[lo:lo + page, 0, 0] = 60.0                          # poison: would win every softmax
+        vc[lo:lo + page] = 99.0
+        bt[0, lp] = -1
+    return kc.to(torch.bfloat16).cuda(), vc.to(torch.bfloat16).cuda(), torch.tensor(bt).cuda(), pages + 2
+
+
+@pytest.mark.parametrize("released", [False, True])
+@pytest.mark.parametrize("impl", ["direct", "stream"])
+@pytest.mark.parametrize("n,window", WINDOW_EDGES)
+def test_decode_attention_window_edge(K, n, window, impl, released):
+    """The key just outside the window carries a huge score and must not be seen; the one just
+    inside must; pages the window has passed may be gone from the block table."""
+    nq, hd, page = 2, 64, 16
+    first = n - window                                         # first visible key of the token at position n - 1
+    for spike, want in ((first - 1, 1.0), (first, -5.0)):
+        kc, vc, bt, mb = _edge_cache(n, page, hd, spike, ((first - 1) // page) * page if released else 0)
+        q = torch.zeros(1, nq * hd); q[:, ::hd] = 8.0
+        splits = (n + 127) // 128
+        part_out = torch.empty(nq * splits * hd, device="cuda"); part_ml = torch.empty(nq * splits * 2, device="cuda")
+        out = torch.empty(1, nq * hd, dtype=torch.bfloat16, device="cuda")
+        K.paged_attention_decode(q.to(torch.bfloat16).cuda(), kc, vc, bt, mb, torch.zeros(1, dtype=torch.int32).cuda(),
+                                 torch.tensor([n - 1], dtype=torch.int32).cuda(), out, part_out, part_ml,
+                                 nq, 1, hd, page, window, 1.0 / math.sqrt(hd), splits, impl=impl)
+        got = out.float().cpu().numpy()
+        assert np.allclose(got, want, atol=2e-2), (impl, spike, got[0, :3])
+    assert K.attention_decode_stream_error() == 0
+
+
+@pytest.mark.parametrize("released", [False, True])
+@pytest.mark.parametrize("impl", ["mma", "tc"])
+@pytest.mark.parametrize("n,window", WINDOW_EDGES)
+def test_prefill_attention_window_edge(K, n, window, impl, released):
+    """A portion of 40 tokens whose rows straddle the edge: the spiked key is inside the window of
+    the first 21 rows and outside that of the other 19."""
+    nq, hd, page, ql = 2, 64, 16, 40
+    p0 = n - ql
+    spike = (p0 + 20) - window + 1                              # row at position p sees it iff p <= p0 + 20
+    kc, vc, bt, mb = _edge_cache(n, page, hd, spike, ((p0 - window + 1) // page) * page if released else 0)
+    q = torch.zeros(ql, nq * hd); q[:, ::hd] = 8.0
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32).cuda()
+    out = torch.empty(ql, nq * hd, dtype=torch.bfloat16, device="cuda")
+    K.paged_attention_prefill(q.to(torch.bfloat16).cuda(), kc, vc, bt, mb, i32([0, ql]), i32([n]), i32([0]), i32([0]), 1,
+                              out, nq, 1, hd, page, window, 1.0 / math.sqrt(hd), impl=impl)
+    got = out.float().cpu().numpy()
+    assert np.allclose(got[:21], -5.0, atol=2e-2), (impl, got[:21, 0])
+    assert np.allclose(got[21:], 1.0, atol=2e-2), (impl, got[21:, 0])
+    assert K.attention_prefill_tc_error() == 0

@@ -99,7 +99,7 @@ def test_attention_mixer_alone(dtype, window):
     att.bind({n: (t.cuda() if dtype == torch.bfloat16 else t.float().cuda()) for n, t in ws.items()})
     lens = [17, 9]
     hs = [torch.randn(n, Hd, generator=g).to(torch.bfloat16) for n in lens]
-    storage = torch.zeros(1, 2, 16 * page, nkv, hd, dtype=dtype, device="cuda")
+    storage = {n: torch.zeros(1, 16 * page, nkv, hd, dtype=dtype, device="cuda") for n in ("k", "v")}
     tables = [[3, 0, 7, 5, 9], [2, 8, 1]]
     bt = torch.full((2, 6), -1, dtype=torch.int32)
     for s, t in enumerate(tables):
@@ -150,20 +150,26 @@ def register_toy_parts():
             return CacheNeed("state", state_shape=(self.hidden_size + 1,), state_dtype="float32")
 
         def forward(self, ctx, h, run):
+            """All on the device, by the contract of fixed-size state (parts/base.py, GroupView): the
+            slot of request s is slot_map[s]; its portion is q_start[s]..q_start[s+1]; a portion that
+            starts at position 0 starts from nothing.  Nothing is read on the host, so decode steps of
+            a model with this mixer are captured in CUDA graphs like any other."""
             group = ctx.groups[run.group]
-            state = group.storage[run.slot]                     # [slots, H+1]
-            q_start, pos, slots = ctx.q_start.cpu().tolist(), ctx.positions.cpu().tolist(), group.slot_map.cpu().tolist()
-            out = torch.empty_like(h)
-            for s in range(ctx.num_seqs):
-                a, b = q_start[s], q_start[s + 1]
-                st = state[slots[s]]
-                if pos[a] == 0:
-                    st.zero_()                                   # a new request starts from nothing
-                sums = st[:-1] + torch.cumsum(h[a:b].float(), 0)
-                counts = st[-1] + torch.arange(1, b - a + 1, device=h.device, dtype=torch.float32)
-                out[a:b] = (sums / counts[:, None]).to(h.dtype)
-                st[:-1] = sums[-1]; st[-1] = counts[-1]
-            return out
+            state = group.storage["state"][run.slot]            # [slots + 1, H+1]
+            S, T = ctx.num_seqs, ctx.num_tokens
+            seq = ctx.seq_of_token[:T].long()
+            first = ctx.q_start[:S].long()
+            last = ctx.q_start[1:S + 1].long() - 1
+            slots = group.slot_map[:S].long()
+            fresh = (ctx.positions[:T].long()[first] == 0)
+            base = torch.where(fresh[:, None], torch.zeros((), device=h.device), state[slots]).double()      # [S, H+1]
+            hd = h.double()
+            csum = torch.cumsum(hd, 0)
+            within = csum - (csum[first] - hd[first])[seq]       # running sums inside each portion
+            sums = base[seq, :-1] + within
+            counts = base[seq, -1] + (torch.arange(T, device=h.device) - first[seq] + 1).double()
+            state[slots] = torch.cat([sums[last], counts[last, None]], 1).float()
+            return (sums / counts[:, None]).to(h.dtype)
 
     @register_feed_forward("toy_routed")
     class Routed(FeedForward):
@@ -336,3 +342,233 @@ def test_windowed_attention_model_frees_pages():
         H.assert_close(np.stack([got[1][p] for p in range(T)]), want, tol, f"windowed model {dtype}")
         st = eng.cache_state()
         assert st["metrics"]["window_releases"] >= 15 and st["free_pages"][1] >= 32 - 5 and st["free_pages"][0] == 32 - 23
+
+
+# ---------------------------------------------------------------------------- more toy parts: other arrangements, other ends, another cache
+def register_more_toy_parts():
+    from aien_sovereign_core_mv_b200 import kernels as K
+    from aien_sovereign_core_mv_b200 import register_block, register_embedding, register_head, register_mixer
+    from aien_sovereign_core_mv_b200.parts import Block, CacheNeed, Embedding, Head, Mixer, add_to_residual, linear
+
+    @register_block("toy_postnorm")
+    class PostNorm(Block):
+        """x = norm_mixer(x + mixer(x)); x = norm_ff(x + ff(x)): the stream itself is normed."""
+        norm_slots = ("norm_mixer", "norm_ff")
+
+        def __init__(self, mixer, feed_forward, norm_mixer, norm_ff):
+            self.mixer, self.feed_forward, self.norm_mixer, self.norm_ff = mixer, feed_forward, norm_mixer, norm_ff
+
+        def parts(self):
+            return {"norm_mixer": self.norm_mixer, "mixer": self.mixer, "norm_ff": self.norm_ff, "feed_forward": self.feed_forward}
+
+        def forward(self, ctx, x, delta, run):
+            add_to_residual(ctx, x, delta)                    # what the block before left pending
+            a = self.mixer.forward(ctx, x.to(ctx.dtype), run)
+            x.copy_(self.norm_mixer.forward(ctx, x, a))       # the norm adds a to x first
+            f = self.feed_forward.forward(ctx, x.to(ctx.dtype))
+            x.copy_(self.norm_ff.forward(ctx, x, f))
+            return None
+
+    @register_block("toy_mixer_only")
+    class MixerOnly(Block):
+        """x += mixer(norm(x)); no feed-forward."""
+        norm_slots = ("norm",)
+
+        def __init__(self, mixer, feed_forward, norm):
+            assert feed_forward is None
+            self.mixer, self.norm = mixer, norm
+
+        def parts(self):
+            return {"norm": self.norm, "mixer": self.mixer}
+
+        def forward(self, ctx, x, delta, run):
+            return self.mixer.forward(ctx, self.norm.forward(ctx, x, delta), run)
+
+    @register_embedding("toy_scaled")
+    class Scaled(Embedding):
+        def __init__(self, vocab_size, hidden_size, scale):
+            self.shape, self.scale = (vocab_size, hidden_size), float(scale)
+
+        def param_shapes(self):
+            return {"weight": (self.shape, "embedding")}
+
+        def bind(self, tensors):
+            self.weight = tensors["weight"].contiguous()
+
+        def tied_weight(self):
+            return self.weight
+
+        def forward(self, ctx, token_ids, x):
+            K.embed_gather(self.weight, token_ids, x)
+            x.mul_(self.scale)
+
+    @register_head("toy_softcap")
+    class SoftCap(Head):
+        """logits = cap * tanh((rows . W^T + bias) / cap), W the embedding's table."""
+        tied = True
+
+        def __init__(self, vocab_size, hidden_size, cap):
+            self.vocab_size, self.cap = vocab_size, float(cap)
+
+        def param_shapes(self):
+            return {"bias": ((self.vocab_size,), "norm")}
+
+        def bind(self, tensors):
+            self.bias = tensors["bias"].float()
+
+        def tie(self, embedding):
+            self.weight = embedding.tied_weight()
+
+        def forward(self, ctx, rows, logits):
+            linear(ctx, rows, self.weight, out=logits)
+            logits.copy_(self.cap * torch.tanh((logits + self.bias) / self.cap))
+
+    @register_mixer("toy_latent")
+    class Latent(Mixer):
+        """One latent vector per token in the cache (a single plane, not keys and values): c = Wd h
+        is stored; a token attends over the latents up to its own, o = softmax(q . c / sqrt(r)) c
+        with q = Wq h, and y = Wu o."""
+
+        def __init__(self, hidden_size, rank, position=None):
+            self.hidden_size, self.rank = hidden_size, rank
+
+        def param_shapes(self):
+            return {"down": ((self.rank, self.hidden_size), "matrix"), "q": ((self.rank, self.hidden_size), "matrix"),
+                    "up": ((self.hidden_size, self.rank), "matrix")}
+
+        def bind(self, tensors):
+            self.t = {k: v.float() for k, v in tensors.items()}
+
+        def cache_need(self):
+            return CacheNeed("full", planes=(("latent", (self.rank,)),))
+
+        def forward(self, ctx, h, run):
+            g = ctx.groups[run.group]
+            plane = g.storage["latent"][run.slot]                 # [tokens of the pool, rank]
+            T, ps = ctx.num_tokens, g.page_size
+            x = h.float()
+            c = (x @ self.t["down"].T).to(plane.dtype)
+            slots = g.slot_map[:T].long()
+            plane[slots.clamp(min=0)] = torch.where((slots >= 0)[:, None], c, plane[slots.clamp(min=0)])
+            q = x @ self.t["q"].T
+            j = torch.arange(max(ctx.max_ctx_len, 1), device=h.device)
+            table = g.block_table[ctx.seq_of_token[:T].long()].long()                    # [T, max_blocks]
+            page = table.gather(1, (j // ps).clamp(max=g.max_blocks - 1)[None].expand(T, -1))
+            seen = j[None] <= ctx.positions[:T].long()[:, None]
+            keys = plane[torch.where(seen, page * ps + j % ps, 0)].float()              # [T, kmax, rank]
+            s = ((keys * q[:, None]).sum(-1) / math.sqrt(self.rank)).masked_fill(~seen, float("-inf"))
+            o = (torch.softmax(s, -1)[..., None] * keys).sum(1)
+            return (o @ self.t["up"].T).to(h.dtype)
+
+
+def toy_spec_two():
+    from aien_sovereign_core_mv_b200 import LayerSpec, ModelSpec, PartSpec, RunEntry
+    Hd, V = 40, 61
+    swiglu = PartSpec("swiglu", {"hidden_size": Hd, "intermediate_size": 56})
+    layers = (
+        LayerSpec("toy_postnorm", PartSpec("toy_latent", {"hidden_size": Hd, "rank": 12}), swiglu, None, PartSpec("none", {}), "a.",
+                  norms={"norm_mixer": PartSpec("rmsnorm", {"eps": 1e-5}), "norm_ff": PartSpec("rmsnorm", {"eps": 1e-2})}),
+        LayerSpec("toy_mixer_only", PartSpec("toy_latent", {"hidden_size": Hd, "rank": 12}), None, PartSpec("rmsnorm", {"eps": 1e-6}),
+                  PartSpec("none", {}), "b."),
+        LayerSpec("prenorm", PartSpec("paged_attention", {"hidden_size": Hd, "num_heads": 2, "num_kv_heads": 1, "head_dim": 16}), swiglu,
+                  PartSpec("rmsnorm", {"eps": 1e-5}), PartSpec("rotary", {"head_dim": 16, "theta": 10000.0}), "c."),
+    )
+    return ModelSpec("ToyTwo", Hd, V, layers, (RunEntry(0, 0), RunEntry(1, 1), RunEntry(2, 2)),
+                     PartSpec("toy_scaled", {"name": "emb", "scale": math.sqrt(Hd)}), PartSpec("rmsnorm", {"eps": 1e-5, "name": "fn"}),
+                     PartSpec("toy_softcap", {"cap": 5.0, "names": {"bias": "head.b"}}), 256)
+
+
+def toy_two_plain(w, ids, round_cache=None):
+    Hd, r = 40, 12
+    T = len(ids)
+    x = pm.f32(w["emb"][ids] * np.float32(math.sqrt(Hd)))
+
+    def latent(prefix, h):
+        c = pm.linear(h, w[prefix + "mixer.down"])
+        if round_cache is not None:
+            c = round_cache(c)
+        q = pm.linear(h, w[prefix + "mixer.q"])
+        s = np.where(np.tril(np.ones((T, T), dtype=bool)), (q @ c.T) / math.sqrt(r), -np.inf)
+        p = np.exp(s - s.max(-1, keepdims=True)); p /= p.sum(-1, keepdims=True)
+        return pm.linear(p @ c, w[prefix + "mixer.up"])
+
+    def swiglu_ff(prefix, h):
+        return pm.linear(pm.swiglu(pm.linear(h, w[prefix + "feed_forward.gate_proj"]), pm.linear(h, w[prefix + "feed_forward.up_proj"])),
+                         w[prefix + "feed_forward.down_proj"])
+
+    x = pm.rms_norm(pm.f32(x + latent("a.", x)), w["a.norm_mixer.weight"], 1e-5)          # post-norm, each norm its own eps
+    x = pm.rms_norm(pm.f32(x + swiglu_ff("a.", x)), w["a.norm_ff.weight"], 1e-2)
+    x = pm.f32(x + latent("b.", pm.rms_norm(x, w["b.norm.weight"], 1e-6)))               # mixer only
+    h = pm.rms_norm(x, w["c.norm_in.weight"], 1e-5)
+    inv = pm.rope_inv_freq(16, 10000.0)
+    q = pm.apply_rope(pm.linear(h, w["c.mixer.q_proj"]).reshape(T, 2, 16), range(T), inv)
+    k = pm.apply_rope(pm.linear(h, w["c.mixer.k_proj"]).reshape(T, 1, 16), range(T), inv)
+    v = pm.linear(h, w["c.mixer.v_proj"]).reshape(T, 1, 16)
+    x = pm.f32(x + pm.linear(pm.attention(q, k, v, np.arange(T)).reshape(T, 32), w["c.mixer.o_proj"]))
+    x = pm.f32(x + swiglu_ff("c.", pm.rms_norm(x, w["c.norm_post.weight"], 1e-5)))
+    logits = pm.linear(pm.rms_norm(x, w["fn"], 1e-5), w["emb"]) + w["head.b"]
+    return 5.0 * np.tanh(logits / 5.0)
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", H.FP32_TOL), ("bfloat16", H.BF16_TOL)])
+def test_other_arrangements_ends_and_cache_planes_from_outside_the_package(dtype, tol):
+    """A post-norm block with two different norms by slot name, a block with one norm and no
+    feed-forward, an embedding that scales, a tied head with a bias and a soft cap, and a mixer
+    that caches one latent plane per token: all registered here, built from the spec by the
+    generic decoder, their cache allocated by the engine from the declared plane shapes."""
+    from aien_sovereign_core_mv_b200 import Engine, EngineConfig
+    from aien_sovereign_core_mv_b200.models import Decoder
+    from aien_sovereign_core_mv_b200.weights import random_tensors
+    register_more_toy_parts()
+    model = Decoder(toy_spec_two())
+    assert [(n.kind, n.planes) for n in model.group_needs] == [("full", (("latent", (12,)),)), ("full", (("k", (1, 16)), ("v", (1, 16))))]
+    assert model.group_slots == [2, 1] and model.tied
+    cat = model.catalog()
+    assert {"emb", "fn", "head.b", "a.norm_mixer.weight", "a.norm_ff.weight", "b.norm.weight", "b.mixer.down"} <= set(cat) and "b.feed_forward.gate_proj" not in cat
+    tensors = dict(random_tensors(cat, 6))
+    model.bind((n, t if dtype == "bfloat16" else t.float()) for n, t in tensors.items())
+    eng = Engine(model, None, EngineConfig(dtype=dtype, page_size=4, max_cache_tokens=96, max_requests=4, max_batch_tokens=64, max_context=64))
+    assert {n: tuple(t.shape) for n, t in eng.storage[0].items()} == {"latent": (2, 96, 12)}
+    assert {n: tuple(t.shape) for n, t in eng.storage[1].items()} == {"k": (1, 96, 1, 16), "v": (1, 96, 1, 16)}
+    w = {n: t.double().numpy() for n, t in tensors.items()}
+    reqs = {1: [t % 61 for t in H.tokens_for("A", 21, 4)], 2: [t % 61 for t in H.tokens_for("A", 10, 5)]}
+    rc = pm.round_bf16 if dtype == "bfloat16" else None
+    want = {r: toy_two_plain(w, toks, rc) for r, toks in reqs.items()}
+    whole = H.run_steps(eng, [([(r, toks, list(range(len(toks))))], [r]) for r, toks in reqs.items()])
+    for r in reqs:
+        H.assert_close(np.stack([whole[r][p] for p in range(len(reqs[r]))]), want[r], tol, f"second toy model whole, request {r}")
+    steps = [([(1, reqs[1][:7], range(7)), (2, reqs[2][:3], range(3))], []),
+             ([(1, reqs[1][7:8], [0]), (2, reqs[2][3:], range(7))], [2])]
+    steps += [([(1, [t], [0])], []) for t in reqs[1][8:]]
+    cut = H.run_steps(eng, steps)
+    for r in reqs:
+        H.assert_close(np.stack([cut[r][p] for p in range(len(reqs[r]))]), want[r], tol, f"second toy model in portions, request {r}")
+    eng.fork(1, 5, 10)                                        # copy-on-write copies every plane of the page
+    a = H.run_steps(eng, [([(5, reqs[1][10:13], range(3))], [1, 5])])
+    H.assert_close(np.stack([a[5][p] for p in range(3)]), want[1][10:13], tol, "child forked inside a page")
+    assert eng.cache_state()["check"] == "" and eng.cache_state()["requests"] == 0
+
+
+def test_state_mixer_on_the_device_keeps_cuda_graphs():
+    """The first toy model in bfloat16: its running-mean mixer follows the device-side contract of
+    fixed-size state, so decode steps are captured and replayed as CUDA graphs (three requests in
+    a graph of four rows: the padding row is pointed at the slot that belongs to nobody)."""
+    from aien_sovereign_core_mv_b200 import Engine, EngineConfig
+    from aien_sovereign_core_mv_b200.models import Decoder
+    from aien_sovereign_core_mv_b200.weights import random_tensors
+    register_toy_parts()
+    model = Decoder(toy_spec())
+    tensors = dict(random_tensors(model.catalog(), 5))
+    model.bind(iter(tensors.items()))
+    eng = Engine(model, None, EngineConfig(dtype="bfloat16", page_size=4, max_cache_tokens=128, max_requests=4, max_batch_tokens=64,
+                                            max_context=64))
+    assert eng._graphable and not eng._replayable            # parts from outside the package: graphs yes, recorded launches no
+    w = {n: t.double().numpy() for n, t in tensors.items()}
+    reqs = {r: [t % 97 for t in H.tokens_for("A", n, r)] for r, n in ((1, 19), (2, 12), (3, 15))}
+    want = {r: toy_plain(w, toks) for r, toks in reqs.items()}
+    H.run_steps(eng, [([(r, toks[:6], []) for r, toks in reqs.items()], [])])
+    steps = [([(r, [toks[6 + s]], [0]) for r, toks in reqs.items()], []) for s in range(6)]
+    got = H.run_steps(eng, steps)
+    assert len(eng._graphs) >= 1
+    for r in reqs:
+        H.assert_close(np.stack([got[r][p] for p in range(6, 12)]), want[r][6:12], H.BF16_TOL, f"state mixer under graphs, request {r}")
