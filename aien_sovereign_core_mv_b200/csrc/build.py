@@ -39,6 +39,49 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr", "--extended-lambda", "-Xcompiler", "-fPIC",
 ]
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall"]
+# AIEN_B200_HOST_SANITIZE=1 builds the host runtime with AddressSanitizer and UndefinedBehaviorSanitizer
+# (any error aborts the process) under a name of its own beside the ordinary one.  The sanitizer runtime
+# must come first in the process, with the C++ runtime beside it (Python itself links neither, and the
+# sanitizer looks up __cxa_throw when it starts): run Python with LD_PRELOAD set to sanitizer_preload().  The
+# reference checks its cache manager and scheduler the same way with Miri (tests/gates/sc-miri.gate).
+SANITIZE_FLAGS = ["-O1", "-g", "-fno-omit-frame-pointer", "-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"]
+
+
+def host_sanitized() -> bool:
+    return os.environ.get("AIEN_B200_HOST_SANITIZE", "").strip() not in ("", "0")
+
+
+def _sanitizing_compiler():
+    """(compiler, path of its libasan.so) for the first C++ compiler at hand that ships the
+    sanitizer runtime, or (None, None)."""
+    for cxx in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), "/usr/bin/g++"):
+        if not cxx or not os.path.exists(cxx):
+            continue
+        try:
+            out = subprocess.run([cxx, "-print-file-name=libasan.so"], capture_output=True, text=True, check=True).stdout.strip()
+        except (OSError, subprocess.CalledProcessError):
+            continue
+        if os.path.isabs(out) and os.path.exists(out):
+            return cxx, out
+    return None, None
+
+
+def sanitizer_runtime() -> Optional[str]:
+    """Path of libasan.so, or None when no compiler here has one."""
+    return _sanitizing_compiler()[1]
+
+
+def sanitizer_preload() -> Optional[str]:
+    """The value of LD_PRELOAD for a Python process that loads the sanitized host runtime:
+    libasan.so and libstdc++.so of the compiler that builds it; None when there is none."""
+    cxx, asan = _sanitizing_compiler()
+    if not cxx:
+        return None
+    try:
+        cpp = subprocess.run([cxx, "-print-file-name=libstdc++.so"], capture_output=True, text=True, check=True).stdout.strip()
+    except (OSError, subprocess.CalledProcessError):
+        return None
+    return f"{asan} {cpp}" if os.path.isabs(cpp) and os.path.exists(cpp) else None
 
 
 class BuildError(RuntimeError):
@@ -157,12 +200,20 @@ def build_host(force: bool = False) -> str:
     out_dir = build_dir()
     sources = sorted(glob.glob(os.path.join(HOST_DIR, "*.cpp")))
     headers = sorted(glob.glob(os.path.join(HOST_DIR, "*.h")))
+    flags = [f for f in CXX_FLAGS if f != "-O2"] + SANITIZE_FLAGS if host_sanitized() else CXX_FLAGS
+    if host_sanitized():
+        out_dir = os.path.join(out_dir, "sanitized")          # same module name, its own folder
+        os.makedirs(out_dir, exist_ok=True)
     lib = os.path.join(out_dir, _host_ext_name())
     stamp = lib + ".stamp"
-    digest = _hash_sources(sources + headers, CXX_FLAGS)
+    digest = _hash_sources(sources + headers, flags)
     if not force and os.path.exists(lib) and os.path.exists(stamp) and open(stamp).read().strip() == digest:
         return lib
     cxx = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
+    if host_sanitized():
+        cxx = _sanitizing_compiler()[0]
+        if not cxx:
+            raise BuildError("AIEN_B200_HOST_SANITIZE=1: no C++ compiler here ships the sanitizer runtime (libasan.so)")
     if not cxx:
         raise BuildError("no C++ compiler found (g++)")
     try:
@@ -171,7 +222,7 @@ def build_host(force: bool = False) -> str:
         raise BuildError(f"pybind11 headers are needed to build the host module: {e}") from None
     _say(f"compiling the host runtime (cache manager, scheduler) into {out_dir}")
     tmp = lib + f".{os.getpid()}.tmp"
-    cmd = [cxx, *CXX_FLAGS, "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"],
+    cmd = [cxx, *flags, "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"],
            "-I", HOST_DIR, *sources, "-o", tmp]
     _run_parallel([cmd], "host", jobs=1)
     os.replace(tmp, lib)

@@ -160,7 +160,7 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
                    const float* __restrict__ top_p, const int* __restrict__ top_k,
                    const unsigned long long* __restrict__ seeds, const long long* __restrict__ request_ids,
                    const int* __restrict__ positions, float* __restrict__ probs_scratch,
-                   int* __restrict__ out_ids) {
+                   int* __restrict__ out_ids, float* __restrict__ out_logprob) {
     __shared__ double red[64];
     __shared__ double scan[SM_THREADS];
     __shared__ uint32_t cand_bits[SM_CAND];         // nucleus candidates: their probabilities, as bit patterns,
@@ -173,6 +173,12 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
     const float T = temperature ? temperature[r] : 0.f;
     if (!(T > 0.001f)) {                           // greedy threshold of the reference
         if (tid == 0) out_ids[r] = amax;
+        if (out_logprob != nullptr) {              // log softmax of the logits as they are, at the maximum: -ln sum exp(l - max)
+            double sum = 0.0;
+            scan_row(row, V, [&](int, float v) { sum += (double)expf(v - maxv); });
+            sum = block_sum_f64(sum, red);
+            if (tid == 0) out_logprob[r] = (float)(-log(sum));
+        }
         return;
     }
     float* probs = probs_scratch + (size_t)r * V;
@@ -312,7 +318,11 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
                     unsigned long long before = 0;
                     for (int i = 0; i < C; ++i)
                         if (cand_bits[i] >= prefix && cand_id[i] < my_id) before += prob_units(__uint_as_float(cand_bits[i]));
-                    if (rr >= before && rr < before + prob_units(__uint_as_float(cand_bits[j]))) out_ids[r] = my_id;
+                    const unsigned long long mine = prob_units(__uint_as_float(cand_bits[j]));
+                    if (rr >= before && rr < before + mine) {
+                        out_ids[r] = my_id;
+                        if (out_logprob != nullptr) out_logprob[r] = (float)log((double)mine / (double)total);   // within the kept set
+                    }
                 }
                 return;
             }
@@ -506,7 +516,11 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
     }
     __syncthreads();
     // rounding may leave the draw at or beyond the last region's end: the last kept token
-    if (tid == 0) out_ids[r] = s_pick >= 0 ? s_pick : (s_last_kept >= 0 ? s_last_kept : amax);
+    if (tid == 0) {
+        const int pick = s_pick >= 0 ? s_pick : (s_last_kept >= 0 ? s_last_kept : amax);
+        out_ids[r] = pick;
+        if (out_logprob != nullptr) out_logprob[r] = total > 0.0 ? (float)log(fmax((double)probs[pick], 1e-300) / total) : 0.f;
+    }
 }
 
 __global__ void __launch_bounds__(SM_THREADS)
@@ -535,6 +549,21 @@ AIEN_API int aien_sample_rows(const float* logits, int R, int V, const float* te
     if (R <= 0) return 0;
     if (V <= 0) return AIEN_E_SHAPE;
     sample_rows_kernel<<<R, SM_THREADS, 0, stream>>>(logits, V, temperature, top_p, top_k, seeds, request_ids,
-                                                     positions, probs_scratch, out_ids);
+                                                     positions, probs_scratch, out_ids, nullptr);
+    return launch_status();
+}
+
+// The same, and the log-probability of each chosen token in out_logprob [R]: for a greedy row the
+// log softmax of the logits at the maximum, -ln sum exp(l - max) (crates/aien-inference-abi/src/
+// tensor.rs:299-318); for a sampled row ln(p / kept mass) with p = softmax(l / T), the probability
+// inside the set the draw was made from (src/transformer_backend.rs:171).
+AIEN_API int aien_sample_rows_logprob(const float* logits, int R, int V, const float* temperature, const float* top_p,
+                                      const int* top_k, const unsigned long long* seeds, const long long* request_ids,
+                                      const int* positions, float* probs_scratch, int* out_ids, float* out_logprob,
+                                      cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (V <= 0 || out_logprob == nullptr) return AIEN_E_SHAPE;
+    sample_rows_kernel<<<R, SM_THREADS, 0, stream>>>(logits, V, temperature, top_p, top_k, seeds, request_ids,
+                                                     positions, probs_scratch, out_ids, out_logprob);
     return launch_status();
 }

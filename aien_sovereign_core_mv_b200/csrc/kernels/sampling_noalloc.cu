@@ -10,7 +10,7 @@ __global__ void sample_rows_kernel(const float* __restrict__ logits, int V, cons
                                    const float* __restrict__ top_p, const int* __restrict__ top_k,
                                    const unsigned long long* __restrict__ seeds, const long long* __restrict__ request_ids,
                                    const int* __restrict__ positions, float* __restrict__ probs_scratch,
-                                   int* __restrict__ out_ids);
+                                   int* __restrict__ out_ids, float* __restrict__ out_logprob);
 
 // The scratch itself.  In host code this name is only a handle for the runtime, not an address a
 // kernel could use: the device address is asked for once per device below.
@@ -39,6 +39,6 @@ AIEN_API int aien_sample_rows_static(const float* logits, int R, int V, const fl
         g_scratch_addr[dev] = static_cast<float*>(p);
     }
     sample_rows_kernel<<<R, 1024, 0, stream>>>(logits, V, temperature, top_p, top_k, seeds, request_ids, positions,
-                                               g_scratch_addr[dev], out_ids);
+                                               g_scratch_addr[dev], out_ids, nullptr);
     return launch_status();
 }

@@ -23,8 +23,9 @@ extern "C" {
 // one Philox draw per row), but without a scratch argument.
 //   logits [R, V] float32; temperature, top_p [R] float32; top_k, positions [R] int32;
 //   seeds [R] uint64; request_ids [R] int64; out_ids [R] int32; all device pointers.
-// Returns 0, a cudaError_t value, or -3 when R * V exceeds AIEN_SAMPLE_STATIC_MAX_ELEMS (nothing
-// is launched then).  It calls no allocating routine.
+// Returns 0, a cudaError_t value, -3 when R * V exceeds AIEN_SAMPLE_STATIC_MAX_ELEMS, or -5 when the
+// current device's index is 64 or more (the table of per-device addresses ends there); nothing is
+// launched in either case.  It calls no allocating routine.
 //
 // The first call on each device looks up the device address of the scratch array (one
 // cudaGetSymbolAddress with that device current) and remembers it; make that first call outside

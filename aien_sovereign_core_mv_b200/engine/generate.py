@@ -43,6 +43,7 @@ class GenerationResult:
     finish_reason: str            # "stop", "length", "cancelled", "aborted"
     message: str = ""
     preemptions: int = 0
+    logprobs: Optional[List[float]] = None     # one per token, when SamplingParams.logprobs asked for them
 
 
 _REASONS = {"StopToken": "stop", "LengthLimit": "length", "Cancelled": "cancelled", "Aborted": "aborted", "NONE": "none"}
@@ -66,18 +67,23 @@ class Generator:
         R = engine.max_requests
         dev = engine.device
         # two of each staging buffer: a step is prepared while the one before it is still in flight
-        # sampled ids, then the four error words of the kernels with bounded waits: one copy brings both
-        self._ids_dev2 = [torch.zeros(R + 4, dtype=torch.int32, device=dev) for _ in range(2)]
-        self._ids_host2 = [torch.zeros(R + 4, dtype=torch.int32, pin_memory=True) for _ in range(2)]
-        self._fparams_host2 = [torch.empty((2, R), dtype=torch.float32, pin_memory=True) for _ in range(2)]   # temperature, top_p
-        self._iparams_host2 = [torch.empty((2, R), dtype=torch.int32, pin_memory=True) for _ in range(2)]     # top_k, position
-        self._lparams_host2 = [torch.empty((2, R), dtype=torch.int64, pin_memory=True) for _ in range(2)]     # seed, request id
+        # sampled ids, then the four error words of the kernels with bounded waits, then (when a request
+        # asks for them) the log-probabilities of the chosen tokens as float32 bits: one copy brings all
+        self._ids_dev2 = [torch.zeros(2 * R + 4, dtype=torch.int32, device=dev) for _ in range(2)]
+        self._ids_host2 = [torch.zeros(2 * R + 4, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._logprobs: Dict[int, List[float]] = {}
+        # sampling parameters of a step's rows, one block of 8 R words so that one copy brings them:
+        # temperature, top_p (float32), top_k, position (int32), seed, request id (int64)
+        self._params_host2 = [torch.zeros(8 * R, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._params_np = [(h.numpy()[:2 * R].view(np.float32).reshape(2, R), h.numpy()[2 * R:4 * R].reshape(2, R),
+                            h.numpy()[4 * R:].view(np.int64).reshape(2, R)) for h in self._params_host2]
         self._turn = 0
         self._events = [torch.cuda.Event() for _ in range(2)]
         self._inflight = None        # (rows, host ids, count, event) of the step whose tokens the host has not seen
-        self._fparams = torch.empty((2, R), dtype=torch.float32, device=dev)
-        self._iparams = torch.empty((2, R), dtype=torch.int32, device=dev)
-        self._lparams = torch.empty((2, R), dtype=torch.int64, device=dev)
+        self._params_dev = torch.zeros(8 * R, dtype=torch.int32, device=dev)
+        self._fparams = self._params_dev[:2 * R].view(torch.float32).view(2, R)
+        self._iparams = self._params_dev[2 * R:4 * R].view(2, R)
+        self._lparams = self._params_dev[4 * R:].view(torch.int64).view(2, R)
         self._scratch: Optional[torch.Tensor] = None
         self.h2d_bytes = 0
         self.d2h_bytes = 0
@@ -98,6 +104,7 @@ class Generator:
             self._drain()                     # a token of an earlier request with this id is still on its way
         self.scheduler.submit(int(request_id), prompt, int(p.max_tokens), stops, int(priority))
         self.params[int(request_id)] = p
+        self._logprobs.pop(int(request_id), None)
 
     def fork(self, parent_id: int, child_id: int, params: Optional[SamplingParams] = None, priority: int = 0) -> None:
         """A running request branches: the child continues from the parent's tokens so far on shared
@@ -116,9 +123,10 @@ class Generator:
         if plan.entries:
             rows, ids_dev = self._launch_or_rollback(plan, None)
             n = len(rows)
+            m = self._copy_len(rows)
             host = self._ids_host2[self._turn & 1]
-            host[:n + 4].copy_(self._ids_dev2[self._turn & 1][:n + 4], non_blocking=False)
-            self.d2h_bytes += 4 * (n + 4)
+            host[:m].copy_(self._ids_dev2[self._turn & 1][:m], non_blocking=False)
+            self.d2h_bytes += 4 * m
             vals = host[:n + 4].tolist()
             msg = K.wait_error_message(vals[n:])
             if msg:
@@ -126,9 +134,25 @@ class Generator:
                 K.read_wait_errors()
                 self.scheduler.rollback()
                 raise K.KernelError(msg)
+            self._keep_logprobs(rows, host, m)
             self.scheduler.commit(vals[:n])
             self._log(plan, n)
         return self._finished()
+
+    def _copy_len(self, rows) -> int:
+        """How many words of the ids buffer a step brings to the host: ids, wait words and, if any
+        of its requests wants them, log-probabilities."""
+        n = len(rows)
+        return 2 * n + 4 if any(self.params[e.id].logprobs for e in rows) else n + 4
+
+    def _keep_logprobs(self, rows, host, m) -> None:
+        n = len(rows)
+        if m <= n + 4:
+            return
+        lp = host[n + 4:m].view(torch.float32).tolist()
+        for e, v in zip(rows, lp):
+            if self.params[e.id].logprobs:
+                self._logprobs.setdefault(e.id, []).append(float(v))
 
     def _launch_or_rollback(self, plan, prev):
         """A launch that is refused (or any other failure before the step is committed) leaves the
@@ -185,7 +209,11 @@ class Generator:
         out = []
         for ev in self.scheduler.take_finished():
             rec_pre = self.scheduler.record(ev.id).preemptions
-            out.append(GenerationResult(ev.id, list(ev.generated), _REASONS.get(ev.reason.name, ev.reason.name), ev.message, rec_pre))
+            toks = list(ev.generated)
+            lps = self._logprobs.pop(ev.id, None)
+            if lps is not None or (ev.id in self.params and self.params[ev.id].logprobs):
+                lps = (lps or [])[:len(toks)]          # a stop id and what was computed beyond it bring no token
+            out.append(GenerationResult(ev.id, toks, _REASONS.get(ev.reason.name, ev.reason.name), ev.message, rec_pre, lps))
             self.params.pop(ev.id, None)
         return out
 
@@ -195,22 +223,22 @@ class Generator:
         turn = self._turn & 1
         ps = [self.params[e.id] for e in rows]
         ids_dev = self._ids_dev2[turn][:R]
-        if all(p.greedy for p in ps):
+        want_lp = any(p.logprobs for p in ps)
+        lp_dev = self._ids_dev2[turn][R + 4:2 * R + 4].view(torch.float32) if want_lp else None
+        if all(p.greedy for p in ps) and not want_lp:
             K.argmax_rows(logits, ids_dev)
         else:
-            f, i, l = self._fparams_host2[turn], self._iparams_host2[turn], self._lparams_host2[turn]
+            f, i, l = self._params_np[turn]
             for r, (e, p) in enumerate(zip(rows, ps)):
                 f[0, r], f[1, r] = p.temperature, p.top_p
                 i[0, r], i[1, r] = p.top_k, e.start + len(e.tokens)
                 l[0, r], l[1, r] = p.seed & 0x7FFFFFFFFFFFFFFF, e.id
-            self._fparams.copy_(f, non_blocking=True)
-            self._iparams.copy_(i, non_blocking=True)
-            self._lparams.copy_(l, non_blocking=True)
-            self.h2d_bytes += R * 24
+            self._params_dev.copy_(self._params_host2[turn], non_blocking=True)
+            self.h2d_bytes += self._params_dev.numel() * 4
             if self._scratch is None or self._scratch.numel() < R * logits.shape[1]:
                 self._scratch = torch.empty(self.engine.max_requests * logits.shape[1], dtype=torch.float32, device=logits.device)
             K.sample_rows(logits, self._fparams[0], self._fparams[1], self._iparams[0], self._lparams[0], self._lparams[1],
-                          self._iparams[1], self._scratch, ids_dev)
+                          self._iparams[1], self._scratch, ids_dev, lp_dev)
         return ids_dev
 
     # ------------------------------------------------------------------ steps that overlap
@@ -224,12 +252,13 @@ class Generator:
             feed_from = ({e.id: r for r, e in enumerate(prev[0])}, prev[4]) if prev is not None else None
             rows, ids_dev = self._launch_or_rollback(plan, feed_from)
             n = len(rows)
+            m = self._copy_len(rows)
             host = self._ids_host2[self._turn & 1]
-            host[:n + 4].copy_(self._ids_dev2[self._turn & 1][:n + 4], non_blocking=True)
+            host[:m].copy_(self._ids_dev2[self._turn & 1][:m], non_blocking=True)
             ev = self._events[self._turn & 1]
             ev.record()
-            self.d2h_bytes += 4 * (n + 4)
-            now = (rows, host, n, ev, ids_dev)
+            self.d2h_bytes += 4 * m
+            now = (rows, host, n, ev, ids_dev, m)
             self.scheduler.commit_deferred()
             self._log(plan, len(rows))
         self._inflight = now
@@ -247,7 +276,7 @@ class Generator:
         return self._finished()
 
     def _resolve(self, flight) -> None:
-        rows, host, n, ev, _ = flight
+        rows, host, n, ev, _, m = flight
         ev.synchronize()
         vals = host[:n + 4].tolist()
         msg = K.wait_error_message(vals[n:])
@@ -259,6 +288,7 @@ class Generator:
             self._inflight = None
             self.scheduler.restart_running()
             raise K.KernelError(msg)
+        self._keep_logprobs(rows, host, m)
         if n:
             self.scheduler.resolve_for([(e.id, t, e.arrival) for e, t in zip(rows, vals[:n])])
 

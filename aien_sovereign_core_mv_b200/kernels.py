@@ -120,6 +120,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_paged_attention_generic": [P, L, P, P, P, I, P, P, P, L, I, I, I, I, I, F, I, I, I, P],
         "aien_argmax_rows": [P, I, I, P, P],
         "aien_sample_rows": [P, I, I, P, P, P, P, P, P, P, P, P],
+        "aien_sample_rows_logprob": [P, I, I, P, P, P, P, P, P, P, P, P, P],
         "aien_gemv_bf16": [P, L, P, L, P, I, L, I, I, I, I, I, c_size_t, P],
         "aien_gemv_stream_bf16": [P, L, P, L, P, I, L, I, I, I, I, I, c_size_t, P],
         "aien_gemv_stream_error": [],
@@ -385,14 +386,20 @@ def argmax_rows(logits: torch.Tensor, out_ids: torch.Tensor) -> None:
 
 def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, top_k: torch.Tensor,
                 seeds: torch.Tensor, request_ids: torch.Tensor, positions: torch.Tensor, scratch: torch.Tensor,
-                out_ids: torch.Tensor) -> None:
-    """One token per row; see csrc/kernels/sampling.cu for the rules.  scratch: R*V float32."""
-    _dev(logits, temperature, top_p, top_k, seeds, request_ids, positions, scratch, out_ids)
+                out_ids: torch.Tensor, out_logprob: Optional[torch.Tensor] = None) -> None:
+    """One token per row; see csrc/kernels/sampling.cu for the rules.  scratch: R*V float32.
+    ``out_logprob`` (float32 [R]) also receives the log-probability of each chosen token."""
+    _dev(logits, temperature, top_p, top_k, seeds, request_ids, positions, scratch, out_ids, out_logprob)
     R, V = logits.shape
     assert logits.dtype == torch.float32 and logits.is_contiguous()
     assert temperature.dtype == torch.float32 and top_p.dtype == torch.float32 and top_k.dtype == torch.int32
     assert seeds.dtype == torch.int64 and request_ids.dtype == torch.int64 and positions.dtype == torch.int32
     assert scratch.dtype == torch.float32 and scratch.numel() >= R * V and out_ids.dtype == torch.int32
+    if out_logprob is not None:
+        assert out_logprob.dtype == torch.float32 and out_logprob.numel() >= R and out_logprob.is_contiguous()
+        _check(lib().aien_sample_rows_logprob(_p(logits), R, V, _p(temperature), _p(top_p), _p(top_k), _p(seeds), _p(request_ids),
+                                              _p(positions), _p(scratch), _p(out_ids), _p(out_logprob), _stream()), "sample_rows_logprob")
+        return
     _check(lib().aien_sample_rows(_p(logits), R, V, _p(temperature), _p(top_p), _p(top_k), _p(seeds), _p(request_ids),
                                   _p(positions), _p(scratch), _p(out_ids), _stream()), "sample_rows")
 

@@ -48,6 +48,10 @@ class SamplingParams:
     max_tokens: int = 512
     stop_token_ids: Optional[Sequence[int]] = None      # None: the model's end-of-sequence ids
     seed: int = 0
+    # Return the log-probability of every generated token with it, as the reference's outputs carry
+    # it (crates/aien-abi-core/src/lib.rs:580-599, DecodeOutput::Token{logprob}): greedy, the log
+    # softmax of the logits at the maximum; sampled, ln(p / kept mass) inside the set drawn from.
+    logprobs: bool = False
 
     @property
     def greedy(self) -> bool:

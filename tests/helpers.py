@@ -135,3 +135,28 @@ def run_trace(model_dir, dtype, out_dir, max_tokens, steps, page_size=None, time
         if os.path.exists(path):
             out[s["step"]] = np.fromfile(path, dtype="<f4").reshape(-1, vocab)
     return out
+
+
+def knife_edge(logits, temperature, top_p, top_k, u, eps=2e-6):
+    """Whether the draw `u` for these logits sits on an edge that float32 exponentials may legitimately
+    move: u times the kept mass within `eps` (of the mass) of a boundary between two kept tokens, or a
+    cumulative mass in the nucleus order within `eps` of top_p (one token more or fewer is kept).
+    Only such a draw may differ between the device sampler and the plain float64 one."""
+    kept, probs = pm.kept_set(logits, temperature, top_p, top_k)
+    mass = sum(probs[i] for i in kept)
+    cum = 0.0
+    for i in kept:
+        cum += probs[i]
+        if abs(cum - u * mass) <= eps * mass:
+            return True
+    if 0.0 < top_p < 1.0:
+        allowed = [i for i in range(len(probs)) if probs[i] > 0.0]
+        order = sorted(allowed, key=lambda i: (-probs[i], i))
+        cum = 0.0
+        for i in order:
+            cum += probs[i]
+            if abs(cum - top_p) <= eps:
+                return True
+            if cum > top_p + eps:
+                break
+    return False
