@@ -143,7 +143,7 @@ class Generator:
         """How many words of the ids buffer a step brings to the host: ids, wait words and, if any
         of its requests wants them, log-probabilities."""
         n = len(rows)
-        return 2 * n + 4 if any(self.params[e.id].logprobs for e in rows) else n + 4
+        return 2 * n + 4 if any(e.id in self.params and self.params[e.id].logprobs for e in rows) else n + 4
 
     def _keep_logprobs(self, rows, host, m) -> None:
         n = len(rows)
@@ -151,7 +151,8 @@ class Generator:
             return
         lp = host[n + 4:m].view(torch.float32).tolist()
         for e, v in zip(rows, lp):
-            if self.params[e.id].logprobs:
+            p = self.params.get(e.id)              # gone: the request ended on an earlier token (a stop id)
+            if p is not None and p.logprobs:
                 self._logprobs.setdefault(e.id, []).append(float(v))
 
     def _launch_or_rollback(self, plan, prev):
