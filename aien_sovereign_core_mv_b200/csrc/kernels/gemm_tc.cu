@@ -209,6 +209,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // tile i+1, and the producer runs ahead across tile borders.  With BN 256 one k-block reads
 // 16 KB of A and 32 KB of W from shared memory for 512 tensor-core cycles, which leaves the
 // shared-memory bandwidth headroom that 128 x 128 tiles (32 KB for 256 cycles) do not have.
+// With `splits` > 1 (float32 output only) every tile is made `splits` times, each over one range of
+// k-blocks, into out + range * part_stride: the caller's consumer adds the ranges in order.  A
+// narrow product with long K (40 tiles of 128 x 256) fills the GPU that way; units are ordered
+// range-major, so the CTAs that run together share the tiles of A and W they load through L2.
+// (Dealing the k-blocks of the last wave out in equal runs, the tiles cut between CTAs put together
+// in the kernel through scratch, was measured and not kept: CTAs that are out of step in K re-read
+// W from HBM, and the addition at the end cost more than the wave it saved.)
 template <int BN> struct TcP {
     static constexpr int STAGE_A = TC_BM * TC_BK * 2, STAGE_B = BN * TC_BK * 2;
     static constexpr int STAGES = (192 * 1024) / (STAGE_A + STAGE_B);          // 4 of 48 KB
@@ -218,7 +225,7 @@ template <int BN> struct TcP {
 template <int BN, int EPI, typename TC>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                          TC* __restrict__ out, long ldc, int M, int N, int K) {
+                          TC* __restrict__ out, long ldc, int M, int N, int K, int splits, int kb_per_split, size_t part_stride) {
     using P = TcP<BN>;
     constexpr int STAGES = P::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -232,8 +239,12 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
-    const int total = m_tiles * n_tiles;
-    const int num_kb = (K + TC_BK - 1) / TC_BK;
+    const int tiles = m_tiles * n_tiles;
+    const int total = tiles * splits;                   // units: (range of K, tile), tiles fastest
+    const int all_kb = (K + TC_BK - 1) / TC_BK;
+    // k-blocks [kb_lo(u), kb_hi(u)) of unit u
+    auto kb_lo = [&](int u) { return (u / tiles) * kb_per_split; };
+    auto kb_hi = [&](int u) { return min(all_kb, (u / tiles + 1) * kb_per_split); };
 
     griddep_launch();
     if (threadIdx.x == 0) {
@@ -254,16 +265,18 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         if (lane == 0) {
             // the first ring of W (of this CTA's first tile) goes out before the wait for the kernel
             // ahead in the stream: A is its result, W is not
-            const uint32_t ahead = blockIdx.x < total ? (uint32_t)min(num_kb, STAGES) : 0u;
-            for (uint32_t kb = 0; kb < ahead; ++kb) {
-                mbar_expect_tx(full0 + 8 * kb, P::STAGE_A + P::STAGE_B);
-                tma_load_2d(sB + kb * P::STAGE_B, &map_w, full0 + 8 * kb, kb * TC_BK, (blockIdx.x / m_tiles) * BN);
+            const int u0 = blockIdx.x;
+            const uint32_t ahead = u0 < total ? (uint32_t)min(kb_hi(u0) - kb_lo(u0), STAGES) : 0u;
+            for (uint32_t i = 0; i < ahead; ++i) {
+                mbar_expect_tx(full0 + 8 * i, P::STAGE_A + P::STAGE_B);
+                tma_load_2d(sB + i * P::STAGE_B, &map_w, full0 + 8 * i, (kb_lo(u0) + (int)i) * TC_BK, ((u0 % tiles) / m_tiles) * BN);
             }
             griddep_wait();
             uint32_t it = 0;
-            for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+            for (int u = blockIdx.x; u < total; u += gridDim.x) {
+                const int tile = u % tiles;
                 const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                for (int kb = kb_lo(u), kbe = kb_hi(u); kb < kbe; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it < ahead) {                                  // W is on its way already
                         tma_load_2d(sA + s * P::STAGE_A, &map_a, full0 + 8 * s, kb * TC_BK, m0);
@@ -281,18 +294,19 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             const uint32_t idesc = umma_idesc_bf16(TC_BM, BN, false);
             uint32_t it = 0;
             int i = 0;
-            for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++i) {
+            for (int u = blockIdx.x; u < total; u += gridDim.x, ++i) {
                 const int acc = i & 1;
                 if (i >= 2) mbar_wait(tempty0 + 8 * acc, ((i >> 1) - 1) & 1, 4);      // the epilogue has drained this accumulator
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int kb_first = kb_lo(u);
+                for (int kb = kb_first, kbe = kb_hi(u); kb < kbe; ++kb, ++it) {
                     const int s = it % STAGES;
                     mbar_wait(full0 + 8 * s, (it / STAGES) & 1, 2);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t da = make_desc_sw128(sA + s * P::STAGE_A), db = make_desc_sw128(sB + s * P::STAGE_B);
 #pragma unroll
                     for (int k = 0; k < TC_BK / 16; ++k)
-                        umma_bf16(tmem_acc + acc * BN, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        umma_bf16(tmem_acc + acc * BN, da + 2 * k, db + 2 * k, idesc, (kb > kb_first || k > 0) ? 1u : 0u);
                     umma_commit(empty0 + 8 * s);
                 }
                 umma_commit(tfull0 + 8 * acc);
@@ -301,9 +315,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     } else {
         const int quarter = warp & 3;
         int i = 0;
-        for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++i) {
+        for (int u = blockIdx.x; u < total; u += gridDim.x, ++i) {
             const int acc = i & 1;
+            const int tile = u % tiles;
             const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
+            TC* out_u = out + (size_t)(u / tiles) * part_stride;
             mbar_wait(tfull0 + 8 * acc, (i >> 1) & 1, 3);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int row = m0 + quarter * 32 + lane;
@@ -312,7 +328,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 uint32_t r[32];
                 tmem_ld32(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + c0), r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (row < M && n0 + c0 < N) tc_store_chunk<EPI, TC>(r, out, ldc, row, n0, c0, N);
+                if (row < M && n0 + c0 < N) tc_store_chunk<EPI, TC>(r, out_u, ldc, row, n0, c0, N);
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -337,7 +353,8 @@ static int tc_num_sms() {
 }
 
 template <int BN, int EPI, typename TC>
-static int launch_tc_persistent(const void* A, long lda, const void* W, long ldw, void* out, long ldc, int M, int N, int K, cudaStream_t stream) {
+static int launch_tc_persistent(const void* A, long lda, const void* W, long ldw, void* out, long ldc, int M, int N, int K,
+                                int splits, size_t part_stride, cudaStream_t stream) {
     CUtensorMap ma, mw;
     if (!make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TC_BK, TC_BM) || !make_map(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, TC_BK, BN))
         return AIEN_E_STATE;
@@ -347,25 +364,32 @@ static int launch_tc_persistent(const void* A, long lda, const void* W, long ldw
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcP<BN>::SMEM) != cudaSuccess) return AIEN_E_STATE;
         configured = true;
     }
-    const long total = (long)((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
+    const int total_kb = (K + TC_BK - 1) / TC_BK;
+    const int kb_per_split = (total_kb + splits - 1) / splits;
+    const int ranges = (total_kb + kb_per_split - 1) / kb_per_split;          // what aien_gemm_tc_ranges says
+    const long total = (long)((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN) * ranges;
     const unsigned grid = (unsigned)(total < tc_num_sms() ? total : tc_num_sms());
-    launch_chain(kern, dim3(grid), dim3(192), (size_t)TcP<BN>::SMEM, stream, ma, mw, (TC*)out, ldc, M, N, K);
+    launch_chain(kern, dim3(grid), dim3(192), (size_t)TcP<BN>::SMEM, stream, ma, mw, (TC*)out, ldc, M, N, K, ranges, kb_per_split, part_stride);
     return launch_status();
 }
 
-// Which kernel a product without split-K takes: 0 the one-tile-per-CTA kernel, 256 the persistent
-// kernel with 128 x 256 tiles, once these give every SM a tile.  (Persistent with 128 x 128 tiles
-// was measured 25-35 % slower than either: one CTA per SM at the shared-memory bandwidth limit.)
+// Which kernel a product takes: 0 the one-tile-per-CTA kernel, 256 the persistent kernel with
+// 128 x 256 tiles.  The persistent one once its units (tiles x ranges of K) give every SM one, and
+// for any product of more than 64 rows of A by at least 256 of W with three fifths of that: its
+// 128 x 256 tile runs at more than twice the rate of the 128 x 128 one, which makes up for idle
+// SMs (512 x 6,144 x 2,560: 96 units, 19 us against 22).  (Persistent with 128 x 128 tiles was
+// measured 25-35 % slower than either: one CTA per SM at the shared-memory bandwidth limit.)
 // AIEN_B200_GEMM_TC=tile | p256 pins the choice.
-static int tc_plan(int M, int N) {
+static int tc_plan(int M, int N, int ranges) {
     static int forced = -1;
     if (forced < 0) {
         const char* e = getenv("AIEN_B200_GEMM_TC");
         forced = e == nullptr ? 1 : (!strcmp(e, "tile") ? 0 : (!strcmp(e, "p256") ? 256 : 1));
     }
     if (forced != 1) return forced;
-    const long mt = (M + TC_BM - 1) / TC_BM;
-    return mt * ((N + 255) / 256) >= tc_num_sms() ? 256 : 0;
+    const long units = (long)((M + TC_BM - 1) / TC_BM) * ((N + 255) / 256) * ranges;
+    if (units >= tc_num_sms()) return 256;
+    return (M > 64 && N >= 256 && 5 * units >= 3 * tc_num_sms()) ? 256 : 0;
 }
 
 static int tc_a_rows(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }
@@ -439,9 +463,9 @@ AIEN_API int aien_gemm_tc(const void* A, long lda, const void* W, long ldw, void
     if ((lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return AIEN_E_ALIGN;
     if (epilogue == 1 && (N & 15)) return AIEN_E_SHAPE;
     if ((M + TC_BM - 1) / TC_BM > 2147483647 / 1 || (N + 95) / 96 > 65535) return AIEN_E_SHAPE;
-    if (splits == 1 && (epilogue == 0 || epilogue == 1)) {
-        const int plan = tc_plan(M, N);
-#define TCP_CASE(BNV, EPIV, T) return launch_tc_persistent<BNV, EPIV, T>(A, lda, W, ldw, out, ldc, M, N, K, stream)
+    if (epilogue == 0 || epilogue == 1) {
+        const int plan = tc_plan(M, N, aien_gemm_tc_ranges(K, splits));
+#define TCP_CASE(BNV, EPIV, T) return launch_tc_persistent<BNV, EPIV, T>(A, lda, W, ldw, out, ldc, M, N, K, splits, part_stride, stream)
         if (plan == 256) {
             if (epilogue == 0 && c_dt == AIEN_DT_BF16) TCP_CASE(256, 0, __nv_bfloat16);
             if (epilogue == 0 && c_dt == AIEN_DT_F32) TCP_CASE(256, 0, float);

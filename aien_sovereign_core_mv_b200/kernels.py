@@ -491,6 +491,13 @@ def gemm_tc_ranges(K_: int, splits: int) -> int:
 def gemm_tc_splits(M: int, N: int, K_: int) -> int:
     """Ranges of K for a product with few rows: enough CTAs to occupy the GPU (148 SMs, two CTAs
     each) when the tile grid alone is small.  Depends on the shapes only."""
+    if M > 64 and N >= 256:
+        # the persistent kernel with 128 x 256 tiles: as many ranges as still give every range 8 k-blocks
+        # and every SM at most one unit
+        tiles = ((M + 127) // 128) * ((N + 255) // 256)
+        if tiles >= 148:
+            return 1
+        return gemm_tc_ranges(K_, max(1, min(4, 148 // tiles, K_ // 512)))
     tiles = ((M + 127) // 128) * ((N + 127) // 128)
     if tiles >= 148:
         return 1

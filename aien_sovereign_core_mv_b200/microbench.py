@@ -52,14 +52,22 @@ def gemv_case(n: int, k: int, m: int, epilogue: int, reps: int = 20) -> None:
     print(f"gemv[{K.GEMV_IMPL}] N={n} K={k} M={m} epilogue={epilogue}: {us:8.2f} us  {n * k * 2 / us / 1e3:7.0f} GB/s of weights", flush=True)
 
 
-def gemm_case(m: int, n: int, k: int, epilogue: int, reps: int = 10) -> None:
+def gemm_case(m: int, n: int, k: int, epilogue: int, reps: int = 10, splits: int = 1) -> None:
+    """splits 1: bfloat16 output; > 1: float32 partial products over that many ranges of K; -1: as many
+    ranges as the engine asks for when its consumer can add partial products (kernels.gemm_tc_splits)."""
     w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
     a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
-    out = torch.empty(m, n // 2 if epilogue else n, device="cuda", dtype=torch.bfloat16)
+    if splits < 0:
+        splits = K.gemm_tc_splits(m, n, k)
+    ranges = K.gemm_tc_ranges(k, splits) if splits > 1 else 1
+    if ranges > 1:
+        out = torch.empty(ranges, m, n, device="cuda", dtype=torch.float32)
+    else:
+        out = torch.empty(m, n // 2 if epilogue else n, device="cuda", dtype=torch.bfloat16)
     for _ in range(3):
         K.gemm_tc(a, w, out, epilogue=epilogue)
     us = _time_graph(lambda i: K.gemm_tc(a, w, out, epilogue=epilogue), reps)
-    print(f"gemm_tc M={m} N={n} K={k} epilogue={epilogue}: {us:9.1f} us  {2.0 * m * n * k / us / 1e6:7.1f} TFLOP/s  (error flag {K.gemm_tc_error()})", flush=True)
+    print(f"gemm_tc M={m} N={n} K={k} epilogue={epilogue} ranges={ranges}: {us:9.1f} us  {2.0 * m * n * k / us / 1e6:7.1f} TFLOP/s  (error flag {K.gemm_tc_error()})", flush=True)
 
 
 def _paged_cache(batch: int, ctx: int, nkv: int, hd: int, page: int):
@@ -175,6 +183,7 @@ def main(argv=None) -> int:
     p = sub.add_parser("gemm")
     p.add_argument("--m", type=int, default=2048); p.add_argument("--n", type=int, default=24576)
     p.add_argument("--k", type=int, default=4096); p.add_argument("--epilogue", type=int, default=0)
+    p.add_argument("--splits", type=int, default=1, help="ranges of K into float32 partial products; -1: what the engine would ask for")
     p = sub.add_parser("attn-decode")
     p.add_argument("--batch", type=int, default=1); p.add_argument("--ctx", type=int, default=1030)
     p.add_argument("--impl", default="stream", choices=["stream", "direct"]); p.add_argument("--page", type=int, default=16)
@@ -193,7 +202,7 @@ def main(argv=None) -> int:
     if args.case == "gemv":
         gemv_case(args.n, args.k, args.m, args.epilogue)
     elif args.case == "gemm":
-        gemm_case(args.m, args.n, args.k, args.epilogue)
+        gemm_case(args.m, args.n, args.k, args.epilogue, splits=args.splits)
     elif args.case == "attn-decode":
         attn_decode_case(args.batch, args.ctx, page=args.page, impl=args.impl)
     elif args.case == "attn-prefill":

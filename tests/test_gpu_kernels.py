@@ -787,7 +787,10 @@ def test_gemv_stream_against_direct(K, M, N, K_, monkeypatch):
         H.assert_close(out.float().cpu().numpy(), ref, 1e-2, "stream gemv + swiglu")
 
 
-@pytest.mark.parametrize("M,N,K_,splits", [(64, 4096, 4096, 4), (17, 130, 1032, 8), (100, 256, 576, 4), (128, 384, 12288, 8)])
+# the last four take the persistent kernel with 128 x 256 tiles, one unit per (range of K, tile): a narrow product with long K
+# (40 tiles x 3 ranges), ragged edges in M, N and K, more units than SMs, and a last range shorter than the others
+@pytest.mark.parametrize("M,N,K_,splits", [(64, 4096, 4096, 4), (17, 130, 1032, 8), (100, 256, 576, 4), (128, 384, 12288, 8),
+                                           (512, 2560, 4096, 3), (536, 2570, 9736, 3), (1100, 2584, 1160, 4), (300, 2000, 1992, 3)])
 def test_gemm_tensor_core_split_k(K, M, N, K_, splits):
     g = torch.Generator().manual_seed(M + N)
     a = torch.randn(M, K_, generator=g).to(torch.bfloat16).cuda()
@@ -801,6 +804,7 @@ def test_gemm_tensor_core_split_k(K, M, N, K_, splits):
     want = (a.double().cpu() @ w.double().cpu().T).numpy()
     H.assert_close(parts.sum(0).cpu().numpy(), want, 2e-5, f"tc gemm split-K {M}x{N}x{K_}/{ranges}")
     assert K.gemm_tc_splits(2048, 4096, 4096) == 1 and K.gemm_tc_splits(64, 4096, 4096) > 1
+    assert K.gemm_tc_splits(512, 2560, 4096) == 3 and K.gemm_tc_splits(512, 6144, 2560) == 1
 
 
 @pytest.mark.parametrize("nq,nkv,hd,page,window,norm", [(8, 2, 128, 16, 0, True), (6, 3, 48, 8, 0, True), (5, 1, 80, 16, 0, False),
