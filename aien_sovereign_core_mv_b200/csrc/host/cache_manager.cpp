@@ -289,8 +289,12 @@ void CacheManager::free_request(int64_t id) {
             if (r.groups[g].state_slot >= 0) drop_page(g, r.groups[g].state_slot);
             continue;
         }
-        for (int page : r.groups[g].pages)
-            if (page >= 0) drop_page(g, page);
+        // last page first: the free list is a stack, so the pages come out again in the order the
+        // request held them, and a request that held a run of consecutive pages hands on a run
+        // (kernels fetch consecutive pages with one copy)
+        const std::vector<int>& pages = r.groups[g].pages;
+        for (auto it = pages.rbegin(); it != pages.rend(); ++it)
+            if (*it >= 0) drop_page(g, *it);
     }
     free_rows_.push_back(r.row);
     requests_.erase(id);

@@ -8,9 +8,13 @@
 // so every key/value block it brings into shared memory is used twice.  Ten warps:
 //   warps 0-3   softmax of head A: thread r owns query row r (tensor-memory lane r)
 //   warps 4-7   softmax of head B
-//   warp 8      producer: TMA copies of Q (once) and of the K and V blocks, page by page through
-//               the block table, into a ring of shared-memory slots (absent pages are fetched at an
-//               out-of-range coordinate, which fills zeros)
+//   warp 8      producer: TMA copies of Q (once) and of the K and V blocks through the block table
+//               into a ring of shared-memory slots.  Pages that lie one after the other in the
+//               pool are fetched together: a block of 128 keys whose pages are all consecutive is
+//               one copy, otherwise every aligned run of 2, 4, ... consecutive pages is one (a copy
+//               of one 16-token page moves 2 KB and costs about as much to issue as one of 32 KB:
+//               a block fetched page by page takes longer to request than to multiply).  Absent
+//               pages are fetched at an out-of-range coordinate, which fills zeros
 //   warp 9      allocates tensor memory; one lane issues tcgen05.mma
 // Per block of 128 keys (aligned to absolute positions) and per head:
 //   S = Q K^T         M 128 x N 128 x K head size; Q and K are K-major tiles; S in tensor memory
@@ -58,13 +62,21 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
+// The cache seen through boxes of 1, 2, 4, ... pages of rows by 64 columns (m[k]: page_size << k
+// rows), and through one box of 128 rows by the whole head (blk; three-dimensional, chunk-major in
+// shared memory as the slots are laid out).
+struct PtMaps {
+    CUtensorMap m[5];
+    CUtensorMap blk;
+};
+
 template <int HD>
 __global__ void __launch_bounds__(PT_THREADS, 1)
-prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                  const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int max_blocks,
+prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ PtMaps maps_k,
+                  const __grid_constant__ PtMaps maps_v, const int* __restrict__ block_table, int max_blocks,
                   const int* __restrict__ q_start, const int* __restrict__ ctx_len, const int* __restrict__ tile_seq,
                   const int* __restrict__ tile_q0, int num_tiles, __nv_bfloat16* __restrict__ out, long out_stride,
-                  int nq, int nkv, int page_size, int window, float scale_log2e, int cache_rows, int heads_per_cta) {
+                  int nq, int nkv, int page_size, int window, float scale_log2e, int cache_rows, int heads_per_cta, int big_boxes) {
     using S = PtShape<HD>;
     extern __shared__ uint8_t pt_smem[];
     const uint32_t base = (smem_u32(pt_smem) + 1023u) & ~1023u;
@@ -135,16 +147,33 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             const int kb = kb_begin + (item >> 1);
             if (lane == 0) mbar_expect_tx(kv_full0 + 8 * slot, S::SLOT_BYTES);
             __syncwarp();
+            int page = -1;
             if (lane < pages_per_block) {
                 const int key0 = kb * PT_BN + lane * page_size;
                 const int blk = key0 / page_size;
-                int page = -1;
                 if (key0 <= pos_last && key0 + page_size > first && blk < max_blocks) page = bt[blk];
+            }
+            // lane i's page continues lane i-1's in the pool; the largest aligned group of 2, 4, ... pages
+            // around this lane whose pages all continue one another is fetched by its first lane
+            const int prev = __shfl_up_sync(0xffffffffu, page, 1);
+            const uint32_t links = __ballot_sync(0xffffffffu, lane > 0 && lane < pages_per_block && page >= 0 && prev >= 0 && page == prev + 1);
+            int g = 1, level = 0;
+            for (int gg = 2, lv = 1; gg <= pages_per_block; gg <<= 1, ++lv) {
+                const int a = lane & ~(gg - 1);
+                const uint32_t need = (((gg >= 32 ? 0u : (1u << gg)) - 1u) << a) & ~(1u << a);
+                if ((links & need) != need) break;
+                g = gg; level = lv;
+            }
+            if (lane < pages_per_block && (lane & (g - 1)) == 0) {
                 const int row = page >= 0 ? page * page_size : cache_rows;     // out of range: zeros
-                const CUtensorMap* map = (item & 1) ? &map_v : &map_k;
+                const PtMaps& maps = (item & 1) ? maps_v : maps_k;
                 const uint32_t dst = sKV + slot * S::SLOT_BYTES + lane * page_size * 128;
-                for (int c = 0; c < S::CHUNKS; ++c)
-                    tma_load_2d(dst + c * (PT_BN * 128), map, kv_full0 + 8 * slot, kvh * HD + c * 64, row);
+                if (g == pages_per_block && big_boxes) {
+                    tma_load_3d(dst, &maps.blk, kv_full0 + 8 * slot, 0, row, kvh * S::CHUNKS);      // the whole block in one copy
+                } else {
+                    for (int c = 0; c < S::CHUNKS; ++c)
+                        tma_load_2d(dst + c * (PT_BN * 128), &maps.m[level], kv_full0 + 8 * slot, kvh * HD + c * 64, row);
+                }
             }
         }
     } else if (warp == 9) {
@@ -315,7 +344,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 }
 
 template <int HD>
-static int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const int* bt, int max_blocks,
+static int launch_prefill_tc(const CUtensorMap& mq, const PtMaps& mk, const PtMaps& mv, int big_boxes, const int* bt, int max_blocks,
                              const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_q0, int num_tiles,
                              void* out, long out_stride, int nq, int nkv, int page_size, int window, float scale, int cache_rows,
                              cudaStream_t stream) {
@@ -328,13 +357,21 @@ static int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mk, const
     const int group = nq / nkv;
     int sms = 148, dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    // pairs of heads halve the K/V traffic; with fewer paired CTAs than SMs, one head per CTA is faster
-    const int heads_per_cta = (group >= 2 && (long)num_tiles * nkv * ((group + 1) / 2) >= sms) ? 2 : 1;
+    // Two heads of a kv head per CTA halve the K/V traffic and let the tensor core work for one head
+    // under the other's softmax: a key block then takes 2.5 us for both heads, against 2.3 us for the
+    // single head of a CTA that has only one.  What decides is the number of waves either way: 512
+    // tokens are 128 single-head CTAs, one wave, 72 us against 82 us in pairs; 1,024 tokens are 256,
+    // two waves, 125 us against 84 us for 128 pairs (32 heads of 128, a portion at offset 3,072).
+    int heads_per_cta = 1;
+    if (group >= 2) {
+        const long single = (long)num_tiles * nkv * group, paired = (long)num_tiles * nkv * ((group + 1) / 2);
+        if (23 * ((single + sms - 1) / sms) > 25 * ((paired + sms - 1) / sms)) heads_per_cta = 2;
+    }
     const long ctas = (long)num_tiles * nkv * ((group + heads_per_cta - 1) / heads_per_cta);
     if (ctas > 2147483647L) return AIEN_E_SHAPE;
     launch_chain(kern, dim3((unsigned)ctas), dim3(PT_THREADS), (size_t)PtShape<HD>::SMEM, stream, mq, mk, mv, bt, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles,
                                                                      (__nv_bfloat16*)out, out_stride, nq, nkv, page_size, window,
-                                                                     scale * 1.4426950408889634f, cache_rows, heads_per_cta);
+                                                                     scale * 1.4426950408889634f, cache_rows, heads_per_cta, big_boxes);
     return launch_status();
 }
 
@@ -360,16 +397,28 @@ AIEN_API int aien_paged_attention_prefill_tc(
     if ((q_stride & 7) || (out_stride & 7) || ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) ||
         ((uintptr_t)out & 15))
         return AIEN_E_ALIGN;
-    CUtensorMap mq, mk, mv;
+    CUtensorMap mq;
+    static PtMaps mk, mv;                      // large: kept out of the stack; filled for every launch
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
     const uint64_t kv_cols = (uint64_t)nkv * hd;
-    if (!make_map(&mq, q, (uint64_t)q_rows, (uint64_t)nq * hd, (uint64_t)q_stride, 64, PT_BM) ||
-        !make_map(&mk, k_cache, (uint64_t)cache_rows, kv_cols, kv_cols, 64, (uint32_t)page_size) ||
-        !make_map(&mv, v_cache, (uint64_t)cache_rows, kv_cols, kv_cols, 64, (uint32_t)page_size))
-        return AIEN_E_STATE;
+    if (!make_map(&mq, q, (uint64_t)q_rows, (uint64_t)nq * hd, (uint64_t)q_stride, 64, PT_BM)) return AIEN_E_STATE;
+    for (int lv = 0; lv < 5; ++lv) {
+        const uint32_t rows = (uint32_t)page_size << lv;
+        if (rows > (uint32_t)PT_BN) { mk.m[lv] = mk.m[0]; mv.m[lv] = mv.m[0]; continue; }
+        if (!make_map(&mk.m[lv], k_cache, (uint64_t)cache_rows, kv_cols, kv_cols, 64, rows) ||
+            !make_map(&mv.m[lv], v_cache, (uint64_t)cache_rows, kv_cols, kv_cols, 64, rows))
+            return AIEN_E_STATE;
+    }
+    // one copy for a whole block of 128 keys, when the pool has that many rows at all
+    const int big_boxes = cache_rows >= PT_BN &&
+                          make_map_chunked(&mk.blk, k_cache, (uint64_t)cache_rows, kv_cols, kv_cols, PT_BN, (uint32_t)(hd / 64)) &&
+                          make_map_chunked(&mv.blk, v_cache, (uint64_t)cache_rows, kv_cols, kv_cols, PT_BN, (uint32_t)(hd / 64)) ? 1 : 0;
+    if (!big_boxes) { mk.blk = mk.m[0]; mv.blk = mv.m[0]; }
     if (hd == 64)
-        return launch_prefill_tc<64>(mq, mk, mv, block_table, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles, out, out_stride,
+        return launch_prefill_tc<64>(mq, mk, mv, big_boxes, block_table, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles, out, out_stride,
                                      nq, nkv, page_size, window, scale, cache_rows, stream);
-    return launch_prefill_tc<128>(mq, mk, mv, block_table, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles, out, out_stride,
+    return launch_prefill_tc<128>(mq, mk, mv, big_boxes, block_table, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles, out, out_stride,
                                   nq, nkv, page_size, window, scale, cache_rows, stream);
 }
 

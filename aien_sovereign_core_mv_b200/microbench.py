@@ -70,14 +70,23 @@ def gemm_case(m: int, n: int, k: int, epilogue: int, reps: int = 10, splits: int
     print(f"gemm_tc M={m} N={n} K={k} epilogue={epilogue} ranges={ranges}: {us:9.1f} us  {2.0 * m * n * k / us / 1e6:7.1f} TFLOP/s  (error flag {K.gemm_tc_error()})", flush=True)
 
 
-def _paged_cache(batch: int, ctx: int, nkv: int, hd: int, page: int):
+def _paged_cache(batch: int, ctx: int, nkv: int, hd: int, page: int, layout: str = "shuffled"):
+    """layout: where a request's pages lie in the pool.  "shuffled": anywhere (the worst case);
+    "sequential": one after the other, as a fresh pool hands them out; "runs4": shuffled runs of 4."""
     pages_per = (ctx + page - 1) // page
     n_pages = batch * pages_per + 4
     kc = torch.randn(n_pages * page, nkv, hd, device="cuda", dtype=torch.bfloat16)
     vc = torch.randn_like(kc)
     width = max(256, pages_per + 1)
     bt = torch.full((batch, width), -1, dtype=torch.int32)
-    bt[:, :pages_per] = torch.randperm(n_pages)[:batch * pages_per].view(batch, pages_per).to(torch.int32)
+    if layout == "sequential":
+        order = torch.arange(batch * pages_per)
+    elif layout == "runs4":
+        runs = torch.randperm(n_pages // 4)[:(batch * pages_per + 3) // 4]
+        order = (runs[:, None] * 4 + torch.arange(4)[None]).reshape(-1)[:batch * pages_per]
+    else:
+        order = torch.randperm(n_pages)[:batch * pages_per]
+    bt[:, :pages_per] = order.view(batch, pages_per).to(torch.int32)
     return kc, vc, bt.cuda(), width
 
 
@@ -105,9 +114,9 @@ def attn_decode_case(batch: int, ctx: int, nq: int = 32, nkv: int = 8, hd: int =
 
 
 def attn_prefill_case(tokens: int, offset: int = 0, nq: int = 32, nkv: int = 8, hd: int = 128, page: int = 16, reps: int = 10,
-                      impl: str = "tc") -> None:
+                      impl: str = "tc", layout: str = "shuffled") -> None:
     ctx = offset + tokens
-    kc, vc, bt, width = _paged_cache(1, ctx, nkv, hd, page)
+    kc, vc, bt, width = _paged_cache(1, ctx, nkv, hd, page, layout)
     q = torch.randn(tokens, nq * hd, device="cuda", dtype=torch.bfloat16)
     out = torch.empty_like(q)
     i32 = lambda a: torch.tensor(a, dtype=torch.int32, device="cuda")
@@ -121,7 +130,7 @@ def attn_prefill_case(tokens: int, offset: int = 0, nq: int = 32, nkv: int = 8, 
         run()
     us = _time_graph(run, reps)
     flops = 4.0 * nq * hd * (tokens * (tokens + 1) / 2 + tokens * offset)
-    print(f"attn-prefill[{impl}] tokens={tokens} offset={offset} page={page} ({nq}q/{nkv}kv x {hd}): {us:8.1f} us  {flops / us / 1e6:7.1f} TFLOP/s"
+    print(f"attn-prefill[{impl}] tokens={tokens} offset={offset} page={page} {layout} ({nq}q/{nkv}kv x {hd}): {us:8.1f} us  {flops / us / 1e6:7.1f} TFLOP/s"
           f"  (error flag {K.attention_prefill_tc_error()})", flush=True)
 
 
@@ -190,6 +199,7 @@ def main(argv=None) -> int:
     p = sub.add_parser("attn-prefill")
     p.add_argument("--tokens", type=int, default=2048); p.add_argument("--offset", type=int, default=0)
     p.add_argument("--impl", default="tc", choices=["tc", "mma"]); p.add_argument("--page", type=int, default=16)
+    p.add_argument("--layout", default="shuffled", choices=["shuffled", "sequential", "runs4"], help="where the request's pages lie in the pool")
     p = sub.add_parser("qk")
     p.add_argument("--tokens", type=int, default=2048); p.add_argument("--parts", type=int, default=0)
     p = sub.add_parser("sample")
@@ -206,7 +216,7 @@ def main(argv=None) -> int:
     elif args.case == "attn-decode":
         attn_decode_case(args.batch, args.ctx, page=args.page, impl=args.impl)
     elif args.case == "attn-prefill":
-        attn_prefill_case(args.tokens, args.offset, page=args.page, impl=args.impl)
+        attn_prefill_case(args.tokens, args.offset, page=args.page, impl=args.impl, layout=args.layout)
     elif args.case == "qk":
         qk_case(args.tokens, args.parts)
     elif args.case == "sample":
