@@ -214,6 +214,54 @@ def serving_workload() -> int:
     return 0
 
 
+def mixed_step_workload() -> int:
+    """One step of the kind a chunked-prefill server runs all day, timed alone on the device: a
+    512-token portion of a prompt at offset 2,048 beside 24 requests that decode one token each at
+    contexts of 500 tokens (Qwen3-4B shape, random bfloat16 weights, seed 3).  The timed step lies
+    between cudaProfilerStart and cudaProfilerStop, so `ncu --profile-from-start off` lists its
+    launches and nothing else."""
+    import torch
+    from aien_sovereign_core_mv_b200 import Engine, EngineConfig
+    from aien_sovereign_core_mv_b200 import kernels as K
+    ec = EngineConfig(dtype="bfloat16", page_size=16, max_cache_tokens=40 * 1024, max_requests=32, max_batch_tokens=1024,
+                      max_context=8192, max_batch_size=32, max_prefill_tokens=512, prefill_chunk_size=512)
+    eng = Engine.from_config(QWEN3_4B, seed=3, engine_config=ec, init_std=0.02, device_init=True)
+    V = QWEN3_4B["vocab_size"]
+    toks = lambda n, s: [(7 * i + s) % V for i in range(n)]
+    decodes, portion, offset, ctx = 24, 512, 1024, 500
+    for r in range(0, decodes, 2):
+        eng.step([(r, toks(ctx, r), []), (r + 1, toks(ctx, r + 1), [])])
+    for k in range(offset // portion):
+        eng.step([(500, toks(portion, k), [])])
+
+    def mixed(s):
+        return eng.step([(r, [s + r], [0]) for r in range(decodes)] + [(500, toks(portion, 9 + s), [portion - 1])])
+
+    times = []
+    for rep in range(5):            # every repetition moves the portion 512 tokens on (the first writes the launches
+        torch.cuda.synchronize()    # down, the others re-issue them); the third, at offset 2,048, is the profiled one
+        if rep == 2:
+            torch.cuda.profiler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        mixed(rep)
+        e1.record()
+        torch.cuda.synchronize()
+        if rep == 2:
+            torch.cuda.profiler.stop()
+        times.append(round(e0.elapsed_time(e1), 3))
+    eng.check_waits()
+    wait_errors = sum(1 for w in K.read_wait_errors() if w != 0)
+    print(json.dumps({
+        "metric": "mixed_step_ms", "value": times[2], "unit": "ms", "n_gpus": 1, "higher_is_better": False, "dtype": "bf16",
+        "data": "synthetic", "impl": "ours", "steps_ms": times, "wait_errors": wait_errors,
+        "config": {"model": "Qwen3-4B shape, random weights", "layers": 36, "hidden": 2560, "heads": 32, "kv_heads": 8, "head_dim": 128,
+                   "intermediate": 9728, "vocab": 151936, "portion_tokens": portion, "portion_offset": "1024 + 512 per step; value: the step at 2048",
+                   "decoding_requests": decodes, "decode_context": ctx, "page_size": 16, "seed": 3},
+    }))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -225,10 +273,11 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "llama3_8b", "serving"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "llama3_8b", "serving", "mixed_step"],
                     help="decode: the headline decode-step measurement (Qwen3-8B shape, 1,024-token prompts); llama3_8b: the same "
                          "line for the Llama-3-8B shape, 16 requests at contexts ending at 8,192 tokens; serving: continuous batching "
-                         "of 32 requests on the Qwen3-4B shape (prompts of 64..4096 tokens, portions of 512, 256 new tokens each)")
+                         "of 32 requests on the Qwen3-4B shape (prompts of 64..4096 tokens, portions of 512, 256 new tokens each); "
+                         "mixed_step: one step of a 512-token portion beside 24 decoding requests on that shape, timed alone")
     ap.add_argument("--fill", default="prefill", choices=["prefill", "cache"],
                     help="how requests get their prompt: real prefill, or (development only) cache pages "
                          "filled with random keys/values without running the model")
@@ -244,6 +293,8 @@ def main() -> int:
     warmup, steps = max(3, args.warmup), max(1, args.steps)
     if args.workload == "serving":
         return serving_workload()
+    if args.workload == "mixed_step":
+        return mixed_step_workload()
 
     import numpy as np
     import torch
