@@ -9,32 +9,39 @@
 //   warps 0-3   softmax of head A: thread r owns query row r (tensor-memory lane r)
 //   warps 4-7   softmax of head B
 //   warp 8      producer: TMA copies of Q (once) and of the K and V blocks through the block table
-//               into a ring of shared-memory slots.  Pages that lie one after the other in the
-//               pool are fetched together: a block of 128 keys whose pages are all consecutive is
-//               one copy, otherwise every aligned run of 2, 4, ... consecutive pages is one (a copy
-//               of one 16-token page moves 2 KB and costs about as much to issue as one of 32 KB:
-//               a block fetched page by page takes longer to request than to multiply).  Absent
-//               pages are fetched at an out-of-range coordinate, which fills zeros
-//   warp 9      allocates tensor memory; one lane issues tcgen05.mma
+//               into a ring of shared-memory slots (five of 32 KB at head size 128).  Pages that lie
+//               one after the other in the pool are fetched together: a block of 128 keys whose
+//               pages are all consecutive is one copy, otherwise every aligned run of 2, 4, ...
+//               consecutive pages is one (a copy of one 16-token page moves 2 KB and costs about as
+//               much to issue as one of 32 KB).  Absent pages are fetched at an out-of-range
+//               coordinate, which fills zeros.  The block table's entries are read one block ahead
+//   warp 9      allocates tensor memory; walks the schedule as a whole warp, one lane issues tcgen05.mma
 // Per block of 128 keys (aligned to absolute positions) and per head:
-//   S = Q K^T         M 128 x N 128 x K head size; Q and K are K-major tiles; S in tensor memory
+//   S = Q K^T         M 128 x N 128 x K head size; Q and K are K-major tiles in shared memory; S in
+//                     tensor memory
 //   softmax           each thread reads its row of S with tcgen05.ld, applies the causal/window
-//                     limits of its row, takes exponentials in float32 and writes P as bfloat16
-//                     into a swizzled K-major tile in shared memory
-//   O += P V          M 128 x N head size x K 128; V is used as stored ([key][dim]: an MN-major
-//                     tile); O accumulates in tensor memory over all blocks.  The exponentials
-//                     are taken against a reference maximum that follows the row's running
-//                     maximum only when that has grown by more than 8 (in log2 units); only then
-//                     is the row of O rescaled (tcgen05.ld, multiply, tcgen05.st), which after
-//                     the first blocks is rare
+//                     limits of its row, takes exponentials in float32 and writes P as bfloat16 back
+//                     into tensor memory (tcgen05.st), two values a column, over the first half of
+//                     the columns S came from
+//   O += P V          M 128 x N head size x K 128; P is the A operand straight from tensor memory,
+//                     V is used as stored ([key][dim]: an MN-major tile in shared memory); O
+//                     accumulates in tensor memory over all blocks.  The exponentials are taken
+//                     against a reference maximum that follows the row's running maximum only when
+//                     that has grown by more than 8 (in log2 units); only then is the row of O
+//                     rescaled (tcgen05.ld, multiply, tcgen05.st), which after the first blocks is rare
+// Shared memory's bandwidth is what this kernel would otherwise run into: a 128 x 128 x 16 product
+// with both operands there reads 8 KB in the 64 cycles it takes, all the 128 bytes a cycle an SM has;
+// P written to and read back from shared memory came on top of that (and took two 32 KB buffers that
+// are now two more slots of the ring).
 // The issue order alternates the heads (PV_A(j), QK_A(j+1), PV_B(j), QK_B(j+1)), so that the
-// tensor core works for one head while the other head's softmax runs.
+// tensor core works for one head while the other head's softmax runs.  Tensor memory's 512 columns
+// are full with that (S and O of two heads), so a head's chain softmax -> PV -> QK -> softmax cannot
+// be shortened by computing scores ahead.
 // A CTA with one head only (steps with few tiles, see launch_prefill_tc) uses what the second head
 // leaves free to run ahead of itself instead: scores alternate between two regions of tensor memory
-// and probabilities between two buffers, so S(j+1) = Q K(j+1)^T is computed while the softmax of
-// block j runs (only P V waits for the probabilities), and the second head's query buffer is a
-// fourth slot of the K/V ring.  Blocks then follow one another at the softmax's pace, without the
-// score product and its hand-over in between (512 tokens at offset 3,584: 73 -> 55 us).
+// (each with its probabilities), so S(j+1) = Q K(j+1)^T is computed while the softmax of block j runs
+// (only P V waits for the probabilities), and the second head's query buffer is one more slot of the
+// K/V ring.  Blocks then follow one another at the softmax's pace.
 // Formulas: crates/aien-inference-abi/src/backend.rs:280-306, scale 1/sqrt(head_dim).
 //
 // Every wait is bounded; one that runs out records a code (aien_attention_prefill_tc_error) and
@@ -47,15 +54,20 @@
 
 namespace aien {
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 constexpr int PT_BM = 128, PT_BN = 128, PT_THREADS = 320;
 constexpr int PT_SMEM_MAX = 227 * 1024;
 
 template <int HD> struct PtShape {
     static constexpr int CHUNKS = HD / 64;                       // 64-column (128-byte) chunks of a row
     static constexpr int Q_BYTES = PT_BM * HD * 2;               // one head's query tile
-    static constexpr int P_BYTES = PT_BM * PT_BN * 2;            // one head's probabilities
     static constexpr int SLOT_BYTES = PT_BN * HD * 2;            // one K or V block
-    static constexpr int FIXED = 2 * Q_BYTES + 2 * P_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr int FIXED = 2 * Q_BYTES + 1024 /*align*/ + 256 /*barriers*/;
     static constexpr int SLOTS_FIT = (PT_SMEM_MAX - FIXED) / SLOT_BYTES;
     static constexpr int SLOTS = SLOTS_FIT > 6 ? 6 : SLOTS_FIT;
     static constexpr int SMEM = FIXED + SLOTS * SLOT_BYTES;
@@ -86,7 +98,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     using S = PtShape<HD>;
     extern __shared__ uint8_t pt_smem[];
     const uint32_t base = (smem_u32(pt_smem) + 1023u) & ~1023u;
-    const uint32_t sQ = base, sP = sQ + 2 * S::Q_BYTES, sKV = sP + 2 * S::P_BYTES;
+    const uint32_t sQ = base, sKV = sQ + 2 * S::Q_BYTES;
     const uint32_t bars = sKV + S::SLOTS * S::SLOT_BYTES;
     const uint32_t q_full = bars, kv_full0 = bars + 8, kv_free0 = kv_full0 + 8 * (S::SLOTS + 1);
     const uint32_t s_ready0 = kv_free0 + 8 * (S::SLOTS + 1), p_ready0 = s_ready0 + 16, o_ready0 = p_ready0 + 16;
@@ -139,6 +151,24 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
     if (warp == 8) {
         // ------------------------------------------------------------------ producer
+        const int pages_per_block = PT_BN / page_size;
+        const int* bt = block_table + (size_t)s * max_blocks;
+        auto item_is_v = [&](int item) { return single ? (item >= 2 && (item & 1) == 0) || item == 2 * nb - 1 : (bool)(item & 1); };
+        auto item_block = [&](int item) {
+            return kb_begin + (single ? (item_is_v(item) ? (item == 2 * nb - 1 ? nb - 1 : item / 2 - 1) : (item + 1) / 2) : (item >> 1));
+        };
+        // this lane's page of a key block (-1: none); asked for one item ahead, so that the table's
+        // latency passes under the wait for a free slot
+        auto page_of = [&](int kb) {
+            int page = -1;
+            if (lane < pages_per_block) {
+                const int key0 = kb * PT_BN + lane * page_size;
+                const int blk = key0 / page_size;
+                if (key0 <= pos_last && key0 + page_size > first && blk < max_blocks) page = bt[blk];
+            }
+            return page;
+        };
+        int page_next = page_of(item_block(0));          // the table is this step's metadata, not the work of the kernel ahead
         // Queries and this step's rows of the caches come from the kernel ahead in the stream: with a
         // dependent launch everything above ran beside its tail, and no other warp touches global
         // memory before it has data from this one.
@@ -149,22 +179,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 for (int c = 0; c < S::CHUNKS; ++c)
                     tma_load_2d(sQ + h * S::Q_BYTES + c * (PT_BM * 128), &map_q, q_full, (head_a + h) * HD + c * 64, qs + q0);
         }
-        const int pages_per_block = PT_BN / page_size;
-        const int* bt = block_table + (size_t)s * max_blocks;
         for (int item = 0; item < 2 * nb; ++item) {                 // K0 V0 K1 V1 ...; one head alone: K0 K1 V0 K2 V1 ...
             const int slot = single ? item % NS1 : item % S::SLOTS;
             const int round = single ? item / NS1 : item / S::SLOTS;
+            const int page = page_next;
+            if (item + 1 < 2 * nb) page_next = page_of(item_block(item + 1));
             if (round > 0) mbar_wait(kv_free0 + 8 * slot, (round - 1) & 1, 1);
-            const bool is_v = single ? (item >= 2 && (item & 1) == 0) || item == 2 * nb - 1 : (item & 1);
-            const int kb = kb_begin + (single ? (is_v ? (item == 2 * nb - 1 ? nb - 1 : item / 2 - 1) : (item + 1) / 2) : (item >> 1));
+            const bool is_v = item_is_v(item);
             if (lane == 0) mbar_expect_tx(kv_full0 + 8 * slot, S::SLOT_BYTES);
             __syncwarp();
-            int page = -1;
-            if (lane < pages_per_block) {
-                const int key0 = kb * PT_BN + lane * page_size;
-                const int blk = key0 / page_size;
-                if (key0 <= pos_last && key0 + page_size > first && blk < max_blocks) page = bt[blk];
-            }
             // lane i's page continues lane i-1's in the pool; the largest aligned group of 2, 4, ... pages
             // around this lane whose pages all continue one another is fetched by its first lane
             const int prev = __shfl_up_sync(0xffffffffu, page, 1);
@@ -190,92 +213,83 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         }
     } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issue
-        if (lane == 0) {
+        // The whole warp walks the schedule and waits on the barriers, so that addresses and descriptors
+        // are the same in every lane (and cheap to form); one lane issues.
+        {
+            const bool issuer = lane == 0;
             const uint32_t idesc_qk = umma_idesc_bf16(PT_BM, PT_BN, false);
             const uint32_t idesc_pv = umma_idesc_bf16(PT_BM, HD, true);
-            auto issue_qk = [&](int h, int slot) {
-                const uint32_t a = sQ + h * S::Q_BYTES, b = sKV + slot * S::SLOT_BYTES;
-#pragma unroll
-                for (int kk = 0; kk < HD / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * (PT_BM * 128) + (kk & 3) * 32;
-                    umma_bf16(tS0 + h * PT_BN, make_desc_sw128(a + off), make_desc_sw128(b + off), idesc_qk, kk > 0 ? 1u : 0u);
-                }
-                umma_commit(s_ready0 + 8 * h);
-            };
-            auto issue_pv = [&](int h, int slot, bool first_block) {
-                const uint32_t a = sP + h * S::P_BYTES, b = sKV + slot * S::SLOT_BYTES;
-#pragma unroll
-                for (int kk = 0; kk < PT_BN / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * (PT_BM * 128) + (kk & 3) * 32;
-                    umma_bf16(tO0 + h * HD, make_desc_sw128(a + off), make_desc_sw128_mn(b + kk * 16 * 128, PT_BN * 128), idesc_pv, (kk > 0 || !first_block) ? 1u : 0u);
-                }
-                umma_commit(o_ready0 + 8 * h);
-            };
-            auto wait_item = [&](int item) {
-                mbar_wait(kv_full0 + 8 * (item % S::SLOTS), (item / S::SLOTS) & 1, 2);
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            };
-            auto wait_item1 = [&](int item) {                            // the same with the ring of a CTA with one head
-                mbar_wait(kv_full0 + 8 * (item % NS1), (item / NS1) & 1, 2);
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            };
-            mbar_wait(q_full, 0, 3);
-            if (single) {
-                // One head: scores of block j go to region j & 1 of tensor memory, probabilities to buffer
-                // j & 1, and the items come in the order they are used: K0 K1 V0 K2 V1 K3 ...
-                auto qk_to = [&](int buf, int slot) {                       // S[buf] = Q K^T
-                    const uint32_t a = sQ, b = slot_addr(slot);
+            const uint64_t desc_q0 = make_desc_sw128(sQ);
+            // S[region] = Q(head) K^T from the K block in the slot at `b`
+            auto qk = [&](int head, int region, uint32_t b, uint32_t bar) {
+                const uint64_t da = desc_q0 + (uint64_t)((head * S::Q_BYTES) >> 4), db = make_desc_sw128(b);
+                if (issuer) {
 #pragma unroll
                     for (int kk = 0; kk < HD / 16; ++kk) {
-                        const uint32_t off = (kk >> 2) * (PT_BM * 128) + (kk & 3) * 32;
-                        umma_bf16(tS0 + buf * PT_BN, make_desc_sw128(a + off), make_desc_sw128(b + off), idesc_qk, kk > 0 ? 1u : 0u);
+                        const uint64_t off = (uint64_t)(((kk >> 2) * (PT_BM * 128) + (kk & 3) * 32) >> 4);
+                        umma_bf16(tS0 + region * PT_BN, da + off, db + off, idesc_qk, kk > 0 ? 1u : 0u);
                     }
-                    umma_commit(s_ready0 + 8 * buf);
-                    umma_commit(kv_free0 + 8 * slot);
-                };
+                    umma_commit(bar);
+                }
+            };
+            // O[head] += P V: P from the first 64 columns of score region `region`, V from the slot at `b`
+            auto pv = [&](int head, int region, uint32_t b, bool first_block, uint32_t bar) {
+                const uint64_t db = make_desc_sw128_mn(b, PT_BN * 128);
+                if (issuer) {
+#pragma unroll
+                    for (int kk = 0; kk < PT_BN / 16; ++kk)
+                        umma_bf16_ts(tO0 + head * HD, tS0 + region * PT_BN + kk * 8, db + (uint64_t)((kk * 16 * 128) >> 4), idesc_pv, (kk > 0 || !first_block) ? 1u : 0u);
+                    umma_commit(bar);
+                }
+            };
+            auto commit = [&](uint32_t bar) { if (issuer) umma_commit(bar); };
+            // (data that TMA wrote is visible to the tensor core once the barrier has completed)
+            auto wait_item = [&](int item) { mbar_wait(kv_full0 + 8 * (item % S::SLOTS), (item / S::SLOTS) & 1, 2); };
+            auto wait_item1 = [&](int item) { mbar_wait(kv_full0 + 8 * (item % NS1), (item / NS1) & 1, 2); };   // the ring of a CTA with one head
+            mbar_wait(q_full, 0, 3);
+            if (single) {
+                // One head: scores of block j go to region j & 1 of tensor memory (and its probabilities
+                // back into that region), and the items come in the order they are used: K0 K1 V0 K2 V1 K3 ...
                 int item = 0;
-                wait_item1(item); qk_to(0, item % NS1); ++item;
-                if (nb > 1) { wait_item1(item); qk_to(1, item % NS1); ++item; }
+                wait_item1(item); qk(0, 0, slot_addr(item % NS1), s_ready0); commit(kv_free0 + 8 * (item % NS1)); ++item;
+                if (nb > 1) { wait_item1(item); qk(0, 1, slot_addr(item % NS1), s_ready0 + 8); commit(kv_free0 + 8 * (item % NS1)); ++item; }
                 for (int j = 0; j < nb; ++j) {
                     const int buf = j & 1;
-                    mbar_wait(p_ready0 + 8 * buf, (j >> 1) & 1, 4);          // P[buf] is written, S[buf] is read
                     wait_item1(item);
-                    {
-                        const uint32_t a = sP + buf * S::P_BYTES, b = slot_addr(item % NS1);
-#pragma unroll
-                        for (int kk = 0; kk < PT_BN / 16; ++kk) {
-                            const uint32_t off = (kk >> 2) * (PT_BM * 128) + (kk & 3) * 32;
-                            umma_bf16(tO0, make_desc_sw128(a + off), make_desc_sw128_mn(b + kk * 16 * 128, PT_BN * 128), idesc_pv, (kk > 0 || j > 0) ? 1u : 0u);
-                        }
-                        umma_commit(o_ready0);
-                        umma_commit(kv_free0 + 8 * (item % NS1));
-                    }
+                    mbar_wait(p_ready0 + 8 * buf, (j >> 1) & 1, 4);          // P[buf] is written
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    pv(0, buf, slot_addr(item % NS1), j == 0, o_ready0);
+                    commit(kv_free0 + 8 * (item % NS1));
                     ++item;
-                    if (j + 2 < nb) { wait_item1(item); qk_to(buf, item % NS1); ++item; }
+                    if (j + 2 < nb) { wait_item1(item); qk(0, buf, slot_addr(item % NS1), s_ready0 + 8 * buf); commit(kv_free0 + 8 * (item % NS1)); ++item; }
                 }
             } else {
-            wait_item(0);
-            issue_qk(0, 0);
-            if (has_b) issue_qk(1, 0);
-            umma_commit(kv_free0);
-            for (int j = 0; j < nb; ++j) {
-                const int v_item = 2 * j + 1, k_item = 2 * j + 2;
-                const bool more = j + 1 < nb;
-                mbar_wait(p_ready0, j & 1, 4);
-                wait_item(v_item);
-                issue_pv(0, v_item % S::SLOTS, j == 0);
-                if (more) { wait_item(k_item); issue_qk(0, k_item % S::SLOTS); }
-                if (has_b) {
-                    mbar_wait(p_ready0 + 8, j & 1, 5);
+                wait_item(0);
+                qk(0, 0, sKV, s_ready0);
+                if (has_b) qk(1, 1, sKV, s_ready0 + 8);
+                commit(kv_free0);
+                for (int j = 0; j < nb; ++j) {
+                    const int v_item = 2 * j + 1, k_item = 2 * j + 2;
+                    const bool more = j + 1 < nb;
+                    const uint32_t v_at = sKV + (v_item % S::SLOTS) * S::SLOT_BYTES, k_at = sKV + (k_item % S::SLOTS) * S::SLOT_BYTES;
+                    // the blocks themselves have long arrived: seen to before the probabilities are awaited
+                    wait_item(v_item);
+                    if (more) wait_item(k_item);
+                    mbar_wait(p_ready0, j & 1, 4);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    issue_pv(1, v_item % S::SLOTS, j == 0);
+                    pv(0, 0, v_at, j == 0, o_ready0);
+                    if (more) qk(0, 0, k_at, s_ready0);
+                    if (has_b) {
+                        mbar_wait(p_ready0 + 8, j & 1, 5);
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        pv(1, 1, v_at, j == 0, o_ready0 + 8);
+                    }
+                    commit(kv_free0 + 8 * (v_item % S::SLOTS));
+                    if (more) {
+                        if (has_b) qk(1, 1, k_at, s_ready0 + 8);
+                        commit(kv_free0 + 8 * (k_item % S::SLOTS));
+                    }
                 }
-                umma_commit(kv_free0 + 8 * (v_item % S::SLOTS));
-                if (more) {
-                    if (has_b) issue_qk(1, k_item % S::SLOTS);
-                    umma_commit(kv_free0 + 8 * (k_item % S::SLOTS));
-                }
-            }
             }
         }
     } else if (warp < 4 || has_b) {
@@ -285,7 +299,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
         // one head alone alternates between two score regions and two probability buffers (h is 0 then)
         const uint32_t tS_base = tS0 + h * PT_BN + lane_off, tO = tO0 + h * HD + lane_off;
-        const uint32_t p_row_base = sP + h * S::P_BYTES + r * 128;
         const int hi = r < rows ? pos0 + r : -1;                                 // last key this row sees
         const int lo = (window > 0 && hi - window + 1 > 0) ? hi - window + 1 : 0;
         // m_ref: the maximum the exponentials are taken against.  It follows the row's running
@@ -296,23 +309,32 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         for (int j = 0; j < nb; ++j) {
             const int key_base = (kb_begin + j) * PT_BN;
             const int buf = single ? (j & 1) : 0;
-            const uint32_t tS = tS_base + buf * PT_BN, p_row = p_row_base + buf * S::P_BYTES;
+            const uint32_t tS = tS_base + buf * PT_BN;
             mbar_wait(s_ready0 + 8 * (single ? buf : h), (single ? (j >> 1) : j) & 1, 6);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t v[PT_BN];
 #pragma unroll
             for (int c0 = 0; c0 < PT_BN; c0 += 32) tmem_ld32(tS + c0, v + c0);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (key_base + PT_BN - 1 > hi || key_base < lo) {
+            if (key_base + PT_BN - 1 > hi) {                                     // the block on the diagonal: columns beyond hi
+                const int last = hi - key_base;
 #pragma unroll
-                for (int i = 0; i < PT_BN; ++i) {
-                    const int key = key_base + i;
-                    if (key < lo || key > hi) v[i] = 0xff800000u;                // -inf
-                }
+                for (int i = 0; i < PT_BN; ++i)
+                    if (i > last) v[i] = 0xff800000u;                            // -inf
             }
-            float mx = -INFINITY;
+            if (key_base < lo) {                                                 // the window's far edge
+                const int first_col = lo - key_base;
 #pragma unroll
-            for (int i = 0; i < PT_BN; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+                for (int i = 0; i < PT_BN; ++i)
+                    if (i < first_col) v[i] = 0xff800000u;
+            }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};           // four chains: the instruction's latency, not its rate, would bound one
+#pragma unroll
+            for (int i = 0; i < PT_BN; i += 8) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) mx4[c] = max3(mx4[c], __uint_as_float(v[i + 2 * c]), __uint_as_float(v[i + 2 * c + 1]));
+            }
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             mx *= scale_log2e;
             if (j == 0) {
                 m_ref = mx;
@@ -341,32 +363,35 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 }
             }
             const float neg_base = (m_ref == -INFINITY) ? 0.f : -m_ref;
+            // The probabilities go back to tensor memory as bfloat16, two a column, over the first half
+            // of the columns the scores came from (all of which this thread has read): the block product
+            // takes them from there as its A operand.  The tensor core runs its products in the order
+            // they were issued, so the score product that next writes these columns comes after it.
             float sum = 0.f;
 #pragma unroll
-            for (int c0 = 0; c0 < PT_BN; c0 += 8) {
-                float p[8];
+            for (int c0 = 0; c0 < PT_BN; c0 += 64) {
+                uint32_t pk[32];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    p[i] = ex2_approx(fmaf(__uint_as_float(v[c0 + i]), scale_log2e, neg_base));   // exp2(-inf) = 0 for masked keys
-                    sum += p[i];
+                for (int i = 0; i < 32; ++i) {
+                    const float p0 = ex2_approx(fmaf(__uint_as_float(v[c0 + 2 * i]), scale_log2e, neg_base));      // exp2(-inf) = 0 for masked keys
+                    const float p1 = ex2_approx(fmaf(__uint_as_float(v[c0 + 2 * i + 1]), scale_log2e, neg_base));
+                    sum += p0 + p1;
+                    __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
+                    pk[i] = *reinterpret_cast<uint32_t*>(&pp);
                 }
-                const uint32_t addr = p_row + (c0 >> 6) * (PT_BM * 128) + (uint32_t)(((((c0 & 63) >> 3)) ^ (r & 7)) << 4);
-                __nv_bfloat162 a = __floats2bfloat162_rn(p[0], p[1]), b = __floats2bfloat162_rn(p[2], p[3]);
-                __nv_bfloat162 c = __floats2bfloat162_rn(p[4], p[5]), d = __floats2bfloat162_rn(p[6], p[7]);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(*reinterpret_cast<uint32_t*>(&a)),
-                             "r"(*reinterpret_cast<uint32_t*>(&b)), "r"(*reinterpret_cast<uint32_t*>(&c)),
-                             "r"(*reinterpret_cast<uint32_t*>(&d)) : "memory");
+                tmem_st32(tS + (c0 >> 1), pk);
             }
             l_run += sum;
-            // P is read by the tensor core through the async proxy
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            // One head alone: the scores of this block were issued behind the block product of two blocks
+            // ago, not of the last one, so they do not tell that that one has landed.  A wait names a
+            // phase by its parity, which is only right while at most one phase can have completed unseen:
+            // every product is therefore seen off here, one block late (it has long landed), before this
+            // thread's hand-over lets the next one be issued.  The waits on o_ready above and at the end
+            // rely on it.
+            if (single && j > 0) mbar_wait(o_ready0, (j - 1) & 1, 7);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(p_ready0 + 8 * (single ? buf : h));
-            // One head alone: the scores of the next block no longer tell that the block product before
-            // this one has landed, so every product is seen off here, one block late (it has long
-            // landed).  A wait on a phase's parity is only right for a thread that has seen the phase
-            // before it complete; the waits on o_ready further up and at the end rely on this one.
-            if (single && j > 0) mbar_wait(o_ready0, (j - 1) & 1, 7);
         }
 
         mbar_wait(o_ready0 + 8 * h, (nb - 1) & 1, 7);
