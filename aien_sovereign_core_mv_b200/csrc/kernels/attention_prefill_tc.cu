@@ -94,7 +94,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                   const __grid_constant__ PtMaps maps_v, const int* __restrict__ block_table, int max_blocks,
                   const int* __restrict__ q_start, const int* __restrict__ ctx_len, const int* __restrict__ tile_seq,
                   const int* __restrict__ tile_q0, int num_tiles, __nv_bfloat16* __restrict__ out, long out_stride,
-                  int nq, int nkv, int page_size, int window, float scale_log2e, int cache_rows, int heads_per_cta, int big_boxes) {
+                  int nq, int nkv, int page_size, int window, float scale_log2e, int cache_rows, int heads_per_cta, int big_boxes,
+                  int nsplit, float* __restrict__ part_o, float* __restrict__ part_ml) {
     using S = PtShape<HD>;
     extern __shared__ uint8_t pt_smem[];
     const uint32_t base = (smem_u32(pt_smem) + 1023u) & ~1023u;
@@ -113,8 +114,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     // for steps with so few tiles that the pairs would leave SMs idle
     const int group = nq / nkv, pairs = (group + heads_per_cta - 1) / heads_per_cta;
     const int per_tile = nkv * pairs;
-    const int tile = num_tiles - 1 - (int)(blockIdx.x / per_tile);
-    const int rem = blockIdx.x % per_tile;
+    // nsplit > 1: the key blocks of a tile are cut into nsplit ranges, one CTA each, which leave
+    // unnormalised partial results that prefill_merge_splits_kernel adds up (steps with few tiles and
+    // long contexts: few long CTAs would leave most SMs idle)
+    const int unit = (int)(blockIdx.x / nsplit), split = (int)(blockIdx.x % nsplit);
+    const int tile = num_tiles - 1 - unit / per_tile;
+    const int rem = unit % per_tile;
     const int kvh = rem / pairs, pair = rem - kvh * pairs;
     const int head_a = kvh * group + heads_per_cta * pair;
     const bool has_b = heads_per_cta == 2 && 2 * pair + 1 < group;
@@ -124,8 +129,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int pos0 = ctx_len[s] - q_len + q0;                      // position of the tile's first query
     const int pos_last = pos0 + rows - 1;
     const int first = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
-    const int kb_begin = first / PT_BN, kb_end = pos_last / PT_BN;
-    const int nb = kb_end - kb_begin + 1;
+    const int kb_first = first / PT_BN, kb_last = pos_last / PT_BN;
+    const int per_split = (kb_last - kb_first + nsplit) / nsplit;         // ranges of whole blocks, in order: what a range holds
+    const int kb_begin = kb_first + split * per_split;                   // depends on the tile's keys and nsplit alone
+    const int kb_end = min(kb_last, kb_begin + per_split - 1);
+    const int nb = kb_end - kb_begin + 1;                                // <= 0: nothing in this range
 
     griddep_launch();
     if (threadIdx.x == 0) {
@@ -149,7 +157,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     constexpr int NS1 = S::SLOTS + 1;                   // ring slots of a CTA with one head
     auto slot_addr = [&](int slot) { return slot < S::SLOTS ? sKV + slot * S::SLOT_BYTES : sQ + S::Q_BYTES; };
 
-    if (warp == 8) {
+    if (nb <= 0) {
+        // an empty range: weight zero in the merge
+        if (warp < 8 && (warp < 4 || has_b)) {
+            const int h = warp >> 2, r = (warp & 3) * 32 + lane;
+            float* ml = part_ml + ((((size_t)tile * PT_BM + r) * nq + head_a + h) * nsplit + split) * 2;
+            ml[0] = -INFINITY;
+            ml[1] = 0.f;
+        }
+    } else if (warp == 8) {
         // ------------------------------------------------------------------ producer
         const int pages_per_block = PT_BN / page_size;
         const int* bt = block_table + (size_t)s * max_blocks;
@@ -396,6 +412,22 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
         mbar_wait(o_ready0 + 8 * h, (nb - 1) & 1, 7);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (nsplit > 1) {
+            // this range's part: the unnormalised sums, the maximum they are taken against (log2 units) and the weight sum
+            const size_t prow = (((size_t)tile * PT_BM + r) * nq + head_a + h) * nsplit + split;
+            part_ml[prow * 2] = m_ref;
+            part_ml[prow * 2 + 1] = l_run;
+            float* dstf = part_o + prow * HD;
+#pragma unroll 1
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t o[32];
+                tmem_ld32(tO + c0, o);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int d = 0; d < 32; d += 4)
+                    *reinterpret_cast<uint4*>(dstf + c0 + d) = make_uint4(o[d], o[d + 1], o[d + 2], o[d + 3]);
+            }
+        } else {
         const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
         __nv_bfloat16* dst = out + (size_t)(qs + q0 + (r < rows ? r : 0)) * out_stride + (size_t)(head_a + h) * HD;
 #pragma unroll 1
@@ -417,6 +449,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 }
             }
         }
+        }
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -427,11 +460,70 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     }
 }
 
+// Adds up the parts that the key ranges of a tile left: out = sum_s w_s O_s / sum_s w_s l_s with
+// w_s = 2^(m_s - max m), in the order of the ranges.  One warp per (query row, head), a lane per
+// HD / 32 dimensions; all loads of a warp are independent of one another.
+constexpr int PT_MAX_SPLITS = 8;
+template <int HD>
+__global__ void __launch_bounds__(256) prefill_merge_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                                   const int* __restrict__ q_start, const int* __restrict__ tile_seq,
+                                                                   const int* __restrict__ tile_q0, __nv_bfloat16* __restrict__ out,
+                                                                   long out_stride, int nq, int nsplit) {
+    constexpr int PER = HD / 32;
+    griddep_launch();
+    const int lane = threadIdx.x & 31;
+    const long unit = (long)blockIdx.x * 8 + (threadIdx.x >> 5);          // (tile, row, head)
+    const int head = (int)(unit % nq);
+    const long trow = unit / nq;
+    const int tile = (int)(trow / PT_BM), r = (int)(trow % PT_BM);
+    const int s = tile_seq[tile], q0 = tile_q0[tile];
+    const int qs = q_start[s], q_len = q_start[s + 1] - qs;
+    griddep_wait();
+    if (r >= min(PT_BM, q_len - q0)) return;
+    const size_t prow = (size_t)unit * nsplit;
+    float m[PT_MAX_SPLITS], l[PT_MAX_SPLITS], o[PT_MAX_SPLITS][PER];
+#pragma unroll
+    for (int sp = 0; sp < PT_MAX_SPLITS; ++sp) {
+        m[sp] = -INFINITY; l[sp] = 0.f;
+        if (sp < nsplit) { m[sp] = __ldcg(part_ml + (prow + sp) * 2); l[sp] = __ldcg(part_ml + (prow + sp) * 2 + 1); }
+    }
+#pragma unroll
+    for (int sp = 0; sp < PT_MAX_SPLITS; ++sp) {
+        const bool live = sp < nsplit && m[sp] != -INFINITY && l[sp] > 0.f;    // an empty range left no sums
+        if (!live) m[sp] = -INFINITY;
+        const float* src = part_o + (prow + sp) * HD + lane * PER;
+        if constexpr (PER == 4) {
+            const float4 t = live ? __ldcg(reinterpret_cast<const float4*>(src)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            o[sp][0] = t.x; o[sp][1] = t.y; o[sp][2] = t.z; o[sp][3] = t.w;
+        } else {
+            const float2 t = live ? __ldcg(reinterpret_cast<const float2*>(src)) : make_float2(0.f, 0.f);
+            o[sp][0] = t.x; o[sp][1] = t.y;
+        }
+    }
+    float M = -INFINITY;
+#pragma unroll
+    for (int sp = 0; sp < PT_MAX_SPLITS; ++sp) M = fmaxf(M, m[sp]);
+    float L = 0.f, acc[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) acc[i] = 0.f;
+#pragma unroll
+    for (int sp = 0; sp < PT_MAX_SPLITS; ++sp) {
+        const float w = m[sp] == -INFINITY ? 0.f : ex2_approx(m[sp] - M);
+        L = fmaf(w, l[sp], L);
+#pragma unroll
+        for (int i = 0; i < PER; ++i) acc[i] = fmaf(w, o[sp][i], acc[i]);
+    }
+    const float inv = L > 0.f ? 1.0f / L : 0.f;
+    __nv_bfloat16* dst = out + (size_t)(qs + q0 + r) * out_stride + (size_t)head * HD + lane * PER;
+#pragma unroll
+    for (int i = 0; i < PER; i += 2) *reinterpret_cast<__nv_bfloat162*>(dst + i) = __floats2bfloat162_rn(acc[i] * inv, acc[i + 1] * inv);
+}
+
 template <int HD>
 static int launch_prefill_tc(const CUtensorMap& mq, const PtMaps& mk, const PtMaps& mv, int big_boxes, const int* bt, int max_blocks,
                              const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_q0, int num_tiles,
                              void* out, long out_stride, int nq, int nkv, int page_size, int window, float scale, int cache_rows,
-                             cudaStream_t stream) {
+                             void* scratch, long scratch_bytes, int max_ctx, int force_splits, cudaStream_t stream) {
     auto kern = prefill_tc_kernel<HD>;
     static bool configured = false;
     if (!configured) {
@@ -442,21 +534,46 @@ static int launch_prefill_tc(const CUtensorMap& mq, const PtMaps& mk, const PtMa
     int sms = 148, dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
     // Two heads of a kv head per CTA halve the K/V traffic and let the tensor core work for one head
-    // under the other's softmax: a key block then takes 2.5 us for both heads, against 1.8 us for the
-    // single head of a CTA that has only one (and runs its score products ahead).  What decides is
-    // the number of waves either way: 512 tokens are 128 single-head CTAs, one wave, 57 us against
-    // 82 us in pairs; 1,024 tokens are 256, two waves, against 84 us for 128 pairs (32 heads of 128,
-    // a portion that ends at 4,096 tokens).
-    int heads_per_cta = 1;
-    if (group >= 2) {
-        const long single = (long)num_tiles * nkv * group, paired = (long)num_tiles * nkv * ((group + 1) / 2);
-        if (18 * ((single + sms - 1) / sms) > 25 * ((paired + sms - 1) / sms)) heads_per_cta = 2;
+    // under the other's softmax: a key block then takes ~3,550 cycles for both heads, against ~2,870 for
+    // the single head of a CTA that has only one (and runs its score products ahead); a CTA costs
+    // ~6,000 cycles beside its blocks.  What decides is the number of waves either way: 512 tokens are
+    // 128 single-head CTAs, one wave, against 64 pairs that leave half the SMs idle.
+    // Few tiles over long contexts (a portion at the end of a long prompt) can do better than either:
+    // pairs, with the keys of every tile cut into ranges on separate CTAs, at the price of the partial
+    // results' way through memory and of the merge: ~20,000 cycles when timed alone, counted double
+    // here because inside a step the partial results also push weights out of L2 (a 512-token portion
+    // at offset 2,048 beside 24 decoding requests: equal alone, 0.4 ms a step slower with two ranges).
+    // Measured (32 / 8 heads of 128): 256 tokens at offset 7,936 110 -> 50 us (4 ranges), 128 at 4,000
+    // 59 -> 26 us (8); 512 tokens at 3,584 would gain little (58 -> 51 us alone) and are left alone.
+    const long single = (long)num_tiles * nkv * group, paired = (long)num_tiles * nkv * ((group + 1) / 2);
+    auto waves = [&](long ctas) { return (ctas + sms - 1) / sms; };
+    const long blocks = max_ctx > 0 ? (max_ctx + PT_BN - 1) / PT_BN : 0;          // of the longest tile, at most
+    int heads_per_cta = (group >= 2 && 18 * waves(single) > 25 * waves(paired)) ? 2 : 1;
+    int nsplit = 1;
+    const long part_rows = (long)num_tiles * PT_BM * nq;
+    auto fits = [&](int n) { return scratch != nullptr && part_rows * n * (HD + 2) * 4 <= scratch_bytes; };
+    if (force_splits > 0) {
+        nsplit = force_splits;
+        if (!fits(nsplit)) return AIEN_E_SHAPE;
+    } else if (group >= 2 && blocks > 0) {
+        long best = heads_per_cta == 2 ? waves(paired) * (blocks * 3550 + 6000) : waves(single) * (blocks * 2870 + 6000);
+        for (int n = 2; n <= PT_MAX_SPLITS && fits(n); ++n) {
+            const long t = waves(paired * n) * ((blocks + n - 1) / n * 3550 + 6000) + 40000;
+            if (t < best) { best = t; nsplit = n; }
+        }
     }
-    const long ctas = (long)num_tiles * nkv * ((group + heads_per_cta - 1) / heads_per_cta);
+    if (nsplit > 1 && group >= 2) heads_per_cta = 2;
+    const long ctas = (long)num_tiles * nkv * ((group + heads_per_cta - 1) / heads_per_cta) * nsplit;
     if (ctas > 2147483647L) return AIEN_E_SHAPE;
+    float* part_o = nsplit > 1 ? (float*)scratch : nullptr;
+    float* part_ml = nsplit > 1 ? part_o + part_rows * nsplit * HD : nullptr;
     launch_chain(kern, dim3((unsigned)ctas), dim3(PT_THREADS), (size_t)PtShape<HD>::SMEM, stream, mq, mk, mv, bt, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles,
                                                                      (__nv_bfloat16*)out, out_stride, nq, nkv, page_size, window,
-                                                                     scale * 1.4426950408889634f, cache_rows, heads_per_cta, big_boxes);
+                                                                     scale * 1.4426950408889634f, cache_rows, heads_per_cta, big_boxes, nsplit, part_o, part_ml);
+    if (launch_status() != 0) return launch_status();
+    if (nsplit > 1)
+        launch_chain(prefill_merge_splits_kernel<HD>, dim3((unsigned)(part_rows / 8)), dim3(256), (size_t)0, stream, (const float*)part_o, (const float*)part_ml,
+                     q_start, tile_seq, tile_q0, (__nv_bfloat16*)out, out_stride, nq, nsplit);
     return launch_status();
 }
 
@@ -472,16 +589,21 @@ AIEN_API int aien_paged_attention_prefill_tc_supports(int hd, int page_size) {
 
 // q [q_rows, nq*hd] (leading dimension q_stride), k_cache/v_cache [cache_rows, nkv*hd] contiguous;
 // the other arguments as aien_paged_attention_prefill.
-AIEN_API int aien_paged_attention_prefill_tc(
+// scratch (may be null), scratch_bytes: room for the partial results of key ranges, num_tiles * 128 * nq *
+// splits * (hd + 2) floats; max_ctx: an upper bound of the contexts in ctx_len, known to the host;
+// force_splits: 0 lets the launch choose, n > 0 asks for n ranges (refused if the scratch is too small).
+AIEN_API int aien_paged_attention_prefill_tc_split(
     const void* q, long q_stride, int q_rows, const void* k_cache, const void* v_cache, int cache_rows, const int* block_table,
     int max_blocks, const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_q0, int num_tiles, void* out,
-    long out_stride, int nq, int nkv, int hd, int page_size, int window, float scale, cudaStream_t stream) {
+    long out_stride, int nq, int nkv, int hd, int page_size, int window, float scale, void* scratch, long scratch_bytes, int max_ctx,
+    int force_splits, cudaStream_t stream) {
     if (num_tiles <= 0) return 0;
     if (!aien_paged_attention_prefill_tc_supports(hd, page_size) || nkv <= 0 || nq % nkv != 0 || q_rows <= 0 || cache_rows <= 0)
         return AIEN_E_SHAPE;
     if ((q_stride & 7) || (out_stride & 7) || ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) ||
-        ((uintptr_t)out & 15))
+        ((uintptr_t)out & 15) || ((uintptr_t)scratch & 15))
         return AIEN_E_ALIGN;
+    if (force_splits < 0 || force_splits > PT_MAX_SPLITS) return AIEN_E_SHAPE;
     CUtensorMap mq;
     static PtMaps mk, mv;                      // large: kept out of the stack; filled for every launch
     static std::mutex mu;
@@ -502,9 +624,19 @@ AIEN_API int aien_paged_attention_prefill_tc(
     if (!big_boxes) { mk.blk = mk.m[0]; mv.blk = mv.m[0]; }
     if (hd == 64)
         return launch_prefill_tc<64>(mq, mk, mv, big_boxes, block_table, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles, out, out_stride,
-                                     nq, nkv, page_size, window, scale, cache_rows, stream);
+                                     nq, nkv, page_size, window, scale, cache_rows, scratch, scratch_bytes, max_ctx, force_splits, stream);
     return launch_prefill_tc<128>(mq, mk, mv, big_boxes, block_table, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles, out, out_stride,
-                                  nq, nkv, page_size, window, scale, cache_rows, stream);
+                                  nq, nkv, page_size, window, scale, cache_rows, scratch, scratch_bytes, max_ctx, force_splits, stream);
+}
+
+// The same without scratch: every tile's keys in one range.
+AIEN_API int aien_paged_attention_prefill_tc(
+    const void* q, long q_stride, int q_rows, const void* k_cache, const void* v_cache, int cache_rows, const int* block_table,
+    int max_blocks, const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_q0, int num_tiles, void* out,
+    long out_stride, int nq, int nkv, int hd, int page_size, int window, float scale, cudaStream_t stream) {
+    return aien_paged_attention_prefill_tc_split(q, q_stride, q_rows, k_cache, v_cache, cache_rows, block_table, max_blocks, q_start, ctx_len,
+                                                 tile_seq, tile_q0, num_tiles, out, out_stride, nq, nkv, hd, page_size, window, scale,
+                                                 nullptr, 0, 0, 0, stream);
 }
 
 // Reads and clears the code a bounded wait may have left (0: none; 1 producer, 2 K/V block,

@@ -135,6 +135,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_attention_prefill_tc_error": [],
         "aien_paged_attention_prefill": [P, L, P, P, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P],
         "aien_paged_attention_prefill_tc": [P, L, I, P, P, I, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P],
+        "aien_paged_attention_prefill_tc_split": [P, L, I, P, P, I, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P, L, I, I, P],
         "aien_paged_attention_prefill_tc_supports": [I, I],
         "aien_paged_attention_decode": [P, L, P, P, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, P],
         "aien_paged_attention_decode_stream": [P, L, P, P, I, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, P],
@@ -584,7 +585,8 @@ PREFILL_TILE = 128         # query tokens per CTA of the prefill attention kerne
 def attention_workspace_bytes(lim, num_heads: int, head_dim: int) -> int:
     """Scratch of the split-key decode kernel for the largest decode-only step."""
     splits = (lim.max_context + DECODE_CHUNK - 1) // DECODE_CHUNK
-    return lim.max_seqs * num_heads * splits * (head_dim + 2) * 4 + 1024
+    return lim.max_seqs * num_heads * splits * (head_dim + 2) * 4 + 1024 \
+        + prefill_split_scratch_bytes(PREFILL_SPLIT_MAX_TILES, num_heads, head_dim, lim.max_context) + 256
 
 
 _ticket_counters: Optional[torch.Tensor] = None
@@ -697,8 +699,11 @@ def paged_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
         # a mixed step: portions go through the tiled kernel, single tokens through the split-key kernel
         tile_seq, tile_q0, n = ctx.prefill_tiles
         if n > 0:
+            room = prefill_split_scratch_bytes(n, num_q_heads, head_dim, ctx.max_ctx_len)
+            scratch = ctx.workspace.take((room // 4,), torch.float32) if room else None
             paged_attention_prefill(q, k2, v2, group.block_table, group.max_blocks, ctx.q_start, ctx.ctx_len, tile_seq, tile_q0, n,
-                                    out, num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale)
+                                    out, num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale,
+                                    scratch=scratch, max_ctx=ctx.max_ctx_len)
         tokens, nd = ctx.single_tokens if ctx.single_tokens is not None else (None, 0)
         if nd > 0:
             splits = max(1, (ctx.max_ctx_len + DECODE_CHUNK - 1) // DECODE_CHUNK)
@@ -726,12 +731,27 @@ def prefill_tc_supports(q, out, head_dim: int, page_size: int) -> bool:
             and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
 
 
+PREFILL_SPLIT_MAX_TILES = 8          # steps with more tiles fill the GPU without cutting the keys
+
+
+def prefill_split_scratch_bytes(num_tiles: int, num_q_heads: int, head_dim: int, max_ctx: int) -> int:
+    """Room the tcgen05 prefill kernel can use to cut the keys of `num_tiles` tiles into ranges
+    (float32 partial results); 0 where it would not cut."""
+    if num_tiles <= 0 or num_tiles > PREFILL_SPLIT_MAX_TILES or max_ctx < 8 * PREFILL_TILE:
+        return 0
+    return num_tiles * PREFILL_TILE * num_q_heads * 8 * (head_dim + 2) * 4
+
+
 def paged_attention_prefill(q, k_cache, v_cache, block_table, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles,
-                            out, num_q_heads, num_kv_heads, head_dim, page_size, window, scale, impl: Optional[str] = None) -> None:
+                            out, num_q_heads, num_kv_heads, head_dim, page_size, window, scale, impl: Optional[str] = None,
+                            scratch: Optional[torch.Tensor] = None, max_ctx: int = 0, splits: int = 0) -> None:
     """Causal attention of portions of prompts over their requests' pages (bfloat16, tensor
     cores).  ``tile_seq``/``tile_q0``: for every 128-token query tile, the index of its request in
     the step and the tile's offset inside that request's portion.  ``impl``: "tc" (tcgen05, where
-    the sizes allow) or "mma" (mma.sync); default from ``AIEN_B200_PREFILL``, else "tc"."""
+    the sizes allow) or "mma" (mma.sync); default from ``AIEN_B200_PREFILL``, else "tc".
+    ``scratch`` (float32, optional) with ``max_ctx`` (an upper bound of the contexts) lets the
+    tcgen05 kernel cut the keys of a step with few tiles into ranges that run on separate SMs;
+    ``splits`` > 0 asks for that many ranges (tests)."""
     _dev(q, k_cache, v_cache, block_table, q_start, ctx_len, tile_seq, tile_q0, out)
     assert q.stride(1) == 1 and out.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous()
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
@@ -739,10 +759,14 @@ def paged_attention_prefill(q, k_cache, v_cache, block_table, max_blocks, q_star
         assert t.dtype == torch.int32
     impl = impl or _PREFILL_IMPL
     if impl == "tc" and prefill_tc_supports(q, out, head_dim, page_size):
-        _check(lib().aien_paged_attention_prefill_tc(
+        if scratch is not None:
+            _dev(scratch)
+            assert scratch.dtype == torch.float32 and scratch.is_contiguous()
+        _check(lib().aien_paged_attention_prefill_tc_split(
             _p(q), q.stride(0), q.shape[0], _p(k_cache), _p(v_cache), k_cache.shape[0], _p(block_table), max_blocks, _p(q_start),
             _p(ctx_len), _p(tile_seq), _p(tile_q0), num_tiles, _p(out), out.stride(0), num_q_heads, num_kv_heads, head_dim,
-            page_size, window, float(scale), _stream()), "paged_attention_prefill_tc")
+            page_size, window, float(scale), _p(scratch) if scratch is not None else None,
+            scratch.numel() * 4 if scratch is not None else 0, int(max_ctx), int(splits), _stream()), "paged_attention_prefill_tc")
         return
     _check(lib().aien_paged_attention_prefill(
         _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), max_blocks, _p(q_start), _p(ctx_len), _p(tile_seq),

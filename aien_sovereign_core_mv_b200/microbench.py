@@ -114,7 +114,9 @@ def attn_decode_case(batch: int, ctx: int, nq: int = 32, nkv: int = 8, hd: int =
 
 
 def attn_prefill_case(tokens: int, offset: int = 0, nq: int = 32, nkv: int = 8, hd: int = 128, page: int = 16, reps: int = 10,
-                      impl: str = "tc", layout: str = "shuffled") -> None:
+                      impl: str = "tc", layout: str = "shuffled", splits: int = 0) -> None:
+    """splits: 0 lets the launch cut the keys into ranges where it sees fit (it is given the room), -1 gives
+    it no room, n > 0 asks for n ranges."""
     ctx = offset + tokens
     kc, vc, bt, width = _paged_cache(1, ctx, nkv, hd, page, layout)
     q = torch.randn(tokens, nq * hd, device="cuda", dtype=torch.bfloat16)
@@ -123,14 +125,18 @@ def attn_prefill_case(tokens: int, offset: int = 0, nq: int = 32, nkv: int = 8, 
     n_tiles = (tokens + K.PREFILL_TILE - 1) // K.PREFILL_TILE
     args = (i32([0, tokens]), i32([ctx]), i32([0] * n_tiles), i32([t * K.PREFILL_TILE for t in range(n_tiles)]), n_tiles)
 
+    room = n_tiles * K.PREFILL_TILE * nq * splits * (hd + 2) * 4 if splits > 0 else K.prefill_split_scratch_bytes(n_tiles, nq, hd, ctx) if splits == 0 else 0
+    scratch = torch.empty(room // 4, device="cuda") if room else None
+
     def run(_=0):
-        K.paged_attention_prefill(q, kc, vc, bt, width, *args, out, nq, nkv, hd, page, 0, 1 / math.sqrt(hd), impl=impl)
+        K.paged_attention_prefill(q, kc, vc, bt, width, *args, out, nq, nkv, hd, page, 0, 1 / math.sqrt(hd), impl=impl,
+                                  scratch=scratch, max_ctx=ctx, splits=max(splits, 0))
 
     for _ in range(3):
         run()
     us = _time_graph(run, reps)
     flops = 4.0 * nq * hd * (tokens * (tokens + 1) / 2 + tokens * offset)
-    print(f"attn-prefill[{impl}] tokens={tokens} offset={offset} page={page} {layout} ({nq}q/{nkv}kv x {hd}): {us:8.1f} us  {flops / us / 1e6:7.1f} TFLOP/s"
+    print(f"attn-prefill[{impl}] tokens={tokens} offset={offset} page={page} {layout} splits={splits} ({nq}q/{nkv}kv x {hd}): {us:8.1f} us  {flops / us / 1e6:7.1f} TFLOP/s"
           f"  (error flag {K.attention_prefill_tc_error()})", flush=True)
 
 
@@ -200,6 +206,7 @@ def main(argv=None) -> int:
     p.add_argument("--tokens", type=int, default=2048); p.add_argument("--offset", type=int, default=0)
     p.add_argument("--impl", default="tc", choices=["tc", "mma"]); p.add_argument("--page", type=int, default=16)
     p.add_argument("--layout", default="shuffled", choices=["shuffled", "sequential", "runs4"], help="where the request's pages lie in the pool")
+    p.add_argument("--splits", type=int, default=0, help="ranges the keys of a tile are cut into: 0 as the launch chooses, -1 never, n > 0 exactly n")
     p = sub.add_parser("qk")
     p.add_argument("--tokens", type=int, default=2048); p.add_argument("--parts", type=int, default=0)
     p = sub.add_parser("sample")
@@ -216,7 +223,7 @@ def main(argv=None) -> int:
     elif args.case == "attn-decode":
         attn_decode_case(args.batch, args.ctx, page=args.page, impl=args.impl)
     elif args.case == "attn-prefill":
-        attn_prefill_case(args.tokens, args.offset, page=args.page, impl=args.impl, layout=args.layout)
+        attn_prefill_case(args.tokens, args.offset, page=args.page, impl=args.impl, layout=args.layout, splits=args.splits)
     elif args.case == "qk":
         qk_case(args.tokens, args.parts)
     elif args.case == "sample":

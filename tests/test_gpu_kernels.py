@@ -608,7 +608,7 @@ def test_gemm_tensor_core_swiglu_epilogue(K, M, I, Hd):
 PREFILL_CASES = [(4, 2, 16, 16, 0), (6, 3, 48, 8, 0), (5, 1, 80, 16, 0), (8, 2, 128, 16, 0), (3, 3, 32, 4, 21), (8, 4, 64, 16, 40), (2, 1, 112, 32, 100)]
 
 
-def _prefill_case(K, nq, nkv, hd, page, window, seq_lens, q_lens, impl):
+def _prefill_case(K, nq, nkv, hd, page, window, seq_lens, q_lens, impl, splits=0):
     dtype = torch.bfloat16
     rng = np.random.default_rng(nq * 31 + hd + len(seq_lens))
     kc, vc, bt, mb, dense = paged_setup(rng, seq_lens, nkv, hd, page, dtype, sum((n + page - 1) // page for n in seq_lens) + 8)
@@ -625,12 +625,16 @@ def _prefill_case(K, nq, nkv, hd, page, window, seq_lens, q_lens, impl):
     scale = 1.0 / math.sqrt(hd)
     i32 = lambda a: torch.tensor(a, dtype=torch.int32).cuda()
     out = torch.full((T, nq * hd), 7.0, dtype=dtype, device="cuda")
+    scratch = None
+    if splits:
+        # NaN everywhere: a range that holds nothing leaves its sums unwritten, and the merge must not read them
+        scratch = torch.full((len(tile_seq) * K.PREFILL_TILE * nq * splits * (hd + 2),), float("nan"), device="cuda")
     K.paged_attention_prefill(q, kc, vc, bt, mb, i32(q_start), i32(seq_lens), i32(tile_seq), i32(tile_q0), len(tile_seq),
-                              out, nq, nkv, hd, page, window, scale, impl=impl)
+                              out, nq, nkv, hd, page, window, scale, impl=impl, scratch=scratch, max_ctx=max(seq_lens), splits=splits)
     torch.cuda.synchronize()
     assert K.attention_prefill_tc_error() == 0
     want = attention_reference(q.float().double().cpu().numpy().reshape(-1, nq, hd), dense, seq_of, positions, nq, nkv, hd, window, scale)
-    H.assert_close(out.float().cpu().numpy(), want, 1.5e-2, f"prefill attention ({impl})")
+    H.assert_close(out.float().cpu().numpy(), want, 1.5e-2, f"prefill attention ({impl}, {splits} ranges)")
 
 
 @pytest.mark.parametrize("nq,nkv,hd,page,window", PREFILL_CASES)
@@ -651,6 +655,40 @@ def test_paged_attention_prefill_tensor_memory(K, nq, nkv, hd, page, window):
     assert K.prefill_tc_supports(torch.empty(1, nq * hd, dtype=torch.bfloat16, device="cuda"),
                                  torch.empty(1, nq * hd, dtype=torch.bfloat16, device="cuda"), hd, page)
     _prefill_case(K, nq, nkv, hd, page, window, [130, 64, 300, 5, 200, 1000, 700], [130, 1, 77, 2, 128, 333, 700], "tc")
+
+
+@pytest.mark.parametrize("splits", [2, 3, 8])
+@pytest.mark.parametrize("nq,nkv,hd,page,window", [(8, 2, 128, 16, 0), (8, 4, 64, 16, 40), (3, 1, 128, 8, 0), (4, 1, 128, 64, 300), (5, 5, 128, 16, 130)])
+def test_paged_attention_prefill_keys_cut_into_ranges(K, nq, nkv, hd, page, window, splits):
+    """The same cases with every tile's key blocks cut into 2, 3 or 8 ranges on separate CTAs whose
+    partial results a second kernel adds up: tiles with fewer blocks than ranges (empty ranges), a
+    window that leaves early ranges empty for late rows, one head alone in a pair's place."""
+    _prefill_case(K, nq, nkv, hd, page, window, [130, 64, 300, 5, 200, 1000, 700], [130, 1, 77, 2, 128, 333, 700], "tc", splits=splits)
+
+
+def test_paged_attention_prefill_chooses_ranges_for_few_tiles_over_a_long_context(K):
+    """The launch's own choice: 256 tokens at the end of 4,200 are two tiles of 16 pairs each, which it
+    cuts into ranges when it is given the room; the result is the same as without."""
+    nq, nkv, hd, page, n = 32, 8, 128, 16, 4200
+    scratch_bytes = K.prefill_split_scratch_bytes(2, nq, hd, n)
+    assert scratch_bytes > 0 and K.prefill_split_scratch_bytes(2, nq, hd, 500) == 0 and K.prefill_split_scratch_bytes(40, nq, hd, n) == 0
+    rng = np.random.default_rng(11)
+    kc, vc, bt, mb, dense = paged_setup(rng, [n], nkv, hd, page, torch.bfloat16, n // page + 9)
+    q = torch.tensor(rng.standard_normal((256, nq * hd)), dtype=torch.float32).to(torch.bfloat16).cuda()
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32).cuda()
+    outs = []
+    for scratch in (None, torch.full((scratch_bytes // 4,), float("nan"), device="cuda")):
+        out = torch.empty_like(q)
+        K.paged_attention_prefill(q, kc, vc, bt, mb, i32([0, 256]), i32([n]), i32([0, 0]), i32([0, 128]), 2, out, nq, nkv, hd, page, 0,
+                                  1.0 / math.sqrt(hd), impl="tc", scratch=scratch, max_ctx=n)
+        torch.cuda.synchronize()
+        assert K.attention_prefill_tc_error() == 0
+        outs.append(out.float().cpu().numpy())
+    assert scratch.isnan().sum().item() < scratch.numel()                    # the room was used
+    want = attention_reference(q.float().double().cpu().numpy().reshape(-1, nq, hd), dense, [0] * 256, list(range(n - 256, n)), nq, nkv, hd, 0,
+                               1.0 / math.sqrt(hd))
+    H.assert_close(outs[0], want, 1.5e-2, "one range")
+    H.assert_close(outs[1], want, 1.5e-2, "chosen ranges")
 
 
 def test_prefill_attention_growing_maximum(K):
