@@ -2,6 +2,7 @@
 // owns, for callers that cannot allocate (see sampling_noalloc.h for who they are and why).
 #include "common.cuh"
 #include "sampling_noalloc.h"
+#include <atomic>
 
 namespace aien {
 
@@ -17,7 +18,7 @@ __global__ void sample_rows_kernel(const float* __restrict__ logits, int V, cons
 static __device__ __align__(256) float g_static_probs[AIEN_SAMPLE_STATIC_MAX_ELEMS];
 
 constexpr int kMaxDevices = 64;
-static float* g_scratch_addr[kMaxDevices] = {};
+static std::atomic<float*> g_scratch_addr[kMaxDevices] = {};     // every thread that asks gets the same answer
 
 }  // namespace aien
 
@@ -32,13 +33,15 @@ AIEN_API int aien_sample_rows_static(const float* logits, int R, int V, const fl
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return static_cast<int>(e);
     if (dev < 0 || dev >= kMaxDevices) return AIEN_E_STATE;
-    if (g_scratch_addr[dev] == nullptr) {                    // set-up, once per device, with that device current
+    float* scratch = g_scratch_addr[dev].load(std::memory_order_acquire);
+    if (scratch == nullptr) {                                // set-up, once per device, with that device current
         void* p = nullptr;
         e = cudaGetSymbolAddress(&p, g_static_probs);
         if (e != cudaSuccess) return static_cast<int>(e);
-        g_scratch_addr[dev] = static_cast<float*>(p);
+        scratch = static_cast<float*>(p);
+        g_scratch_addr[dev].store(scratch, std::memory_order_release);
     }
     sample_rows_kernel<<<R, 1024, 0, stream>>>(logits, V, temperature, top_p, top_k, seeds, request_ids, positions,
-                                               g_scratch_addr[dev], out_ids, nullptr);
+                                               scratch, out_ids, nullptr);
     return launch_status();
 }

@@ -212,3 +212,17 @@ def test_a_request_of_4200_tokens(long_request, dtype, tol):
     eng.check_waits()
     H.assert_close(np.concatenate(got), want, tol, f"{dtype} 4,200-token request (rows {rows[:7]} and 4096..4199)")
     assert eng.cache_state()["check"] == ""
+
+
+def test_a_short_last_portion_of_a_long_request_is_cut_over_key_ranges(long_request):
+    """3,944 tokens in two portions, then the last 256 as one: two query tiles over 33 key blocks, which
+    the tcgen05 prefill kernel cuts into key ranges on separate CTAs and merges.  Held to the plain
+    implementation at rows of both tiles."""
+    d, toks, rows, want = long_request
+    eng = H.engine_for(d, "bfloat16", 16, 4352, max_requests=2, max_batch_tokens=2048, max_context=4352)
+    eng.step([(1, toks[:2048], [])])
+    eng.step([(1, toks[2048:3944], [])])
+    got = eng.step([(1, toks[3944:], [r - 3944 for r in rows if r >= 3944])]).cpu().numpy()
+    eng.check_waits()
+    H.assert_close(got, want[[i for i, r in enumerate(rows) if r >= 3944]], H.BF16_TOL, "last 256 tokens of 4,200 as one portion")
+    assert eng.cache_state()["check"] == ""
