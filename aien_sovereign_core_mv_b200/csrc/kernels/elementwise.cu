@@ -680,6 +680,53 @@ AIEN_API int aien_feed_token_ids(int* token_ids, const int* src, const int* prev
     return launch_status();
 }
 
+// ---------------------------------------------------------------------------------------------
+// Cache housekeeping: the copy of a page (or of a state slot) in every run of a cache group, and zero fill.
+// buf holds `slots` runs, slot_stride bytes apart; in each, n bytes at src_off are copied to dst_off
+// (the two spans must not overlap).  16 bytes a thread where everything is 16-byte aligned.
+__global__ void __launch_bounds__(256) copy_spans_kernel(uint8_t* __restrict__ buf, size_t slot_stride, size_t src_off, size_t dst_off, size_t n, int vec) {
+    uint8_t* base = buf + (size_t)blockIdx.y * slot_stride;
+    const size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x, step = (size_t)gridDim.x * blockDim.x;
+    if (vec) {
+        const uint4* s = reinterpret_cast<const uint4*>(base + src_off);
+        uint4* d = reinterpret_cast<uint4*>(base + dst_off);
+        for (size_t i = i0; i < n / 16; i += step) d[i] = s[i];
+    } else {
+        for (size_t i = i0; i < n; i += step) base[dst_off + i] = base[src_off + i];
+    }
+}
+
+AIEN_API int aien_copy_spans(void* buf, size_t slot_stride, int slots, size_t src_off, size_t dst_off, size_t n, cudaStream_t stream) {
+    if (slots <= 0 || n == 0) return 0;
+    if (slots > 65535) return AIEN_E_SHAPE;
+    if ((src_off < dst_off ? dst_off - src_off : src_off - dst_off) < n) return AIEN_E_SHAPE;        // overlapping spans
+    const int vec = (((uintptr_t)buf | slot_stride | src_off | dst_off | n) & 15) == 0;
+    const size_t items = vec ? n / 16 : n;
+    const unsigned blocks = (unsigned)((items + 255) / 256 < 1024 ? (items + 255) / 256 : 1024);
+    copy_spans_kernel<<<dim3(blocks, (unsigned)slots), 256, 0, stream>>>((uint8_t*)buf, slot_stride, src_off, dst_off, n, vec);
+    return launch_status();
+}
+
+__global__ void __launch_bounds__(256) zero_fill_kernel(uint8_t* __restrict__ buf, size_t n, size_t head, size_t body16) {
+    // head bytes up to the first 16-byte boundary, body16 vectors, then the tail
+    const size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x, step = (size_t)gridDim.x * blockDim.x;
+    uint4* body = reinterpret_cast<uint4*>(buf + head);
+    for (size_t i = i0; i < body16; i += step) body[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (size_t i = i0; i < head; i += step) buf[i] = 0;
+    for (size_t i = head + body16 * 16 + i0; i < n; i += step) buf[i] = 0;
+}
+
+AIEN_API int aien_zero_fill(void* buf, size_t n, cudaStream_t stream) {
+    if (n == 0) return 0;
+    size_t head = (16 - ((uintptr_t)buf & 15)) & 15;
+    if (head > n) head = n;
+    const size_t body16 = (n - head) / 16;
+    const size_t items = body16 > 256 ? body16 : 256;
+    const unsigned blocks = (unsigned)((items + 255) / 256 < 148 * 16 ? (items + 255) / 256 : 148 * 16);
+    zero_fill_kernel<<<blocks, 256, 0, stream>>>((uint8_t*)buf, n, head, body16);
+    return launch_status();
+}
+
 AIEN_API int aien_gather_add_rows(const float* x, const void* delta, int delta_dt, int nparts, size_t part_stride,
                                   const int* rows, float* out, int R, int H, cudaStream_t stream) {
     if (R <= 0) return 0;

@@ -90,13 +90,13 @@ class Engine:
             if need.kind == "state":
                 gspecs.append(self.host.GroupSpec(kinds["state"], 0, self.max_requests))
                 sdt = getattr(torch, need.state_dtype)
-                self.storage.append({"state": torch.zeros((slots, self.max_requests + 1) + tuple(need.state_shape), dtype=sdt, device=self.device)})
+                self.storage.append({"state": K.zero_fill(torch.empty((slots, self.max_requests + 1) + tuple(need.state_shape), dtype=sdt, device=self.device))})
             else:
                 if not need.planes:
                     raise ValueError(f"a mixer asks for a {need.kind!r} cache and names no planes to keep in it")
                 gspecs.append(self.host.GroupSpec(kinds[need.kind], need.window, pages))
                 pdt = getattr(torch, need.dtype) if need.dtype else self.dtype
-                self.storage.append({name: torch.zeros((slots, pages * self.page_size) + tuple(int(d) for d in shape), dtype=pdt, device=self.device)
+                self.storage.append({name: K.zero_fill(torch.empty((slots, pages * self.page_size) + tuple(int(d) for d in shape), dtype=pdt, device=self.device))
                                      for name, shape in need.planes})
         self.cache = self.host.CacheManager(self.page_size, gspecs, self.max_requests)
         self.max_blocks = (self.table_context + self.page_size - 1) // self.page_size
@@ -202,9 +202,9 @@ class Engine:
             state = self.model.group_needs[g].kind == "state"
             for st in self.storage[g].values():
                 if state:
-                    st[:, dst].copy_(st[:, src])
+                    K.copy_rows(st, src, dst)
                 else:
-                    st[:, dst * ps:(dst + 1) * ps].copy_(st[:, src * ps:(src + 1) * ps])
+                    K.copy_rows(st, src * ps, dst * ps, ps)
 
     # ------------------------------------------------------------------ the step
     def step(self, entries: Sequence, logits_out: Optional[torch.Tensor] = None) -> torch.Tensor:

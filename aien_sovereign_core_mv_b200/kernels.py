@@ -130,6 +130,8 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_gemv_stream_residual": [P, L, P, L, P, L, P, I, P, L, P, I, I, I, P],
         "aien_gemv_stream_grid": [I],
         "aien_feed_token_ids": [P, P, P, I, P],
+        "aien_copy_spans": [P, c_size_t, I, c_size_t, c_size_t, c_size_t, P],
+        "aien_zero_fill": [P, c_size_t, P],
         "aien_scale_rows_ssq": [P, L, P, I, F, P, L, I, I, P],
         "aien_gemm_tc_error": [],
         "aien_attention_prefill_tc_error": [],
@@ -561,6 +563,24 @@ def feed_token_ids(token_ids: torch.Tensor, src: torch.Tensor, prev: torch.Tenso
     _dev(token_ids, src, prev)
     assert token_ids.dtype == torch.int32 and src.dtype == torch.int32 and prev.dtype == torch.int32 and src.numel() >= token_ids.numel()
     _check(lib().aien_feed_token_ids(_p(token_ids), _p(src), _p(prev), token_ids.numel(), _stream()), "feed_token_ids")
+
+
+def copy_rows(storage: torch.Tensor, src: int, dst: int, count: int = 1) -> None:
+    """storage[:, dst:dst+count] = storage[:, src:src+count] for a contiguous [runs, rows, ...] tensor: the copy
+    of a cache page (count = tokens a page) or of a state slot in every run of a cache group."""
+    _dev(storage)
+    assert storage.is_contiguous() and storage.dim() >= 2
+    row = storage[0, 0].numel() * storage.element_size()
+    _check(lib().aien_copy_spans(_p(storage), storage.shape[1] * row, storage.shape[0], src * row, dst * row, count * row, _stream()),
+           "copy_spans")
+
+
+def zero_fill(t: torch.Tensor) -> torch.Tensor:
+    """Zeroes a contiguous device tensor in place (the cache pools at start: the paged kernels load whole pages)."""
+    _dev(t)
+    assert t.is_contiguous()
+    _check(lib().aien_zero_fill(_p(t), t.numel() * t.element_size(), _stream()), "zero_fill")
+    return t
 
 
 def scale_rows_ssq(xw: torch.Tensor, ssq: torch.Tensor, parts: int, eps: float, out: torch.Tensor) -> None:

@@ -1066,3 +1066,24 @@ def test_sampling_edges_of_the_nucleus_and_of_top_k(K, V):
     K.sample_rows(lg, f([0.0] * R, torch.float32), f([1.0] * R, torch.float32), f([0] * R, torch.int32),
                   f([7] * R, torch.int64), f(list(range(R)), torch.int64), f([0] * R, torch.int32), scratch, ids, lps)
     assert ids.cpu().tolist() == [order[0]] * R and abs(lps[0].item() - math.log(16.0 / 36.0)) < 1e-5
+
+
+def test_cache_housekeeping_kernels(K):
+    """The copy of a page in every run of a group (16-byte and odd row sizes, spans that touch) and zero fill
+    from an odd address."""
+    for shape, dtype in (((3, 64, 2, 16), torch.bfloat16), ((2, 40, 5), torch.float32), ((4, 17, 3), torch.int8)):
+        st = torch.arange(int(np.prod(shape)), dtype=torch.float32).reshape(shape).to(dtype).cuda()
+        want = st.clone()
+        want[:, 8:16] = want[:, 0:8]
+        K.copy_rows(st, 0, 8, 8)
+        assert torch.equal(st, want)
+        want[:, 1] = want[:, 7]
+        K.copy_rows(st, 7, 1)
+        assert torch.equal(st, want)
+        with pytest.raises(K.KernelError):
+            K.copy_rows(st, 0, 4, 8)                              # the spans overlap
+    buf = torch.full((1000,), 7, dtype=torch.uint8, device="cuda")
+    K.zero_fill(buf[3:990])
+    assert (buf[3:990] == 0).all() and (buf[:3] == 7).all() and (buf[990:] == 7).all()
+    big = torch.full((1 << 20,), 3.0, device="cuda")
+    assert (K.zero_fill(big) == 0).all()
