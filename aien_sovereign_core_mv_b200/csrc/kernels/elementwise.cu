@@ -383,7 +383,7 @@ qk_norm_rope_kv_write_hd128_kernel(
 // rows are requested before the first is used.  A third of the instructions per row of the kernel
 // above, which is what bounds it.
 template <int HB>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 qk_norm_rope_kv_write_hd128_pairs_kernel(
     const __nv_bfloat16* q, long q_stride, int nq, const __nv_bfloat16* __restrict__ k, long k_stride,
     const __nv_bfloat16* __restrict__ v, long v_stride, int nkv, __nv_bfloat16* q_out, long q_out_stride,
@@ -419,6 +419,12 @@ qk_norm_rope_kv_write_hd128_pairs_kernel(
         const float4 c0 = ld_act4(cp), c1 = ld_act4(cp + 4), s0 = ld_act4(sp), s1 = ld_act4(sp + 4);
         cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
         sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+    }
+    // the first half of a row is a c - b s, the second a s + b c with a, b = (own, partner) and (partner, own):
+    // either way own * c + partner * (-+ s), so the sign goes into the sine once
+    if (l16 < 8) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sn[e] = -sn[e];
     }
     // this lane's heads: 2 * pair + half, pair = (warp >> 2) + 2 * gridDim.y * i + 2 * blockIdx.y
     const int pstep = 2 * gridDim.y;
@@ -467,13 +473,8 @@ qk_norm_rope_kv_write_hd128_pairs_kernel(
 #pragma unroll
             for (int e = 0; e < 8; ++e) y[e] = __shfl_xor_sync(0xffffffffu, x[e], 8);        // the rotation partner, 64 values away
             if (rotate) {
-                if (l16 < 8) {
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) x[e] = x[e] * cs[e] - y[e] * sn[e];
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) x[e] = y[e] * sn[e] + x[e] * cs[e];
-                }
+                for (int e = 0; e < 8; ++e) x[e] = fmaf(y[e], sn[e], x[e] * cs[e]);
             }
             if (!valid || (!is_q && slot < 0)) continue;
             uint4 o;
@@ -782,8 +783,21 @@ AIEN_API int aien_qk_norm_rope_kv_write(
     if (hd == 128 && act_dt == AIEN_DT_BF16 && (k == nullptr || kv_dt == AIEN_DT_BF16) && (cos_t == nullptr || rot == 128) && a16 &&
         ((in_dt == AIEN_DT_BF16 && nparts == 1) || in_dt == AIEN_DT_F32)) {
         const dim3 fast_grid((T + QK_TOKENS - 1) / QK_TOKENS, grid.y);
-        // few tokens: the heads of a token group are shared out over two or four CTAs, so that the grid fills the GPU
-        const unsigned head_ctas = fast_grid.x >= 512 ? 1u : (fast_grid.x >= 256 || n_heads <= 16 ? 2u : 4u);
+        // the heads of a token group are shared out over one, two or four CTAs: as many as make the fewest
+        // waves of work over the GPU (three CTAs an SM), a CTA's fixed part (its tokens' rotation tables and
+        // the norm weights) counted as 15 % of a whole token group
+        unsigned head_ctas = 1;
+        {
+            int sms = 148, dev = 0;
+            if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+            const long slots = 3L * sms;
+            double best = 1e30;
+            for (unsigned hc = 1; hc <= 4; hc *= 2) {
+                if (hc > 1 && (int)(hc * 8) > n_heads) break;
+                const double cost = (double)(((long)fast_grid.x * hc + slots - 1) / slots) * (1.0 / hc + 0.15);
+                if (cost < best) { best = cost; head_ctas = hc; }
+            }
+        }
         const bool wide = (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0 &&
                           ((q_stride | k_stride | v_stride | q_out_stride) & 7) == 0;
         if (in_dt == AIEN_DT_BF16 && T >= 128 && wide)
