@@ -331,8 +331,12 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    ad_merge_chunks<NH>(smem, part_out, part_ml, out + (size_t)t * out_stride + (size_t)kvh * G * hd, (size_t)zt * nq + kvh * G,
-                        G, hd, max_splits, s_lo, s_hi - s_lo + 1, threadIdx.x, AD_WARPS * 32, [] { __syncthreads(); });
+    if (hd <= 128)
+        ad_merge_chunks<NH, 1>(smem, part_out, part_ml, out + (size_t)t * out_stride + (size_t)kvh * G * hd, (size_t)zt * nq + kvh * G,
+                               G, hd, max_splits, s_lo, s_hi - s_lo + 1, threadIdx.x, AD_WARPS * 32, [] { __syncthreads(); });
+    else
+        ad_merge_chunks<NH, 2>(smem, part_out, part_ml, out + (size_t)t * out_stride + (size_t)kvh * G * hd, (size_t)zt * nq + kvh * G,
+                               G, hd, max_splits, s_lo, s_hi - s_lo + 1, threadIdx.x, AD_WARPS * 32, [] { __syncthreads(); });
 }
 
 template <int HS, int NT>
@@ -345,7 +349,7 @@ static int launch_decode(const void* q, long q_stride, const void* kc, const voi
     size_t loop_bytes = ((size_t)AD_CHUNK * NH + 2 * NH) * 4 + (size_t)NH * AD_CHUNK * 2;          // scores, max/denominator, probabilities
     if (fq.k != nullptr) loop_bytes += (size_t)AD_WARPS * 256 * 4 + (size_t)NH * hd * 2 + 16;      // fused q/k scratch, q
     const size_t comb_bytes = 0;
-    const size_t merge_bytes = ((size_t)2 * max_splits * NH + NH) * 4;
+    const size_t merge_bytes = ad_merge_scratch_floats(max_splits, nq / nkv, hd) * 4;
     size_t smem = loop_bytes > comb_bytes ? loop_bytes : comb_bytes;
     if (merge_bytes > smem) smem = merge_bytes;
     const int misc_bytes = (int)((smem + 127) & ~(size_t)127);           // per-warp scratch, combine and merge areas

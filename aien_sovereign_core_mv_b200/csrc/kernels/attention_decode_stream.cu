@@ -387,7 +387,7 @@ paged_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
             }
             if (solo || s_is_last) {
                 if (!solo) __threadfence();
-                ad_merge_chunks<NH>(misc, part_out, part_ml, out + (size_t)m.t * out_stride + (size_t)m.kvh * G * HD,
+                ad_merge_chunks<NH, 1>(misc, part_out, part_ml, out + (size_t)m.t * out_stride + (size_t)m.kvh * G * HD,
                                     (size_t)m.zt * nq + m.kvh * G, G, HD, max_splits, m.s_lo, m.s_hi - m.s_lo + 1, tid,
                                     DS_MATH_WARPS * 32, [] { ds_math_sync(); });
             }
@@ -399,10 +399,10 @@ paged_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
 // Shared memory of one CTA: alignment slack, the ring, two query buffers, two DsMeta, the barriers,
 // and the scratch of the phases or of the merge, whichever is larger.  Up to 113 KB two CTAs share an SM.
 constexpr size_t DS_SMEM_LIMIT = 200 * 1024;
-static size_t ds_smem_bytes(int hd, int nt, int max_splits, size_t* misc_out) {
+static size_t ds_smem_bytes(int hd, int nt, int G, int max_splits, size_t* misc_out) {
     const size_t NH = (size_t)nt * 8;
     const size_t loop_bytes = ((size_t)(DS_CHUNK + 4) * NH + 2 * NH) * 4 + NH * (DS_CHUNK + 8) * 2;
-    const size_t merge_bytes = ((size_t)2 * max_splits * NH + NH) * 4;
+    const size_t merge_bytes = ad_merge_scratch_floats(max_splits, G, hd) * 4;
     const size_t misc_bytes = ((loop_bytes > merge_bytes ? loop_bytes : merge_bytes) + 127) & ~(size_t)127;
     if (misc_out) *misc_out = misc_bytes;
     return 1024 + (size_t)DS_SLOTS * DS_CHUNK * hd * 2 + 2 * NH * hd * 2 + 2 * sizeof(DsMeta) + 16 * DS_SLOTS + 16 + misc_bytes;
@@ -435,7 +435,7 @@ static int launch_decode_stream(const CUtensorMap& mk, const CUtensorMap& mv, co
                                 int* counters, void* out, long out_stride, int nq, int nkv, int page_size, int window, float scale,
                                 int max_splits, int T, int cache_rows, cudaStream_t stream) {
     size_t misc_bytes = 0;
-    const size_t smem = ds_smem_bytes(HD, NT, max_splits, &misc_bytes);
+    const size_t smem = ds_smem_bytes(HD, NT, nq / nkv, max_splits, &misc_bytes);
     if (smem > DS_SMEM_LIMIT) return AIEN_E_SHAPE;
     auto kern = paged_decode_stream_kernel<HD, NT>;
     static size_t configured = 0;
@@ -472,7 +472,7 @@ using namespace aien;
 AIEN_API int aien_paged_attention_decode_stream_supports(int nq, int nkv, int hd, int page_size, int max_splits) {
     if (nkv <= 0 || nq % nkv != 0 || nq / nkv > 16) return 0;
     if (!(hd == 64 || hd == 128) || page_size < 8 || page_size > 128 || (page_size & 7) || 128 % page_size != 0) return 0;
-    return (max_splits > 0 && ds_smem_bytes(hd, (nq / nkv + 7) / 8, max_splits, nullptr) <= DS_SMEM_LIMIT) ? 1 : 0;
+    return (max_splits > 0 && ds_smem_bytes(hd, (nq / nkv + 7) / 8, nq / nkv, max_splits, nullptr) <= DS_SMEM_LIMIT) ? 1 : 0;
 }
 
 // Arguments as aien_paged_attention_decode, plus the number of rows of the caches ([cache_rows, nkv*hd]).
