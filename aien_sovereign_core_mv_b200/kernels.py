@@ -495,12 +495,12 @@ def gemm_tc_splits(M: int, N: int, K_: int) -> int:
     """Ranges of K for a product with few rows: enough CTAs to occupy the GPU (148 SMs, two CTAs
     each) when the tile grid alone is small.  Depends on the shapes only."""
     if M > 64 and N >= 256:
-        # the persistent kernel with 128 x 256 tiles: as many ranges as still give every range 8 k-blocks
-        # and every SM at most one unit
+        # the persistent kernel with 128 x 256 tiles: as many ranges (eight at most) as still give every range
+        # 8 k-blocks and every SM at most one unit (128 rows x 4,096 x 12,288: 16 tiles, 4 -> 8 ranges, 29.9 -> 25.9 us)
         tiles = ((M + 127) // 128) * ((N + 255) // 256)
         if tiles >= 148:
             return 1
-        return gemm_tc_ranges(K_, max(1, min(4, 148 // tiles, K_ // 512)))
+        return gemm_tc_ranges(K_, max(1, min(8, 148 // tiles, K_ // 512)))
     tiles = ((M + 127) // 128) * ((N + 127) // 128)
     if tiles >= 148:
         return 1
