@@ -459,6 +459,47 @@ def test_paged_attention_decode_stream_gives_the_same_bits(K, nq, nkv, hd, page,
     assert K.attention_decode_stream_error() == 0
 
 
+@pytest.mark.parametrize("nq,nkv,hd,page,window,lens", [(8, 2, 128, 16, 0, [20001, 9000, 130]), (4, 1, 64, 64, 12000, [16500, 1]),
+                                                          (6, 2, 96, 16, 0, [8300, 700])])
+def test_decode_attention_over_long_contexts(K, nq, nkv, hd, page, window, lens):
+    """Up to 157 chunks of 128 keys per token: the merge adds them in eight interleaved series with
+    several chunks of a series in flight, beyond one round of every loop; three keys spread over the
+    context decide head 0 of every token.  Both kernels (the same bits where both take the shape), with a
+    window that starts inside the context."""
+    dtype = torch.bfloat16
+    rng = np.random.default_rng(hd + len(lens))
+    kc, vc, bt, mb, dense = paged_setup(rng, lens, nkv, hd, page, dtype, sum((n + page - 1) // page for n in lens) + 8)
+    T = len(lens)
+    positions = torch.tensor([n - 1 for n in lens], dtype=torch.int32).cuda()
+    seq_of = torch.arange(T, dtype=torch.int32).cuda()
+    q = torch.tensor(rng.standard_normal((T, nq * hd)), dtype=torch.float32).to(dtype).cuda()
+    scale = 1.0 / math.sqrt(hd)
+    splits = (max(lens) + 127) // 128
+    # for head 0 of every token three keys stand out, in chunks that fall into different series and rounds of
+    # the merge; a chunk lost or weighed wrongly moves that head's result by a third
+    btc = bt.cpu().numpy()
+    for s_, n in enumerate(lens):
+        lo = max(0, n - window) if window > 0 else 0
+        for p_ in sorted({lo + (n - 1 - lo) * f // 100 for f in (3, 47, 96)}):
+            kv = (q[s_, :hd].float().cpu() * 1.5).to(dtype)
+            dense[s_][0][p_, 0] = kv.float()
+            kc[int(btc[s_, p_ // page]) * page + p_ % page, 0] = kv.cuda()
+    want = attention_reference(q.float().double().cpu().numpy().reshape(-1, nq, hd), dense, list(range(T)), [n - 1 for n in lens],
+                               nq, nkv, hd, window, scale)
+    impls = ["direct"] + (["stream"] if K.decode_stream_supports(nq, nkv, hd, page, splits) else [])
+    outs = []
+    for impl in impls:
+        part_out = torch.empty(T * nq * splits * hd, device="cuda"); part_ml = torch.empty(T * nq * splits * 2, device="cuda")
+        out = torch.full((T, nq * hd), 5.0, dtype=dtype, device="cuda")
+        K.paged_attention_decode(q, kc, vc, bt, mb, seq_of, positions, out, part_out, part_ml, nq, nkv, hd, page, window, scale, splits, impl=impl)
+        torch.cuda.synchronize()
+        assert K.attention_decode_stream_error() == 0
+        H.assert_close(out.float().cpu().numpy(), want, 1.5e-2, f"decode attention over {max(lens)} keys ({impl})")
+        outs.append(out)
+    if len(outs) == 2:
+        assert torch.equal(outs[0], outs[1])
+
+
 def test_decode_attention_one_far_key_decides(K):
     nq, nkv, hd, page, n = 4, 1, 64, 16, 1500
     for far in (0, 255, 256, 1023, 1499):
