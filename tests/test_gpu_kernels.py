@@ -732,6 +732,38 @@ def test_paged_attention_prefill_chooses_ranges_for_few_tiles_over_a_long_contex
     H.assert_close(outs[1], want, 1.5e-2, "chosen ranges")
 
 
+@pytest.mark.parametrize("splits", [0, 1, 5])
+def test_prefill_attention_of_a_portion_at_the_end_of_a_long_context(K, splits):
+    """256 tokens at offset 20,000: 159 key blocks per tile, the ring and every barrier go round many
+    times; three keys far apart decide head 0 of every row.  With every tile's keys in one range, in
+    five, and as the launch chooses."""
+    nq, nkv, hd, page, n, ql = 8, 2, 128, 16, 20256, 256
+    rng = np.random.default_rng(3)
+    kc, vc, bt, mb, dense = paged_setup(rng, [n], nkv, hd, page, torch.bfloat16, n // page + 9)
+    q = torch.tensor(rng.standard_normal((ql, nq * hd)), dtype=torch.float32)
+    q[:, :hd] = q[0, :hd]                                                      # head 0 asks the same of every row
+    q = q.to(torch.bfloat16).cuda()
+    btc = bt.cpu().numpy()
+    for p_ in (611, 9500, 19990):
+        kv = (q[0, :hd].float().cpu() * 1.5).to(torch.bfloat16)
+        dense[0][0][p_, 0] = kv.float()
+        kc[int(btc[0, p_ // page]) * page + p_ % page, 0] = kv.cuda()
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32).cuda()
+    scale = 1.0 / math.sqrt(hd)
+    room = 2 * K.PREFILL_TILE * nq * 8 * (hd + 2)
+    scratch = torch.full((room,), float("nan"), device="cuda") if splits != 1 else None
+    out = torch.empty(ql, nq * hd, dtype=torch.bfloat16, device="cuda")
+    K.paged_attention_prefill(q, kc, vc, bt, mb, i32([0, ql]), i32([n]), i32([0, 0]), i32([0, 128]), 2, out, nq, nkv, hd, page, 0, scale,
+                              impl="tc", scratch=scratch, max_ctx=n, splits=splits if splits > 1 else 0)
+    torch.cuda.synchronize()
+    assert K.attention_prefill_tc_error() == 0
+    rows = [0, 1, 63, 127, 128, 129, 200, 255]                               # the reference for some rows of both tiles
+    want = attention_reference(q[rows].float().double().cpu().numpy().reshape(-1, nq, hd), dense, [0] * len(rows), [n - ql + r for r in rows],
+                               nq, nkv, hd, 0, scale)
+    H.assert_close(out[rows].float().cpu().numpy(), want, 1.5e-2, f"prefill attention at offset 20,000 ({splits} ranges)")
+    assert torch.isfinite(out.float()).all()
+
+
 def test_prefill_attention_growing_maximum(K):
     """Scores that keep growing with the key position: every row's maximum rises block after
     block, so the tensor-memory kernel must rescale its output again and again."""
