@@ -343,6 +343,141 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The persistent form with tiles of 256 x 256: two accumulators of 128 rows side by side in tensor
+// memory (all 512 columns), eight products per k-block (the two row halves of A against the same 256
+// rows of W).  What bounds the 128 x 256 tile is shared memory, not the tensor core: per k-block TMA
+// writes 48 KB and the four products read 48 KB, 768 cycles at 128 bytes a cycle for 512 cycles of
+// products (measured: 756).  A 256 x 256 tile writes 64 KB and reads 96 KB for 1,024 cycles of
+// products.  The price: no second pair of accumulators, so a tile's epilogue (eight warps) does not
+// run under the next tile's main loop (the producer does fill the ring meanwhile), and half as many
+// tiles to deal out; tc_plan chooses by the number of waves either way.  No ranges of K.
+struct TcM {
+    static constexpr int BM = 256, BN = 256;
+    static constexpr int STAGE_A = BM * TC_BK * 2, STAGE_B = BN * TC_BK * 2;      // 32 KB each
+    static constexpr int STAGES = 3;
+    static constexpr int SMEM = STAGES * (STAGE_A + STAGE_B) + 1024 + 256;
+    static constexpr int THREADS = 320;                                            // producer, MMA, eight epilogue warps
+};
+
+template <int EPI, typename TC>
+__global__ void __launch_bounds__(TcM::THREADS, 1)
+gemm_tc_persistent_m256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                               TC* __restrict__ out, long ldc, int M, int N, int K) {
+    using P = TcM;
+    constexpr int STAGES = P::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sA = base, sB = base + STAGES * P::STAGE_A;
+    const uint32_t bars = sB + STAGES * P::STAGE_B;
+    const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, tfull = bars + 16 * STAGES, tempty = tfull + 8;
+    const uint32_t tmem_slot = tempty + 8;
+    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen + (tmem_slot - base));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tiles = (M + P::BM - 1) / P::BM, n_tiles = (N + P::BN - 1) / P::BN;
+    const int tiles = m_tiles * n_tiles;                 // M-tiles fastest: the CTAs that run together share W
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+
+    griddep_launch();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(tfull, 1);
+        mbar_init(tempty, 8);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_acc = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // the first ring of W goes out before the wait for the kernel ahead in the stream: A is its result, W is not
+            const int t0 = blockIdx.x;
+            const uint32_t ahead = t0 < tiles ? (uint32_t)min(num_kb, STAGES) : 0u;
+            for (uint32_t i = 0; i < ahead; ++i) {
+                mbar_expect_tx(full0 + 8 * i, P::STAGE_A + P::STAGE_B);
+                tma_load_2d(sB + i * P::STAGE_B, &map_w, full0 + 8 * i, (int)i * TC_BK, (t0 / m_tiles) * P::BN);
+            }
+            griddep_wait();
+            uint32_t it = 0;
+            for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
+                const int m0 = (t % m_tiles) * P::BM, n0 = (t / m_tiles) * P::BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (it < ahead) {                                  // W is on its way already
+                        tma_load_2d(sA + s * P::STAGE_A, &map_a, full0 + 8 * s, kb * TC_BK, m0);
+                        continue;
+                    }
+                    if (it >= (uint32_t)STAGES) mbar_wait(empty0 + 8 * s, ((it / STAGES) - 1) & 1, 1);
+                    mbar_expect_tx(full0 + 8 * s, P::STAGE_A + P::STAGE_B);
+                    tma_load_2d(sA + s * P::STAGE_A, &map_a, full0 + 8 * s, kb * TC_BK, m0);
+                    tma_load_2d(sB + s * P::STAGE_B, &map_w, full0 + 8 * s, kb * TC_BK, n0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // the whole warp walks the schedule; one lane issues
+        const bool issuer = lane == 0;
+        const uint32_t idesc = umma_idesc_bf16(TC_BM, P::BN, false);
+        const uint64_t da0 = make_desc_sw128(sA), db0 = make_desc_sw128(sB);
+        uint32_t it = 0;
+        int i = 0;
+        for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++i) {
+            if (i >= 1) {                                              // the epilogue has drained the accumulators
+                mbar_wait(tempty, (i - 1) & 1, 4);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int s = it % STAGES;
+                mbar_wait(full0 + 8 * s, (it / STAGES) & 1, 2);        // what TMA wrote is visible once the barrier has completed
+                const uint64_t da = da0 + (uint64_t)((s * P::STAGE_A) >> 4), db = db0 + (uint64_t)((s * P::STAGE_B) >> 4);
+                if (issuer) {
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k) {
+                        const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+                        umma_bf16(tmem_acc, da + 2 * k, db + 2 * k, idesc, accum);                                        // rows 0..127
+                        umma_bf16(tmem_acc + P::BN, da + (uint64_t)((TC_BM * 128) >> 4) + 2 * k, db + 2 * k, idesc, accum);   // rows 128..255
+                    }
+                    umma_commit(empty0 + 8 * s);
+                }
+            }
+            if (issuer) umma_commit(tfull);
+        }
+    } else {
+        const int e = warp - 2, half = e >> 2, quarter = warp & 3;     // a warp reads the lanes 32 (warp % 4) .. of tensor memory
+        int i = 0;
+        for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++i) {
+            const int m0 = (t % m_tiles) * P::BM + half * TC_BM, n0 = (t / m_tiles) * P::BN;
+            mbar_wait(tfull, i & 1, 3);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = m0 + quarter * 32 + lane;
+#pragma unroll 1
+            for (int c0 = 0; c0 < P::BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * P::BN + c0), r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row < M && n0 + c0 < N) tc_store_chunk<EPI, TC>(r, out, ldc, row, n0, c0, N);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(512u) : "memory");
+    }
+}
+
 static int tc_num_sms() {
     static int n = 0;
     if (n == 0) {
@@ -373,6 +508,24 @@ static int launch_tc_persistent(const void* A, long lda, const void* W, long ldw
     return launch_status();
 }
 
+template <int EPI, typename TC>
+static int launch_tc_persistent_m256(const void* A, long lda, const void* W, long ldw, void* out, long ldc, int M, int N, int K,
+                                     cudaStream_t stream) {
+    CUtensorMap ma, mw;
+    if (!make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TC_BK, TcM::BM) || !make_map(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, TC_BK, TcM::BN))
+        return AIEN_E_STATE;
+    auto kern = gemm_tc_persistent_m256_kernel<EPI, TC>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcM::SMEM) != cudaSuccess) return AIEN_E_STATE;
+        configured = true;
+    }
+    const long total = (long)((M + TcM::BM - 1) / TcM::BM) * ((N + TcM::BN - 1) / TcM::BN);
+    const unsigned grid = (unsigned)(total < tc_num_sms() ? total : tc_num_sms());
+    launch_chain(kern, dim3(grid), dim3(TcM::THREADS), (size_t)TcM::SMEM, stream, ma, mw, (TC*)out, ldc, M, N, K);
+    return launch_status();
+}
+
 // Which kernel a product takes: 0 the one-tile-per-CTA kernel, 256 the persistent kernel with
 // 128 x 256 tiles.  The persistent one once its units (tiles x ranges of K) give every SM one, and
 // for any product of more than 64 rows of A by at least 256 of W with three fifths of that: its
@@ -384,12 +537,31 @@ static int tc_plan(int M, int N, int ranges) {
     static int forced = -1;
     if (forced < 0) {
         const char* e = getenv("AIEN_B200_GEMM_TC");
-        forced = e == nullptr ? 1 : (!strcmp(e, "tile") ? 0 : (!strcmp(e, "p256") ? 256 : 1));
+        forced = e == nullptr ? 1 : (!strcmp(e, "tile") ? 0 : ((!strcmp(e, "p256") || !strcmp(e, "m256")) ? 256 : 1));
     }
     if (forced != 1) return forced;
     const long units = (long)((M + TC_BM - 1) / TC_BM) * ((N + 255) / 256) * ranges;
     if (units >= tc_num_sms()) return 256;
     return (M > 64 && N >= 256 && 5 * units >= 3 * tc_num_sms()) ? 256 : 0;
+}
+
+// Whether a product that runs on the persistent kernel takes tiles of 256 x 256 instead of 128 x 256: by
+// the time either way, in cycles: waves of tiles x (k-blocks x the cycles shared memory needs for one
+// (768 and 1,250 by the count of bytes, 756 measured for the first) + what of a tile's epilogue stays
+// visible).  AIEN_B200_GEMM_TC=m256 | p256 pins it.
+static bool tc_use_m256(int M, int N, int K, int ranges) {
+    static int forced = -1;
+    if (forced < 0) {
+        const char* e = getenv("AIEN_B200_GEMM_TC");
+        forced = e == nullptr ? 0 : (!strcmp(e, "m256") ? 1 : (!strcmp(e, "p256") ? 2 : 0));
+    }
+    if (ranges != 1 || forced == 2) return false;
+    if (forced == 1) return true;
+    if (M <= TC_BM) return false;
+    const long sms = tc_num_sms(), kb = (K + TC_BK - 1) / TC_BK;
+    const long t256 = (long)((M + 127) / 128) * ((N + 255) / 256), t512 = (long)((M + 255) / 256) * ((N + 255) / 256);
+    const long c256 = ((t256 + sms - 1) / sms) * (kb * 768 + 700), c512 = ((t512 + sms - 1) / sms) * (kb * 1250 + 4500);
+    return c512 * 100 < c256 * 97;
 }
 
 static int tc_a_rows(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }
@@ -455,6 +627,13 @@ AIEN_API int aien_gemm_tc_ranges(int K, int splits) {
     return (total_kb + kb_per_split - 1) / kb_per_split;
 }
 
+// Whether aien_gemm_tc runs this product on the persistent kernel with tiles of 256 x 256 (1) or not (0).
+AIEN_API int aien_gemm_tc_m256_supports(int M, int N, int K, int splits) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    const int ranges = aien_gemm_tc_ranges(K, splits);
+    return (tc_plan(M, N, ranges) == 256 && tc_use_m256(M, N, K, ranges)) ? 1 : 0;
+}
+
 AIEN_API int aien_gemm_tc(const void* A, long lda, const void* W, long ldw, void* out, int c_dt, long ldc,
                           int M, int N, int K, int epilogue, int splits, size_t part_stride, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
@@ -466,6 +645,12 @@ AIEN_API int aien_gemm_tc(const void* A, long lda, const void* W, long ldw, void
     if (epilogue == 0 || epilogue == 1) {
         const int plan = tc_plan(M, N, aien_gemm_tc_ranges(K, splits));
 #define TCP_CASE(BNV, EPIV, T) return launch_tc_persistent<BNV, EPIV, T>(A, lda, W, ldw, out, ldc, M, N, K, splits, part_stride, stream)
+        if (plan == 256 && tc_use_m256(M, N, K, aien_gemm_tc_ranges(K, splits))) {
+            if (epilogue == 0 && c_dt == AIEN_DT_BF16) return launch_tc_persistent_m256<0, __nv_bfloat16>(A, lda, W, ldw, out, ldc, M, N, K, stream);
+            if (epilogue == 0 && c_dt == AIEN_DT_F32) return launch_tc_persistent_m256<0, float>(A, lda, W, ldw, out, ldc, M, N, K, stream);
+            if (epilogue == 1 && c_dt == AIEN_DT_BF16) return launch_tc_persistent_m256<1, __nv_bfloat16>(A, lda, W, ldw, out, ldc, M, N, K, stream);
+            if (epilogue == 1 && c_dt == AIEN_DT_F32) return launch_tc_persistent_m256<1, float>(A, lda, W, ldw, out, ldc, M, N, K, stream);
+        }
         if (plan == 256) {
             if (epilogue == 0 && c_dt == AIEN_DT_BF16) TCP_CASE(256, 0, __nv_bfloat16);
             if (epilogue == 0 && c_dt == AIEN_DT_F32) TCP_CASE(256, 0, float);

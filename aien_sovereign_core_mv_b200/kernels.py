@@ -126,6 +126,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_gemv_stream_error": [],
         "aien_gemm_tc": [P, L, P, L, P, I, L, I, I, I, I, I, c_size_t, P],
         "aien_gemm_tc_ranges": [I, I],
+        "aien_gemm_tc_m256_supports": [I, I, I, I],
         "aien_gemv_stream_scaled": [P, L, P, L, P, I, L, I, I, I, I, P, I, F, P],
         "aien_gemv_stream_residual": [P, L, P, L, P, L, P, I, P, L, P, I, I, I, P],
         "aien_gemv_stream_grid": [I],
@@ -489,6 +490,11 @@ PARTIALS_MAX_BYTES = 296 * 128 * 128 * 4 + (1 << 16)
 def gemm_tc_ranges(K_: int, splits: int) -> int:
     """How many ranges of K the tensor-core kernel makes when asked for ``splits``."""
     return int(lib().aien_gemm_tc_ranges(int(K_), int(splits)))
+
+
+def gemm_tc_takes_256_rows(M: int, N: int, K_: int, splits: int = 1) -> bool:
+    """Whether gemm_tc runs this product on the persistent kernel with tiles of 256 x 256."""
+    return bool(lib().aien_gemm_tc_m256_supports(int(M), int(N), int(K_), int(splits)))
 
 
 def gemm_tc_splits(M: int, N: int, K_: int) -> int:

@@ -630,6 +630,44 @@ def test_gemm_tensor_core(K, out_dtype, M, N, K_):
     assert (out_full[:, N:] == 9.0).all()                    # nothing written beyond N
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K_", [(2048, 4096, 1024), (1000, 9000, 1032), (4100, 4112, 1032)])
+def test_gemm_tensor_core_tiles_of_256_rows(K, M, N, K_, out_dtype):
+    """Products that the persistent kernel takes with tiles of 256 x 256 (two accumulators side by side,
+    eight epilogue warps): last row tiles with 232 and 4 rows, widths that are no multiple of the tile, a K
+    that is no multiple of the k-block, more tiles than SMs (two per CTA, so the accumulators are handed
+    back and forth)."""
+    assert K.gemm_tc_takes_256_rows(M, N, K_) and not K.gemm_tc_takes_256_rows(2048, 6144, 4096) and not K.gemm_tc_takes_256_rows(128, 24576, 4096)
+    g = torch.Generator().manual_seed(M + N)
+    a = torch.randn(M, K_, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K_, generator=g) / math.sqrt(K_)).to(torch.bfloat16).cuda()
+    out_full = torch.full((M, N + 8), 9.0, dtype=out_dtype, device="cuda")
+    out = out_full[:, :N]
+    K.gemm_tc(a, w, out)
+    torch.cuda.synchronize()
+    assert K.gemm_tc_error() == 0
+    want = a.double().cpu() @ w.double().cpu().T
+    H.assert_close(out.float().cpu().numpy(), want.numpy(), 2e-5 if out_dtype == torch.float32 else 1e-2, f"tc gemm, 256-row tiles, {M}x{N}x{K_}")
+    assert (out_full[:, N:] == 9.0).all()
+
+
+def test_gemm_tensor_core_tiles_of_256_rows_with_swiglu(K):
+    M, I, Hd = 2048, 2056, 1032
+    assert K.gemm_tc_takes_256_rows(M, 2 * I, Hd)
+    g = torch.Generator().manual_seed(3)
+    a = torch.randn(M, Hd, generator=g).to(torch.bfloat16).cuda()
+    gate = (torch.randn(I, Hd, generator=g) / math.sqrt(Hd)).to(torch.bfloat16)
+    up = (torch.randn(I, Hd, generator=g) / math.sqrt(Hd)).to(torch.bfloat16)
+    inter = torch.stack([gate.view(I // 8, 8, Hd), up.view(I // 8, 8, Hd)], dim=1).reshape(2 * I, Hd).contiguous().cuda()
+    out = torch.empty(M, I, dtype=torch.bfloat16, device="cuda")
+    K.gemm_tc(a, inter, out, epilogue=1)
+    torch.cuda.synchronize()
+    assert K.gemm_tc_error() == 0
+    ad = a.double().cpu()
+    want = pm.swiglu((ad @ gate.double().T).numpy(), (ad @ up.double().T).numpy())
+    H.assert_close(out.float().cpu().numpy(), want, 1e-2, "tc gemm with 256-row tiles + swiglu")
+
+
 @pytest.mark.parametrize("M,I,Hd", [(150, 264, 136), (1100, 2152, 200)])     # the second: the persistent kernel
 def test_gemm_tensor_core_swiglu_epilogue(K, M, I, Hd):
     g = torch.Generator().manual_seed(2)
