@@ -352,19 +352,20 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 // products.  The price: no second pair of accumulators, so a tile's epilogue (eight warps) does not
 // run under the next tile's main loop (the producer does fill the ring meanwhile), and half as many
 // tiles to deal out; tc_plan chooses by the number of waves either way.  No ranges of K.
-struct TcM {
-    static constexpr int BM = 256, BN = 256;
-    static constexpr int STAGE_A = BM * TC_BK * 2, STAGE_B = BN * TC_BK * 2;      // 32 KB each
+template <int BNV> struct TcM {
+    static constexpr int BM = 256, BN = BNV;                                       // BN 256, or 240 / 224 where that makes fewer waves
+    static constexpr int STAGE_A = BM * TC_BK * 2, STAGE_B = 256 * TC_BK * 2;      // 32 KB each (a narrower W tile leaves the rest unused)
     static constexpr int STAGES = 3;
     static constexpr int SMEM = STAGES * (STAGE_A + STAGE_B) + 1024 + 256;
     static constexpr int THREADS = 320;                                            // producer, MMA, eight epilogue warps
 };
 
-template <int EPI, typename TC>
-__global__ void __launch_bounds__(TcM::THREADS, 1)
+template <int BNV, int EPI, typename TC>
+__global__ void __launch_bounds__(TcM<BNV>::THREADS, 1)
 gemm_tc_persistent_m256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                                TC* __restrict__ out, long ldc, int M, int N, int K) {
-    using P = TcM;
+    using P = TcM<BNV>;
+    constexpr int W_BYTES = P::BN * TC_BK * 2;           // what one copy of W brings
     constexpr int STAGES = P::STAGES;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -402,7 +403,7 @@ gemm_tc_persistent_m256_kernel(const __grid_constant__ CUtensorMap map_a, const 
             const int t0 = blockIdx.x;
             const uint32_t ahead = t0 < tiles ? (uint32_t)min(num_kb, STAGES) : 0u;
             for (uint32_t i = 0; i < ahead; ++i) {
-                mbar_expect_tx(full0 + 8 * i, P::STAGE_A + P::STAGE_B);
+                mbar_expect_tx(full0 + 8 * i, P::STAGE_A + W_BYTES);
                 tma_load_2d(sB + i * P::STAGE_B, &map_w, full0 + 8 * i, (int)i * TC_BK, (t0 / m_tiles) * P::BN);
             }
             griddep_wait();
@@ -416,7 +417,7 @@ gemm_tc_persistent_m256_kernel(const __grid_constant__ CUtensorMap map_a, const 
                         continue;
                     }
                     if (it >= (uint32_t)STAGES) mbar_wait(empty0 + 8 * s, ((it / STAGES) - 1) & 1, 1);
-                    mbar_expect_tx(full0 + 8 * s, P::STAGE_A + P::STAGE_B);
+                    mbar_expect_tx(full0 + 8 * s, P::STAGE_A + W_BYTES);
                     tma_load_2d(sA + s * P::STAGE_A, &map_a, full0 + 8 * s, kb * TC_BK, m0);
                     tma_load_2d(sB + s * P::STAGE_B, &map_w, full0 + 8 * s, kb * TC_BK, n0);
                 }
@@ -458,12 +459,13 @@ gemm_tc_persistent_m256_kernel(const __grid_constant__ CUtensorMap map_a, const 
             mbar_wait(tfull, i & 1, 3);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int row = m0 + quarter * 32 + lane;
+            const int n_end = min(N, n0 + P::BN);                      // a tile of 240 or 224 columns ends inside its last chunk of 32
 #pragma unroll 1
             for (int c0 = 0; c0 < P::BN; c0 += 32) {
                 uint32_t r[32];
                 tmem_ld32(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * P::BN + c0), r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (row < M && n0 + c0 < N) tc_store_chunk<EPI, TC>(r, out, ldc, row, n0, c0, N);
+                if (row < M && n0 + c0 < n_end) tc_store_chunk<EPI, TC>(r, out, ldc, row, n0, c0, n_end);
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -508,22 +510,31 @@ static int launch_tc_persistent(const void* A, long lda, const void* W, long ldw
     return launch_status();
 }
 
-template <int EPI, typename TC>
-static int launch_tc_persistent_m256(const void* A, long lda, const void* W, long ldw, void* out, long ldc, int M, int N, int K,
-                                     cudaStream_t stream) {
+template <int BNV, int EPI, typename TC>
+static int launch_tc_persistent_m256_bn(const void* A, long lda, const void* W, long ldw, void* out, long ldc, int M, int N, int K,
+                                        cudaStream_t stream) {
+    using P = TcM<BNV>;
     CUtensorMap ma, mw;
-    if (!make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TC_BK, TcM::BM) || !make_map(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, TC_BK, TcM::BN))
+    if (!make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TC_BK, P::BM) || !make_map(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, TC_BK, P::BN))
         return AIEN_E_STATE;
-    auto kern = gemm_tc_persistent_m256_kernel<EPI, TC>;
+    auto kern = gemm_tc_persistent_m256_kernel<BNV, EPI, TC>;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcM::SMEM) != cudaSuccess) return AIEN_E_STATE;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P::SMEM) != cudaSuccess) return AIEN_E_STATE;
         configured = true;
     }
-    const long total = (long)((M + TcM::BM - 1) / TcM::BM) * ((N + TcM::BN - 1) / TcM::BN);
+    const long total = (long)((M + P::BM - 1) / P::BM) * ((N + P::BN - 1) / P::BN);
     const unsigned grid = (unsigned)(total < tc_num_sms() ? total : tc_num_sms());
-    launch_chain(kern, dim3(grid), dim3(TcM::THREADS), (size_t)TcM::SMEM, stream, ma, mw, (TC*)out, ldc, M, N, K);
+    launch_chain(kern, dim3(grid), dim3(P::THREADS), (size_t)P::SMEM, stream, ma, mw, (TC*)out, ldc, M, N, K);
     return launch_status();
+}
+
+template <int EPI, typename TC>
+static int launch_tc_persistent_m256(int bn, const void* A, long lda, const void* W, long ldw, void* out, long ldc, int M, int N, int K,
+                                     cudaStream_t stream) {
+    if (bn == 240) return launch_tc_persistent_m256_bn<240, EPI, TC>(A, lda, W, ldw, out, ldc, M, N, K, stream);
+    if (bn == 224) return launch_tc_persistent_m256_bn<224, EPI, TC>(A, lda, W, ldw, out, ldc, M, N, K, stream);
+    return launch_tc_persistent_m256_bn<256, EPI, TC>(A, lda, W, ldw, out, ldc, M, N, K, stream);
 }
 
 // Which kernel a product takes: 0 the one-tile-per-CTA kernel, 256 the persistent kernel with
@@ -545,23 +556,33 @@ static int tc_plan(int M, int N, int ranges) {
     return (M > 64 && N >= 256 && 5 * units >= 3 * tc_num_sms()) ? 256 : 0;
 }
 
-// Whether a product that runs on the persistent kernel takes tiles of 256 x 256 instead of 128 x 256: by
-// the time either way, in cycles: waves of tiles x (k-blocks x the cycles shared memory needs for one
-// (768 and 1,250 by the count of bytes, 756 measured for the first) + what of a tile's epilogue stays
-// visible).  AIEN_B200_GEMM_TC=m256 | p256 pins it.
-static bool tc_use_m256(int M, int N, int K, int ranges) {
+// Whether a product that runs on the persistent kernel takes tiles of 256 rows instead of 128 x 256, and how
+// wide (256, 240 or 224 columns; 0: no): by the time either way, in cycles: waves of tiles x (k-blocks x
+// the cycles shared memory needs for one + what of a tile's epilogue stays visible).  Per k-block the
+// 128 x 256 tile moves 96 KB through shared memory, 768 cycles at 128 bytes a cycle (756 measured); the
+// 256 x BN tile (64 + 3 BN / 8) KB, 5 % more measured.  AIEN_B200_GEMM_TC=m256 | p256 pins it (m256: 256 wide).
+static int tc_m256_cols(int M, int N, int K, int ranges) {
     static int forced = -1;
     if (forced < 0) {
         const char* e = getenv("AIEN_B200_GEMM_TC");
         forced = e == nullptr ? 0 : (!strcmp(e, "m256") ? 1 : (!strcmp(e, "p256") ? 2 : 0));
     }
-    if (ranges != 1 || forced == 2) return false;
-    if (forced == 1) return true;
-    if (M <= TC_BM) return false;
+    if (ranges != 1 || forced == 2) return 0;
+    if (forced == 1) return 256;
+    if (M <= TC_BM) return 0;
     const long sms = tc_num_sms(), kb = (K + TC_BK - 1) / TC_BK;
-    const long t256 = (long)((M + 127) / 128) * ((N + 255) / 256), t512 = (long)((M + 255) / 256) * ((N + 255) / 256);
-    const long c256 = ((t256 + sms - 1) / sms) * (kb * 768 + 700), c512 = ((t512 + sms - 1) / sms) * (kb * 1250 + 4500);
-    return c512 * 100 < c256 * 97;
+    const long t256 = (long)((M + 127) / 128) * ((N + 255) / 256);
+    long best = ((t256 + sms - 1) / sms) * (kb * 768 + 700) * 97 / 100;
+    int cols = 0;
+    for (int bn = 256; bn >= 224; bn -= 16) {
+        const long t = (long)((M + 255) / 256) * ((N + bn - 1) / bn), w = (t + sms - 1) / sms;
+        // narrower tiles pay where they shorten several waves; in a single wave more, smaller CTAs measured no faster
+        // (2,048 x 4,096 x 4,096: 144 tiles of 240 columns 51.9 us, 128 of 256 49.8 us)
+        if (bn < 256 && w == 1) continue;
+        const long c = w * (kb * (512 + 3 * bn) * 105 / 100 + 4500);
+        if (c < best) { best = c; cols = bn; }
+    }
+    return cols;
 }
 
 static int tc_a_rows(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }
@@ -631,7 +652,7 @@ AIEN_API int aien_gemm_tc_ranges(int K, int splits) {
 AIEN_API int aien_gemm_tc_m256_supports(int M, int N, int K, int splits) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     const int ranges = aien_gemm_tc_ranges(K, splits);
-    return (tc_plan(M, N, ranges) == 256 && tc_use_m256(M, N, K, ranges)) ? 1 : 0;
+    return (tc_plan(M, N, ranges) == 256 && tc_m256_cols(M, N, K, ranges) > 0) ? 1 : 0;
 }
 
 AIEN_API int aien_gemm_tc(const void* A, long lda, const void* W, long ldw, void* out, int c_dt, long ldc,
@@ -645,11 +666,12 @@ AIEN_API int aien_gemm_tc(const void* A, long lda, const void* W, long ldw, void
     if (epilogue == 0 || epilogue == 1) {
         const int plan = tc_plan(M, N, aien_gemm_tc_ranges(K, splits));
 #define TCP_CASE(BNV, EPIV, T) return launch_tc_persistent<BNV, EPIV, T>(A, lda, W, ldw, out, ldc, M, N, K, splits, part_stride, stream)
-        if (plan == 256 && tc_use_m256(M, N, K, aien_gemm_tc_ranges(K, splits))) {
-            if (epilogue == 0 && c_dt == AIEN_DT_BF16) return launch_tc_persistent_m256<0, __nv_bfloat16>(A, lda, W, ldw, out, ldc, M, N, K, stream);
-            if (epilogue == 0 && c_dt == AIEN_DT_F32) return launch_tc_persistent_m256<0, float>(A, lda, W, ldw, out, ldc, M, N, K, stream);
-            if (epilogue == 1 && c_dt == AIEN_DT_BF16) return launch_tc_persistent_m256<1, __nv_bfloat16>(A, lda, W, ldw, out, ldc, M, N, K, stream);
-            if (epilogue == 1 && c_dt == AIEN_DT_F32) return launch_tc_persistent_m256<1, float>(A, lda, W, ldw, out, ldc, M, N, K, stream);
+        const int wide = plan == 256 ? tc_m256_cols(M, N, K, aien_gemm_tc_ranges(K, splits)) : 0;
+        if (wide > 0) {
+            if (epilogue == 0 && c_dt == AIEN_DT_BF16) return launch_tc_persistent_m256<0, __nv_bfloat16>(wide, A, lda, W, ldw, out, ldc, M, N, K, stream);
+            if (epilogue == 0 && c_dt == AIEN_DT_F32) return launch_tc_persistent_m256<0, float>(wide, A, lda, W, ldw, out, ldc, M, N, K, stream);
+            if (epilogue == 1 && c_dt == AIEN_DT_BF16) return launch_tc_persistent_m256<1, __nv_bfloat16>(wide, A, lda, W, ldw, out, ldc, M, N, K, stream);
+            if (epilogue == 1 && c_dt == AIEN_DT_F32) return launch_tc_persistent_m256<1, float>(wide, A, lda, W, ldw, out, ldc, M, N, K, stream);
         }
         if (plan == 256) {
             if (epilogue == 0 && c_dt == AIEN_DT_BF16) TCP_CASE(256, 0, __nv_bfloat16);

@@ -631,12 +631,12 @@ def test_gemm_tensor_core(K, out_dtype, M, N, K_):
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("M,N,K_", [(2048, 4096, 1024), (1000, 9000, 1032), (4100, 4112, 1032)])
+@pytest.mark.parametrize("M,N,K_", [(512, 18944, 2048), (4096, 4112, 1032), (2900, 5000, 1032)])      # tiles 256, 240 and 224 wide
 def test_gemm_tensor_core_tiles_of_256_rows(K, M, N, K_, out_dtype):
     """Products that the persistent kernel takes with tiles of 256 x 256 (two accumulators side by side,
-    eight epilogue warps): last row tiles with 232 and 4 rows, widths that are no multiple of the tile, a K
-    that is no multiple of the k-block, more tiles than SMs (two per CTA, so the accumulators are handed
-    back and forth)."""
+    eight epilogue warps), 256, 240 or 224 columns wide as makes the shortest waves: a last row tile of 84
+    rows, widths that are no multiple of the tile or of a chunk of 32 columns, a K that is no multiple of
+    the k-block, two tiles per CTA (the accumulators handed back and forth)."""
     assert K.gemm_tc_takes_256_rows(M, N, K_) and not K.gemm_tc_takes_256_rows(2048, 6144, 4096) and not K.gemm_tc_takes_256_rows(128, 24576, 4096)
     g = torch.Generator().manual_seed(M + N)
     a = torch.randn(M, K_, generator=g).to(torch.bfloat16).cuda()
@@ -652,7 +652,7 @@ def test_gemm_tensor_core_tiles_of_256_rows(K, M, N, K_, out_dtype):
 
 
 def test_gemm_tensor_core_tiles_of_256_rows_with_swiglu(K):
-    M, I, Hd = 2048, 2056, 1032
+    M, I, Hd = 2900, 2504, 1032                     # tiles of 224 columns over 5,008: the last one 80 wide
     assert K.gemm_tc_takes_256_rows(M, 2 * I, Hd)
     g = torch.Generator().manual_seed(3)
     a = torch.randn(M, Hd, generator=g).to(torch.bfloat16).cuda()
