@@ -1,9 +1,10 @@
 // C[M,N] = A[M,K] . W[N,K]^T on the fifth-generation tensor cores: tcgen05.mma with the
 // accumulator in tensor memory, operands brought into shared memory by TMA.
 //
-// Two forms (tc_plan chooses): one CTA per 128 x 128 tile, described here, for products with few
-// tiles and for split-K; and a persistent form with 128 x 256 tiles and two accumulators, described
-// further down, for the large products of a prefill.  The first form, six warps, three roles:
+// Three forms (tc_plan and tc_m256_cols choose): one CTA per 128 x 128 tile, described here, for
+// products with few tiles and for split-K; a persistent form with 128 x 256 tiles and two
+// accumulators, and one with tiles of 256 rows, both described further down, for the large products
+// of a prefill.  The first form, six warps, three roles:
 //   warp 0      producer: one lane issues the TMA loads of the A and W k-blocks (128 rows x 64
 //               bfloat16 = one 128-byte swizzled row each) into a 3-stage ring;
 //   warp 1      allocates tensor memory, then one lane issues tcgen05.mma (M 128, N 128, K 16,
