@@ -376,6 +376,56 @@ qk_norm_rope_kv_write_hd128_kernel(
     }
 }
 
+// One head row of the kernel below, held by 16 lanes with eight values each: norm, rotation, store.
+// KIND 0 a query head, 1 a key head, 2 a value head (stored as it came): chosen per warp, so that
+// nothing is decided per lane.
+template <int KIND>
+__device__ __forceinline__ void qk_pairs_row(const uint4 raw, bool live, int hh, int t, long slot, int l16, const float (&w)[8], bool normed,
+                                             bool rotate, float eps, const float (&cs)[8], const float (&sn)[8],
+                                             __nv_bfloat16* q_out, long q_out_stride, __nv_bfloat16* __restrict__ k_cache,
+                                             __nv_bfloat16* __restrict__ v_cache, int nkv) {
+    if (KIND == 2) {
+        if (live && slot >= 0) *reinterpret_cast<uint4*>(v_cache + ((size_t)slot * nkv + hh) * 128 + l16 * 8) = raw;
+        return;
+    }
+    float x[8];
+    {
+        const uint32_t w32[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w32[e]));
+            x[2 * e] = f.x; x[2 * e + 1] = f.y;
+        }
+    }
+    if (normed) {
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);        // over the 16 lanes of the row
+        const float scale = 1.0f / sqrtf(ss / 128.0f + eps);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = x[e] * scale * w[e];
+    }
+    if (rotate) {
+        float y[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] = __shfl_xor_sync(0xffffffffu, x[e], 8);        // the rotation partner, 64 values away
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = fmaf(y[e], sn[e], x[e] * cs[e]);
+    }
+    if (!live || (KIND == 1 && slot < 0)) return;
+    uint4 o;
+    {
+        __nv_bfloat162 p0b = __floats2bfloat162_rn(x[0], x[1]), p1b = __floats2bfloat162_rn(x[2], x[3]);
+        __nv_bfloat162 p2b = __floats2bfloat162_rn(x[4], x[5]), p3b = __floats2bfloat162_rn(x[6], x[7]);
+        o.x = *reinterpret_cast<uint32_t*>(&p0b); o.y = *reinterpret_cast<uint32_t*>(&p1b);
+        o.z = *reinterpret_cast<uint32_t*>(&p2b); o.w = *reinterpret_cast<uint32_t*>(&p3b);
+    }
+    __nv_bfloat16* dst = KIND == 0 ? (q_out + (size_t)t * q_out_stride + (size_t)hh * 128) : (k_cache + ((size_t)slot * nkv + hh) * 128);
+    *reinterpret_cast<uint4*>(dst + l16 * 8) = o;
+}
+
 // The same for many tokens with two head rows per warp: lanes 0-15 hold one row (eight values each,
 // one 16-byte load), lanes 16-31 another; the sum of squares runs over 16 lanes, the rotation
 // partner of a value is in lane ^ 8.  A CTA of eight warps takes four tokens, two warps each (the
@@ -428,7 +478,36 @@ qk_norm_rope_kv_write_hd128_pairs_kernel(
     }
     // this lane's heads: 2 * pair + half, pair = (warp >> 2) + 2 * gridDim.y * i + 2 * blockIdx.y
     const int pstep = 2 * gridDim.y;
-    for (int p0 = (warp >> 2) + 2 * blockIdx.y; 2 * p0 < n_heads; p0 += pstep * HB) {
+    // with even numbers of query and of key/value heads the two rows of a pair are of one kind, which the warp
+    // then decides once for all its lanes
+    const bool pairs_of_a_kind = ((nq | nkv) & 1) == 0 || !write_kv && (nq & 1) == 0;
+    const bool rot = cos_t != nullptr;
+    for (int p0 = (warp >> 2) + 2 * blockIdx.y; pairs_of_a_kind && 2 * p0 < n_heads; p0 += pstep * HB) {
+        uint4 raw[HB];
+#pragma unroll
+        for (int u = 0; u < HB; ++u) {
+            const int h0 = 2 * (p0 + pstep * u), head = h0 + half;
+            raw[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (live && h0 < n_heads) {
+                const __nv_bfloat16* src = h0 < nq ? q + (size_t)t * q_stride + (size_t)head * 128
+                                         : (h0 < nq + nkv ? k + (size_t)t * k_stride + (size_t)(head - nq) * 128
+                                                          : v + (size_t)t * v_stride + (size_t)(head - nq - nkv) * 128);
+                raw[u] = __ldcg(reinterpret_cast<const uint4*>(src + l16 * 8));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < HB; ++u) {
+            const int h0 = 2 * (p0 + pstep * u), head = h0 + half;
+            if (h0 >= n_heads) break;
+            if (h0 < nq)
+                qk_pairs_row<0>(raw[u], live, head, t, slot, l16, wq, q_norm_w != nullptr, rot, eps, cs, sn, q_out, q_out_stride, k_cache, v_cache, nkv);
+            else if (h0 < nq + nkv)
+                qk_pairs_row<1>(raw[u], live, head - nq, t, slot, l16, wk, k_norm_w != nullptr, rot, eps, cs, sn, q_out, q_out_stride, k_cache, v_cache, nkv);
+            else
+                qk_pairs_row<2>(raw[u], live, head - nq - nkv, t, slot, l16, wk, false, false, eps, cs, sn, q_out, q_out_stride, k_cache, v_cache, nkv);
+        }
+    }
+    for (int p0 = (warp >> 2) + 2 * blockIdx.y; !pairs_of_a_kind && 2 * p0 < n_heads; p0 += pstep * HB) {
         uint4 raw[HB];
 #pragma unroll
         for (int u = 0; u < HB; ++u) {

@@ -139,7 +139,7 @@ def test_qk_norm_rope_kv_write(K, dtype, nq, nkv, hd, rot, norm):
     assert (kcn[untouched] == 7.0).all() and (vcn[untouched] == 7.0).all()     # a token without a slot writes nothing
 
 
-@pytest.mark.parametrize("nq,nkv,norm", [(5, 2, True), (8, 1, False), (16, 8, True)])
+@pytest.mark.parametrize("nq,nkv,norm", [(5, 2, True), (8, 1, False), (16, 8, True), (32, 8, False), (6, 2, True)])
 def test_qk_kernel_head128_many_tokens(K, nq, nkv, norm):
     """The prompt-portion form of the head-128 q/k kernel (128 tokens and more): a token count that
     is no multiple of its group of four, head counts that are no multiple of its eight warps,
