@@ -533,8 +533,10 @@ static int launch_tc_persistent_m256_bn(const void* A, long lda, const void* W, 
 template <int EPI, typename TC>
 static int launch_tc_persistent_m256(int bn, const void* A, long lda, const void* W, long ldw, void* out, long ldc, int M, int N, int K,
                                      cudaStream_t stream) {
-    if (bn == 240) return launch_tc_persistent_m256_bn<240, EPI, TC>(A, lda, W, ldw, out, ldc, M, N, K, stream);
-    if (bn == 224) return launch_tc_persistent_m256_bn<224, EPI, TC>(A, lda, W, ldw, out, ldc, M, N, K, stream);
+    if (sizeof(TC) == 2) {                       // the narrower tiles for bfloat16 results only (fewer kernels to compile)
+        if (bn == 240) return launch_tc_persistent_m256_bn<240, EPI, __nv_bfloat16>(A, lda, W, ldw, out, ldc, M, N, K, stream);
+        if (bn == 224) return launch_tc_persistent_m256_bn<224, EPI, __nv_bfloat16>(A, lda, W, ldw, out, ldc, M, N, K, stream);
+    }
     return launch_tc_persistent_m256_bn<256, EPI, TC>(A, lda, W, ldw, out, ldc, M, N, K, stream);
 }
 
