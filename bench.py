@@ -19,7 +19,10 @@ line is printed:
 
 Peaks come from ``MEASURED_PEAKS.json`` beside this file when present, else from the fallback
 measured earlier on the same pool (6.65 TB/s, 1.59 PFLOP/s).  The weights of one step (15 GB) are
-far larger than the 126 MB L2, so consecutive steps cannot be served from cache.
+far larger than the 126 MB L2, so consecutive steps cannot be served from cache.  Every decode
+run first fills its requests' cache by prefill, pauses 0.3 s and then takes its W warm-up steps: the
+fill runs at the power cap and leaves the SM clock low for some 70 ms, which 20 timed steps straight
+after it would measure instead of decoding (steps of 4.2 ms that settle at 3.5 ms).
 ``--workload llama3_8b`` prints the same line for the Llama-3-8B shape with 16 requests decoding at
 contexts that end at 8,192 tokens (the cache, 17 GB a step, outweighs the weights) and a 2,048-token
 prefill; ``--workload serving`` runs continuous batching of 32 requests on the Qwen3-4B shape and adds
@@ -53,6 +56,7 @@ LLAMA3_8B = dict(
     hidden_act="silu", attention_bias=False, eos_token_id=128001,
 )
 PAGE, PREFILL_TOKENS = 16, 2048
+SETTLE_S = 0.3           # pause between a cache fill (a prefill at the power cap) and the decode steps after it
 # prompt_len None: as long as lets the timed steps end exactly at `context` tokens
 WORKLOADS = {
     "decode": dict(cfg=QWEN3_8B, label="Qwen3-8B shape, random weights", prompt_len=1024, context=4096, batch=8, seed=2, points=(1, 64)),
@@ -336,6 +340,14 @@ def main() -> int:
         nonlocal wait_errors
         wait_errors += sum(1 for w in K.read_wait_errors() if w != 0)
 
+    def settle():
+        """Filling the cache is a prefill at the power cap, and the SM clock stays low for some 70 ms
+        after it: decode steps of 4.2 ms, then 3.8, then the 3.5 ms that decoding sustains for as
+        long as it goes on.  A short pause between the fill and the warm-up steps lets the timed
+        steps run at the clocks that decoding itself settles at."""
+        torch.cuda.synchronize()
+        time.sleep(SETTLE_S)
+
     def fill_requests(batch, first_id):
         """Each request gets a PROMPT_LEN-token prompt by real prefill: portions of at most 2,048
         tokens, several requests in a step where they fit."""
@@ -362,6 +374,7 @@ def main() -> int:
 
     def decode_run(batch, first_id, n_warm, n_steps, sample_clocks=False):
         ids = fill_requests(batch, first_id)
+        settle()
         toks = rng.integers(0, V, (n_warm + n_steps, batch))
         for s in range(n_warm):
             engine.step([(rid, [int(toks[s, j])], [0]) for j, rid in enumerate(ids)])
@@ -444,6 +457,8 @@ def main() -> int:
             return m["prefill_tokens"] >= batch_main * PROMPT_LEN and gen.scheduler.num_running == batch_main
         while not all_decoding():
             gen.advance()
+        gen.flush()
+        settle()
         for _ in range(warmup):
             gen.advance()
         gen.flush()
@@ -461,7 +476,7 @@ def main() -> int:
         new_tokens = gen.scheduler.metrics()["decode_tokens"] - dec0
         for i in range(batch_main):
             gen.scheduler.cancel(5000 + i)
-        e2e = {"value": round(new_tokens / dt, 1), "unit": "tokens/s", "steps": n_steps,
+        e2e = {"value": round(new_tokens / dt, 1), "unit": "tokens/s", "steps": n_steps, "pause_after_prefill_s": SETTLE_S,
                "h2d_bytes_per_step": int((gen.h2d_bytes - h0) / n_steps), "d2h_bytes_per_step": int((gen.d2h_bytes - d0) / n_steps)}
 
     out = {
