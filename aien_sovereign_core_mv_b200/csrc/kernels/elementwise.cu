@@ -81,8 +81,10 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
 // between the passes, every access is a vector, and all loads of a thread (the row, the pending
 // sums, the weights) are issued before the first use.
 // PARTS: the pending sum comes in several parts (the register budget of that case is its own).
-template <typename TD, typename TO, int NV, bool PARTS>
-__global__ void __launch_bounds__(256)
+// BS threads a row: 256, or 1,024 for steps of so few rows that the grid leaves most SMs empty; a
+// thread then holds one vector of the row and has every load it makes in flight at once.
+template <typename TD, typename TO, int NV, bool PARTS, int BS>
+__global__ void __launch_bounds__(BS)
 add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int nparts, size_t part_stride,
                        const void* __restrict__ w, int wdt, float eps, TO* __restrict__ h, int H) {
     __shared__ float red[32];
@@ -90,7 +92,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int 
     float4 wv[NV];
 #pragma unroll
     for (int j = 0; j < NV; ++j) {                                   // weights do not depend on the kernel ahead
-        const int i = (j * 256 + threadIdx.x) * 4;
+        const int i = (j * BS + threadIdx.x) * 4;
         wv[j] = i < H ? load4_dyn(w, wdt, i) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     griddep_wait();
@@ -98,7 +100,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int 
     float4 v[NV];
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
-        const int i = (j * 256 + threadIdx.x) * 4;
+        const int i = (j * BS + threadIdx.x) * 4;
         v[j] = i < H ? load4(x + base + i) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     if (delta != nullptr) {
@@ -106,7 +108,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int 
             float4 dv[NV];
 #pragma unroll
             for (int j = 0; j < NV; ++j) {
-                const int i = (j * 256 + threadIdx.x) * 4;
+                const int i = (j * BS + threadIdx.x) * 4;
                 dv[j] = i < H ? ld_act4(delta + base + i) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
 #pragma unroll
@@ -114,14 +116,14 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int 
         } else {
             // four parts are requested at once (the loads of a part do not wait for the sums of the one
             // before); they are added in index order
-            constexpr int PU = NV <= 4 ? 4 : 2;
+            constexpr int PU = NV == 1 ? 8 : (NV <= 4 ? 4 : 2);
             for (int p0 = 0; p0 < nparts; p0 += PU) {
                 float4 d[PU][NV];
 #pragma unroll
                 for (int pp = 0; pp < PU; ++pp)
 #pragma unroll
                     for (int j = 0; j < NV; ++j) {
-                        const int i = (j * 256 + threadIdx.x) * 4;
+                        const int i = (j * BS + threadIdx.x) * 4;
                         if (p0 + pp < nparts && i < H) d[pp][j] = ld_act4(delta + (size_t)(p0 + pp) * part_stride + base + i);
                     }
 #pragma unroll
@@ -129,7 +131,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int 
                     if (p0 + pp < nparts) {
 #pragma unroll
                         for (int j = 0; j < NV; ++j) {
-                            const int i = (j * 256 + threadIdx.x) * 4;
+                            const int i = (j * BS + threadIdx.x) * 4;
                             if (i < H) { v[j].x += d[pp][j].x; v[j].y += d[pp][j].y; v[j].z += d[pp][j].z; v[j].w += d[pp][j].w; }
                         }
                     }
@@ -143,7 +145,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int 
     const float scale = 1.0f / sqrtf(total / (float)H + eps);
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
-        const int i = (j * 256 + threadIdx.x) * 4;
+        const int i = (j * BS + threadIdx.x) * 4;
         if (i < H) {
             if (delta != nullptr) store4(x + base + i, v[j]);
             store4(h + base + i, make_float4(v[j].x * scale * wv[j].x, v[j].y * scale * wv[j].y,
@@ -688,19 +690,25 @@ static void launch_add_rmsnorm(float* x, const TD* delta, int nparts, size_t par
                                float eps, TO* h, int T, int H, cudaStream_t stream) {
     const bool vec = (H % 4 == 0) && (((uintptr_t)x & 15) == 0) && (((uintptr_t)delta & 15) == 0) && (((uintptr_t)h & 15) == 0) &&
                      (((uintptr_t)w & 15) == 0) && (part_stride % 4 == 0);
-#define VEC_CASE(NV)                                                                                                              \
+#define VEC_CASE(NV, BS)                                                                                                          \
     do {                                                                                                                          \
         if (delta != nullptr && nparts > 1)                                                                                       \
-            launch_chain(add_rmsnorm_vec_kernel<TD, TO, NV, true>, dim3(T), dim3(256), 0, stream, x, delta, nparts, part_stride, w, w_dt, eps, h, H); \
+            launch_chain(add_rmsnorm_vec_kernel<TD, TO, NV, true, BS>, dim3(T), dim3(BS), 0, stream, x, delta, nparts, part_stride, w, w_dt, eps, h, H); \
         else                                                                                                                      \
-            launch_chain(add_rmsnorm_vec_kernel<TD, TO, NV, false>, dim3(T), dim3(256), 0, stream, x, delta, nparts, part_stride, w, w_dt, eps, h, H); \
+            launch_chain(add_rmsnorm_vec_kernel<TD, TO, NV, false, BS>, dim3(T), dim3(BS), 0, stream, x, delta, nparts, part_stride, w, w_dt, eps, h, H); \
     } while (0)
-    if (vec && H <= 256 * 4 * 2)
-        VEC_CASE(2);
+    // fewer rows than SMs: the rows' latency is the kernel's time, so more threads share a row
+    const bool few_rows = T <= 148 && H > 256 * 4;
+    if (vec && few_rows && H <= 1024 * 4)
+        VEC_CASE(1, 1024);
+    else if (vec && few_rows && H <= 1024 * 4 * 2)
+        VEC_CASE(2, 1024);
+    else if (vec && H <= 256 * 4 * 2)
+        VEC_CASE(2, 256);
     else if (vec && H <= 256 * 4 * 4)
-        VEC_CASE(4);
+        VEC_CASE(4, 256);
     else if (vec && H <= 256 * 4 * 8)
-        VEC_CASE(8);
+        VEC_CASE(8, 256);
     else
         launch_chain(add_rmsnorm_kernel<TD, TO>, dim3(T), dim3(row_threads(H)), 0, stream, x, delta, nparts, part_stride, w, w_dt, eps, h, H);
 #undef VEC_CASE
