@@ -112,4 +112,92 @@ __device__ __forceinline__ void ad_merge_chunks(float* scratch, const float* __r
     }
 }
 
+// The same merge as a kernel of its own, for contexts so long that one CTA per (token, kv head) would spend
+// more time reading the chunks than the attention took (256 chunks at 32,768 keys).  One CTA per (token,
+// query head, 32 dims of the head): warp v adds series v, a lane one dim, sixteen chunks requested at a
+// time.  Every sum is made in the order ad_merge_chunks makes it, so the bits are the same.
+// Launched with launch_chain behind the kernel that wrote the partial results.
+constexpr int AD_MERGE_KERNEL_THREADS = AD_MERGE_WAYS * 32;
+inline size_t ad_merge_kernel_smem(int max_splits) { return ((size_t)2 * max_splits + AD_MERGE_WAYS * 32 + 4) * sizeof(float); }
+
+template <int HD>
+__global__ void __launch_bounds__(AD_MERGE_KERNEL_THREADS)
+paged_decode_merge_kernel(const float* __restrict__ part_out, const float* __restrict__ part_ml, const int* __restrict__ positions,
+                          const int* __restrict__ token_list, __nv_bfloat16* __restrict__ out, long out_stride, int nq, int window,
+                          int max_splits, int chunk) {
+    extern __shared__ float adm_smem[];
+    float* Fm = adm_smem;                                // [nsp]: chunk max, then the chunk's weight
+    float* Fl = Fm + max_splits;                         // [nsp]: chunk denominator
+    float* Ps = Fl + max_splits;                         // [AD_MERGE_WAYS][32]: the series' sums
+    float* Fi = Ps + AD_MERGE_WAYS * 32;                 // 1 / total denominator
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int zt = blockIdx.x / nq, head = blockIdx.x - zt * nq;
+    const int t = token_list ? token_list[zt] : zt;
+    const int pos = positions[t];
+    const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int s_lo = first / chunk, nsp = pos / chunk - s_lo + 1;
+    const size_t row = (size_t)blockIdx.x;               // part rows are (token, query head)
+    griddep_launch();
+    griddep_wait();
+    for (int i = tid; i < nsp; i += AD_MERGE_KERNEL_THREADS) {
+        Fm[i] = __ldcg(part_ml + (row * max_splits + s_lo + i) * 2);
+        Fl[i] = __ldcg(part_ml + (row * max_splits + s_lo + i) * 2 + 1);
+    }
+    __syncthreads();
+    if (warp == 0) {
+        float M = -INFINITY;
+        for (int sp = lane; sp < nsp; sp += 32) M = fmaxf(M, Fm[sp]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        float L = 0.f;
+        for (int sp = lane; sp < nsp; sp += 32) {
+            const float ms = Fm[sp];
+            const float f = ms == -INFINITY ? 0.f : expf(ms - M);
+            L += Fl[sp] * f;
+            Fm[sp] = f;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+        if (lane == 0) Fi[0] = L > 0.f ? 1.0f / L : 0.f;
+    }
+    __syncthreads();
+    const int d = blockIdx.y * 32 + lane;
+    const float* src = part_out + (row * max_splits + s_lo) * HD + d;
+    constexpr int U = 16;
+    float acc = 0.f;
+    for (int sp = warp; sp < nsp; sp += U * AD_MERGE_WAYS) {
+        float tv[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int c = sp + u * AD_MERGE_WAYS;
+            tv[u] = c < nsp ? __ldcg(src + (size_t)c * HD) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int c = sp + u * AD_MERGE_WAYS;
+            if (c >= nsp) break;
+            acc += tv[u] * Fm[c];
+        }
+    }
+    Ps[warp * 32 + lane] = acc;
+    __syncthreads();
+    if (tid < 32) {
+        float o = 0.f;
+#pragma unroll
+        for (int v = 0; v < AD_MERGE_WAYS; ++v) o += Ps[v * 32 + tid];
+        out[(size_t)t * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(o * Fi[0]);
+    }
+}
+
+// 0, or the CUDA error of the launch
+template <int HD>
+inline void launch_decode_merge(const float* part_out, const float* part_ml, const int* positions, const int* token_list,
+                                __nv_bfloat16* out, long out_stride, int nq, int window, int max_splits, int chunk, int T,
+                                cudaStream_t stream) {
+    static_assert(HD % 32 == 0, "a CTA takes 32 dims of a head");
+    launch_chain(paged_decode_merge_kernel<HD>, dim3((unsigned)(T * nq), HD / 32), dim3(AD_MERGE_KERNEL_THREADS),
+                 ad_merge_kernel_smem(max_splits), stream, part_out, part_ml, positions, token_list, out, out_stride, nq, window,
+                 max_splits, chunk);
+}
+
 }  // namespace aien

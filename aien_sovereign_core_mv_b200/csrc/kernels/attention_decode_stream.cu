@@ -15,7 +15,9 @@
 // assigns fragment rows to keys so that the two rows a quarter-warp reads differ in swizzle group.
 // At the end of a segment the CTA adds the segment's chunk count to the (token, kv head) ticket;
 // the CTA that completes the count merges all chunks in chunk order.  The math warps wait for the
-// ticket while the producer keeps streaming.
+// ticket while the producer keeps streaming.  When the launch allows 128 chunks a token or more, no
+// tickets are taken and a second, small kernel behind this one merges every (token, query head) with
+// many CTAs (the same sums in the same order).
 //
 // Needs head size 64 or 128, pages of 8..128 tokens that divide 128, at most 16 query heads per
 // kv head; other shapes take the kernel in attention_decode.cu.  The cache must hold finite values
@@ -64,7 +66,7 @@ paged_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                            const int* __restrict__ seq_of_token, const int* __restrict__ positions, const int* __restrict__ token_list,
                            float* __restrict__ part_out, float* __restrict__ part_ml, int* __restrict__ counters,
                            __nv_bfloat16* __restrict__ out, long out_stride, int nq, int nkv, int page_size, int window, float scale,
-                           int max_splits, int T, int segs, int cache_rows, int misc_bytes) {
+                           int max_splits, int T, int segs, int cache_rows, int misc_bytes, int merge_outside) {
     constexpr int HALVES = HD / 64, HS = HD / 32, NH = NT * 8;
     constexpr uint32_t TILE = DS_CHUNK * HD * 2;                  // one K or V chunk
     extern __shared__ uint8_t ds_smem[];
@@ -372,7 +374,7 @@ paged_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
             part_ml[row * 2] = Hm[tid];
             part_ml[row * 2 + 1] = Hl[tid];
         }
-        if (m.seg_chunks > 0) {
+        if (m.seg_chunks > 0 && !merge_outside) {
             // ---- the segment is done: ticket; the CTA that completes the count merges the chunks
             ds_math_sync();                                        // every thread's partial results are written
             const bool solo = m.seg_chunks == m.s_hi - m.s_lo + 1; // this CTA made every chunk of the token: no ticket
@@ -399,10 +401,21 @@ paged_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
 // Shared memory of one CTA: alignment slack, the ring, two query buffers, two DsMeta, the barriers,
 // and the scratch of the phases or of the merge, whichever is larger.  Up to 113 KB two CTAs share an SM.
 constexpr size_t DS_SMEM_LIMIT = 200 * 1024;
+// From how many chunks per token on (the launch's limit, not the token's own count) the merge is a kernel of its
+// own behind this one (paged_decode_merge_kernel) and this kernel takes no tickets.  Measured on the 32q/8kv x 128
+// shape, merge inside -> outside: one request of 32,768 keys 41.8 -> 28.1 us, of 16,384 keys 17.8 -> 14.2 us, four of
+// 32,768 109.4 -> 93.1 us, eight of 16,384 98.4 -> 94.5 us; at 64 chunks (sixteen of 8,192) 93.7 -> 97.5 us, so from 128.
+// AIEN_B200_DECODE_MERGE_KERNEL_FROM overrides the limit.
+constexpr int DS_MERGE_OUTSIDE_FROM = 128;
+static bool ds_merge_outside(int max_splits) {
+    static int from = -1;
+    if (from < 0) { const char* e = getenv("AIEN_B200_DECODE_MERGE_KERNEL_FROM"); from = (e && atoi(e) > 0) ? atoi(e) : DS_MERGE_OUTSIDE_FROM; }
+    return max_splits >= from && ad_merge_kernel_smem(max_splits) <= 48 * 1024;
+}
 static size_t ds_smem_bytes(int hd, int nt, int G, int max_splits, size_t* misc_out) {
     const size_t NH = (size_t)nt * 8;
     const size_t loop_bytes = ((size_t)(DS_CHUNK + 4) * NH + 2 * NH) * 4 + NH * (DS_CHUNK + 8) * 2;
-    const size_t merge_bytes = ad_merge_scratch_floats(max_splits, G, hd) * 4;
+    const size_t merge_bytes = ds_merge_outside(max_splits) ? 0 : ad_merge_scratch_floats(max_splits, G, hd) * 4;
     const size_t misc_bytes = ((loop_bytes > merge_bytes ? loop_bytes : merge_bytes) + 127) & ~(size_t)127;
     if (misc_out) *misc_out = misc_bytes;
     return 1024 + (size_t)DS_SLOTS * DS_CHUNK * hd * 2 + 2 * NH * hd * 2 + 2 * sizeof(DsMeta) + 16 * DS_SLOTS + 16 + misc_bytes;
@@ -444,6 +457,7 @@ static int launch_decode_stream(const CUtensorMap& mk, const CUtensorMap& mv, co
         configured = smem;
     }
     const long slots = 2L * ds_num_sms();
+    const bool outside = ds_merge_outside(max_splits);
     int segs = ds_segments_per_pair((long)T * nkv, max_splits, slots);
     if (const char* e = getenv("AIEN_B200_DECODE_SEGMENTS")) { const int v = atoi(e); if (v > 0 && v <= max_splits) segs = v; }
     // more pairs than CTAs: equal ranges of chunks instead of whole pairs (segs = 0 tells the kernel); AIEN_B200_DECODE_BALANCED=0: off
@@ -458,7 +472,10 @@ static int launch_decode_stream(const CUtensorMap& mk, const CUtensorMap& mv, co
     const unsigned grid = (unsigned)(total < slots ? total : slots);
     launch_chain(kern, dim3(grid), dim3(DS_THREADS), smem, stream, mk, mv, (const __nv_bfloat16*)q, q_stride, bt, max_blocks, seq_of_token,
                  positions, token_list, part_out, part_ml, counters, (__nv_bfloat16*)out, out_stride, nq, nkv, page_size, window, scale,
-                 max_splits, T, segs, cache_rows, (int)misc_bytes);
+                 max_splits, T, segs, cache_rows, (int)misc_bytes, outside ? 1 : 0);
+    if (outside)
+        launch_decode_merge<HD>(part_out, part_ml, positions, token_list, (__nv_bfloat16*)out, out_stride, nq, window, max_splits,
+                                DS_CHUNK, T, stream);
     return launch_status();
 }
 

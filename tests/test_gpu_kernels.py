@@ -465,7 +465,8 @@ def test_decode_attention_over_long_contexts(K, nq, nkv, hd, page, window, lens)
     """Up to 157 chunks of 128 keys per token: the merge adds them in eight interleaved series with
     several chunks of a series in flight, beyond one round of every loop; three keys spread over the
     context decide head 0 of every token.  Both kernels (the same bits where both take the shape), with a
-    window that starts inside the context."""
+    window that starts inside the context.  From 128 chunks on the streamed kernel leaves the merge to a
+    kernel of its own (the first two cases), which must add in the same order as the merge inside."""
     dtype = torch.bfloat16
     rng = np.random.default_rng(hd + len(lens))
     kc, vc, bt, mb, dense = paged_setup(rng, lens, nkv, hd, page, dtype, sum((n + page - 1) // page for n in lens) + 8)
