@@ -90,16 +90,18 @@ def test_norm_spread_over_the_products_around_it(big, monkeypatch):
 
 def test_long_context_bfloat16_follows_float32():
     """9,000 tokens through the production layer sizes: prompt portions at offsets far into the
-    context, then single tokens over 71 key chunks.  The plain implementation is too slow here, so
-    the bfloat16 kernels are held against the engine's own 32-bit path, itself checked above."""
+    context, then single tokens over 71 key chunks.  The engine allows contexts of 17,000 tokens, so its
+    decode steps are laid out for 128 chunks a token, where the chunks are merged by a kernel of its own.
+    The plain implementation is too slow here, so the bfloat16 kernels are held against the engine's own
+    32-bit path, itself checked above."""
     from aien_sovereign_core_mv_b200 import Engine, EngineConfig
     import torch
-    cfg = dict(SHAPES["qwen3_8b"], max_position_embeddings=16384)
+    cfg = dict(SHAPES["qwen3_8b"], max_position_embeddings=32768)
     n = 9000
     toks = [int(t) for t in np.random.default_rng(1).integers(0, cfg["vocab_size"], n + 12)]
     out = {}
     for dtype in ("float32", "bfloat16"):
-        ec = EngineConfig(dtype=dtype, page_size=16, max_cache_tokens=n + 2048, max_requests=4, max_batch_tokens=2048, max_context=n + 1024)
+        ec = EngineConfig(dtype=dtype, page_size=16, max_cache_tokens=n + 2048, max_requests=4, max_batch_tokens=2048, max_context=n + 8000)
         eng = Engine.from_config(cfg, seed=3, engine_config=ec, init_std=0.02, device_init=True)
         rows = []
         for i in range(0, n, 2048):
