@@ -274,6 +274,9 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=0, help="requests decoding together (0: the workload's own: 8, or 16 for llama3_8b)")
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (0 = all)")
+    ap.add_argument("--prompt-len", type=int, default=0,
+                    help="decode workload: tokens each request holds before the timed steps (default 1,024); the context limit "
+                         "grows with it, and the points at batch 1 and 64 are left out")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
@@ -307,7 +310,11 @@ def main() -> int:
     from aien_sovereign_core_mv_b200.engine.generate import Generator
     from aien_sovereign_core_mv_b200.sampling import SamplingParams
 
-    wl = WORKLOADS[args.workload]
+    wl = dict(WORKLOADS[args.workload])
+    if args.prompt_len > 0 and wl["prompt_len"]:
+        wl["prompt_len"] = args.prompt_len
+        wl["context"] = max(wl["context"], args.prompt_len + warmup + steps + 64)
+        wl["points"] = ()
     batch_main = args.batch or wl["batch"]
     cfg = dict(wl["cfg"])
     layers_cfg = cfg["num_hidden_layers"]
