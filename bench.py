@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Headline measurement: decode tokens per second of the Qwen3-8B-shaped model on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch B] [--layers N] [--workload decode|llama3_8b|serving]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch B] [--prompt-len L] [--layers N] [--workload decode|llama3_8b|serving|mixed_step]
 
 A step is one decode step of a batch of requests that each hold a 1,024-token prompt (context
 limit 4,096, pages of 16 tokens), random bfloat16 weights, synthetic uniform token ids.  One JSON
