@@ -463,11 +463,13 @@ static int launch_decode_stream(const CUtensorMap& mk, const CUtensorMap& mv, co
     // more pairs than CTAs: equal ranges of chunks instead of whole pairs (segs = 0 tells the kernel); AIEN_B200_DECODE_BALANCED=0: off
     static int balanced = -1;
     if (balanced < 0) { const char* e = getenv("AIEN_B200_DECODE_BALANCED"); balanced = (e && e[0] == '0') ? 0 : 1; }
-    // (measured, 32q/8kv x 128 at 1,030 keys, whole pairs -> ranges: batch 48 the same, 64 54.3 -> 53.5 us, 96 81.2 -> 76.9 us,
-    // 128 108.0 -> 99.0 us: a range shares pairs with its neighbours, and every shared pair is a ticket and a merge more,
-    // which the even load pays for from 64 requests on and never loses to.)
-    const long pairs = (long)T * nkv;
-    if (balanced && segs == 1 && pairs > slots && T <= 256 && getenv("AIEN_B200_DECODE_SEGMENTS") == nullptr) segs = 0;
+    // (measured, 32q/8kv x 128 at 1,030 keys, whole pairs -> ranges, the kernel alone: batch 48 the same, 64 54.3 -> 53.5 us,
+    // 96 81.2 -> 76.9 us, 128 108.0 -> 99.0 us; inside a decode step of 36 layers: batch 48 5.26 -> 5.03 ms, 64 5.69 -> 5.73 ms,
+    // 96 7.09 -> 7.02 ms, 128 8.37 -> 8.25 ms.  A range shares pairs with its neighbours, and every shared pair is a ticket
+    // and a merge more: so only when whole pairs would leave a fifth of the CTA rounds empty, or take three rounds or more.)
+    const long pairs = (long)T * nkv, rounds = (pairs + slots - 1) / slots;
+    if (balanced && segs == 1 && pairs > slots && (pairs * 10 < slots * rounds * 8 || rounds >= 3) && T <= 256 &&
+        getenv("AIEN_B200_DECODE_SEGMENTS") == nullptr) segs = 0;
     const long total = segs > 0 ? (long)segs * T * nkv : slots;
     const unsigned grid = (unsigned)(total < slots ? total : slots);
     launch_chain(kern, dim3(grid), dim3(DS_THREADS), smem, stream, mk, mv, (const __nv_bfloat16*)q, q_stride, bt, max_blocks, seq_of_token,
