@@ -483,8 +483,9 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int =
 
 
 # Upper bound of the float32 partial products one deferred product may leave in the workspace:
-# ranges x M x N <= (296 / tiles) x (tiles x 128 x 128) elements.
-PARTIALS_MAX_BYTES = 296 * 128 * 128 * 4 + (1 << 16)
+# ranges x M x N <= (296 / tiles) x (tiles x 128 x 128) elements within one wave of units; ranges over
+# several waves (gemm_tc_splits) are taken only while they fit.
+PARTIALS_MAX_BYTES = 40 * 1024 * 1024 + (1 << 16)
 
 
 def gemm_tc_ranges(K_: int, splits: int) -> int:
@@ -506,7 +507,31 @@ def gemm_tc_splits(M: int, N: int, K_: int) -> int:
         tiles = ((M + 127) // 128) * ((N + 255) // 256)
         if tiles >= 148:
             return 1
-        return gemm_tc_ranges(K_, max(1, min(8, 148 // tiles, K_ // 512)))
+        one_wave = gemm_tc_ranges(K_, max(1, min(8, 148 // tiles, K_ // 512)))
+        # Three sevenths of the SMs or more idle over a long K: ranges over two or three waves of units can still be
+        # faster, the float32 partial products they write and their consumer reads counted in (536 rows x 4,096
+        # x 12,288: 80 tiles; one range 80.1 us, three 60.0 us + 3.5 us for the consumer; x 14,336: 89.9 -> 68.4 us).
+        # Costs in cycles: a k-block of a tile 768, a tile's fixed part 1,500, a partly filled GPU clocks higher,
+        # partial products at 3,800 bytes a cycle both ways.  Taken when a tenth faster by this count.
+        kb = (K_ + 63) // 64
+
+        def cost(r: int) -> float:
+            units = tiles * r
+            waves = (units + 147) // 148
+            c = waves * (-(-kb // r) * 768 + 1500)
+            if units < 148:
+                c *= 0.75 + 0.25 * units / 148
+            return c + ((r * M * N * 8) / 3800 + 2000 if r > 1 else 0)
+
+        best, best_cost = one_wave, cost(one_wave)
+        if tiles * 7 > 148 * 4:         # with more than four sevenths of the SMs busy it measured no faster (724 rows: 96 tiles)
+            return best
+        for r in range(one_wave + 1, 9):
+            if K_ // 512 < r or r * M * N * 4 > PARTIALS_MAX_BYTES - (1 << 16) or gemm_tc_ranges(K_, r) != r:
+                continue
+            if cost(r) < 0.9 * best_cost:
+                best, best_cost = r, cost(r)
+        return best
     tiles = ((M + 127) // 128) * ((N + 127) // 128)
     if tiles >= 148:
         return 1

@@ -955,6 +955,8 @@ def test_gemm_tensor_core_split_k(K, M, N, K_, splits):
     H.assert_close(parts.sum(0).cpu().numpy(), want, 2e-5, f"tc gemm split-K {M}x{N}x{K_}/{ranges}")
     assert K.gemm_tc_splits(2048, 4096, 4096) == 1 and K.gemm_tc_splits(64, 4096, 4096) > 1
     assert K.gemm_tc_splits(512, 2560, 4096) == 3 and K.gemm_tc_splits(512, 6144, 2560) == 1
+    # 80 tiles over a long K: three ranges in two waves of units; 96 tiles: left alone
+    assert K.gemm_tc_splits(536, 4096, 12288) == 3 and K.gemm_tc_splits(724, 4096, 12288) == 1
 
 
 @pytest.mark.parametrize("nq,nkv,hd,page,window,norm", [(8, 2, 128, 16, 0, True), (6, 3, 48, 8, 0, True), (5, 1, 80, 16, 0, False),
