@@ -1,8 +1,8 @@
 // C[M,N] = A[M,K] . W[N,K]^T on the fifth-generation tensor cores: tcgen05.mma with the
 // accumulator in tensor memory, operands brought into shared memory by TMA.
 //
-// Three forms (tc_plan and tc_m256_cols choose): one CTA per 128 x 128 tile, described here, for
-// products with few tiles and for split-K; a persistent form with 128 x 256 tiles and two
+// Three forms (tc_plan, tc_m256_cols and tc_p_cols choose): one CTA per 128 x 128 tile, described here, for
+// products with few tiles and for split-K; a persistent form with 128 x 256 (or 192) tiles and two
 // accumulators, and one with tiles of 256 rows, both described further down, for the large products
 // of a prefill.  The first form, six warps, three roles:
 //   warp 0      producer: one lane issues the TMA loads of the A and W k-blocks (128 rows x 64
@@ -221,6 +221,7 @@ template <int BN> struct TcP {
     static constexpr int STAGE_A = TC_BM * TC_BK * 2, STAGE_B = BN * TC_BK * 2;
     static constexpr int STAGES = (192 * 1024) / (STAGE_A + STAGE_B);          // 4 of 48 KB
     static constexpr int SMEM = STAGES * (STAGE_A + STAGE_B) + 1024 + 256;
+    static constexpr int TMEM_COLS = 2 * BN <= 256 ? 256 : 512;                // two accumulators of BN columns; a power of two
 };
 
 template <int BN, int EPI, typename TC>
@@ -254,7 +255,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)(2 * BN)) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)P::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -307,7 +308,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                     const uint64_t da = make_desc_sw128(sA + s * P::STAGE_A), db = make_desc_sw128(sB + s * P::STAGE_B);
 #pragma unroll
                     for (int k = 0; k < TC_BK / 16; ++k)
-                        umma_bf16(tmem_acc + acc * BN, da + 2 * k, db + 2 * k, idesc, (kb > kb_first || k > 0) ? 1u : 0u);
+                        umma_bf16(tmem_acc + acc * (P::TMEM_COLS / 2), da + 2 * k, db + 2 * k, idesc, (kb > kb_first || k > 0) ? 1u : 0u);
                     umma_commit(empty0 + 8 * s);
                 }
                 umma_commit(tfull0 + 8 * acc);
@@ -327,7 +328,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
-                tmem_ld32(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + c0), r);
+                tmem_ld32(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * (P::TMEM_COLS / 2) + c0), r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (row < M && n0 + c0 < N) tc_store_chunk<EPI, TC>(r, out_u, ldc, row, n0, c0, N);
             }
@@ -340,7 +341,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)(2 * BN)) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)P::TMEM_COLS) : "memory");
     }
 }
 
@@ -588,6 +589,18 @@ static int tc_m256_cols(int M, int N, int K, int ranges) {
     return cols;
 }
 
+// How wide the tiles of the persistent kernel with 128 rows are: 256 columns, or 192 where the units of 256 leave
+// a quarter of the SMs or more idle and those of 192 fill nine tenths of them in one wave (536 rows x 2,560 x 9,728
+// in two ranges: 100 units or 140 on 148 SMs, 39.2 -> 36.2 us; x 4,096: 23.5 -> 21.7 us).  Elsewhere the narrower
+// tile measured no faster or slower (80 -> 110 units: 26.8 -> 29.5 us; two waves either way: 36.2 -> 37.1 us): per
+// flop it moves a ninth more through shared memory.  AIEN_B200_GEMM_TC=p256 | m256 pins 256.
+static int tc_p_cols(int M, int N, int ranges) {
+    if (const char* e = getenv("AIEN_B200_GEMM_TC")) { if (!strcmp(e, "p256") || !strcmp(e, "m256")) return 256; }
+    const long sms = tc_num_sms(), mt = (M + TC_BM - 1) / TC_BM;
+    const long u256 = mt * ((N + 255) / 256) * ranges, u192 = mt * ((N + 191) / 192) * ranges;
+    return (u256 * 4 <= sms * 3 && u192 <= sms && u192 * 10 >= sms * 9) ? 192 : 256;
+}
+
 static int tc_a_rows(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }
 
 // Rows of W per tile.  The CTAs of a launch all run at once (two per SM), and the launch ends when
@@ -675,6 +688,10 @@ AIEN_API int aien_gemm_tc(const void* A, long lda, const void* W, long ldw, void
             if (epilogue == 0 && c_dt == AIEN_DT_F32) return launch_tc_persistent_m256<0, float>(wide, A, lda, W, ldw, out, ldc, M, N, K, stream);
             if (epilogue == 1 && c_dt == AIEN_DT_BF16) return launch_tc_persistent_m256<1, __nv_bfloat16>(wide, A, lda, W, ldw, out, ldc, M, N, K, stream);
             if (epilogue == 1 && c_dt == AIEN_DT_F32) return launch_tc_persistent_m256<1, float>(wide, A, lda, W, ldw, out, ldc, M, N, K, stream);
+        }
+        if (plan == 256 && epilogue == 0 && tc_p_cols(M, N, aien_gemm_tc_ranges(K, splits)) == 192) {
+            if (c_dt == AIEN_DT_BF16) TCP_CASE(192, 0, __nv_bfloat16);
+            if (c_dt == AIEN_DT_F32) TCP_CASE(192, 0, float);
         }
         if (plan == 256) {
             if (epilogue == 0 && c_dt == AIEN_DT_BF16) TCP_CASE(256, 0, __nv_bfloat16);

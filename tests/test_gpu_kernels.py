@@ -610,7 +610,8 @@ def test_swiglu_interleaved_layout(K):
 
 # the last three have at least 148 tiles of 128 x 256 and take the persistent kernel (ragged edges in M, N and K)
 TC_SHAPES = [(128, 128, 64), (1, 16, 8), (17, 100, 200), (130, 333, 72), (256, 384, 4096), (300, 130, 1032), (2048, 512, 256), (64, 1000, 512),
-             (2053, 2584, 136), (300, 37900, 72), (4096, 1280, 1024)]
+             (2053, 2584, 136), (300, 37900, 72), (4096, 1280, 1024),
+             (600, 5130, 264)]          # the last: persistent tiles of 192 columns (100 units of 256 columns, 135 of 192)
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
@@ -940,7 +941,8 @@ def test_gemv_stream_against_direct(K, M, N, K_, monkeypatch):
 # the last four take the persistent kernel with 128 x 256 tiles, one unit per (range of K, tile): a narrow product with long K
 # (40 tiles x 3 ranges), ragged edges in M, N and K, more units than SMs, and a last range shorter than the others
 @pytest.mark.parametrize("M,N,K_,splits", [(64, 4096, 4096, 4), (17, 130, 1032, 8), (100, 256, 576, 4), (128, 384, 12288, 8),
-                                           (512, 2560, 4096, 3), (536, 2570, 9736, 3), (1100, 2584, 1160, 4), (300, 2000, 1992, 3)])
+                                           (512, 2560, 4096, 3), (536, 2570, 9736, 3), (1100, 2584, 1160, 4), (300, 2000, 1992, 3),
+                                           (536, 2570, 4104, 2)])       # the last: tiles of 192 columns (110 units of 256, 140 of 192)
 def test_gemm_tensor_core_split_k(K, M, N, K_, splits):
     g = torch.Generator().manual_seed(M + N)
     a = torch.randn(M, K_, generator=g).to(torch.bfloat16).cuda()
