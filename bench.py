@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Headline measurement: decode tokens per second of the Qwen3-8B-shaped model on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch B] [--prompt-len L] [--layers N] [--workload decode|llama3_8b|serving|mixed_step]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch B] [--prompt-len L] [--prefill-tokens T] [--layers N] [--workload decode|llama3_8b|serving|mixed_step]
 
 A step is one decode step of a batch of requests that each hold a 1,024-token prompt (context
 limit 4,096, pages of 16 tokens), random bfloat16 weights, synthetic uniform token ids.  One JSON
@@ -277,6 +277,8 @@ def main() -> int:
     ap.add_argument("--prompt-len", type=int, default=0,
                     help="decode workload: tokens each request holds before the timed steps (default 1,024); the context limit "
                          "grows with it, and the points at batch 1 and 64 are left out")
+    ap.add_argument("--prefill-tokens", type=int, default=0,
+                    help="length of the prompt whose one-step prefill is timed (default 2,048); another length leaves out the points")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
@@ -316,6 +318,10 @@ def main() -> int:
         wl["context"] = max(wl["context"], args.prompt_len + warmup + steps + 64)
         wl["points"] = ()
     batch_main = args.batch or wl["batch"]
+    ptok = args.prefill_tokens if args.prefill_tokens > 0 else PREFILL_TOKENS
+    if ptok != PREFILL_TOKENS:
+        wl["context"] = max(wl["context"], ptok + 64)
+        wl["points"] = ()
     cfg = dict(wl["cfg"])
     layers_cfg = cfg["num_hidden_layers"]
     layers_run = args.layers or layers_cfg
@@ -326,10 +332,10 @@ def main() -> int:
     # the timed steps end at `context` tokens when the workload gives no prompt length
     PROMPT_LEN = wl["prompt_len"] or CONTEXT - (warmup + steps)
     max_batch = max([batch_main, *wl["points"]])
-    pool_tokens = max_batch * (PROMPT_LEN + warmup + steps + 64)
+    pool_tokens = max_batch * (PROMPT_LEN + warmup + steps + 64) + ptok
     ec = EngineConfig(dtype="bfloat16", page_size=PAGE, max_cache_tokens=pool_tokens, max_requests=max_batch,
-                      max_batch_tokens=PREFILL_TOKENS, max_context=CONTEXT + (0 if wl["prompt_len"] else 64), max_batch_size=max_batch,
-                      max_prefill_tokens=PREFILL_TOKENS, prefill_chunk_size=PREFILL_TOKENS)
+                      max_batch_tokens=max(PREFILL_TOKENS, ptok), max_context=CONTEXT + (0 if wl["prompt_len"] else 64), max_batch_size=max_batch,
+                      max_prefill_tokens=max(PREFILL_TOKENS, ptok), prefill_chunk_size=max(PREFILL_TOKENS, ptok))
     t_load = time.time()
     engine = Engine.from_config(cfg, seed=SEED, engine_config=ec, init_std=0.02, device_init=True)
     torch.cuda.synchronize()
@@ -412,7 +418,7 @@ def main() -> int:
         a pause of 0.3 s, because the peak it is set against is a burst figure too (back to back, a
         25 ms GEMM-bound step runs into the power cap after the third or fourth repetition, as a
         cuBLAS loop does); the median of the four."""
-        ptoks = rng.integers(0, V, PREFILL_TOKENS)
+        ptoks = rng.integers(0, V, ptok)
         times = []
         for rep in range(7):
             torch.cuda.synchronize()
@@ -420,7 +426,7 @@ def main() -> int:
                 time.sleep(0.3)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            engine.step([(9000 + rep, ptoks, [PREFILL_TOKENS - 1])])
+            engine.step([(9000 + rep, ptoks, [ptok - 1])])
             e1.record()
             torch.cuda.synchronize()
             times.append(e0.elapsed_time(e1))
@@ -428,7 +434,7 @@ def main() -> int:
         engine.check_waits()
         count_wait_errors()
         pms = float(np.median(times[3:]))
-        T = PREFILL_TOKENS
+        T = ptok
         flops = 2.0 * (nums["linear_params"] - V * cfg["hidden_size"]) * T + 2.0 * V * cfg["hidden_size"] \
             + layers_run * 4.0 * nums["Q"] * T * (T + 1) / 2
         return {"value": round(T / (pms / 1e3), 1), "tokens": T, "ms": round(pms, 3), "runs_ms": [round(t, 2) for t in times],
@@ -495,7 +501,7 @@ def main() -> int:
             "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
             "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": V,
             "global_batch": batch_main, "seq_len": PROMPT_LEN, "context": CONTEXT, "page_size": PAGE,
-            "parallelism": "single GPU", "prefill_tokens": PREFILL_TOKENS, "seed": SEED,
+            "parallelism": "single GPU", "prefill_tokens": ptok, "seed": SEED,
             "l2": "inputs larger than L2: 15 GB of weights per step", "fill": args.fill,
         },
         "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "wait_errors": int(wait_errors),
