@@ -552,7 +552,7 @@ static int tc_plan(int M, int N, int ranges) {
     static int forced = -1;
     if (forced < 0) {
         const char* e = getenv("AIEN_B200_GEMM_TC");
-        forced = e == nullptr ? 1 : (!strcmp(e, "tile") ? 0 : ((!strcmp(e, "p256") || !strcmp(e, "m256")) ? 256 : 1));
+        forced = e == nullptr ? 1 : (!strcmp(e, "tile") ? 0 : ((!strcmp(e, "p256") || !strcmp(e, "m256") || !strcmp(e, "p192")) ? 256 : 1));
     }
     if (forced != 1) return forced;
     const long units = (long)((M + TC_BM - 1) / TC_BM) * ((N + 255) / 256) * ranges;
@@ -569,7 +569,7 @@ static int tc_m256_cols(int M, int N, int K, int ranges) {
     static int forced = -1;
     if (forced < 0) {
         const char* e = getenv("AIEN_B200_GEMM_TC");
-        forced = e == nullptr ? 0 : (!strcmp(e, "m256") ? 1 : (!strcmp(e, "p256") ? 2 : 0));
+        forced = e == nullptr ? 0 : (!strcmp(e, "m256") ? 1 : ((!strcmp(e, "p256") || !strcmp(e, "p192")) ? 2 : 0));
     }
     if (ranges != 1 || forced == 2) return 0;
     if (forced == 1) return 256;
@@ -593,9 +593,12 @@ static int tc_m256_cols(int M, int N, int K, int ranges) {
 // a quarter of the SMs or more idle and those of 192 fill nine tenths of them in one wave (536 rows x 2,560 x 9,728
 // in two ranges: 100 units or 140 on 148 SMs, 39.2 -> 36.2 us; x 4,096: 23.5 -> 21.7 us).  Elsewhere the narrower
 // tile measured no faster or slower (80 -> 110 units: 26.8 -> 29.5 us; two waves either way: 36.2 -> 37.1 us): per
-// flop it moves a ninth more through shared memory.  AIEN_B200_GEMM_TC=p256 | m256 pins 256.
+// flop it moves a ninth more through shared memory.  AIEN_B200_GEMM_TC=p256 | m256 pins 256, p192 pins 192.
 static int tc_p_cols(int M, int N, int ranges) {
-    if (const char* e = getenv("AIEN_B200_GEMM_TC")) { if (!strcmp(e, "p256") || !strcmp(e, "m256")) return 256; }
+    if (const char* e = getenv("AIEN_B200_GEMM_TC")) {
+        if (!strcmp(e, "p256") || !strcmp(e, "m256")) return 256;
+        if (!strcmp(e, "p192")) return 192;
+    }
     const long sms = tc_num_sms(), mt = (M + TC_BM - 1) / TC_BM;
     const long u256 = mt * ((N + 255) / 256) * ranges, u192 = mt * ((N + 191) / 192) * ranges;
     return (u256 * 4 <= sms * 3 && u192 <= sms && u192 * 10 >= sms * 9) ? 192 : 256;
