@@ -15,7 +15,8 @@
 // image of the floats, which needs no sort.  The nucleus bisects over the few tokens that can
 // belong to it, gathered in shared memory (tokens too light to matter are left out by a bound
 // that is exact); a flat distribution with more than 4,096 such tokens bisects over the row.
-// Masses are summed as integers, so no result depends on an order of summation.
+// Masses are summed as integers, so no result depends on an order of summation.  Temperature alone
+// (every token drawable) sums runs of consecutive tokens per thread and walks the run that holds the draw.
 // `probs` is scratch of V floats per row.
 #include "common.cuh"
 #include <cooperative_groups.h>
@@ -392,6 +393,64 @@ __device__ __forceinline__ void sample_row(const float* __restrict__ logits, int
             }
             C = cand_count;
             listed = C <= SM_CAND;
+        } else if (!use_k && !use_p) {
+            // Temperature alone: every token stays drawable, so the draw walks the whole row in id order.  Masses in
+            // integer units again: a thread sums a run of consecutive tokens of its rank's part, the runs are added up
+            // in order (and the ranks' parts through the cluster), the thread whose run holds the draw walks it.
+            const int run = (hi - lo + SM_THREADS - 1) / SM_THREADS;
+            const int a = min(hi, lo + tid * run), b = min(hi, a + run);
+            unsigned long long mine = 0;
+            for (int i = a; i < b; ++i) mine += prob_units(expf((row[i] - maxv) * inv_t0));
+            // exclusive sums over the threads: within the warp by shuffles, the warps' totals through shared memory
+            unsigned long long incl = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+                if ((tid & 31) >= o) incl += up;
+            }
+            unsigned long long* warp_tot = reinterpret_cast<unsigned long long*>(scan);
+            __syncthreads();
+            if ((tid & 31) == 31) warp_tot[tid >> 5] = incl;
+            __syncthreads();
+            unsigned long long before = 0, part = 0;
+            for (int w = 0; w < SM_THREADS / 32; ++w) {
+                if (w < (tid >> 5)) before += warp_tot[w];
+                part += warp_tot[w];
+            }
+            before += incl - mine;                                          // units of this rank's part before this thread's run
+            unsigned long long total = part, part_before = 0;
+            if (CL) {
+                cg::cluster_group cluster = cg::this_cluster();
+                if (tid == 0) cl.z = part;
+                cluster.sync();
+                total = 0;
+                for (int rk = 0; rk < SM_CLUSTER; ++rk) {
+                    const unsigned long long zr = cluster.map_shared_rank(&cl, rk)->z;
+                    if (rk < rank) part_before += zr;
+                    total += zr;
+                }
+                cluster.sync();                                             // everybody has read
+            }
+            if (total == 0) {                                               // cannot be (the largest token weighs 2^40 units); never leave the id unset
+                if (rank == 0 && tid == 0) { out_ids[r] = amax; if (out_logprob != nullptr) out_logprob[r] = 0.f; }
+                return;
+            }
+            unsigned long long rr = (unsigned long long)(u * (double)total);
+            if (rr >= total) rr = total - 1;
+            const unsigned long long first = part_before + before;          // this thread's run owns the units [first, first + mine)
+            if (rr >= first && rr < first + mine) {
+                unsigned long long cum = first;
+                for (int i = a; i < b; ++i) {
+                    const unsigned long long w = prob_units(expf((row[i] - maxv) * inv_t0));
+                    if (rr < cum + w) {
+                        out_ids[r] = i;
+                        if (out_logprob != nullptr) out_logprob[r] = (float)log((double)w / (double)total);
+                        break;
+                    }
+                    cum += w;
+                }
+            }
+            return;
         } else if (CL && rank != 0) {
             return;                                                         // no shared pass for these options
         }
