@@ -171,7 +171,7 @@ def serving_workload() -> int:
     rng = np.random.default_rng(3)
     lens = rng.integers(64, 4097, 32)
     prompts = [rng.integers(0, QWEN3_4B["vocab_size"], int(n)).tolist() for n in lens]
-    sp = SamplingParams(temperature=0.0, max_tokens=256, stop_token_ids=[])
+    sp = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k, seed=SEED, max_tokens=256, stop_token_ids=[])
 
     def job(first_id, timed):
         gen = Generator(engine)
@@ -279,6 +279,9 @@ def main() -> int:
                          "grows with it, and the points at batch 1 and 64 are left out")
     ap.add_argument("--prefill-tokens", type=int, default=0,
                     help="length of the prompt whose one-step prefill is timed (default 2,048); another length leaves out the points")
+    ap.add_argument("--temperature", type=float, default=0.0, help="sampling temperature of the end-to-end run (0: greedy)")
+    ap.add_argument("--top-p", type=float, default=1.0, help="nucleus of the end-to-end run")
+    ap.add_argument("--top-k", type=int, default=0, help="top-k of the end-to-end run")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
@@ -462,7 +465,7 @@ def main() -> int:
         # token ids and block tables go host->device from pinned memory, the chosen ids come back.
         gen = Generator(engine)
         prompts = [rng.integers(0, V, PROMPT_LEN).tolist() for _ in range(batch_main)]
-        sp = SamplingParams(temperature=0.0, max_tokens=4 * warmup + steps + 64, stop_token_ids=[])
+        sp = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k, seed=SEED, max_tokens=4 * warmup + steps + 64, stop_token_ids=[])
         for i, p in enumerate(prompts):
             gen.submit(5000 + i, p, sp)
         def all_decoding():
@@ -490,6 +493,7 @@ def main() -> int:
         for i in range(batch_main):
             gen.scheduler.cancel(5000 + i)
         e2e = {"value": round(new_tokens / dt, 1), "unit": "tokens/s", "steps": n_steps, "pause_after_prefill_s": SETTLE_S,
+               "sampling": {"temperature": args.temperature, "top_p": args.top_p, "top_k": args.top_k},
                "h2d_bytes_per_step": int((gen.h2d_bytes - h0) / n_steps), "d2h_bytes_per_step": int((gen.d2h_bytes - d0) / n_steps)}
 
     out = {
