@@ -66,17 +66,23 @@ def cmd_generate(args) -> int:
     engine = _build_engine(args)
     cap = args.max_tokens_cap or args.max_tokens
     sp = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k, max_tokens=min(args.max_tokens, cap),
-                        stop_token_ids=_ids(args.stop_token_ids) if args.stop_token_ids is not None else None, seed=args.seed)
+                        stop_token_ids=_ids(args.stop_token_ids) if args.stop_token_ids is not None else None, seed=args.seed,
+                        logprobs=args.logprobs)
     gen = Generator(engine)
     t0 = time.perf_counter()
     results = gen.generate(prompts, sp)
     dt = time.perf_counter() - t0
     if args.json:
-        print(json.dumps({"tokens": [r.tokens for r in results], "finish_reasons": [r.finish_reason for r in results],
-                          "seconds": round(dt, 4), "steps": gen.steps}))
+        out = {"tokens": [r.tokens for r in results], "finish_reasons": [r.finish_reason for r in results],
+               "seconds": round(dt, 4), "steps": gen.steps}
+        if args.logprobs:
+            out["logprobs"] = [r.logprobs for r in results]
+        print(json.dumps(out))
     else:
         for i, r in enumerate(results):
             print(f"[{i}] {r.finish_reason}: {' '.join(map(str, r.tokens))}")
+            if args.logprobs and r.logprobs is not None:
+                print(f"[{i}] logprobs: {' '.join(f'{v:.4f}' for v in r.logprobs)}")
         n = sum(len(r.tokens) for r in results)
         print(f"{n} tokens in {dt:.3f} s ({n / dt:.1f} tokens/s, {gen.steps} steps)", file=sys.stderr)
     return 0
@@ -118,6 +124,7 @@ def main(argv=None) -> int:
     g.add_argument("--top-k", type=int, default=0)
     g.add_argument("--seed", type=int, default=0)
     g.add_argument("--stop-token-ids", default=None, help="default: the model's end-of-sequence ids")
+    g.add_argument("--logprobs", action="store_true", help="the log-probability of every generated token with it")
     g.add_argument("--json", action="store_true")
     g.set_defaults(fn=cmd_generate)
     r = sub.add_parser("random-model", help="write config.json + model.safetensors with random weights")

@@ -165,11 +165,13 @@ def test_command_line(folders, tmp_path):
     prompt = H.tokens_for("A", 13, 3)
     want = plain_greedy(d, prompt, 6)
     cmd = [os.path.join(H.ROOT, "bin", "aien-b200"), "generate", "--model-dir", d, "--dtype", "float32", "--prompt-ids",
-           ",".join(map(str, prompt)), "--max-tokens", "6", "--temperature", "0", "--stop-token-ids", "", "--json"]
+           ",".join(map(str, prompt)), "--max-tokens", "6", "--temperature", "0", "--stop-token-ids", "", "--logprobs", "--json"]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stderr[-2000:]
     rec = json.loads(out.stdout.strip().splitlines()[-1])
     assert rec["tokens"] == [want]
+    # greedy: the log softmax at the maximum, one per token, never positive
+    assert len(rec["logprobs"]) == 1 and len(rec["logprobs"][0]) == 6 and all(-20.0 < v <= 0.0 for v in rec["logprobs"][0])
     bad = subprocess.run([cmd[0], "generate", "--model-dir", str(tmp_path), "--prompt-ids", "1"], capture_output=True, text=True, timeout=600)
     assert bad.returncode != 0 and "config.json" in bad.stderr
 
