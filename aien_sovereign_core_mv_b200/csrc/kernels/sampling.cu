@@ -754,9 +754,10 @@ static void launch_sample_rows(const float* logits, int R, int V, const float* t
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        cudaLaunchKernelEx(&cfg, sample_rows_cluster_kernel, logits, V, temperature, top_p, top_k, seeds, request_ids, positions,
-                           probs_scratch, out_ids, out_logprob);
-        return;
+        if (cudaLaunchKernelEx(&cfg, sample_rows_cluster_kernel, logits, V, temperature, top_p, top_k, seeds, request_ids, positions,
+                               probs_scratch, out_ids, out_logprob) == cudaSuccess)
+            return;
+        (void)cudaGetLastError();                      // a device that refuses the cluster: one CTA a row draws the same tokens
     }
     sample_rows_kernel<<<R, SM_THREADS, 0, stream>>>(logits, V, temperature, top_p, top_k, seeds, request_ids, positions,
                                                      probs_scratch, out_ids, out_logprob);
