@@ -24,6 +24,7 @@ class EngineConfig:
     prefill_chunk_size: int = 512
     chunk_prefill: bool = True
     watermark_blocks: int = 4
+    align_step_tokens: int = 0         # own option: cut a portion so that a step's tokens fill whole tiles of this many rows (0: off)
     # execution
     use_cuda_graphs: bool = True       # replay captured graphs for decode-only steps
     async_scheduling: bool = True      # plan and launch step n+1 while step n runs; its tokens are fed on the device

@@ -17,7 +17,7 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 Scheduler::Scheduler(SchedulerConfig cfg, CacheManager* cache) : cfg_(cfg), cache_(cache) {
     if (!cache_) throw std::invalid_argument("scheduler needs a cache manager");
     if (cfg_.max_batch_size <= 0 || cfg_.max_batch_tokens <= 0 || cfg_.max_prefill_tokens <= 0 ||
-        cfg_.prefill_chunk_size <= 0 || cfg_.watermark_blocks < 0)
+        cfg_.prefill_chunk_size <= 0 || cfg_.watermark_blocks < 0 || cfg_.align_step_tokens < 0)
         throw std::invalid_argument("scheduler limits must be positive");
 }
 
@@ -208,9 +208,10 @@ StepPlan Scheduler::plan() {
     }
 
     // 2. running requests in id order: one decode token, or the next portion of the input
-    struct Cand { int64_t id; int n; };
+    struct Cand { int64_t id; int n; int pending; };
     std::vector<Cand> cands;
     int seqs = 0, tokens = 0, prefill = 0;
+    int held_back = 0;               // tokens taken off a portion to fill whole tiles: nobody else gets them this step
     for (int64_t id : running_) {
         if (seqs >= cfg_.max_batch_size || tokens >= cfg_.max_batch_tokens) break;
         const SeqRecord& s = seqs_.at(id);
@@ -224,9 +225,22 @@ StepPlan Scheduler::plan() {
             if (n <= 0) continue;
             prefill += n;
         }
-        cands.push_back({id, n});
+        cands.push_back({id, n, pending});
         tokens += n;
         ++seqs;
+    }
+    // whole tiles: the last portion that is not the end of its input gives up what overhangs
+    if (cfg_.align_step_tokens > 1) {
+        for (auto it = cands.rbegin(); it != cands.rend(); ++it) {
+            if (it->n <= 1 || it->n >= it->pending) continue;
+            const int excess = tokens % cfg_.align_step_tokens;
+            if (excess > 0 && excess * 4 <= it->n) {
+                it->n -= excess;
+                tokens -= excess;
+                held_back += excess;
+            }
+            break;
+        }
     }
 
     // 3. take the pages; when they run out, preempt the lowest-priority running request and retry
@@ -271,9 +285,13 @@ StepPlan Scheduler::plan() {
             const int64_t id = q.front();
             SeqRecord& s = seqs_.at(id);
             const int pending = s.input_len();
-            const int budget = std::min(cfg_.max_prefill_tokens - prefill, cfg_.max_batch_tokens - tokens);
-            const int n = cfg_.chunk_prefill ? std::min({pending, cfg_.prefill_chunk_size, budget})
-                                             : (pending <= budget ? pending : 0);
+            const int budget = std::min(cfg_.max_prefill_tokens - prefill, cfg_.max_batch_tokens - tokens) - held_back;
+            int n = cfg_.chunk_prefill ? std::min({pending, cfg_.prefill_chunk_size, budget})
+                                       : (pending <= budget ? pending : 0);
+            if (cfg_.align_step_tokens > 1 && n > 1 && n < pending) {
+                const int excess = (tokens + n) % cfg_.align_step_tokens;
+                if (excess > 0 && excess * 4 <= n) { n -= excess; held_back += excess; }
+            }
             if (n <= 0) {
                 if (!cfg_.chunk_prefill && pending > std::min(cfg_.max_prefill_tokens, cfg_.max_batch_tokens)) {
                     q.pop_front();
@@ -456,7 +474,8 @@ void bind_scheduler(pybind11::module_& m) {
         .def_readwrite("prefill_chunk_size", &SchedulerConfig::prefill_chunk_size)
         .def_readwrite("chunk_prefill", &SchedulerConfig::chunk_prefill)
         .def_readwrite("watermark_blocks", &SchedulerConfig::watermark_blocks)
-        .def_readwrite("max_context", &SchedulerConfig::max_context);
+        .def_readwrite("max_context", &SchedulerConfig::max_context)
+        .def_readwrite("align_step_tokens", &SchedulerConfig::align_step_tokens);
     py::class_<StepEntry>(m, "StepEntry")
         .def_readonly("id", &StepEntry::id)
         .def_readonly("tokens", &StepEntry::tokens)

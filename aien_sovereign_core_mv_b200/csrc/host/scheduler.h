@@ -36,6 +36,10 @@ struct SchedulerConfig {
     bool chunk_prefill = true;
     int watermark_blocks = 4;
     int max_context = 0;        // 0: unlimited; else a request ends when it holds this many tokens
+    // Own option, off at 0: a step that holds a portion of a longer input is cut so that its tokens fill whole
+    // tiles of this many rows (the products work on 128 rows at a time: 536 rows cost what 640 do).  Only a
+    // portion that is not its input's last is cut, and by a quarter of its length at most.
+    int align_step_tokens = 0;
 };
 
 enum class SeqState : int { Waiting = 0, Running = 1, Preempted = 2, Finished = 3 };

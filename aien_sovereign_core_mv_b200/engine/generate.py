@@ -61,6 +61,7 @@ class Generator:
         sc.prefill_chunk_size = cfg.prefill_chunk_size
         sc.chunk_prefill = cfg.chunk_prefill
         sc.watermark_blocks = cfg.watermark_blocks
+        sc.align_step_tokens = cfg.align_step_tokens
         sc.max_context = engine.max_context
         self.scheduler = host.Scheduler(sc, engine.cache)
         self.params: Dict[int, SamplingParams] = {}

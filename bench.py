@@ -152,7 +152,7 @@ def _dist(ms):
             "mean_ms": round(sum(v) / len(v), 3)}
 
 
-def serving_workload() -> int:
+def serving_workload(align_step_tokens: int = 0) -> int:
     """Continuous batching through the public entry point: 32 requests with uniform-random prompt
     lengths in [64, 4096], prompts cut into portions under a 512-token budget, 256 greedy tokens
     each (Qwen3-4B shape, random bfloat16 weights, seed 3).  Wall-clock time of the whole job, and
@@ -166,12 +166,13 @@ def serving_workload() -> int:
     from aien_sovereign_core_mv_b200.engine.generate import Generator
     from aien_sovereign_core_mv_b200.sampling import SamplingParams
     ec = EngineConfig(dtype="bfloat16", page_size=16, max_cache_tokens=32 * 4400, max_requests=32, max_batch_tokens=1024,
-                      max_context=8192, max_batch_size=32, max_prefill_tokens=512, prefill_chunk_size=512)
+                      max_context=8192, max_batch_size=32, max_prefill_tokens=512, prefill_chunk_size=512,
+                      align_step_tokens=align_step_tokens)
     engine = Engine.from_config(QWEN3_4B, seed=3, engine_config=ec, init_std=0.02, device_init=True)
     rng = np.random.default_rng(3)
     lens = rng.integers(64, 4097, 32)
     prompts = [rng.integers(0, QWEN3_4B["vocab_size"], int(n)).tolist() for n in lens]
-    sp = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k, seed=SEED, max_tokens=256, stop_token_ids=[])
+    sp = SamplingParams(temperature=0.0, max_tokens=256, stop_token_ids=[])
 
     def job(first_id, timed):
         gen = Generator(engine)
@@ -212,7 +213,7 @@ def serving_workload() -> int:
         "clocks": clocks, "wait_errors": int(wait_errors),
         "config": {"model": "Qwen3-4B shape, random weights", "layers": 36, "hidden": 2560, "heads": 32, "kv_heads": 8, "head_dim": 128,
                    "intermediate": 9728, "vocab": 151936, "requests": 32, "prompt_len": "uniform 64..4096",
-                   "prefill_budget": 512, "new_tokens": 256, "context": 8192, "page_size": 16, "seed": 3,
+                   "prefill_budget": 512, "align_step_tokens": align_step_tokens, "new_tokens": 256, "context": 8192, "page_size": 16, "seed": 3,
                    "timing": "second run of the job; the first, untimed, meets every step shape once"},
     }))
     return 0
@@ -282,6 +283,8 @@ def main() -> int:
     ap.add_argument("--temperature", type=float, default=0.0, help="sampling temperature of the end-to-end run (0: greedy)")
     ap.add_argument("--top-p", type=float, default=1.0, help="nucleus of the end-to-end run")
     ap.add_argument("--top-k", type=int, default=0, help="top-k of the end-to-end run")
+    ap.add_argument("--align-step-tokens", type=int, default=0,
+                    help="serving workload: the scheduler cuts portions so that a step's tokens fill whole tiles of this many rows")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
@@ -304,7 +307,7 @@ def main() -> int:
         return 2
     warmup, steps = max(3, args.warmup), max(1, args.steps)
     if args.workload == "serving":
-        return serving_workload()
+        return serving_workload(args.align_step_tokens)
     if args.workload == "mixed_step":
         return mixed_step_workload()
 

@@ -328,3 +328,34 @@ def test_a_value_of_an_earlier_submission_never_reaches_a_new_request_with_the_s
     s.take_finished()
     done = drive(s, cm)
     assert done[5][0] == expected(5, 7, 8)
+
+
+def test_steps_cut_to_whole_tiles():
+    """align_step_tokens: a portion that is not its input's last gives up what overhangs the last whole tile
+    of the step (a quarter of itself at most); the end of an input and plain decode steps are left alone,
+    nobody else is given the tokens held back, and the requests produce what they produce without it."""
+    def run(align):
+        cm, s = make(pages=256, max_batch_tokens=64, max_prefill_tokens=32, prefill_chunk_size=32, align_step_tokens=align)
+        s.submit(1, list(range(6)), 12)              # decoding from the second step on
+        s.submit(2, list(range(7)), 12)
+        s.submit(3, list(range(100)), 4)             # the long input: portions of 32 beside two decode tokens
+        s.submit(4, list(range(50)), 4)              # waits for prefill room
+        log = []
+        done = drive(s, cm, log=log)
+        return log, done
+    plain_log, plain_done = run(0)
+    log, done = run(16)
+    assert done == plain_done and set(done) == {1, 2, 3, 4}
+    # without the option some step holds 32 + 2 = 34 tokens
+    assert any(p.num_tokens == 34 for p in plain_log)
+    for p in log:
+        sizes = {e.id: len(e.tokens) for e in p.entries}
+        longest = max(sizes.values())
+        ends = any(e.wants_logits and len(e.tokens) > 1 for e in p.entries)
+        if longest > 1 and not ends and longest >= 4 * (p.num_tokens % 16 or 16):
+            assert p.num_tokens % 16 == 0, (p.num_tokens, sizes)
+        assert p.num_tokens <= 64 and p.prefill_tokens <= 32
+    # the portion beside the two decoding requests: 30 tokens, not 32
+    assert any({1, 2, 3} <= {e.id for e in p.entries} and p.num_tokens == 32 and max(len(e.tokens) for e in p.entries) == 30 for p in log)
+    with pytest.raises(Exception):
+        make(align_step_tokens=-1)
