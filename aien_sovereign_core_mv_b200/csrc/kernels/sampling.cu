@@ -14,7 +14,9 @@
 // walked in token-id order.  Thresholds are found by bisection on an order-preserving integer
 // image of the floats, which needs no sort.  The nucleus bisects over the few tokens that can
 // belong to it, gathered in shared memory (tokens too light to matter are left out by a bound
-// that is exact); a flat distribution with more than 4,096 such tokens bisects over the row.
+// that is exact); a flat distribution with more than 4,096 such tokens bisects over the row (pass by pass
+// in one CTA; in a cluster with every thread's tokens in registers).  The draw walks the kept tokens in id
+// order with integer masses: a thread sums a run of consecutive tokens, the runs are added up in order.
 // Masses are summed as integers, so no result depends on an order of summation.  Temperature alone
 // (every token drawable) sums runs of consecutive tokens per thread and walks the run that holds the draw.
 // `probs` is scratch of V floats per row.
@@ -184,40 +186,194 @@ __device__ __forceinline__ unsigned long long prob_units(float e) { return __flo
 
 constexpr int SM_CAND = 4096;
 
+// Exclusive sums over the block of one value per thread, in thread order (within a warp by shuffles, the
+// warps' totals through `wt`, 32 values of shared memory); *block_total receives the sum.
+__device__ __forceinline__ unsigned long long block_exclusive_u64(unsigned long long mine, unsigned long long* wt,
+                                                                  unsigned long long* block_total) {
+    const int tid = threadIdx.x;
+    unsigned long long incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+        if ((tid & 31) >= o) incl += up;
+    }
+    __syncthreads();
+    if ((tid & 31) == 31) wt[tid >> 5] = incl;
+    __syncthreads();
+    unsigned long long before = 0, all = 0;
+    for (int w = 0; w < SM_THREADS / 32; ++w) {
+        if (w < (tid >> 5)) before += wt[w];
+        all += wt[w];
+    }
+    *block_total = all;
+    return before + incl - mine;
+}
+
+// Two sums over the ranks of a cluster, of values that every thread of a rank holds alike, and the sum of
+// v0 over the ranks before this one.  `xs`: two pairs of shared memory per rank, used in turn (`it` counts the
+// exchanges), so that one cluster barrier per exchange is enough: a rank can write a pair again only after the
+// barrier of the exchange between, which every rank reaches after it has read that pair.  ACROSS false: one rank alone.
+template <bool ACROSS>
+__device__ __forceinline__ void cluster_sums(unsigned long long v0, unsigned long long v1, unsigned long long (*xs)[2], int& it, int rank,
+                                             unsigned long long* t0, unsigned long long* t1, unsigned long long* before0) {
+    if (!ACROSS) { *t0 = v0; *t1 = v1; *before0 = 0; return; }
+    cg::cluster_group cluster = cg::this_cluster();
+    const int slot = it & 1;
+    ++it;
+    if (threadIdx.x == 0) { xs[slot][0] = v0; xs[slot][1] = v1; }
+    cluster.sync();
+    unsigned long long a0 = 0, a1 = 0, b0 = 0;
+    for (int rk = 0; rk < SM_CLUSTER; ++rk) {
+        const unsigned long long* o = cluster.map_shared_rank(&xs[slot][0], rk);
+        const unsigned long long x0 = o[0], x1 = o[1];
+        if (rk < rank) b0 += x0;
+        a0 += x0; a1 += x1;
+    }
+    *t0 = a0; *t1 = a1; *before0 = b0;
+}
+
+// The draw among the tokens lo <= i < hi of this rank (and of the other ranks' parts when ACROSS), in id order,
+// masses in integer units: units_of(i) is what token i weighs (0: not kept).  A thread sums a run of consecutive
+// tokens, the runs are added up in order, the thread whose run holds the draw walks it.  Every thread calls this.
+template <bool ACROSS, typename UnitsOf>
+__device__ __forceinline__ void draw_by_runs(int lo, int hi, double u, UnitsOf units_of, unsigned long long* wt,
+                                             unsigned long long (*xs)[2], int& it, int rank, int r, int fallback_id,
+                                             int* __restrict__ out_ids, float* __restrict__ out_logprob) {
+    const int tid = threadIdx.x;
+    const int run = (hi - lo + SM_THREADS - 1) / SM_THREADS;
+    const int a = min(hi, lo + tid * run), b = min(hi, a + run);
+    unsigned long long mine = 0;
+    for (int i = a; i < b; ++i) mine += units_of(i);
+    unsigned long long part = 0, total = 0, unused = 0, part_before = 0;
+    const unsigned long long before = block_exclusive_u64(mine, wt, &part);
+    cluster_sums<ACROSS>(part, 0ull, xs, it, rank, &total, &unused, &part_before);
+    if (total == 0) {                                   // nothing kept weighs a unit: cannot be, but never leave the id unset
+        if (rank == 0 && tid == 0) { out_ids[r] = fallback_id; if (out_logprob != nullptr) out_logprob[r] = 0.f; }
+        return;
+    }
+    unsigned long long rr = (unsigned long long)(u * (double)total);
+    if (rr >= total) rr = total - 1;
+    const unsigned long long first = part_before + before;          // this thread's run owns the units [first, first + mine)
+    if (rr >= first && rr < first + mine) {
+        unsigned long long cum = first;
+        for (int i = a; i < b; ++i) {
+            const unsigned long long w = units_of(i);
+            if (rr < cum + w) {
+                out_ids[r] = i;
+                if (out_logprob != nullptr) out_logprob[r] = (float)log((double)w / (double)total);   // within the kept set
+                break;
+            }
+            cum += w;
+        }
+    }
+}
+
+// The nucleus of a row whose tokens that can matter do not fit in shared memory (a flat distribution), by all
+// ranks of the cluster: a thread keeps the probabilities of its run of consecutive tokens in registers, the
+// bisection for the threshold adds the masses over block and cluster (integers: no order), ties at the threshold
+// go to the lower ids, and the draw walks the kept tokens in id order (draw_by_runs).  The same threshold, the
+// same kept set and the same token as the pass-by-pass way of one CTA.  Needs runs of SM_RUN_MAX tokens at most.
+constexpr int SM_RUN_MAX = 20;
+__device__ __forceinline__ void nucleus_across_cluster(const float* __restrict__ row, int lo, int hi, int V, float maxv, float inv_t,
+                                                       float tp, unsigned long long z, double u, unsigned long long* wt, double* red,
+                                                       unsigned long long (*xs)[2], int& it, int rank, int r, int fallback_id,
+                                                       int* __restrict__ out_ids, float* __restrict__ out_logprob) {
+    const int tid = threadIdx.x;
+    const int run = (hi - lo + SM_THREADS - 1) / SM_THREADS;
+    const int a = min(hi, lo + tid * run), b = min(hi, a + run);
+    uint32_t eb[SM_RUN_MAX];
+#pragma unroll
+    for (int j = 0; j < SM_RUN_MAX; ++j) eb[j] = (a + j < b) ? __float_as_uint(expf((row[a + j] - maxv) * inv_t)) : 0u;
+    unsigned long long target = (unsigned long long)ceil((double)tp * (double)z);
+    if (target > z) target = z;
+    if (target < 1) target = 1;
+    unsigned long long t0 = 0, t1 = 0, before = 0;
+    uint32_t prefix = 0;
+    for (int bit = 30; bit >= 0; --bit) {                                   // bit 31 is the sign: never set
+        const uint32_t cand = prefix | (1u << bit);
+        unsigned long long m = 0;
+#pragma unroll
+        for (int j = 0; j < SM_RUN_MAX; ++j) m += eb[j] >= cand ? prob_units(__uint_as_float(eb[j])) : 0ull;
+        m = block_sum_u64(m, red);
+        cluster_sums<true>(m, 0ull, xs, it, rank, &t0, &t1, &before);
+        if (t0 >= target) prefix = cand;
+    }
+    if (prefix == 0) prefix = 1;
+    unsigned long long m_gt = 0, n_eq = 0;
+#pragma unroll
+    for (int j = 0; j < SM_RUN_MAX; ++j) {
+        if (eb[j] > prefix) m_gt += prob_units(__uint_as_float(eb[j]));
+        else if (eb[j] == prefix) n_eq += 1;
+    }
+    const unsigned long long mine_eq = n_eq;
+    m_gt = block_sum_u64(m_gt, red);
+    n_eq = block_sum_u64(n_eq, red);
+    cluster_sums<true>(m_gt, n_eq, xs, it, rank, &t0, &t1, &before);
+    m_gt = t0; n_eq = t1;
+    const unsigned long long q_thr = prob_units(__uint_as_float(prefix));
+    unsigned long long need = 1;
+    if (q_thr > 0 && target > m_gt) need = (target - m_gt + q_thr - 1) / q_thr;
+    if (need > n_eq) need = n_eq;
+    if (need < 1) need = 1;
+    int cut = V - 1;
+    if (need < n_eq) {                                                      // ties at the threshold: the lower ids
+        unsigned long long part = 0, part_before = 0;
+        const unsigned long long first = block_exclusive_u64(mine_eq, wt, &part);
+        cluster_sums<true>(part, 0ull, xs, it, rank, &t0, &t1, &part_before);
+        const unsigned long long mine_first = part_before + first;         // ties before this thread's run
+        unsigned long long found = 0;                                      // id + 1 of the need-th tie, in the one thread that holds it
+        if (mine_first < need && need <= mine_first + mine_eq) {
+            unsigned long long seen = mine_first;
+#pragma unroll
+            for (int j = 0; j < SM_RUN_MAX; ++j)
+                if (eb[j] == prefix && ++seen == need) found = (unsigned long long)(a + j) + 1;
+        }
+        found = block_sum_u64(found, red);
+        cluster_sums<true>(found, 0ull, xs, it, rank, &t0, &t1, &before);
+        if (t0 > 0) cut = (int)(t0 - 1);
+    }
+    const uint32_t thr = prefix;
+    draw_by_runs<true>(lo, hi, u, [&](int i) {
+        const float e = expf((row[i] - maxv) * inv_t);
+        const uint32_t bits = __float_as_uint(e);
+        return (e > 0.f && (bits > thr || (bits == thr && i <= cut))) ? prob_units(e) : 0ull;
+    }, wt, xs, it, rank, r, fallback_id, out_ids, out_logprob);
+    cg::this_cluster().sync();                                              // nobody leaves while its pairs may still be read
+}
+
 // The candidate lists of a cluster's ranks put together in rank 0 (in no particular order: what is made of
 // them are sets and integer sums), with the sum of the ranks' masses in *z when z is given.  A rank's count
 // may exceed SM_CAND (its list is then cut short): the total does too and the caller takes another way.
-// Returns false in the ranks that are done (all but rank 0); every thread of every rank calls this.
-__device__ __forceinline__ bool collect_candidates(SmClusterSlot& cl, uint32_t* cand_bits, int* cand_id, int* cand_count,
-                                                   unsigned long long* z, int rank) {
+// Returns the total (SM_CAND + 1 at most) to every rank; every thread of every rank calls this.
+__device__ __forceinline__ int collect_candidates(SmClusterSlot& cl, uint32_t* cand_bits, int* cand_id, int* cand_count,
+                                                  unsigned long long* z, int rank) {
     cg::cluster_group cluster = cg::this_cluster();
     const int tid = threadIdx.x;
     if (tid == 0) { cl.count = min(*cand_count, SM_CAND + 1); cl.z = z ? *z : 0ull; }
     cluster.sync();
-    if (rank == 0) {
-        int total = cl.count;
-        unsigned long long zsum = cl.z;
-        bool fits = total <= SM_CAND;
-        for (int rk = 1; rk < SM_CLUSTER; ++rk) {
-            const SmClusterSlot* o = cluster.map_shared_rank(&cl, rk);
-            const int n = o->count;
-            zsum += o->z;
-            if (fits && total + n <= SM_CAND) {
-                const uint32_t* rb = cluster.map_shared_rank(cand_bits, rk);
-                const int* ri = cluster.map_shared_rank(cand_id, rk);
-                for (int j = tid; j < n; j += blockDim.x) { cand_bits[total + j] = rb[j]; cand_id[total + j] = ri[j]; }
-            } else {
-                fits = false;
-            }
-            total = min(total + n, SM_CAND + 1);
+    int total = 0;
+    unsigned long long zsum = 0;
+    bool fits = true;
+    for (int rk = 0; rk < SM_CLUSTER; ++rk) {                        // rank 0's own list stays where it is, the others follow it
+        const SmClusterSlot* o = cluster.map_shared_rank(&cl, rk);
+        const int n = o->count;
+        zsum += o->z;
+        if (total + n > SM_CAND) fits = false;
+        if (rank == 0 && rk > 0 && fits) {
+            const uint32_t* rb = cluster.map_shared_rank(cand_bits, rk);
+            const int* ri = cluster.map_shared_rank(cand_id, rk);
+            for (int j = tid; j < n; j += blockDim.x) { cand_bits[total + j] = rb[j]; cand_id[total + j] = ri[j]; }
         }
+        total = min(total + n, SM_CAND + 1);
+    }
+    if (rank == 0) {
         __syncthreads();
         if (tid == 0) *cand_count = total;
-        if (z) *z = zsum;
         __syncthreads();
     }
+    if (z) *z = zsum;
     cluster.sync();                                    // rank 0 has read the others' lists
-    return rank == 0;
+    return total;
 }
 
 // One row.  CL: the CTA is rank `rank` of a cluster of SM_CLUSTER that shares the row; ranks other than 0
@@ -239,6 +395,8 @@ __device__ __forceinline__ void sample_row(const float* __restrict__ logits, int
     __shared__ int s_tie;
     __shared__ long long s_count;
     __shared__ unsigned long long s_total;
+    __shared__ unsigned long long cl_x[2][2];       // pairs the ranks of a cluster exchange (cluster_sums)
+    int cl_it = 0;
     const int tid = threadIdx.x;
     const float* row = logits + (size_t)r * V;
     // this rank's part of the row in the shared passes
@@ -340,7 +498,8 @@ __device__ __forceinline__ void sample_row(const float* __restrict__ logits, int
                 });
                 __syncthreads();
                 if (CL) {
-                    if (!collect_candidates(cl, cand_bits, cand_id, &cand_count, nullptr, rank)) return;
+                    collect_candidates(cl, cand_bits, cand_id, &cand_count, nullptr, rank);      // at most `cum`: it fits
+                    if (rank != 0) return;
                 }
                 C = cand_count;
             } else if (CL && rank != 0) {
@@ -389,7 +548,14 @@ __device__ __forceinline__ void sample_row(const float* __restrict__ logits, int
             });
             z0 = block_sum_u64(z0, red);
             if (CL) {
-                if (!collect_candidates(cl, cand_bits, cand_id, &cand_count, &z0, rank)) return;
+                const int all = collect_candidates(cl, cand_bits, cand_id, &cand_count, &z0, rank);
+                if (all > SM_CAND && (hi - lo + SM_THREADS - 1) / SM_THREADS <= SM_RUN_MAX) {
+                    // too many for shared memory (a flat distribution): every rank keeps its part of the row in registers
+                    nucleus_across_cluster(row, lo, hi, V, maxv, inv_t0, tp0, z0, u, reinterpret_cast<unsigned long long*>(scan), red,
+                                           cl_x, cl_it, rank, r, amax, out_ids, out_logprob);
+                    return;
+                }
+                if (rank != 0) return;
             }
             C = cand_count;
             listed = C <= SM_CAND;
@@ -397,59 +563,9 @@ __device__ __forceinline__ void sample_row(const float* __restrict__ logits, int
             // Temperature alone: every token stays drawable, so the draw walks the whole row in id order.  Masses in
             // integer units again: a thread sums a run of consecutive tokens of its rank's part, the runs are added up
             // in order (and the ranks' parts through the cluster), the thread whose run holds the draw walks it.
-            const int run = (hi - lo + SM_THREADS - 1) / SM_THREADS;
-            const int a = min(hi, lo + tid * run), b = min(hi, a + run);
-            unsigned long long mine = 0;
-            for (int i = a; i < b; ++i) mine += prob_units(expf((row[i] - maxv) * inv_t0));
-            // exclusive sums over the threads: within the warp by shuffles, the warps' totals through shared memory
-            unsigned long long incl = mine;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
-                if ((tid & 31) >= o) incl += up;
-            }
-            unsigned long long* warp_tot = reinterpret_cast<unsigned long long*>(scan);
-            __syncthreads();
-            if ((tid & 31) == 31) warp_tot[tid >> 5] = incl;
-            __syncthreads();
-            unsigned long long before = 0, part = 0;
-            for (int w = 0; w < SM_THREADS / 32; ++w) {
-                if (w < (tid >> 5)) before += warp_tot[w];
-                part += warp_tot[w];
-            }
-            before += incl - mine;                                          // units of this rank's part before this thread's run
-            unsigned long long total = part, part_before = 0;
-            if (CL) {
-                cg::cluster_group cluster = cg::this_cluster();
-                if (tid == 0) cl.z = part;
-                cluster.sync();
-                total = 0;
-                for (int rk = 0; rk < SM_CLUSTER; ++rk) {
-                    const unsigned long long zr = cluster.map_shared_rank(&cl, rk)->z;
-                    if (rk < rank) part_before += zr;
-                    total += zr;
-                }
-                cluster.sync();                                             // everybody has read
-            }
-            if (total == 0) {                                               // cannot be (the largest token weighs 2^40 units); never leave the id unset
-                if (rank == 0 && tid == 0) { out_ids[r] = amax; if (out_logprob != nullptr) out_logprob[r] = 0.f; }
-                return;
-            }
-            unsigned long long rr = (unsigned long long)(u * (double)total);
-            if (rr >= total) rr = total - 1;
-            const unsigned long long first = part_before + before;          // this thread's run owns the units [first, first + mine)
-            if (rr >= first && rr < first + mine) {
-                unsigned long long cum = first;
-                for (int i = a; i < b; ++i) {
-                    const unsigned long long w = prob_units(expf((row[i] - maxv) * inv_t0));
-                    if (rr < cum + w) {
-                        out_ids[r] = i;
-                        if (out_logprob != nullptr) out_logprob[r] = (float)log((double)w / (double)total);
-                        break;
-                    }
-                    cum += w;
-                }
-            }
+            draw_by_runs<CL>(lo, hi, u, [&](int i) { return prob_units(expf((row[i] - maxv) * inv_t0)); },
+                             reinterpret_cast<unsigned long long*>(scan), cl_x, cl_it, rank, r, amax, out_ids, out_logprob);
+            if (CL) cg::this_cluster().sync();                              // nobody leaves while its pairs may still be read
             return;
         } else if (CL && rank != 0) {
             return;                                                         // no shared pass for these options
@@ -619,95 +735,14 @@ __device__ __forceinline__ void sample_row(const float* __restrict__ logits, int
             cut_p = id_cutoff(probs, V, need, [&](int, float e) { return __float_as_uint(e) == tpk && e > 0.f; }, run_count, &cut_result);
     }
 
-    // ---- draw: walk the kept set in id order.  A warp owns a contiguous region of the row and goes
-    // through it in pieces of 128 tokens (four per lane, neighbours in neighbouring lanes), keeping
-    // the kept mass before each piece; pass one gives every region's mass, pass two (the warp whose
-    // region holds the draw) finds the piece, the lane and the token.  Both passes add in the same order.
-    auto kept = [&](int i, float e) {
-        const uint32_t b = __float_as_uint(e);
-        return e > 0.f && (b > thr_p || (b == thr_p && i <= cut_p));
-    };
-    const int lane = tid & 31, warp = tid >> 5;
-    constexpr int NW = SM_THREADS / 32;
-    const int region = (((V + NW - 1) / NW) + 127) & ~127;
-    const int wlo = min(V, warp * region), whi = min(V, wlo + region);
-    __shared__ int s_pick, s_last_kept;
-    if (tid == 0) { s_pick = -1; s_last_kept = -1; }
-    // one piece: this lane's four values and their kept sum; then the inclusive sums over the lanes
-    auto piece = [&](int c, float e4[4], double& mine) {
-        mine = 0.0;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const int i = c + lane * 4 + q;
-            e4[q] = i < whi ? probs[i] : 0.f;
-            if (i < whi && kept(i, e4[q])) mine += (double)e4[q]; else e4[q] = 0.f;
-        }
-        double incl = mine;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const double up = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += up;
-        }
-        return incl;
-    };
-    double region_mass = 0.0;
-    int my_last = -1;
-    for (int c = wlo; c < whi; c += 128) {
-        float e4[4]; double mine;
-        const double incl = piece(c, e4, mine);
-        region_mass += __shfl_sync(0xffffffffu, incl, 31);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) if (e4[q] > 0.f) my_last = c + lane * 4 + q;
-    }
-    __syncthreads();
-    if (lane == 0) red[warp] = region_mass;
-    if (my_last >= 0) atomicMax(&s_last_kept, my_last);
-    __syncthreads();
-    double before = 0.0, total = 0.0;
-    for (int w = 0; w < NW; ++w) {
-        if (w < warp) before += red[w];
-        total += red[w];
-    }
-    const double rr = u * total;
-    if (rr >= before && rr < before + region_mass) {                    // warp-uniform: this region holds the draw
-        double base = before;
-        bool found = false;
-        for (int c = wlo; c < whi; c += 128) {
-            float e4[4]; double mine;
-            const double incl = piece(c, e4, mine);
-            const double piece_mass = __shfl_sync(0xffffffffu, incl, 31);
-            const unsigned hit = __ballot_sync(0xffffffffu, rr < base + incl);
-            if (hit != 0u) {
-                if (lane == __ffs(hit) - 1) {
-                    double cum = base + incl - mine;
-                    int pick = -1, last = -1;
-#pragma unroll
-                    for (int q = 0; q < 4; ++q)
-                        if (e4[q] > 0.f) {
-                            cum += (double)e4[q];
-                            last = c + lane * 4 + q;
-                            if (pick < 0 && rr < cum) pick = last;
-                        }
-                    s_pick = pick >= 0 ? pick : last;
-                }
-                found = true;
-                break;
-            }
-            base += piece_mass;
-        }
-        if (!found) {                                                    // the pieces added up a rounding short: the region's last kept token
-            int wl = my_last;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) wl = max(wl, __shfl_xor_sync(0xffffffffu, wl, o));
-            if (lane == 0) s_pick = wl;
-        }
-    }
-    __syncthreads();
-    // rounding may leave the draw at or beyond the last region's end: the last kept token
-    if (tid == 0) {
-        const int pick = s_pick >= 0 ? s_pick : (s_last_kept >= 0 ? s_last_kept : amax);
-        out_ids[r] = pick;
-        if (out_logprob != nullptr) out_logprob[r] = total > 0.0 ? (float)log(fmax((double)probs[pick], 1e-300) / total) : 0.f;
+    // ---- draw: the kept set in id order, masses in integer units (this CTA alone, over the whole row)
+    {
+        const uint32_t tp_thr = thr_p; const int tp_cut = cut_p;
+        draw_by_runs<false>(0, V, u, [&](int i) {
+            const float e = probs[i];
+            const uint32_t b = __float_as_uint(e);
+            return (e > 0.f && (b > tp_thr || (b == tp_thr && i <= tp_cut))) ? prob_units(e) : 0ull;
+        }, reinterpret_cast<unsigned long long*>(scan), cl_x, cl_it, 0, r, amax, out_ids, out_logprob);
     }
 }
 
